@@ -1,0 +1,73 @@
+"""ctypes binding of ``libcleave_b200.so`` (declared in ``include/cleave_b200.h``).
+
+There is no fallback: if the shared library is missing or a launch fails, the call raises.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libcleave_b200.so")
+
+F16, BF16 = 0, 1
+OK = 0
+ERR_DEVICE_TIMEOUT = 6
+
+
+class Cb200Error(RuntimeError):
+    """A C-ABI call returned a non-zero ``cb200_status``."""
+
+    def __init__(self, status: int, message: str):
+        super().__init__(f"cleave_b200: status {status}: {message}")
+        self.status = status
+
+
+class AttnDecodeArgs(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("k_cache", C.c_void_p), ("v_cache", C.c_void_p),
+        ("kv_indptr", C.c_void_p), ("kv_indices", C.c_void_p), ("kv_last_page_len", C.c_void_p),
+        ("out", C.c_void_p), ("lse", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("batch", C.c_int32), ("num_qo_heads", C.c_int32), ("num_kv_heads", C.c_int32),
+        ("head_dim", C.c_int32), ("page_size", C.c_int32), ("num_pages", C.c_int32),
+        ("num_kv_indices", C.c_int32), ("kv_len", C.c_int32), ("q_rows", C.c_int32),
+        ("dtype", C.c_int32), ("max_ctas", C.c_int32), ("sm_scale", C.c_float),
+    ]
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    """The loaded library; raises if it has not been built (``python -c 'import __graft_entry__ as g; g.build()'``)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(
+                f"{LIB_PATH} is missing: build it with cleave_b200/csrc/build.sh "
+                "(there is no CPU or PyTorch fallback)")
+        L = C.CDLL(LIB_PATH)
+        L.cb200_version.restype = C.c_int
+        L.cb200_strerror.restype = C.c_char_p
+        L.cb200_strerror.argtypes = [C.c_int]
+        L.cb200_last_cuda_error.restype = C.c_int
+        L.cb200_sm_count.restype = C.c_int
+        L.cb200_workspace_status.restype = C.c_int
+        L.cb200_workspace_status.argtypes = [C.c_void_p, C.c_void_p]
+        L.cb200_attn_decode_workspace_bytes.restype = C.c_size_t
+        L.cb200_attn_decode_workspace_bytes.argtypes = [C.POINTER(AttnDecodeArgs)]
+        L.cb200_attn_decode.restype = C.c_int
+        L.cb200_attn_decode.argtypes = [C.POINTER(AttnDecodeArgs), C.c_void_p]
+        _lib = L
+    return _lib
+
+
+def check(status: int) -> None:
+    if status != OK:
+        L = lib()
+        msg = L.cb200_strerror(status).decode()
+        if status == 5:
+            msg += f" [cuda error {L.cb200_last_cuda_error()}]"
+        raise Cb200Error(status, msg)

@@ -1,0 +1,674 @@
+// Decode attention (MHA / GQA / MQA; contiguous or paged KV) for sm_100a.
+//
+// One persistent launch, one CTA per SM. The KV cache is cut into tiles of 64 tokens; the tiles of
+// all (request, kv head) items form one stream that is split evenly over the CTAs, so a CTA's
+// share may start or end in the middle of an item. A producer warp streams its share of tiles
+// into a ring of shared-memory stages (TMA tiled loads with the 128-byte swizzle when a tile maps
+// to whole boxes of the cache; otherwise one untiled bulk copy per gathered token row) and the
+// consumer warps run QK^T and PV on m16n8k16 tensor-core MMAs with a warp-shuffle online softmax
+// in the exp2 domain. An item finished inside one CTA is written directly; an item cut across
+// CTAs leaves fp32 partials (O, m, l) in the workspace and the last CTA to arrive does the
+// log-sum-exp combine (no second launch, nobody waits).
+//
+// Semantics follow python/cleave/dynamic/reference.py:143-200 of the reference (paged) and
+// demo/attention.py:5-8 (static); the valid-length clamp follows
+// python/cleave/dynamic/paging/builders/slab.py:132-142.
+
+#include "common.cuh"
+
+#include <cstring>
+
+namespace cb200 {
+
+constexpr int kTile = 64;          // tokens per KV tile
+constexpr int kRowsMax = 16;       // query rows one item carries (M of the MMA tile)
+constexpr int kConsumerWarps = 4;  // each owns 16 tokens of every tile
+constexpr float kLog2e = 1.4426950408889634f;
+
+struct DecodeParams {
+  const void* q;
+  const void* k;
+  const void* v;
+  const int* kv_indptr;
+  const int* kv_indices;
+  const int* kv_last;
+  void* out;
+  float* lse;
+  int* status;     // workspace header
+  int* counters;   // one arrival counter per item, zero between launches
+  float* partials; // gridDim.x * 2 slots
+  int batch, hkv, vblk, rows, page_size, num_pages, n_idx, kv_len, paged, box_tok;
+  float scale_log2;
+};
+
+template <int D, bool GATHER>
+struct SmemPlan {
+  static constexpr int kRowBytes = GATHER ? D * 2 + 16 : 128;  // padded row / swizzled 128-byte row
+  static constexpr int kMatBytes = GATHER ? kTile * kRowBytes : kTile * D * 2;
+  static constexpr int kStageBytes = 2 * kMatBytes;
+  static constexpr int kStages = GATHER ? 4 : 5;
+  static constexpr int kMergeFloats = kRowsMax * D + 2 * kRowsMax;
+  static constexpr int kMergeBytes = kConsumerWarps * kMergeFloats * 4;
+  static constexpr int kFixedBytes = kStages * kStageBytes + kMergeBytes + 256;  // + barriers/flags
+};
+
+__device__ __forceinline__ int item_valid_len(const DecodeParams& p, int b) {
+  if (!p.paged) return p.kv_len;
+  const int n_pages = p.kv_indptr[b + 1] - p.kv_indptr[b];
+  if (p.page_size == 1 || p.kv_last == nullptr) return max(n_pages, 0) * p.page_size;
+  const int v = max(n_pages - 1, 0) * p.page_size + max(p.kv_last[b], 0);
+  return max(min(v, n_pages * p.page_size), 0);
+}
+
+// The walk over a CTA's share of the tile stream; identical in the producer and the consumers.
+struct Piece {
+  int b, hv, tile0, count, n_tiles, unit0;  // unit0: stream position of the item's first tile
+};
+
+struct Walker {
+  const int* P;  // tile prefix per request (paged) or nullptr
+  int batch, hkvv, tiles_per_req;
+  __device__ __forceinline__ Piece at(int u, int u_end) const {
+    Piece pc;
+    int base;
+    if (P) {
+      const int key = u / hkvv;
+      int lo = 0, hi = batch;  // largest b with P[b] <= key
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (P[mid] <= key) lo = mid; else hi = mid;
+      }
+      pc.b = lo;
+      pc.n_tiles = P[lo + 1] - P[lo];
+      base = hkvv * P[lo];
+    } else {
+      pc.n_tiles = tiles_per_req;
+      pc.b = u / (hkvv * tiles_per_req);
+      base = pc.b * hkvv * tiles_per_req;
+    }
+    const int r = u - base;
+    pc.hv = r / pc.n_tiles;
+    pc.tile0 = r - pc.hv * pc.n_tiles;
+    pc.count = min(pc.n_tiles - pc.tile0, u_end - u);
+    pc.unit0 = base + pc.hv * pc.n_tiles;
+    return pc;
+  }
+};
+
+template <typename T, int D, bool GATHER>
+__global__ void __launch_bounds__((kConsumerWarps + 1) * 32, 1)
+decode_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                   const DecodeParams p) {
+  using Plan = SmemPlan<D, GATHER>;
+  constexpr int kStages = Plan::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* stages = smem;
+  float* merge = reinterpret_cast<float*>(smem + kStages * Plan::kStageBytes);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kStages * Plan::kStageBytes + Plan::kMergeBytes);
+  uint64_t* empty_bar = full_bar + kStages;
+  int* flags = reinterpret_cast<int*>(empty_bar + kStages);  // [0] last-arriver flag, [1..] scan scratch
+  int* P = reinterpret_cast<int*>(smem + Plan::kFixedBytes);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int nthreads = blockDim.x;
+  const int hkvv = p.hkv * p.vblk;
+
+  // ---- tile prefix over requests (every CTA computes the same table)
+  int tiles_per_req = 0;
+  if (p.paged) {
+    int* scratch = reinterpret_cast<int*>(merge);  // merge buffer is free at this point
+    const int per = ceil_div(p.batch, nthreads);
+    const int i0 = min(tid * per, p.batch), i1 = min(i0 + per, p.batch);
+    int sum = 0;
+    for (int i = i0; i < i1; ++i) sum += ceil_div(item_valid_len(p, i), kTile);
+    scratch[tid] = sum;
+    __syncthreads();
+    if (tid == 0) {
+      int run = 0;
+      for (int t = 0; t < nthreads; ++t) {
+        const int s = scratch[t];
+        scratch[t] = run;
+        run += s;
+      }
+      P[p.batch] = run;
+    }
+    __syncthreads();
+    int run = scratch[tid];
+    for (int i = i0; i < i1; ++i) {
+      P[i] = run;
+      run += ceil_div(item_valid_len(p, i), kTile);
+    }
+  } else {
+    tiles_per_req = ceil_div(p.kv_len, kTile);
+  }
+  if (tid == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], kConsumerWarps);
+    }
+    mbar_fence_init();
+    if (!GATHER) {
+      tma_prefetch_desc(&tm_k);
+      tma_prefetch_desc(&tm_v);
+    }
+  }
+  __syncthreads();
+
+  const int total_per_head = p.paged ? P[p.batch] : p.batch * tiles_per_req;
+  const int total = hkvv * total_per_head;
+  const int G = gridDim.x;
+  const int span = total > 0 ? ceil_div(total, G) : 1;
+  const int u0 = min(static_cast<int>(blockIdx.x) * span, total);
+  const int u1 = min(u0 + span, total);
+  Walker walker{p.paged ? P : nullptr, p.batch, hkvv, tiles_per_req};
+
+  if (warp == kConsumerWarps) {
+    // ================================================================= producer warp
+    int stage = 0, phase = 0;
+    for (int u = u0; u < u1;) {
+      const Piece pc = walker.at(u, u1);
+      const int h = pc.hv / p.vblk;
+      const int valid = item_valid_len(p, pc.b);
+      const int page_base = p.paged ? p.kv_indptr[pc.b] : 0;
+      const int n_pages = p.paged ? ceil_div(valid, p.page_size) : 0;
+      if constexpr (!GATHER) {
+        int win = -1, cur_idx = 0, next_idx = 0;
+        for (int t = pc.tile0; t < pc.tile0 + pc.count; ++t) {
+          mbar_wait(&empty_bar[stage], phase ^ 1, p.status, kFaultEmptyBarrier);
+          uint8_t* kdst = stages + stage * Plan::kStageBytes;
+          uint8_t* vdst = kdst + Plan::kMatBytes;
+          if (lane == 0) mbar_arrive_expect_tx(&full_bar[stage], Plan::kStageBytes);
+          __syncwarp();
+          if (p.paged) {
+            const int nbox = kTile / p.box_tok;
+            for (int j = 0; j < nbox; ++j) {
+              const int tok = t * kTile + j * p.box_tok;
+              const int pord = min(tok / p.page_size, n_pages - 1);
+              const int slot = tok - (tok / p.page_size) * p.page_size;
+              const int w = pord >> 5;
+              if (w != win) {  // warp-uniform: refill the 32-entry window of page ids
+                if (w == win + 1 && win >= 0) {
+                  cur_idx = next_idx;
+                } else {
+                  cur_idx = __ldg(p.kv_indices + page_base + min(w * 32 + lane, n_pages - 1));
+                }
+                next_idx = __ldg(p.kv_indices + page_base + min((w + 1) * 32 + lane, n_pages - 1));
+                win = w;
+              }
+              int page = __shfl_sync(0xffffffffu, cur_idx, pord & 31);
+              page = min(max(page, 0), p.num_pages - 1);
+              if (lane == 0) {
+#pragma unroll
+                for (int hf = 0; hf < D / 64; ++hf) {
+                  const int off = hf * (kTile * 128) + j * p.box_tok * 128;
+                  tma_load_4d(kdst + off, &tm_k, &full_bar[stage], hf * 64, h, slot, page);
+                  tma_load_4d(vdst + off, &tm_v, &full_bar[stage], hf * 64, h, slot, page);
+                }
+              }
+            }
+          } else if (lane == 0) {
+#pragma unroll
+            for (int hf = 0; hf < D / 64; ++hf) {
+              const int off = hf * (kTile * 128);
+              tma_load_4d(kdst + off, &tm_k, &full_bar[stage], hf * 64, 0, t * kTile, pc.b * p.hkv + h);
+              tma_load_4d(vdst + off, &tm_v, &full_bar[stage], hf * 64, 0, t * kTile, pc.b * p.hkv + h);
+            }
+          }
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+      } else {
+        // Row gather: lane l fetches token rows l and l+32 of each tile; page ids are read one
+        // tile ahead so their latency stays off the critical path.
+        const T* kc = reinterpret_cast<const T*>(p.k);
+        const T* vc = reinterpret_cast<const T*>(p.v);
+        auto page_of = [&](int t, int i) {
+          const int tok = min(t * kTile + lane + 32 * i, valid - 1);
+          const int pord = tok / p.page_size;
+          return __ldg(p.kv_indices + page_base + pord);
+        };
+        int pg0 = page_of(pc.tile0, 0), pg1 = page_of(pc.tile0, 1);
+        for (int t = pc.tile0; t < pc.tile0 + pc.count; ++t) {
+          const int cur0 = pg0, cur1 = pg1;
+          if (t + 1 < pc.tile0 + pc.count) {
+            pg0 = page_of(t + 1, 0);
+            pg1 = page_of(t + 1, 1);
+          }
+          mbar_wait(&empty_bar[stage], phase ^ 1, p.status, kFaultEmptyBarrier);
+          uint8_t* kdst = stages + stage * Plan::kStageBytes;
+          uint8_t* vdst = kdst + Plan::kMatBytes;
+          if (lane == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * kTile * D * 2);
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < 2; ++i) {
+            const int row = lane + 32 * i;
+            const int tok = min(t * kTile + row, valid - 1);
+            const int slot = tok - (tok / p.page_size) * p.page_size;
+            const long long page = min(max(i ? cur1 : cur0, 0), p.num_pages - 1);
+            const long long off = ((page * p.page_size + slot) * p.hkv + h) * D;
+            bulk_load_1d(kdst + row * Plan::kRowBytes, kc + off, D * 2, &full_bar[stage]);
+            bulk_load_1d(vdst + row * Plan::kRowBytes, vc + off, D * 2, &full_bar[stage]);
+          }
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+      u += pc.count;
+    }
+    return;
+  }
+
+  // =================================================================== consumer warps
+  const int ctid = tid;  // 0 .. kConsumerWarps*32-1
+  constexpr int kCThreads = kConsumerWarps * 32;
+  T* outp = reinterpret_cast<T*>(p.out);
+
+  // Requests without any live token: out = 0, lse = -inf.
+  if (p.paged) {
+    const int rows_all = p.hkv * p.rows;  // query rows per request
+    for (int b = blockIdx.x; b < p.batch; b += G) {
+      if (P[b + 1] - P[b] != 0) continue;
+      for (int i = ctid; i < rows_all * D; i += kCThreads) outp[static_cast<size_t>(b) * rows_all * D + i] = T(0.f);
+      if (p.lse)
+        for (int i = ctid; i < rows_all; i += kCThreads) p.lse[static_cast<size_t>(b) * rows_all + i] = -INFINITY;
+    }
+  }
+
+  const int ws = warp;  // token slice of this warp inside a tile
+  const int r0 = lane >> 2, c2 = (lane & 3) * 2;
+  const uint32_t stages_u32 = smem_u32(stages);
+  float* my_merge = merge + warp * Plan::kMergeFloats;
+  const int slot_floats = Plan::kMergeFloats;
+
+  int stage = 0, phase = 0;
+  for (int u = u0; u < u1;) {
+    const Piece pc = walker.at(u, u1);
+    const int h = pc.hv / p.vblk, blk = pc.hv - h * p.vblk;
+    const int valid = item_valid_len(p, pc.b);
+    const int rows_here = min(kRowsMax, p.rows - blk * kRowsMax);
+    const size_t row_base = (static_cast<size_t>(pc.b) * p.hkv + h) * p.rows + blk * kRowsMax;
+
+    // ---- Q fragments (A operand), rows beyond rows_here are zero
+    uint32_t qf[D / 16][4];
+    {
+      const T* qrow0 = reinterpret_cast<const T*>(p.q) + (row_base + r0) * D;
+      const T* qrow1 = qrow0 + 8 * D;
+      const bool ok0 = r0 < rows_here, ok1 = r0 + 8 < rows_here;
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) {
+        const int d = kk * 16 + c2;
+        qf[kk][0] = ok0 ? *reinterpret_cast<const uint32_t*>(qrow0 + d) : 0u;
+        qf[kk][1] = ok1 ? *reinterpret_cast<const uint32_t*>(qrow1 + d) : 0u;
+        qf[kk][2] = ok0 ? *reinterpret_cast<const uint32_t*>(qrow0 + d + 8) : 0u;
+        qf[kk][3] = ok1 ? *reinterpret_cast<const uint32_t*>(qrow1 + d + 8) : 0u;
+      }
+    }
+    float acc[D / 8][4];
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+
+    for (int t = pc.tile0; t < pc.tile0 + pc.count; ++t) {
+      mbar_wait(&full_bar[stage], phase, p.status, kFaultFullBarrier);
+      const int tok0 = t * kTile + ws * 16;
+      if (tok0 < valid) {
+        const uint32_t kbase = stages_u32 + stage * Plan::kStageBytes;
+        const uint32_t vbase = kbase + Plan::kMatBytes;
+        const int mi = lane >> 3, rr = lane & 7;
+        // ---- S = Q K^T for this warp's 16 tokens
+        float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        {
+          const int row = ws * 16 + (mi >> 1) * 8 + rr;
+#pragma unroll
+          for (int kk = 0; kk < D / 16; ++kk) {
+            const int d = kk * 16 + (mi & 1) * 8;
+            uint32_t addr;
+            if constexpr (GATHER) {
+              addr = kbase + row * Plan::kRowBytes + d * 2;
+            } else {
+              addr = kbase + (d >> 6) * (kTile * 128) + row * 128 + ((((d & 63) >> 3) ^ (row & 7)) << 4);
+            }
+            uint32_t b0, b1, b2, b3;
+            ldmatrix_x4(b0, b1, b2, b3, addr);
+            mma_16816<T>(s[0], qf[kk], b0, b1);
+            mma_16816<T>(s[1], qf[kk], b2, b3);
+          }
+        }
+        // ---- online softmax (exp2 domain)
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int nb = 0; nb < 2; ++nb) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int tok = tok0 + nb * 8 + c2 + (e & 1);
+            const float x = tok < valid ? s[nb][e] * p.scale_log2 : -INFINITY;
+            s[nb][e] = x;
+            if (e < 2) mx0 = fmaxf(mx0, x); else mx1 = fmaxf(mx1, x);
+          }
+        }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);
+        const float mu0 = mn0 == -INFINITY ? 0.f : mn0, mu1 = mn1 == -INFINITY ? 0.f : mn1;
+        const float sc0 = fast_exp2(m_run[0] - mu0), sc1 = fast_exp2(m_run[1] - mu1);
+        m_run[0] = mn0;
+        m_run[1] = mn1;
+        uint32_t pf[4];
+        float ps0 = 0.f, ps1 = 0.f;
+        {
+          const float p00 = fast_exp2(s[0][0] - mu0), p01 = fast_exp2(s[0][1] - mu0);
+          const float p02 = fast_exp2(s[0][2] - mu1), p03 = fast_exp2(s[0][3] - mu1);
+          const float p10 = fast_exp2(s[1][0] - mu0), p11 = fast_exp2(s[1][1] - mu0);
+          const float p12 = fast_exp2(s[1][2] - mu1), p13 = fast_exp2(s[1][3] - mu1);
+          ps0 = p00 + p01 + p10 + p11;
+          ps1 = p02 + p03 + p12 + p13;
+          pf[0] = pack2<T>(p00, p01);
+          pf[1] = pack2<T>(p02, p03);
+          pf[2] = pack2<T>(p10, p11);
+          pf[3] = pack2<T>(p12, p13);
+        }
+        l_run[0] = l_run[0] * sc0 + ps0;
+        l_run[1] = l_run[1] * sc1 + ps1;
+#pragma unroll
+        for (int n = 0; n < D / 8; ++n) {
+          acc[n][0] *= sc0;
+          acc[n][1] *= sc0;
+          acc[n][2] *= sc1;
+          acc[n][3] *= sc1;
+        }
+        // ---- O += P V
+        {
+          const int row = ws * 16 + (mi & 1) * 8 + rr;
+#pragma unroll
+          for (int dp = 0; dp < D / 16; ++dp) {
+            const int d = dp * 16 + (mi >> 1) * 8;
+            uint32_t addr;
+            if constexpr (GATHER) {
+              addr = vbase + row * Plan::kRowBytes + d * 2;
+            } else {
+              addr = vbase + (d >> 6) * (kTile * 128) + row * 128 + ((((d & 63) >> 3) ^ (row & 7)) << 4);
+            }
+            uint32_t b0, b1, b2, b3;
+            ldmatrix_x4_trans(b0, b1, b2, b3, addr);
+            mma_16816<T>(acc[2 * dp], pf, b0, b1);
+            mma_16816<T>(acc[2 * dp + 1], pf, b2, b3);
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty_bar[stage]);
+      if (++stage == kStages) { stage = 0; phase ^= 1; }
+    }
+
+    // ---- merge the four warps' states through shared memory
+    l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], 1);
+    l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], 2);
+    l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], 1);
+    l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], 2);
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n) {
+      *reinterpret_cast<float2*>(my_merge + r0 * D + n * 8 + c2) = make_float2(acc[n][0], acc[n][1]);
+      *reinterpret_cast<float2*>(my_merge + (r0 + 8) * D + n * 8 + c2) = make_float2(acc[n][2], acc[n][3]);
+    }
+    if ((lane & 3) == 0) {
+      my_merge[kRowsMax * D + r0] = m_run[0];
+      my_merge[kRowsMax * D + r0 + 8] = m_run[1];
+      my_merge[kRowsMax * D + kRowsMax + r0] = l_run[0];
+      my_merge[kRowsMax * D + kRowsMax + r0 + 8] = l_run[1];
+    }
+    named_bar_sync(1, kCThreads);
+
+    constexpr int kColsPerThread = kRowsMax * D / kCThreads;  // 16 (D=128) or 8 (D=64)
+    constexpr int kThreadsPerRow = kCThreads / kRowsMax;      // 8
+    const int mrow = ctid / kThreadsPerRow, mcol = (ctid % kThreadsPerRow) * kColsPerThread;
+    float M = -INFINITY, L = 0.f, o[kColsPerThread];
+    {
+      float mw[kConsumerWarps];
+#pragma unroll
+      for (int w = 0; w < kConsumerWarps; ++w) {
+        mw[w] = merge[w * Plan::kMergeFloats + kRowsMax * D + mrow];
+        M = fmaxf(M, mw[w]);
+      }
+      const float Mu = M == -INFINITY ? 0.f : M;
+#pragma unroll
+      for (int c = 0; c < kColsPerThread; ++c) o[c] = 0.f;
+#pragma unroll
+      for (int w = 0; w < kConsumerWarps; ++w) {
+        const float cf = fast_exp2(mw[w] - Mu);
+        L += cf * merge[w * Plan::kMergeFloats + kRowsMax * D + kRowsMax + mrow];
+        const float* src = merge + w * Plan::kMergeFloats + mrow * D + mcol;
+#pragma unroll
+        for (int c = 0; c < kColsPerThread; c += 4) {
+          const float4 x = *reinterpret_cast<const float4*>(src + c);
+          o[c] += cf * x.x;
+          o[c + 1] += cf * x.y;
+          o[c + 2] += cf * x.z;
+          o[c + 3] += cf * x.w;
+        }
+      }
+    }
+
+    const bool starts_here = (u == pc.unit0);
+    const bool whole = starts_here && pc.count == pc.n_tiles;
+    auto store_final = [&](float Mf, float Lf, const float* of) {
+      if (mrow < rows_here) {
+        const float inv = Lf > 0.f ? 1.f / Lf : 0.f;
+        T* dst = outp + (row_base + mrow) * D + mcol;
+#pragma unroll
+        for (int c = 0; c < kColsPerThread; c += 8) {
+          uint4 pk;
+          pk.x = pack2<T>(of[c] * inv, of[c + 1] * inv);
+          pk.y = pack2<T>(of[c + 2] * inv, of[c + 3] * inv);
+          pk.z = pack2<T>(of[c + 4] * inv, of[c + 5] * inv);
+          pk.w = pack2<T>(of[c + 6] * inv, of[c + 7] * inv);
+          *reinterpret_cast<uint4*>(dst + c) = pk;
+        }
+        if (p.lse && mcol == 0) p.lse[row_base + mrow] = Lf > 0.f ? Mf + fast_log2(Lf) : -INFINITY;
+      }
+    };
+
+    if (whole) {
+      store_final(M, L, o);
+    } else {
+      // ---- leave a partial, then let the last arriver combine
+      float* slot = p.partials + (static_cast<size_t>(blockIdx.x) * 2 + (starts_here ? 1 : 0)) * slot_floats;
+      if (mrow < rows_here) {
+#pragma unroll
+        for (int c = 0; c < kColsPerThread; c += 4)
+          *reinterpret_cast<float4*>(slot + mrow * D + mcol + c) = make_float4(o[c], o[c + 1], o[c + 2], o[c + 3]);
+        if (mcol == 0) {
+          slot[kRowsMax * D + mrow] = M;
+          slot[kRowsMax * D + kRowsMax + mrow] = L;
+        }
+      }
+      __threadfence();
+      named_bar_sync(1, kCThreads);
+      const int c_first = pc.unit0 / span, c_last = (pc.unit0 + pc.n_tiles - 1) / span;
+      int* counter = p.counters + pc.b * hkvv + pc.hv;
+      if (ctid == 0) {
+        const int old = atomicAdd(counter, 1);
+        flags[0] = (old == c_last - c_first) ? 1 : 0;
+      }
+      named_bar_sync(1, kCThreads);
+      if (flags[0]) {
+        __threadfence();
+        float Mc = -INFINITY, Lc = 0.f, oc[kColsPerThread];
+#pragma unroll
+        for (int c = 0; c < kColsPerThread; ++c) oc[c] = 0.f;
+        if (mrow < rows_here) {
+          for (int cta = c_first; cta <= c_last; ++cta) {
+            const float* src = p.partials + (static_cast<size_t>(cta) * 2 + (cta == c_first ? 1 : 0)) * slot_floats;
+            const float mi_ = __ldcg(src + kRowsMax * D + mrow);
+            const float li_ = __ldcg(src + kRowsMax * D + kRowsMax + mrow);
+            const float Mn = fmaxf(Mc, mi_);
+            const float Mu = Mn == -INFINITY ? 0.f : Mn;
+            const float a = fast_exp2(Mc - Mu), bb = fast_exp2(mi_ - Mu);
+            Lc = a * Lc + bb * li_;
+#pragma unroll
+            for (int c = 0; c < kColsPerThread; c += 4) {
+              const float4 x = __ldcg(reinterpret_cast<const float4*>(src + mrow * D + mcol + c));
+              oc[c] = a * oc[c] + bb * x.x;
+              oc[c + 1] = a * oc[c + 1] + bb * x.y;
+              oc[c + 2] = a * oc[c + 2] + bb * x.z;
+              oc[c + 3] = a * oc[c + 3] + bb * x.w;
+            }
+            Mc = Mn;
+          }
+        }
+        store_final(Mc, Lc, oc);
+        if (ctid == 0) *counter = 0;  // ready for the next launch
+      }
+    }
+    named_bar_sync(1, kCThreads);  // merge buffer and flag are free again
+    u += pc.count;
+  }
+}
+
+// ------------------------------------------------------------------------------------- host side
+namespace {
+
+struct DecodeSetup {
+  DecodeParams p;
+  bool gather;
+  int grid, smem_bytes;
+  size_t ws_needed, counters_off, partials_off;
+  CUtensorMap tm_k, tm_v;
+};
+
+int plan_decode(const cb200_attn_decode_args* a, DecodeSetup* s, bool need_maps) {
+  if (!a) return CB200_ERR_BAD_ARG;
+  if (a->batch <= 0 || a->num_qo_heads <= 0 || a->num_kv_heads <= 0) return CB200_ERR_BAD_ARG;
+  if (a->num_qo_heads % a->num_kv_heads) return CB200_ERR_BAD_ARG;
+  if (a->head_dim != 64 && a->head_dim != 128) return CB200_ERR_UNSUPPORTED;
+  if (a->dtype != CB200_F16 && a->dtype != CB200_BF16) return CB200_ERR_UNSUPPORTED;
+  const bool paged = a->kv_indptr != nullptr;
+  const int D = a->head_dim;
+  const int q_rows = a->q_rows > 1 ? a->q_rows : 1;
+  const int rows = (a->num_qo_heads / a->num_kv_heads) * q_rows;
+  DecodeParams& p = s->p;
+  p = DecodeParams{};
+  p.batch = a->batch;
+  p.hkv = a->num_kv_heads;
+  p.rows = rows;
+  p.vblk = ceil_div(rows, kRowsMax);
+  p.paged = paged ? 1 : 0;
+  p.scale_log2 = a->sm_scale * kLog2e;
+  long long tiles_ub;
+  if (paged) {
+    if (a->page_size <= 0 || a->num_pages <= 0 || a->num_kv_indices < 0) return CB200_ERR_BAD_ARG;
+    p.page_size = a->page_size;
+    p.num_pages = a->num_pages;
+    p.n_idx = a->num_kv_indices;
+    const int ps = a->page_size;
+    s->gather = !(ps >= 8 && ps % 8 == 0 && (kTile % ps == 0 || ps % kTile == 0));
+    p.box_tok = ps < kTile ? ps : kTile;
+    tiles_ub = (static_cast<long long>(a->num_kv_indices) * ps + kTile - 1) / kTile + a->batch;
+  } else {
+    if (a->kv_len <= 0) return CB200_ERR_BAD_ARG;
+    p.kv_len = a->kv_len;
+    s->gather = false;
+    p.box_tok = kTile;
+    tiles_ub = static_cast<long long>(a->batch) * ceil_div(a->kv_len, kTile);
+  }
+  const long long units_ub = tiles_ub * p.hkv * p.vblk;
+  if (units_ub >= (1LL << 31)) return CB200_ERR_UNSUPPORTED;
+  const int sms = sm_count();
+  if (sms <= 0) return CB200_ERR_CUDA;
+  int grid = sms;
+  if (a->max_ctas > 0 && a->max_ctas < grid) grid = a->max_ctas;
+  // The workspace is sized for a full grid so that one allocation serves every launch.
+  const int fixed = D == 128 ? (s->gather ? SmemPlan<128, true>::kFixedBytes : SmemPlan<128, false>::kFixedBytes)
+                             : (s->gather ? SmemPlan<64, true>::kFixedBytes : SmemPlan<64, false>::kFixedBytes);
+  const int merge_floats = kRowsMax * D + 2 * kRowsMax;
+  s->smem_bytes = fixed + (paged ? (a->batch + 1) * 4 : 0) + 1024 + 16;
+  if (s->smem_bytes > 227 * 1024) return CB200_ERR_UNSUPPORTED;  // too many requests for one launch
+  s->counters_off = kWsHeaderBytes;
+  s->partials_off = align_up(s->counters_off + static_cast<size_t>(a->batch) * p.hkv * p.vblk * 4, 256);
+  s->ws_needed = s->partials_off + static_cast<size_t>(sms) * 2 * merge_floats * 4;
+  s->grid = static_cast<int>(units_ub < grid ? (units_ub > 0 ? units_ub : 1) : grid);
+  if (!need_maps) return CB200_OK;
+
+  if (!a->q || !a->k_cache || !a->v_cache || !a->out) return CB200_ERR_BAD_ARG;
+  if (paged && !a->kv_indices && a->num_kv_indices > 0) return CB200_ERR_BAD_ARG;
+  if (paged && a->page_size != 1 && !a->kv_last_page_len) return CB200_ERR_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(a->q) | reinterpret_cast<uintptr_t>(a->k_cache) |
+       reinterpret_cast<uintptr_t>(a->v_cache) | reinterpret_cast<uintptr_t>(a->out)) & 15)
+    return CB200_ERR_ALIGNMENT;
+  if (!a->workspace || a->workspace_bytes < s->ws_needed) return CB200_ERR_WORKSPACE;
+  if (reinterpret_cast<uintptr_t>(a->workspace) & 255) return CB200_ERR_ALIGNMENT;
+  p.q = a->q;
+  p.k = a->k_cache;
+  p.v = a->v_cache;
+  p.kv_indptr = a->kv_indptr;
+  p.kv_indices = a->kv_indices;
+  p.kv_last = a->kv_last_page_len;
+  p.out = a->out;
+  p.lse = a->lse;
+  uint8_t* ws = static_cast<uint8_t*>(a->workspace);
+  p.status = reinterpret_cast<int*>(ws);
+  p.counters = reinterpret_cast<int*>(ws + s->counters_off);
+  p.partials = reinterpret_cast<float*>(ws + s->partials_off);
+
+  if (!s->gather) {
+    const CUtensorMapDataType dt = a->dtype == CB200_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    uint64_t dims[4], strides[3];
+    uint32_t box[4] = {64u, 1u, static_cast<uint32_t>(p.box_tok), 1u};
+    const uint64_t rowb = static_cast<uint64_t>(D) * 2;
+    if (paged) {
+      dims[0] = D; dims[1] = p.hkv; dims[2] = p.page_size; dims[3] = p.num_pages;
+      strides[0] = rowb; strides[1] = rowb * p.hkv; strides[2] = rowb * p.hkv * p.page_size;
+    } else {
+      dims[0] = D; dims[1] = 1; dims[2] = p.kv_len; dims[3] = static_cast<uint64_t>(p.batch) * p.hkv;
+      strides[0] = rowb; strides[1] = rowb; strides[2] = rowb * p.kv_len;
+    }
+    if (!encode_tensor_map(&s->tm_k, dt, 4, const_cast<void*>(a->k_cache), dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B) ||
+        !encode_tensor_map(&s->tm_v, dt, 4, const_cast<void*>(a->v_cache), dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
+      return CB200_ERR_CUDA;
+  } else {
+    memset(&s->tm_k, 0, sizeof(CUtensorMap));
+    memset(&s->tm_v, 0, sizeof(CUtensorMap));
+  }
+  return CB200_OK;
+}
+
+template <typename T, int D, bool GATHER>
+int launch_decode(const DecodeSetup& s, cudaStream_t stream) {
+  auto kern = decode_attn_kernel<T, D, GATHER>;
+  static int configured_smem[16] = {0};  // per device
+  int dev = 0;
+  CB200_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 16 && configured_smem[dev] < s.smem_bytes) {
+    CB200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    configured_smem[dev] = 227 * 1024;
+  } else if (dev >= 16) {
+    CB200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+  }
+  kern<<<s.grid, (kConsumerWarps + 1) * 32, s.smem_bytes, stream>>>(s.tm_k, s.tm_v, s.p);
+  CB200_CUDA_TRY(cudaGetLastError());
+  return CB200_OK;
+}
+
+}  // namespace
+}  // namespace cb200
+
+extern "C" size_t cb200_attn_decode_workspace_bytes(const cb200_attn_decode_args* a) {
+  cb200::DecodeSetup s;
+  if (cb200::plan_decode(a, &s, false) != CB200_OK) return 0;
+  return s.ws_needed;
+}
+
+extern "C" int cb200_attn_decode(const cb200_attn_decode_args* a, void* stream) {
+  using namespace cb200;
+  DecodeSetup s;
+  const int rc = plan_decode(a, &s, true);
+  if (rc != CB200_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const bool f16 = a->dtype == CB200_F16;
+  if (a->head_dim == 128) {
+    if (s.gather) return f16 ? launch_decode<__half, 128, true>(s, st) : launch_decode<__nv_bfloat16, 128, true>(s, st);
+    return f16 ? launch_decode<__half, 128, false>(s, st) : launch_decode<__nv_bfloat16, 128, false>(s, st);
+  }
+  if (s.gather) return f16 ? launch_decode<__half, 64, true>(s, st) : launch_decode<__nv_bfloat16, 64, true>(s, st);
+  return f16 ? launch_decode<__half, 64, false>(s, st) : launch_decode<__nv_bfloat16, 64, false>(s, st);
+}

@@ -1,0 +1,135 @@
+"""Tensor-level entry to the kernel library: torch CUDA tensors in, torch CUDA tensors out.
+
+Torch is plumbing here (device memory, the current stream); every operator body is a
+hand-written sm_100a kernel reached through the C ABI of ``include/cleave_b200.h``.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lib
+
+_DT = {torch.float16: _lib.F16, torch.bfloat16: _lib.BF16}
+_workspaces: dict = {}
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise TypeError(f"unsupported storage dtype {t.dtype}; use float16 or bfloat16") from None
+
+
+def _cuda(t: torch.Tensor, name: str) -> torch.Tensor:
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor (there is no CPU path)")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+    return t
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def workspace(kind: str, nbytes: int, device) -> torch.Tensor:
+    """A zero-initialised scratch buffer cached per (kind, device, stream); launches on one
+    stream run in order, so they can share it. It is allocated once per size, never per call
+    (the reference's split wrappers do the same, python/cleave/runtime/autotune.py:191-222)."""
+    index = torch.device(device).index
+    if index is None:
+        index = torch.cuda.current_device()
+    key = (kind, index, _stream())
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.zeros(max(nbytes, 1), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def check_workspace(ws: torch.Tensor) -> None:
+    """Synchronise and raise if a kernel recorded a bounded-wait timeout in ``ws``."""
+    _lib.check(_lib.lib().cb200_workspace_status(ws.data_ptr(), _stream()))
+
+
+def _attn_args(q, k_cache, v_cache, out, lse, ws, *, batch, hq, hkv, d, sm_scale, q_rows=1,
+               kv_indptr=None, kv_indices=None, kv_last_page_len=None, page_size=0, num_pages=0,
+               kv_len=0, max_ctas=0):
+    a = _lib.AttnDecodeArgs()
+    a.q, a.k_cache, a.v_cache = q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr()
+    a.kv_indptr = None if kv_indptr is None else kv_indptr.data_ptr()
+    a.kv_indices = None if kv_indices is None else kv_indices.data_ptr()
+    a.kv_last_page_len = None if kv_last_page_len is None else kv_last_page_len.data_ptr()
+    a.out = out.data_ptr()
+    a.lse = None if lse is None else lse.data_ptr()
+    a.workspace = None if ws is None else ws.data_ptr()
+    a.workspace_bytes = 0 if ws is None else ws.numel()
+    a.batch, a.num_qo_heads, a.num_kv_heads, a.head_dim = batch, hq, hkv, d
+    a.page_size, a.num_pages = page_size, num_pages
+    a.num_kv_indices = 0 if kv_indices is None else kv_indices.numel()
+    a.kv_len, a.q_rows, a.dtype, a.max_ctas = kv_len, q_rows, _dtype_code(q), max_ctas
+    a.sm_scale = float(sm_scale)
+    return a
+
+
+def gqa_paged_decode(q, k_cache, v_cache, kv_indptr, kv_indices, kv_last_page_len, sm_scale, *,
+                     out=None, lse=None, max_ctas=0):
+    """Paged GQA/MHA/MQA decode. Argument order and meaning follow the reference's operator
+    (python/cleave/dynamic/reference.py:156-200): q (batch, HQ, D); caches
+    (num_pages, page_size, HKV, D); ``kv_indptr`` in pages; ``kv_last_page_len`` may be None
+    when page_size is 1. Returns ``(out, lse)`` with ``lse`` base 2."""
+    q, k_cache, v_cache = _cuda(q, "q"), _cuda(k_cache, "k_cache"), _cuda(v_cache, "v_cache")
+    batch, hq, d = q.shape
+    num_pages, page_size, hkv, d2 = k_cache.shape
+    if d2 != d or v_cache.shape != k_cache.shape:
+        raise ValueError("k_cache / v_cache must be (num_pages, page_size, HKV, D) with q's D")
+    if kv_indptr.dtype != torch.int32 or kv_indices.dtype != torch.int32:
+        raise TypeError("kv_indptr / kv_indices must be int32")
+    if kv_indptr.numel() != batch + 1:
+        raise ValueError("kv_indptr must have batch + 1 entries")
+    if page_size != 1 and kv_last_page_len is None:
+        raise TypeError("missing input 'kv_last_page_len'")
+    if out is None:
+        out = torch.empty_like(q)
+    if lse is None:
+        lse = torch.empty((batch, hq), dtype=torch.float32, device=q.device)
+    probe = _attn_args(q, k_cache, v_cache, out, lse, None, batch=batch, hq=hq, hkv=hkv, d=d,
+                       sm_scale=sm_scale, kv_indptr=kv_indptr, kv_indices=kv_indices,
+                       kv_last_page_len=kv_last_page_len, page_size=page_size, num_pages=num_pages,
+                       max_ctas=max_ctas)
+    need = _lib.lib().cb200_attn_decode_workspace_bytes(C.byref(probe))
+    if need == 0:
+        _lib.check(_lib.lib().cb200_attn_decode(C.byref(probe), _stream()))  # raises the real status
+    ws = workspace("attn_decode", need, q.device)
+    probe.workspace, probe.workspace_bytes = ws.data_ptr(), ws.numel()
+    _lib.check(_lib.lib().cb200_attn_decode(C.byref(probe), _stream()))
+    return out, lse
+
+
+def attention_decode(q, k, v, sm_scale=None, *, out=None, lse=None, max_ctas=0):
+    """Static decode attention over contiguous caches. ``q`` (HQ, SQ, D) with a small SQ;
+    ``k``, ``v`` (HKV, SKV, D); query head h reads kv head h // (HQ/HKV)
+    (reference: demo/attention.py:5-8, demo/{mha,gqa,mqa}_decode.py). Returns ``out`` (HQ, SQ, D);
+    pass ``lse`` (HQ, SQ) fp32 to also get the base-2 log-sum-exp."""
+    q, k, v = _cuda(q, "q"), _cuda(k, "k"), _cuda(v, "v")
+    hq, sq, d = q.shape
+    hkv, skv, d2 = k.shape
+    if d2 != d or v.shape != k.shape or hq % hkv:
+        raise ValueError("shapes: q (HQ,SQ,D), k/v (HKV,SKV,D), HQ a multiple of HKV")
+    if sm_scale is None:
+        sm_scale = float(d) ** -0.5
+    if out is None:
+        out = torch.empty_like(q)
+    # the C ABI sees batch = HKV requests of one kv head each with HQ/HKV query heads
+    probe = _attn_args(q, k, v, out, lse, None, batch=hkv, hq=hq // hkv, hkv=1, d=d,
+                       sm_scale=sm_scale, q_rows=sq, kv_len=skv, max_ctas=max_ctas)
+    need = _lib.lib().cb200_attn_decode_workspace_bytes(C.byref(probe))
+    if need == 0:
+        _lib.check(_lib.lib().cb200_attn_decode(C.byref(probe), _stream()))
+    ws = workspace("attn_decode", need, q.device)
+    probe.workspace, probe.workspace_bytes = ws.data_ptr(), ws.numel()
+    _lib.check(_lib.lib().cb200_attn_decode(C.byref(probe), _stream()))
+    return out

@@ -1,0 +1,110 @@
+/*
+ * cleave_b200 - C ABI of the sm_100a kernel library behind Cleave's scheduled plans.
+ *
+ * The reference (nyu-systems/cleave) has no C FFI: a scheduled plan is turned into TileLang
+ * source (python/cleave/codegen/__init__.py:24-48), JIT-compiled (python/cleave/runtime/compile.py:30-34)
+ * and called as kernel(*tensors). Each entry point below is what such a compiled kernel object
+ * binds to instead; the comment on every function names the reference kernel it replaces.
+ *
+ * Conventions
+ *  - plain pointers and sizes only; all tensor pointers are DEVICE pointers, caller-owned,
+ *    inputs are never written;
+ *  - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream);
+ *  - every launch function returns a cb200_status (0 = ok); nothing throws, nothing
+ *    allocates device memory, nothing synchronises: a launch can be captured in a CUDA graph
+ *    (the reference times kernels by graph replay, python/cleave/runtime/timer.py:14-108);
+ *  - scratch ("workspace") is caller-owned; ask cb200_*_workspace_bytes() for the size. A
+ *    workspace must be zero-filled once before its first use; every launch leaves it
+ *    zero-filled where that matters, so it can be reused by the next launch on the same
+ *    stream. Two launches that overlap on the GPU must not share a workspace;
+ *  - a kernel that gives up a bounded wait records it in the first word of its workspace;
+ *    cb200_workspace_status() reads it back (synchronises the stream).
+ *  - storage dtypes are IEEE half (CB200_F16) or bfloat16 (CB200_BF16); accumulation, softmax
+ *    and norm statistics are fp32.
+ */
+#ifndef CLEAVE_B200_H
+#define CLEAVE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CB200_VERSION 1
+
+typedef enum {
+  CB200_OK = 0,
+  CB200_ERR_BAD_ARG = 1,       /* NULL pointer, non-positive extent, inconsistent shapes */
+  CB200_ERR_UNSUPPORTED = 2,   /* shape / dtype outside what the kernels implement */
+  CB200_ERR_ALIGNMENT = 3,     /* pointer or stride not 16-byte aligned */
+  CB200_ERR_WORKSPACE = 4,     /* workspace NULL or too small */
+  CB200_ERR_CUDA = 5,          /* a CUDA runtime / driver call failed (see cb200_last_cuda_error) */
+  CB200_ERR_DEVICE_TIMEOUT = 6 /* a bounded device-side wait gave up (from cb200_workspace_status) */
+} cb200_status;
+
+typedef enum { CB200_F16 = 0, CB200_BF16 = 1 } cb200_dtype;
+
+int cb200_version(void);
+const char* cb200_strerror(int status);
+/* cudaError_t of the most recent failing CUDA call made by this library on this thread. */
+int cb200_last_cuda_error(void);
+/* Number of SMs of the current device (grid sizing is a multiple of it). */
+int cb200_sm_count(void);
+/* Copies the status word of `workspace` to the host after synchronising `stream`.
+ * Returns CB200_OK, CB200_ERR_DEVICE_TIMEOUT or CB200_ERR_CUDA. */
+int cb200_workspace_status(const void* workspace, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Decode attention, one query token per request: O = softmax(Q K^T * scale) V, plus the base-2
+ * log-sum-exp. Query head h reads kv head h / (num_qo_heads / num_kv_heads)  (MHA, GQA, MQA).
+ *
+ * Replaces, for contiguous caches, the static split-KV pair
+ *   tests/graph/handwritten/expected_kernels/{gqa,mha,mqa}_split_partial.py + mha_split_combine.py
+ *   (operator: demo/attention.py:5-8, demo/{mha,gqa,mqa}_decode.py),
+ * and, for paged caches, the paged decode kernels
+ *   tests/graph/handwritten/expected_kernels/gqa_paged_decode_h32_kv8_d128_ps64.py  (slab, page 64)
+ *   tests/graph/handwritten/expected_kernels/gqa_paged_decode_h32_kv{8,4}_d128_ps1.py (row gather)
+ *   tests/graph/handwritten/expected_kernels/splitkv/gqa_paged_decode_*_splitkv8.py (split pair)
+ *   built by python/cleave/dynamic/paging/builders/{slab,decode,combine}.py; argument order and
+ *   meaning follow python/cleave/dynamic/reference.py:156-200.
+ *
+ * One persistent launch: KV tiles of 64 tokens are dealt evenly to one CTA per SM; a request
+ * whose tiles span several CTAs is finished by the last CTA to arrive (fused log-sum-exp
+ * combine, no second launch). Empty requests give out = 0, lse = -inf.
+ * ---------------------------------------------------------------------------------------- */
+typedef struct {
+  const void* q;       /* (batch, num_qo_heads, head_dim) */
+  const void* k_cache; /* paged: (num_pages, page_size, num_kv_heads, head_dim)
+                          contiguous: (batch, num_kv_heads, kv_len, head_dim) */
+  const void* v_cache; /* same layout as k_cache */
+  const int32_t* kv_indptr;        /* (batch + 1), in pages; NULL selects contiguous caches */
+  const int32_t* kv_indices;       /* (num_kv_indices) page ids */
+  const int32_t* kv_last_page_len; /* (batch) tokens in each request's last page; may be NULL
+                                      when page_size == 1 */
+  void* out;  /* (batch, num_qo_heads, head_dim), storage dtype */
+  float* lse; /* (batch, num_qo_heads) base-2 log-sum-exp; may be NULL */
+  void* workspace;
+  size_t workspace_bytes;
+  int32_t batch;
+  int32_t num_qo_heads;
+  int32_t num_kv_heads;
+  int32_t head_dim;       /* 64 or 128 */
+  int32_t page_size;      /* paged only */
+  int32_t num_pages;      /* paged only: pages in the pool */
+  int32_t num_kv_indices; /* paged only: entries of kv_indices */
+  int32_t kv_len;         /* contiguous only: tokens per request */
+  int32_t q_rows;         /* query rows per head (S_Q of the static operator); 0 or 1 = decode */
+  int32_t dtype;          /* cb200_dtype */
+  int32_t max_ctas;       /* 0 = one CTA per SM; otherwise an upper bound on the grid */
+  float sm_scale;
+} cb200_attn_decode_args;
+
+size_t cb200_attn_decode_workspace_bytes(const cb200_attn_decode_args* a);
+int cb200_attn_decode(const cb200_attn_decode_args* a, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CLEAVE_B200_H */

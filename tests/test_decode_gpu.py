@@ -1,0 +1,142 @@
+"""GPU parity of the decode-attention kernels (through the C ABI) against the oracle, the
+reference's golden vectors and size-independent properties."""
+
+import numpy as np
+import pytest
+import torch
+
+import cases
+from _util import assert_close, assert_lse_close, dev, host
+from oracle import cleave_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = cases.load_golden()
+
+
+def _ops():
+    from cleave_b200 import ops
+
+    return ops
+
+
+def _run_paged(inp, dt, page_size, **kw):
+    ops = _ops()
+    last = dev(inp["kv_last_page_len"]) if page_size != 1 else None
+    out, lse = ops.gqa_paged_decode(dev(inp["q"], dt), dev(inp["k_cache"], dt), dev(inp["v_cache"], dt),
+                                    dev(inp["kv_indptr"]), dev(inp["kv_indices"]), last, inp["sm_scale"], **kw)
+    ops.check_workspace(ops.workspace("attn_decode", 0, "cuda"))
+    return host(out), host(lse)
+
+
+@pytest.mark.parametrize("name", [n for n, c in cases.CASES.items() if c[0] == "gqa_paged"])
+def test_paged_decode_matches_reference_golden(name):
+    _, inp, opt = cases.build(name)
+    out, lse = _run_paged(inp, opt["dtype"], opt["page_size"])
+    want_out, want_lse = GOLDEN[name]
+    assert_close(out, want_out)
+    assert_lse_close(lse, want_lse)
+
+
+@pytest.mark.parametrize("name", [n for n, c in cases.CASES.items() if c[0] == "attention"])
+def test_static_decode_matches_reference_golden(name):
+    _, inp, opt = cases.build(name)
+    dt = opt["dtype"]
+    out = _ops().attention_decode(dev(inp["q"], dt), dev(inp["k"], dt), dev(inp["v"], dt))
+    assert_close(host(out), GOLDEN[name][0])
+
+
+@pytest.mark.parametrize("dt", ["f16", "bf16"])
+@pytest.mark.parametrize("page_size", [1, 8, 16, 64, 128, 5])
+@pytest.mark.parametrize("hq,hkv", [(32, 8), (8, 8), (32, 1), (16, 4)])
+def test_paged_decode_vs_oracle(dt, page_size, hq, hkv):
+    lens = [0, 1, 63, 64, 65, 700, 2049, 17]
+    inp = cases.gqa_paged_inputs(100 + page_size, lens, hq, hkv, 128, page_size, dt)
+    out, lse = _run_paged(inp, dt, page_size)
+    last = inp["kv_last_page_len"] if page_size != 1 else None
+    want_out, want_lse = orc.gqa_paged_decode(inp["q"], inp["k_cache"], inp["v_cache"], inp["kv_indptr"],
+                                              inp["kv_indices"], last, inp["sm_scale"], out_dtype=dt)
+    assert_close(out, want_out)
+    assert_lse_close(lse, want_lse)
+
+
+@pytest.mark.parametrize("max_ctas", [1, 3, 148])
+def test_split_kv_combine_is_grid_invariant(max_ctas):
+    """Cutting the tile stream over 1, 3 or all CTAs changes only the summation order."""
+    lens = [5000, 1, 300, 4097, 129]
+    inp = cases.gqa_paged_inputs(7, lens, 32, 8, 128, 64, "bf16")
+    out, lse = _run_paged(inp, "bf16", 64, max_ctas=max_ctas)
+    want_out, want_lse = orc.gqa_paged_decode(inp["q"], inp["k_cache"], inp["v_cache"], inp["kv_indptr"],
+                                              inp["kv_indices"], inp["kv_last_page_len"], inp["sm_scale"])
+    assert_close(out, want_out)
+    assert_lse_close(lse, want_lse)
+
+
+def test_paged_decode_d64():
+    inp = cases.gqa_paged_inputs(9, [100, 0, 257], 16, 4, 64, 16, "f16")
+    out, lse = _run_paged(inp, "f16", 16)
+    want_out, want_lse = orc.gqa_paged_decode(inp["q"], inp["k_cache"], inp["v_cache"], inp["kv_indptr"],
+                                              inp["kv_indices"], inp["kv_last_page_len"], inp["sm_scale"], "f16")
+    assert_close(out, want_out)
+    assert_lse_close(lse, want_lse)
+
+
+def test_valid_len_clamp_on_device():
+    """A last-page length larger than the page, or negative, is clamped exactly as the
+    reference's access layer clamps it (python/cleave/dynamic/paging/builders/slab.py:132-142)."""
+    inp = cases.gqa_paged_inputs(11, [128, 70, 64], 32, 8, 128, 64, "bf16")
+    inp["kv_last_page_len"] = np.array([999, -4, 64], dtype=np.int32)
+    out, lse = _run_paged(inp, "bf16", 64)
+    want_out, want_lse = orc.gqa_paged_decode(inp["q"], inp["k_cache"], inp["v_cache"], inp["kv_indptr"],
+                                              inp["kv_indices"], inp["kv_last_page_len"], inp["sm_scale"])
+    assert_close(out, want_out)
+    assert_lse_close(lse, want_lse)
+
+
+def test_named_and_repeat_calls_are_bit_identical():
+    """Reference: tests/frontend_dynamic/test_paged_pipeline.py:63-92 (a second call reproduces
+    the same bits; the workspace is left clean by every launch)."""
+    inp = cases.gqa_paged_inputs(12, [700, 1, 129, 64, 9000], 32, 8, 128, 64, "bf16")
+    a = _run_paged(inp, "bf16", 64)
+    b = _run_paged(inp, "bf16", 64)
+    assert np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1])
+
+
+@pytest.mark.parametrize("hq,hkv,sq", [(32, 8, 1), (8, 8, 1), (32, 1, 1), (8, 2, 3), (64, 8, 1)])
+def test_static_decode_vs_oracle(hq, hkv, sq):
+    inp = cases.attention_inputs(5, hq, hkv, sq, 1500, 128, "f16")
+    out = _ops().attention_decode(dev(inp["q"], "f16"), dev(inp["k"], "f16"), dev(inp["v"], "f16"))
+    assert_close(host(out), orc.attention(inp["q"], inp["k"], inp["v"], "f16"))
+
+
+def test_static_gqa_decode_full_config_properties():
+    """BASELINE config 3 at full size (batch 8, 32/8 heads, d 128, KV 8192, fp16): compared with
+    the oracle on a sample of kv heads, and invariant under a permutation of the KV positions."""
+    g = torch.Generator(device="cpu").manual_seed(0)
+    q = torch.randn(8 * 32, 1, 128, generator=g).half()
+    k = torch.randn(8 * 8, 8192, 128, generator=g).half()
+    v = torch.randn(8 * 8, 8192, 128, generator=g).half()
+    ops = _ops()
+    out = ops.attention_decode(q.cuda(), k.cuda(), v.cuda())
+    perm = torch.randperm(8192, generator=g)
+    out_p = ops.attention_decode(q.cuda(), k[:, perm].contiguous().cuda(), v[:, perm].contiguous().cuda())
+    assert_close(host(out), host(out_p), rtol=5e-3, atol=5e-3)
+    for h in (0, 17, 63):
+        want = orc.attention(q[h * 4:(h + 1) * 4].float().numpy(), k[h:h + 1].float().numpy(),
+                             v[h:h + 1].float().numpy(), "f16")
+        assert_close(host(out[h * 4:(h + 1) * 4]), want)
+
+
+def test_unsupported_and_bad_arguments_raise():
+    from cleave_b200 import Cb200Error
+
+    ops = _ops()
+    q = torch.zeros(2, 8, 96, dtype=torch.float16, device="cuda")
+    kc = torch.zeros(4, 16, 2, 96, dtype=torch.float16, device="cuda")
+    ptr = torch.tensor([0, 1, 2], dtype=torch.int32, device="cuda")
+    idx = torch.tensor([0, 1], dtype=torch.int32, device="cuda")
+    last = torch.tensor([3, 3], dtype=torch.int32, device="cuda")
+    with pytest.raises(Cb200Error):
+        ops.gqa_paged_decode(q, kc, kc, ptr, idx, last, 0.1)  # head_dim 96
+    with pytest.raises(ValueError):
+        ops.gqa_paged_decode(q.cpu(), kc, kc, ptr, idx, last, 0.1)

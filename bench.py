@@ -1,0 +1,338 @@
+"""Benchmark of the hot path: paged-KV GQA decode attention (batch 128, 32/8 heads, head_dim 128,
+page 64, lengths uniform in [512, 32768], fp16), one step = one pass over one batch.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+N > 1 is launched by ``python -m torch.distributed.run``; the batch is sharded by request with no
+collective on the data path: every rank decodes its own 128-request batch (weak scaling), the
+time is the maximum over ranks and the value is the whole job's algorithmic KV bandwidth.
+Prints ONE JSON line on rank 0.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "paged_gqa_decode_algorithmic_hbm_bandwidth"
+UNIT = "TB/s"
+WORKLOAD = dict(workload="paged GQA decode: batch 128 per GPU, 32 q / 8 kv heads, head_dim 128, page 64, "
+                         "kv_len ~ U[512, 32768], block table = seeded permutation, fp16",
+                batch_per_gpu=128, num_qo_heads=32, num_kv_heads=8, head_dim=128, page_size=64,
+                kv_len_range=[512, 32768], sharding="by request, no collective",
+                l2="inputs (about 8 GB per GPU) are far larger than the 126 MB L2; no flush needed")
+FALLBACK_HBM_GBS = 6650.0
+# DRAM bytes the kernel moves per algorithmic byte, from the committed ncu capture
+# (profiles/decode_attn_paged_ps64.md); None until a capture exists.
+TRAFFIC_PER_ALGORITHMIC_BYTE = 1.0046
+CPU_SAMPLE_REQUESTS = 8
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            d = json.load(f)
+        return float(d["hbm_gbs"]), "measured"
+    except Exception:  # noqa: BLE001
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while a region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index: int):
+        import torch
+
+        try:
+            uuid = str(torch.cuda.get_device_properties(device_index).uuid)
+            self.sel = uuid if uuid.startswith("GPU-") else "GPU-" + uuid
+        except Exception:  # noqa: BLE001
+            self.sel = str(device_index)
+        self.proc, self.lines = None, []
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", self.sel, f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except Exception:  # noqa: BLE001
+            self.proc = None
+        return self
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:  # noqa: BLE001
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def cpu_baseline_run(sample, steps, warmup):
+    """Times the CPU oracle (numpy port of the reference's torch path) on ``sample``; returns
+    (TB/s, seconds per step, thread count)."""
+    from oracle import cleave_oracle as orc
+
+    try:
+        from threadpoolctl import threadpool_info
+
+        threads = max([p.get("num_threads", 1) for p in threadpool_info()] or [1])
+    except Exception:  # noqa: BLE001
+        threads = os.cpu_count() or 1
+    a = [sample.q.float().numpy(), sample.k_cache.float().numpy(), sample.v_cache.float().numpy(),
+         sample.kv_indptr.numpy(), sample.kv_indices.numpy(), sample.kv_last_page_len.numpy()]
+    times = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        orc.gqa_paged_decode(*a, sample.sm_scale, out_dtype="f16")
+        if i >= warmup:
+            times.append(time.perf_counter() - t0)
+    per = sum(times) / len(times)
+    return sample.algorithmic_bytes() / per / 1e12, per, threads
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--e2e-steps", type=int, default=3, help="steps of the host-buffer end-to-end leg")
+    ap.add_argument("--batch", type=int, default=128, help="requests per GPU (smaller only for profiler captures)")
+    ap.add_argument("--kernel-only", action="store_true",
+                    help="skip the end-to-end and CPU legs (profiler captures)")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    import torch
+
+    from cleave_b200.workloads import paged_decode_workload, sub_workload
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    if args.impl == "reference":
+        # The reference's own implementation of this path is its torch CPU code
+        # (python/cleave/dynamic/reference.py:180-200); its numpy port under oracle/ is what can
+        # travel to the benchmark box. Rank 0 alone runs it, on a bounded sample per step.
+        if rank != 0:
+            return
+        w = paged_decode_workload(seed=0, device="cpu", batch=CPU_SAMPLE_REQUESTS)
+        tbs, per, threads = cpu_baseline_run(w, args.steps, args.warmup)
+        sample = (f"{CPU_SAMPLE_REQUESTS} requests of the workload's length distribution "
+                  f"({w.tokens} tokens, {w.algorithmic_bytes() / 1e9:.2f} GB of KV) per step")
+        print(json.dumps({
+            "impl": "reference", "metric": METRIC, "value": tbs, "unit": UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": per * 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": WORKLOAD,
+            "cpu_baseline": {"value": tbs, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+            "e2e": {"value": tbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}))
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU path")
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    from cleave_b200 import ops
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x: float) -> float:
+        if dist is None:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def sum_over_ranks(x: float) -> float:
+        if dist is None:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        return float(t.item())
+
+    w = paged_decode_workload(seed=rank, device="cuda", batch=args.batch)
+    out = torch.empty_like(w.q)
+    lse = torch.empty(w.q.shape[:2], dtype=torch.float32, device="cuda")
+    step = lambda: ops.gqa_paged_decode(*w.args(), out=out, lse=lse)  # noqa: E731
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    events = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    with ClockSampler(local_rank) as clocks:
+        barrier()
+        events[0].record()
+        for i in range(args.steps):
+            step()
+            events[i + 1].record()
+        barrier()
+    ops.check_workspace(ops.workspace("attn_decode", 0, "cuda"))
+    total_ms = max_over_ranks(events[0].elapsed_time(events[-1]))
+    launch_ms = [events[i].elapsed_time(events[i + 1]) for i in range(args.steps)]
+    my_bytes = w.algorithmic_bytes()
+    all_bytes = sum_over_ranks(float(my_bytes))
+    ms_per_step = total_ms / args.steps
+    value = all_bytes / (ms_per_step * 1e-3) / 1e12
+
+    if args.kernel_only:
+        if rank == 0:
+            kern_ms = sum(launch_ms) / len(launch_ms)
+            print(json.dumps({"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                              "ms_per_step": ms_per_step, "kernel_only": True, "batch": args.batch,
+                              "algorithmic_bytes_per_launch": my_bytes,
+                              "achieved_gbs": my_bytes / (kern_ms * 1e-3) / 1e9}))
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    # ---- end to end through the public API with HOST buffers (rank-local, max over ranks)
+    e2e = None
+    try:
+        import psutil
+
+        host_free = psutil.virtual_memory().available
+    except Exception:  # noqa: BLE001
+        host_free = 0
+    names = ["q", "k_cache", "v_cache", "kv_indptr", "kv_indices", "kv_last_page_len"]
+    dev_in = [getattr(w, n) for n in names]
+    h2d = sum(t.numel() * t.element_size() for t in dev_in)
+    d2h = out.numel() * out.element_size() + lse.numel() * 4
+    if host_free > 3 * h2d * max(1, world):
+        pinned = [torch.empty(t.shape, dtype=t.dtype, pin_memory=True).copy_(t) for t in dev_in]
+        h_out = torch.empty(out.shape, dtype=out.dtype, pin_memory=True)
+        h_lse = torch.empty(lse.shape, dtype=lse.dtype, pin_memory=True)
+
+        def e2e_step():
+            for dst, src in zip(dev_in, pinned):
+                dst.copy_(src, non_blocking=True)
+            ops.gqa_paged_decode(*w.args(), out=out, lse=lse)
+            h_out.copy_(out, non_blocking=True)
+            h_lse.copy_(lse, non_blocking=True)
+
+        e2e_step()
+        barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(args.e2e_steps):
+            e2e_step()
+        b.record()
+        barrier()
+        e2e_ms = max_over_ranks(a.elapsed_time(b)) / args.e2e_steps
+        e2e = {"value": all_bytes / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": h2d,
+               "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": args.e2e_steps,
+               "what": "every operator input, the KV cache included, copied from pinned host memory each step; "
+                       "out and lse read back"}
+        del pinned
+    # the serving case: the KV cache stays in HBM, only Q and the page tables come from the host
+    small = [t for n, t in zip(names, dev_in) if n not in ("k_cache", "v_cache")]
+    pinned_small = [torch.empty(t.shape, dtype=t.dtype, pin_memory=True).copy_(t) for t in small]
+    h_out = torch.empty(out.shape, dtype=out.dtype, pin_memory=True)
+    h_lse = torch.empty(lse.shape, dtype=lse.dtype, pin_memory=True)
+
+    def resident_step():
+        for dst, src in zip(small, pinned_small):
+            dst.copy_(src, non_blocking=True)
+        ops.gqa_paged_decode(*w.args(), out=out, lse=lse)
+        h_out.copy_(out, non_blocking=True)
+        h_lse.copy_(lse, non_blocking=True)
+        torch.cuda.current_stream().synchronize()  # the caller reads the result every step
+
+    resident_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        resident_step()
+    barrier()
+    res_ms = max_over_ranks((time.perf_counter() - t0) * 1e3) / args.steps
+    e2e_resident = {"value": all_bytes / (res_ms * 1e-3) / 1e12, "unit": UNIT,
+                    "h2d_bytes_per_step": sum(t.numel() * t.element_size() for t in small),
+                    "d2h_bytes_per_step": d2h, "ms_per_step": res_ms,
+                    "what": "KV cache resident in HBM; Q and page tables from pinned host memory, out and lse "
+                            "read back and waited for every step (wall clock)"}
+    if e2e is None:
+        e2e = dict(e2e_resident, note="host memory too small to stage the KV cache; cache kept resident")
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    peak, peak_kind = measured_peaks()
+    kern_ms = sum(launch_ms) / len(launch_ms)
+    achieved = my_bytes / (kern_ms * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                "peak_kind": f"of {peak_kind}", "kernel": "decode_attn_kernel<half,128,tma>",
+                "launch_ms": kern_ms, "algorithmic_bytes_per_launch": my_bytes,
+                "traffic": None if TRAFFIC_PER_ALGORITHMIC_BYTE is None else my_bytes * TRAFFIC_PER_ALGORITHMIC_BYTE,
+                "frac_of_nominal_8TBs": achieved / 8000.0}
+
+    sample = sub_workload(w, range(CPU_SAMPLE_REQUESTS))
+    cpu_tbs, cpu_s, threads = cpu_baseline_run(sample, 2, 1)
+    cpu = {"value": cpu_tbs, "unit": UNIT, "cores": threads, "kind": "port",
+           "sample": f"first {CPU_SAMPLE_REQUESTS} requests of rank 0's batch ({sample.tokens} tokens, "
+                     f"{sample.algorithmic_bytes() / 1e9:.2f} GB of KV), {cpu_s:.2f} s per pass, 2 passes after 1 warm-up"}
+
+    print(json.dumps({
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16", "data": "synthetic", "config": dict(WORKLOAD, batch_per_gpu=args.batch, tokens_rank0=w.tokens),
+        "clocks": clocks.summary(), "e2e": e2e, "e2e_kv_resident": e2e_resident, "gpu_launches": args.steps,
+        "roofline": roofline, "cpu_baseline": cpu}))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

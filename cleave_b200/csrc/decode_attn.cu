@@ -580,12 +580,16 @@ int plan_decode(const cb200_attn_decode_args* a, DecodeSetup* s, bool need_maps)
   // The workspace is sized for a full grid so that one allocation serves every launch.
   const int fixed = D == 128 ? (s->gather ? SmemPlan<128, true>::kFixedBytes : SmemPlan<128, false>::kFixedBytes)
                              : (s->gather ? SmemPlan<64, true>::kFixedBytes : SmemPlan<64, false>::kFixedBytes);
-  const int merge_floats = kRowsMax * D + 2 * kRowsMax;
   s->smem_bytes = fixed + (paged ? (a->batch + 1) * 4 : 0) + 1024 + 16;
   if (s->smem_bytes > 227 * 1024) return CB200_ERR_UNSUPPORTED;  // too many requests for one launch
-  s->counters_off = kWsHeaderBytes;
-  s->partials_off = align_up(s->counters_off + static_cast<size_t>(a->batch) * p.hkv * p.vblk * 4, 256);
-  s->ws_needed = s->partials_off + static_cast<size_t>(sms) * 2 * merge_floats * 4;
+  // Layout: header | partial slots (two per SM, sized for head_dim 128) | arrival counters.
+  // The counters sit at an offset that does not depend on the problem shape: launches of
+  // different shapes may share one workspace, and a region that one launch used for partials
+  // is never read as counters by the next.
+  constexpr size_t kSlotBytesMax = (kRowsMax * 128 + 2 * kRowsMax) * 4;
+  s->partials_off = kWsHeaderBytes;
+  s->counters_off = align_up(s->partials_off + static_cast<size_t>(sms) * 2 * kSlotBytesMax, 256);
+  s->ws_needed = s->counters_off + static_cast<size_t>(a->batch) * p.hkv * p.vblk * 4;
   s->grid = static_cast<int>(units_ub < grid ? (units_ub > 0 ? units_ub : 1) : grid);
   if (!need_maps) return CB200_OK;
 

@@ -140,3 +140,17 @@ def test_unsupported_and_bad_arguments_raise():
         ops.gqa_paged_decode(q, kc, kc, ptr, idx, last, 0.1)  # head_dim 96
     with pytest.raises(ValueError):
         ops.gqa_paged_decode(q.cpu(), kc, kc, ptr, idx, last, 0.1)
+
+
+def test_workspace_shared_by_launches_of_different_shapes():
+    """One workspace serves launches of different batch and head counts back to back: the
+    arrival counters live at a shape-independent offset, so partials left by a small problem are
+    never read as counters by a larger one."""
+    small = cases.gqa_paged_inputs(21, [5000, 3000], 8, 2, 128, 64, "bf16")
+    large = cases.gqa_paged_inputs(22, [300] * 40 + [9000] * 8, 32, 8, 128, 64, "bf16")
+    for inp in (small, large, small, large):
+        out, lse = _run_paged(inp, "bf16", 64)
+        want_out, want_lse = orc.gqa_paged_decode(inp["q"], inp["k_cache"], inp["v_cache"], inp["kv_indptr"],
+                                                  inp["kv_indices"], inp["kv_last_page_len"], inp["sm_scale"])
+        assert_close(out, want_out)
+        assert_lse_close(lse, want_lse)

@@ -60,6 +60,9 @@ def lib() -> C.CDLL:
         L.cb200_attn_decode_workspace_bytes.argtypes = [C.POINTER(AttnDecodeArgs)]
         L.cb200_attn_decode.restype = C.c_int
         L.cb200_attn_decode.argtypes = [C.POINTER(AttnDecodeArgs), C.c_void_p]
+        L.cb200_attn_decode_static_scratch_max_bytes.restype = C.c_size_t
+        L.cb200_attn_decode_static_scratch.restype = C.c_int
+        L.cb200_attn_decode_static_scratch.argtypes = [C.POINTER(AttnDecodeArgs), C.c_void_p]
         _lib = L
     return _lib
 

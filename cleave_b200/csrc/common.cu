@@ -77,6 +77,9 @@ extern "C" const char* cb200_strerror(int status) {
     case CB200_ERR_WORKSPACE: return "workspace missing or too small";
     case CB200_ERR_CUDA: return "a CUDA call failed (see cb200_last_cuda_error)";
     case CB200_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait gave up";
+    case CB200_ERR_SCRATCH_LIMIT:
+      return "the problem needs more scratch than the library's built-in static array holds; "
+             "use the entry point that takes a caller-owned workspace";
     default: return "unknown status";
   }
 }

@@ -17,6 +17,7 @@
 #include "common.cuh"
 
 #include <cstring>
+#include <mutex>
 
 namespace cb200 {
 
@@ -655,6 +656,67 @@ int launch_decode(const DecodeSetup& s, cudaStream_t stream) {
 
 }  // namespace
 }  // namespace cb200
+
+namespace cb200 {
+namespace {
+
+// Scratch for cb200_attn_decode_static_scratch: lives in the library's device image, so every GPU
+// that loads the library holds these 4 MiB until the process exits.
+constexpr size_t kStaticScratchBytes = size_t(4) << 20;
+static __device__ __align__(256) unsigned char g_decode_static_scratch[kStaticScratchBytes];
+
+// In host code the array's name is only a handle for the runtime, not a device address. The
+// address is looked up once per device, with that device current, and cached.
+int static_scratch_address(unsigned char** out) {
+  static unsigned char* cached[64] = {nullptr};
+  static std::mutex mu;
+  int dev = 0;
+  CB200_CUDA_TRY(cudaGetDevice(&dev));
+  std::lock_guard<std::mutex> lock(mu);
+  if (dev < 64 && cached[dev]) {
+    *out = cached[dev];
+    return CB200_OK;
+  }
+  unsigned char* ptr = nullptr;
+  CB200_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_decode_static_scratch));
+  if (!ptr) return CB200_ERR_CUDA;
+  if (dev < 64) cached[dev] = ptr;
+  *out = ptr;
+  return CB200_OK;
+}
+
+}  // namespace
+}  // namespace cb200
+
+extern "C" size_t cb200_attn_decode_static_scratch_max_bytes(void) { return cb200::kStaticScratchBytes; }
+
+extern "C" int cb200_attn_decode_static_scratch(const cb200_attn_decode_args* a, void* stream) {
+  using namespace cb200;
+  DecodeSetup s;
+  int rc = plan_decode(a, &s, false);
+  if (rc != CB200_OK) return rc;
+  if (s.ws_needed > kStaticScratchBytes) return CB200_ERR_SCRATCH_LIMIT;
+  unsigned char* scratch = nullptr;
+  rc = static_scratch_address(&scratch);
+  if (rc != CB200_OK) return rc;
+  cb200_attn_decode_args b = *a;
+  b.workspace = scratch;
+  b.workspace_bytes = kStaticScratchBytes;
+  rc = plan_decode(&b, &s, true);
+  if (rc != CB200_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // The array keeps whatever the previous call left behind; the status word and this call's
+  // arrival counters must start at zero.
+  CB200_CUDA_TRY(cudaMemsetAsync(scratch, 0, kWsHeaderBytes, st));
+  CB200_CUDA_TRY(cudaMemsetAsync(scratch + s.counters_off, 0, s.ws_needed - s.counters_off, st));
+  const bool f16 = b.dtype == CB200_F16;
+  if (b.head_dim == 128) {
+    if (s.gather) return f16 ? launch_decode<__half, 128, true>(s, st) : launch_decode<__nv_bfloat16, 128, true>(s, st);
+    return f16 ? launch_decode<__half, 128, false>(s, st) : launch_decode<__nv_bfloat16, 128, false>(s, st);
+  }
+  if (s.gather) return f16 ? launch_decode<__half, 64, true>(s, st) : launch_decode<__nv_bfloat16, 64, true>(s, st);
+  return f16 ? launch_decode<__half, 64, false>(s, st) : launch_decode<__nv_bfloat16, 64, false>(s, st);
+}
 
 extern "C" size_t cb200_attn_decode_workspace_bytes(const cb200_attn_decode_args* a) {
   cb200::DecodeSetup s;

@@ -133,3 +133,24 @@ def attention_decode(q, k, v, sm_scale=None, *, out=None, lse=None, max_ctas=0):
     probe.workspace, probe.workspace_bytes = ws.data_ptr(), ws.numel()
     _lib.check(_lib.lib().cb200_attn_decode(C.byref(probe), _stream()))
     return out
+
+
+def gqa_paged_decode_static_scratch(q, k_cache, v_cache, kv_indptr, kv_indices, kv_last_page_len, sm_scale,
+                                    *, out, lse, max_ctas=0):
+    """Paged decode for hosts that may not allocate device memory (a server that gave this
+    library only tensors from its own arena, a runtime that bans allocation after start-up, a
+    GPU already filled by the KV cache). The split-KV scratch is a fixed 4 MiB array inside the
+    library instead of a torch buffer, so the caller must pass ``out`` and ``lse`` too: nothing is
+    allocated here. Same results as :func:`gqa_paged_decode`. Problems that need more scratch
+    than the array holds raise ``Cb200Error`` (status 7). All calls on a device share the array:
+    keep them on one stream, or order them, or they race. The first call on a device resolves
+    the array's address; make it before any stream capture."""
+    q, k_cache, v_cache = _cuda(q, "q"), _cuda(k_cache, "k_cache"), _cuda(v_cache, "v_cache")
+    batch, hq, d = q.shape
+    num_pages, page_size, hkv, _ = k_cache.shape
+    a = _attn_args(q, k_cache, v_cache, out, lse, None, batch=batch, hq=hq, hkv=hkv, d=d,
+                   sm_scale=sm_scale, kv_indptr=kv_indptr, kv_indices=kv_indices,
+                   kv_last_page_len=kv_last_page_len, page_size=page_size, num_pages=num_pages,
+                   max_ctas=max_ctas)
+    _lib.check(_lib.lib().cb200_attn_decode_static_scratch(C.byref(a), _stream()))
+    return out, lse

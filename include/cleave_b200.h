@@ -41,7 +41,8 @@ typedef enum {
   CB200_ERR_ALIGNMENT = 3,     /* pointer or stride not 16-byte aligned */
   CB200_ERR_WORKSPACE = 4,     /* workspace NULL or too small */
   CB200_ERR_CUDA = 5,          /* a CUDA runtime / driver call failed (see cb200_last_cuda_error) */
-  CB200_ERR_DEVICE_TIMEOUT = 6 /* a bounded device-side wait gave up (from cb200_workspace_status) */
+  CB200_ERR_DEVICE_TIMEOUT = 6, /* a bounded device-side wait gave up (from cb200_workspace_status) */
+  CB200_ERR_SCRATCH_LIMIT = 7   /* the problem needs more scratch than the built-in static array holds */
 } cb200_status;
 
 typedef enum { CB200_F16 = 0, CB200_BF16 = 1 } cb200_dtype;
@@ -103,6 +104,32 @@ typedef struct {
 
 size_t cb200_attn_decode_workspace_bytes(const cb200_attn_decode_args* a);
 int cb200_attn_decode(const cb200_attn_decode_args* a, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Decode attention for callers that cannot allocate device memory. (No counterpart in the
+ * reference, whose wrappers always own a torch-allocated scratch buffer.)
+ *
+ * Who needs it: a host that runs inside someone else's memory plan - an inference server that
+ * hands this library only the tensors it carved out of its own arena at start-up, a plugin
+ * loaded by a runtime that forbids cudaMalloc after initialisation, or a process whose device
+ * memory is fully committed to the KV cache. Such a caller has nowhere to get the split-KV
+ * workspace from, so this variant keeps it inside the library: a 4 MiB array in the library's
+ * device image (cb200_attn_decode_static_scratch_max_bytes()). Every GPU that loads the library
+ * holds those 4 MiB until the process exits, whether or not this function is ever called.
+ *
+ * Same arguments and results as cb200_attn_decode; `workspace` / `workspace_bytes` are ignored.
+ * The function calls no allocating routine. A problem whose scratch need
+ * (cb200_attn_decode_workspace_bytes) exceeds the array is refused with CB200_ERR_SCRATCH_LIMIT;
+ * on a 148-SM GPU that leaves room for about 430 000 (request, kv head) pairs.
+ *
+ * The first call on each device looks up the array's device address (one runtime query, with
+ * that device current) and caches it; make that first call before starting any stream capture.
+ * All calls on a device share the one array: each call clears the words it needs at zero on
+ * `stream` before its kernel, and two calls that overlap on the GPU (different streams with no
+ * ordering between them) race on it - keep them on one stream or order them with events.
+ * ---------------------------------------------------------------------------------------- */
+size_t cb200_attn_decode_static_scratch_max_bytes(void);
+int cb200_attn_decode_static_scratch(const cb200_attn_decode_args* a, void* stream);
 
 #ifdef __cplusplus
 }

@@ -37,6 +37,17 @@ class AttnDecodeArgs(C.Structure):
     ]
 
 
+class GemmArgs(C.Structure):
+    _fields_ = [
+        ("x", C.c_void_p), ("w", C.c_void_p), ("w1", C.c_void_p), ("gamma", C.c_void_p), ("y", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("m", C.c_int32), ("n", C.c_int32), ("k", C.c_int32), ("op", C.c_int32), ("dtype", C.c_int32),
+        ("split_k", C.c_int32), ("max_ctas", C.c_int32), ("eps", C.c_float),
+    ]
+
+
+GEMM_MATMUL, GEMM_RMSNORM, GEMM_SWIGLU = 0, 1, 2
+
 _lib = None
 
 
@@ -63,6 +74,12 @@ def lib() -> C.CDLL:
         L.cb200_attn_decode_static_scratch_max_bytes.restype = C.c_size_t
         L.cb200_attn_decode_static_scratch.restype = C.c_int
         L.cb200_attn_decode_static_scratch.argtypes = [C.POINTER(AttnDecodeArgs), C.c_void_p]
+        L.cb200_gemm_workspace_bytes.restype = C.c_size_t
+        L.cb200_gemm_workspace_bytes.argtypes = [C.POINTER(GemmArgs)]
+        L.cb200_gemm_effective_split.restype = C.c_int
+        L.cb200_gemm_effective_split.argtypes = [C.POINTER(GemmArgs)]
+        L.cb200_gemm.restype = C.c_int
+        L.cb200_gemm.argtypes = [C.POINTER(GemmArgs), C.c_void_p]
         _lib = L
     return _lib
 

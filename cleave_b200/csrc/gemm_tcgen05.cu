@@ -1,0 +1,541 @@
+// Fused dense contractions on the 5th-generation tensor cores (tcgen05 + TMEM) for sm_100a:
+//   MODE 0  Y = X @ W                                   (split-K matmul)
+//   MODE 1  Y = (X * rsqrt(mean(X^2) + eps) [* gamma]) @ W   (RMSNorm fused into the GEMM)
+//   MODE 2  Y = silu(X @ W0) * (X @ W1)                 (SwiGLU, one A stream, two accumulators)
+// X is (M, K) row-major (K-major A operand), W is (K, N) row-major (MN-major B operand).
+//
+// One persistent launch, one CTA per SM. The work is the list of (output tile, K chunk) pairs,
+// tile-major; every CTA takes an equal contiguous share of it (stream-K). Chunks of one tile that
+// fall to the same CTA accumulate in TMEM; a tile finished inside one CTA goes straight through
+// the fused epilogue; a tile cut across CTAs leaves fp32 partials in the workspace and the last
+// CTA to arrive sums them in a fixed order and runs the epilogue (no second launch, nobody
+// waits, bit-stable results).
+//
+// Warp roles: 0 = TMA producer, 1 = MMA issuer (one elected thread) and TMEM owner,
+// 2..5 = epilogue (TMEM -> registers -> global), 6..9 = RMSNorm statistics / gamma scaling of the
+// A tile in shared memory (MODE 1 only). Two TMEM accumulators let the epilogue of one tile
+// overlap the main loop of the next.
+//
+// Replaces the reference's generated kernels
+//   tests/graph/handwritten/expected_kernels/matmul.py, matmul_splitk_partial.py, matmul_splitk_combine.py,
+//   rmsnorm_matmul.py, rmsnorm_matmul_split_partial.py, rmsnorm_matmul_split_combine.py, swiglu.py
+// (operators: demo/matmul.py:11-13, demo/rmsnorm_matmul.py:11-13 with
+// python/cleave/frontend/composites.py:48-53, demo/swiglu.py:6-10).
+
+#include "common.cuh"
+
+#include <cstring>
+#include <type_traits>
+
+namespace cb200 {
+
+constexpr int kBM = 128;  // rows per output tile (UMMA M)
+constexpr int kBK = 64;   // K elements per stage: one 128-byte swizzle row
+constexpr int kChunkN = 64;                       // columns per B chunk: one 128-byte swizzle row
+constexpr int kABytes = kBM * kBK * 2;            // 16 KB
+constexpr int kBChunkBytes = kBK * kChunkN * 2;   // 8 KB
+
+struct GemmParams {
+  void* y;
+  const void* gamma;  // MODE 1, may be null
+  int* status;
+  int* counters;    // one per output tile, zero between launches
+  float* partials;  // gridDim.x * 2 slots of (128 x UMMA_N + 128) floats
+  int M, N, K;
+  int tiles_m, tiles_n;
+  int kblocks;         // ceil(K / 64)
+  int chunk_kblocks;   // K blocks per chunk
+  int chunks_per_tile; // S
+  float eps;
+};
+
+template <int MODE, int NBW>
+struct GemmPlan {
+  static constexpr int kWeights = MODE == 2 ? 2 : 1;
+  static constexpr int kNBT = NBW * kWeights;        // B chunks per stage
+  static constexpr int kUmmaN = kNBT * kChunkN;      // accumulator columns
+  static constexpr int kTileN = NBW * kChunkN;       // output columns per tile
+  static constexpr int kStageBytes = kABytes + kNBT * kBChunkBytes;
+  static constexpr int kStages = kNBT == 2 ? 6 : 4;
+  static constexpr int kThreads = MODE == 1 ? 320 : 192;
+  static constexpr int kSlotFloats = kBM * kUmmaN + kBM;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 2048 /*barriers, rowsums*/ + 1024 /*alignment*/;
+};
+
+// Which CTA owns chunk x when C chunks are dealt as floor(c * C / G) .. floor((c + 1) * C / G).
+__device__ __forceinline__ int cta_of_chunk(long long x, long long C, long long G) {
+  long long c = x * G / C;
+  if ((c + 1) * C / G <= x) ++c;
+  return static_cast<int>(c);
+}
+
+template <int MODE, typename T, int NBW>
+__global__ void __launch_bounds__(GemmPlan<MODE, NBW>::kThreads, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b0,
+            const __grid_constant__ CUtensorMap tm_b1, const GemmParams p) {
+  using Plan = GemmPlan<MODE, NBW>;
+  constexpr int kStages = Plan::kStages;
+  constexpr int kUmmaN = Plan::kUmmaN;
+  constexpr uint32_t kTmemCols = 2 * kUmmaN;  // two accumulators: 256 or 512 columns
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* stages = smem;
+  uint8_t* misc = smem + kStages * Plan::kStageBytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(misc);   // TMA landed
+  uint64_t* empty_bar = full_bar + kStages;                  // MMA finished reading the stage
+  uint64_t* ready_bar = empty_bar + kStages;                 // MODE 1: statistics taken, A scaled
+  uint64_t* acc_full = ready_bar + kStages;                  // [2] accumulator complete
+  uint64_t* acc_empty = acc_full + 2;                        // [2] accumulator drained
+  uint64_t* rs_full = acc_empty + 2;                         // [2] MODE 1: row sums published
+  uint64_t* rs_empty = rs_full + 2;                          // [2]
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(rs_empty + 2);
+  int* flag = reinterpret_cast<int*>(tmem_holder + 1);
+  float* rowsum_smem = reinterpret_cast<float*>(misc + 512);  // [2][128]
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  if (tid == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], MODE == 1 ? 5 : 1);  // MMA commit (+ the 4 statistics warps)
+      mbar_init(&ready_bar[s], 4);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      // one arrival per warp (after __syncwarp): arrivals on one mbarrier serialise
+      mbar_init(&acc_empty[b], 4);
+      mbar_init(&rs_full[b], 4);
+      mbar_init(&rs_empty[b], 4);
+    }
+    mbar_fence_init();
+    tma_prefetch_desc(&tm_a);
+    tma_prefetch_desc(&tm_b0);
+    if (MODE == 2) tma_prefetch_desc(&tm_b1);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_holder, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_holder);
+
+  // ---- this CTA's share of the (tile, chunk) list
+  const int S = p.chunks_per_tile;
+  const long long C = static_cast<long long>(p.tiles_m) * p.tiles_n * S;
+  const long long G = gridDim.x;
+  const long long x0 = static_cast<long long>(blockIdx.x) * C / G;
+  const long long x1 = static_cast<long long>(blockIdx.x + 1) * C / G;
+
+  if (warp == 0) {
+    // ================================================================ TMA producer
+    int stage = 0, phase = 0;
+    for (long long x = x0; x < x1;) {
+      const int tile = static_cast<int>(x / S), s0 = static_cast<int>(x - static_cast<long long>(tile) * S);
+      const int nseg = static_cast<int>(min(static_cast<long long>(S - s0), x1 - x));
+      const int tm = tile / p.tiles_n, tn = tile - tm * p.tiles_n;
+      const int kb0 = s0 * p.chunk_kblocks, kb1 = min((s0 + nseg) * p.chunk_kblocks, p.kblocks);
+      for (int kb = kb0; kb < kb1; ++kb) {
+        mbar_wait(&empty_bar[stage], phase ^ 1, p.status, kFaultEmptyBarrier);
+        if (lane == 0) {
+          uint8_t* a_dst = stages + stage * Plan::kStageBytes;
+          uint8_t* b_dst = a_dst + kABytes;
+          mbar_arrive_expect_tx(&full_bar[stage], Plan::kStageBytes);
+          tma_load_2d(a_dst, &tm_a, &full_bar[stage], kb * kBK, tm * kBM);
+#pragma unroll
+          for (int j = 0; j < NBW; ++j)
+            tma_load_2d(b_dst + j * kBChunkBytes, &tm_b0, &full_bar[stage], tn * Plan::kTileN + j * kChunkN, kb * kBK);
+          if constexpr (MODE == 2) {
+#pragma unroll
+            for (int j = 0; j < NBW; ++j)
+              tma_load_2d(b_dst + (NBW + j) * kBChunkBytes, &tm_b1, &full_bar[stage],
+                          tn * Plan::kTileN + j * kChunkN, kb * kBK);
+          }
+        }
+        __syncwarp();
+        if (++stage == kStages) { stage = 0; phase ^= 1; }
+      }
+      x += nseg;
+    }
+  } else if (warp == 1) {
+    // ================================================================ MMA issuer
+    constexpr uint32_t idesc = umma_idesc(std::is_same<T, __nv_bfloat16>::value, true, kBM, kUmmaN);
+    int stage = 0, phase = 0, buf = 0, acc_phase = 0;
+    for (long long x = x0; x < x1;) {
+      const int tile = static_cast<int>(x / S), s0 = static_cast<int>(x - static_cast<long long>(tile) * S);
+      const int nseg = static_cast<int>(min(static_cast<long long>(S - s0), x1 - x));
+      const int kb0 = s0 * p.chunk_kblocks, kb1 = min((s0 + nseg) * p.chunk_kblocks, p.kblocks);
+      mbar_wait(&acc_empty[buf], acc_phase ^ 1, p.status, kFaultTmemBarrier);
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + buf * kUmmaN;
+      for (int kb = kb0; kb < kb1; ++kb) {
+        mbar_wait((MODE == 1 && p.gamma != nullptr) ? &ready_bar[stage] : &full_bar[stage], phase, p.status,
+                  kFaultFullBarrier);
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t a_addr = smem_u32(stages + stage * Plan::kStageBytes);
+          const uint32_t b_addr = a_addr + kABytes;
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k) {
+            // A: K-major, 16 K elements = 32 bytes inside the swizzled 128-byte row
+            const uint64_t adesc = umma_smem_desc(a_addr + k * 32, 16, 8 * 128);
+            // B: MN-major, 16 K rows = 2048 bytes; 64-column chunks are kBChunkBytes apart
+            const uint64_t bdesc = umma_smem_desc(b_addr + k * 16 * 128, kBChunkBytes, 8 * 128);
+            umma_f16(d_tmem, adesc, bdesc, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);
+        }
+        __syncwarp();
+        if (++stage == kStages) { stage = 0; phase ^= 1; }
+      }
+      if (lane == 0) umma_commit(&acc_full[buf]);
+      __syncwarp();
+      if (++buf == 2) { buf = 0; acc_phase ^= 1; }
+      x += nseg;
+    }
+  }
+  else if (MODE == 1 && warp >= 6) {
+    // ================================================================ RMSNorm statistics (+ gamma)
+    // Thread r owns row r of the A tile: it sums x^2 over the K blocks of the segment and, when a
+    // weight is given, rewrites the row as x * gamma before the MMA reads it.
+    const int row = (warp - 6) * 32 + lane;
+    const T* gamma = reinterpret_cast<const T*>(p.gamma);
+    int stage = 0, phase = 0, buf = 0, acc_phase = 0;
+    for (long long x = x0; x < x1;) {
+      const int tile = static_cast<int>(x / S), s0 = static_cast<int>(x - static_cast<long long>(tile) * S);
+      const int nseg = static_cast<int>(min(static_cast<long long>(S - s0), x1 - x));
+      const int kb0 = s0 * p.chunk_kblocks, kb1 = min((s0 + nseg) * p.chunk_kblocks, p.kblocks);
+      float sumsq = 0.f;
+      const bool row_live = (tile / p.tiles_n) * kBM + row < p.M;  // padded rows are all zero
+      for (int kb = kb0; kb < kb1; ++kb) {
+        mbar_wait(&full_bar[stage], phase, p.status, kFaultFullBarrier);
+        uint8_t* a_row = stages + stage * Plan::kStageBytes + row * 128;
+        if (row_live) {
+#pragma unroll
+          for (int lc = 0; lc < 8; ++lc) {
+            // logical 16-byte chunk lc of row r sits at physical chunk lc ^ (r & 7) (128-byte
+            // swizzle); eight consecutive rows therefore touch eight different bank groups
+            uint8_t* chunk = a_row + ((lc ^ (row & 7)) << 4);
+            uint4 raw = *reinterpret_cast<const uint4*>(chunk);
+            T* e = reinterpret_cast<T*>(&raw);
+            float f[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              f[j] = static_cast<float>(e[j]);
+              sumsq += f[j] * f[j];
+            }
+            if (gamma) {
+              const int k = kb * kBK + (lc << 3);
+              if (k < p.K) {  // K is a multiple of 8, so a chunk is inside or outside as a whole
+                const uint4 graw = __ldg(reinterpret_cast<const uint4*>(gamma + k));
+                const T* g = reinterpret_cast<const T*>(&graw);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) e[j] = static_cast<T>(f[j] * static_cast<float>(g[j]));
+                *reinterpret_cast<uint4*>(chunk) = raw;
+              }
+            }
+          }
+        }
+        if (gamma) fence_proxy_async_smem();  // generic-proxy writes must be visible to the MMA
+        __syncwarp();
+        if (lane == 0) {
+          if (gamma) mbar_arrive(&ready_bar[stage]);
+          mbar_arrive(&empty_bar[stage]);  // this warp is done with the stage
+        }
+        if (++stage == kStages) { stage = 0; phase ^= 1; }
+      }
+      mbar_wait(&rs_empty[buf], acc_phase ^ 1, p.status, kFaultTmemBarrier);
+      rowsum_smem[buf * kBM + row] = sumsq;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&rs_full[buf]);
+      if (++buf == 2) { buf = 0; acc_phase ^= 1; }
+      x += nseg;
+    }
+  } else if (warp >= 2 && warp < 6) {
+    // ================================================================ epilogue
+    const int quarter = warp & 3;  // the TMEM lanes this warp may read
+    const int row = quarter * 32 + lane;
+    const int etid = tid - 64;     // 0..127
+    T* yout = reinterpret_cast<T*>(p.y);
+    const float inv_k = 1.f / static_cast<float>(p.K);
+    int buf = 0, acc_phase = 0;
+
+    // v: 32 consecutive accumulator columns starting at tile column c0 (for MODE 2: gate and up)
+    auto finish_and_store = [&](const float* v, const float* up, int gr, int gc0, float rs) {
+      if (gr >= p.M) return;
+      float o[32];
+      if constexpr (MODE == 1) {
+        const float sc = rsqrtf(rs * inv_k + p.eps);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) o[j] = v[j] * sc;
+      } else if constexpr (MODE == 2) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) o[j] = v[j] / (1.f + __expf(-v[j])) * up[j];
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) o[j] = v[j];
+      }
+      T* dst = yout + static_cast<size_t>(gr) * p.N + gc0;
+#pragma unroll
+      for (int j = 0; j < 32; j += 8) {
+        if (gc0 + j < p.N) {
+          uint4 pk;
+          pk.x = pack2<T>(o[j], o[j + 1]);
+          pk.y = pack2<T>(o[j + 2], o[j + 3]);
+          pk.z = pack2<T>(o[j + 4], o[j + 5]);
+          pk.w = pack2<T>(o[j + 6], o[j + 7]);
+          *reinterpret_cast<uint4*>(dst + j) = pk;
+        }
+      }
+    };
+
+    for (long long x = x0; x < x1;) {
+      const int tile = static_cast<int>(x / S), s0 = static_cast<int>(x - static_cast<long long>(tile) * S);
+      const int nseg = static_cast<int>(min(static_cast<long long>(S - s0), x1 - x));
+      const int tm = tile / p.tiles_n, tn = tile - tm * p.tiles_n;
+      const int gr = tm * kBM + row;
+      const bool starts_here = s0 == 0, whole = starts_here && nseg == S;
+      mbar_wait(&acc_full[buf], acc_phase, p.status, kFaultMmaBarrier);
+      tc_fence_after();
+      float rs = 0.f;
+      if constexpr (MODE == 1) {
+        mbar_wait(&rs_full[buf], acc_phase, p.status, kFaultTmemBarrier);
+        rs = rowsum_smem[buf * kBM + row];
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&rs_empty[buf]);
+      }
+      const uint32_t t_acc = tmem_base + buf * kUmmaN + (static_cast<uint32_t>(quarter * 32) << 16);
+      if (whole) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < Plan::kTileN; c0 += 32) {
+          uint32_t r[32], r2[32];
+          tmem_ld_32x32(t_acc + c0, r);
+          if constexpr (MODE == 2) tmem_ld_32x32(t_acc + Plan::kTileN + c0, r2);
+          tmem_ld_wait();
+          finish_and_store(reinterpret_cast<float*>(r), reinterpret_cast<float*>(r2), gr,
+                           tn * Plan::kTileN + c0, rs);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[buf]);
+      } else {
+        // Partial layout: [column group of 32][row][32 floats], so that a warp (32 consecutive
+        // rows) reads and writes 4 KB contiguously; row sums follow the accumulator block.
+        float* slot = p.partials + (static_cast<size_t>(blockIdx.x) * 2 + (starts_here ? 1 : 0)) * Plan::kSlotFloats;
+        const bool live = gr < p.M;
+#pragma unroll 1
+        for (int c0 = 0; c0 < kUmmaN; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32(t_acc + c0, r);
+          tmem_ld_wait();
+          if (live) {
+            float4* dst = reinterpret_cast<float4*>(slot + (static_cast<size_t>(c0 >> 5) * kBM + row) * 32);
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              dst[j] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                   __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+          }
+        }
+        if constexpr (MODE == 1) slot[kBM * kUmmaN + row] = rs;
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[buf]);
+        __threadfence();
+        named_bar_sync(2, 128);
+        const long long first_chunk = static_cast<long long>(tile) * S;
+        const int c_first = cta_of_chunk(first_chunk, C, G), c_last = cta_of_chunk(first_chunk + S - 1, C, G);
+        if (etid == 0) {
+          const int old = atomicAdd(p.counters + tile, 1);
+          *flag = (old == c_last - c_first) ? 1 : 0;
+        }
+        named_bar_sync(2, 128);
+        if (*flag) {
+          __threadfence();
+          auto piece = [&](int c) {
+            return p.partials + (static_cast<size_t>(c) * 2 + (c == c_first ? 1 : 0)) * Plan::kSlotFloats;
+          };
+          float rs_all = 0.f;
+          if constexpr (MODE == 1) {
+            for (int c = c_first; c <= c_last; ++c) rs_all += __ldcg(piece(c) + kBM * kUmmaN + row);
+          }
+          if (live) {
+#pragma unroll 1
+            for (int c0 = 0; c0 < Plan::kTileN; c0 += 32) {
+              float v[32], up[32];
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = up[j] = 0.f;
+              const size_t off = (static_cast<size_t>(c0 >> 5) * kBM + row) * 32;
+              const size_t off_up = (static_cast<size_t>((Plan::kTileN + c0) >> 5) * kBM + row) * 32;
+              for (int c = c_first; c <= c_last; ++c) {  // fixed order: bit-stable sums
+                const float* src = piece(c);
+                float4 a4[8], b4[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {  // all loads of a piece are in flight together
+                  a4[j] = __ldcg(reinterpret_cast<const float4*>(src + off) + j);
+                  if constexpr (MODE == 2) b4[j] = __ldcg(reinterpret_cast<const float4*>(src + off_up) + j);
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  v[4 * j] += a4[j].x; v[4 * j + 1] += a4[j].y; v[4 * j + 2] += a4[j].z; v[4 * j + 3] += a4[j].w;
+                  if constexpr (MODE == 2) {
+                    up[4 * j] += b4[j].x; up[4 * j + 1] += b4[j].y; up[4 * j + 2] += b4[j].z; up[4 * j + 3] += b4[j].w;
+                  }
+                }
+              }
+              finish_and_store(v, up, gr, tn * Plan::kTileN + c0, rs_all);
+            }
+          }
+          if (etid == 0) p.counters[tile] = 0;  // ready for the next launch
+        }
+        named_bar_sync(2, 128);
+      }
+      if (++buf == 2) { buf = 0; acc_phase ^= 1; }
+      x += nseg;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------------------------- host side
+namespace {
+
+constexpr size_t kGemmSlotBytesMax = (static_cast<size_t>(kBM) * 256 + kBM) * 4;
+
+struct GemmSetup {
+  GemmParams p;
+  int mode, nbw, grid;
+  size_t ws_needed, partials_off, counters_off;
+  CUtensorMap tm_a, tm_b0, tm_b1;
+};
+
+int plan_gemm(const cb200_gemm_args* a, GemmSetup* s, bool need_maps) {
+  if (!a) return CB200_ERR_BAD_ARG;
+  if (a->m <= 0 || a->n <= 0 || a->k <= 0) return CB200_ERR_BAD_ARG;
+  if (a->op < CB200_GEMM_MATMUL || a->op > CB200_GEMM_SWIGLU) return CB200_ERR_BAD_ARG;
+  if (a->dtype != CB200_F16 && a->dtype != CB200_BF16) return CB200_ERR_UNSUPPORTED;
+  if (a->k % 8 || a->n % 8) return CB200_ERR_UNSUPPORTED;  // TMA strides are multiples of 16 bytes
+  const int sms = sm_count();
+  if (sms <= 0) return CB200_ERR_CUDA;
+  int grid_max = sms;
+  if (a->max_ctas > 0 && a->max_ctas < grid_max) grid_max = a->max_ctas;
+  s->mode = a->op;
+  GemmParams& p = s->p;
+  p = GemmParams{};
+  p.M = a->m; p.N = a->n; p.K = a->k;
+  p.eps = a->eps;
+  p.tiles_m = ceil_div(a->m, kBM);
+  // 256-column tiles when there are plenty of tiles, 128-column tiles otherwise (SwiGLU always
+  // pairs two 128-column accumulators).
+  s->nbw = 2;
+  if (a->op != CB200_GEMM_SWIGLU && static_cast<long long>(p.tiles_m) * ceil_div(a->n, 256) >= 2LL * grid_max) s->nbw = 4;
+  p.tiles_n = ceil_div(a->n, s->nbw * kChunkN);
+  p.kblocks = ceil_div(a->k, kBK);
+  const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
+  if (tiles >= (1LL << 24)) return CB200_ERR_UNSUPPORTED;
+  int split = a->split_k;
+  if (split <= 0) {  // pick the K split that gives every CTA several chunks
+    split = 1;
+    if (tiles % grid_max != 0)
+      while (split < 16 && tiles * split < 8LL * grid_max) split *= 2;
+  }
+  if (split > p.kblocks) split = p.kblocks;
+  p.chunk_kblocks = ceil_div(p.kblocks, split);
+  p.chunks_per_tile = ceil_div(p.kblocks, p.chunk_kblocks);
+  const long long chunks = tiles * p.chunks_per_tile;
+  s->grid = static_cast<int>(chunks < grid_max ? chunks : grid_max);
+  s->partials_off = kWsHeaderBytes;
+  s->counters_off = align_up(s->partials_off + static_cast<size_t>(sms) * 2 * kGemmSlotBytesMax, 256);
+  s->ws_needed = s->counters_off + static_cast<size_t>(tiles) * 4;
+  if (!need_maps) return CB200_OK;
+
+  if (!a->x || !a->w || !a->y) return CB200_ERR_BAD_ARG;
+  if (a->op == CB200_GEMM_SWIGLU && !a->w1) return CB200_ERR_BAD_ARG;
+  uintptr_t bits = reinterpret_cast<uintptr_t>(a->x) | reinterpret_cast<uintptr_t>(a->w) |
+                   reinterpret_cast<uintptr_t>(a->y) | reinterpret_cast<uintptr_t>(a->w1) |
+                   reinterpret_cast<uintptr_t>(a->gamma);
+  if (bits & 15) return CB200_ERR_ALIGNMENT;
+  if (!a->workspace || a->workspace_bytes < s->ws_needed) return CB200_ERR_WORKSPACE;
+  if (reinterpret_cast<uintptr_t>(a->workspace) & 255) return CB200_ERR_ALIGNMENT;
+  p.y = a->y;
+  p.gamma = a->op == CB200_GEMM_RMSNORM ? a->gamma : nullptr;
+  uint8_t* ws = static_cast<uint8_t*>(a->workspace);
+  p.status = reinterpret_cast<int*>(ws);
+  p.partials = reinterpret_cast<float*>(ws + s->partials_off);
+  p.counters = reinterpret_cast<int*>(ws + s->counters_off);
+
+  const CUtensorMapDataType dt = a->dtype == CB200_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  {
+    uint64_t dims[2] = {static_cast<uint64_t>(a->k), static_cast<uint64_t>(a->m)};
+    uint64_t strides[1] = {static_cast<uint64_t>(a->k) * 2};
+    uint32_t box[2] = {kBK, kBM};
+    if (!encode_tensor_map(&s->tm_a, dt, 2, const_cast<void*>(a->x), dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
+      return CB200_ERR_CUDA;
+  }
+  {
+    uint64_t dims[2] = {static_cast<uint64_t>(a->n), static_cast<uint64_t>(a->k)};
+    uint64_t strides[1] = {static_cast<uint64_t>(a->n) * 2};
+    uint32_t box[2] = {kChunkN, kBK};
+    if (!encode_tensor_map(&s->tm_b0, dt, 2, const_cast<void*>(a->w), dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
+      return CB200_ERR_CUDA;
+    const void* w1 = a->op == CB200_GEMM_SWIGLU ? a->w1 : a->w;
+    if (!encode_tensor_map(&s->tm_b1, dt, 2, const_cast<void*>(w1), dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
+      return CB200_ERR_CUDA;
+  }
+  return CB200_OK;
+}
+
+template <int MODE, typename T, int NBW>
+int launch_gemm(const GemmSetup& s, cudaStream_t stream) {
+  using Plan = GemmPlan<MODE, NBW>;
+  auto kern = gemm_kernel<MODE, T, NBW>;
+  static bool configured[64] = {false};
+  int dev = 0;
+  CB200_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev >= 64 || !configured[dev]) {
+    CB200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Plan::kSmemBytes));
+    if (dev < 64) configured[dev] = true;
+  }
+  kern<<<s.grid, Plan::kThreads, Plan::kSmemBytes, stream>>>(s.tm_a, s.tm_b0, s.tm_b1, s.p);
+  CB200_CUDA_TRY(cudaGetLastError());
+  return CB200_OK;
+}
+
+template <typename T>
+int dispatch_gemm(const GemmSetup& s, cudaStream_t st) {
+  switch (s.mode) {
+    case CB200_GEMM_MATMUL: return s.nbw == 4 ? launch_gemm<0, T, 4>(s, st) : launch_gemm<0, T, 2>(s, st);
+    case CB200_GEMM_RMSNORM: return s.nbw == 4 ? launch_gemm<1, T, 4>(s, st) : launch_gemm<1, T, 2>(s, st);
+    default: return launch_gemm<2, T, 2>(s, st);
+  }
+}
+
+}  // namespace
+}  // namespace cb200
+
+extern "C" size_t cb200_gemm_workspace_bytes(const cb200_gemm_args* a) {
+  cb200::GemmSetup s;
+  if (cb200::plan_gemm(a, &s, false) != CB200_OK) return 0;
+  return s.ws_needed;
+}
+
+extern "C" int cb200_gemm_effective_split(const cb200_gemm_args* a) {
+  cb200::GemmSetup s;
+  if (cb200::plan_gemm(a, &s, false) != CB200_OK) return 0;
+  return s.p.chunks_per_tile;
+}
+
+extern "C" int cb200_gemm(const cb200_gemm_args* a, void* stream) {
+  using namespace cb200;
+  GemmSetup s;
+  const int rc = plan_gemm(a, &s, true);
+  if (rc != CB200_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  return a->dtype == CB200_F16 ? dispatch_gemm<__half>(s, st) : dispatch_gemm<__nv_bfloat16>(s, st);
+}

@@ -154,3 +154,46 @@ def gqa_paged_decode_static_scratch(q, k_cache, v_cache, kv_indptr, kv_indices, 
                    max_ctas=max_ctas)
     _lib.check(_lib.lib().cb200_attn_decode_static_scratch(C.byref(a), _stream()))
     return out, lse
+
+
+def _gemm(op, x, w, w1=None, gamma=None, eps=0.0, split_k=0, out=None, max_ctas=0):
+    x, w = _cuda(x, "x"), _cuda(w, "w")
+    m, k = x.shape
+    k2, n = w.shape
+    if k2 != k or w.dtype != x.dtype:
+        raise ValueError(f"shapes/dtypes: x {tuple(x.shape)} {x.dtype}, w {tuple(w.shape)} {w.dtype}")
+    if w1 is not None and (_cuda(w1, "w1").shape != w.shape or w1.dtype != x.dtype):
+        raise ValueError("w1 must match w")
+    if gamma is not None and (_cuda(gamma, "gamma").numel() != k or gamma.dtype != x.dtype):
+        raise ValueError("gamma must hold K values of x's dtype")
+    if out is None:
+        out = torch.empty((m, n), dtype=x.dtype, device=x.device)
+    a = _lib.GemmArgs()
+    a.x, a.w, a.y = x.data_ptr(), w.data_ptr(), out.data_ptr()
+    a.w1 = None if w1 is None else w1.data_ptr()
+    a.gamma = None if gamma is None else gamma.data_ptr()
+    a.m, a.n, a.k, a.op, a.dtype = m, n, k, op, _dtype_code(x)
+    a.split_k, a.max_ctas, a.eps = int(split_k), int(max_ctas), float(eps)
+    need = _lib.lib().cb200_gemm_workspace_bytes(C.byref(a))
+    if need == 0:
+        _lib.check(_lib.lib().cb200_gemm(C.byref(a), _stream()))  # raises the real status
+    ws = workspace("gemm", need, x.device)
+    a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+    _lib.check(_lib.lib().cb200_gemm(C.byref(a), _stream()))
+    return out
+
+
+def matmul(x, w, *, split_k=0, out=None, max_ctas=0):
+    """``Y = X @ W`` (reference operator: demo/matmul.py:11-13); ``split_k`` is the plan's K split."""
+    return _gemm(_lib.GEMM_MATMUL, x, w, split_k=split_k, out=out, max_ctas=max_ctas)
+
+
+def rmsnorm_matmul(x, w, *, eps=0.0, gamma=None, split_k=0, out=None, max_ctas=0):
+    """``Y = (X * rsqrt(mean(X^2) + eps) [* gamma]) @ W`` (reference operator:
+    demo/rmsnorm_matmul.py:11-13 with python/cleave/frontend/composites.py:48-53)."""
+    return _gemm(_lib.GEMM_RMSNORM, x, w, gamma=gamma, eps=eps, split_k=split_k, out=out, max_ctas=max_ctas)
+
+
+def swiglu(x, w0, w1, *, split_k=0, out=None, max_ctas=0):
+    """``Y = silu(X @ W0) * (X @ W1)`` (reference operator: demo/swiglu.py:6-10)."""
+    return _gemm(_lib.GEMM_SWIGLU, x, w0, w1=w1, split_k=split_k, out=out, max_ctas=max_ctas)

@@ -106,6 +106,45 @@ size_t cb200_attn_decode_workspace_bytes(const cb200_attn_decode_args* a);
 int cb200_attn_decode(const cb200_attn_decode_args* a, void* stream);
 
 /* ------------------------------------------------------------------------------------------
+ * Fused dense contractions on the tcgen05 tensor cores. X is (m, k) row-major, W (and W1) are
+ * (k, n) row-major, Y is (m, n) row-major; k and n must be multiples of 8.
+ *   CB200_GEMM_MATMUL   Y = X @ W
+ *       replaces tests/graph/handwritten/expected_kernels/matmul.py and the split-K pair
+ *       matmul_splitk_partial.py + matmul_splitk_combine.py (operator demo/matmul.py:11-13)
+ *   CB200_GEMM_RMSNORM  Y = (X * rsqrt(mean_k(X^2) + eps) [* gamma]) @ W, fp32 statistics
+ *       replaces expected_kernels/rmsnorm_matmul.py and rmsnorm_matmul_split_{partial,combine}.py
+ *       (operator demo/rmsnorm_matmul.py:11-13, python/cleave/frontend/composites.py:48-53);
+ *       gamma (k) is an optional per-column weight of the normalised row, NULL = none
+ *   CB200_GEMM_SWIGLU   Y = silu(X @ W) * (X @ W1)
+ *       replaces expected_kernels/swiglu.py (operator demo/swiglu.py:6-10)
+ * split_k is the plan's split factor (K chunks per output tile, e.g. 4, 8, 16); 0 lets the
+ * library choose. The split-K combine is fused: one launch, partial tiles are summed in a fixed
+ * order by the last CTA to arrive, so results are bit-stable for a given (shape, split, grid).
+ * ---------------------------------------------------------------------------------------- */
+typedef enum { CB200_GEMM_MATMUL = 0, CB200_GEMM_RMSNORM = 1, CB200_GEMM_SWIGLU = 2 } cb200_gemm_op;
+
+typedef struct {
+  const void* x;     /* (m, k) */
+  const void* w;     /* (k, n) */
+  const void* w1;    /* (k, n), SwiGLU only */
+  const void* gamma; /* (k), RMSNorm only, may be NULL */
+  void* y;           /* (m, n) */
+  void* workspace;
+  size_t workspace_bytes;
+  int32_t m, n, k;
+  int32_t op;       /* cb200_gemm_op */
+  int32_t dtype;    /* cb200_dtype */
+  int32_t split_k;  /* 0 = auto */
+  int32_t max_ctas; /* 0 = one CTA per SM */
+  float eps;        /* RMSNorm only */
+} cb200_gemm_args;
+
+size_t cb200_gemm_workspace_bytes(const cb200_gemm_args* a);
+/* K chunks per output tile the launch will use (the requested split clamped to the K extent). */
+int cb200_gemm_effective_split(const cb200_gemm_args* a);
+int cb200_gemm(const cb200_gemm_args* a, void* stream);
+
+/* ------------------------------------------------------------------------------------------
  * Decode attention for callers that cannot allocate device memory. (No counterpart in the
  * reference, whose wrappers always own a torch-allocated scratch buffer.)
  *

@@ -1,0 +1,118 @@
+"""GPU parity of the tcgen05 GEMM family (through the C ABI) against the reference's golden
+vectors, the oracle, and size-independent properties."""
+
+import numpy as np
+import pytest
+import torch
+
+import cases
+from _util import assert_close, dev, host
+from oracle import cleave_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = cases.load_golden()
+
+
+def _ops():
+    from cleave_b200 import ops
+
+    return ops
+
+
+def _check_ws():
+    ops = _ops()
+    ops.check_workspace(ops.workspace("gemm", 0, "cuda"))
+
+
+def _run(family, inp, opt, split_k=0, max_ctas=0):
+    ops, dt = _ops(), opt["dtype"]
+    x, w0 = dev(inp["x"], dt), dev(inp["w0"], dt)
+    if family == "matmul":
+        y = ops.matmul(x, w0, split_k=split_k, max_ctas=max_ctas)
+    elif family == "rmsnorm_matmul":
+        g = dev(inp["gamma"], dt) if "gamma" in inp else None
+        y = ops.rmsnorm_matmul(x, w0, eps=opt["eps"], gamma=g, split_k=split_k, max_ctas=max_ctas)
+    else:
+        y = ops.swiglu(x, w0, dev(inp["w1"], dt), split_k=split_k, max_ctas=max_ctas)
+    _check_ws()
+    return host(y)
+
+
+GEMM_CASES = [n for n, c in cases.CASES.items() if c[0] in ("matmul", "rmsnorm_matmul", "swiglu")]
+
+
+@pytest.mark.parametrize("split_k", [0, 1, 4, 8])
+@pytest.mark.parametrize("name", GEMM_CASES)
+def test_gemm_family_matches_reference_golden(name, split_k):
+    family, inp, opt = cases.build(name)
+    assert_close(_run(family, inp, opt, split_k), GOLDEN[name][0])
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 128, 4096), (64, 1024, 4096), (1, 64, 64), (300, 520, 1000), (129, 136, 72)])
+@pytest.mark.parametrize("split_k", [0, 1, 4, 16])
+@pytest.mark.parametrize("dt", ["f16", "bf16"])
+def test_matmul_vs_oracle(m, n, k, split_k, dt):
+    inp = cases.gemm_inputs(m + n + k, m, n, k, dt)
+    got = _run("matmul", inp, {"dtype": dt}, split_k)
+    assert_close(got, orc.matmul(inp["x"], inp["w0"], dt))
+
+
+@pytest.mark.parametrize("m,n,k", [(64, 1280, 4096), (200, 264, 520)])
+@pytest.mark.parametrize("split_k", [0, 1, 8])
+@pytest.mark.parametrize("gamma", [False, True])
+def test_rmsnorm_matmul_vs_oracle(m, n, k, split_k, gamma):
+    inp = cases.gemm_inputs(7, m, n, k, "f16", gamma=gamma)
+    got = _run("rmsnorm_matmul", inp, {"dtype": "f16", "eps": 1e-6}, split_k)
+    assert_close(got, orc.rmsnorm_matmul(inp["x"], inp["w0"], 1e-6, inp.get("gamma"), "f16"))
+
+
+@pytest.mark.parametrize("m,n,k", [(256, 512, 1024), (70, 200, 328)])
+@pytest.mark.parametrize("split_k", [0, 1, 4])
+def test_swiglu_vs_oracle(m, n, k, split_k):
+    inp = cases.gemm_inputs(8, m, n, k, "bf16", n_w=2)
+    got = _run("swiglu", inp, {"dtype": "bf16"}, split_k)
+    assert_close(got, orc.swiglu(inp["x"], inp["w0"], inp["w1"], "bf16"))
+
+
+def test_split_k_partials_sum_like_the_unsplit_product():
+    """Reference: tests/pipeline_api/test_e2e.py:58-81 (the split-K chain equals x.float() @ w.float());
+    here every split factor and every grid size must agree with the unsplit launch to fp32 round-off."""
+    inp = cases.gemm_inputs(3, 128, 128, 4096, "f16")
+    base = _run("matmul", inp, {"dtype": "f16"}, 1)
+    for split_k, max_ctas in [(4, 0), (8, 0), (16, 0), (16, 3), (64, 0)]:
+        got = _run("matmul", inp, {"dtype": "f16"}, split_k, max_ctas)
+        np.testing.assert_allclose(got, base, rtol=2e-3, atol=2e-3)
+
+
+def test_repeat_launches_are_bit_identical():
+    inp = cases.gemm_inputs(4, 64, 1024, 2048, "f16", gamma=True)
+    a = _run("rmsnorm_matmul", inp, {"dtype": "f16", "eps": 1e-6}, 8)
+    b = _run("rmsnorm_matmul", inp, {"dtype": "f16", "eps": 1e-6}, 8)
+    assert np.array_equal(a, b)
+
+
+def test_linearity_at_full_rmsnorm_config():
+    """BASELINE config 2 at full size (M 64, K 4096, N 11008, fp16): compared with the oracle, and
+    scaling X by 2 leaves RMSNorm(X) @ W unchanged (the norm is scale-invariant when eps is tiny)."""
+    g = torch.Generator(device="cpu").manual_seed(0)
+    x = torch.randn(64, 4096, generator=g).half()
+    gamma = (1 + 0.1 * torch.randn(4096, generator=g)).half()
+    w = (torch.randn(4096, 11008, generator=g) / 64).half()
+    ops = _ops()
+    y = ops.rmsnorm_matmul(x.cuda(), w.cuda(), eps=1e-6, gamma=gamma.cuda())
+    y2 = ops.rmsnorm_matmul((2 * x).cuda(), w.cuda(), eps=1e-6, gamma=gamma.cuda())
+    _check_ws()
+    assert_close(host(y), host(y2), rtol=4e-3, atol=4e-3)
+    want = orc.rmsnorm_matmul(x.float().numpy(), w.float().numpy(), 1e-6, gamma.float().numpy(), "f16")
+    assert_close(host(y), want)
+
+
+def test_gemm_bad_arguments():
+    from cleave_b200 import Cb200Error
+
+    ops = _ops()
+    x = torch.zeros(8, 60, dtype=torch.float16, device="cuda")
+    w = torch.zeros(60, 64, dtype=torch.float16, device="cuda")
+    with pytest.raises(Cb200Error):
+        ops.matmul(x, w)  # K not a multiple of 8

@@ -12,7 +12,7 @@
 // waits, bit-stable results).
 //
 // Warp roles: 0 = TMA producer, 1 = MMA issuer (one elected thread) and TMEM owner,
-// 2..5 = epilogue (TMEM -> registers -> global), 6..9 = RMSNorm statistics / gamma scaling of the
+// 2..5 = epilogue (TMEM -> registers -> global), 6..13 = RMSNorm statistics / gamma scaling of the
 // A tile in shared memory (MODE 1 only). Two TMEM accumulators let the epilogue of one tile
 // overlap the main loop of the next.
 //
@@ -25,6 +25,7 @@
 #include "common.cuh"
 
 #include <cstring>
+#include <cstdlib>
 #include <type_traits>
 
 namespace cb200 {
@@ -47,6 +48,8 @@ struct GemmParams {
   int chunk_kblocks;   // K blocks per chunk
   int chunks_per_tile; // S
   float eps;
+  int a_rows;  // rows of the A box: 128, or M rounded up to 8 when M is smaller
+  int debug;
 };
 
 template <int MODE, int NBW>
@@ -57,9 +60,9 @@ struct GemmPlan {
   static constexpr int kTileN = NBW * kChunkN;       // output columns per tile
   static constexpr int kStageBytes = kABytes + kNBT * kBChunkBytes;
   static constexpr int kStages = kNBT == 2 ? 6 : 4;
-  static constexpr int kThreads = MODE == 1 ? 320 : 192;
+  static constexpr int kThreads = MODE == 1 ? 448 : 192;
   static constexpr int kSlotFloats = kBM * kUmmaN + kBM;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 2048 /*barriers, rowsums*/ + 1024 /*alignment*/;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 4096 /*barriers, rowsums*/ + 1024 /*alignment*/;
 };
 
 // Which CTA owns chunk x when C chunks are dealt as floor(c * C / G) .. floor((c + 1) * C / G).
@@ -90,9 +93,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
   uint64_t* rs_empty = rs_full + 2;                          // [2]
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(rs_empty + 2);
   int* flag = reinterpret_cast<int*>(tmem_holder + 1);
-  float* rowsum_smem = reinterpret_cast<float*>(misc + 512);  // [2][128]
+  float* rowsum_smem = reinterpret_cast<float*>(misc + 512);  // [2 accumulators][2 groups][128]
+  float* rs_red = reinterpret_cast<float*>(misc + 2560);      // [128] row sums of a reduced tile
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const long long dbg_t0 = clock64();
 
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -104,7 +109,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
       mbar_init(&acc_full[b], 1);
       // one arrival per warp (after __syncwarp): arrivals on one mbarrier serialise
       mbar_init(&acc_empty[b], 4);
-      mbar_init(&rs_full[b], 4);
+      mbar_init(&rs_full[b], 8);
       mbar_init(&rs_empty[b], 4);
     }
     mbar_fence_init();
@@ -121,6 +126,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_holder);
 
+  const long long dbg_t1 = clock64();
   // ---- this CTA's share of the (tile, chunk) list
   const int S = p.chunks_per_tile;
   const long long C = static_cast<long long>(p.tiles_m) * p.tiles_n * S;
@@ -141,7 +147,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         if (lane == 0) {
           uint8_t* a_dst = stages + stage * Plan::kStageBytes;
           uint8_t* b_dst = a_dst + kABytes;
-          mbar_arrive_expect_tx(&full_bar[stage], Plan::kStageBytes);
+          // rows of the A tile beyond a_rows are never fetched; the MMA reads whatever is there,
+          // and the rows of D they produce are never stored
+          mbar_arrive_expect_tx(&full_bar[stage], Plan::kStageBytes - (kBM - p.a_rows) * kBK * 2);
           tma_load_2d(a_dst, &tm_a, &full_bar[stage], kb * kBK, tm * kBM);
 #pragma unroll
           for (int j = 0; j < NBW; ++j)
@@ -158,6 +166,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
       }
       x += nseg;
     }
+    if ((p.debug & 2) && lane == 0 && blockIdx.x == 0) { p.status[16] = (int)(dbg_t1 - dbg_t0); p.status[17] = (int)(clock64() - dbg_t0); }
   } else if (warp == 1) {
     // ================================================================ MMA issuer
     constexpr uint32_t idesc = umma_idesc(std::is_same<T, __nv_bfloat16>::value, true, kBM, kUmmaN);
@@ -191,6 +200,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
       }
       if (lane == 0) umma_commit(&acc_full[buf]);
       __syncwarp();
+      if ((p.debug & 2) && lane == 0 && blockIdx.x == 0) p.status[18] = (int)(clock64() - dbg_t0);
       if (++buf == 2) { buf = 0; acc_phase ^= 1; }
       x += nseg;
     }
@@ -199,54 +209,78 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     // ================================================================ RMSNorm statistics (+ gamma)
     // Thread r owns row r of the A tile: it sums x^2 over the K blocks of the segment and, when a
     // weight is given, rewrites the row as x * gamma before the MMA reads it.
-    const int row = (warp - 6) * 32 + lane;
+    // Two groups of four warps take alternate K blocks, so that two TMA -> scale -> MMA chains
+    // are in flight; the number of stages is even, so a stage always belongs to the same group.
+    const int group = (warp - 6) >> 2;
+    const int row = ((warp - 6) & 3) * 32 + lane;
     const T* gamma = reinterpret_cast<const T*>(p.gamma);
-    int stage = 0, phase = 0, buf = 0, acc_phase = 0;
+    int stage = 0, phase = 0, buf = 0, acc_phase = 0, kb_count = 0;
     for (long long x = x0; x < x1;) {
       const int tile = static_cast<int>(x / S), s0 = static_cast<int>(x - static_cast<long long>(tile) * S);
       const int nseg = static_cast<int>(min(static_cast<long long>(S - s0), x1 - x));
       const int kb0 = s0 * p.chunk_kblocks, kb1 = min((s0 + nseg) * p.chunk_kblocks, p.kblocks);
       float sumsq = 0.f;
       const bool row_live = (tile / p.tiles_n) * kBM + row < p.M;  // padded rows are all zero
-      for (int kb = kb0; kb < kb1; ++kb) {
-        mbar_wait(&full_bar[stage], phase, p.status, kFaultFullBarrier);
-        uint8_t* a_row = stages + stage * Plan::kStageBytes + row * 128;
-        if (row_live) {
+      for (int kb = kb0; kb < kb1; ++kb, ++kb_count) {
+        if ((kb_count & 1) != group) {
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+          continue;
+        }
+        // gamma for this K block is fetched before the wait: its latency is off the
+        // TMA -> scale -> MMA chain. (K is a multiple of 8: a chunk is inside or outside whole.)
+        uint4 graw[8];
+        if (gamma && row_live) {
 #pragma unroll
           for (int lc = 0; lc < 8; ++lc) {
-            // logical 16-byte chunk lc of row r sits at physical chunk lc ^ (r & 7) (128-byte
-            // swizzle); eight consecutive rows therefore touch eight different bank groups
-            uint8_t* chunk = a_row + ((lc ^ (row & 7)) << 4);
-            uint4 raw = *reinterpret_cast<const uint4*>(chunk);
-            T* e = reinterpret_cast<T*>(&raw);
-            float f[8];
+            const int k = kb * kBK + (lc << 3);
+            graw[lc] = k < p.K ? __ldg(reinterpret_cast<const uint4*>(gamma + k)) : make_uint4(0u, 0u, 0u, 0u);
+          }
+        }
+        mbar_wait(&full_bar[stage], phase, p.status, kFaultFullBarrier);
+        uint8_t* a_row = stages + stage * Plan::kStageBytes + row * 128;
+        // logical 16-byte chunk lc of row r sits at physical chunk lc ^ (r & 7) (128-byte swizzle);
+        // eight consecutive rows therefore touch eight different bank groups.
+        uint4 raw[8];
+        if (row_live) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              f[j] = static_cast<float>(e[j]);
-              sumsq += f[j] * f[j];
-            }
-            if (gamma) {
-              const int k = kb * kBK + (lc << 3);
-              if (k < p.K) {  // K is a multiple of 8, so a chunk is inside or outside as a whole
-                const uint4 graw = __ldg(reinterpret_cast<const uint4*>(gamma + k));
-                const T* g = reinterpret_cast<const T*>(&graw);
+          for (int lc = 0; lc < 8; ++lc) raw[lc] = *reinterpret_cast<const uint4*>(a_row + ((lc ^ (row & 7)) << 4));
+          if (gamma) {  // the MMA waits for this: scale, store, publish - statistics come after
 #pragma unroll
-                for (int j = 0; j < 8; ++j) e[j] = static_cast<T>(f[j] * static_cast<float>(g[j]));
-                *reinterpret_cast<uint4*>(chunk) = raw;
-              }
+            for (int lc = 0; lc < 8; ++lc) {
+              uint4 sc;
+              sc.x = mul2<T>(raw[lc].x, graw[lc].x);
+              sc.y = mul2<T>(raw[lc].y, graw[lc].y);
+              sc.z = mul2<T>(raw[lc].z, graw[lc].z);
+              sc.w = mul2<T>(raw[lc].w, graw[lc].w);
+              *reinterpret_cast<uint4*>(a_row + ((lc ^ (row & 7)) << 4)) = sc;
             }
           }
         }
-        if (gamma) fence_proxy_async_smem();  // generic-proxy writes must be visible to the MMA
-        __syncwarp();
-        if (lane == 0) {
-          if (gamma) mbar_arrive(&ready_bar[stage]);
-          mbar_arrive(&empty_bar[stage]);  // this warp is done with the stage
+        if (gamma) {
+          fence_proxy_async_smem();  // generic-proxy writes must be visible to the MMA
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&ready_bar[stage]);
         }
+        if (row_live) {
+          // four independent partial sums keep the FMA chain short
+          float part[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int lc = 0; lc < 8; ++lc) {
+            const T* e = reinterpret_cast<const T*>(&raw[lc]);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float f = static_cast<float>(e[j]);
+              part[j & 3] += f * f;
+            }
+          }
+          sumsq += (part[0] + part[1]) + (part[2] + part[3]);
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty_bar[stage]);  // this warp is done with the stage
         if (++stage == kStages) { stage = 0; phase ^= 1; }
       }
       mbar_wait(&rs_empty[buf], acc_phase ^ 1, p.status, kFaultTmemBarrier);
-      rowsum_smem[buf * kBM + row] = sumsq;
+      rowsum_smem[(buf * 2 + group) * kBM + row] = sumsq;
       __syncwarp();
       if (lane == 0) mbar_arrive(&rs_full[buf]);
       if (++buf == 2) { buf = 0; acc_phase ^= 1; }
@@ -298,10 +332,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
       const bool starts_here = s0 == 0, whole = starts_here && nseg == S;
       mbar_wait(&acc_full[buf], acc_phase, p.status, kFaultMmaBarrier);
       tc_fence_after();
+      if ((p.debug & 2) && etid == 0 && blockIdx.x == 0) p.status[19] = (int)(clock64() - dbg_t0);
       float rs = 0.f;
       if constexpr (MODE == 1) {
         mbar_wait(&rs_full[buf], acc_phase, p.status, kFaultTmemBarrier);
-        rs = rowsum_smem[buf * kBM + row];
+        rs = rowsum_smem[(buf * 2) * kBM + row] + rowsum_smem[(buf * 2 + 1) * kBM + row];
         __syncwarp();
         if (lane == 0) mbar_arrive(&rs_empty[buf]);
       }
@@ -355,41 +390,109 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
           auto piece = [&](int c) {
             return p.partials + (static_cast<size_t>(c) * 2 + (c == c_first ? 1 : 0)) * Plan::kSlotFloats;
           };
-          float rs_all = 0.f;
+          // The reduction is latency-bound (every piece comes from L2), so the work is spread
+          // flat over all 128 threads - items of 8 columns, whatever the number of live rows -
+          // and the loads of several items and several pieces are put in flight before any add.
+          // Pieces are added in CTA order: the sum is bit-stable.
           if constexpr (MODE == 1) {
-            for (int c = c_first; c <= c_last; ++c) rs_all += __ldcg(piece(c) + kBM * kUmmaN + row);
+            float rs_all = 0.f;
+            for (int cb = c_first; cb <= c_last; cb += 4) {  // four loads in flight, added in order
+              float t[4];
+#pragma unroll
+              for (int q = 0; q < 4; ++q) t[q] = cb + q <= c_last ? __ldcg(piece(cb + q) + kBM * kUmmaN + row) : 0.f;
+#pragma unroll
+              for (int q = 0; q < 4; ++q) rs_all += t[q];
+            }
+            rs_red[row] = rs_all;
+            named_bar_sync(3, 128);
           }
-          if (live) {
+          constexpr int kItemsPerRow = Plan::kTileN / 8;
+          constexpr int kU = 4;                      // items per thread per step
+          constexpr int kPB = MODE == 2 ? 2 : 3;     // pieces loaded together
+          const int rows_live = min(kBM, p.M - tm * kBM);
+          const int items = rows_live * kItemsPerRow;
 #pragma unroll 1
-            for (int c0 = 0; c0 < Plan::kTileN; c0 += 32) {
-              float v[32], up[32];
+          for (int it0 = 0; it0 < items; it0 += 128 * kU) {
+            float v[kU][8], up[kU][8];
+            size_t off[kU];
+            bool ok[kU];
 #pragma unroll
-              for (int j = 0; j < 32; ++j) v[j] = up[j] = 0.f;
-              const size_t off = (static_cast<size_t>(c0 >> 5) * kBM + row) * 32;
-              const size_t off_up = (static_cast<size_t>((Plan::kTileN + c0) >> 5) * kBM + row) * 32;
-              for (int c = c_first; c <= c_last; ++c) {  // fixed order: bit-stable sums
-                const float* src = piece(c);
-                float4 a4[8], b4[8];
+            for (int u = 0; u < kU; ++u) {
+              const int it = it0 + u * 128 + etid;
+              ok[u] = it < items;
+              const int r = ok[u] ? it / kItemsPerRow : 0, col = ok[u] ? (it % kItemsPerRow) * 8 : 0;
+              off[u] = (static_cast<size_t>(col >> 5) * kBM + r) * 32 + (col & 31);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {  // all loads of a piece are in flight together
-                  a4[j] = __ldcg(reinterpret_cast<const float4*>(src + off) + j);
-                  if constexpr (MODE == 2) b4[j] = __ldcg(reinterpret_cast<const float4*>(src + off_up) + j);
-                }
+              for (int j = 0; j < 8; ++j) v[u][j] = up[u][j] = 0.f;
+            }
+#pragma unroll 1
+            for (int cb = c_first; cb <= c_last; cb += kPB) {
+              float4 ld[kPB][kU][2], ld_up[kPB][kU][2];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                  v[4 * j] += a4[j].x; v[4 * j + 1] += a4[j].y; v[4 * j + 2] += a4[j].z; v[4 * j + 3] += a4[j].w;
-                  if constexpr (MODE == 2) {
-                    up[4 * j] += b4[j].x; up[4 * j + 1] += b4[j].y; up[4 * j + 2] += b4[j].z; up[4 * j + 3] += b4[j].w;
+              for (int q = 0; q < kPB; ++q) {
+                const bool have = cb + q <= c_last;
+                const float* src = piece(have ? cb + q : cb);
+#pragma unroll
+                for (int u = 0; u < kU; ++u) {
+#pragma unroll
+                  for (int h = 0; h < 2; ++h) {
+                    ld[q][u][h] = (have && ok[u]) ? __ldcg(reinterpret_cast<const float4*>(src + off[u]) + h)
+                                                  : make_float4(0.f, 0.f, 0.f, 0.f);
+                    if constexpr (MODE == 2)
+                      ld_up[q][u][h] = (have && ok[u])
+                                           ? __ldcg(reinterpret_cast<const float4*>(src + off[u] + (Plan::kTileN >> 5) * kBM * 32) + h)
+                                           : make_float4(0.f, 0.f, 0.f, 0.f);
                   }
                 }
               }
-              finish_and_store(v, up, gr, tn * Plan::kTileN + c0, rs_all);
+#pragma unroll
+              for (int q = 0; q < kPB; ++q) {
+#pragma unroll
+                for (int u = 0; u < kU; ++u) {
+#pragma unroll
+                  for (int h = 0; h < 2; ++h) {
+                    v[u][4 * h] += ld[q][u][h].x; v[u][4 * h + 1] += ld[q][u][h].y;
+                    v[u][4 * h + 2] += ld[q][u][h].z; v[u][4 * h + 3] += ld[q][u][h].w;
+                    if constexpr (MODE == 2) {
+                      up[u][4 * h] += ld_up[q][u][h].x; up[u][4 * h + 1] += ld_up[q][u][h].y;
+                      up[u][4 * h + 2] += ld_up[q][u][h].z; up[u][4 * h + 3] += ld_up[q][u][h].w;
+                    }
+                  }
+                }
+              }
+            }
+#pragma unroll
+            for (int u = 0; u < kU; ++u) {
+              if (!ok[u]) continue;
+              const int it = it0 + u * 128 + etid;
+              const int r = it / kItemsPerRow, col = (it % kItemsPerRow) * 8;
+              const int gcol = tn * Plan::kTileN + col;
+              if (gcol >= p.N) continue;
+              float o[8];
+              if constexpr (MODE == 1) {
+                const float sc = rsqrtf(rs_red[r] * inv_k + p.eps);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) o[j] = v[u][j] * sc;
+              } else if constexpr (MODE == 2) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) o[j] = v[u][j] / (1.f + __expf(-v[u][j])) * up[u][j];
+              } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) o[j] = v[u][j];
+              }
+              uint4 pk;
+              pk.x = pack2<T>(o[0], o[1]);
+              pk.y = pack2<T>(o[2], o[3]);
+              pk.z = pack2<T>(o[4], o[5]);
+              pk.w = pack2<T>(o[6], o[7]);
+              *reinterpret_cast<uint4*>(yout + static_cast<size_t>(tm * kBM + r) * p.N + gcol) = pk;
             }
           }
           if (etid == 0) p.counters[tile] = 0;  // ready for the next launch
         }
         named_bar_sync(2, 128);
       }
+      if ((p.debug & 2) && etid == 0 && blockIdx.x == 0) p.status[20] = (int)(clock64() - dbg_t0);
       if (++buf == 2) { buf = 0; acc_phase ^= 1; }
       x += nseg;
     }
@@ -430,7 +533,9 @@ int plan_gemm(const cb200_gemm_args* a, GemmSetup* s, bool need_maps) {
   p = GemmParams{};
   p.M = a->m; p.N = a->n; p.K = a->k;
   p.eps = a->eps;
+  p.debug = getenv("CB200_DEBUG") ? atoi(getenv("CB200_DEBUG")) : 0;
   p.tiles_m = ceil_div(a->m, kBM);
+  p.a_rows = a->m >= kBM ? kBM : (a->m + 7) / 8 * 8;
   // 256-column tiles when there are plenty of tiles, 128-column tiles otherwise (SwiGLU always
   // pairs two 128-column accumulators).
   s->nbw = 2;
@@ -474,7 +579,7 @@ int plan_gemm(const cb200_gemm_args* a, GemmSetup* s, bool need_maps) {
   {
     uint64_t dims[2] = {static_cast<uint64_t>(a->k), static_cast<uint64_t>(a->m)};
     uint64_t strides[1] = {static_cast<uint64_t>(a->k) * 2};
-    uint32_t box[2] = {kBK, kBM};
+    uint32_t box[2] = {kBK, static_cast<uint32_t>(p.a_rows)};
     if (!encode_tensor_map(&s->tm_a, dt, 2, const_cast<void*>(a->x), dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
       return CB200_ERR_CUDA;
   }

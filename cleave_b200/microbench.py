@@ -1,0 +1,122 @@
+"""Per-operator timing of the kernel library on the benchmark configurations.
+
+    python -m cleave_b200.microbench                      # every configuration, one line each
+    python -m cleave_b200.microbench --op rmsnorm_matmul --m 4096 --n 14336 --k 4096 --launches 3
+
+Timing follows the reference's protocol (python/cleave/runtime/timer.py:76-108,
+python/cleave/runtime/autotune.py:36-43): CUDA events around CUDA-graph replays, minimum over
+rounds. ``--launches N`` instead runs N plain launches after a warm-up (what a profiler capture
+wants) and prints nothing but a completion line.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+from . import ops
+from .runtime.timer import min_launch_us
+
+NOMINAL_HBM_GBS, NOMINAL_TFLOPS = 8000.0, 2250.0
+
+
+def _peaks():
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            d = json.load(f)
+        return float(d["hbm_gbs"]), float(d["bf16_tflops"]), "measured"
+    except Exception:  # noqa: BLE001
+        return 6650.0, 1590.0, "fallback"
+
+
+def _gen(seed=0):
+    return torch.Generator(device="cpu").manual_seed(seed)
+
+
+def gemm_case(op, m, n, k, dtype=torch.float16, gamma=True, split_k=0):
+    """(callable, flops, algorithmic bytes) for one GEMM-family configuration."""
+    g = _gen()
+    x = torch.randn(m, k, generator=g).to(dtype).cuda()
+    w0 = (torch.randn(k, n, generator=g) / k ** 0.5).to(dtype).cuda()
+    out = torch.empty(m, n, dtype=dtype, device="cuda")
+    esz = 2
+    if op == "matmul":
+        return (lambda: ops.matmul(x, w0, split_k=split_k, out=out)), 2 * m * n * k, (m * k + k * n + m * n) * esz
+    if op == "rmsnorm_matmul":
+        gm = (1 + 0.1 * torch.randn(k, generator=g)).to(dtype).cuda() if gamma else None
+        fn = lambda: ops.rmsnorm_matmul(x, w0, eps=1e-6, gamma=gm, split_k=split_k, out=out)  # noqa: E731
+        return fn, 2 * m * n * k, (m * k + k * n + m * n + (k if gamma else 0)) * esz
+    if op == "swiglu":
+        w1 = (torch.randn(k, n, generator=g) / k ** 0.5).to(dtype).cuda()
+        return (lambda: ops.swiglu(x, w0, w1, split_k=split_k, out=out)), 4 * m * n * k, (m * k + 2 * k * n + m * n) * esz
+    raise KeyError(op)
+
+
+def gqa_decode_case(batch=8, hq=32, hkv=8, d=128, skv=8192, dtype=torch.float16):
+    g = _gen()
+    q = torch.randn(batch * hq, 1, d, generator=g).to(dtype).cuda()
+    k = torch.randn(batch * hkv, skv, d, generator=g).to(dtype).cuda()
+    v = torch.randn(batch * hkv, skv, d, generator=g).to(dtype).cuda()
+    out = torch.empty_like(q)
+    byts = (2 * k.numel() + 2 * q.numel()) * 2
+    return (lambda: ops.attention_decode(q, k, v, out=out)), 4 * batch * hq * skv * d, byts
+
+
+CONFIGS = {
+    "cfg1_matmul_128x128x4096": lambda: gemm_case("matmul", 128, 128, 4096),
+    "cfg2_rmsnorm_matmul_64x11008x4096": lambda: gemm_case("rmsnorm_matmul", 64, 11008, 4096),
+    "demo_rmsnorm_matmul_4096x14336x4096": lambda: gemm_case("rmsnorm_matmul", 4096, 14336, 4096, gamma=False),
+    "demo_matmul_4096x14336x4096": lambda: gemm_case("matmul", 4096, 14336, 4096),
+    "demo_swiglu_4096x14336x4096": lambda: gemm_case("swiglu", 4096, 14336, 4096),
+    "cfg3_gqa_decode_b8_h32_kv8_d128_s8192": lambda: gqa_decode_case(),
+}
+
+
+def measure(name, build):
+    fn, flops, byts = build()
+    us = min_launch_us(fn, [], batch=20, repeats=5)
+    hbm, tf, kind = _peaks()
+    gbs, tfs = byts / us / 1e3, flops / us / 1e6
+    return {"config": name, "us": us, "GB/s": gbs, "TFLOP/s": tfs,
+            "hbm_frac": gbs / hbm, "tensor_frac": tfs / tf, "peaks": f"of {kind}",
+            "hbm_frac_nominal": gbs / NOMINAL_HBM_GBS, "tensor_frac_nominal": tfs / NOMINAL_TFLOPS}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--op", default=None, choices=["matmul", "rmsnorm_matmul", "swiglu", "gqa_decode"])
+    ap.add_argument("--m", type=int, default=4096)
+    ap.add_argument("--n", type=int, default=4096)
+    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--split-k", type=int, default=0)
+    ap.add_argument("--no-gamma", action="store_true")
+    ap.add_argument("--launches", type=int, default=0)
+    ap.add_argument("--only", default=None, help="substring filter on the configuration names")
+    a = ap.parse_args()
+    if a.op:
+        if a.op == "gqa_decode":
+            build = gqa_decode_case
+        else:
+            build = lambda: gemm_case(a.op, a.m, a.n, a.k, gamma=not a.no_gamma, split_k=a.split_k)  # noqa: E731
+        if a.launches:
+            fn, _, _ = build()
+            for _ in range(3 + a.launches):
+                fn()
+            torch.cuda.synchronize()
+            print(f"ran {a.launches} launches of {a.op}")
+            return
+        print(json.dumps(measure(f"{a.op}_{a.m}x{a.n}x{a.k}", build)))
+        return
+    for name, build in CONFIGS.items():
+        if a.only and a.only not in name:
+            continue
+        print(json.dumps(measure(name, build)), flush=True)
+        torch.cuda.empty_cache()
+
+
+if __name__ == "__main__":
+    main()

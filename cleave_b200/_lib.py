@@ -48,6 +48,17 @@ class GemmArgs(C.Structure):
 
 GEMM_MATMUL, GEMM_RMSNORM, GEMM_SWIGLU = 0, 1, 2
 
+
+class MlaDecodeArgs(C.Structure):
+    _fields_ = [
+        ("q_nope", C.c_void_p), ("q_pe", C.c_void_p), ("ckv_cache", C.c_void_p), ("kpe_cache", C.c_void_p),
+        ("kv_indptr", C.c_void_p), ("kv_indices", C.c_void_p), ("out", C.c_void_p), ("lse", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("batch", C.c_int32), ("num_heads", C.c_int32), ("ckv_dim", C.c_int32), ("kpe_dim", C.c_int32),
+        ("page_size", C.c_int32), ("num_pages", C.c_int32), ("num_kv_indices", C.c_int32),
+        ("kv_len", C.c_int32), ("dtype", C.c_int32), ("max_ctas", C.c_int32), ("sm_scale", C.c_float),
+    ]
+
 _lib = None
 
 
@@ -80,6 +91,10 @@ def lib() -> C.CDLL:
         L.cb200_gemm_effective_split.argtypes = [C.POINTER(GemmArgs)]
         L.cb200_gemm.restype = C.c_int
         L.cb200_gemm.argtypes = [C.POINTER(GemmArgs), C.c_void_p]
+        L.cb200_mla_decode_workspace_bytes.restype = C.c_size_t
+        L.cb200_mla_decode_workspace_bytes.argtypes = [C.POINTER(MlaDecodeArgs)]
+        L.cb200_mla_decode.restype = C.c_int
+        L.cb200_mla_decode.argtypes = [C.POINTER(MlaDecodeArgs), C.c_void_p]
         _lib = L
     return _lib
 

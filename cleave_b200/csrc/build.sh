@@ -9,7 +9,7 @@ mkdir -p "$HERE/build"
 pids=""
 for f in "$HERE"/*.cu; do
   o="$HERE/build/$(basename "$f" .cu).o"
-  if [ ! -f "$o" ] || [ "$f" -nt "$o" ] || [ "$HERE/common.cuh" -nt "$o" ] || [ "$HERE/../../include/cleave_b200.h" -nt "$o" ]; then
+  if [ ! -f "$o" ] || [ "$f" -nt "$o" ] || [ "$HERE/common.cuh" -nt "$o" ] || [ "$HERE/stream_walk.cuh" -nt "$o" ] || [ "$HERE/../../include/cleave_b200.h" -nt "$o" ]; then
     $NVCC $FLAGS $EXTRA_NVCC_FLAGS -c "$f" -o "$o" &
     pids="$pids $!"
   fi

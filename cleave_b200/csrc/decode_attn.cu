@@ -15,6 +15,7 @@
 // python/cleave/dynamic/paging/builders/slab.py:132-142.
 
 #include "common.cuh"
+#include "stream_walk.cuh"
 
 #include <cstring>
 #include <mutex>
@@ -60,41 +61,6 @@ __device__ __forceinline__ int item_valid_len(const DecodeParams& p, int b) {
   const int v = max(n_pages - 1, 0) * p.page_size + max(p.kv_last[b], 0);
   return max(min(v, n_pages * p.page_size), 0);
 }
-
-// The walk over a CTA's share of the tile stream; identical in the producer and the consumers.
-struct Piece {
-  int b, hv, tile0, count, n_tiles, unit0;  // unit0: stream position of the item's first tile
-};
-
-struct Walker {
-  const int* P;  // tile prefix per request (paged) or nullptr
-  int batch, hkvv, tiles_per_req;
-  __device__ __forceinline__ Piece at(int u, int u_end) const {
-    Piece pc;
-    int base;
-    if (P) {
-      const int key = u / hkvv;
-      int lo = 0, hi = batch;  // largest b with P[b] <= key
-      while (hi - lo > 1) {
-        const int mid = (lo + hi) >> 1;
-        if (P[mid] <= key) lo = mid; else hi = mid;
-      }
-      pc.b = lo;
-      pc.n_tiles = P[lo + 1] - P[lo];
-      base = hkvv * P[lo];
-    } else {
-      pc.n_tiles = tiles_per_req;
-      pc.b = u / (hkvv * tiles_per_req);
-      base = pc.b * hkvv * tiles_per_req;
-    }
-    const int r = u - base;
-    pc.hv = r / pc.n_tiles;
-    pc.tile0 = r - pc.hv * pc.n_tiles;
-    pc.count = min(pc.n_tiles - pc.tile0, u_end - u);
-    pc.unit0 = base + pc.hv * pc.n_tiles;
-    return pc;
-  }
-};
 
 template <typename T, int D, bool GATHER>
 __global__ void __launch_bounds__((kConsumerWarps + 1) * 32, 1)

@@ -197,3 +197,51 @@ def rmsnorm_matmul(x, w, *, eps=0.0, gamma=None, split_k=0, out=None, max_ctas=0
 def swiglu(x, w0, w1, *, split_k=0, out=None, max_ctas=0):
     """``Y = silu(X @ W0) * (X @ W1)`` (reference operator: demo/swiglu.py:6-10)."""
     return _gemm(_lib.GEMM_SWIGLU, x, w0, w1=w1, split_k=split_k, out=out, max_ctas=max_ctas)
+
+
+def _mla(q_nope, q_pe, ckv, kpe, sm_scale, *, kv_indptr=None, kv_indices=None, out=None, lse=None, max_ctas=0):
+    q_nope, q_pe, ckv, kpe = _cuda(q_nope, "q_nope"), _cuda(q_pe, "q_pe"), _cuda(ckv, "ckv"), _cuda(kpe, "kpe")
+    batch, heads, dc = q_nope.shape
+    dp = q_pe.shape[2]
+    if q_pe.shape[:2] != (batch, heads) or ckv.shape[-1] != dc or kpe.shape[-1] != dp:
+        raise ValueError("shapes: q_nope (B,H,CKV), q_pe (B,H,KPE), caches (..., CKV) / (..., KPE)")
+    if out is None:
+        out = torch.empty_like(q_nope)
+    a = _lib.MlaDecodeArgs()
+    a.q_nope, a.q_pe, a.ckv_cache, a.kpe_cache = q_nope.data_ptr(), q_pe.data_ptr(), ckv.data_ptr(), kpe.data_ptr()
+    a.out = out.data_ptr()
+    a.lse = None if lse is None else lse.data_ptr()
+    a.batch, a.num_heads, a.ckv_dim, a.kpe_dim = batch, heads, dc, dp
+    a.dtype, a.max_ctas, a.sm_scale = _dtype_code(q_nope), max_ctas, float(sm_scale)
+    if kv_indptr is not None:
+        if kv_indptr.dtype != torch.int32 or kv_indices.dtype != torch.int32:
+            raise TypeError("kv_indptr / kv_indices must be int32")
+        a.kv_indptr, a.kv_indices = kv_indptr.data_ptr(), kv_indices.data_ptr()
+        a.page_size, a.num_pages, a.num_kv_indices = ckv.shape[1], ckv.shape[0], kv_indices.numel()
+    else:
+        a.kv_len = ckv.shape[1]
+    need = _lib.lib().cb200_mla_decode_workspace_bytes(C.byref(a))
+    if need == 0:
+        _lib.check(_lib.lib().cb200_mla_decode(C.byref(a), _stream()))  # raises the real status
+    ws = workspace("mla_decode", need, q_nope.device)
+    a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+    _lib.check(_lib.lib().cb200_mla_decode(C.byref(a), _stream()))
+    return out
+
+
+def mla_decode(q, kv, q_pe, k_pe, sm_scale, *, out=None, lse=None, max_ctas=0):
+    """Static absorbed-latent MLA decode (reference operator: demo/mla_decode.py:8-13):
+    q (B,H,512), kv (B,SKV,512), q_pe (B,H,64), k_pe (B,SKV,64) -> out (B,H,512)."""
+    return _mla(q, q_pe, kv, k_pe, sm_scale, out=out, lse=lse, max_ctas=max_ctas)
+
+
+def mla_paged_decode(q_nope, q_pe, ckv_cache, kpe_cache, kv_indptr, kv_indices, sm_scale, *, out=None, lse=None,
+                     max_ctas=0):
+    """Paged MLA decode, one token per page; argument order follows the reference's operator
+    (python/cleave/dynamic/reference.py:282-320). Returns ``(out, lse)``, ``lse`` base 2."""
+    batch, heads = q_nope.shape[:2]
+    if lse is None:
+        lse = torch.empty((batch, heads), dtype=torch.float32, device=q_nope.device)
+    out = _mla(q_nope, q_pe, ckv_cache, kpe_cache, sm_scale, kv_indptr=kv_indptr, kv_indices=kv_indices,
+               out=out, lse=lse, max_ctas=max_ctas)
+    return out, lse

@@ -145,6 +145,42 @@ int cb200_gemm_effective_split(const cb200_gemm_args* a);
 int cb200_gemm(const cb200_gemm_args* a, void* stream);
 
 /* ------------------------------------------------------------------------------------------
+ * MLA decode (absorbed latent): S = (Q_nope CKV^T + Q_pe KPE^T) * scale, O = softmax(S) CKV, plus
+ * the base-2 log-sum-exp; ckv_dim = 512, kpe_dim = 64.
+ *
+ * Replaces the static MLA decode kernel of demo/mla_decode.py:8-13 (contiguous caches) and the
+ * paged kernels tests/graph/handwritten/expected_kernels/mla_paged_decode_h16_ckv512_kpe64_ps1.py and
+ * splitkv/mla_paged_decode_*_splitkv8.py (python/cleave/dynamic/paging/builders/mla.py); argument order
+ * and meaning follow python/cleave/dynamic/reference.py:282-320. Paged caches hold one token per page.
+ * ---------------------------------------------------------------------------------------- */
+typedef struct {
+  const void* q_nope;    /* (batch, num_heads, 512) */
+  const void* q_pe;      /* (batch, num_heads, 64) */
+  const void* ckv_cache; /* paged: (num_pages, 1, 512); contiguous: (batch, kv_len, 512) */
+  const void* kpe_cache; /* paged: (num_pages, 1, 64);  contiguous: (batch, kv_len, 64) */
+  const int32_t* kv_indptr;  /* (batch + 1), in tokens; NULL selects contiguous caches */
+  const int32_t* kv_indices; /* (num_kv_indices) page ids */
+  void* out;  /* (batch, num_heads, 512) */
+  float* lse; /* (batch, num_heads) base 2, may be NULL */
+  void* workspace;
+  size_t workspace_bytes;
+  int32_t batch;
+  int32_t num_heads;
+  int32_t ckv_dim;        /* 512 */
+  int32_t kpe_dim;        /* 64 */
+  int32_t page_size;      /* paged only: 1 */
+  int32_t num_pages;      /* paged only */
+  int32_t num_kv_indices; /* paged only */
+  int32_t kv_len;         /* contiguous only */
+  int32_t dtype;          /* cb200_dtype */
+  int32_t max_ctas;       /* 0 = one CTA per SM */
+  float sm_scale;
+} cb200_mla_decode_args;
+
+size_t cb200_mla_decode_workspace_bytes(const cb200_mla_decode_args* a);
+int cb200_mla_decode(const cb200_mla_decode_args* a, void* stream);
+
+/* ------------------------------------------------------------------------------------------
  * Decode attention for callers that cannot allocate device memory. (No counterpart in the
  * reference, whose wrappers always own a torch-allocated scratch buffer.)
  *

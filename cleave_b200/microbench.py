@@ -66,6 +66,18 @@ def gqa_decode_case(batch=8, hq=32, hkv=8, d=128, skv=8192, dtype=torch.float16)
     return (lambda: ops.attention_decode(q, k, v, out=out)), 4 * batch * hq * skv * d, byts
 
 
+def mla_decode_case(batch=16, heads=128, skv=4096, dtype=torch.bfloat16):
+    g = _gen()
+    q = torch.randn(batch, heads, 512, generator=g).to(dtype).cuda()
+    qp = torch.randn(batch, heads, 64, generator=g).to(dtype).cuda()
+    kv = torch.randn(batch, skv, 512, generator=g).to(dtype).cuda()
+    kp = torch.randn(batch, skv, 64, generator=g).to(dtype).cuda()
+    out = torch.empty_like(q)
+    flops = 2 * batch * heads * skv * (576 + 512)
+    byts = (kv.numel() + kp.numel() + q.numel() + qp.numel() + out.numel()) * 2
+    return (lambda: ops.mla_decode(q, kv, qp, kp, 192 ** -0.5, out=out)), flops, byts
+
+
 CONFIGS = {
     "cfg1_matmul_128x128x4096": lambda: gemm_case("matmul", 128, 128, 4096),
     "cfg2_rmsnorm_matmul_64x11008x4096": lambda: gemm_case("rmsnorm_matmul", 64, 11008, 4096),
@@ -73,6 +85,7 @@ CONFIGS = {
     "demo_matmul_4096x14336x4096": lambda: gemm_case("matmul", 4096, 14336, 4096),
     "demo_swiglu_4096x14336x4096": lambda: gemm_case("swiglu", 4096, 14336, 4096),
     "cfg3_gqa_decode_b8_h32_kv8_d128_s8192": lambda: gqa_decode_case(),
+    "cfg4_mla_decode_b16_h128_s4096": lambda: mla_decode_case(),
 }
 
 
@@ -88,7 +101,7 @@ def measure(name, build):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default=None, choices=["matmul", "rmsnorm_matmul", "swiglu", "gqa_decode"])
+    ap.add_argument("--op", default=None, choices=["matmul", "rmsnorm_matmul", "swiglu", "gqa_decode", "mla_decode"])
     ap.add_argument("--m", type=int, default=4096)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
@@ -100,6 +113,8 @@ def main():
     if a.op:
         if a.op == "gqa_decode":
             build = gqa_decode_case
+        elif a.op == "mla_decode":
+            build = mla_decode_case
         else:
             build = lambda: gemm_case(a.op, a.m, a.n, a.k, gamma=not a.no_gamma, split_k=a.split_k)  # noqa: E731
         if a.launches:

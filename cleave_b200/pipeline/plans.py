@@ -1,0 +1,64 @@
+"""Plans: one kernel candidate each (reference: python/cleave/pipeline/plans.py:17-38, 203-234).
+
+The reference's scheduler proposes many tilings per graph, scored by a Hopper cost model; here
+a plan keeps what the backend honours - the structure (solo or split, split factor) - and leaves
+tile shapes to the hand-written kernels. A split-K variant is ONE fused kernel (role "main").
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any
+
+from ..codegen import make_spec
+
+GEMM_FAMILIES = ("matmul", "rmsnorm_matmul", "swiglu")
+
+
+@dataclass(eq=False)
+class Plan:
+    graph_index: int
+    variant: str        # "solo" | "split-k=N"
+    role: str           # "main"
+    spec: Any           # codegen.KernelSpec
+    inputs: list        # kernel placeholder names, in the Program's input order
+    split_factor: int = 1
+    label: str = ""
+    tile: Any = None    # the reference's TileDict slot; unused (tile shapes are the kernels' own)
+
+
+@dataclass
+class PlanSet:
+    program: Any
+    plans: list = field(default_factory=list)
+    refused: list = field(default_factory=list)
+
+    def __iter__(self):
+        return iter(self.plans)
+
+    def __len__(self):
+        return len(self.plans)
+
+    def summary(self) -> str:
+        return f"{len(self.plans)} plan(s): " + ", ".join(p.variant for p in self.plans)
+
+
+def schedule(program, splits=None) -> PlanSet:
+    """Solo plus one fused split-K plan per factor for the GEMM family; the decode families
+    split their KV stream inside the kernel and have a single plan."""
+    by_input = {v: k for k, v in program.bind.items()}  # Program input name -> placeholder name
+    inputs = [by_input[n] for n in program.input_names]
+    out = PlanSet(program)
+
+    def add(variant, split):
+        spec = make_spec(program.family, program.dtype, program.dims, split=split, attrs=program.attrs)
+        out.plans.append(Plan(0, variant, "main", spec, inputs, split,
+                              f"{program.family} {variant} {'x'.join(str(v) for v in program.dims.values())}"))
+
+    add("solo", 1)
+    if program.family in GEMM_FAMILIES:
+        kblocks = -(-program.dims["K"] // 64)
+        for s in (splits if splits is not None else program.split):
+            if 1 < s <= kblocks:
+                add(f"split-k={s}", int(s))
+    return out

@@ -1,0 +1,208 @@
+"""Host-side logic that needs no GPU: the C ABI exports, kernel-spec text, plan recognition,
+tracing, the split-K pairing rule, and candidate orchestration with injected failures."""
+
+import ctypes
+import os
+import re
+import time
+from types import SimpleNamespace
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_loads_and_exports_every_declared_symbol():
+    header = open(os.path.join(ROOT, "include", "cleave_b200.h")).read()
+    declared = set(re.findall(r"^(?:int|size_t|const char\*)\s+(cb200_[a-z0-9_]+)\s*\(", header, re.M))
+    assert len(declared) >= 14
+    lib = ctypes.CDLL(os.path.join(ROOT, "cleave_b200", "libcleave_b200.so"))
+    for name in declared:
+        assert hasattr(lib, name), f"{name} is declared in the header but not exported"
+    lib.cb200_strerror.restype = ctypes.c_char_p
+    assert lib.cb200_version() == 1
+    assert b"workspace" in lib.cb200_strerror(4)
+
+
+def test_kernel_text_is_deterministic_and_round_trips():
+    from cleave_b200.codegen import B200CodeGen, make_spec
+    from cleave_b200.pipeline.build import pass_configs_of
+    from cleave_b200.runtime.compile import _load_main_kernel_from_code
+
+    a = make_spec("matmul", "float16", {"M": 128, "N": 128, "K": 4096}, split=4)
+    b = make_spec("matmul", "float16", {"K": 4096, "N": 128, "M": 128}, split=4)  # other key order
+    ta, tb = B200CodeGen().gen(a), B200CodeGen(apply_rasterization=16).gen(b)
+    assert ta == tb and "main_kernel" in ta
+    back = _load_main_kernel_from_code(ta)
+    assert back == a and back._cache_source_hint == ta
+    assert B200CodeGen().gen(make_spec("matmul", "float16", {"M": 128, "N": 128, "K": 4096}, split=8)) != ta
+    assert pass_configs_of(ta) == {}
+    assert pass_configs_of("PASS_CONFIGS = {'tl.x': 1}\nmain_kernel = 0\n") == {"tl.x": 1}
+    assert [p.name for p in a.params] == ["PlaceHolder_x", "PlaceHolder_w", "OutputNode"]
+
+
+class _Node:
+    def __init__(self, kind, shape=(), dtype="float16"):
+        self.op = None if kind in ("PlaceHolderNode", "OutputNode") else type(kind, (), {})()
+        self._kind, self._shape, self._dtype = kind, shape, dtype
+        if self.op is None:
+            self.__class__ = type(kind, (_Node,), {})
+
+    def get_shape(self, _):
+        return self._shape
+
+    def get_dtype(self, _):
+        return self._dtype
+
+
+def _plan(nodes, split=None):
+    return SimpleNamespace(tile=SimpleNamespace(flat_graph=SimpleNamespace(nodes=nodes)), split_factor=split)
+
+
+def test_plan_recognition_from_flat_graph_patterns():
+    """Node patterns as the reference's scheduler emits them for the split-K matmul partial
+    (python/cleave/lower/split.py, observed: PlaceHolder, SplitView, PlaceHolder, SplitView, Matmul, Output)."""
+    from cleave_b200.codegen import recognise
+
+    N = _Node
+    mm = _plan([N("PlaceHolderNode", (128, 4096)), N("SplitView", (4, 128, 1024)), N("PlaceHolderNode", (4096, 128)),
+                N("SplitView", (4, 1024, 128)), N("Matmul", (4, 128, 128)), N("OutputNode", (4, 128, 128))])
+    s = recognise(mm)
+    assert (s.family, s.split, s.dims) == ("matmul", 4, {"M": 128, "N": 128, "K": 4096})
+    assert recognise([mm, _plan([N("ReduceSum")])]).split == 4  # [partial, combine] -> one fused kernel
+    rms = _plan([N("PlaceHolderNode", (64, 4096)), N("PlaceHolderNode", (4096, 11008)), N("Mul"), N("ReduceSum"),
+                 N("Div"), N("RSqrt"), N("Matmul"), N("Mul"), N("OutputNode")])
+    assert recognise(rms).family == "rmsnorm_matmul"
+    sw = _plan([N("PlaceHolderNode", (8, 32)), N("PlaceHolderNode", (32, 16)), N("PlaceHolderNode", (32, 16)),
+                N("Matmul"), N("Matmul"), N("Silu"), N("Mul"), N("OutputNode")])
+    assert recognise(sw).family == "swiglu"
+    att = _plan([N("PlaceHolderNode", (256, 1, 128)), N("PlaceHolderNode", (64, 8192, 128)),
+                 N("PlaceHolderNode", (64, 8192, 128)), N("Matmul"), N("Div"), N("Add"), N("Exp"), N("ReduceSum"),
+                 N("Matmul"), N("Div"), N("OutputNode")])
+    a = recognise(att)
+    assert a.family == "attention_decode" and a.dims["HKV"] == 64 and a.dims["SKV"] == 8192
+    with pytest.raises(Exception):
+        recognise(_plan([N("PlaceHolderNode", (4, 4)), N("Exp"), N("OutputNode")]))
+
+
+def test_trace_matches_the_demo_operators():
+    import cleave_b200.lang as cl
+    from cleave_b200.core.errors import SpecError
+    from cleave_b200.frontend import jit, trace
+
+    @jit
+    def rmsnorm_matmul(x: cl.Tensor["M", "K"], w: cl.Tensor["K", "N"]):
+        return cl.rms_norm(x, dim=-1) @ w
+
+    p = trace(rmsnorm_matmul, dict(M=64, N=11008, K=4096), split=cl.Split("K", (4, 8)))
+    assert (p.family, p.split, p.input_names) == ("rmsnorm_matmul", (4, 8), ["x", "w"])
+
+    @jit
+    def attention(q: cl.Tensor["HQ", "SQ", "D"], k: cl.Tensor["HKV", "SKV", "D"], v: cl.Tensor["HKV", "SKV", "D"]):
+        n = q.shape[-1] ** 0.5
+        return cl.softmax((q @ k.mT) / n, dim=-1, shift=-50 / n) @ v
+
+    p = trace(attention, dict(HQ=32, HKV=8, SQ=1, SKV=4096, D=128))
+    assert p.family == "attention_decode" and abs(p.attrs["scale"] - 128 ** -0.5) < 1e-9
+
+    @jit
+    def unknown(x: cl.Tensor["M", "K"]):
+        return x * 2.0
+
+    with pytest.raises(SpecError):
+        trace(unknown, dict(M=4, K=4))
+    with pytest.raises(SpecError):
+        trace(rmsnorm_matmul, dict(M=4))
+
+
+def _result(variant, role, ms, label=""):
+    from cleave_b200.pipeline.report import Result
+    from cleave_b200.runtime.evaluate import CandidateResult
+
+    plan = SimpleNamespace(variant=variant, role=role, label=label or f"{variant}/{role}")
+    run = CandidateResult(plan, "ok" if ms is not None else "failed", None if ms is not None else "validate",
+                          None, "code", "src", ms, plan.label)
+    return Result(plan, run)
+
+
+def test_split_k_pairing_rule():
+    """Reference: python/cleave/pipeline/report.py:123-153 - solo = best main; a split variant is a single
+    fused main, or partial + combine summed; a variant with a missing member is dropped."""
+    from cleave_b200.pipeline.report import Report
+
+    rep = Report([_result("solo", "main", 0.010), _result("solo", "main", 0.008),
+                  _result("split-k=4", "main", 0.006), _result("split-k=8", "partial", 0.003),
+                  _result("split-k=8", "combine", 0.002), _result("split-k=16", "partial", 0.001),
+                  _result("split-k=2", "main", None)])
+    v = rep.variants()
+    assert set(v) == {"solo", "split-k=4", "split-k=8"}
+    assert abs(v["solo"].latency_us - 8.0) < 1e-9 and abs(v["split-k=8"].latency_us - 5.0) < 1e-9
+    assert min(v.values(), key=lambda x: x.latency_us).variant == "split-k=8"
+    assert rep.histogram() == {"validate": 1}
+
+
+def _fake_check(code, **kw):
+    if code == "slow":
+        time.sleep(30)
+    if code == "crash":
+        os._exit(3)
+    if code == "wrong":
+        err = AssertionError("mismatch")
+        err._cleave_stage = "validate"
+        raise err
+    return "src:" + code, 0.001
+
+
+def test_run_candidates_classifies_timeout_crash_and_wrong_answers():
+    """Reference: tests/test_runtime_parallel.py:18-56 - failures are injected on the host."""
+    from cleave_b200.core.errors import CandidateTimeout, CodegenError, ValidationError, WorkerCrash
+    from cleave_b200.runtime.evaluate import run_candidates
+
+    def build(c):
+        if c == "nogen":
+            raise ValueError("cannot generate")
+        return c
+
+    cands = ["good", "slow", "crash", "wrong", "nogen", "good2"]
+    t0 = time.monotonic()
+    res = run_candidates(cands, build_fn=build, check_fn=_fake_check, pool="fork", max_parallel=3, timeout_s=1.5)
+    assert time.monotonic() - t0 < 20
+    assert [r.status for r in res] == ["ok", "failed", "failed", "failed", "failed", "ok"]
+    assert [r.stage for r in res] == [None, "timeout", "crash", "validate", "codegen", None]
+    assert isinstance(res[1].error, CandidateTimeout) and isinstance(res[2].error, WorkerCrash)
+    assert isinstance(res[3].error, ValidationError) and isinstance(res[4].error, CodegenError)
+    assert res[0].cuda_src == "src:good" and res[0].latency_ms == 0.001
+    # in process, without a pool
+    res = run_candidates(["good", "wrong"], build_fn=build, check_fn=_fake_check)
+    assert [r.stage for r in res] == [None, "validate"]
+
+
+def test_kernel_binding_errors_and_save_load_roundtrip(tmp_path):
+    from cleave_b200.codegen import B200CodeGen, make_spec
+    from cleave_b200.pipeline.kernel import Kernel, Param, Stage, load
+
+    src = B200CodeGen().gen(make_spec("matmul", "float16", {"M": 4, "N": 8, "K": 64}))
+    k = Kernel([Stage("main", src, [-1], [Param("PlaceHolder_x", "input", 0, (4, 64)),
+                                          Param("PlaceHolder_w", "input", 1, (64, 8))], "lbl", 1.5)],
+               name="mm", input_names=["x", "w"], input_shapes=[(4, 64), (64, 8)], output_shapes=[(4, 8)],
+               variant="solo", latency_us=1.5)
+    x, w = SimpleNamespace(shape=(4, 64)), SimpleNamespace(shape=(64, 8))
+    with pytest.raises(TypeError):
+        k._bind((x,), {})
+    with pytest.raises(TypeError):
+        k._bind((x,), {"w": w})
+    with pytest.raises(ValueError):
+        k._bind((w, x), {})
+    assert k._bind((), {"w": w, "x": x}) == [x, w]
+    back = load(k.save(tmp_path / "k"))
+    assert back.source == k.source and back.variant == "solo" and back.stages[0].params[1].shape == (64, 8)
+    assert (tmp_path / "k" / "kernel.json").exists() and (tmp_path / "k" / "kernel.py").read_text() == src
+
+
+def test_paged_workload_generator_is_seeded_and_ragged():
+    from cleave_b200.pipeline.dynamic import paged_decode_workloads
+
+    a, b = paged_decode_workloads(), paged_decode_workloads()
+    assert a == b and len(a) == 18
+    assert min(min(l) for _, l in a) >= 1 and max(max(l) for _, l in a) == 8192
+    assert any(len(set(l)) > 1 for _, l in a)

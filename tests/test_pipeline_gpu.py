@@ -1,0 +1,155 @@
+"""End-to-end ``compile`` on the GPU: candidates are validated and timed, the best becomes a
+callable Kernel that can be saved, loaded and cached; paged operators return a PagedKernel."""
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _fast():
+    from cleave_b200.pipeline import EvalConfig
+
+    return EvalConfig(warmup=2, iters=20)
+
+
+def test_compile_matmul_split_k_save_load_cache(tmp_path, monkeypatch):
+    """Reference: tests/pipeline_api/test_e2e.py:32-99 (matmul e2e, split-K chain == x.float() @ w.float(),
+    save/load, cache hit)."""
+    import cleave_b200 as cleave
+    import cleave_b200.lang as cl
+
+    monkeypatch.setenv("CLEAVE_CACHE_ROOT", str(tmp_path / "cache"))
+
+    @cleave.jit
+    def matmul(x: cl.Tensor["M", "K"], w: cl.Tensor["K", "N"]):
+        return x @ w
+
+    k = cleave.compile(matmul, shapes=dict(M=128, N=128, K=4096), dtype=cl.f16, split=cl.Split("K", (4, 8)),
+                       eval=_fast())
+    assert "main_kernel" in k.source
+    rep = k.report
+    assert set(rep.variants()) == {"solo", "split-k=4", "split-k=8"} and len(rep.correct) == 3
+    assert k.latency_us == min(v.latency_us for v in rep.variants().values())
+    x = torch.randn(128, 4096, device="cuda").half()
+    w = (torch.randn(4096, 128, device="cuda") / 64).half()
+    y = k(x, w)
+    torch.testing.assert_close(y.float(), x.float() @ w.float(), rtol=2e-2, atol=5e-2)
+    assert torch.equal(k(x=x, w=w), y)
+    for variant in ("solo", "split-k=8"):
+        torch.testing.assert_close(rep.best(variant)(x, w).float(), x.float() @ w.float(), rtol=2e-2, atol=5e-2)
+    with pytest.raises(ValueError):
+        k(w, x)
+    loaded = cleave.load(k.save(tmp_path / "saved"))
+    assert torch.equal(loaded(x, w), y) and loaded.variant == k.variant
+    again = cleave.compile(matmul, shapes=dict(M=128, N=128, K=4096), dtype=cl.f16, split=cl.Split("K", (4, 8)),
+                           eval=_fast())
+    assert again.meta.get("cache_hit") and torch.equal(again(x, w), y)
+
+
+def test_compile_rmsnorm_gamma_swiglu_attention_and_mla():
+    import cleave_b200 as cleave
+    import cleave_b200.lang as cl
+    from cleave_b200.runtime import reference as R
+
+    @cleave.jit
+    def rn(x: cl.Tensor["M", "K"], g: cl.Tensor["K"], w: cl.Tensor["K", "N"]):
+        return (cl.rms_norm(x, eps=1e-6) * g) @ w
+
+    @cleave.jit
+    def sw(x: cl.Tensor["M", "K"], w0: cl.Tensor["K", "N"], w1: cl.Tensor["K", "N"]):
+        return cl.silu(x @ w0) * (x @ w1)
+
+    @cleave.jit
+    def att(q: cl.Tensor["HQ", "SQ", "D"], k: cl.Tensor["HKV", "SKV", "D"], v: cl.Tensor["HKV", "SKV", "D"]):
+        n = q.shape[-1] ** 0.5
+        return cl.softmax((q @ k.mT) / n, dim=-1, shift=-50 / n) @ v
+
+    @cleave.jit
+    def mla(q: cl.Tensor["B", "H", "D"], kv: cl.Tensor["B", "SKV", "D"], q_pe: cl.Tensor["B", "H", "PE"],
+            k_pe: cl.Tensor["B", "SKV", "PE"]):
+        s = (q @ kv.mT + q_pe @ k_pe.mT) * 0.07
+        return cl.softmax(s, dim=-1) @ kv
+
+    g = torch.Generator(device="cuda").manual_seed(1)
+    rnd = lambda *s, dt=torch.float16: torch.randn(*s, device="cuda", generator=g).to(dt)  # noqa: E731
+    k1 = cleave.compile(rn, shapes=dict(M=64, N=512, K=1024), eval=_fast(), cache_kernels=False)
+    x, gm, w = rnd(64, 1024), 1 + 0.1 * rnd(1024), rnd(1024, 512) / 32
+    torch.testing.assert_close(k1(x, gm, w).float(), R.rmsnorm_matmul(x, w, 1e-6, gm), rtol=2e-2, atol=2e-2)
+    k2 = cleave.compile(sw, shapes=dict(M=128, N=256, K=512), eval=_fast(), cache_kernels=False)
+    x, w0, w1 = rnd(128, 512), rnd(512, 256) / 22, rnd(512, 256) / 22
+    torch.testing.assert_close(k2(x, w0, w1).float(), R.swiglu(x, w0, w1), rtol=2e-2, atol=2e-2)
+    k3 = cleave.compile(att, shapes=dict(HQ=32, HKV=8, SQ=1, SKV=777, D=128), eval=_fast(), cache_kernels=False)
+    q, kk, v = rnd(32, 1, 128), rnd(8, 777, 128), rnd(8, 777, 128)
+    torch.testing.assert_close(k3(q, kk, v).float(), R.attention(q, kk, v), rtol=2e-2, atol=2e-2)
+    assert set(k3.report.variants()) == {"solo"}
+    k4 = cleave.compile(mla, shapes=dict(B=2, H=32, SKV=300, D=512, PE=64), dtype=cl.bf16, eval=_fast(),
+                        cache_kernels=False)
+    bf = torch.bfloat16
+    q, kv, qp, kp = rnd(2, 32, 512, dt=bf), rnd(2, 300, 512, dt=bf), rnd(2, 32, 64, dt=bf), rnd(2, 300, 64, dt=bf)
+    torch.testing.assert_close(k4(q, kv, qp, kp).float(), R.mla_decode(q, kv, qp, kp, 0.07), rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("page_size", [64, 1])
+def test_compile_paged_gqa_decode(tmp_path, page_size):
+    """Reference: tests/frontend_dynamic/test_paged_pipeline.py:63-92 - lens [700, 1, 129, 64], a pool three
+    pages larger than needed, out and lse at 1e-2, named call bit-identical, page size 1 takes None for
+    the unread kv_last_page_len, a saved and loaded kernel reproduces the same bits."""
+    import cleave_b200 as cleave
+    from cleave_b200.pipeline.dynamic import make_inputs, reference
+
+    dims = dict(num_qo_heads=32, num_kv_heads=8, head_dim=128, page_size=page_size)
+    wl = [("a", [700, 1, 129, 64]), ("b", [5, 0, 7]), ("c", [3000] * 3)]
+    k = cleave.compile("gqa_paged_decode", dtype="bfloat16", workloads=wl, **dims)
+    assert k.report.n_workloads == 3 and k.report.best() is not None and k.dispatch is None
+    args = make_inputs("gqa_paged_decode", dims, [700, 1, 129, 64], "bfloat16", seed=5)
+    want_out, want_lse = reference("gqa_paged_decode", args)
+    out, lse = k(*args)
+    torch.testing.assert_close(out.float(), want_out.float(), rtol=1e-2, atol=1e-2)
+    torch.testing.assert_close(lse, want_lse, rtol=1e-2, atol=1e-2)
+    names = ["q", "k_cache", "v_cache", "kv_indptr", "kv_indices", "kv_last_page_len", "sm_scale"]
+    out2, lse2 = k(**dict(zip(names, args)))
+    assert torch.equal(out, out2) and torch.equal(lse, lse2)
+    if page_size == 1:
+        assert args[5] is None
+        with pytest.raises(ValueError):
+            k(*args[:5], torch.zeros(4, dtype=torch.int32, device="cuda"), args[6])
+    else:
+        with pytest.raises(TypeError):
+            k(*args[:5], None, args[6])
+    loaded = cleave.load(k.save(tmp_path / "paged"))
+    out3, lse3 = loaded(*args)
+    assert torch.equal(out, out3) and torch.equal(lse, lse3)
+
+
+def test_compile_paged_mla_decode_and_refusals():
+    import cleave_b200 as cleave
+    from cleave_b200.core.errors import PagingRefusal
+    from cleave_b200.pipeline.dynamic import make_inputs, reference
+
+    dims = dict(num_qo_heads=16, head_dim_ckv=512, head_dim_kpe=64)
+    k = cleave.compile("mla_paged_decode", dtype="bfloat16", workloads=[("a", [5, 0, 7, 300])], **dims)
+    args = make_inputs("mla_paged_decode", dims, [64, 2000, 1], "bfloat16", seed=2)
+    want_out, want_lse = reference("mla_paged_decode", args)
+    out, lse = k(*args)
+    torch.testing.assert_close(out.float(), want_out.float(), rtol=1e-2, atol=1e-2)
+    torch.testing.assert_close(lse, want_lse, rtol=1e-2, atol=1e-2)
+    with pytest.raises(PagingRefusal):
+        cleave.compile("gqa_paged_decode", num_qo_heads=32, num_kv_heads=8, head_dim=96, page_size=16)
+    with pytest.raises(PagingRefusal):
+        cleave.compile("mla_paged_decode", num_qo_heads=16, head_dim_ckv=256, head_dim_kpe=64)
+
+
+def test_check_code_in_a_spawned_worker(tmp_path):
+    """The default check function is picklable and runs in a spawned worker with its own CUDA context,
+    reading the parent-built reference file (reference: python/cleave/runtime/workers.py:104-122)."""
+    from cleave_b200.codegen import make_spec
+    from cleave_b200.runtime.evaluate import run_candidates
+    from cleave_b200.runtime.validate import BenchOptions, publish_reference
+
+    specs = [make_spec("matmul", "float16", {"M": 64, "N": 128, "K": 512}, split=s) for s in (1, 4)]
+    res = run_candidates(specs, reference_fn=lambda d: publish_reference(d, specs[0])[0], pool="spawn",
+                         max_parallel=1, timeout_s=240, benchmark=BenchOptions(2, 10))
+    assert [r.status for r in res] == ["ok", "ok"], [str(r.error) for r in res]
+    assert all(r.latency_ms and r.latency_ms > 0 for r in res)

@@ -119,7 +119,7 @@ def make_spec(family: str, dtype: str, dims: dict, *, split: int = 1, attrs: dic
 
 _HEADER = ("# cleave_b200 kernel spec: selects and parameterises a hand-written sm_100a kernel.\n"
            "# Loaded by cleave_b200.runtime.compile._load_main_kernel_from_code; no code is generated.\n"
-           "from cleave_b200.codegen import KernelSpec\n\n")
+           "import json\n\nfrom cleave_b200.codegen import KernelSpec\n\n")
 
 
 class B200CodeGen:
@@ -134,7 +134,7 @@ class B200CodeGen:
         ``[partial, combine]`` pair of those - a split pair collapses into ONE fused kernel."""
         spec = plan_or_spec if isinstance(plan_or_spec, KernelSpec) else recognise(plan_or_spec)
         body = json.dumps(spec.to_dict(), sort_keys=True, indent=1)
-        return f"{_HEADER}main_kernel = KernelSpec.from_dict({body})\n"
+        return f'{_HEADER}main_kernel = KernelSpec.from_dict(json.loads(r"""\n{body}\n"""))\n'
 
 
 # ----------------------------------------------------------------------------- plan recogniser

@@ -25,7 +25,6 @@
 #include "common.cuh"
 
 #include <cstring>
-#include <cstdlib>
 #include <type_traits>
 
 namespace cb200 {
@@ -49,7 +48,6 @@ struct GemmParams {
   int chunks_per_tile; // S
   float eps;
   int a_rows;  // rows of the A box: 128, or M rounded up to 8 when M is smaller
-  int debug;
 };
 
 template <int MODE, int NBW>
@@ -97,7 +95,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
   float* rs_red = reinterpret_cast<float*>(misc + 2560);      // [128] row sums of a reduced tile
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const long long dbg_t0 = clock64();
 
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -126,7 +123,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_holder);
 
-  const long long dbg_t1 = clock64();
   // ---- this CTA's share of the (tile, chunk) list
   const int S = p.chunks_per_tile;
   const long long C = static_cast<long long>(p.tiles_m) * p.tiles_n * S;
@@ -166,7 +162,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
       }
       x += nseg;
     }
-    if ((p.debug & 2) && lane == 0 && blockIdx.x == 0) { p.status[16] = (int)(dbg_t1 - dbg_t0); p.status[17] = (int)(clock64() - dbg_t0); }
   } else if (warp == 1) {
     // ================================================================ MMA issuer
     constexpr uint32_t idesc = umma_idesc(std::is_same<T, __nv_bfloat16>::value, true, kBM, kUmmaN);
@@ -200,7 +195,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
       }
       if (lane == 0) umma_commit(&acc_full[buf]);
       __syncwarp();
-      if ((p.debug & 2) && lane == 0 && blockIdx.x == 0) p.status[18] = (int)(clock64() - dbg_t0);
       if (++buf == 2) { buf = 0; acc_phase ^= 1; }
       x += nseg;
     }
@@ -332,7 +326,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
       const bool starts_here = s0 == 0, whole = starts_here && nseg == S;
       mbar_wait(&acc_full[buf], acc_phase, p.status, kFaultMmaBarrier);
       tc_fence_after();
-      if ((p.debug & 2) && etid == 0 && blockIdx.x == 0) p.status[19] = (int)(clock64() - dbg_t0);
       float rs = 0.f;
       if constexpr (MODE == 1) {
         mbar_wait(&rs_full[buf], acc_phase, p.status, kFaultTmemBarrier);
@@ -492,7 +485,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         }
         named_bar_sync(2, 128);
       }
-      if ((p.debug & 2) && etid == 0 && blockIdx.x == 0) p.status[20] = (int)(clock64() - dbg_t0);
       if (++buf == 2) { buf = 0; acc_phase ^= 1; }
       x += nseg;
     }
@@ -533,7 +525,6 @@ int plan_gemm(const cb200_gemm_args* a, GemmSetup* s, bool need_maps) {
   p = GemmParams{};
   p.M = a->m; p.N = a->n; p.K = a->k;
   p.eps = a->eps;
-  p.debug = getenv("CB200_DEBUG") ? atoi(getenv("CB200_DEBUG")) : 0;
   p.tiles_m = ceil_div(a->m, kBM);
   p.a_rows = a->m >= kBM ? kBM : (a->m + 7) / 8 * 8;
   // 256-column tiles when there are plenty of tiles, 128-column tiles otherwise (SwiGLU always

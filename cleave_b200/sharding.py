@@ -1,0 +1,96 @@
+"""Multi-GPU use of the kernels, one process per GPU (``torch.distributed``).
+
+The reference is single-GPU. Its operators shard naturally: decode requests are independent, so
+a batch is partitioned by request with NO collective on the data path; a large GEMM shards its
+weight along N, every rank recomputes the per-row RMSNorm statistics locally, and one all-gather
+over NVLink reassembles Y only when the caller wants the full matrix on every rank.
+"""
+
+from __future__ import annotations
+
+import heapq
+
+
+def partition_requests(kv_lens, world: int, tile: int = 64, balance: bool = True):
+    """Request indices per rank. ``balance=True``: longest-processing-time-first over KV tile counts
+    (skewed lengths would leave a contiguous split far from even); each rank's list is sorted so
+    that results can be put back in request order. Empty requests cost one unit of bookkeeping."""
+    n = len(kv_lens)
+    if world <= 0:
+        raise ValueError("world must be positive")
+    if not balance:
+        per = -(-n // world)
+        return [list(range(r * per, min(n, (r + 1) * per))) for r in range(world)]
+    cost = [max(1, -(-int(l) // tile)) for l in kv_lens]
+    heap = [(0, r) for r in range(world)]
+    heapq.heapify(heap)
+    out = [[] for _ in range(world)]
+    for i in sorted(range(n), key=lambda i: -cost[i]):
+        load, r = heapq.heappop(heap)
+        out[r].append(i)
+        heapq.heappush(heap, (load + cost[i], r))
+    return [sorted(x) for x in out]
+
+
+def shard_paged_tables(kv_indptr, kv_indices, kv_last_page_len, requests):
+    """Page tables of one rank's requests over a private pool: ``(indptr, indices, last, pages)``
+    where ``pages`` lists the global page ids the rank must hold, in its local numbering."""
+    ptr = [int(x) for x in kv_indptr]
+    new_ptr, new_idx, pages = [0], [], []
+    for b in requests:
+        mine = [int(x) for x in kv_indices[ptr[b]:ptr[b + 1]]]
+        new_idx.extend(range(len(pages), len(pages) + len(mine)))
+        pages.extend(mine)
+        new_ptr.append(new_ptr[-1] + len(mine))
+    last = None if kv_last_page_len is None else [int(kv_last_page_len[b]) for b in requests]
+    return new_ptr, new_idx, last, pages
+
+
+def gather_by_request(local_out, requests_per_rank, group=None):
+    """All ranks' per-request outputs back in request order (only for callers that need every
+    request everywhere; the decode data path itself has no collective)."""
+    import torch
+    import torch.distributed as dist
+
+    world = dist.get_world_size(group)
+    counts = [len(r) for r in requests_per_rank]
+    width = max(counts) if counts else 0
+    pad = torch.zeros((width,) + tuple(local_out.shape[1:]), dtype=local_out.dtype, device=local_out.device)
+    pad[:local_out.shape[0]] = local_out
+    bufs = [torch.empty_like(pad) for _ in range(world)]
+    dist.all_gather(bufs, pad, group=group)
+    total = sum(counts)
+    full = torch.empty((total,) + tuple(local_out.shape[1:]), dtype=local_out.dtype, device=local_out.device)
+    for r, reqs in enumerate(requests_per_rank):
+        if reqs:
+            full[torch.tensor(reqs, device=local_out.device)] = bufs[r][:len(reqs)]
+    return full
+
+
+def n_shard(n: int, rank: int, world: int, align: int = 8):
+    """Column range ``[lo, hi)`` of rank's weight shard; boundaries are multiples of ``align``."""
+    blocks = -(-n // align)
+    lo = min(n, (blocks * rank // world) * align)
+    hi = min(n, (blocks * (rank + 1) // world) * align)
+    return lo, hi
+
+
+def gemm_n_sharded(local_gemm, x, w_shards, n_total, *, gather=True, group=None):
+    """``Y = op(X, W)`` with W sharded along N. ``local_gemm(x, *w_shards)`` computes this rank's
+    columns (any of the GEMM family; RMSNorm statistics are per row over K and need no exchange).
+    With ``gather`` the shards are all-gathered and concatenated along N."""
+    import torch
+    import torch.distributed as dist
+
+    y_local = local_gemm(x, *w_shards)
+    if not gather:
+        return y_local
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    bounds = [n_shard(n_total, r, world) for r in range(world)]
+    width = max(hi - lo for lo, hi in bounds)
+    pad = torch.zeros((y_local.shape[0], width), dtype=y_local.dtype, device=y_local.device)
+    pad[:, :y_local.shape[1]] = y_local
+    bufs = [torch.empty_like(pad) for _ in range(world)]
+    dist.all_gather(bufs, pad, group=group)
+    assert bounds[rank][1] - bounds[rank][0] == y_local.shape[1]
+    return torch.cat([b[:, :hi - lo] for b, (lo, hi) in zip(bufs, bounds)], dim=1)

@@ -140,6 +140,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--e2e-steps", type=int, default=3, help="steps of the host-buffer end-to-end leg")
     ap.add_argument("--batch", type=int, default=128, help="requests per GPU (smaller only for profiler captures)")
+    ap.add_argument("--no-other-configs", action="store_true", help="skip the per-configuration readings")
     ap.add_argument("--kernel-only", action="store_true",
                     help="skip the end-to-end and CPU legs (profiler captures)")
     args = ap.parse_args()
@@ -324,12 +325,26 @@ def main():
            "sample": f"first {CPU_SAMPLE_REQUESTS} requests of rank 0's batch ({sample.tokens} tokens, "
                      f"{sample.algorithmic_bytes() / 1e9:.2f} GB of KV), {cpu_s:.2f} s per pass, 2 passes after 1 warm-up"}
 
+    # The other benchmark configurations (parity-test cases, not the headline): one CUDA-graph-timed
+    # reading each, with its fraction of the measured HBM / tensor peaks.
+    others = []
+    if world == 1 and not args.no_other_configs:
+        try:
+            from cleave_b200 import microbench
+
+            for name, build in microbench.CONFIGS.items():
+                r = microbench.measure(name, build)
+                others.append({k: (round(v, 4) if isinstance(v, float) else v) for k, v in r.items()})
+                torch.cuda.empty_cache()
+        except Exception as exc:  # noqa: BLE001 - the headline line must still be printed
+            others.append({"error": f"{type(exc).__name__}: {exc}"})
+
     print(json.dumps({
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f16", "data": "synthetic", "config": dict(WORKLOAD, batch_per_gpu=args.batch, tokens_rank0=w.tokens),
         "clocks": clocks.summary(), "e2e": e2e, "e2e_kv_resident": e2e_resident, "gpu_launches": args.steps,
-        "roofline": roofline, "cpu_baseline": cpu}))
+        "roofline": roofline, "cpu_baseline": cpu, "other_configs": others}))
     if dist is not None:
         dist.destroy_process_group()
 

@@ -56,8 +56,12 @@ class MlaDecodeArgs(C.Structure):
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("batch", C.c_int32), ("num_heads", C.c_int32), ("ckv_dim", C.c_int32), ("kpe_dim", C.c_int32),
         ("page_size", C.c_int32), ("num_pages", C.c_int32), ("num_kv_indices", C.c_int32),
-        ("kv_len", C.c_int32), ("dtype", C.c_int32), ("max_ctas", C.c_int32), ("sm_scale", C.c_float),
+        ("kv_len", C.c_int32), ("dtype", C.c_int32), ("max_ctas", C.c_int32), ("impl", C.c_int32),
+        ("sm_scale", C.c_float),
     ]
+
+
+MLA_IMPL = {"auto": 0, "mma_sync": 1, "tcgen05": 2}
 
 _lib = None
 

@@ -4,7 +4,8 @@
 // all (request, kv head) items form one stream that is split evenly over the CTAs, so a CTA's
 // share may start or end in the middle of an item. A producer warp streams its share of tiles
 // into a ring of shared-memory stages (TMA tiled loads with the 128-byte swizzle when a tile maps
-// to whole boxes of the cache; otherwise one untiled bulk copy per gathered token row) and the
+// to whole boxes of the cache; otherwise four producer warps gather the token rows with 16-byte
+// cp.async into the same swizzled layout) and the
 // consumer warps run QK^T and PV on m16n8k16 tensor-core MMAs with a warp-shuffle online softmax
 // in the exp2 domain. An item finished inside one CTA is written directly; an item cut across
 // CTAs leaves fp32 partials (O, m, l) in the workspace and the last CTA to arrive does the
@@ -45,10 +46,13 @@ struct DecodeParams {
 
 template <int D, bool GATHER>
 struct SmemPlan {
-  static constexpr int kRowBytes = GATHER ? D * 2 + 16 : 128;  // padded row / swizzled 128-byte row
-  static constexpr int kMatBytes = GATHER ? kTile * kRowBytes : kTile * D * 2;
+  // Both paths use the same tile layout: per 64-column half, 64 rows of 128 bytes with the
+  // 128-byte swizzle (what TMA writes; the gather path reproduces it with 16-byte cp.async).
+  static constexpr int kMatBytes = kTile * D * 2;
   static constexpr int kStageBytes = 2 * kMatBytes;
-  static constexpr int kStages = GATHER ? 4 : 5;
+  static constexpr int kStages = 5;
+  static constexpr int kProducerWarps = GATHER ? 4 : 1;
+  static constexpr int kThreads = (kConsumerWarps + kProducerWarps) * 32;
   static constexpr int kMergeFloats = kRowsMax * D + 2 * kRowsMax;
   static constexpr int kMergeBytes = kConsumerWarps * kMergeFloats * 4;
   static constexpr int kFixedBytes = kStages * kStageBytes + kMergeBytes + 256;  // + barriers/flags
@@ -63,7 +67,7 @@ __device__ __forceinline__ int item_valid_len(const DecodeParams& p, int b) {
 }
 
 template <typename T, int D, bool GATHER>
-__global__ void __launch_bounds__((kConsumerWarps + 1) * 32, 1)
+__global__ void __launch_bounds__(SmemPlan<D, GATHER>::kThreads, 1)
 decode_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                    const DecodeParams p) {
   using Plan = SmemPlan<D, GATHER>;
@@ -111,7 +115,7 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
   }
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(&full_bar[s], 1);
+      mbar_init(&full_bar[s], GATHER ? Plan::kProducerWarps * 32 : 1);  // gather: one arrival per copying thread
       mbar_init(&empty_bar[s], kConsumerWarps);
     }
     mbar_fence_init();
@@ -130,8 +134,8 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
   const int u1 = min(u0 + span, total);
   Walker walker{p.paged ? P : nullptr, p.batch, hkvv, tiles_per_req};
 
-  if (warp == kConsumerWarps) {
-    // ================================================================= producer warp
+  if (warp >= kConsumerWarps) {
+    // ================================================================= producer warp(s)
     int stage = 0, phase = 0;
     for (int u = u0; u < u1;) {
       const Piece pc = walker.at(u, u1);
@@ -185,37 +189,38 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
       } else {
-        // Row gather: lane l fetches token rows l and l+32 of each tile; page ids are read one
-        // tile ahead so their latency stays off the critical path.
+        // Row gather (page size 1 or not a multiple of 8): four producer warps copy the 64 token
+        // rows of a tile with 16-byte cp.async into the swizzled layout, two threads per row; a
+        // thread's arrival on the full barrier fires when its copies have landed. Page ids are
+        // read one tile ahead so their latency stays off the critical path.
         const T* kc = reinterpret_cast<const T*>(p.k);
         const T* vc = reinterpret_cast<const T*>(p.v);
-        auto page_of = [&](int t, int i) {
-          const int tok = min(t * kTile + lane + 32 * i, valid - 1);
-          const int pord = tok / p.page_size;
-          return __ldg(p.kv_indices + page_base + pord);
+        const int ptid = tid - kConsumerWarps * 32;
+        const int row = ptid >> 1, part = ptid & 1;
+        constexpr int kChunks = D / 8;  // 16-byte chunks per row
+        auto page_of = [&](int t) {
+          const int tok = min(t * kTile + row, valid - 1);
+          return __ldg(p.kv_indices + page_base + tok / p.page_size);
         };
-        int pg0 = page_of(pc.tile0, 0), pg1 = page_of(pc.tile0, 1);
+        int pg = page_of(pc.tile0);
         for (int t = pc.tile0; t < pc.tile0 + pc.count; ++t) {
-          const int cur0 = pg0, cur1 = pg1;
-          if (t + 1 < pc.tile0 + pc.count) {
-            pg0 = page_of(t + 1, 0);
-            pg1 = page_of(t + 1, 1);
-          }
+          const int cur = pg;
+          if (t + 1 < pc.tile0 + pc.count) pg = page_of(t + 1);
           mbar_wait(&empty_bar[stage], phase ^ 1, p.status, kFaultEmptyBarrier);
-          uint8_t* kdst = stages + stage * Plan::kStageBytes;
-          uint8_t* vdst = kdst + Plan::kMatBytes;
-          if (lane == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * kTile * D * 2);
-          __syncwarp();
+          const uint32_t kdst = smem_u32(stages + stage * Plan::kStageBytes);
+          const uint32_t vdst = kdst + Plan::kMatBytes;
+          const int tok = min(t * kTile + row, valid - 1);
+          const int slot = tok - (tok / p.page_size) * p.page_size;
+          const long long page = min(max(cur, 0), p.num_pages - 1);
+          const long long off = ((page * p.page_size + slot) * p.hkv + h) * D;
 #pragma unroll
-          for (int i = 0; i < 2; ++i) {
-            const int row = lane + 32 * i;
-            const int tok = min(t * kTile + row, valid - 1);
-            const int slot = tok - (tok / p.page_size) * p.page_size;
-            const long long page = min(max(i ? cur1 : cur0, 0), p.num_pages - 1);
-            const long long off = ((page * p.page_size + slot) * p.hkv + h) * D;
-            bulk_load_1d(kdst + row * Plan::kRowBytes, kc + off, D * 2, &full_bar[stage]);
-            bulk_load_1d(vdst + row * Plan::kRowBytes, vc + off, D * 2, &full_bar[stage]);
+          for (int ci = 0; ci < kChunks / 2; ++ci) {
+            const int c = part * (kChunks / 2) + ci;
+            const uint32_t dst_off = (c >> 3) * (kTile * 128) + row * 128 + (((c & 7) ^ (row & 7)) << 4);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(kdst + dst_off), "l"(kc + off + c * 8) : "memory");
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(vdst + dst_off), "l"(vc + off + c * 8) : "memory");
           }
+          asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&full_bar[stage])) : "memory");
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
       }
@@ -288,12 +293,7 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
 #pragma unroll
           for (int kk = 0; kk < D / 16; ++kk) {
             const int d = kk * 16 + (mi & 1) * 8;
-            uint32_t addr;
-            if constexpr (GATHER) {
-              addr = kbase + row * Plan::kRowBytes + d * 2;
-            } else {
-              addr = kbase + (d >> 6) * (kTile * 128) + row * 128 + ((((d & 63) >> 3) ^ (row & 7)) << 4);
-            }
+            const uint32_t addr = kbase + (d >> 6) * (kTile * 128) + row * 128 + ((((d & 63) >> 3) ^ (row & 7)) << 4);
             uint32_t b0, b1, b2, b3;
             ldmatrix_x4(b0, b1, b2, b3, addr);
             mma_16816<T>(s[0], qf[kk], b0, b1);
@@ -350,12 +350,7 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
 #pragma unroll
           for (int dp = 0; dp < D / 16; ++dp) {
             const int d = dp * 16 + (mi >> 1) * 8;
-            uint32_t addr;
-            if constexpr (GATHER) {
-              addr = vbase + row * Plan::kRowBytes + d * 2;
-            } else {
-              addr = vbase + (d >> 6) * (kTile * 128) + row * 128 + ((((d & 63) >> 3) ^ (row & 7)) << 4);
-            }
+            const uint32_t addr = vbase + (d >> 6) * (kTile * 128) + row * 128 + ((((d & 63) >> 3) ^ (row & 7)) << 4);
             uint32_t b0, b1, b2, b3;
             ldmatrix_x4_trans(b0, b1, b2, b3, addr);
             mma_16816<T>(acc[2 * dp], pf, b0, b1);
@@ -615,7 +610,7 @@ int launch_decode(const DecodeSetup& s, cudaStream_t stream) {
   } else if (dev >= 16) {
     CB200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
   }
-  kern<<<s.grid, (kConsumerWarps + 1) * 32, s.smem_bytes, stream>>>(s.tm_k, s.tm_v, s.p);
+  kern<<<s.grid, SmemPlan<D, GATHER>::kThreads, s.smem_bytes, stream>>>(s.tm_k, s.tm_v, s.p);
   CB200_CUDA_TRY(cudaGetLastError());
   return CB200_OK;
 }

@@ -25,6 +25,12 @@
 #include <cstring>
 
 namespace cb200 {
+
+// tcgen05 variant for contiguous caches (mla_decode_tc.cu)
+bool mla_tc_supported(const cb200_mla_decode_args* a);
+size_t mla_tc_partial_bytes(const cb200_mla_decode_args* a, int sms);
+int launch_mla_tc(const cb200_mla_decode_args* a, int* status, int* counters, float* partials, cudaStream_t stream);
+
 namespace mla {
 
 constexpr int kTile = 64;     // tokens per KV tile
@@ -463,8 +469,8 @@ namespace {
 struct MlaSetup {
   mla::Params p;
   int nhb, grid, smem_bytes;
-  bool gather;
-  size_t ws_needed, partials_off, counters_off;
+  bool gather, use_tc;
+  size_t ws_needed, partials_off, counters_off, tc_partials_off;
   CUtensorMap tm_ckv, tm_kpe;
 };
 
@@ -505,7 +511,17 @@ int plan_mla(const cb200_mla_decode_args* a, MlaSetup* s, bool need_maps) {
   constexpr size_t kSlotBytesMax = static_cast<size_t>(Smem<2, false>::kSlotFloats) * 4;
   s->partials_off = kWsHeaderBytes;
   s->counters_off = align_up(s->partials_off + static_cast<size_t>(sms) * 2 * kSlotBytesMax, 256);
-  s->ws_needed = s->counters_off + static_cast<size_t>(a->batch) * p.head_blocks * 4;
+  // Layout: header | partial slots of the mma.sync kernel | arrival counters (shape-independent
+  // offset, shared by both kernels) | partial slots of the tcgen05 kernel.
+  // "auto" takes the warp-MMA kernel: a tcgen05.mma of 128 x N x 16 costs about 93 clocks however small
+  // N is (measured), and the 32-token tiles that fit beside a resident Q leave the tensor-memory
+  // kernel issue-bound. It stays selectable for callers and tests.
+  s->use_tc = mla_tc_supported(a) && a->impl == CB200_MLA_IMPL_TCGEN05;
+  if (a->impl == CB200_MLA_IMPL_TCGEN05 && !s->use_tc) return CB200_ERR_UNSUPPORTED;
+  const size_t n_counters = static_cast<size_t>(a->batch) * (p.head_blocks > 2 * ceil_div(a->num_heads, 128)
+                                                                ? p.head_blocks : 2 * ceil_div(a->num_heads, 128));
+  s->tc_partials_off = align_up(s->counters_off + n_counters * 4, 256);
+  s->ws_needed = s->tc_partials_off + (s->use_tc ? mla_tc_partial_bytes(a, sms) : 0);
   s->grid = static_cast<int>(units_ub < grid ? (units_ub > 0 ? units_ub : 1) : grid);
   if (!need_maps) return CB200_OK;
 
@@ -582,5 +598,8 @@ extern "C" int cb200_mla_decode(const cb200_mla_decode_args* a, void* stream) {
   const int rc = plan_mla(a, &s, true);
   if (rc != CB200_OK) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (s.use_tc)
+    return launch_mla_tc(a, s.p.status, s.p.counters,
+                         reinterpret_cast<float*>(static_cast<uint8_t*>(a->workspace) + s.tc_partials_off), st);
   return a->dtype == CB200_F16 ? dispatch_mla<__half>(s, st) : dispatch_mla<__nv_bfloat16>(s, st);
 }

@@ -199,7 +199,8 @@ def swiglu(x, w0, w1, *, split_k=0, out=None, max_ctas=0):
     return _gemm(_lib.GEMM_SWIGLU, x, w0, w1=w1, split_k=split_k, out=out, max_ctas=max_ctas)
 
 
-def _mla(q_nope, q_pe, ckv, kpe, sm_scale, *, kv_indptr=None, kv_indices=None, out=None, lse=None, max_ctas=0):
+def _mla(q_nope, q_pe, ckv, kpe, sm_scale, *, kv_indptr=None, kv_indices=None, out=None, lse=None, max_ctas=0,
+         impl="auto"):
     q_nope, q_pe, ckv, kpe = _cuda(q_nope, "q_nope"), _cuda(q_pe, "q_pe"), _cuda(ckv, "ckv"), _cuda(kpe, "kpe")
     batch, heads, dc = q_nope.shape
     dp = q_pe.shape[2]
@@ -213,6 +214,7 @@ def _mla(q_nope, q_pe, ckv, kpe, sm_scale, *, kv_indptr=None, kv_indices=None, o
     a.lse = None if lse is None else lse.data_ptr()
     a.batch, a.num_heads, a.ckv_dim, a.kpe_dim = batch, heads, dc, dp
     a.dtype, a.max_ctas, a.sm_scale = _dtype_code(q_nope), max_ctas, float(sm_scale)
+    a.impl = _lib.MLA_IMPL[impl]
     if kv_indptr is not None:
         if kv_indptr.dtype != torch.int32 or kv_indices.dtype != torch.int32:
             raise TypeError("kv_indptr / kv_indices must be int32")
@@ -229,10 +231,12 @@ def _mla(q_nope, q_pe, ckv, kpe, sm_scale, *, kv_indptr=None, kv_indices=None, o
     return out
 
 
-def mla_decode(q, kv, q_pe, k_pe, sm_scale, *, out=None, lse=None, max_ctas=0):
+def mla_decode(q, kv, q_pe, k_pe, sm_scale, *, out=None, lse=None, max_ctas=0, impl="auto"):
     """Static absorbed-latent MLA decode (reference operator: demo/mla_decode.py:8-13):
-    q (B,H,512), kv (B,SKV,512), q_pe (B,H,64), k_pe (B,SKV,64) -> out (B,H,512)."""
-    return _mla(q, q_pe, kv, k_pe, sm_scale, out=out, lse=lse, max_ctas=max_ctas)
+    q (B,H,512), kv (B,SKV,512), q_pe (B,H,64), k_pe (B,SKV,64) -> out (B,H,512).
+    ``impl``: "auto", "tcgen05" (tensor-memory kernel) or "mma_sync" (the warp-MMA kernel that also
+    serves paged caches)."""
+    return _mla(q, q_pe, kv, k_pe, sm_scale, out=out, lse=lse, max_ctas=max_ctas, impl=impl)
 
 
 def mla_paged_decode(q_nope, q_pe, ckv_cache, kpe_cache, kv_indptr, kv_indices, sm_scale, *, out=None, lse=None,

@@ -153,6 +153,8 @@ int cb200_gemm(const cb200_gemm_args* a, void* stream);
  * splitkv/mla_paged_decode_*_splitkv8.py (python/cleave/dynamic/paging/builders/mla.py); argument order
  * and meaning follow python/cleave/dynamic/reference.py:282-320. Paged caches hold one token per page.
  * ---------------------------------------------------------------------------------------- */
+typedef enum { CB200_MLA_IMPL_AUTO = 0, CB200_MLA_IMPL_MMA_SYNC = 1, CB200_MLA_IMPL_TCGEN05 = 2 } cb200_mla_impl;
+
 typedef struct {
   const void* q_nope;    /* (batch, num_heads, 512) */
   const void* q_pe;      /* (batch, num_heads, 64) */
@@ -174,6 +176,7 @@ typedef struct {
   int32_t kv_len;         /* contiguous only */
   int32_t dtype;          /* cb200_dtype */
   int32_t max_ctas;       /* 0 = one CTA per SM */
+  int32_t impl;           /* cb200_mla_impl: 0 = choose, 1 = mma.sync kernel, 2 = tcgen05 kernel (contiguous caches) */
   float sm_scale;
 } cb200_mla_decode_args;
 

@@ -54,13 +54,14 @@ def test_paged_mla_matches_reference_golden(name):
     assert_lse_close(lse, GOLDEN[name][1])
 
 
-@pytest.mark.parametrize("b,h,skv", [(1, 16, 64), (2, 128, 1000), (3, 32, 65), (1, 48, 4097)])
+@pytest.mark.parametrize("impl", ["tcgen05", "mma_sync"])
+@pytest.mark.parametrize("b,h,skv", [(1, 16, 64), (2, 128, 1000), (3, 32, 65), (1, 48, 4097), (1, 200, 33)])
 @pytest.mark.parametrize("dt", ["bf16", "f16"])
 @pytest.mark.parametrize("max_ctas", [0, 1, 5])
-def test_static_mla_vs_oracle(b, h, skv, dt, max_ctas):
+def test_static_mla_vs_oracle(b, h, skv, dt, max_ctas, impl):
     inp = cases.mla_inputs(b + h + skv, b, h, skv, 512, 64, dt)
     scale = 192 ** -0.5
-    got = _run_static(inp, dt, scale, max_ctas=max_ctas)
+    got = _run_static(inp, dt, scale, max_ctas=max_ctas, impl=impl)
     assert_close(got, orc.mla_decode(inp["q"], inp["kv"], inp["q_pe"], inp["k_pe"], scale, dt))
 
 
@@ -74,6 +75,19 @@ def test_paged_mla_vs_oracle(h, max_ctas):
                                               inp["kv_indptr"], inp["kv_indices"], inp["sm_scale"])
     assert_close(out, want_out)
     assert_lse_close(lse, want_lse)
+
+
+def test_static_mla_large_logits_rescale_path():
+    """Logits that jump half-way along the sequence force the tensor-memory kernel through its
+    rescale of the accumulator (the running maximum grows by far more than 2^8 between two tiles)."""
+    inp = cases.mla_inputs(99, 1, 128, 512, 512, 64, "bf16")
+    step = np.where(np.arange(512) < 256, 0.2, 3.0).astype(np.float32)[None, :, None]
+    inp["kv"] = orc.round_to(inp["kv"] * step, "bf16")
+    scale = 0.1
+    want = orc.mla_decode(inp["q"], inp["kv"], inp["q_pe"], inp["k_pe"], scale, "bf16")
+    assert np.isfinite(want).all()
+    for impl in ("tcgen05", "mma_sync"):
+        assert_close(_run_static(inp, "bf16", scale, impl=impl), want, rtol=3e-2, atol=3e-2)
 
 
 def test_mla_full_config_properties():

@@ -120,6 +120,13 @@ def cpu_baseline_run(sample, steps, warmup):
         threads = max([p.get("num_threads", 1) for p in threadpool_info()] or [1])
     except Exception:  # noqa: BLE001
         threads = os.cpu_count() or 1
+    try:  # a launcher may have pinned OMP_NUM_THREADS to 1: give the BLAS pool every host core back
+        from threadpoolctl import threadpool_limits
+
+        threadpool_limits(limits=os.cpu_count())
+        threads = max([p.get("num_threads", 1) for p in threadpool_info()] or [threads])
+    except Exception:  # noqa: BLE001
+        pass
     a = [sample.q.float().numpy(), sample.k_cache.float().numpy(), sample.v_cache.float().numpy(),
          sample.kv_indptr.numpy(), sample.kv_indices.numpy(), sample.kv_last_page_len.numpy()]
     times = []

@@ -70,7 +70,7 @@ __device__ __forceinline__ int cta_of_chunk(long long x, long long C, long long 
   return static_cast<int>(c);
 }
 
-template <int MODE, typename T, int NBW>
+template <int MODE, typename T, int NBW, bool CLUSTER>
 __global__ void __launch_bounds__(GemmPlan<MODE, NBW>::kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b0,
             const __grid_constant__ CUtensorMap tm_b1, const GemmParams p) {
@@ -127,8 +127,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
   const int S = p.chunks_per_tile;
   const long long C = static_cast<long long>(p.tiles_m) * p.tiles_n * S;
   const long long G = gridDim.x;
-  const long long x0 = static_cast<long long>(blockIdx.x) * C / G;
-  const long long x1 = static_cast<long long>(blockIdx.x + 1) * C / G;
+  // Cluster mode: the S chunks of a tile are the S CTAs of one cluster, one chunk each.
+  const long long x0 = CLUSTER ? static_cast<long long>(blockIdx.x) : static_cast<long long>(blockIdx.x) * C / G;
+  const long long x1 = CLUSTER ? x0 + 1 : static_cast<long long>(blockIdx.x + 1) * C / G;
 
   if (warp == 0) {
     // ================================================================ TMA producer
@@ -347,6 +348,90 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&acc_empty[buf]);
+      } else if constexpr (CLUSTER) {
+        // Split-K inside a thread-block cluster: every CTA parks its fp32 accumulator in its own
+        // shared memory (the pipeline stages are idle: all MMAs have completed), the cluster
+        // meets at a hardware barrier, and CTA r reduces rows [r, r + 1) * rows / S over all peers
+        // through distributed shared memory, in rank order (bit-stable), and stores them. No
+        // workspace, no atomics, nobody spins.
+        float* stg = reinterpret_cast<float*>(stages);
+#pragma unroll 1
+        for (int c0 = 0; c0 < kUmmaN; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32(t_acc + c0, r);
+          tmem_ld_wait();
+          float4* dst = reinterpret_cast<float4*>(stg + (static_cast<size_t>(c0 >> 5) * kBM + row) * 32);
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            dst[j] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                 __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+        }
+        if constexpr (MODE == 1) stg[kBM * kUmmaN + row] = rs;
+        cluster_sync();
+        {
+          const int rank = static_cast<int>(cluster_ctarank());
+          constexpr int kItemsPerRow = Plan::kTileN / 8;
+          const int rows_live = min(kBM, p.M - tm * kBM);
+          const int per = ceil_div(rows_live, S);
+          const int r_lo = min(rank * per, rows_live), r_hi = min(r_lo + per, rows_live);
+          const int items = (r_hi - r_lo) * kItemsPerRow;
+          const uint32_t stg_u32 = smem_u32(stg);
+          for (int it = etid; it < items; it += 128) {
+            const int r = r_lo + it / kItemsPerRow, col = (it % kItemsPerRow) * 8;
+            const uint32_t off = ((static_cast<uint32_t>(col >> 5) * kBM + r) * 32 + (col & 31)) * 4;
+            float v[8], up[8], rs_all = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = up[j] = 0.f;
+            for (int q0 = 0; q0 < S; q0 += 2) {  // S is even: two peers' loads in flight, added in rank order
+              float4 a[2][2], bq[2][2];
+              float rq[2] = {0.f, 0.f};
+#pragma unroll
+              for (int u = 0; u < 2; ++u) {
+                const uint32_t base = dsmem_addr(stg_u32, q0 + u);
+                a[u][0] = dsmem_ld_v4(base + off);
+                a[u][1] = dsmem_ld_v4(base + off + 16);
+                if constexpr (MODE == 2) {
+                  const uint32_t uo = off + (Plan::kTileN >> 5) * kBM * 32 * 4;
+                  bq[u][0] = dsmem_ld_v4(base + uo);
+                  bq[u][1] = dsmem_ld_v4(base + uo + 16);
+                }
+                if constexpr (MODE == 1) rq[u] = dsmem_ld_f32(base + (kBM * kUmmaN + r) * 4);
+              }
+#pragma unroll
+              for (int u = 0; u < 2; ++u) {
+                v[0] += a[u][0].x; v[1] += a[u][0].y; v[2] += a[u][0].z; v[3] += a[u][0].w;
+                v[4] += a[u][1].x; v[5] += a[u][1].y; v[6] += a[u][1].z; v[7] += a[u][1].w;
+                if constexpr (MODE == 2) {
+                  up[0] += bq[u][0].x; up[1] += bq[u][0].y; up[2] += bq[u][0].z; up[3] += bq[u][0].w;
+                  up[4] += bq[u][1].x; up[5] += bq[u][1].y; up[6] += bq[u][1].z; up[7] += bq[u][1].w;
+                }
+                rs_all += rq[u];
+              }
+            }
+            const int gcol = tn * Plan::kTileN + col;
+            if (gcol < p.N) {
+              float o[8];
+              if constexpr (MODE == 1) {
+                const float sc = rsqrtf(rs_all * inv_k + p.eps);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) o[j] = v[j] * sc;
+              } else if constexpr (MODE == 2) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) o[j] = v[j] / (1.f + __expf(-v[j])) * up[j];
+              } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) o[j] = v[j];
+              }
+              uint4 pk;
+              pk.x = pack2<T>(o[0], o[1]);
+              pk.y = pack2<T>(o[2], o[3]);
+              pk.z = pack2<T>(o[4], o[5]);
+              pk.w = pack2<T>(o[6], o[7]);
+              *reinterpret_cast<uint4*>(yout + static_cast<size_t>(tm * kBM + r) * p.N + gcol) = pk;
+            }
+          }
+        }
+        cluster_sync();  // nobody leaves while a peer still reads its shared memory
       } else {
         // Partial layout: [column group of 32][row][32 floats], so that a warp (32 consecutive
         // rows) reads and writes 4 KB contiguously; row sums follow the accumulator block.
@@ -490,6 +575,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     }
   }
 
+  if constexpr (CLUSTER) {
+    // the epilogue warps met the cluster twice inside their branch; everyone else does so here
+    if (!(warp >= 2 && warp < 6)) {
+      cluster_sync();
+      cluster_sync();
+    }
+  }
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -506,6 +598,7 @@ constexpr size_t kGemmSlotBytesMax = (static_cast<size_t>(kBM) * 256 + kBM) * 4;
 struct GemmSetup {
   GemmParams p;
   int mode, nbw, grid;
+  bool cluster;  // split-K inside a thread-block cluster (tiny outputs)
   size_t ws_needed, partials_off, counters_off;
   CUtensorMap tm_a, tm_b0, tm_b1;
 };
@@ -538,14 +631,22 @@ int plan_gemm(const cb200_gemm_args* a, GemmSetup* s, bool need_maps) {
   int split = a->split_k;
   if (split <= 0) {  // pick the K split that gives every CTA several chunks
     split = 1;
-    if (tiles % grid_max != 0)
+    if (tiles * 8 <= grid_max && p.kblocks >= 16) {
+      split = 8;  // tiny output: an 8-CTA cluster per tile (portable cluster size)
+    } else if (tiles % grid_max != 0) {
       while (split < 16 && tiles * split < 8LL * grid_max) split *= 2;
+    }
   }
   if (split > p.kblocks) split = p.kblocks;
   p.chunk_kblocks = ceil_div(p.kblocks, split);
   p.chunks_per_tile = ceil_div(p.kblocks, p.chunk_kblocks);
   const long long chunks = tiles * p.chunks_per_tile;
   s->grid = static_cast<int>(chunks < grid_max ? chunks : grid_max);
+  // Few tiles and a power-of-two split that fits the SMs at once: the chunks of a tile become the CTAs
+  // of one cluster and the reduction goes through distributed shared memory.
+  const int S = p.chunks_per_tile;
+  s->cluster = S >= 2 && S <= 16 && (S & (S - 1)) == 0 && chunks <= grid_max && a->max_ctas == 0;
+  if (s->cluster) s->grid = static_cast<int>(chunks);
   s->partials_off = kWsHeaderBytes;
   s->counters_off = align_up(s->partials_off + static_cast<size_t>(sms) * 2 * kGemmSlotBytesMax, 256);
   s->ws_needed = s->counters_off + static_cast<size_t>(tiles) * 4;
@@ -587,20 +688,38 @@ int plan_gemm(const cb200_gemm_args* a, GemmSetup* s, bool need_maps) {
   return CB200_OK;
 }
 
-template <int MODE, typename T, int NBW>
-int launch_gemm(const GemmSetup& s, cudaStream_t stream) {
+template <int MODE, typename T, int NBW, bool CLUSTER>
+int launch_gemm_variant(const GemmSetup& s, cudaStream_t stream) {
   using Plan = GemmPlan<MODE, NBW>;
-  auto kern = gemm_kernel<MODE, T, NBW>;
-  static bool configured[64] = {false};
-  int dev = 0;
-  CB200_CUDA_TRY(cudaGetDevice(&dev));
-  if (dev >= 64 || !configured[dev]) {
-    CB200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Plan::kSmemBytes));
-    if (dev < 64) configured[dev] = true;
+  auto kern = gemm_kernel<MODE, T, NBW, CLUSTER>;
+  CB200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Plan::kSmemBytes));
+  if constexpr (CLUSTER) {
+    if (s.p.chunks_per_tile > 8)
+      CB200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(s.grid, 1, 1);
+    cfg.blockDim = dim3(Plan::kThreads, 1, 1);
+    cfg.dynamicSmemBytes = Plan::kSmemBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = s.p.chunks_per_tile;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    CB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, s.tm_a, s.tm_b0, s.tm_b1, s.p));
+  } else {
+    kern<<<s.grid, Plan::kThreads, Plan::kSmemBytes, stream>>>(s.tm_a, s.tm_b0, s.tm_b1, s.p);
   }
-  kern<<<s.grid, Plan::kThreads, Plan::kSmemBytes, stream>>>(s.tm_a, s.tm_b0, s.tm_b1, s.p);
   CB200_CUDA_TRY(cudaGetLastError());
   return CB200_OK;
+}
+
+template <int MODE, typename T, int NBW>
+int launch_gemm(const GemmSetup& s, cudaStream_t stream) {
+  return s.cluster ? launch_gemm_variant<MODE, T, NBW, true>(s, stream)
+                   : launch_gemm_variant<MODE, T, NBW, false>(s, stream);
 }
 
 template <typename T>

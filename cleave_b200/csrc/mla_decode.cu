@@ -9,10 +9,11 @@
 //
 // Inside a CTA a producer warp streams (CKV, KPE) tiles into a two-stage shared-memory ring (TMA
 // tiled loads with the 128-byte swizzle for contiguous caches, one bulk copy per gathered row
-// otherwise). The four warps of a head block each compute S for 16 of the tile's 64 tokens, agree on
-// the tile's row maxima through shared memory, publish P = exp2(S - m) as 16-bit values, and
-// then each accumulates O for its own 128 of the 512 latent columns: the CKV tile is read from
-// HBM once and used as K and as V.
+// otherwise). The four consumer warps each compute S for 16 of the tile's 64 tokens (for every
+// 16-head block of the item, so that a K fragment feeds several MMAs), agree on the tile's row
+// maxima through shared memory, publish P = exp2(S - m) as 16-bit values, and then each
+// accumulates O for its own 128 of the 512 latent columns: the CKV tile is read from HBM once and
+// used as K and as V.
 //
 // Semantics follow demo/mla_decode.py:8-13 (static) and python/cleave/dynamic/reference.py:108-128,
 // 297-320 (paged) of the reference; it replaces
@@ -68,10 +69,10 @@ struct Smem {
   static constexpr int kStageBytes = (kCkvBytes + kKpeBytes + 1023) / 1024 * 1024;
   static constexpr int kPPitch = kTile * 2 + 16;         // padded P row (64 tokens)
   static constexpr int kPBytes = kRows * kPPitch;
-  static constexpr int kExchFloats = NHB * 4 * 16;       // per-warp row maxima / row sums
+  static constexpr int kExchFloats = 4 * kRows;          // per-warp row maxima / row sums
   static constexpr int kFixed = kStages * kStageBytes + kQBytes + kPBytes + 2 * kExchFloats * 4 + 256;
   static constexpr int kSlotFloats = kRows * kCkv + 2 * kRows;  // partial O, m, l
-  static constexpr int kThreads = (NHB * 4 + 1) * 32;
+  static constexpr int kThreads = (4 + 1) * 32;          // four consumer warps and the producer
 };
 
 template <typename T, int NHB, bool GATHER>
@@ -79,7 +80,7 @@ __global__ void __launch_bounds__(Smem<NHB, GATHER>::kThreads, 1)
 mla_decode_kernel(const __grid_constant__ CUtensorMap tm_ckv, const __grid_constant__ CUtensorMap tm_kpe,
                   const Params p) {
   using L = Smem<NHB, GATHER>;
-  constexpr int kConsumerWarps = NHB * 4;
+  constexpr int kConsumerWarps = 4;
   constexpr int kCThreads = kConsumerWarps * 32;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -202,7 +203,10 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_ckv, const __grid_const
   }
 
   // =================================================================== consumer warps
-  const int hb = warp >> 2, ws = warp & 3;  // head block of this warp; its token slice / latent slice
+  // Warp ws computes S for tokens [16 ws, 16 ws + 16) of every tile and O for latent columns
+  // [128 ws, 128 ws + 128), in both cases for all NHB 16-head blocks of the item: a K (or V)
+  // fragment read from shared memory feeds NHB MMAs.
+  const int ws = warp;
   const int r0 = lane >> 2, c2 = (lane & 3) * 2;
   const int mi = lane >> 3, rr = lane & 7;
   T* outp = reinterpret_cast<T*>(p.out);
@@ -244,12 +248,18 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_ckv, const __grid_const
     }
     named_bar_sync(1, kCThreads);
 
-    float acc[16][4];
+    float acc[NHB][16][4];
+    float m_run[NHB][2], l_run[NHB][2];
 #pragma unroll
-    for (int n = 0; n < 16; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
-    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
-    const uint32_t q_row_addr = q_u32 + (hb * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * L::kQPitch + (lane >> 4) * 16;
-    const uint32_t p_row_addr = p_u32 + (hb * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * L::kPPitch + (lane >> 4) * 16;
+    for (int hb = 0; hb < NHB; ++hb) {
+#pragma unroll
+      for (int n = 0; n < 16; ++n) acc[hb][n][0] = acc[hb][n][1] = acc[hb][n][2] = acc[hb][n][3] = 0.f;
+      m_run[hb][0] = m_run[hb][1] = -INFINITY;
+      l_run[hb][0] = l_run[hb][1] = 0.f;
+    }
+    // ldmatrix row address of an A fragment (Q or P) for head block 0; block hb is 16 rows further
+    const uint32_t q_row_addr = q_u32 + ((lane & 7) + ((lane >> 3) & 1) * 8) * L::kQPitch + (lane >> 4) * 16;
+    const uint32_t p_row_addr = p_u32 + ((lane & 7) + ((lane >> 3) & 1) * 8) * L::kPPitch + (lane >> 4) * 16;
 
     for (int t = pc.tile0; t < pc.tile0 + pc.count; ++t) {
       mbar_wait(&full_bar[stage], phase, p.status, kFaultFullBarrier);
@@ -257,14 +267,19 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_ckv, const __grid_const
       const uint32_t kpe_base = ckv_base + L::kCkvBytes;
       const int tok0 = t * kTile + ws * 16;
 
-      // ---- S = Q_nope CKV^T + Q_pe KPE^T for this warp's 16 tokens
-      float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+      // ---- S = Q_nope CKV^T + Q_pe KPE^T for this warp's 16 tokens, all head blocks
+      float s[NHB][2][4], s2[NHB][2][4];
+#pragma unroll
+      for (int hb = 0; hb < NHB; ++hb)
+#pragma unroll
+        for (int nb = 0; nb < 2; ++nb) {
+          s[hb][nb][0] = s[hb][nb][1] = s[hb][nb][2] = s[hb][nb][3] = 0.f;
+          s2[hb][nb][0] = s2[hb][nb][1] = s2[hb][nb][2] = s2[hb][nb][3] = 0.f;
+        }
       {
         const int row = ws * 16 + (mi >> 1) * 8 + rr;  // token row of this lane's ldmatrix address
 #pragma unroll 4
         for (int kk = 0; kk < kQk / 16; ++kk) {
-          uint32_t a[4];
-          ldmatrix_x4(a[0], a[1], a[2], a[3], q_row_addr + kk * 32);
           uint32_t addr;
           if (kk < kCkv / 16) {
             const int d = kk * 16 + (mi & 1) * 8;
@@ -277,72 +292,99 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_ckv, const __grid_const
           }
           uint32_t b0, b1, b2, b3;
           ldmatrix_x4(b0, b1, b2, b3, addr);
-          mma_16816<T>(s[0], a, b0, b1);
-          mma_16816<T>(s[1], a, b2, b3);
+#pragma unroll
+          for (int hb = 0; hb < NHB; ++hb) {
+            uint32_t a[4];
+            ldmatrix_x4(a[0], a[1], a[2], a[3], q_row_addr + hb * 16 * L::kQPitch + kk * 32);
+            if (kk & 1) {  // odd K steps go to a second accumulator: half the dependent-MMA chain
+              mma_16816<T>(s2[hb][0], a, b0, b1);
+              mma_16816<T>(s2[hb][1], a, b2, b3);
+            } else {
+              mma_16816<T>(s[hb][0], a, b0, b1);
+              mma_16816<T>(s[hb][1], a, b2, b3);
+            }
+          }
+        }
+#pragma unroll
+        for (int hb = 0; hb < NHB; ++hb)
+#pragma unroll
+          for (int nb = 0; nb < 2; ++nb)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) s[hb][nb][e] += s2[hb][nb][e];
+      }
+      // ---- tile-wide row maxima (the four warps agree through shared memory)
+#pragma unroll
+      for (int hb = 0; hb < NHB; ++hb) {
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int nb = 0; nb < 2; ++nb) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int tok = tok0 + nb * 8 + c2 + (e & 1);
+            const float x = tok < valid ? s[hb][nb][e] * p.scale_log2 : -INFINITY;
+            s[hb][nb][e] = x;
+            if (e < 2) mx0 = fmaxf(mx0, x); else mx1 = fmaxf(mx1, x);
+          }
+        }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        if ((lane & 3) == 0) {
+          max_exch[ws * L::kRows + hb * 16 + r0] = mx0;
+          max_exch[ws * L::kRows + hb * 16 + r0 + 8] = mx1;
         }
       }
-      // ---- tile-wide row maxima (the four warps of the head block agree through shared memory)
-      float mx0 = -INFINITY, mx1 = -INFINITY;
+      named_bar_sync(2, kCThreads);
+      float sc[NHB][2];
 #pragma unroll
-      for (int nb = 0; nb < 2; ++nb) {
+      for (int hb = 0; hb < NHB; ++hb) {
+        float mt0 = -INFINITY, mt1 = -INFINITY;
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int tok = tok0 + nb * 8 + c2 + (e & 1);
-          const float x = tok < valid ? s[nb][e] * p.scale_log2 : -INFINITY;
-          s[nb][e] = x;
-          if (e < 2) mx0 = fmaxf(mx0, x); else mx1 = fmaxf(mx1, x);
+        for (int w = 0; w < 4; ++w) {
+          mt0 = fmaxf(mt0, max_exch[w * L::kRows + hb * 16 + r0]);
+          mt1 = fmaxf(mt1, max_exch[w * L::kRows + hb * 16 + r0 + 8]);
         }
-      }
-      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
-      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
-      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
-      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-      if ((lane & 3) == 0) {
-        max_exch[warp * 16 + r0] = mx0;
-        max_exch[warp * 16 + r0 + 8] = mx1;
-      }
-      named_bar_sync(2 + hb, 128);
-      float mt0 = -INFINITY, mt1 = -INFINITY;
-#pragma unroll
-      for (int w = 0; w < 4; ++w) {
-        mt0 = fmaxf(mt0, max_exch[(hb * 4 + w) * 16 + r0]);
-        mt1 = fmaxf(mt1, max_exch[(hb * 4 + w) * 16 + r0 + 8]);
-      }
-      const float mn0 = fmaxf(m_run[0], mt0), mn1 = fmaxf(m_run[1], mt1);
-      const float mu0 = mn0 == -INFINITY ? 0.f : mn0, mu1 = mn1 == -INFINITY ? 0.f : mn1;
-      const float sc0 = fast_exp2(m_run[0] - mu0), sc1 = fast_exp2(m_run[1] - mu1);
-      m_run[0] = mn0;
-      m_run[1] = mn1;
-      // ---- P = exp2(S - m), published as 16-bit values for all four warps
-      {
+        const float mn0 = fmaxf(m_run[hb][0], mt0), mn1 = fmaxf(m_run[hb][1], mt1);
+        const float mu0 = mn0 == -INFINITY ? 0.f : mn0, mu1 = mn1 == -INFINITY ? 0.f : mn1;
+        sc[hb][0] = fast_exp2(m_run[hb][0] - mu0);
+        sc[hb][1] = fast_exp2(m_run[hb][1] - mu1);
+        m_run[hb][0] = mn0;
+        m_run[hb][1] = mn1;
+        // ---- P = exp2(S - m), published as 16-bit values for all four warps
         float ps0 = 0.f, ps1 = 0.f;
         uint8_t* prow0 = p_smem + (hb * 16 + r0) * L::kPPitch + (ws * 16 + c2) * 2;
         uint8_t* prow1 = prow0 + 8 * L::kPPitch;
 #pragma unroll
         for (int nb = 0; nb < 2; ++nb) {
-          const float p0 = fast_exp2(s[nb][0] - mu0), p1 = fast_exp2(s[nb][1] - mu0);
-          const float p2 = fast_exp2(s[nb][2] - mu1), p3 = fast_exp2(s[nb][3] - mu1);
+          const float p0 = fast_exp2(s[hb][nb][0] - mu0), p1 = fast_exp2(s[hb][nb][1] - mu0);
+          const float p2 = fast_exp2(s[hb][nb][2] - mu1), p3 = fast_exp2(s[hb][nb][3] - mu1);
           ps0 += p0 + p1;
           ps1 += p2 + p3;
           *reinterpret_cast<uint32_t*>(prow0 + nb * 16) = pack2<T>(p0, p1);
           *reinterpret_cast<uint32_t*>(prow1 + nb * 16) = pack2<T>(p2, p3);
         }
-        l_run[0] = l_run[0] * sc0 + ps0;
-        l_run[1] = l_run[1] * sc1 + ps1;
+        l_run[hb][0] = l_run[hb][0] * sc[hb][0] + ps0;
+        l_run[hb][1] = l_run[hb][1] * sc[hb][1] + ps1;
       }
-      named_bar_sync(2 + hb, 128);
+      named_bar_sync(2, kCThreads);
 #pragma unroll
-      for (int n = 0; n < 16; ++n) {
-        acc[n][0] *= sc0;
-        acc[n][1] *= sc0;
-        acc[n][2] *= sc1;
-        acc[n][3] *= sc1;
+      for (int hb = 0; hb < NHB; ++hb) {
+#pragma unroll
+        for (int n = 0; n < 16; ++n) {
+          acc[hb][n][0] *= sc[hb][0];
+          acc[hb][n][1] *= sc[hb][0];
+          acc[hb][n][2] *= sc[hb][1];
+          acc[hb][n][3] *= sc[hb][1];
+        }
       }
       // ---- O[:, 128 ws .. 128 ws + 127] += P CKV (the same tile, now as V)
 #pragma unroll
       for (int ks = 0; ks < kTile / 16; ++ks) {
-        uint32_t pf[4];
-        ldmatrix_x4(pf[0], pf[1], pf[2], pf[3], p_row_addr + ks * 32);
+        uint32_t pf[NHB][4];
+#pragma unroll
+        for (int hb = 0; hb < NHB; ++hb)
+          ldmatrix_x4(pf[hb][0], pf[hb][1], pf[hb][2], pf[hb][3], p_row_addr + hb * 16 * L::kPPitch + ks * 32);
         const int row = ks * 16 + (mi & 1) * 8 + rr;
 #pragma unroll
         for (int dp = 0; dp < 8; ++dp) {
@@ -351,8 +393,11 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_ckv, const __grid_const
                                        : ckv_base + (d >> 6) * (kTile * 128) + row * 128 + ((((d & 63) >> 3) ^ (row & 7)) << 4);
           uint32_t b0, b1, b2, b3;
           ldmatrix_x4_trans(b0, b1, b2, b3, addr);
-          mma_16816<T>(acc[2 * dp], pf, b0, b1);
-          mma_16816<T>(acc[2 * dp + 1], pf, b2, b3);
+#pragma unroll
+          for (int hb = 0; hb < NHB; ++hb) {
+            mma_16816<T>(acc[hb][2 * dp], pf[hb], b0, b1);
+            mma_16816<T>(acc[hb][2 * dp + 1], pf[hb], b2, b3);
+          }
         }
       }
       __syncwarp();
@@ -361,26 +406,24 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_ckv, const __grid_const
     }
 
     // ---- finish the piece: total row sums over the four token slices
-    l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], 1);
-    l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], 2);
-    l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], 1);
-    l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], 2);
-    if ((lane & 3) == 0) {
-      sum_exch[warp * 16 + r0] = l_run[0];
-      sum_exch[warp * 16 + r0 + 8] = l_run[1];
-    }
-    named_bar_sync(2 + hb, 128);
-    float L0 = 0.f, L1 = 0.f;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) {
-      L0 += sum_exch[(hb * 4 + w) * 16 + r0];
-      L1 += sum_exch[(hb * 4 + w) * 16 + r0 + 8];
+    for (int hb = 0; hb < NHB; ++hb) {
+#pragma unroll
+      for (int h2 = 0; h2 < 2; ++h2) {
+        float l = l_run[hb][h2];
+        l += __shfl_xor_sync(0xffffffffu, l, 1);
+        l += __shfl_xor_sync(0xffffffffu, l, 2);
+        if ((lane & 3) == 0) sum_exch[ws * L::kRows + hb * 16 + r0 + 8 * h2] = l;
+      }
     }
-    const int row0 = hb * 16 + r0, row1 = row0 + 8;  // rows inside the item
-    const int h0 = head0 + row0, h1 = head0 + row1;  // heads
+    named_bar_sync(2, kCThreads);
     const size_t bh = static_cast<size_t>(pc.b) * p.heads;
+    const bool starts_here = (u == pc.unit0);
+    const bool whole = starts_here && pc.count == pc.n_tiles;
+    float* slot = p.partials + (static_cast<size_t>(blockIdx.x) * 2 + (starts_here ? 1 : 0)) * L::kSlotFloats;
 
-    auto store_final = [&](const float (&o)[16][4], float M0, float M1, float S0, float S1) {
+    auto store_final = [&](int hb, const float (&o)[16][4], float M0, float M1, float S0, float S1) {
+      const int h0 = head0 + hb * 16 + r0, h1 = h0 + 8;
       const float inv0 = S0 > 0.f ? 1.f / S0 : 0.f, inv1 = S1 > 0.f ? 1.f / S1 : 0.f;
 #pragma unroll
       for (int n = 0; n < 16; ++n) {
@@ -396,25 +439,34 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_ckv, const __grid_const
       }
     };
 
-    const bool starts_here = (u == pc.unit0);
-    const bool whole = starts_here && pc.count == pc.n_tiles;
-    if (whole) {
-      store_final(acc, m_run[0], m_run[1], L0, L1);
-    } else {
-      // ---- leave a partial (unnormalised O, m, l); the last CTA to arrive combines
-      float* slot = p.partials + (static_cast<size_t>(blockIdx.x) * 2 + (starts_here ? 1 : 0)) * L::kSlotFloats;
 #pragma unroll
-      for (int n = 0; n < 16; ++n) {
-        const int col = ws * 128 + n * 8 + c2;
-        *reinterpret_cast<float2*>(slot + row0 * kCkv + col) = make_float2(acc[n][0], acc[n][1]);
-        *reinterpret_cast<float2*>(slot + row1 * kCkv + col) = make_float2(acc[n][2], acc[n][3]);
+    for (int hb = 0; hb < NHB; ++hb) {
+      float L0 = 0.f, L1 = 0.f;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        L0 += sum_exch[w * L::kRows + hb * 16 + r0];
+        L1 += sum_exch[w * L::kRows + hb * 16 + r0 + 8];
       }
-      if (ws == 0 && (lane & 3) == 0) {
-        slot[L::kRows * kCkv + row0] = m_run[0];
-        slot[L::kRows * kCkv + row1] = m_run[1];
-        slot[L::kRows * kCkv + L::kRows + row0] = L0;
-        slot[L::kRows * kCkv + L::kRows + row1] = L1;
+      const int row0 = hb * 16 + r0, row1 = row0 + 8;  // rows inside the item
+      if (whole) {
+        store_final(hb, acc[hb], m_run[hb][0], m_run[hb][1], L0, L1);
+      } else {
+        // ---- leave a partial (unnormalised O, m, l); the last CTA to arrive combines
+#pragma unroll
+        for (int n = 0; n < 16; ++n) {
+          const int col = ws * 128 + n * 8 + c2;
+          *reinterpret_cast<float2*>(slot + row0 * kCkv + col) = make_float2(acc[hb][n][0], acc[hb][n][1]);
+          *reinterpret_cast<float2*>(slot + row1 * kCkv + col) = make_float2(acc[hb][n][2], acc[hb][n][3]);
+        }
+        if (ws == 0 && (lane & 3) == 0) {
+          slot[L::kRows * kCkv + row0] = m_run[hb][0];
+          slot[L::kRows * kCkv + row1] = m_run[hb][1];
+          slot[L::kRows * kCkv + L::kRows + row0] = L0;
+          slot[L::kRows * kCkv + L::kRows + row1] = L1;
+        }
       }
+    }
+    if (!whole) {
       __threadfence();
       named_bar_sync(1, kCThreads);
       const int c_first = pc.unit0 / span, c_last = (pc.unit0 + pc.n_tiles - 1) / span;
@@ -426,34 +478,45 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_ckv, const __grid_const
       named_bar_sync(1, kCThreads);
       if (flags[0]) {
         __threadfence();
-        float Mc0 = -INFINITY, Mc1 = -INFINITY, Lc0 = 0.f, Lc1 = 0.f;
 #pragma unroll
-        for (int n = 0; n < 16; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
-        for (int cta = c_first; cta <= c_last; ++cta) {
-          const float* src = p.partials + (static_cast<size_t>(cta) * 2 + (cta == c_first ? 1 : 0)) * L::kSlotFloats;
-          const float mi0 = __ldcg(src + L::kRows * kCkv + row0), mi1 = __ldcg(src + L::kRows * kCkv + row1);
-          const float li0 = __ldcg(src + L::kRows * kCkv + L::kRows + row0);
-          const float li1 = __ldcg(src + L::kRows * kCkv + L::kRows + row1);
-          const float Mn0 = fmaxf(Mc0, mi0), Mn1 = fmaxf(Mc1, mi1);
-          const float Mu0 = Mn0 == -INFINITY ? 0.f : Mn0, Mu1 = Mn1 == -INFINITY ? 0.f : Mn1;
-          const float a0 = fast_exp2(Mc0 - Mu0), b0 = fast_exp2(mi0 - Mu0);
-          const float a1 = fast_exp2(Mc1 - Mu1), b1 = fast_exp2(mi1 - Mu1);
-          Lc0 = a0 * Lc0 + b0 * li0;
-          Lc1 = a1 * Lc1 + b1 * li1;
+        for (int hb = 0; hb < NHB; ++hb) {
+          const int row0 = hb * 16 + r0, row1 = row0 + 8;
+          float Mc0 = -INFINITY, Mc1 = -INFINITY, Lc0 = 0.f, Lc1 = 0.f;
 #pragma unroll
-          for (int n = 0; n < 16; ++n) {
-            const int col = ws * 128 + n * 8 + c2;
-            const float2 x0 = __ldcg(reinterpret_cast<const float2*>(src + row0 * kCkv + col));
-            const float2 x1 = __ldcg(reinterpret_cast<const float2*>(src + row1 * kCkv + col));
-            acc[n][0] = a0 * acc[n][0] + b0 * x0.x;
-            acc[n][1] = a0 * acc[n][1] + b0 * x0.y;
-            acc[n][2] = a1 * acc[n][2] + b1 * x1.x;
-            acc[n][3] = a1 * acc[n][3] + b1 * x1.y;
+          for (int n = 0; n < 16; ++n) acc[hb][n][0] = acc[hb][n][1] = acc[hb][n][2] = acc[hb][n][3] = 0.f;
+          for (int cta = c_first; cta <= c_last; ++cta) {
+            const float* src = p.partials + (static_cast<size_t>(cta) * 2 + (cta == c_first ? 1 : 0)) * L::kSlotFloats;
+            const float mi0 = __ldcg(src + L::kRows * kCkv + row0), mi1 = __ldcg(src + L::kRows * kCkv + row1);
+            const float li0 = __ldcg(src + L::kRows * kCkv + L::kRows + row0);
+            const float li1 = __ldcg(src + L::kRows * kCkv + L::kRows + row1);
+            const float Mn0 = fmaxf(Mc0, mi0), Mn1 = fmaxf(Mc1, mi1);
+            const float Mu0 = Mn0 == -INFINITY ? 0.f : Mn0, Mu1 = Mn1 == -INFINITY ? 0.f : Mn1;
+            const float a0 = fast_exp2(Mc0 - Mu0), b0 = fast_exp2(mi0 - Mu0);
+            const float a1 = fast_exp2(Mc1 - Mu1), b1 = fast_exp2(mi1 - Mu1);
+            Lc0 = a0 * Lc0 + b0 * li0;
+            Lc1 = a1 * Lc1 + b1 * li1;
+#pragma unroll
+            for (int n0 = 0; n0 < 16; n0 += 4) {  // four column blocks' loads in flight together
+              float2 x0[4], x1[4];
+#pragma unroll
+              for (int n = 0; n < 4; ++n) {
+                const int col = ws * 128 + (n0 + n) * 8 + c2;
+                x0[n] = __ldcg(reinterpret_cast<const float2*>(src + row0 * kCkv + col));
+                x1[n] = __ldcg(reinterpret_cast<const float2*>(src + row1 * kCkv + col));
+              }
+#pragma unroll
+              for (int n = 0; n < 4; ++n) {
+                acc[hb][n0 + n][0] = a0 * acc[hb][n0 + n][0] + b0 * x0[n].x;
+                acc[hb][n0 + n][1] = a0 * acc[hb][n0 + n][1] + b0 * x0[n].y;
+                acc[hb][n0 + n][2] = a1 * acc[hb][n0 + n][2] + b1 * x1[n].x;
+                acc[hb][n0 + n][3] = a1 * acc[hb][n0 + n][3] + b1 * x1[n].y;
+              }
+            }
+            Mc0 = Mn0;
+            Mc1 = Mn1;
           }
-          Mc0 = Mn0;
-          Mc1 = Mn1;
+          store_final(hb, acc[hb], Mc0, Mc1, Lc0, Lc1);
         }
-        store_final(acc, Mc0, Mc1, Lc0, Lc1);
         if (tid == 0) *counter = 0;  // ready for the next launch
       }
     }

@@ -1,0 +1,261 @@
+// Large GEMMs on CTA pairs: tcgen05.mma.cta_group::2 computes a 256 x 256 output tile on two
+// neighbouring SMs. Each CTA of the pair holds its 128 rows of A and of the accumulator and only
+// HALF of B's columns (the hardware feeds both halves to both SMs), so a CTA moves 32 KB of operands
+// per K block where the single-CTA kernel moves 48 KB for the same 128 x 256 x 64 of work per SM.
+//   MODE 0  Y = X @ W                    B half of CTA r: columns [256 tn + 128 r, +128) of W
+//   MODE 2  Y = silu(X @ W0) * (X @ W1)  B half of CTA 0: 128 columns of W0; of CTA 1: the same columns of W1,
+//                                        so every CTA's accumulator is gate | up for its own rows
+// Used for whole tiles only (no split-K); small or skinny problems stay with gemm_tcgen05.cu.
+//
+// Every CTA loads its own operands (TMA without multicast; the transaction bytes of both CTAs are
+// counted on the first CTA's barrier); the first CTA's MMA thread issues for the pair; one commit
+// arrives on the barriers of both CTAs. Warp roles per CTA: 0 = TMA producer, 1 = MMA issuer
+// (first CTA only) and TMEM owner, 2..5 = epilogue for the CTA's own 128 rows.
+//
+// Replaces the same reference kernels as gemm_tcgen05.cu (expected_kernels/matmul.py, swiglu.py).
+
+#include "common.cuh"
+
+#include <cstring>
+#include <type_traits>
+
+namespace cb200 {
+namespace pair {
+
+constexpr int kBM = 128, kBK = 64, kChunkN = 64;
+constexpr int kABytes = kBM * kBK * 2;           // 16 KB
+constexpr int kBChunkBytes = kBK * kChunkN * 2;  // 8 KB
+constexpr int kBHalfChunks = 2;                  // 128 columns of B per CTA
+constexpr int kStageBytes = kABytes + kBHalfChunks * kBChunkBytes;  // 32 KB
+constexpr int kStages = 6;
+constexpr int kUmmaN = 256;
+constexpr int kThreads = 192;
+constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 1024;
+constexpr uint32_t kTmemCols = 512;  // two accumulators of 256 columns
+
+struct Params {
+  void* y;
+  int* status;
+  int M, N, K, tiles_m, tiles_n, kblocks;
+};
+
+template <int MODE, typename T>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b0,
+                 const __grid_constant__ CUtensorMap tm_b1, const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* stages = smem;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);  // used on the first CTA
+  uint64_t* empty_bar = full_bar + kStages;
+  uint64_t* acc_full = empty_bar + kStages;   // [2]
+  uint64_t* acc_empty = acc_full + 2;         // [2] used on the first CTA: both CTAs' epilogue warps arrive
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_empty + 2);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t rank = cluster_ctarank();  // 0 = first CTA of the pair (issues the MMAs)
+
+  if (tid == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 8);  // four epilogue warps of each CTA
+    }
+    mbar_fence_init();
+    tma_prefetch_desc(&tm_a);
+    tma_prefetch_desc(&tm_b0);
+    if (MODE == 2) tma_prefetch_desc(&tm_b1);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_holder, kTmemCols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync();  // both CTAs' barriers exist before anyone signals across the pair
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_holder);
+
+  const int pair_id = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  const int tiles = p.tiles_m * p.tiles_n;
+  constexpr int kTileN = MODE == 2 ? 128 : 256;  // output columns per tile
+
+  if (warp == 0) {
+    // ================================================================ TMA producer (both CTAs)
+    int stage = 0, phase = 0;
+    const CUtensorMap* tm_b = (MODE == 2 && rank == 1) ? &tm_b1 : &tm_b0;
+    for (int t = pair_id; t < tiles; t += n_pairs) {
+      const int tm = t / p.tiles_n, tn = t - tm * p.tiles_n;
+      const int row0 = tm * 256 + static_cast<int>(rank) * kBM;
+      const int col0 = MODE == 2 ? tn * 128 : tn * 256 + static_cast<int>(rank) * 128;
+      for (int kb = 0; kb < p.kblocks; ++kb) {
+        mbar_wait(&empty_bar[stage], phase ^ 1, p.status, kFaultEmptyBarrier);
+        if (lane == 0) {
+          uint8_t* a_dst = stages + stage * kStageBytes;
+          uint8_t* b_dst = a_dst + kABytes;
+          if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * kStageBytes);  // both CTAs' bytes
+          tma_load_2d_pair(a_dst, &tm_a, &full_bar[stage], kb * kBK, row0);
+#pragma unroll
+          for (int j = 0; j < kBHalfChunks; ++j)
+            tma_load_2d_pair(b_dst + j * kBChunkBytes, tm_b, &full_bar[stage], col0 + j * kChunkN, kb * kBK);
+        }
+        __syncwarp();
+        if (++stage == kStages) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else if (warp == 1) {
+    // ================================================================ MMA issuer (first CTA only)
+    if (rank == 0) {
+      constexpr uint32_t idesc = umma_idesc(std::is_same<T, __nv_bfloat16>::value, true, 256, kUmmaN);
+      int stage = 0, phase = 0, buf = 0, acc_phase = 0;
+      for (int t = pair_id; t < tiles; t += n_pairs) {
+        mbar_wait(&acc_empty[buf], acc_phase ^ 1, p.status, kFaultTmemBarrier);
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * kUmmaN;
+        for (int kb = 0; kb < p.kblocks; ++kb) {
+          mbar_wait(&full_bar[stage], phase, p.status, kFaultFullBarrier);
+          tc_fence_after();
+          if (lane == 0) {
+            const uint32_t a_addr = smem_u32(stages + stage * kStageBytes);
+            const uint32_t b_addr = a_addr + kABytes;
+#pragma unroll
+            for (int k = 0; k < kBK / 16; ++k) {
+              const uint64_t adesc = umma_smem_desc(a_addr + k * 32, 16, 8 * 128);
+              const uint64_t bdesc = umma_smem_desc(b_addr + k * 16 * 128, kBChunkBytes, 8 * 128);
+              umma_f16_pair(d_tmem, adesc, bdesc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            }
+            umma_commit_pair(&empty_bar[stage]);
+          }
+          __syncwarp();
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+        if (lane == 0) umma_commit_pair(&acc_full[buf]);
+        __syncwarp();
+        if (++buf == 2) { buf = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    // ================================================================ epilogue (both CTAs, own rows)
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    T* yout = reinterpret_cast<T*>(p.y);
+    int buf = 0, acc_phase = 0;
+    for (int t = pair_id; t < tiles; t += n_pairs) {
+      const int tm = t / p.tiles_n, tn = t - tm * p.tiles_n;
+      const int gr = tm * 256 + static_cast<int>(rank) * kBM + row;
+      mbar_wait(&acc_full[buf], acc_phase, p.status, kFaultMmaBarrier);
+      tc_fence_after();
+      const uint32_t t_acc = tmem_base + buf * kUmmaN + (static_cast<uint32_t>(quarter * 32) << 16);
+#pragma unroll 1
+      for (int c0 = 0; c0 < kTileN; c0 += 32) {
+        uint32_t r[32], r2[32];
+        tmem_ld_32x32(t_acc + c0, r);
+        if constexpr (MODE == 2) tmem_ld_32x32(t_acc + 128 + c0, r2);
+        tmem_ld_wait();
+        if (gr < p.M) {
+          float o[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float v = __uint_as_float(r[j]);
+            o[j] = MODE == 2 ? v / (1.f + __expf(-v)) * __uint_as_float(r2[j]) : v;
+          }
+          const int gc0 = tn * kTileN + c0;
+          T* dst = yout + static_cast<size_t>(gr) * p.N + gc0;
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            if (gc0 + j < p.N) {
+              uint4 pk;
+              pk.x = pack2<T>(o[j], o[j + 1]);
+              pk.y = pack2<T>(o[j + 2], o[j + 3]);
+              pk.z = pack2<T>(o[j + 4], o[j + 5]);
+              pk.w = pack2<T>(o[j + 6], o[j + 7]);
+              *reinterpret_cast<uint4*>(dst + j) = pk;
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_remote(&acc_empty[buf], 0);  // the first CTA's MMA thread waits for all eight warps
+      if (++buf == 2) { buf = 0; acc_phase ^= 1; }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync();  // no CTA frees tensor memory or leaves while the pair's MMAs may still touch it
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace pair
+
+// ------------------------------------------------------------------------------------- host side
+bool gemm_pair_supported(const cb200_gemm_args* a, int sms) {
+  if (a->op == CB200_GEMM_RMSNORM || a->split_k > 1 || a->max_ctas != 0) return false;
+  if (a->m < 512) return false;
+  const long long tiles = static_cast<long long>(ceil_div(a->m, 256)) * ceil_div(a->n, a->op == CB200_GEMM_SWIGLU ? 128 : 256);
+  return tiles >= 2LL * (sms / 2);  // enough whole tiles to keep every pair busy
+}
+
+template <int MODE, typename T>
+static int launch_pair_kernel(const pair::Params& p, const CUtensorMap& ta, const CUtensorMap& tb0,
+                              const CUtensorMap& tb1, cudaStream_t stream) {
+  auto kern = pair::gemm_pair_kernel<MODE, T>;
+  CB200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, pair::kSmemBytes));
+  cudaLaunchConfig_t cfg = {};
+  cfg.blockDim = dim3(pair::kThreads, 1, 1);
+  cfg.dynamicSmemBytes = pair::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  // The tiles are dealt round-robin to the pairs, so the grid must be exactly the number of pairs
+  // that are resident at once (SMs that cannot form a pair inside their GPC stay idle).
+  static int resident_pairs[16] = {};
+  int dev = 0;
+  CB200_CUDA_TRY(cudaGetDevice(&dev));
+  int pairs = (dev >= 0 && dev < 16) ? resident_pairs[dev] : 0;
+  if (pairs == 0) {
+    cfg.gridDim = dim3((sm_count() / 2) * 2, 1, 1);
+    CB200_CUDA_TRY(cudaOccupancyMaxActiveClusters(&pairs, kern, &cfg));
+    if (pairs <= 0) return CB200_ERR_CUDA;
+    if (dev >= 0 && dev < 16) resident_pairs[dev] = pairs;
+  }
+  const int tiles = p.tiles_m * p.tiles_n;
+  if (pairs > tiles) pairs = tiles;
+  cfg.gridDim = dim3(2 * pairs, 1, 1);
+  CB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, ta, tb0, tb1, p));
+  CB200_CUDA_TRY(cudaGetLastError());
+  return CB200_OK;
+}
+
+int launch_gemm_pair(const cb200_gemm_args* a, int* status, const CUtensorMap& tm_a, const CUtensorMap& tm_b0,
+                     const CUtensorMap& tm_b1, cudaStream_t stream) {
+  const int sms = sm_count();
+  if (sms <= 0) return CB200_ERR_CUDA;
+  pair::Params p{};
+  p.y = a->y;
+  p.status = status;
+  p.M = a->m; p.N = a->n; p.K = a->k;
+  p.tiles_m = ceil_div(a->m, 256);
+  p.tiles_n = ceil_div(a->n, a->op == CB200_GEMM_SWIGLU ? 128 : 256);
+  p.kblocks = ceil_div(a->k, pair::kBK);
+  const bool f16 = a->dtype == CB200_F16;
+  if (a->op == CB200_GEMM_SWIGLU)
+    return f16 ? launch_pair_kernel<2, __half>(p, tm_a, tm_b0, tm_b1, stream)
+               : launch_pair_kernel<2, __nv_bfloat16>(p, tm_a, tm_b0, tm_b1, stream);
+  return f16 ? launch_pair_kernel<0, __half>(p, tm_a, tm_b0, tm_b1, stream)
+             : launch_pair_kernel<0, __nv_bfloat16>(p, tm_a, tm_b0, tm_b1, stream);
+}
+
+}  // namespace cb200

@@ -24,6 +24,7 @@
 
 #include "common.cuh"
 
+#include <cstdlib>
 #include <cstring>
 #include <type_traits>
 
@@ -591,7 +592,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
 }
 
 // ------------------------------------------------------------------------------------- host side
+bool gemm_pair_supported(const cb200_gemm_args* a, int sms);
+int launch_gemm_pair(const cb200_gemm_args* a, int* status, const CUtensorMap& tm_a, const CUtensorMap& tm_b0,
+                     const CUtensorMap& tm_b1, cudaStream_t stream);
+
 namespace {
+
+bool gemm_pair_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("CB200_GEMM_PAIR");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
 
 constexpr size_t kGemmSlotBytesMax = (static_cast<size_t>(kBM) * 256 + kBM) * 4;
 
@@ -599,6 +612,7 @@ struct GemmSetup {
   GemmParams p;
   int mode, nbw, grid;
   bool cluster;  // split-K inside a thread-block cluster (tiny outputs)
+  bool pair;     // whole 256 x 256 tiles on CTA pairs (gemm_pair.cu)
   size_t ws_needed, partials_off, counters_off;
   CUtensorMap tm_a, tm_b0, tm_b1;
 };
@@ -647,6 +661,12 @@ int plan_gemm(const cb200_gemm_args* a, GemmSetup* s, bool need_maps) {
   const int S = p.chunks_per_tile;
   s->cluster = S >= 2 && S <= 16 && (S & (S - 1)) == 0 && chunks <= grid_max && a->max_ctas == 0;
   if (s->cluster) s->grid = static_cast<int>(chunks);
+  s->pair = gemm_pair_supported(a, sms) && gemm_pair_enabled();
+  if (s->pair) {
+    s->cluster = false;
+    p.chunk_kblocks = p.kblocks;
+    p.chunks_per_tile = 1;
+  }
   s->partials_off = kWsHeaderBytes;
   s->counters_off = align_up(s->partials_off + static_cast<size_t>(sms) * 2 * kGemmSlotBytesMax, 256);
   s->ws_needed = s->counters_off + static_cast<size_t>(tiles) * 4;
@@ -752,5 +772,6 @@ extern "C" int cb200_gemm(const cb200_gemm_args* a, void* stream) {
   const int rc = plan_gemm(a, &s, true);
   if (rc != CB200_OK) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (s.pair) return launch_gemm_pair(a, s.p.status, s.tm_a, s.tm_b0, s.tm_b1, st);
   return a->dtype == CB200_F16 ? dispatch_gemm<__half>(s, st) : dispatch_gemm<__nv_bfloat16>(s, st);
 }

@@ -75,6 +75,21 @@ def test_swiglu_vs_oracle(m, n, k, split_k):
     assert_close(got, orc.swiglu(inp["x"], inp["w0"], inp["w1"], "bf16"))
 
 
+@pytest.mark.parametrize("family,m,n,k,dt", [
+    ("matmul", 3000, 3336, 200, "f16"),    # ragged in M, N and K; a K shorter than the stage ring
+    ("matmul", 2048, 4864, 1032, "bf16"),  # 17 K blocks: the stage ring wraps inside a tile
+    ("swiglu", 2100, 2504, 136, "bf16"),
+    ("swiglu", 1024, 4736, 520, "f16"),
+])
+def test_large_gemms_on_cta_pairs(family, m, n, k, dt):
+    """Shapes with at least one 256 x 256 tile per CTA pair take the cta_group::2 kernel."""
+    inp = cases.gemm_inputs(m + k, m, n, k, dt, n_w=2 if family == "swiglu" else 1)
+    got = _run(family, inp, {"dtype": dt})
+    want = orc.swiglu(inp["x"], inp["w0"], inp["w1"], dt) if family == "swiglu" else orc.matmul(inp["x"], inp["w0"], dt)
+    assert_close(got, want)
+    assert np.array_equal(got, _run(family, inp, {"dtype": dt}))
+
+
 def test_split_k_partials_sum_like_the_unsplit_product():
     """Reference: tests/pipeline_api/test_e2e.py:58-81 (the split-K chain equals x.float() @ w.float());
     here every split factor and every grid size must agree with the unsplit launch to fp32 round-off."""

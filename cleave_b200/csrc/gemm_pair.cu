@@ -39,6 +39,18 @@ struct Params {
   int M, N, K, tiles_m, tiles_n, kblocks;
 };
 
+// Tile order: bands of kGroupM tile rows, column-major inside a band, so the tiles that the resident
+// pairs work on at the same time share a few row strips of X and a few column strips of W in L2.
+constexpr int kGroupM = 8;
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& tm, int& tn) {
+  const int per_band = kGroupM * tiles_n;
+  const int band = t / per_band, r = t - band * per_band;
+  const int first = band * kGroupM;
+  const int rows = min(kGroupM, tiles_m - first);
+  tn = r / rows;
+  tm = first + (r - tn * rows);
+}
+
 template <int MODE, typename T>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b0,
@@ -88,7 +100,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     int stage = 0, phase = 0;
     const CUtensorMap* tm_b = (MODE == 2 && rank == 1) ? &tm_b1 : &tm_b0;
     for (int t = pair_id; t < tiles; t += n_pairs) {
-      const int tm = t / p.tiles_n, tn = t - tm * p.tiles_n;
+      int tm, tn;
+      tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
       const int row0 = tm * 256 + static_cast<int>(rank) * kBM;
       const int col0 = MODE == 2 ? tn * 128 : tn * 256 + static_cast<int>(rank) * 128;
       for (int kb = 0; kb < p.kblocks; ++kb) {
@@ -144,7 +157,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     T* yout = reinterpret_cast<T*>(p.y);
     int buf = 0, acc_phase = 0;
     for (int t = pair_id; t < tiles; t += n_pairs) {
-      const int tm = t / p.tiles_n, tn = t - tm * p.tiles_n;
+      int tm, tn;
+      tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
       const int gr = tm * 256 + static_cast<int>(rank) * kBM + row;
       mbar_wait(&acc_full[buf], acc_phase, p.status, kFaultMmaBarrier);
       tc_fence_after();

@@ -575,11 +575,13 @@ int plan_mla(const cb200_mla_decode_args* a, MlaSetup* s, bool need_maps) {
   s->partials_off = kWsHeaderBytes;
   s->counters_off = align_up(s->partials_off + static_cast<size_t>(sms) * 2 * kSlotBytesMax, 256);
   // Layout: header | partial slots of the mma.sync kernel | arrival counters (shape-independent
-  // offset, shared by both kernels) | partial slots of the tcgen05 kernel.
-  // "auto" takes the warp-MMA kernel: a tcgen05.mma of 128 x N x 16 costs about 93 clocks however small
-  // N is (measured), and the 32-token tiles that fit beside a resident Q leave the tensor-memory
-  // kernel issue-bound. It stays selectable for callers and tests.
-  s->use_tc = mla_tc_supported(a) && a->impl == CB200_MLA_IMPL_TCGEN05;
+  // offset, shared by both paths) | P, block statistics and partial slots of the tcgen05 kernels.
+  // "auto" takes the tcgen05 pair of kernels for contiguous caches when its 128-row MMAs are at least
+  // half full and there are enough token blocks to spread over the SMs; the warp-MMA kernel serves
+  // paged caches, few heads and short caches.
+  s->use_tc = mla_tc_supported(a) &&
+              (a->impl == CB200_MLA_IMPL_TCGEN05 ||
+               (a->impl == CB200_MLA_IMPL_AUTO && a->num_heads >= 64 && a->kv_len >= 512));
   if (a->impl == CB200_MLA_IMPL_TCGEN05 && !s->use_tc) return CB200_ERR_UNSUPPORTED;
   const size_t n_counters = static_cast<size_t>(a->batch) * (p.head_blocks > 2 * ceil_div(a->num_heads, 128)
                                                                 ? p.head_blocks : 2 * ceil_div(a->num_heads, 128));

@@ -1,21 +1,28 @@
-// MLA decode on the tcgen05 tensor cores for contiguous caches (the static operator).
+// MLA decode on the tcgen05 tensor cores for contiguous caches (the static operator), in two
+// kernels that meet in the workspace:
 //
-// A CTA owns (request, block of up to 128 heads, half of the 512 latent output columns, one of S
-// equal KV ranges). Rows of every MMA are the heads (UMMA M = 128):
-//   S = Q K^T      A = Q  (shared memory, K-major, resident for the whole CTA: 9 chunks of 64 columns)
-//                  B = KV tile of 32 tokens (shared memory, K-major), D = S in TMEM (32 columns, two buffers)
-//   O += P V       A = P  (TMEM, 16-bit pairs written by the softmax warps)
-//                  B = the same KV tile, columns [256 half, 256 half + 256) read MN-major, D = O in TMEM (256 columns)
-// so a KV tile is fetched once and used as K and as V. The accumulator of all 512 latent columns
-// would fill tensor memory on its own; splitting the output columns over two CTAs leaves room for
-// S and P at the price of computing S in both.
+//   scores   P = exp2(scale * Q K^T - m)  per block of 128 tokens, with the block's row maximum m and
+//            row sum l. A CTA owns (request, block of up to 128 heads, a range of token blocks). Q
+//            (128 heads x 576) and the latent and rope caches stream together through a four-stage
+//            ring, a 64-column chunk of Q beside 64 columns x 256 tokens of cache, so every MMA
+//            is 128 x 256 x 16. S sits in tensor memory (two buffers of 256 columns); eight epilogue
+//            warps (thread = head row = TMEM lane, one warp group per 128-token block) turn it into
+//            P in the cache's 16-bit type and write P, m and l to the workspace.
+//   values   O = sum_blocks 2^(m_block - m_ref) P_block V_block. A CTA owns (request, head block, half
+//            of the 512 output columns, one of S token ranges). The softmax warps read a block of P
+//            rows, scale them to the running reference maximum and store them to tensor memory,
+//            where they are the A operand; B is the latent tile (128 tokens x 256 columns, MN-major)
+//            from a three-stage TMA ring; O (128 x 256 fp32) stays in tensor memory and is rescaled
+//            only when the reference maximum grows by more than 2^8 (exact: the factor is applied to
+//            O and to the row sum alike). The S CTAs of an item are one thread-block cluster and
+//            combine their partial results through distributed shared memory; with more than
+//            eight splits they leave fp32 partials in the workspace and the last one to arrive
+//            combines them (nobody waits).
 //
-// Warp roles: 0 = TMA producer, 1 = MMA issuer and TMEM owner, 2..5 = softmax / epilogue (thread =
-// head row = TMEM lane). The softmax keeps a reference maximum per row and rescales O only when
-// the running maximum has grown by more than 2^8 (exact: the factor is applied to O and to the row
-// sum alike), so O stays in tensor memory between tiles.
-// With S > 1 the CTAs of an item leave fp32 partials in the workspace and the last one to arrive
-// combines them (fused split-KV log-sum-exp combine, nobody waits).
+// Why two kernels: the accumulator for 128 heads x 512 columns fills tensor memory on its own, and
+// Q plus a KV tile large enough for full-width MMAs does not fit in shared memory. Splitting the
+// work at P keeps every MMA 256 wide; P (2 bytes per head and token) is small next to the caches
+// and is still in L2 when the second kernel reads it.
 //
 // Reference semantics: demo/mla_decode.py:8-13.
 
@@ -27,22 +34,30 @@
 namespace cb200 {
 namespace mlatc {
 
-constexpr int kBN = 32;                 // tokens per KV tile
 constexpr int kCkv = 512, kKpe = 64, kQk = 576;
-constexpr int kChunks = kQk / 64;       // 9 chunks of 64 columns (128 bytes)
-constexpr int kQChunkBytes = 128 * 128; // 128 heads x 128 bytes
-constexpr int kKvChunkBytes = kBN * 128;
-constexpr int kQBytes = kChunks * kQChunkBytes;      // 147 456
-constexpr int kStageBytes = kChunks * kKvChunkBytes; // 36 864
-constexpr int kStages = 2;
-constexpr int kDvHalf = 256;
-constexpr int kSmemBytes = kQBytes + kStages * kStageBytes + 1024 /*barriers*/ + 1024 /*alignment*/;
-constexpr int kThreads = 192;
-constexpr int kSlotFloats = 128 * kDvHalf + 256;  // O partial, m, l
-// TMEM columns
-constexpr uint32_t kColO = 0, kColS = 256, kColP = 320, kTmemCols = 512;
+constexpr int kChunks = kQk / 64;        // 9 chunks of 64 columns (128 bytes)
+constexpr int kBlk = 128;                // tokens per block of P
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.f;  // log2 units
+
+// ---- scores kernel
+constexpr int kQChunkBytes = 128 * 128;             // 128 heads x 128 bytes
+constexpr int kSTile = 256;                         // tokens per MMA tile (two blocks)
+constexpr int kKChunkBytes = kSTile * 128;          // 32 768
+constexpr int kKStageBytes = kQChunkBytes + kKChunkBytes;  // a Q chunk and the matching cache chunk
+constexpr int kKStages = 4;
+constexpr int kScoreSmem = kKStages * kKStageBytes + 1024 + 1024;
+constexpr int kScoreThreads = 320;                  // producer, MMA, eight epilogue warps
+
+// ---- values kernel
+constexpr int kDvHalf = 256;
+constexpr int kVChunkBytes = kBlk * 128;            // 64 columns x 128 tokens
+constexpr int kVStageBytes = (kDvHalf / 64) * kVChunkBytes;  // 65 536
+constexpr int kVStages = 3;
+constexpr int kValueSmem = kVStages * kVStageBytes + 1024 + 1024;
+constexpr int kValueThreads = 192;
+constexpr int kSlotFloats = 128 * kDvHalf + 256;    // O partial, m, l
+constexpr uint32_t kColO = 0, kColP = 256;          // P: two buffers of 64 columns
 
 struct Params {
   void* out;
@@ -50,52 +65,47 @@ struct Params {
   int* status;
   int* counters;
   float* partials;
-  int batch, heads, head_blocks, kv_len, splits, tiles_per_split;
+  void* pbuf;      // (batch * heads, kv_pad) 16-bit
+  float2* stats;   // (batch * heads, blocks): (m, l) per block
+  int batch, heads, head_blocks, kv_len, kv_pad, blocks;
+  int ranges, blocks_per_range;   // scores kernel
+  int splits, blocks_per_split;   // values kernel
   float scale_log2;
 };
 
 template <typename T>
-__global__ void __launch_bounds__(kThreads, 1)
-mla_tc_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_constant__ CUtensorMap tm_qp,
-              const __grid_constant__ CUtensorMap tm_ckv, const __grid_constant__ CUtensorMap tm_kpe, const Params p) {
+__global__ void __launch_bounds__(kScoreThreads, 1)
+mla_scores_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_constant__ CUtensorMap tm_qp,
+                  const __grid_constant__ CUtensorMap tm_ckv, const __grid_constant__ CUtensorMap tm_kpe,
+                  const Params p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* q_smem = smem;
-  uint8_t* kv_smem = smem + kQBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kQBytes + kStages * kStageBytes);
-  uint64_t* kv_full = bars;         // [2] TMA landed
-  uint64_t* kv_empty = bars + 2;    // [2] S and PV of the tile have finished reading the stage
-  uint64_t* q_full = bars + 4;
-  uint64_t* s_full = bars + 5;      // [2] S complete in TMEM
-  uint64_t* s_empty = bars + 7;     // [2] softmax has read S
-  uint64_t* p_full = bars + 9;      // P written (and O rescaled if needed)
-  uint64_t* pv_done = bars + 10;    // PV of the tile complete
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 11);
-  int* flag = reinterpret_cast<int*>(tmem_holder + 1);
+  uint8_t* k_smem = smem;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kKStages * kKStageBytes);
+  uint64_t* k_full = bars;                  // [kKStages] TMA landed
+  uint64_t* k_empty = bars + kKStages;      // [kKStages] the MMAs have read the stage
+  uint64_t* s_full = bars + 2 * kKStages;   // [2] S complete in TMEM
+  uint64_t* s_empty = s_full + 2;           // [2] the epilogue has read S
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(s_empty + 2);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-
-  // ---- which piece is this CTA's
   int x = blockIdx.x;
-  const int split = x % p.splits; x /= p.splits;
-  const int dh = x & 1; x >>= 1;
+  const int rg = x % p.ranges; x /= p.ranges;
   const int hb = x % p.head_blocks;
   const int b = x / p.head_blocks;
-  const int n_tiles_total = ceil_div(p.kv_len, kBN);
-  const int t0 = min(split * p.tiles_per_split, n_tiles_total);
-  const int t1 = min(t0 + p.tiles_per_split, n_tiles_total);
-  const int nt = t1 - t0;  // the host picks splits so that every split owns at least one tile
+  const int u0 = min(rg * p.blocks_per_range, p.blocks);
+  const int u1 = min(u0 + p.blocks_per_range, p.blocks);
+  const int n_tiles = (u1 - u0 + 1) / 2;  // MMA tiles of two blocks
 
   if (tid == 0) {
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(&kv_full[s], 1);
-      mbar_init(&kv_empty[s], 1);
-      mbar_init(&s_full[s], 1);
-      mbar_init(&s_empty[s], 4);
+    for (int s = 0; s < kKStages; ++s) {
+      mbar_init(&k_full[s], 1);
+      mbar_init(&k_empty[s], 1);
     }
-    mbar_init(q_full, 1);
-    mbar_init(p_full, 4);
-    mbar_init(pv_done, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&s_full[s], 1);
+      mbar_init(&s_empty[s], 8);
+    }
     mbar_fence_init();
     tma_prefetch_desc(&tm_qn);
     tma_prefetch_desc(&tm_qp);
@@ -103,7 +113,7 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_constant__
     tma_prefetch_desc(&tm_kpe);
   }
   if (warp == 1) {
-    tmem_alloc(tmem_holder, kTmemCols);
+    tmem_alloc(tmem_holder, 512);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -113,111 +123,268 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_constant__
 
   if (warp == 0) {
     // ================================================================ TMA producer
-    if (lane == 0) {
-      mbar_arrive_expect_tx(q_full, kQBytes);
-#pragma unroll
-      for (int c = 0; c < kCkv / 64; ++c) tma_load_3d(q_smem + c * kQChunkBytes, &tm_qn, q_full, c * 64, hb * 128, b);
-      tma_load_3d(q_smem + (kCkv / 64) * kQChunkBytes, &tm_qp, q_full, 0, hb * 128, b);
-    }
-    __syncwarp();
-    for (int j = 0; j < nt; ++j) {
-      const int st = j & 1;
-      mbar_wait(&kv_empty[st], ((j >> 1) & 1) ^ 1, p.status, kFaultEmptyBarrier);
-      if (lane == 0) {
-        uint8_t* dst = kv_smem + st * kStageBytes;
-        mbar_arrive_expect_tx(&kv_full[st], kStageBytes);
-#pragma unroll
-        for (int c = 0; c < kCkv / 64; ++c)
-          tma_load_3d(dst + c * kKvChunkBytes, &tm_ckv, &kv_full[st], c * 64, (t0 + j) * kBN, b);
-        tma_load_3d(dst + (kCkv / 64) * kKvChunkBytes, &tm_kpe, &kv_full[st], 0, (t0 + j) * kBN, b);
+    // Q is streamed with the cache (a CTA has only a few tiles; Q comes from L2 after the first
+    // touch), which leaves the whole of shared memory to the ring: 192 KB in flight per SM.
+    int st = 0, ph = 0;
+    for (int t = 0; t < n_tiles; ++t) {
+      const int tok0 = (u0 + 2 * t) * kBlk;
+      for (int c = 0; c < kChunks; ++c) {
+        mbar_wait(&k_empty[st], ph ^ 1, p.status, kFaultEmptyBarrier);
+        if (lane == 0) {
+          uint8_t* q_dst = k_smem + st * kKStageBytes;
+          uint8_t* k_dst = q_dst + kQChunkBytes;
+          mbar_arrive_expect_tx(&k_full[st], kKStageBytes);
+          if (c < kCkv / 64) {
+            tma_load_3d(k_dst, &tm_ckv, &k_full[st], c * 64, tok0, b);
+            tma_load_3d(q_dst, &tm_qn, &k_full[st], c * 64, hb * 128, b);
+          } else {
+            tma_load_3d(k_dst, &tm_kpe, &k_full[st], 0, tok0, b);
+            tma_load_3d(q_dst, &tm_qp, &k_full[st], 0, hb * 128, b);
+          }
+        }
+        __syncwarp();
+        if (++st == kKStages) { st = 0; ph ^= 1; }
       }
-      __syncwarp();
     }
   } else if (warp == 1) {
     // ================================================================ MMA issuer
-    constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
-    constexpr uint32_t idesc_s = umma_idesc(kBf16, /*b_mn_major=*/false, 128, kBN);
-    constexpr uint32_t idesc_pv = umma_idesc(kBf16, /*b_mn_major=*/true, 128, kDvHalf);
-    const uint32_t q_addr = smem_u32(q_smem), kv_addr = smem_u32(kv_smem);
-    auto issue_s = [&](int j) {
-      const int st = j & 1, sb = j & 1;
-      mbar_wait(&kv_full[st], (j >> 1) & 1, p.status, kFaultFullBarrier);
-      mbar_wait(&s_empty[sb], ((j >> 1) & 1) ^ 1, p.status, kFaultTmemBarrier);
+    constexpr uint32_t idesc = umma_idesc(std::is_same<T, __nv_bfloat16>::value, /*b_mn_major=*/false, 128, kSTile);
+    const uint32_t k_addr = smem_u32(k_smem);
+    int st = 0, ph = 0;
+    for (int t = 0; t < n_tiles; ++t) {
+      const int sb = t & 1;
+      mbar_wait(&s_empty[sb], ((t >> 1) & 1) ^ 1, p.status, kFaultTmemBarrier);
       tc_fence_after();
-      if (lane == 0) {
-        const uint32_t d = tmem_base + kColS + sb * kBN;
-#pragma unroll 1
-        for (int c = 0; c < kChunks; ++c) {
+      const uint32_t d = tmem_base + sb * kSTile;
+      for (int c = 0; c < kChunks; ++c) {
+        mbar_wait(&k_full[st], ph, p.status, kFaultFullBarrier);
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t q_addr = k_addr + st * kKStageBytes;
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) {
-            const uint64_t adesc = umma_smem_desc(q_addr + c * kQChunkBytes + kk * 32, 16, 8 * 128);
-            const uint64_t bdesc = umma_smem_desc(kv_addr + st * kStageBytes + c * kKvChunkBytes + kk * 32, 16, 8 * 128);
-            umma_f16(d, adesc, bdesc, idesc_s, (c > 0 || kk > 0) ? 1u : 0u);
+            const uint64_t adesc = umma_smem_desc(q_addr + kk * 32, 16, 8 * 128);
+            const uint64_t bdesc = umma_smem_desc(q_addr + kQChunkBytes + kk * 32, 16, 8 * 128);
+            umma_f16(d, adesc, bdesc, idesc, (c > 0 || kk > 0) ? 1u : 0u);
           }
+          umma_commit(&k_empty[st]);
         }
-        umma_commit(&s_full[sb]);
+        __syncwarp();
+        if (++st == kKStages) { st = 0; ph ^= 1; }
       }
-      __syncwarp();
-    };
-    mbar_wait(q_full, 0, p.status, kFaultFullBarrier);
-    if (nt > 0) issue_s(0);
-    for (int j = 0; j < nt; ++j) {
-      if (j + 1 < nt) issue_s(j + 1);
-      mbar_wait(p_full, j & 1, p.status, kFaultTmemBarrier);
-      tc_fence_after();
-      if (lane == 0) {
-        const int st = j & 1;
-        const uint32_t v_addr = kv_addr + st * kStageBytes + (dh * (kDvHalf / 64)) * kKvChunkBytes;
-#pragma unroll
-        for (int ks = 0; ks < kBN / 16; ++ks) {
-          // B: MN-major, 16 token rows of 128 bytes; 64-column chunks are kKvChunkBytes apart
-          const uint64_t bdesc = umma_smem_desc(v_addr + ks * 16 * 128, kKvChunkBytes, 8 * 128);
-          umma_f16_ts(tmem_base + kColO, tmem_base + kColP + ks * 8, bdesc, idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
-        }
-        umma_commit(&kv_empty[st]);
-        umma_commit(pv_done);
-      }
+      if (lane == 0) umma_commit(&s_full[sb]);
       __syncwarp();
     }
   } else {
-    // ================================================================ softmax / epilogue
-    const int quarter = warp & 3;
-    const int row = quarter * 32 + lane;  // head row inside the block = TMEM lane
-    const int etid = tid - 64;
+    // ================================================================ epilogue: S -> P, m, l
+    const int quarter = warp & 3;          // the TMEM lanes this warp may read
+    const int half = (warp - 2) >> 2;      // which block of the MMA tile
+    const int row = quarter * 32 + lane;
+    const int head = hb * 128 + row;
+    const bool live = head < p.heads;
     const uint32_t lane_field = static_cast<uint32_t>(quarter * 32) << 16;
-    float m_ref = 0.f, l_run = 0.f;
-    for (int j = 0; j < nt; ++j) {
-      const int sb = j & 1;
-      mbar_wait(&s_full[sb], (j >> 1) & 1, p.status, kFaultMmaBarrier);
+    const size_t prow = (static_cast<size_t>(b) * p.heads + head) * p.kv_pad;
+    for (int t = 0; t < n_tiles; ++t) {
+      const int sb = t & 1;
+      const int u = u0 + 2 * t + half;
+      mbar_wait(&s_full[sb], (t >> 1) & 1, p.status, kFaultMmaBarrier);
       tc_fence_after();
-      uint32_t r[32];
-      tmem_ld_32x32(tmem_base + lane_field + kColS + sb * kBN, r);
-      tmem_ld_wait();
+      if (u < u1) {
+        const uint32_t t_s = tmem_base + lane_field + sb * kSTile + half * kBlk;
+        const int tok0 = u * kBlk;
+        float mx = -INFINITY;
+#pragma unroll 1
+        for (int c0 = 0; c0 < kBlk; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32(t_s + c0, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (tok0 + c0 + i < p.kv_len) mx = fmaxf(mx, __uint_as_float(r[i]) * p.scale_log2);
+        }
+        const float m = mx == -INFINITY ? 0.f : mx;
+        float l = 0.f;
+        T* pdst = reinterpret_cast<T*>(p.pbuf) + prow + tok0;
+#pragma unroll 1
+        for (int c0 = 0; c0 < kBlk; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32(t_s + c0, r);
+          tmem_ld_wait();
+          float e[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            e[i] = tok0 + c0 + i < p.kv_len ? fast_exp2(fmaf(__uint_as_float(r[i]), p.scale_log2, -m)) : 0.f;
+            l += e[i];
+          }
+          if (live) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              uint4 q4;
+              q4.x = pack2<T>(e[i], e[i + 1]);
+              q4.y = pack2<T>(e[i + 2], e[i + 3]);
+              q4.z = pack2<T>(e[i + 4], e[i + 5]);
+              q4.w = pack2<T>(e[i + 6], e[i + 7]);
+              *reinterpret_cast<uint4*>(pdst + c0 + i) = q4;
+            }
+          }
+        }
+        if (live) p.stats[(static_cast<size_t>(b) * p.heads + head) * p.blocks + u] = make_float2(m, l);
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_empty[sb]);
-      const int tok0 = (t0 + j) * kBN;
-      float xs[32], mx = -INFINITY;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <typename T, bool CLUSTER>
+__global__ void __launch_bounds__(kValueThreads, 1)
+mla_values_kernel(const __grid_constant__ CUtensorMap tm_ckv, const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* v_smem = smem;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kVStages * kVStageBytes);
+  uint64_t* v_full = bars;                 // [3] TMA landed
+  uint64_t* v_empty = bars + kVStages;     // [3] the MMAs have read the stage
+  uint64_t* p_full = bars + 2 * kVStages;  // [2] scaled P stored to TMEM (and O rescaled if needed)
+  uint64_t* p_empty = p_full + 2;          // [2] the MMAs that read the P buffer have completed
+  uint64_t* o_done = p_empty + 2;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(o_done + 1);
+  int* flag = reinterpret_cast<int*>(tmem_holder + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  int x = blockIdx.x;
+  const int split = x % p.splits; x /= p.splits;  // cluster mode: the splits of an item are one cluster
+  const int dh = x & 1; x >>= 1;
+  const int hb = x % p.head_blocks;
+  const int b = x / p.head_blocks;
+  const int t0 = min(split * p.blocks_per_split, p.blocks);
+  const int t1 = min(t0 + p.blocks_per_split, p.blocks);
+  const int nt = t1 - t0;
+
+  if (tid == 0) {
+    for (int s = 0; s < kVStages; ++s) {
+      mbar_init(&v_full[s], 1);
+      mbar_init(&v_empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&p_full[s], 4);
+      mbar_init(&p_empty[s], 1);
+    }
+    mbar_init(o_done, 1);
+    mbar_fence_init();
+    tma_prefetch_desc(&tm_ckv);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_holder, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_holder);
+
+  if (warp == 0) {
+    // ================================================================ TMA producer
+    int st = 0, ph = 0;
+    for (int j = 0; j < nt; ++j) {
+      mbar_wait(&v_empty[st], ph ^ 1, p.status, kFaultEmptyBarrier);
+      if (lane == 0) {
+        uint8_t* dst = v_smem + st * kVStageBytes;
+        mbar_arrive_expect_tx(&v_full[st], kVStageBytes);
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        xs[i] = tok0 + i < p.kv_len ? __uint_as_float(r[i]) * p.scale_log2 : -INFINITY;
-        mx = fmaxf(mx, xs[i]);
+        for (int c = 0; c < kDvHalf / 64; ++c)
+          tma_load_3d(dst + c * kVChunkBytes, &tm_ckv, &v_full[st], dh * kDvHalf + c * 64, (t0 + j) * kBlk, b);
       }
+      __syncwarp();
+      if (++st == kVStages) { st = 0; ph ^= 1; }
+    }
+    if constexpr (CLUSTER) {  // the two meetings of the combine
+      cluster_sync();
+      cluster_sync();
+    }
+  } else if (warp == 1) {
+    // ================================================================ MMA issuer
+    constexpr uint32_t idesc = umma_idesc(std::is_same<T, __nv_bfloat16>::value, /*b_mn_major=*/true, 128, kDvHalf);
+    const uint32_t v_addr0 = smem_u32(v_smem);
+    int st = 0, ph = 0;
+    for (int j = 0; j < nt; ++j) {
+      const int pb = j & 1;
+      mbar_wait(&v_full[st], ph, p.status, kFaultFullBarrier);
+      mbar_wait(&p_full[pb], (j >> 1) & 1, p.status, kFaultTmemBarrier);
+      tc_fence_after();
+      if (lane == 0) {
+        const uint32_t v_addr = v_addr0 + st * kVStageBytes;
+#pragma unroll
+        for (int ks = 0; ks < kBlk / 16; ++ks) {
+          // B: MN-major, 16 token rows of 128 bytes per step; 64-column chunks are kVChunkBytes apart
+          const uint64_t bdesc = umma_smem_desc(v_addr + ks * 16 * 128, kVChunkBytes, 8 * 128);
+          umma_f16_ts(tmem_base + kColO, tmem_base + kColP + pb * 64 + ks * 8, bdesc, idesc, (j > 0 || ks > 0) ? 1u : 0u);
+        }
+        umma_commit(&v_empty[st]);
+        umma_commit(&p_empty[pb]);
+        if (j == nt - 1) umma_commit(o_done);
+      }
+      __syncwarp();
+      if (++st == kVStages) { st = 0; ph ^= 1; }
+    }
+    if constexpr (CLUSTER) {
+      cluster_sync();
+      cluster_sync();
+    }
+  } else {
+    // ================================================================ P scaling / epilogue
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;  // head row inside the block = TMEM lane
+    const int etid = tid - 64;
+    const int head = hb * 128 + row;
+    const bool live = head < p.heads;
+    const uint32_t lane_field = static_cast<uint32_t>(quarter * 32) << 16;
+    const size_t hrow = static_cast<size_t>(b) * p.heads + head;
+    const T* prow = reinterpret_cast<const T*>(p.pbuf) + hrow * p.kv_pad;
+    float m_ref = 0.f, l_run = 0.f;
+    // P rows and statistics of the next block are fetched while the current one is processed
+    uint4 raw[16];
+    float2 st_next = make_float2(0.f, 0.f);
+    auto fetch = [&](int u) {
+      if (live) {
+        st_next = __ldcg(p.stats + hrow * p.blocks + u);
+        const uint4* src = reinterpret_cast<const uint4*>(prow + static_cast<size_t>(u) * kBlk);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) raw[i] = __ldcg(src + i);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) raw[i] = make_uint4(0u, 0u, 0u, 0u);
+      }
+    };
+    if (nt > 0) fetch(t0);
+    for (int j = 0; j < nt; ++j) {
+      const int pb = j & 1;
+      const float2 st = st_next;
       float alpha = 1.f;
       bool rescale = false;
       if (j == 0) {
-        m_ref = mx == -INFINITY ? 0.f : mx;
-      } else if (mx > m_ref + kRescaleThreshold) {
-        alpha = fast_exp2(m_ref - mx);
-        m_ref = mx;
+        m_ref = st.x;
+      } else if (st.x > m_ref + kRescaleThreshold) {
+        alpha = fast_exp2(m_ref - st.x);
+        m_ref = st.x;
         rescale = true;
       }
-      // O and P may only be touched once the previous tile's PV has completed
-      if (j > 0) {
-        mbar_wait(pv_done, (j - 1) & 1, p.status, kFaultMmaBarrier);
+      const float f = fast_exp2(st.x - m_ref);
+      l_run = l_run * alpha + st.y * f;
+      // the P buffer is free once the MMAs of tile j - 2 have completed
+      mbar_wait(&p_empty[pb], ((j >> 1) & 1) ^ 1, p.status, kFaultMmaBarrier);
+      if (__any_sync(0xffffffffu, rescale)) {  // rare: the reference maximum grew by more than 2^8
+        // O may only be touched when no MMA is in flight: tile j - 1 is the last one issued
+        mbar_wait(&p_empty[pb ^ 1], ((j - 1) >> 1) & 1, p.status, kFaultMmaBarrier);
         tc_fence_after();
-      }
-      if (__any_sync(0xffffffffu, rescale)) {  // rare: the running maximum grew by more than 2^8
 #pragma unroll 1
         for (int c0 = 0; c0 < kDvHalf; c0 += 32) {
           uint32_t o[32];
@@ -229,29 +396,32 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_constant__
         }
         tmem_st_wait();
       }
-      float psum = 0.f;
-      uint32_t pk[16];
+      tc_fence_after();
+      const uint32_t f2 = pack2<T>(f, f);
+      uint32_t pk[32];
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const float p0 = fast_exp2(xs[2 * i] - m_ref), p1 = fast_exp2(xs[2 * i + 1] - m_ref);
-        psum += p0 + p1;
-        pk[i] = pack2<T>(p0, p1);
+      for (int h = 0; h < 2; ++h) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          pk[4 * i] = mul2<T>(raw[8 * h + i].x, f2);
+          pk[4 * i + 1] = mul2<T>(raw[8 * h + i].y, f2);
+          pk[4 * i + 2] = mul2<T>(raw[8 * h + i].z, f2);
+          pk[4 * i + 3] = mul2<T>(raw[8 * h + i].w, f2);
+        }
+        tmem_st_32x32(tmem_base + lane_field + kColP + pb * 64 + h * 32, pk);
       }
-      l_run = l_run * alpha + psum;
-      tmem_st_32x16(tmem_base + lane_field + kColP, pk);
+      if (j + 1 < nt) fetch(t0 + j + 1);
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(p_full);
+      if (lane == 0) mbar_arrive(&p_full[pb]);
     }
     // ---- epilogue: O / l, or a partial for the combine
     if (nt > 0) {
-      mbar_wait(pv_done, (nt - 1) & 1, p.status, kFaultMmaBarrier);
+      mbar_wait(o_done, 0, p.status, kFaultMmaBarrier);
       tc_fence_after();
     }
-    const int head = hb * 128 + row;
-    const bool live = head < p.heads;
-    T* outp = reinterpret_cast<T*>(p.out) + (static_cast<size_t>(b) * p.heads + head) * kCkv + dh * kDvHalf;
+    T* outp = reinterpret_cast<T*>(p.out) + hrow * kCkv + dh * kDvHalf;
     auto store32 = [&](const float* v, int c0, float inv) {
       if (!live) return;
 #pragma unroll
@@ -265,18 +435,93 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_constant__
       }
     };
     auto store_lse = [&](float M, float L) {
-      if (live && dh == 0 && p.lse) p.lse[static_cast<size_t>(b) * p.heads + head] = L > 0.f ? M + fast_log2(L) : -INFINITY;
+      if (live && dh == 0 && p.lse) p.lse[hrow] = L > 0.f ? M + fast_log2(L) : -INFINITY;
     };
     if (p.splits == 1) {
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
 #pragma unroll 1
       for (int c0 = 0; c0 < kDvHalf; c0 += 32) {
         uint32_t o[32];
-        tmem_ld_32x32(tmem_base + lane_field + kColO + c0, o);
-        tmem_ld_wait();
+        if (nt > 0) {
+          tmem_ld_32x32(tmem_base + lane_field + kColO + c0, o);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = 0u;
+        }
         store32(reinterpret_cast<const float*>(o), c0, inv);
       }
       store_lse(m_ref, l_run);
+    } else if constexpr (CLUSTER) {
+      // Split-KV combine inside the cluster: every CTA parks its fp32 accumulator, m and l in its own
+      // shared memory (the ring is idle: all MMAs have completed), the cluster meets at a hardware
+      // barrier, and CTA r combines rows [r, r + 1) * 128 / S over all peers through distributed
+      // shared memory, in rank order (bit-stable). No workspace, no atomics, nobody spins.
+      float* stg = reinterpret_cast<float*>(v_smem);
+#pragma unroll 1
+      for (int c0 = 0; c0 < kDvHalf; c0 += 32) {
+        uint32_t o[32];
+        if (nt > 0) {
+          tmem_ld_32x32(tmem_base + lane_field + kColO + c0, o);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = 0u;
+        }
+        float4* dst = reinterpret_cast<float4*>(stg + (static_cast<size_t>(c0 >> 5) * 128 + row) * 32);
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          dst[i] = make_float4(__uint_as_float(o[4 * i]), __uint_as_float(o[4 * i + 1]), __uint_as_float(o[4 * i + 2]),
+                               __uint_as_float(o[4 * i + 3]));
+      }
+      stg[128 * kDvHalf + row] = l_run > 0.f ? m_ref : -INFINITY;
+      stg[128 * kDvHalf + 128 + row] = l_run;
+      cluster_sync();
+      {
+        const int S = p.splits;
+        const int r0 = split * 128 / S, r1 = (split + 1) * 128 / S;
+        const uint32_t stg_addr = smem_u32(stg);
+        for (int item = etid; item < (r1 - r0) * 32; item += 128) {
+          const int rr = r0 + (item >> 5), c8 = item & 31;
+          float cf[8], L = 0.f, M = -INFINITY;
+#pragma unroll
+          for (int s2 = 0; s2 < 8; ++s2)
+            if (s2 < S) {
+              cf[s2] = dsmem_ld_f32(dsmem_addr(stg_addr + (128 * kDvHalf + rr) * 4, s2));
+              M = fmaxf(M, cf[s2]);
+            }
+          const float Mu = M == -INFINITY ? 0.f : M;
+#pragma unroll
+          for (int s2 = 0; s2 < 8; ++s2)
+            if (s2 < S) {
+              cf[s2] = fast_exp2(cf[s2] - Mu);
+              L += cf[s2] * dsmem_ld_f32(dsmem_addr(stg_addr + (128 * kDvHalf + 128 + rr) * 4, s2));
+            }
+          float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          const uint32_t off = ((static_cast<uint32_t>(c8 >> 2) * 128 + rr) * 32 + (c8 & 3) * 8) * 4;
+#pragma unroll
+          for (int s2 = 0; s2 < 8; ++s2)
+            if (s2 < S) {
+              const float4 a0 = dsmem_ld_v4(dsmem_addr(stg_addr + off, s2));
+              const float4 a1 = dsmem_ld_v4(dsmem_addr(stg_addr + off + 16, s2));
+              acc[0] += cf[s2] * a0.x; acc[1] += cf[s2] * a0.y; acc[2] += cf[s2] * a0.z; acc[3] += cf[s2] * a0.w;
+              acc[4] += cf[s2] * a1.x; acc[5] += cf[s2] * a1.y; acc[6] += cf[s2] * a1.z; acc[7] += cf[s2] * a1.w;
+            }
+          const int hd = hb * 128 + rr;
+          if (hd < p.heads) {
+            const float inv = L > 0.f ? 1.f / L : 0.f;
+            const size_t hr = static_cast<size_t>(b) * p.heads + hd;
+            uint4 q4;
+            q4.x = pack2<T>(acc[0] * inv, acc[1] * inv);
+            q4.y = pack2<T>(acc[2] * inv, acc[3] * inv);
+            q4.z = pack2<T>(acc[4] * inv, acc[5] * inv);
+            q4.w = pack2<T>(acc[6] * inv, acc[7] * inv);
+            *reinterpret_cast<uint4*>(reinterpret_cast<T*>(p.out) + hr * kCkv + dh * kDvHalf + c8 * 8) = q4;
+            if (c8 == 0 && dh == 0 && p.lse) p.lse[hr] = L > 0.f ? M + fast_log2(L) : -INFINITY;
+          }
+        }
+      }
+      cluster_sync();  // nobody leaves while a peer may still read its shared memory
     } else {
       const int item = (b * p.head_blocks + hb) * 2 + dh;
       float* slot = p.partials + (static_cast<size_t>(item) * p.splits + split) * kSlotFloats;
@@ -284,15 +529,20 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_constant__
 #pragma unroll 1
       for (int c0 = 0; c0 < kDvHalf; c0 += 32) {
         uint32_t o[32];
-        tmem_ld_32x32(tmem_base + lane_field + kColO + c0, o);
-        tmem_ld_wait();
+        if (nt > 0) {
+          tmem_ld_32x32(tmem_base + lane_field + kColO + c0, o);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = 0u;
+        }
         float4* dst = reinterpret_cast<float4*>(slot + (static_cast<size_t>(c0 >> 5) * 128 + row) * 32);
 #pragma unroll
         for (int i = 0; i < 8; ++i)
           dst[i] = make_float4(__uint_as_float(o[4 * i]), __uint_as_float(o[4 * i + 1]), __uint_as_float(o[4 * i + 2]),
                                __uint_as_float(o[4 * i + 3]));
       }
-      slot[128 * kDvHalf + row] = m_ref;
+      slot[128 * kDvHalf + row] = l_run > 0.f ? m_ref : -INFINITY;
       slot[128 * kDvHalf + 128 + row] = l_run;
       __threadfence();
       named_bar_sync(2, 128);
@@ -343,7 +593,7 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_constant__
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, kTmemCols);
+    tmem_dealloc(tmem_base, 512);
   }
 }
 
@@ -354,58 +604,118 @@ bool mla_tc_supported(const cb200_mla_decode_args* a) {
   return a->kv_indptr == nullptr && a->kv_len >= 1 && a->ckv_dim == mlatc::kCkv && a->kpe_dim == mlatc::kKpe;
 }
 
-// Splits per item: fill the SMs once, never more splits than KV tiles.
-static void mla_tc_shape(const cb200_mla_decode_args* a, int sms, int* head_blocks, int* splits, int* tiles_per_split) {
-  *head_blocks = ceil_div(a->num_heads, 128);
-  const long long items = static_cast<long long>(a->batch) * *head_blocks * 2;
-  const int tiles = ceil_div(a->kv_len, mlatc::kBN);
-  int s = static_cast<int>(sms / items);
-  if (s < 1) s = 1;
-  if (s > tiles) s = tiles;
-  if (a->max_ctas > 0 && s * items > a->max_ctas) s = static_cast<int>(a->max_ctas / items > 0 ? a->max_ctas / items : 1);
-  *tiles_per_split = ceil_div(tiles, s);
-  *splits = ceil_div(tiles, *tiles_per_split);
+namespace {
+
+struct TcShape {
+  int head_blocks, blocks, kv_pad;
+  int ranges, blocks_per_range;  // scores kernel: token ranges per (request, head block)
+  int splits, blocks_per_split;  // values kernel: token ranges per (request, head block, column half)
+  size_t p_bytes, stats_bytes, partial_bytes;
+};
+
+// Both kernels fill the SMs once: as many token ranges per item as fit, never more than there are blocks.
+TcShape mla_tc_shape(const cb200_mla_decode_args* a, int sms) {
+  TcShape s{};
+  s.head_blocks = ceil_div(a->num_heads, 128);
+  s.blocks = ceil_div(a->kv_len, mlatc::kBlk);
+  s.kv_pad = s.blocks * mlatc::kBlk;
+  int ctas = sms;
+  if (a->max_ctas > 0 && a->max_ctas < ctas) ctas = a->max_ctas;
+  const long long items1 = static_cast<long long>(a->batch) * s.head_blocks;
+  int r = static_cast<int>(ctas / items1);
+  if (r < 1) r = 1;
+  const int tiles = ceil_div(s.blocks, 2);  // a range is made of whole MMA tiles (two blocks)
+  if (r > tiles) r = tiles;
+  s.blocks_per_range = 2 * ceil_div(tiles, r);
+  s.ranges = ceil_div(s.blocks, s.blocks_per_range);
+  const long long items2 = items1 * 2;
+  int sp = static_cast<int>(ctas / items2);
+  if (sp < 1) sp = 1;
+  if (sp > s.blocks) sp = s.blocks;
+  s.blocks_per_split = ceil_div(s.blocks, sp);
+  s.splits = ceil_div(s.blocks, s.blocks_per_split);
+  const size_t rows = static_cast<size_t>(a->batch) * a->num_heads;
+  s.p_bytes = align_up(rows * s.kv_pad * 2, 256);
+  s.stats_bytes = align_up(rows * s.blocks * sizeof(float2), 256);
+  s.partial_bytes = s.splits <= 8 ? 0 :  // up to eight splits combine inside a cluster
+                    static_cast<size_t>(items2) * s.splits * mlatc::kSlotFloats * 4;
+  return s;
 }
 
-size_t mla_tc_partial_bytes(const cb200_mla_decode_args* a, int sms) {
-  int hb, s, tps;
-  mla_tc_shape(a, sms, &hb, &s, &tps);
-  if (s == 1) return 0;
-  return static_cast<size_t>(a->batch) * hb * 2 * s * mlatc::kSlotFloats * 4;
-}
-
-template <typename Kern>
-static int launch_mla_tc_kernel(Kern kern, long long grid, const CUtensorMap& tm_qn, const CUtensorMap& tm_qp,
-                                const CUtensorMap& tm_ckv, const CUtensorMap& tm_kpe, const mlatc::Params& p,
-                                cudaStream_t stream) {
+template <typename T>
+int launch_mla_tc_kernels(long long grid1, long long grid2, const CUtensorMap& tm_qn, const CUtensorMap& tm_qp,
+                          const CUtensorMap& tm_ckv_k, const CUtensorMap& tm_kpe, const CUtensorMap& tm_ckv_v,
+                          const mlatc::Params& p, cudaStream_t stream) {
+  auto k1 = mlatc::mla_scores_kernel<T>;
+  const bool cluster = p.splits >= 2 && p.splits <= 8;
+  auto k2 = cluster ? mlatc::mla_values_kernel<T, true> : mlatc::mla_values_kernel<T, false>;
   // set on every launch: the attribute is per function and per device, and the call is cheap
-  CB200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, mlatc::kSmemBytes));
-  kern<<<static_cast<unsigned>(grid), mlatc::kThreads, mlatc::kSmemBytes, stream>>>(tm_qn, tm_qp, tm_ckv, tm_kpe, p);
+  CB200_CUDA_TRY(cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, mlatc::kScoreSmem));
+  CB200_CUDA_TRY(cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, mlatc::kValueSmem));
+  k1<<<static_cast<unsigned>(grid1), mlatc::kScoreThreads, mlatc::kScoreSmem, stream>>>(tm_qn, tm_qp, tm_ckv_k, tm_kpe, p);
+  CB200_CUDA_TRY(cudaGetLastError());
+  if (cluster) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(grid2), 1, 1);
+    cfg.blockDim = dim3(mlatc::kValueThreads, 1, 1);
+    cfg.dynamicSmemBytes = mlatc::kValueSmem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = p.splits;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    CB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, k2, tm_ckv_v, p));
+  } else {
+    k2<<<static_cast<unsigned>(grid2), mlatc::kValueThreads, mlatc::kValueSmem, stream>>>(tm_ckv_v, p);
+  }
   CB200_CUDA_TRY(cudaGetLastError());
   return CB200_OK;
+}
+
+}  // namespace
+
+// Workspace of the two-kernel path behind the caller's header and counters: P | block statistics | partials.
+size_t mla_tc_partial_bytes(const cb200_mla_decode_args* a, int sms) {
+  const TcShape s = mla_tc_shape(a, sms);
+  return s.p_bytes + s.stats_bytes + s.partial_bytes;
 }
 
 int launch_mla_tc(const cb200_mla_decode_args* a, int* status, int* counters, float* partials, cudaStream_t stream) {
   using namespace mlatc;
   const int sms = sm_count();
   if (sms <= 0) return CB200_ERR_CUDA;
+  const TcShape s = mla_tc_shape(a, sms);
   Params p{};
   p.out = a->out;
   p.lse = a->lse;
   p.status = status;
   p.counters = counters;
-  p.partials = partials;
+  uint8_t* ws = reinterpret_cast<uint8_t*>(partials);
+  p.pbuf = ws;
+  p.stats = reinterpret_cast<float2*>(ws + s.p_bytes);
+  p.partials = reinterpret_cast<float*>(ws + s.p_bytes + s.stats_bytes);
   p.batch = a->batch;
   p.heads = a->num_heads;
+  p.head_blocks = s.head_blocks;
   p.kv_len = a->kv_len;
+  p.kv_pad = s.kv_pad;
+  p.blocks = s.blocks;
+  p.ranges = s.ranges;
+  p.blocks_per_range = s.blocks_per_range;
+  p.splits = s.splits;
+  p.blocks_per_split = s.blocks_per_split;
   p.scale_log2 = a->sm_scale * kLog2e;
-  mla_tc_shape(a, sms, &p.head_blocks, &p.splits, &p.tiles_per_split);
-  const long long grid = static_cast<long long>(a->batch) * p.head_blocks * 2 * p.splits;
-  if (grid >= (1LL << 31)) return CB200_ERR_UNSUPPORTED;
+  const long long grid1 = static_cast<long long>(a->batch) * s.head_blocks * s.ranges;
+  const long long grid2 = static_cast<long long>(a->batch) * s.head_blocks * 2 * s.splits;
+  if (grid1 >= (1LL << 31) || grid2 >= (1LL << 31)) return CB200_ERR_UNSUPPORTED;
   const CUtensorMapDataType dt = a->dtype == CB200_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
-  CUtensorMap tm_qn, tm_qp, tm_ckv, tm_kpe;
+  CUtensorMap tm_qn, tm_qp, tm_ckv_k, tm_kpe, tm_ckv_v;
   {
-    uint32_t qbox[3] = {64u, 128u, 1u}, kbox[3] = {64u, static_cast<uint32_t>(kBN), 1u};
+    uint32_t qbox[3] = {64u, 128u, 1u}, kbox[3] = {64u, static_cast<uint32_t>(kSTile), 1u},
+             vbox[3] = {64u, static_cast<uint32_t>(kBlk), 1u};
     uint64_t dq[3] = {kCkv, static_cast<uint64_t>(a->num_heads), static_cast<uint64_t>(a->batch)};
     uint64_t sq[2] = {kCkv * 2, static_cast<uint64_t>(a->num_heads) * kCkv * 2};
     uint64_t dp[3] = {kKpe, static_cast<uint64_t>(a->num_heads), static_cast<uint64_t>(a->batch)};
@@ -417,13 +727,14 @@ int launch_mla_tc(const cb200_mla_decode_args* a, int* status, int* counters, fl
     const CUtensorMapSwizzle sw = CU_TENSOR_MAP_SWIZZLE_128B;
     if (!encode_tensor_map(&tm_qn, dt, 3, const_cast<void*>(a->q_nope), dq, sq, qbox, sw) ||
         !encode_tensor_map(&tm_qp, dt, 3, const_cast<void*>(a->q_pe), dp, sp, qbox, sw) ||
-        !encode_tensor_map(&tm_ckv, dt, 3, const_cast<void*>(a->ckv_cache), dc, sc, kbox, sw) ||
-        !encode_tensor_map(&tm_kpe, dt, 3, const_cast<void*>(a->kpe_cache), dk, sk, kbox, sw))
+        !encode_tensor_map(&tm_ckv_k, dt, 3, const_cast<void*>(a->ckv_cache), dc, sc, kbox, sw) ||
+        !encode_tensor_map(&tm_kpe, dt, 3, const_cast<void*>(a->kpe_cache), dk, sk, kbox, sw) ||
+        !encode_tensor_map(&tm_ckv_v, dt, 3, const_cast<void*>(a->ckv_cache), dc, sc, vbox, sw))
       return CB200_ERR_CUDA;
   }
   return a->dtype == CB200_F16
-             ? launch_mla_tc_kernel(mla_tc_kernel<__half>, grid, tm_qn, tm_qp, tm_ckv, tm_kpe, p, stream)
-             : launch_mla_tc_kernel(mla_tc_kernel<__nv_bfloat16>, grid, tm_qn, tm_qp, tm_ckv, tm_kpe, p, stream);
+             ? launch_mla_tc_kernels<__half>(grid1, grid2, tm_qn, tm_qp, tm_ckv_k, tm_kpe, tm_ckv_v, p, stream)
+             : launch_mla_tc_kernels<__nv_bfloat16>(grid1, grid2, tm_qn, tm_qp, tm_ckv_k, tm_kpe, tm_ckv_v, p, stream);
 }
 
 }  // namespace cb200

@@ -55,7 +55,7 @@ def test_paged_mla_matches_reference_golden(name):
 
 
 @pytest.mark.parametrize("impl", ["tcgen05", "mma_sync"])
-@pytest.mark.parametrize("b,h,skv", [(1, 16, 64), (2, 128, 1000), (3, 32, 65), (1, 48, 4097), (1, 200, 33)])
+@pytest.mark.parametrize("b,h,skv", [(1, 16, 64), (2, 128, 1000), (3, 32, 65), (1, 48, 4097), (1, 200, 33), (5, 128, 700), (9, 72, 600)])
 @pytest.mark.parametrize("dt", ["bf16", "f16"])
 @pytest.mark.parametrize("max_ctas", [0, 1, 5])
 def test_static_mla_vs_oracle(b, h, skv, dt, max_ctas, impl):

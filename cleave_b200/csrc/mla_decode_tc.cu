@@ -38,7 +38,6 @@ constexpr int kCkv = 512, kKpe = 64, kQk = 576;
 constexpr int kChunks = kQk / 64;        // 9 chunks of 64 columns (128 bytes)
 constexpr int kBlk = 128;                // tokens per block of P
 constexpr float kLog2e = 1.4426950408889634f;
-constexpr float kRescaleThreshold = 8.f;  // log2 units
 
 // ---- scores kernel
 constexpr int kQChunkBytes = 128 * 128;             // 128 heads x 128 bytes
@@ -54,10 +53,16 @@ constexpr int kDvHalf = 256;
 constexpr int kVChunkBytes = kBlk * 128;            // 64 columns x 128 tokens
 constexpr int kVStageBytes = (kDvHalf / 64) * kVChunkBytes;  // 65 536
 constexpr int kVStages = 3;
-constexpr int kValueSmem = kVStages * kVStageBytes + 1024 + 1024;
-constexpr int kValueThreads = 192;
-constexpr int kSlotFloats = 128 * kDvHalf + 256;    // O partial, m, l
+constexpr int kValueSmem = kVStages * kVStageBytes + 2048 /*barriers, row sums*/ + 1024 /*alignment*/;
+constexpr int kValueThreads = 320;  // producer, MMA, two groups of four P-scaling warps
 constexpr uint32_t kColO = 0, kColP = 256;          // P: two buffers of 64 columns
+
+__device__ long long g_dbg[1024 * 16];
+__device__ __forceinline__ void stamp(int slot) {
+  long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  if (blockIdx.x < 1024) g_dbg[blockIdx.x * 16 + slot] = t;
+}
 
 struct Params {
   void* out;
@@ -65,8 +70,8 @@ struct Params {
   int* status;
   int* counters;
   float* partials;
-  void* pbuf;      // (batch * heads, kv_pad) 16-bit
-  float2* stats;   // (batch * heads, blocks): (m, l) per block
+  void* pbuf;      // (batch, head blocks, token blocks) tiles of 128 rows x 128 tokens, 16-bit
+  float2* stats;   // (batch, head blocks, token blocks, 128 rows): (m, l) per row and block
   int batch, heads, head_blocks, kv_len, kv_pad, blocks;
   int ranges, blocks_per_range;   // scores kernel
   int splits, blocks_per_split;   // values kernel
@@ -120,6 +125,7 @@ mla_scores_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_holder);
+  pdl_launch_dependents();  // the values kernel may set up and prefetch V while this grid drains
 
   if (warp == 0) {
     // ================================================================ TMA producer
@@ -151,6 +157,7 @@ mla_scores_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_consta
     constexpr uint32_t idesc = umma_idesc(std::is_same<T, __nv_bfloat16>::value, /*b_mn_major=*/false, 128, kSTile);
     const uint32_t k_addr = smem_u32(k_smem);
     int st = 0, ph = 0;
+    if (lane == 0) stamp(0);
     for (int t = 0; t < n_tiles; ++t) {
       const int sb = t & 1;
       mbar_wait(&s_empty[sb], ((t >> 1) & 1) ^ 1, p.status, kFaultTmemBarrier);
@@ -159,6 +166,7 @@ mla_scores_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_consta
       for (int c = 0; c < kChunks; ++c) {
         mbar_wait(&k_full[st], ph, p.status, kFaultFullBarrier);
         tc_fence_after();
+        if (lane == 0 && t == 0 && c == 0) stamp(1);
         if (lane == 0) {
           const uint32_t q_addr = k_addr + st * kKStageBytes;
 #pragma unroll
@@ -173,6 +181,7 @@ mla_scores_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_consta
         if (++st == kKStages) { st = 0; ph ^= 1; }
       }
       if (lane == 0) umma_commit(&s_full[sb]);
+      if (lane == 0) stamp(2 + (t & 1));
       __syncwarp();
     }
   } else {
@@ -180,59 +189,63 @@ mla_scores_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_consta
     const int quarter = warp & 3;          // the TMEM lanes this warp may read
     const int half = (warp - 2) >> 2;      // which block of the MMA tile
     const int row = quarter * 32 + lane;
-    const int head = hb * 128 + row;
-    const bool live = head < p.heads;
     const uint32_t lane_field = static_cast<uint32_t>(quarter * 32) << 16;
-    const size_t prow = (static_cast<size_t>(b) * p.heads + head) * p.kv_pad;
     for (int t = 0; t < n_tiles; ++t) {
       const int sb = t & 1;
       const int u = u0 + 2 * t + half;
       mbar_wait(&s_full[sb], (t >> 1) & 1, p.status, kFaultMmaBarrier);
       tc_fence_after();
+      if (tid == 64) stamp(4 + 2 * (t & 1));
+      uint32_t r[4][32];
       if (u < u1) {
         const uint32_t t_s = tmem_base + lane_field + sb * kSTile + half * kBlk;
-        const int tok0 = u * kBlk;
-        float mx = -INFINITY;
-#pragma unroll 1
-        for (int c0 = 0; c0 < kBlk; c0 += 32) {
-          uint32_t r[32];
-          tmem_ld_32x32(t_s + c0, r);
-          tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (tok0 + c0 + i < p.kv_len) mx = fmaxf(mx, __uint_as_float(r[i]) * p.scale_log2);
-        }
-        const float m = mx == -INFINITY ? 0.f : mx;
-        float l = 0.f;
-        T* pdst = reinterpret_cast<T*>(p.pbuf) + prow + tok0;
-#pragma unroll 1
-        for (int c0 = 0; c0 < kBlk; c0 += 32) {
-          uint32_t r[32];
-          tmem_ld_32x32(t_s + c0, r);
-          tmem_ld_wait();
-          float e[32];
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            e[i] = tok0 + c0 + i < p.kv_len ? fast_exp2(fmaf(__uint_as_float(r[i]), p.scale_log2, -m)) : 0.f;
-            l += e[i];
-          }
-          if (live) {
-#pragma unroll
-            for (int i = 0; i < 32; i += 8) {
-              uint4 q4;
-              q4.x = pack2<T>(e[i], e[i + 1]);
-              q4.y = pack2<T>(e[i + 2], e[i + 3]);
-              q4.z = pack2<T>(e[i + 4], e[i + 5]);
-              q4.w = pack2<T>(e[i + 6], e[i + 7]);
-              *reinterpret_cast<uint4*>(pdst + c0 + i) = q4;
-            }
-          }
-        }
-        if (live) p.stats[(static_cast<size_t>(b) * p.heads + head) * p.blocks + u] = make_float2(m, l);
+        for (int q = 0; q < 4; ++q) tmem_ld_32x32(t_s + q * 32, r[q]);
+        tmem_ld_wait();
       }
+      // S is in registers: the MMAs may reuse the buffer while P is computed and stored
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_empty[sb]);
+      if (u < u1) {
+        const int tok0 = u * kBlk;
+        float mx = -INFINITY;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float v = tok0 + q * 32 + i < p.kv_len ? __uint_as_float(r[q][i]) * p.scale_log2 : -INFINITY;
+            r[q][i] = __float_as_uint(v);
+            mx = fmaxf(mx, v);
+          }
+        }
+        const float m = mx == -INFINITY ? 0.f : mx;
+        float l = 0.f;
+        // P tile of (head block, token block): 16-byte piece k of row r at piece index k * 128 + r, so
+        // that a warp's store (and the values kernel's load) covers 512 contiguous bytes
+        const size_t tile = (static_cast<size_t>(b) * p.head_blocks + hb) * p.blocks + u;
+        uint4* ptile = reinterpret_cast<uint4*>(p.pbuf) + tile * (kBlk * 128 / 8);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            float e[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              e[k] = fast_exp2(__uint_as_float(r[q][i + k]) - m);  // exp2(-inf) = 0 for masked tokens
+              l += e[k];
+            }
+            uint4 q4;
+            q4.x = pack2<T>(e[0], e[1]);
+            q4.y = pack2<T>(e[2], e[3]);
+            q4.z = pack2<T>(e[4], e[5]);
+            q4.w = pack2<T>(e[6], e[7]);
+            ptile[(q * 4 + (i >> 3)) * 128 + row] = q4;
+          }
+        }
+        p.stats[tile * 128 + row] = make_float2(m, l);
+      }
+      if (tid == 64) stamp(5 + 2 * (t & 1));
     }
   }
 
@@ -244,7 +257,10 @@ mla_scores_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_consta
   }
 }
 
-template <typename T, bool CLUSTER>
+// ---- values kernel: warp roles 0 = TMA producer, 1 = MMA issuer and TMEM owner, 2..5 and 6..9 = two
+// groups of P-scaling warps (thread = head row = TMEM lane); group g owns P buffer g and the token
+// blocks j = g (mod 2), so two blocks' loads are in flight while a third is multiplied.
+template <typename T>
 __global__ void __launch_bounds__(kValueThreads, 1)
 mla_values_kernel(const __grid_constant__ CUtensorMap tm_ckv, const Params p) {
   extern __shared__ uint8_t smem_raw[];
@@ -253,15 +269,16 @@ mla_values_kernel(const __grid_constant__ CUtensorMap tm_ckv, const Params p) {
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kVStages * kVStageBytes);
   uint64_t* v_full = bars;                 // [3] TMA landed
   uint64_t* v_empty = bars + kVStages;     // [3] the MMAs have read the stage
-  uint64_t* p_full = bars + 2 * kVStages;  // [2] scaled P stored to TMEM (and O rescaled if needed)
+  uint64_t* p_full = bars + 2 * kVStages;  // [2] scaled P stored to TMEM
   uint64_t* p_empty = p_full + 2;          // [2] the MMAs that read the P buffer have completed
   uint64_t* o_done = p_empty + 2;
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(o_done + 1);
-  int* flag = reinterpret_cast<int*>(tmem_holder + 1);
+  float* l_part = reinterpret_cast<float*>(bars + 16);  // [2][128] row sums of the two groups
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int S = p.splits;  // the S CTAs of an item are one cluster (S = 1: no cluster)
   int x = blockIdx.x;
-  const int split = x % p.splits; x /= p.splits;  // cluster mode: the splits of an item are one cluster
+  const int split = x % S; x /= S;
   const int dh = x & 1; x >>= 1;
   const int hb = x % p.head_blocks;
   const int b = x / p.head_blocks;
@@ -306,7 +323,7 @@ mla_values_kernel(const __grid_constant__ CUtensorMap tm_ckv, const Params p) {
       __syncwarp();
       if (++st == kVStages) { st = 0; ph ^= 1; }
     }
-    if constexpr (CLUSTER) {  // the two meetings of the combine
+    if (S > 1) {  // the two meetings of the combine
       cluster_sync();
       cluster_sync();
     }
@@ -315,10 +332,14 @@ mla_values_kernel(const __grid_constant__ CUtensorMap tm_ckv, const Params p) {
     constexpr uint32_t idesc = umma_idesc(std::is_same<T, __nv_bfloat16>::value, /*b_mn_major=*/true, 128, kDvHalf);
     const uint32_t v_addr0 = smem_u32(v_smem);
     int st = 0, ph = 0;
+    if (lane == 0) stamp(8);
     for (int j = 0; j < nt; ++j) {
       const int pb = j & 1;
       mbar_wait(&v_full[st], ph, p.status, kFaultFullBarrier);
+      if (lane == 0 && j == 0) stamp(9);
       mbar_wait(&p_full[pb], (j >> 1) & 1, p.status, kFaultTmemBarrier);
+      if (lane == 0 && j == 0) stamp(10);
+      if (lane == 0 && j == nt - 1) stamp(11);
       tc_fence_after();
       if (lane == 0) {
         const uint32_t v_addr = v_addr0 + st * kVStageBytes;
@@ -335,67 +356,41 @@ mla_values_kernel(const __grid_constant__ CUtensorMap tm_ckv, const Params p) {
       __syncwarp();
       if (++st == kVStages) { st = 0; ph ^= 1; }
     }
-    if constexpr (CLUSTER) {
+    if (S > 1) {
       cluster_sync();
       cluster_sync();
     }
   } else {
     // ================================================================ P scaling / epilogue
     const int quarter = warp & 3;
+    const int group = (warp - 2) >> 2;
     const int row = quarter * 32 + lane;  // head row inside the block = TMEM lane
-    const int etid = tid - 64;
+    const int etid = tid - 64;            // 0..255
     const int head = hb * 128 + row;
     const bool live = head < p.heads;
     const uint32_t lane_field = static_cast<uint32_t>(quarter * 32) << 16;
-    const size_t hrow = static_cast<size_t>(b) * p.heads + head;
-    const T* prow = reinterpret_cast<const T*>(p.pbuf) + hrow * p.kv_pad;
-    float m_ref = 0.f, l_run = 0.f;
-    // P rows and statistics of the next block are fetched while the current one is processed
+    const size_t tile0 = (static_cast<size_t>(b) * p.head_blocks + hb) * p.blocks;
+    const uint4* pbase = reinterpret_cast<const uint4*>(p.pbuf);
+    pdl_wait();  // P and the statistics come from the scores kernel
     uint4 raw[16];
-    float2 st_next = make_float2(0.f, 0.f);
     auto fetch = [&](int u) {
-      if (live) {
-        st_next = __ldcg(p.stats + hrow * p.blocks + u);
-        const uint4* src = reinterpret_cast<const uint4*>(prow + static_cast<size_t>(u) * kBlk);
+      const uint4* src = pbase + (tile0 + u) * (kBlk * 128 / 8) + row;
 #pragma unroll
-        for (int i = 0; i < 16; ++i) raw[i] = __ldcg(src + i);
-      } else {
-#pragma unroll
-        for (int i = 0; i < 16; ++i) raw[i] = make_uint4(0u, 0u, 0u, 0u);
-      }
+      for (int i = 0; i < 16; ++i) raw[i] = __ldcg(src + i * 128);
     };
-    if (nt > 0) fetch(t0);
-    for (int j = 0; j < nt; ++j) {
-      const int pb = j & 1;
-      const float2 st = st_next;
-      float alpha = 1.f;
-      bool rescale = false;
-      if (j == 0) {
-        m_ref = st.x;
-      } else if (st.x > m_ref + kRescaleThreshold) {
-        alpha = fast_exp2(m_ref - st.x);
-        m_ref = st.x;
-        rescale = true;
-      }
+    if (group < nt) fetch(t0 + group);
+    // The reference maximum is the largest block maximum of the whole range (the statistics of every
+    // block are already in memory), so the factors are at most 1 and O never needs rescaling.
+    float m_ref = -INFINITY;
+    for (int j = 0; j < nt; ++j) m_ref = fmaxf(m_ref, p.stats[(tile0 + t0 + j) * 128 + row].x);
+    if (m_ref == -INFINITY) m_ref = 0.f;
+    float l_run = 0.f;
+    for (int j = group; j < nt; j += 2) {
+      const float2 st = p.stats[(tile0 + t0 + j) * 128 + row];  // second touch: L1
       const float f = fast_exp2(st.x - m_ref);
-      l_run = l_run * alpha + st.y * f;
-      // the P buffer is free once the MMAs of tile j - 2 have completed
-      mbar_wait(&p_empty[pb], ((j >> 1) & 1) ^ 1, p.status, kFaultMmaBarrier);
-      if (__any_sync(0xffffffffu, rescale)) {  // rare: the reference maximum grew by more than 2^8
-        // O may only be touched when no MMA is in flight: tile j - 1 is the last one issued
-        mbar_wait(&p_empty[pb ^ 1], ((j - 1) >> 1) & 1, p.status, kFaultMmaBarrier);
-        tc_fence_after();
-#pragma unroll 1
-        for (int c0 = 0; c0 < kDvHalf; c0 += 32) {
-          uint32_t o[32];
-          tmem_ld_32x32(tmem_base + lane_field + kColO + c0, o);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-          tmem_st_32x32(tmem_base + lane_field + kColO + c0, o);
-        }
-        tmem_st_wait();
-      }
+      l_run += st.y * f;
+      // the group's P buffer is free once the MMAs of its previous block have completed
+      mbar_wait(&p_empty[group], ((j >> 1) & 1) ^ 1, p.status, kFaultMmaBarrier);
       tc_fence_after();
       const uint32_t f2 = pack2<T>(f, f);
       uint32_t pk[32];
@@ -408,39 +403,30 @@ mla_values_kernel(const __grid_constant__ CUtensorMap tm_ckv, const Params p) {
           pk[4 * i + 2] = mul2<T>(raw[8 * h + i].z, f2);
           pk[4 * i + 3] = mul2<T>(raw[8 * h + i].w, f2);
         }
-        tmem_st_32x32(tmem_base + lane_field + kColP + pb * 64 + h * 32, pk);
+        tmem_st_32x32(tmem_base + lane_field + kColP + group * 64 + h * 32, pk);
       }
-      if (j + 1 < nt) fetch(t0 + j + 1);
+      if (j + 2 < nt) fetch(t0 + j + 2);
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&p_full[pb]);
+      if (lane == 0) mbar_arrive(&p_full[group]);
     }
-    // ---- epilogue: O / l, or a partial for the combine
+    // ---- epilogue: O / l, or the cluster combine. Both groups take half of the columns.
+    l_part[group * 128 + row] = l_run;
+    named_bar_sync(2, 256);
+    const float L = l_part[row] + l_part[128 + row];  // the same sum in both groups
     if (nt > 0) {
       mbar_wait(o_done, 0, p.status, kFaultMmaBarrier);
       tc_fence_after();
     }
-    T* outp = reinterpret_cast<T*>(p.out) + hrow * kCkv + dh * kDvHalf;
-    auto store32 = [&](const float* v, int c0, float inv) {
-      if (!live) return;
-#pragma unroll
-      for (int i = 0; i < 32; i += 8) {
-        uint4 q4;
-        q4.x = pack2<T>(v[i] * inv, v[i + 1] * inv);
-        q4.y = pack2<T>(v[i + 2] * inv, v[i + 3] * inv);
-        q4.z = pack2<T>(v[i + 4] * inv, v[i + 5] * inv);
-        q4.w = pack2<T>(v[i + 6] * inv, v[i + 7] * inv);
-        *reinterpret_cast<uint4*>(outp + c0 + i) = q4;
-      }
-    };
-    auto store_lse = [&](float M, float L) {
-      if (live && dh == 0 && p.lse) p.lse[hrow] = L > 0.f ? M + fast_log2(L) : -INFINITY;
-    };
-    if (p.splits == 1) {
-      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+    if (tid == 64) stamp(12);
+    const size_t hrow = static_cast<size_t>(b) * p.heads + head;
+    T* outg = reinterpret_cast<T*>(p.out);
+    const int cbeg = group * (kDvHalf / 2), cend = cbeg + kDvHalf / 2;
+    if (S == 1) {
+      const float inv = L > 0.f ? 1.f / L : 0.f;
 #pragma unroll 1
-      for (int c0 = 0; c0 < kDvHalf; c0 += 32) {
+      for (int c0 = cbeg; c0 < cend; c0 += 32) {
         uint32_t o[32];
         if (nt > 0) {
           tmem_ld_32x32(tmem_base + lane_field + kColO + c0, o);
@@ -449,17 +435,32 @@ mla_values_kernel(const __grid_constant__ CUtensorMap tm_ckv, const Params p) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) o[i] = 0u;
         }
-        store32(reinterpret_cast<const float*>(o), c0, inv);
+        if (live) {
+          const float* v = reinterpret_cast<const float*>(o);
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint4 q4;
+            q4.x = pack2<T>(v[i] * inv, v[i + 1] * inv);
+            q4.y = pack2<T>(v[i + 2] * inv, v[i + 3] * inv);
+            q4.z = pack2<T>(v[i + 4] * inv, v[i + 5] * inv);
+            q4.w = pack2<T>(v[i + 6] * inv, v[i + 7] * inv);
+            *reinterpret_cast<uint4*>(outg + hrow * kCkv + dh * kDvHalf + c0 + i) = q4;
+          }
+        }
       }
-      store_lse(m_ref, l_run);
-    } else if constexpr (CLUSTER) {
+      if (live && group == 0 && dh == 0 && p.lse) p.lse[hrow] = L > 0.f ? m_ref + fast_log2(L) : -INFINITY;
+    } else {
       // Split-KV combine inside the cluster: every CTA parks its fp32 accumulator, m and l in its own
       // shared memory (the ring is idle: all MMAs have completed), the cluster meets at a hardware
       // barrier, and CTA r combines rows [r, r + 1) * 128 / S over all peers through distributed
       // shared memory, in rank order (bit-stable). No workspace, no atomics, nobody spins.
+      // Staging layout: [column group of 32][row][8 pieces of 16 bytes], piece i of row r stored at
+      // i ^ (r & 7) so that a warp's stores spread over all banks.
       float* stg = reinterpret_cast<float*>(v_smem);
+      float* ml = stg + 128 * kDvHalf;        // [128] m, [128] l
+      float* cft = ml + 256;                  // [64 rows][8] combine factors (already divided by L)
 #pragma unroll 1
-      for (int c0 = 0; c0 < kDvHalf; c0 += 32) {
+      for (int c0 = cbeg; c0 < cend; c0 += 32) {
         uint32_t o[32];
         if (nt > 0) {
           tmem_ld_32x32(tmem_base + lane_field + kColO + c0, o);
@@ -471,121 +472,87 @@ mla_values_kernel(const __grid_constant__ CUtensorMap tm_ckv, const Params p) {
         float4* dst = reinterpret_cast<float4*>(stg + (static_cast<size_t>(c0 >> 5) * 128 + row) * 32);
 #pragma unroll
         for (int i = 0; i < 8; ++i)
-          dst[i] = make_float4(__uint_as_float(o[4 * i]), __uint_as_float(o[4 * i + 1]), __uint_as_float(o[4 * i + 2]),
-                               __uint_as_float(o[4 * i + 3]));
+          dst[i ^ (row & 7)] = make_float4(__uint_as_float(o[4 * i]), __uint_as_float(o[4 * i + 1]),
+                                           __uint_as_float(o[4 * i + 2]), __uint_as_float(o[4 * i + 3]));
       }
-      stg[128 * kDvHalf + row] = l_run > 0.f ? m_ref : -INFINITY;
-      stg[128 * kDvHalf + 128 + row] = l_run;
+      if (group == 0) {
+        ml[row] = L > 0.f ? m_ref : -INFINITY;
+        ml[128 + row] = L;
+      }
       cluster_sync();
-      {
-        const int S = p.splits;
-        const int r0 = split * 128 / S, r1 = (split + 1) * 128 / S;
-        const uint32_t stg_addr = smem_u32(stg);
-        for (int item = etid; item < (r1 - r0) * 32; item += 128) {
-          const int rr = r0 + (item >> 5), c8 = item & 31;
-          float cf[8], L = 0.f, M = -INFINITY;
+      if (tid == 64) stamp(13);
+      const int r0 = split * 128 / S, r1 = (split + 1) * 128 / S, nrows = r1 - r0;  // at most 64
+      const uint32_t stg_addr = smem_u32(stg), ml_addr = smem_u32(ml);
+      if (etid < nrows) {  // factors of one row: 2 S remote loads in one round trip
+        const int rr = r0 + etid;
+        float ms[8], ls[8];
 #pragma unroll
-          for (int s2 = 0; s2 < 8; ++s2)
-            if (s2 < S) {
-              cf[s2] = dsmem_ld_f32(dsmem_addr(stg_addr + (128 * kDvHalf + rr) * 4, s2));
-              M = fmaxf(M, cf[s2]);
-            }
-          const float Mu = M == -INFINITY ? 0.f : M;
-#pragma unroll
-          for (int s2 = 0; s2 < 8; ++s2)
-            if (s2 < S) {
-              cf[s2] = fast_exp2(cf[s2] - Mu);
-              L += cf[s2] * dsmem_ld_f32(dsmem_addr(stg_addr + (128 * kDvHalf + 128 + rr) * 4, s2));
-            }
-          float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-          const uint32_t off = ((static_cast<uint32_t>(c8 >> 2) * 128 + rr) * 32 + (c8 & 3) * 8) * 4;
-#pragma unroll
-          for (int s2 = 0; s2 < 8; ++s2)
-            if (s2 < S) {
-              const float4 a0 = dsmem_ld_v4(dsmem_addr(stg_addr + off, s2));
-              const float4 a1 = dsmem_ld_v4(dsmem_addr(stg_addr + off + 16, s2));
-              acc[0] += cf[s2] * a0.x; acc[1] += cf[s2] * a0.y; acc[2] += cf[s2] * a0.z; acc[3] += cf[s2] * a0.w;
-              acc[4] += cf[s2] * a1.x; acc[5] += cf[s2] * a1.y; acc[6] += cf[s2] * a1.z; acc[7] += cf[s2] * a1.w;
-            }
-          const int hd = hb * 128 + rr;
-          if (hd < p.heads) {
-            const float inv = L > 0.f ? 1.f / L : 0.f;
-            const size_t hr = static_cast<size_t>(b) * p.heads + hd;
-            uint4 q4;
-            q4.x = pack2<T>(acc[0] * inv, acc[1] * inv);
-            q4.y = pack2<T>(acc[2] * inv, acc[3] * inv);
-            q4.z = pack2<T>(acc[4] * inv, acc[5] * inv);
-            q4.w = pack2<T>(acc[6] * inv, acc[7] * inv);
-            *reinterpret_cast<uint4*>(reinterpret_cast<T*>(p.out) + hr * kCkv + dh * kDvHalf + c8 * 8) = q4;
-            if (c8 == 0 && dh == 0 && p.lse) p.lse[hr] = L > 0.f ? M + fast_log2(L) : -INFINITY;
+        for (int s2 = 0; s2 < 8; ++s2) {
+          ms[s2] = -INFINITY;
+          ls[s2] = 0.f;
+          if (s2 < S) {
+            ms[s2] = dsmem_ld_f32(dsmem_addr(ml_addr + rr * 4, s2));
+            ls[s2] = dsmem_ld_f32(dsmem_addr(ml_addr + (128 + rr) * 4, s2));
           }
         }
-      }
-      cluster_sync();  // nobody leaves while a peer may still read its shared memory
-    } else {
-      const int item = (b * p.head_blocks + hb) * 2 + dh;
-      float* slot = p.partials + (static_cast<size_t>(item) * p.splits + split) * kSlotFloats;
-      // layout [column group of 32][row][32]: a warp writes and reads 4 KB contiguously
-#pragma unroll 1
-      for (int c0 = 0; c0 < kDvHalf; c0 += 32) {
-        uint32_t o[32];
-        if (nt > 0) {
-          tmem_ld_32x32(tmem_base + lane_field + kColO + c0, o);
-          tmem_ld_wait();
-        } else {
+        float M = -INFINITY, L = 0.f;
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = 0u;
-        }
-        float4* dst = reinterpret_cast<float4*>(slot + (static_cast<size_t>(c0 >> 5) * 128 + row) * 32);
-#pragma unroll
-        for (int i = 0; i < 8; ++i)
-          dst[i] = make_float4(__uint_as_float(o[4 * i]), __uint_as_float(o[4 * i + 1]), __uint_as_float(o[4 * i + 2]),
-                               __uint_as_float(o[4 * i + 3]));
-      }
-      slot[128 * kDvHalf + row] = l_run > 0.f ? m_ref : -INFINITY;
-      slot[128 * kDvHalf + 128 + row] = l_run;
-      __threadfence();
-      named_bar_sync(2, 128);
-      if (etid == 0) {
-        const int old = atomicAdd(p.counters + item, 1);
-        *flag = (old == p.splits - 1) ? 1 : 0;
-      }
-      named_bar_sync(2, 128);
-      if (*flag) {
-        __threadfence();
-        const float* base = p.partials + static_cast<size_t>(item) * p.splits * kSlotFloats;
-        float M = -INFINITY;
-        for (int s = 0; s < p.splits; ++s) M = fmaxf(M, __ldcg(base + static_cast<size_t>(s) * kSlotFloats + 128 * kDvHalf + row));
+        for (int s2 = 0; s2 < 8; ++s2) M = fmaxf(M, ms[s2]);
         const float Mu = M == -INFINITY ? 0.f : M;
-        float L = 0.f;
-        for (int s = 0; s < p.splits; ++s) {
-          const float* sl = base + static_cast<size_t>(s) * kSlotFloats + 128 * kDvHalf;
-          L += fast_exp2(__ldcg(sl + row) - Mu) * __ldcg(sl + 128 + row);
+#pragma unroll
+        for (int s2 = 0; s2 < 8; ++s2) {
+          ms[s2] = fast_exp2(ms[s2] - Mu);
+          L += ms[s2] * ls[s2];
         }
         const float inv = L > 0.f ? 1.f / L : 0.f;
-#pragma unroll 1
-        for (int c0 = 0; c0 < kDvHalf; c0 += 32) {
-          float v[32];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = 0.f;
-          for (int s = 0; s < p.splits; ++s) {
-            const float* sl = base + static_cast<size_t>(s) * kSlotFloats;
-            const float cf = fast_exp2(__ldcg(sl + 128 * kDvHalf + row) - Mu);
-            const float4* src = reinterpret_cast<const float4*>(sl + (static_cast<size_t>(c0 >> 5) * 128 + row) * 32);
-            float4 ld[8];
+        for (int s2 = 0; s2 < 8; ++s2) cft[etid * 8 + s2] = ms[s2] * inv;
+        const int hd = hb * 128 + rr;
+        if (hd < p.heads && dh == 0 && p.lse)
+          p.lse[static_cast<size_t>(b) * p.heads + hd] = L > 0.f ? M + fast_log2(L) : -INFINITY;
+      }
+      named_bar_sync(2, 256);
+      // A warp reads 512 contiguous bytes of a peer per load: four rows of one column group, lane =
+      // (row, 16-byte piece). Four such items per pass keep 4 S remote loads in flight per thread.
+      {
+        const int ewarp = etid >> 5, quads = (nrows + 3) >> 2, n_items = 8 * quads;
+        for (int w0 = ewarp; w0 < n_items; w0 += 32) {
+          float4 ld[4][8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) ld[i] = __ldcg(src + i);
+          for (int q = 0; q < 4; ++q) {
+            const int wi = min(w0 + q * 8, n_items - 1);
+            const int g = wi & 7, rl = min((wi >> 3) * 4 + (lane >> 3), nrows - 1), rr = r0 + rl;
+            const uint32_t off = ((static_cast<uint32_t>(g) * 128 + rr) * 32) * 4 + (lane & 7) * 16;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              v[4 * i] += cf * ld[i].x; v[4 * i + 1] += cf * ld[i].y;
-              v[4 * i + 2] += cf * ld[i].z; v[4 * i + 3] += cf * ld[i].w;
+            for (int s2 = 0; s2 < 8; ++s2)
+              if (s2 < S) ld[q][s2] = dsmem_ld_v4(dsmem_addr(stg_addr + off, s2));
+          }
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const int wi = w0 + q * 8;
+            const int g = wi & 7, rl = (wi >> 3) * 4 + (lane >> 3), rr = r0 + rl;
+            if (wi >= n_items || rl >= nrows) continue;
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int s2 = 0; s2 < 8; ++s2)
+              if (s2 < S) {
+                const float cf = cft[rl * 8 + s2];
+                acc[0] += cf * ld[q][s2].x; acc[1] += cf * ld[q][s2].y;
+                acc[2] += cf * ld[q][s2].z; acc[3] += cf * ld[q][s2].w;
+              }
+            const int hd = hb * 128 + rr;
+            if (hd < p.heads) {
+              const int col = g * 32 + (((lane & 7) ^ (rr & 7)) << 2);  // undo the staging swizzle
+              uint2 q2;
+              q2.x = pack2<T>(acc[0], acc[1]);
+              q2.y = pack2<T>(acc[2], acc[3]);
+              *reinterpret_cast<uint2*>(outg + (static_cast<size_t>(b) * p.heads + hd) * kCkv + dh * kDvHalf + col) = q2;
             }
           }
-          store32(v, c0, inv);
         }
-        store_lse(M, L);
-        if (etid == 0) p.counters[item] = 0;  // ready for the next launch
       }
+      if (tid == 64) stamp(14);
+      cluster_sync();  // nobody leaves while a peer may still read its shared memory
     }
   }
 
@@ -632,13 +599,13 @@ TcShape mla_tc_shape(const cb200_mla_decode_args* a, int sms) {
   int sp = static_cast<int>(ctas / items2);
   if (sp < 1) sp = 1;
   if (sp > s.blocks) sp = s.blocks;
+  if (sp > 8) sp = 8;  // the splits of an item are one thread-block cluster (portable size)
   s.blocks_per_split = ceil_div(s.blocks, sp);
   s.splits = ceil_div(s.blocks, s.blocks_per_split);
-  const size_t rows = static_cast<size_t>(a->batch) * a->num_heads;
-  s.p_bytes = align_up(rows * s.kv_pad * 2, 256);
-  s.stats_bytes = align_up(rows * s.blocks * sizeof(float2), 256);
-  s.partial_bytes = s.splits <= 8 ? 0 :  // up to eight splits combine inside a cluster
-                    static_cast<size_t>(items2) * s.splits * mlatc::kSlotFloats * 4;
+  const size_t tiles_p = static_cast<size_t>(items1) * s.blocks;  // P tiles of 128 rows x 128 tokens
+  s.p_bytes = tiles_p * mlatc::kBlk * 128 * 2;
+  s.stats_bytes = align_up(tiles_p * 128 * sizeof(float2), 256);
+  s.partial_bytes = 0;
   return s;
 }
 
@@ -647,29 +614,30 @@ int launch_mla_tc_kernels(long long grid1, long long grid2, const CUtensorMap& t
                           const CUtensorMap& tm_ckv_k, const CUtensorMap& tm_kpe, const CUtensorMap& tm_ckv_v,
                           const mlatc::Params& p, cudaStream_t stream) {
   auto k1 = mlatc::mla_scores_kernel<T>;
-  const bool cluster = p.splits >= 2 && p.splits <= 8;
-  auto k2 = cluster ? mlatc::mla_values_kernel<T, true> : mlatc::mla_values_kernel<T, false>;
+  const bool cluster = p.splits >= 2;
+  auto k2 = mlatc::mla_values_kernel<T>;
   // set on every launch: the attribute is per function and per device, and the call is cheap
   CB200_CUDA_TRY(cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, mlatc::kScoreSmem));
   CB200_CUDA_TRY(cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, mlatc::kValueSmem));
   k1<<<static_cast<unsigned>(grid1), mlatc::kScoreThreads, mlatc::kScoreSmem, stream>>>(tm_qn, tm_qp, tm_ckv_k, tm_kpe, p);
   CB200_CUDA_TRY(cudaGetLastError());
-  if (cluster) {
+  {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(grid2), 1, 1);
     cfg.blockDim = dim3(mlatc::kValueThreads, 1, 1);
     cfg.dynamicSmemBytes = mlatc::kValueSmem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = p.splits;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
+    cudaLaunchAttribute attr[2];
+    // the kernel starts while the scores kernel drains and waits (griddepcontrol.wait) before it reads P
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = p.splits;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = cluster ? 2 : 1;
     CB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, k2, tm_ckv_v, p));
-  } else {
-    k2<<<static_cast<unsigned>(grid2), mlatc::kValueThreads, mlatc::kValueSmem, stream>>>(tm_ckv_v, p);
   }
   CB200_CUDA_TRY(cudaGetLastError());
   return CB200_OK;
@@ -738,3 +706,7 @@ int launch_mla_tc(const cb200_mla_decode_args* a, int* status, int* counters, fl
 }
 
 }  // namespace cb200
+
+extern "C" int cb200_debug_read(long long* host, int n) {
+  return static_cast<int>(cudaMemcpyFromSymbol(host, cb200::mlatc::g_dbg, n * sizeof(long long)));
+}

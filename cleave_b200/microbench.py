@@ -5,7 +5,9 @@
 
 Timing follows the reference's protocol (python/cleave/runtime/timer.py:76-108,
 python/cleave/runtime/autotune.py:36-43): CUDA events around CUDA-graph replays, minimum over
-rounds. ``--launches N`` instead runs N plain launches after a warm-up (what a profiler capture
+rounds. Successive launches of a graph read different copies of the inputs (enough copies to
+cover 2.5x the 126 MB L2) unless one copy is already larger than L2, so no launch is served from
+the cache lines of the one before. ``--launches N`` instead runs N plain launches after a warm-up (what a profiler capture
 wants) and prints nothing but a completion line.
 """
 
@@ -37,6 +39,29 @@ def _gen(seed=0):
     return torch.Generator(device="cpu").manual_seed(seed)
 
 
+L2_BYTES = 126 * 1024 * 1024
+
+
+def _rotating(make_call, tensors, max_sets=8):
+    """Successive launches read different copies of the inputs, so that no launch finds its
+    operands in L2 from the one before: as many copies as it takes to cover 2.5x the L2 (at most
+    ``max_sets``; a working set that is already larger than L2 keeps one copy).
+    ``make_call(tensors)`` returns the zero-argument launch for one copy."""
+    per_set = sum(t.numel() * t.element_size() for t in tensors if t is not None)
+    n = max(1, min(max_sets, -(-int(2.5 * L2_BYTES) // max(per_set, 1)))) if per_set < L2_BYTES else 1
+    calls = [make_call(tensors)]
+    for _ in range(n - 1):
+        calls.append(make_call([None if t is None else t.clone() for t in tensors]))
+    state = {"i": 0}
+
+    def fn():
+        calls[state["i"] % n]()
+        state["i"] += 1
+
+    fn.n_sets = n
+    return fn
+
+
 def gemm_case(op, m, n, k, dtype=torch.float16, gamma=True, split_k=0):
     """(callable, flops, algorithmic bytes) for one GEMM-family configuration."""
     g = _gen()
@@ -45,14 +70,17 @@ def gemm_case(op, m, n, k, dtype=torch.float16, gamma=True, split_k=0):
     out = torch.empty(m, n, dtype=dtype, device="cuda")
     esz = 2
     if op == "matmul":
-        return (lambda: ops.matmul(x, w0, split_k=split_k, out=out)), 2 * m * n * k, (m * k + k * n + m * n) * esz
+        fn = _rotating(lambda t: (lambda: ops.matmul(t[0], t[1], split_k=split_k, out=t[2])), [x, w0, out])
+        return fn, 2 * m * n * k, (m * k + k * n + m * n) * esz
     if op == "rmsnorm_matmul":
         gm = (1 + 0.1 * torch.randn(k, generator=g)).to(dtype).cuda() if gamma else None
-        fn = lambda: ops.rmsnorm_matmul(x, w0, eps=1e-6, gamma=gm, split_k=split_k, out=out)  # noqa: E731
+        fn = _rotating(lambda t: (lambda: ops.rmsnorm_matmul(t[0], t[1], eps=1e-6, gamma=t[3], split_k=split_k, out=t[2])),
+                       [x, w0, out, gm])
         return fn, 2 * m * n * k, (m * k + k * n + m * n + (k if gamma else 0)) * esz
     if op == "swiglu":
         w1 = (torch.randn(k, n, generator=g) / k ** 0.5).to(dtype).cuda()
-        return (lambda: ops.swiglu(x, w0, w1, split_k=split_k, out=out)), 4 * m * n * k, (m * k + 2 * k * n + m * n) * esz
+        fn = _rotating(lambda t: (lambda: ops.swiglu(t[0], t[1], t[3], split_k=split_k, out=t[2])), [x, w0, out, w1])
+        return fn, 4 * m * n * k, (m * k + 2 * k * n + m * n) * esz
     raise KeyError(op)
 
 
@@ -63,7 +91,8 @@ def gqa_decode_case(batch=8, hq=32, hkv=8, d=128, skv=8192, dtype=torch.float16)
     v = torch.randn(batch * hkv, skv, d, generator=g).to(dtype).cuda()
     out = torch.empty_like(q)
     byts = (2 * k.numel() + 2 * q.numel()) * 2
-    return (lambda: ops.attention_decode(q, k, v, out=out)), 4 * batch * hq * skv * d, byts
+    fn = _rotating(lambda t: (lambda: ops.attention_decode(t[0], t[1], t[2], out=t[3])), [q, k, v, out])
+    return fn, 4 * batch * hq * skv * d, byts
 
 
 def mla_decode_case(batch=16, heads=128, skv=4096, dtype=torch.bfloat16):
@@ -75,7 +104,8 @@ def mla_decode_case(batch=16, heads=128, skv=4096, dtype=torch.bfloat16):
     out = torch.empty_like(q)
     flops = 2 * batch * heads * skv * (576 + 512)
     byts = (kv.numel() + kp.numel() + q.numel() + qp.numel() + out.numel()) * 2
-    return (lambda: ops.mla_decode(q, kv, qp, kp, 192 ** -0.5, out=out)), flops, byts
+    fn = _rotating(lambda t: (lambda: ops.mla_decode(t[0], t[1], t[2], t[3], 192 ** -0.5, out=t[4])), [q, kv, qp, kp, out])
+    return fn, flops, byts
 
 
 CONFIGS = {
@@ -94,7 +124,7 @@ def measure(name, build):
     us = min_launch_us(fn, [], batch=20, repeats=5)
     hbm, tf, kind = _peaks()
     gbs, tfs = byts / us / 1e3, flops / us / 1e6
-    return {"config": name, "us": us, "GB/s": gbs, "TFLOP/s": tfs,
+    return {"config": name, "us": us, "input_sets": getattr(fn, "n_sets", 1), "GB/s": gbs, "TFLOP/s": tfs,
             "hbm_frac": gbs / hbm, "tensor_frac": tfs / tf, "peaks": f"of {kind}",
             "hbm_frac_nominal": gbs / NOMINAL_HBM_GBS, "tensor_frac_nominal": tfs / NOMINAL_TFLOPS}
 

@@ -355,80 +355,79 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         // meets at a hardware barrier, and CTA r reduces rows [r, r + 1) * rows / S over all peers
         // through distributed shared memory, in rank order (bit-stable), and stores them. No
         // workspace, no atomics, nobody spins.
+        // Staging layout: [column group of 32][row][8 pieces of 16 bytes], piece i of row r stored at
+        // i ^ (r & 7) so that a warp's stores spread over all banks.
         float* stg = reinterpret_cast<float*>(stages);
+        const int rows_live = min(kBM, p.M - tm * kBM);
 #pragma unroll 1
         for (int c0 = 0; c0 < kUmmaN; c0 += 32) {
           uint32_t r[32];
           tmem_ld_32x32(t_acc + c0, r);
           tmem_ld_wait();
-          float4* dst = reinterpret_cast<float4*>(stg + (static_cast<size_t>(c0 >> 5) * kBM + row) * 32);
+          if (row < rows_live) {
+            float4* dst = reinterpret_cast<float4*>(stg + (static_cast<size_t>(c0 >> 5) * kBM + row) * 32);
 #pragma unroll
-          for (int j = 0; j < 8; ++j)
-            dst[j] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
-                                 __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+            for (int j = 0; j < 8; ++j)
+              dst[j ^ (row & 7)] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                               __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+          }
         }
         if constexpr (MODE == 1) stg[kBM * kUmmaN + row] = rs;
         cluster_sync();
         {
+          // CTA `rank` owns rows [r_lo, r_hi). A warp reads 512 contiguous bytes of a peer per load:
+          // four rows of one column group, lane = (row, 16-byte piece); peers are added in rank order.
           const int rank = static_cast<int>(cluster_ctarank());
-          constexpr int kItemsPerRow = Plan::kTileN / 8;
-          const int rows_live = min(kBM, p.M - tm * kBM);
+          constexpr int kGroups = Plan::kTileN / 32;
           const int per = ceil_div(rows_live, S);
           const int r_lo = min(rank * per, rows_live), r_hi = min(r_lo + per, rows_live);
-          const int items = (r_hi - r_lo) * kItemsPerRow;
+          const int quads = (r_hi - r_lo + 3) >> 2, n_items = quads * kGroups;
           const uint32_t stg_u32 = smem_u32(stg);
-          for (int it = etid; it < items; it += 128) {
-            const int r = r_lo + it / kItemsPerRow, col = (it % kItemsPerRow) * 8;
-            const uint32_t off = ((static_cast<uint32_t>(col >> 5) * kBM + r) * 32 + (col & 31)) * 4;
-            float v[8], up[8], rs_all = 0.f;
+          const int ewarp = etid >> 5;
+          for (int wi = ewarp; wi < n_items; wi += 4) {
+            const int g = wi % kGroups, r = r_lo + (wi / kGroups) * 4 + (lane >> 3);
+            const int rc = min(r, r_hi - 1);  // clamped for the loads; rows past the end are not stored
+            const uint32_t off = ((static_cast<uint32_t>(g) * kBM + rc) * 32) * 4 + (lane & 7) * 16;
+            float v[4] = {0.f, 0.f, 0.f, 0.f}, up[4] = {0.f, 0.f, 0.f, 0.f}, rs_all = 0.f;
+            for (int q0 = 0; q0 < S; q0 += 4) {  // four peers' loads in flight
+              float4 a[4], bq[4];
+              float rq[4];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = up[j] = 0.f;
-            for (int q0 = 0; q0 < S; q0 += 2) {  // S is even: two peers' loads in flight, added in rank order
-              float4 a[2][2], bq[2][2];
-              float rq[2] = {0.f, 0.f};
-#pragma unroll
-              for (int u = 0; u < 2; ++u) {
-                const uint32_t base = dsmem_addr(stg_u32, q0 + u);
-                a[u][0] = dsmem_ld_v4(base + off);
-                a[u][1] = dsmem_ld_v4(base + off + 16);
-                if constexpr (MODE == 2) {
-                  const uint32_t uo = off + (Plan::kTileN >> 5) * kBM * 32 * 4;
-                  bq[u][0] = dsmem_ld_v4(base + uo);
-                  bq[u][1] = dsmem_ld_v4(base + uo + 16);
+              for (int u = 0; u < 4; ++u) {
+                a[u] = bq[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                rq[u] = 0.f;
+                if (q0 + u < S) {
+                  const uint32_t base = dsmem_addr(stg_u32, q0 + u);
+                  a[u] = dsmem_ld_v4(base + off);
+                  if constexpr (MODE == 2) bq[u] = dsmem_ld_v4(base + off + kGroups * kBM * 32 * 4);
+                  if constexpr (MODE == 1) rq[u] = dsmem_ld_f32(base + (kBM * kUmmaN + rc) * 4);
                 }
-                if constexpr (MODE == 1) rq[u] = dsmem_ld_f32(base + (kBM * kUmmaN + r) * 4);
               }
 #pragma unroll
-              for (int u = 0; u < 2; ++u) {
-                v[0] += a[u][0].x; v[1] += a[u][0].y; v[2] += a[u][0].z; v[3] += a[u][0].w;
-                v[4] += a[u][1].x; v[5] += a[u][1].y; v[6] += a[u][1].z; v[7] += a[u][1].w;
-                if constexpr (MODE == 2) {
-                  up[0] += bq[u][0].x; up[1] += bq[u][0].y; up[2] += bq[u][0].z; up[3] += bq[u][0].w;
-                  up[4] += bq[u][1].x; up[5] += bq[u][1].y; up[6] += bq[u][1].z; up[7] += bq[u][1].w;
-                }
+              for (int u = 0; u < 4; ++u) {
+                v[0] += a[u].x; v[1] += a[u].y; v[2] += a[u].z; v[3] += a[u].w;
+                if constexpr (MODE == 2) { up[0] += bq[u].x; up[1] += bq[u].y; up[2] += bq[u].z; up[3] += bq[u].w; }
                 rs_all += rq[u];
               }
             }
-            const int gcol = tn * Plan::kTileN + col;
-            if (gcol < p.N) {
-              float o[8];
+            const int gcol = tn * Plan::kTileN + g * 32 + (((lane & 7) ^ (rc & 7)) << 2);  // undo the swizzle
+            if (r < r_hi && gcol < p.N) {
+              float o[4];
               if constexpr (MODE == 1) {
                 const float sc = rsqrtf(rs_all * inv_k + p.eps);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) o[j] = v[j] * sc;
+                for (int j = 0; j < 4; ++j) o[j] = v[j] * sc;
               } else if constexpr (MODE == 2) {
 #pragma unroll
-                for (int j = 0; j < 8; ++j) o[j] = v[j] / (1.f + __expf(-v[j])) * up[j];
+                for (int j = 0; j < 4; ++j) o[j] = v[j] / (1.f + __expf(-v[j])) * up[j];
               } else {
 #pragma unroll
-                for (int j = 0; j < 8; ++j) o[j] = v[j];
+                for (int j = 0; j < 4; ++j) o[j] = v[j];
               }
-              uint4 pk;
+              uint2 pk;
               pk.x = pack2<T>(o[0], o[1]);
               pk.y = pack2<T>(o[2], o[3]);
-              pk.z = pack2<T>(o[4], o[5]);
-              pk.w = pack2<T>(o[6], o[7]);
-              *reinterpret_cast<uint4*>(yout + static_cast<size_t>(tm * kBM + r) * p.N + gcol) = pk;
+              *reinterpret_cast<uint2*>(yout + static_cast<size_t>(tm * kBM + r) * p.N + gcol) = pk;
             }
           }
         }
@@ -638,12 +637,34 @@ int plan_gemm(const cb200_gemm_args* a, GemmSetup* s, bool need_maps) {
   // pairs two 128-column accumulators).
   s->nbw = 2;
   if (a->op != CB200_GEMM_SWIGLU && static_cast<long long>(p.tiles_m) * ceil_div(a->n, 256) >= 2LL * grid_max) s->nbw = 4;
-  p.tiles_n = ceil_div(a->n, s->nbw * kChunkN);
   p.kblocks = ceil_div(a->k, kBK);
+  // One row of tiles (M <= 128, the decode-sized GEMMs): W is streamed once, so the plan is the
+  // (tile width, cluster split) pair that puts the most SMs on it, with at least four K blocks per CTA.
+  int skinny_split = 0;
+  if (a->split_k <= 0 && a->max_ctas == 0 && p.tiles_m == 1) {
+    long long best_ctas = 0, best_pad = 0;
+    for (int nbw = 2; nbw <= (a->op == CB200_GEMM_SWIGLU ? 2 : 4); nbw *= 2) {
+      const int tn = ceil_div(a->n, nbw * kChunkN);
+      int smax = grid_max / tn;
+      if (smax > 8) smax = 8;
+      if (smax > p.kblocks / 4) smax = p.kblocks / 4;
+      if (smax < 1) continue;
+      const long long ctas = static_cast<long long>(tn) * smax, pad = static_cast<long long>(tn) * nbw * kChunkN - a->n;
+      if (ctas > best_ctas || (ctas == best_ctas && pad < best_pad)) {
+        best_ctas = ctas;
+        best_pad = pad;
+        s->nbw = nbw;
+        skinny_split = smax;
+      }
+    }
+  }
+  p.tiles_n = ceil_div(a->n, s->nbw * kChunkN);
   const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
   if (tiles >= (1LL << 24)) return CB200_ERR_UNSUPPORTED;
   int split = a->split_k;
-  if (split <= 0) {  // pick the K split that gives every CTA several chunks
+  if (split <= 0 && skinny_split > 0) {
+    split = skinny_split;
+  } else if (split <= 0) {  // pick the K split that gives every CTA several chunks
     split = 1;
     if (tiles * 8 <= grid_max && p.kblocks >= 16) {
       split = 8;  // tiny output: an 8-CTA cluster per tile (portable cluster size)
@@ -656,10 +677,10 @@ int plan_gemm(const cb200_gemm_args* a, GemmSetup* s, bool need_maps) {
   p.chunks_per_tile = ceil_div(p.kblocks, p.chunk_kblocks);
   const long long chunks = tiles * p.chunks_per_tile;
   s->grid = static_cast<int>(chunks < grid_max ? chunks : grid_max);
-  // Few tiles and a power-of-two split that fits the SMs at once: the chunks of a tile become the CTAs
+  // Few tiles and a split that fits the SMs at once (cluster of up to 8 CTAs, or 16): the chunks of a tile become the CTAs
   // of one cluster and the reduction goes through distributed shared memory.
   const int S = p.chunks_per_tile;
-  s->cluster = S >= 2 && S <= 16 && (S & (S - 1)) == 0 && chunks <= grid_max && a->max_ctas == 0;
+  s->cluster = S >= 2 && (S <= 8 || S == 16) && chunks <= grid_max && a->max_ctas == 0;
   if (s->cluster) s->grid = static_cast<int>(chunks);
   s->pair = gemm_pair_supported(a, sms) && gemm_pair_enabled();
   if (s->pair) {

@@ -50,7 +50,7 @@ def test_gemm_family_matches_reference_golden(name, split_k):
 
 
 @pytest.mark.parametrize("m,n,k", [(128, 128, 4096), (64, 1024, 4096), (1, 64, 64), (300, 520, 1000), (129, 136, 72)])
-@pytest.mark.parametrize("split_k", [0, 1, 4, 16])
+@pytest.mark.parametrize("split_k", [0, 1, 3, 4, 16])
 @pytest.mark.parametrize("dt", ["f16", "bf16"])
 def test_matmul_vs_oracle(m, n, k, split_k, dt):
     inp = cases.gemm_inputs(m + n + k, m, n, k, dt)
@@ -59,7 +59,7 @@ def test_matmul_vs_oracle(m, n, k, split_k, dt):
 
 
 @pytest.mark.parametrize("m,n,k", [(64, 1280, 4096), (200, 264, 520)])
-@pytest.mark.parametrize("split_k", [0, 1, 8])
+@pytest.mark.parametrize("split_k", [0, 1, 3, 8])
 @pytest.mark.parametrize("gamma", [False, True])
 def test_rmsnorm_matmul_vs_oracle(m, n, k, split_k, gamma):
     inp = cases.gemm_inputs(7, m, n, k, "f16", gamma=gamma)
@@ -68,7 +68,7 @@ def test_rmsnorm_matmul_vs_oracle(m, n, k, split_k, gamma):
 
 
 @pytest.mark.parametrize("m,n,k", [(256, 512, 1024), (70, 200, 328)])
-@pytest.mark.parametrize("split_k", [0, 1, 4])
+@pytest.mark.parametrize("split_k", [0, 1, 4, 5])
 def test_swiglu_vs_oracle(m, n, k, split_k):
     inp = cases.gemm_inputs(8, m, n, k, "bf16", n_w=2)
     got = _run("swiglu", inp, {"dtype": "bf16"}, split_k)

@@ -30,7 +30,7 @@ namespace cb200 {
 // tcgen05 variant for contiguous caches (mla_decode_tc.cu)
 bool mla_tc_supported(const cb200_mla_decode_args* a);
 size_t mla_tc_partial_bytes(const cb200_mla_decode_args* a, int sms);
-int launch_mla_tc(const cb200_mla_decode_args* a, int* status, int* counters, float* partials, cudaStream_t stream);
+int launch_mla_tc(const cb200_mla_decode_args* a, int* status, void* scratch, cudaStream_t stream);
 
 namespace mla {
 
@@ -664,7 +664,6 @@ extern "C" int cb200_mla_decode(const cb200_mla_decode_args* a, void* stream) {
   if (rc != CB200_OK) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (s.use_tc)
-    return launch_mla_tc(a, s.p.status, s.p.counters,
-                         reinterpret_cast<float*>(static_cast<uint8_t*>(a->workspace) + s.tc_partials_off), st);
+    return launch_mla_tc(a, s.p.status, static_cast<uint8_t*>(a->workspace) + s.tc_partials_off, st);
   return a->dtype == CB200_F16 ? dispatch_mla<__half>(s, st) : dispatch_mla<__nv_bfloat16>(s, st);
 }

@@ -8,16 +8,19 @@
 //            is 128 x 256 x 16. S sits in tensor memory (two buffers of 256 columns); eight epilogue
 //            warps (thread = head row = TMEM lane, one warp group per 128-token block) turn it into
 //            P in the cache's 16-bit type and write P, m and l to the workspace.
-//   values   O = sum_blocks 2^(m_block - m_ref) P_block V_block. A CTA owns (request, head block, half
-//            of the 512 output columns, one of S token ranges). The softmax warps read a block of P
-//            rows, scale them to the running reference maximum and store them to tensor memory,
-//            where they are the A operand; B is the latent tile (128 tokens x 256 columns, MN-major)
-//            from a three-stage TMA ring; O (128 x 256 fp32) stays in tensor memory and is rescaled
-//            only when the reference maximum grows by more than 2^8 (exact: the factor is applied to
-//            O and to the row sum alike). The S CTAs of an item are one thread-block cluster and
-//            combine their partial results through distributed shared memory; with more than
-//            eight splits they leave fp32 partials in the workspace and the last one to arrive
-//            combines them (nobody waits).
+//   values   O = sum_blocks 2^(m_block - m_ref) P_block V_block / l. A CTA owns (request, head block,
+//            a part of 128 or 256 of the 512 output columns, one of S token ranges). m_ref is the
+//            largest block maximum of the CTA's range - every block's statistics are already in
+//            memory - so the factors are at most 1 and O never needs rescaling. P tiles arrive in
+//            shared memory by bulk copies (one warp) and the latent tile (128 tokens x the CTA's
+//            columns, MN-major) by TMA (another warp); two groups of four warps (thread = head row
+//            = TMEM lane) take alternate blocks: read the P rows, multiply by the factor, store them
+//            to tensor memory, where they are the A operand. O stays in tensor memory. The S CTAs
+//            of an item are one thread-block cluster and combine their partial results through
+//            distributed shared memory (rows dealt to the ranks, peers added in rank order); the
+//            kernel is launched with programmatic stream serialization, so its set-up and first V
+//            tiles overlap the tail of the scores kernel, and waits (griddepcontrol.wait) before it
+//            touches P.
 //
 // Why two kernels: the accumulator for 128 heads x 512 columns fills tensor memory on its own, and
 // Q plus a KV tile large enough for full-width MMAs does not fit in shared memory. Splitting the
@@ -49,27 +52,16 @@ constexpr int kScoreSmem = kKStages * kKStageBytes + 1024 + 1024;
 constexpr int kScoreThreads = 320;                  // producer, MMA, eight epilogue warps
 
 // ---- values kernel
-constexpr int kDvHalf = 256;
+constexpr int kVRingBytes = 3 * 65536;              // the V ring, whatever the column split
 constexpr int kVChunkBytes = kBlk * 128;            // 64 columns x 128 tokens
-constexpr int kVStageBytes = (kDvHalf / 64) * kVChunkBytes;  // 65 536
-constexpr int kVStages = 3;
-constexpr int kValueSmem = kVStages * kVStageBytes + 2048 /*barriers, row sums*/ + 1024 /*alignment*/;
-constexpr int kValueThreads = 320;  // producer, MMA, two groups of four P-scaling warps
+constexpr int kValueSmem = kVRingBytes + 2048 /*barriers, row sums*/ + 1024 /*alignment*/;
+constexpr int kValueThreads = 352;  // V producer, MMA, two groups of four P-scaling warps, P producer
 constexpr uint32_t kColO = 0, kColP = 256;          // P: two buffers of 64 columns
-
-__device__ long long g_dbg[1024 * 16];
-__device__ __forceinline__ void stamp(int slot) {
-  long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  if (blockIdx.x < 1024) g_dbg[blockIdx.x * 16 + slot] = t;
-}
 
 struct Params {
   void* out;
   float* lse;
   int* status;
-  int* counters;
-  float* partials;
   void* pbuf;      // (batch, head blocks, token blocks) tiles of 128 rows x 128 tokens, 16-bit
   float2* stats;   // (batch, head blocks, token blocks, 128 rows): (m, l) per row and block
   int batch, heads, head_blocks, kv_len, kv_pad, blocks;
@@ -157,7 +149,6 @@ mla_scores_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_consta
     constexpr uint32_t idesc = umma_idesc(std::is_same<T, __nv_bfloat16>::value, /*b_mn_major=*/false, 128, kSTile);
     const uint32_t k_addr = smem_u32(k_smem);
     int st = 0, ph = 0;
-    if (lane == 0) stamp(0);
     for (int t = 0; t < n_tiles; ++t) {
       const int sb = t & 1;
       mbar_wait(&s_empty[sb], ((t >> 1) & 1) ^ 1, p.status, kFaultTmemBarrier);
@@ -166,7 +157,6 @@ mla_scores_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_consta
       for (int c = 0; c < kChunks; ++c) {
         mbar_wait(&k_full[st], ph, p.status, kFaultFullBarrier);
         tc_fence_after();
-        if (lane == 0 && t == 0 && c == 0) stamp(1);
         if (lane == 0) {
           const uint32_t q_addr = k_addr + st * kKStageBytes;
 #pragma unroll
@@ -181,7 +171,6 @@ mla_scores_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_consta
         if (++st == kKStages) { st = 0; ph ^= 1; }
       }
       if (lane == 0) umma_commit(&s_full[sb]);
-      if (lane == 0) stamp(2 + (t & 1));
       __syncwarp();
     }
   } else {
@@ -195,7 +184,6 @@ mla_scores_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_consta
       const int u = u0 + 2 * t + half;
       mbar_wait(&s_full[sb], (t >> 1) & 1, p.status, kFaultMmaBarrier);
       tc_fence_after();
-      if (tid == 64) stamp(4 + 2 * (t & 1));
       uint32_t r[4][32];
       if (u < u1) {
         const uint32_t t_s = tmem_base + lane_field + sb * kSTile + half * kBlk;
@@ -245,7 +233,6 @@ mla_scores_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_consta
         }
         p.stats[tile * 128 + row] = make_float2(m, l);
       }
-      if (tid == 64) stamp(5 + 2 * (t & 1));
     }
   }
 
@@ -257,29 +244,40 @@ mla_scores_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_consta
   }
 }
 
-// ---- values kernel: warp roles 0 = TMA producer, 1 = MMA issuer and TMEM owner, 2..5 and 6..9 = two
-// groups of P-scaling warps (thread = head row = TMEM lane); group g owns P buffer g and the token
+// ---- values kernel: warp roles 0 = V producer (TMA), 10 = P tile producer (bulk copies), 1 = MMA
+// issuer and TMEM owner, 2..5 and 6..9 = two groups of P-scaling warps (thread = head row = TMEM lane); group g owns P buffer g and the token
 // blocks j = g (mod 2), so two blocks' loads are in flight while a third is multiplied.
-template <typename T>
+// DV = output columns per CTA: 256 (two column parts per item) or 128 (four parts, half as many
+// token splits for the same number of CTAs, so a quarter of the combine traffic per CTA).
+template <typename T, int DV>
 __global__ void __launch_bounds__(kValueThreads, 1)
 mla_values_kernel(const __grid_constant__ CUtensorMap tm_ckv, const Params p) {
+  constexpr int kDvHalf = DV;
+  constexpr int kVStageBytes = (DV / 64) * kVChunkBytes;  // 64 KB or 32 KB
+  constexpr int kVStages = DV == 256 ? 2 : 3;
+  constexpr int kPTileBytes = kBlk * 128 * 2;            // one P tile: 128 rows x 128 tokens
+  constexpr int kPStages = (kVRingBytes - kVStages * kVStageBytes) / kPTileBytes;  // 2 or 3
+  constexpr int kParts = kCkv / DV, kGroups = DV / 32;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* v_smem = smem;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kVStages * kVStageBytes);
-  uint64_t* v_full = bars;                 // [3] TMA landed
-  uint64_t* v_empty = bars + kVStages;     // [3] the MMAs have read the stage
-  uint64_t* p_full = bars + 2 * kVStages;  // [2] scaled P stored to TMEM
+  uint8_t* pt_smem = smem + kVStages * kVStageBytes;  // P tiles as the scores kernel wrote them
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kVRingBytes);
+  uint64_t* v_full = bars;                 // [kVStages] TMA landed
+  uint64_t* v_empty = bars + kVStages;     // [kVStages] the MMAs have read the stage
+  uint64_t* pt_full = bars + 2 * kVStages; // [kPStages] P tile landed
+  uint64_t* pt_empty = pt_full + kPStages; // [kPStages] the four warps of a group have read the tile
+  uint64_t* p_full = pt_empty + kPStages;  // [2] scaled P stored to TMEM
   uint64_t* p_empty = p_full + 2;          // [2] the MMAs that read the P buffer have completed
   uint64_t* o_done = p_empty + 2;
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(o_done + 1);
-  float* l_part = reinterpret_cast<float*>(bars + 16);  // [2][128] row sums of the two groups
+  float* l_part = reinterpret_cast<float*>(bars + 32);  // [2][128] row sums of the two groups
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int S = p.splits;  // the S CTAs of an item are one cluster (S = 1: no cluster)
   int x = blockIdx.x;
   const int split = x % S; x /= S;
-  const int dh = x & 1; x >>= 1;
+  const int dh = x % kParts; x /= kParts;
   const int hb = x % p.head_blocks;
   const int b = x / p.head_blocks;
   const int t0 = min(split * p.blocks_per_split, p.blocks);
@@ -290,6 +288,10 @@ mla_values_kernel(const __grid_constant__ CUtensorMap tm_ckv, const Params p) {
     for (int s = 0; s < kVStages; ++s) {
       mbar_init(&v_full[s], 1);
       mbar_init(&v_empty[s], 1);
+    }
+    for (int s = 0; s < kPStages; ++s) {
+      mbar_init(&pt_full[s], 1);
+      mbar_init(&pt_empty[s], 4);
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&p_full[s], 4);
@@ -310,20 +312,45 @@ mla_values_kernel(const __grid_constant__ CUtensorMap tm_ckv, const Params p) {
 
   if (warp == 0) {
     // ================================================================ TMA producer
-    int st = 0, ph = 0;
-    for (int j = 0; j < nt; ++j) {
-      mbar_wait(&v_empty[st], ph ^ 1, p.status, kFaultEmptyBarrier);
+    // V does not depend on the scores kernel: its first stages are fetched while that kernel drains.
+    int vst = 0, vph = 0, jv = 0;
+    auto load_v = [&]() {
+      mbar_wait(&v_empty[vst], vph ^ 1, p.status, kFaultEmptyBarrier);
       if (lane == 0) {
-        uint8_t* dst = v_smem + st * kVStageBytes;
-        mbar_arrive_expect_tx(&v_full[st], kVStageBytes);
+        uint8_t* dst = v_smem + vst * kVStageBytes;
+        mbar_arrive_expect_tx(&v_full[vst], kVStageBytes);
 #pragma unroll
-        for (int c = 0; c < kDvHalf / 64; ++c)
-          tma_load_3d(dst + c * kVChunkBytes, &tm_ckv, &v_full[st], dh * kDvHalf + c * 64, (t0 + j) * kBlk, b);
+        for (int c = 0; c < DV / 64; ++c)
+          tma_load_3d(dst + c * kVChunkBytes, &tm_ckv, &v_full[vst], dh * DV + c * 64, (t0 + jv) * kBlk, b);
       }
       __syncwarp();
-      if (++st == kVStages) { st = 0; ph ^= 1; }
-    }
+      ++jv;
+      if (++vst == kVStages) { vst = 0; vph ^= 1; }
+    };
+    while (jv < nt) load_v();
     if (S > 1) {  // the two meetings of the combine
+      cluster_sync();
+      cluster_sync();
+    }
+  } else if (warp == 10) {
+    // ================================================================ P tile producer
+    pdl_wait();  // P comes from the scores kernel
+    const uint8_t* ptiles = reinterpret_cast<const uint8_t*>(p.pbuf) +
+                            ((static_cast<size_t>(b) * p.head_blocks + hb) * p.blocks + t0) * kPTileBytes;
+    int pst = 0, pph = 0;
+    for (int j = 0; j < nt; ++j) {
+      mbar_wait(&pt_empty[pst], pph ^ 1, p.status, kFaultEmptyBarrier);
+      if (lane == 0) {
+        mbar_arrive_expect_tx(&pt_full[pst], kPTileBytes);
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+          bulk_load_1d(pt_smem + pst * kPTileBytes + q * (kPTileBytes / 4),
+                       ptiles + static_cast<size_t>(j) * kPTileBytes + q * (kPTileBytes / 4), kPTileBytes / 4, &pt_full[pst]);
+      }
+      __syncwarp();
+      if (++pst == kPStages) { pst = 0; pph ^= 1; }
+    }
+    if (S > 1) {
       cluster_sync();
       cluster_sync();
     }
@@ -332,14 +359,10 @@ mla_values_kernel(const __grid_constant__ CUtensorMap tm_ckv, const Params p) {
     constexpr uint32_t idesc = umma_idesc(std::is_same<T, __nv_bfloat16>::value, /*b_mn_major=*/true, 128, kDvHalf);
     const uint32_t v_addr0 = smem_u32(v_smem);
     int st = 0, ph = 0;
-    if (lane == 0) stamp(8);
     for (int j = 0; j < nt; ++j) {
       const int pb = j & 1;
       mbar_wait(&v_full[st], ph, p.status, kFaultFullBarrier);
-      if (lane == 0 && j == 0) stamp(9);
       mbar_wait(&p_full[pb], (j >> 1) & 1, p.status, kFaultTmemBarrier);
-      if (lane == 0 && j == 0) stamp(10);
-      if (lane == 0 && j == nt - 1) stamp(11);
       tc_fence_after();
       if (lane == 0) {
         const uint32_t v_addr = v_addr0 + st * kVStageBytes;
@@ -370,15 +393,7 @@ mla_values_kernel(const __grid_constant__ CUtensorMap tm_ckv, const Params p) {
     const bool live = head < p.heads;
     const uint32_t lane_field = static_cast<uint32_t>(quarter * 32) << 16;
     const size_t tile0 = (static_cast<size_t>(b) * p.head_blocks + hb) * p.blocks;
-    const uint4* pbase = reinterpret_cast<const uint4*>(p.pbuf);
-    pdl_wait();  // P and the statistics come from the scores kernel
-    uint4 raw[16];
-    auto fetch = [&](int u) {
-      const uint4* src = pbase + (tile0 + u) * (kBlk * 128 / 8) + row;
-#pragma unroll
-      for (int i = 0; i < 16; ++i) raw[i] = __ldcg(src + i * 128);
-    };
-    if (group < nt) fetch(t0 + group);
+    pdl_wait();  // the statistics come from the scores kernel
     // The reference maximum is the largest block maximum of the whole range (the statistics of every
     // block are already in memory), so the factors are at most 1 and O never needs rescaling.
     float m_ref = -INFINITY;
@@ -389,7 +404,16 @@ mla_values_kernel(const __grid_constant__ CUtensorMap tm_ckv, const Params p) {
       const float2 st = p.stats[(tile0 + t0 + j) * 128 + row];  // second touch: L1
       const float f = fast_exp2(st.x - m_ref);
       l_run += st.y * f;
-      // the group's P buffer is free once the MMAs of its previous block have completed
+      const int pst = j % kPStages, pph = (j / kPStages) & 1;
+      mbar_wait(&pt_full[pst], pph, p.status, kFaultFullBarrier);
+      // 16-byte piece k of row r sits at piece index k * 128 + r: a warp reads 512 contiguous bytes
+      const uint4* src = reinterpret_cast<const uint4*>(pt_smem + pst * kPTileBytes) + row;
+      uint4 raw[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) raw[i] = src[i * 128];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&pt_empty[pst]);
+      // the group's P buffer in TMEM is free once the MMAs of its previous block have completed
       mbar_wait(&p_empty[group], ((j >> 1) & 1) ^ 1, p.status, kFaultMmaBarrier);
       tc_fence_after();
       const uint32_t f2 = pack2<T>(f, f);
@@ -405,7 +429,6 @@ mla_values_kernel(const __grid_constant__ CUtensorMap tm_ckv, const Params p) {
         }
         tmem_st_32x32(tmem_base + lane_field + kColP + group * 64 + h * 32, pk);
       }
-      if (j + 2 < nt) fetch(t0 + j + 2);
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
@@ -419,7 +442,6 @@ mla_values_kernel(const __grid_constant__ CUtensorMap tm_ckv, const Params p) {
       mbar_wait(o_done, 0, p.status, kFaultMmaBarrier);
       tc_fence_after();
     }
-    if (tid == 64) stamp(12);
     const size_t hrow = static_cast<size_t>(b) * p.heads + head;
     T* outg = reinterpret_cast<T*>(p.out);
     const int cbeg = group * (kDvHalf / 2), cend = cbeg + kDvHalf / 2;
@@ -480,7 +502,6 @@ mla_values_kernel(const __grid_constant__ CUtensorMap tm_ckv, const Params p) {
         ml[128 + row] = L;
       }
       cluster_sync();
-      if (tid == 64) stamp(13);
       const int r0 = split * 128 / S, r1 = (split + 1) * 128 / S, nrows = r1 - r0;  // at most 64
       const uint32_t stg_addr = smem_u32(stg), ml_addr = smem_u32(ml);
       if (etid < nrows) {  // factors of one row: 2 S remote loads in one round trip
@@ -515,13 +536,13 @@ mla_values_kernel(const __grid_constant__ CUtensorMap tm_ckv, const Params p) {
       // A warp reads 512 contiguous bytes of a peer per load: four rows of one column group, lane =
       // (row, 16-byte piece). Four such items per pass keep 4 S remote loads in flight per thread.
       {
-        const int ewarp = etid >> 5, quads = (nrows + 3) >> 2, n_items = 8 * quads;
+        const int ewarp = etid >> 5, quads = (nrows + 3) >> 2, n_items = kGroups * quads;
         for (int w0 = ewarp; w0 < n_items; w0 += 32) {
           float4 ld[4][8];
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
             const int wi = min(w0 + q * 8, n_items - 1);
-            const int g = wi & 7, rl = min((wi >> 3) * 4 + (lane >> 3), nrows - 1), rr = r0 + rl;
+            const int g = wi % kGroups, rl = min((wi / kGroups) * 4 + (lane >> 3), nrows - 1), rr = r0 + rl;
             const uint32_t off = ((static_cast<uint32_t>(g) * 128 + rr) * 32) * 4 + (lane & 7) * 16;
 #pragma unroll
             for (int s2 = 0; s2 < 8; ++s2)
@@ -530,7 +551,7 @@ mla_values_kernel(const __grid_constant__ CUtensorMap tm_ckv, const Params p) {
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
             const int wi = w0 + q * 8;
-            const int g = wi & 7, rl = (wi >> 3) * 4 + (lane >> 3), rr = r0 + rl;
+            const int g = wi % kGroups, rl = (wi / kGroups) * 4 + (lane >> 3), rr = r0 + rl;
             if (wi >= n_items || rl >= nrows) continue;
             float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -551,7 +572,6 @@ mla_values_kernel(const __grid_constant__ CUtensorMap tm_ckv, const Params p) {
           }
         }
       }
-      if (tid == 64) stamp(14);
       cluster_sync();  // nobody leaves while a peer may still read its shared memory
     }
   }
@@ -576,8 +596,9 @@ namespace {
 struct TcShape {
   int head_blocks, blocks, kv_pad;
   int ranges, blocks_per_range;  // scores kernel: token ranges per (request, head block)
-  int splits, blocks_per_split;  // values kernel: token ranges per (request, head block, column half)
-  size_t p_bytes, stats_bytes, partial_bytes;
+  int dv;                        // values kernel: output columns per CTA (256 or 128)
+  int splits, blocks_per_split;  // values kernel: token ranges per (request, head block, column part)
+  size_t p_bytes, stats_bytes;
 };
 
 // Both kernels fill the SMs once: as many token ranges per item as fit, never more than there are blocks.
@@ -595,7 +616,14 @@ TcShape mla_tc_shape(const cb200_mla_decode_args* a, int sms) {
   if (r > tiles) r = tiles;
   s.blocks_per_range = 2 * ceil_div(tiles, r);
   s.ranges = ceil_div(s.blocks, s.blocks_per_range);
-  const long long items2 = items1 * 2;
+  // Column parts of 256 need twice the token splits of parts of 128 for the same number of CTAs, and
+  // the cluster combine moves (S - 1) / S of a CTA's accumulator: prefer 128 when 256 would split.
+  s.dv = 256;
+  long long items2 = items1 * 2;
+  if (ctas / items2 >= 2 && s.blocks >= 2) {
+    s.dv = 128;
+    items2 = items1 * 4;
+  }
   int sp = static_cast<int>(ctas / items2);
   if (sp < 1) sp = 1;
   if (sp > s.blocks) sp = s.blocks;
@@ -605,17 +633,16 @@ TcShape mla_tc_shape(const cb200_mla_decode_args* a, int sms) {
   const size_t tiles_p = static_cast<size_t>(items1) * s.blocks;  // P tiles of 128 rows x 128 tokens
   s.p_bytes = tiles_p * mlatc::kBlk * 128 * 2;
   s.stats_bytes = align_up(tiles_p * 128 * sizeof(float2), 256);
-  s.partial_bytes = 0;
   return s;
 }
 
 template <typename T>
-int launch_mla_tc_kernels(long long grid1, long long grid2, const CUtensorMap& tm_qn, const CUtensorMap& tm_qp,
+int launch_mla_tc_kernels(int dv, long long grid1, long long grid2, const CUtensorMap& tm_qn, const CUtensorMap& tm_qp,
                           const CUtensorMap& tm_ckv_k, const CUtensorMap& tm_kpe, const CUtensorMap& tm_ckv_v,
                           const mlatc::Params& p, cudaStream_t stream) {
   auto k1 = mlatc::mla_scores_kernel<T>;
   const bool cluster = p.splits >= 2;
-  auto k2 = mlatc::mla_values_kernel<T>;
+  auto k2 = dv == 128 ? mlatc::mla_values_kernel<T, 128> : mlatc::mla_values_kernel<T, 256>;
   // set on every launch: the attribute is per function and per device, and the call is cheap
   CB200_CUDA_TRY(cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, mlatc::kScoreSmem));
   CB200_CUDA_TRY(cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, mlatc::kValueSmem));
@@ -645,13 +672,13 @@ int launch_mla_tc_kernels(long long grid1, long long grid2, const CUtensorMap& t
 
 }  // namespace
 
-// Workspace of the two-kernel path behind the caller's header and counters: P | block statistics | partials.
+// Workspace of the two-kernel path behind the caller's header and counters: P tiles | block statistics.
 size_t mla_tc_partial_bytes(const cb200_mla_decode_args* a, int sms) {
   const TcShape s = mla_tc_shape(a, sms);
-  return s.p_bytes + s.stats_bytes + s.partial_bytes;
+  return s.p_bytes + s.stats_bytes;
 }
 
-int launch_mla_tc(const cb200_mla_decode_args* a, int* status, int* counters, float* partials, cudaStream_t stream) {
+int launch_mla_tc(const cb200_mla_decode_args* a, int* status, void* scratch, cudaStream_t stream) {
   using namespace mlatc;
   const int sms = sm_count();
   if (sms <= 0) return CB200_ERR_CUDA;
@@ -660,11 +687,9 @@ int launch_mla_tc(const cb200_mla_decode_args* a, int* status, int* counters, fl
   p.out = a->out;
   p.lse = a->lse;
   p.status = status;
-  p.counters = counters;
-  uint8_t* ws = reinterpret_cast<uint8_t*>(partials);
+  uint8_t* ws = static_cast<uint8_t*>(scratch);
   p.pbuf = ws;
   p.stats = reinterpret_cast<float2*>(ws + s.p_bytes);
-  p.partials = reinterpret_cast<float*>(ws + s.p_bytes + s.stats_bytes);
   p.batch = a->batch;
   p.heads = a->num_heads;
   p.head_blocks = s.head_blocks;
@@ -677,7 +702,7 @@ int launch_mla_tc(const cb200_mla_decode_args* a, int* status, int* counters, fl
   p.blocks_per_split = s.blocks_per_split;
   p.scale_log2 = a->sm_scale * kLog2e;
   const long long grid1 = static_cast<long long>(a->batch) * s.head_blocks * s.ranges;
-  const long long grid2 = static_cast<long long>(a->batch) * s.head_blocks * 2 * s.splits;
+  const long long grid2 = static_cast<long long>(a->batch) * s.head_blocks * (mlatc::kCkv / s.dv) * s.splits;
   if (grid1 >= (1LL << 31) || grid2 >= (1LL << 31)) return CB200_ERR_UNSUPPORTED;
   const CUtensorMapDataType dt = a->dtype == CB200_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   CUtensorMap tm_qn, tm_qp, tm_ckv_k, tm_kpe, tm_ckv_v;
@@ -701,12 +726,8 @@ int launch_mla_tc(const cb200_mla_decode_args* a, int* status, int* counters, fl
       return CB200_ERR_CUDA;
   }
   return a->dtype == CB200_F16
-             ? launch_mla_tc_kernels<__half>(grid1, grid2, tm_qn, tm_qp, tm_ckv_k, tm_kpe, tm_ckv_v, p, stream)
-             : launch_mla_tc_kernels<__nv_bfloat16>(grid1, grid2, tm_qn, tm_qp, tm_ckv_k, tm_kpe, tm_ckv_v, p, stream);
+             ? launch_mla_tc_kernels<__half>(s.dv, grid1, grid2, tm_qn, tm_qp, tm_ckv_k, tm_kpe, tm_ckv_v, p, stream)
+             : launch_mla_tc_kernels<__nv_bfloat16>(s.dv, grid1, grid2, tm_qn, tm_qp, tm_ckv_k, tm_kpe, tm_ckv_v, p, stream);
 }
 
 }  // namespace cb200
-
-extern "C" int cb200_debug_read(long long* host, int n) {
-  return static_cast<int>(cudaMemcpyFromSymbol(host, cb200::mlatc::g_dbg, n * sizeof(long long)));
-}

@@ -176,7 +176,8 @@ typedef struct {
   int32_t kv_len;         /* contiguous only */
   int32_t dtype;          /* cb200_dtype */
   int32_t max_ctas;       /* 0 = one CTA per SM */
-  int32_t impl;           /* cb200_mla_impl: 0 = choose, 1 = mma.sync kernel, 2 = tcgen05 kernel (contiguous caches) */
+  int32_t impl;           /* cb200_mla_impl: 0 = choose (tcgen05 kernels for contiguous caches with at least 64
+                             heads and 512 tokens), 1 = mma.sync kernel, 2 = tcgen05 kernels (contiguous caches) */
   float sm_scale;
 } cb200_mla_decode_args;
 

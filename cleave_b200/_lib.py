@@ -61,6 +61,15 @@ class MlaDecodeArgs(C.Structure):
     ]
 
 
+class AttnPrefillArgs(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("out", C.c_void_p), ("lse", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("num_qo_heads", C.c_int32), ("num_kv_heads", C.c_int32), ("q_len", C.c_int32), ("kv_len", C.c_int32),
+        ("head_dim", C.c_int32), ("dtype", C.c_int32), ("causal", C.c_int32), ("sm_scale", C.c_float),
+    ]
+
+
 MLA_IMPL = {"auto": 0, "mma_sync": 1, "tcgen05": 2}
 
 _lib = None
@@ -99,6 +108,10 @@ def lib() -> C.CDLL:
         L.cb200_mla_decode_workspace_bytes.argtypes = [C.POINTER(MlaDecodeArgs)]
         L.cb200_mla_decode.restype = C.c_int
         L.cb200_mla_decode.argtypes = [C.POINTER(MlaDecodeArgs), C.c_void_p]
+        L.cb200_attn_prefill_workspace_bytes.restype = C.c_size_t
+        L.cb200_attn_prefill_workspace_bytes.argtypes = [C.POINTER(AttnPrefillArgs)]
+        L.cb200_attn_prefill.restype = C.c_int
+        L.cb200_attn_prefill.argtypes = [C.POINTER(AttnPrefillArgs), C.c_void_p]
         _lib = L
     return _lib
 

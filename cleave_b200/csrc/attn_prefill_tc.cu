@@ -1,0 +1,412 @@
+// Unsplit attention with many query rows (the "prefill" shapes) on the tcgen05 tensor cores.
+//
+//   O = softmax(scale * Q K^T [+ end-aligned causal mask]) V      q (HQ, SQ, D); k, v (HKV, SKV, D)
+//
+// A CTA owns (query head, tile of 128 query rows) and walks the KV tiles of 128 tokens it may see.
+// Rows of every MMA are the query rows (UMMA M = 128):
+//   S = Q K^T    A = Q tile (shared memory, K-major, resident), B = K tile (shared memory, K-major),
+//                D = S in tensor memory (128 columns, two buffers)
+//   O += P V     A = P (tensor memory, 16-bit pairs written by the softmax warps, two buffers),
+//                B = V tile (shared memory, MN-major), D = O in tensor memory (D columns)
+// Warp roles: 0 = TMA producer for Q and K, 6 = TMA producer for V, 1 = MMA issuer and TMEM owner,
+// 2..5 = softmax / epilogue (thread = query row = TMEM lane). S(j+1) is issued before PV(j), so the
+// tensor pipe computes the next scores while the softmax warps work on the current ones. The softmax
+// keeps a reference maximum per row and rescales O only when the running maximum has grown by more
+// than 2^8 (exact: the factor is applied to O and to the row sum alike), so O stays in tensor memory.
+//
+// Reference semantics: demo/attention.py:5-8 with demo/{mha,gqa,mqa}_prefill.py (no mask), and the
+// end-aligned causal mask of python/cleave/dynamic/reference.py:129-133.
+
+#include "common.cuh"
+
+#include <cstring>
+#include <type_traits>
+
+namespace cb200 {
+namespace fa {
+
+constexpr int kBM = 128, kBN = 128;
+constexpr int kThreads = 224;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kRescaleThreshold = 8.f;  // log2 units
+// TMEM columns: S0 | S1 | O | P0 | P1
+constexpr uint32_t kColS = 0, kColO = 256, kColP = 384;
+
+template <int D>
+struct Cfg {
+  static constexpr int kChunks = D / 64;                 // 64-column chunks (128 bytes)
+  static constexpr int kChunkBytes = 128 * 128;          // 128 rows x 128 bytes
+  static constexpr int kTileBytes = kChunks * kChunkBytes;
+  static constexpr int kStages = D == 64 ? 3 : 2;        // per K ring and per V ring
+  static constexpr int kSmemBytes = (1 + 2 * kStages) * kTileBytes + 1024 + 1024;
+};
+
+struct Params {
+  void* out;
+  float* lse;
+  int* status;
+  int hq, hkv, sq, skv, q_tiles, causal;
+  float scale_log2;
+};
+
+template <typename T, int D>
+__global__ void __launch_bounds__(kThreads, 1)
+attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                    const __grid_constant__ CUtensorMap tm_v, const Params p) {
+  using C = Cfg<D>;
+  constexpr int kStages = C::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* q_smem = smem;
+  uint8_t* k_smem = q_smem + C::kTileBytes;
+  uint8_t* v_smem = k_smem + kStages * C::kTileBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(v_smem + kStages * C::kTileBytes);
+  uint64_t* k_full = bars;
+  uint64_t* k_empty = k_full + kStages;
+  uint64_t* v_full = k_empty + kStages;
+  uint64_t* v_empty = v_full + kStages;
+  uint64_t* q_full = v_empty + kStages;
+  uint64_t* s_full = q_full + 1;   // [2] S complete in TMEM
+  uint64_t* s_empty = s_full + 2;  // [2] the softmax warps have read S
+  uint64_t* p_full = s_empty + 2;  // [2] P stored to TMEM (and O rescaled if needed)
+  uint64_t* p_empty = p_full + 2;  // [2] the PV MMAs that read the P buffer have completed
+  uint64_t* o_done = p_empty + 2;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(o_done + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  // heads of one query tile are neighbours (they share K/V in L2); late query tiles, which see the
+  // most keys under the causal mask, come first
+  const int h = blockIdx.x % p.hq;
+  const int qt = p.q_tiles - 1 - blockIdx.x / p.hq;
+  const int hk = h / (p.hq / p.hkv);
+  const int q0 = qt * kBM;
+  const int off = p.skv - p.sq;  // end-aligned causal mask: row r sees keys <= r + off
+  int nt = ceil_div(p.skv, kBN);
+  if (p.causal) {
+    const int last_key = min(p.sq, q0 + kBM) - 1 + off;
+    nt = last_key < 0 ? 0 : min(nt, last_key / kBN + 1);
+  }
+
+  if (tid == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&k_full[s], 1);
+      mbar_init(&k_empty[s], 1);
+      mbar_init(&v_full[s], 1);
+      mbar_init(&v_empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&s_full[s], 1);
+      mbar_init(&s_empty[s], 4);
+      mbar_init(&p_full[s], 4);
+      mbar_init(&p_empty[s], 1);
+    }
+    mbar_init(q_full, 1);
+    mbar_init(o_done, 1);
+    mbar_fence_init();
+    tma_prefetch_desc(&tm_q);
+    tma_prefetch_desc(&tm_k);
+    tma_prefetch_desc(&tm_v);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_holder, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_holder);
+
+  if (warp == 0) {
+    // ================================================================ TMA producer: Q, then K tiles
+    if (lane == 0 && nt > 0) {
+      mbar_arrive_expect_tx(q_full, C::kTileBytes);
+#pragma unroll
+      for (int c = 0; c < C::kChunks; ++c) tma_load_3d(q_smem + c * C::kChunkBytes, &tm_q, q_full, c * 64, q0, h);
+    }
+    __syncwarp();
+    int st = 0, ph = 0;
+    for (int j = 0; j < nt; ++j) {
+      mbar_wait(&k_empty[st], ph ^ 1, p.status, kFaultEmptyBarrier);
+      if (lane == 0) {
+        mbar_arrive_expect_tx(&k_full[st], C::kTileBytes);
+#pragma unroll
+        for (int c = 0; c < C::kChunks; ++c)
+          tma_load_3d(k_smem + st * C::kTileBytes + c * C::kChunkBytes, &tm_k, &k_full[st], c * 64, j * kBN, hk);
+      }
+      __syncwarp();
+      if (++st == kStages) { st = 0; ph ^= 1; }
+    }
+  } else if (warp == 6) {
+    // ================================================================ TMA producer: V tiles
+    int st = 0, ph = 0;
+    for (int j = 0; j < nt; ++j) {
+      mbar_wait(&v_empty[st], ph ^ 1, p.status, kFaultEmptyBarrier);
+      if (lane == 0) {
+        mbar_arrive_expect_tx(&v_full[st], C::kTileBytes);
+#pragma unroll
+        for (int c = 0; c < C::kChunks; ++c)
+          tma_load_3d(v_smem + st * C::kTileBytes + c * C::kChunkBytes, &tm_v, &v_full[st], c * 64, j * kBN, hk);
+      }
+      __syncwarp();
+      if (++st == kStages) { st = 0; ph ^= 1; }
+    }
+  } else if (warp == 1) {
+    // ================================================================ MMA issuer
+    constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
+    constexpr uint32_t idesc_s = umma_idesc(kBf16, /*b_mn_major=*/false, kBM, kBN);
+    constexpr uint32_t idesc_pv = umma_idesc(kBf16, /*b_mn_major=*/true, kBM, D);
+    const uint32_t q_addr = smem_u32(q_smem), k_addr = smem_u32(k_smem), v_addr = smem_u32(v_smem);
+    int kst = 0, kph = 0, vst = 0, vph = 0;
+    auto issue_s = [&](int j) {
+      const int sb = j & 1;
+      mbar_wait(&k_full[kst], kph, p.status, kFaultFullBarrier);
+      mbar_wait(&s_empty[sb], ((j >> 1) & 1) ^ 1, p.status, kFaultTmemBarrier);
+      tc_fence_after();
+      if (lane == 0) {
+        const uint32_t d = tmem_base + kColS + sb * kBN;
+#pragma unroll
+        for (int c = 0; c < C::kChunks; ++c) {
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            const uint64_t adesc = umma_smem_desc(q_addr + c * C::kChunkBytes + kk * 32, 16, 8 * 128);
+            const uint64_t bdesc = umma_smem_desc(k_addr + kst * C::kTileBytes + c * C::kChunkBytes + kk * 32, 16, 8 * 128);
+            umma_f16(d, adesc, bdesc, idesc_s, (c > 0 || kk > 0) ? 1u : 0u);
+          }
+        }
+        umma_commit(&k_empty[kst]);
+        umma_commit(&s_full[sb]);
+      }
+      __syncwarp();
+      if (++kst == kStages) { kst = 0; kph ^= 1; }
+    };
+    if (nt > 0) {
+      mbar_wait(q_full, 0, p.status, kFaultFullBarrier);
+      issue_s(0);
+    }
+    for (int j = 0; j < nt; ++j) {
+      if (j + 1 < nt) issue_s(j + 1);
+      const int pb = j & 1;
+      mbar_wait(&v_full[vst], vph, p.status, kFaultFullBarrier);
+      mbar_wait(&p_full[pb], (j >> 1) & 1, p.status, kFaultTmemBarrier);
+      tc_fence_after();
+      if (lane == 0) {
+        const uint32_t va = v_addr + vst * C::kTileBytes;
+#pragma unroll
+        for (int ks = 0; ks < kBN / 16; ++ks) {
+          // B: MN-major, 16 token rows of 128 bytes per step; 64-column chunks are kChunkBytes apart
+          const uint64_t bdesc = umma_smem_desc(va + ks * 16 * 128, C::kChunkBytes, 8 * 128);
+          umma_f16_ts(tmem_base + kColO, tmem_base + kColP + pb * 64 + ks * 8, bdesc, idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+        }
+        umma_commit(&v_empty[vst]);
+        umma_commit(&p_empty[pb]);
+        if (j == nt - 1) umma_commit(o_done);
+      }
+      __syncwarp();
+      if (++vst == kStages) { vst = 0; vph ^= 1; }
+    }
+  } else {
+    // ================================================================ softmax / epilogue
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;  // query row inside the tile = TMEM lane
+    const int qrow = q0 + row;
+    const uint32_t lane_field = static_cast<uint32_t>(quarter * 32) << 16;
+    const int key_limit = p.causal ? min(p.skv - 1, qrow + off) : p.skv - 1;  // last key this row sees
+    float m_ref = 0.f, l_run = 0.f;
+    for (int j = 0; j < nt; ++j) {
+      const int sb = j & 1, pb = j & 1;
+      mbar_wait(&s_full[sb], (j >> 1) & 1, p.status, kFaultMmaBarrier);
+      tc_fence_after();
+      uint32_t r[4][32];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) tmem_ld_32x32(tmem_base + lane_field + kColS + sb * kBN + q * 32, r[q]);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_empty[sb]);
+      const int k0 = j * kBN;
+      float mx = -INFINITY;
+      if (k0 + kBN - 1 <= key_limit) {  // whole tile visible to this row
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float v = __uint_as_float(r[q][i]) * p.scale_log2;
+            r[q][i] = __float_as_uint(v);
+            mx = fmaxf(mx, v);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float v = k0 + q * 32 + i <= key_limit ? __uint_as_float(r[q][i]) * p.scale_log2 : -INFINITY;
+            r[q][i] = __float_as_uint(v);
+            mx = fmaxf(mx, v);
+          }
+        }
+      }
+      float alpha = 1.f;
+      bool rescale = false;
+      if (j == 0) {
+        m_ref = mx == -INFINITY ? 0.f : mx;
+      } else if (mx > m_ref + kRescaleThreshold) {
+        alpha = fast_exp2(m_ref - mx);
+        m_ref = mx;
+        rescale = true;
+      }
+      // the P buffer is free once the PV MMAs of tile j - 2 have completed
+      mbar_wait(&p_empty[pb], ((j >> 1) & 1) ^ 1, p.status, kFaultMmaBarrier);
+      if (__any_sync(0xffffffffu, rescale)) {  // rare: the running maximum grew by more than 2^8
+        // O may only be touched when no PV MMA is in flight: tile j - 1 is the last one issued
+        mbar_wait(&p_empty[pb ^ 1], ((j - 1) >> 1) & 1, p.status, kFaultMmaBarrier);
+        tc_fence_after();
+#pragma unroll 1
+        for (int c0 = 0; c0 < D; c0 += 32) {
+          uint32_t o[32];
+          tmem_ld_32x32(tmem_base + lane_field + kColO + c0, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st_32x32(tmem_base + lane_field + kColO + c0, o);
+        }
+        tmem_st_wait();
+      }
+      tc_fence_after();
+      float psum = 0.f;
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        uint32_t pk[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int c = hh * 64 + 2 * i;
+          const float p0 = fast_exp2(__uint_as_float(r[c >> 5][c & 31]) - m_ref);
+          const float p1 = fast_exp2(__uint_as_float(r[(c + 1) >> 5][(c + 1) & 31]) - m_ref);
+          psum += p0 + p1;
+          pk[i] = pack2<T>(p0, p1);
+        }
+        tmem_st_32x32(tmem_base + lane_field + kColP + pb * 64 + hh * 32, pk);
+      }
+      l_run = l_run * alpha + psum;
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[pb]);
+    }
+    // ---- epilogue: O / l
+    if (nt > 0) {
+      mbar_wait(o_done, 0, p.status, kFaultMmaBarrier);
+      tc_fence_after();
+    }
+    const bool live = qrow < p.sq;
+    const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+    T* outp = reinterpret_cast<T*>(p.out) + (static_cast<size_t>(h) * p.sq + qrow) * D;
+#pragma unroll 1
+    for (int c0 = 0; c0 < D; c0 += 32) {
+      uint32_t o[32];
+      if (nt > 0) {
+        tmem_ld_32x32(tmem_base + lane_field + kColO + c0, o);
+        tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[i] = 0u;
+      }
+      if (live) {
+        const float* v = reinterpret_cast<const float*>(o);
+#pragma unroll
+        for (int i = 0; i < 32; i += 8) {
+          uint4 q4;
+          q4.x = pack2<T>(v[i] * inv, v[i + 1] * inv);
+          q4.y = pack2<T>(v[i + 2] * inv, v[i + 3] * inv);
+          q4.z = pack2<T>(v[i + 4] * inv, v[i + 5] * inv);
+          q4.w = pack2<T>(v[i + 6] * inv, v[i + 7] * inv);
+          *reinterpret_cast<uint4*>(outp + c0 + i) = q4;
+        }
+      }
+    }
+    if (live && p.lse) p.lse[static_cast<size_t>(h) * p.sq + qrow] = l_run > 0.f ? m_ref + fast_log2(l_run) : -INFINITY;
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+}  // namespace fa
+
+// ------------------------------------------------------------------------------------- host side
+namespace {
+
+int plan_prefill(const cb200_attn_prefill_args* a) {
+  if (!a) return CB200_ERR_BAD_ARG;
+  if (a->num_qo_heads <= 0 || a->num_kv_heads <= 0 || a->q_len <= 0 || a->kv_len <= 0) return CB200_ERR_BAD_ARG;
+  if (a->num_qo_heads % a->num_kv_heads) return CB200_ERR_BAD_ARG;
+  if (a->head_dim != 64 && a->head_dim != 128) return CB200_ERR_UNSUPPORTED;
+  if (a->dtype != CB200_F16 && a->dtype != CB200_BF16) return CB200_ERR_UNSUPPORTED;
+  if (a->causal && a->q_len > a->kv_len) return CB200_ERR_UNSUPPORTED;  // rows that see no key at all
+  const long long ctas = static_cast<long long>(a->num_qo_heads) * ceil_div(a->q_len, fa::kBM);
+  if (ctas >= (1LL << 31)) return CB200_ERR_UNSUPPORTED;
+  return CB200_OK;
+}
+
+template <typename T, int D>
+int launch_prefill(const cb200_attn_prefill_args* a, cudaStream_t stream) {
+  using namespace fa;
+  Params p{};
+  p.out = a->out;
+  p.lse = a->lse;
+  p.status = reinterpret_cast<int*>(a->workspace);
+  p.hq = a->num_qo_heads;
+  p.hkv = a->num_kv_heads;
+  p.sq = a->q_len;
+  p.skv = a->kv_len;
+  p.q_tiles = ceil_div(a->q_len, kBM);
+  p.causal = a->causal ? 1 : 0;
+  p.scale_log2 = a->sm_scale * kLog2e;
+  const CUtensorMapDataType dt = a->dtype == CB200_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  CUtensorMap tm_q, tm_k, tm_v;
+  {
+    uint32_t box[3] = {64u, 128u, 1u};
+    uint64_t dq[3] = {static_cast<uint64_t>(D), static_cast<uint64_t>(a->q_len), static_cast<uint64_t>(a->num_qo_heads)};
+    uint64_t sq[2] = {static_cast<uint64_t>(D) * 2, static_cast<uint64_t>(a->q_len) * D * 2};
+    uint64_t dk[3] = {static_cast<uint64_t>(D), static_cast<uint64_t>(a->kv_len), static_cast<uint64_t>(a->num_kv_heads)};
+    uint64_t sk[2] = {static_cast<uint64_t>(D) * 2, static_cast<uint64_t>(a->kv_len) * D * 2};
+    const CUtensorMapSwizzle sw = CU_TENSOR_MAP_SWIZZLE_128B;
+    if (!encode_tensor_map(&tm_q, dt, 3, const_cast<void*>(a->q), dq, sq, box, sw) ||
+        !encode_tensor_map(&tm_k, dt, 3, const_cast<void*>(a->k), dk, sk, box, sw) ||
+        !encode_tensor_map(&tm_v, dt, 3, const_cast<void*>(a->v), dk, sk, box, sw))
+      return CB200_ERR_CUDA;
+  }
+  auto kern = attn_prefill_kernel<T, D>;
+  CB200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<D>::kSmemBytes));
+  const unsigned grid = static_cast<unsigned>(p.hq) * p.q_tiles;
+  kern<<<grid, kThreads, Cfg<D>::kSmemBytes, stream>>>(tm_q, tm_k, tm_v, p);
+  CB200_CUDA_TRY(cudaGetLastError());
+  return CB200_OK;
+}
+
+}  // namespace
+}  // namespace cb200
+
+extern "C" size_t cb200_attn_prefill_workspace_bytes(const cb200_attn_prefill_args* a) {
+  return cb200::plan_prefill(a) == CB200_OK ? cb200::kWsHeaderBytes : 0;
+}
+
+extern "C" int cb200_attn_prefill(const cb200_attn_prefill_args* a, void* stream) {
+  using namespace cb200;
+  const int rc = plan_prefill(a);
+  if (rc != CB200_OK) return rc;
+  if (!a->q || !a->k || !a->v || !a->out) return CB200_ERR_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(a->q) | reinterpret_cast<uintptr_t>(a->k) | reinterpret_cast<uintptr_t>(a->v) |
+       reinterpret_cast<uintptr_t>(a->out)) & 15)
+    return CB200_ERR_ALIGNMENT;
+  if (!a->workspace || a->workspace_bytes < kWsHeaderBytes) return CB200_ERR_WORKSPACE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const bool f16 = a->dtype == CB200_F16;
+  if (a->head_dim == 64)
+    return f16 ? launch_prefill<__half, 64>(a, st) : launch_prefill<__nv_bfloat16, 64>(a, st);
+  return f16 ? launch_prefill<__half, 128>(a, st) : launch_prefill<__nv_bfloat16, 128>(a, st);
+}

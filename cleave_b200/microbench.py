@@ -108,6 +108,18 @@ def mla_decode_case(batch=16, heads=128, skv=4096, dtype=torch.bfloat16):
     return fn, flops, byts
 
 
+def attn_prefill_case(hq=32, hkv=32, s=4096, d=64, dtype=torch.float16, causal=False):
+    g = _gen()
+    q = torch.randn(hq, s, d, generator=g).to(dtype).cuda()
+    k = torch.randn(hkv, s, d, generator=g).to(dtype).cuda()
+    v = torch.randn(hkv, s, d, generator=g).to(dtype).cuda()
+    out = torch.empty_like(q)
+    flops = 4 * hq * s * s * d // (2 if causal else 1)
+    byts = (2 * q.numel() + 2 * k.numel()) * 2
+    fn = _rotating(lambda t: (lambda: ops.attention_prefill(t[0], t[1], t[2], causal=causal, out=t[3])), [q, k, v, out])
+    return fn, flops, byts
+
+
 CONFIGS = {
     "cfg1_matmul_128x128x4096": lambda: gemm_case("matmul", 128, 128, 4096),
     "cfg2_rmsnorm_matmul_64x11008x4096": lambda: gemm_case("rmsnorm_matmul", 64, 11008, 4096),
@@ -116,6 +128,10 @@ CONFIGS = {
     "demo_swiglu_4096x14336x4096": lambda: gemm_case("swiglu", 4096, 14336, 4096),
     "cfg3_gqa_decode_b8_h32_kv8_d128_s8192": lambda: gqa_decode_case(),
     "cfg4_mla_decode_b16_h128_s4096": lambda: mla_decode_case(),
+    "demo_mha_prefill_h32_s4096_d64": lambda: attn_prefill_case(32, 32, 4096, 64),
+    "demo_gqa_prefill_h32_kv8_s4096_d64": lambda: attn_prefill_case(32, 8, 4096, 64),
+    "gqa_prefill_causal_h32_kv8_s4096_d128": lambda: attn_prefill_case(32, 8, 4096, 128, torch.bfloat16, True),
+    "gqa_prefill_h32_kv8_s4096_d128": lambda: attn_prefill_case(32, 8, 4096, 128, torch.bfloat16, False),
 }
 
 
@@ -131,7 +147,7 @@ def measure(name, build):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default=None, choices=["matmul", "rmsnorm_matmul", "swiglu", "gqa_decode", "mla_decode"])
+    ap.add_argument("--op", default=None, choices=["matmul", "rmsnorm_matmul", "swiglu", "gqa_decode", "mla_decode", "attn_prefill"])
     ap.add_argument("--m", type=int, default=4096)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
@@ -145,6 +161,8 @@ def main():
             build = gqa_decode_case
         elif a.op == "mla_decode":
             build = mla_decode_case
+        elif a.op == "attn_prefill":
+            build = lambda: attn_prefill_case(32, 8, a.m, a.k if a.k in (64, 128) else 128, torch.bfloat16, False)  # noqa: E731
         else:
             build = lambda: gemm_case(a.op, a.m, a.n, a.k, gamma=not a.no_gamma, split_k=a.split_k)  # noqa: E731
         if a.launches:

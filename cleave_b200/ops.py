@@ -135,6 +135,35 @@ def attention_decode(q, k, v, sm_scale=None, *, out=None, lse=None, max_ctas=0):
     return out
 
 
+def attention_prefill(q, k, v, sm_scale=None, *, causal=False, out=None, lse=None):
+    """Unsplit attention with many query rows (reference: demo/attention.py:5-8 at the shapes of
+    demo/{mha,gqa,mqa}_prefill.py). ``q`` (HQ, SQ, D); ``k``, ``v`` (HKV, SKV, D); D 64 or 128; query
+    head h reads kv head h // (HQ/HKV). ``causal`` applies the end-aligned mask of the paged and
+    ragged prefill operators (python/cleave/dynamic/reference.py:129-133). Returns ``out``
+    (HQ, SQ, D); pass ``lse`` (HQ, SQ) fp32 to also get the base-2 log-sum-exp."""
+    q, k, v = _cuda(q, "q"), _cuda(k, "k"), _cuda(v, "v")
+    hq, sq, d = q.shape
+    hkv, skv, d2 = k.shape
+    if d2 != d or v.shape != k.shape or hq % hkv:
+        raise ValueError("shapes: q (HQ,SQ,D), k/v (HKV,SKV,D), HQ a multiple of HKV")
+    if sm_scale is None:
+        sm_scale = float(d) ** -0.5
+    if out is None:
+        out = torch.empty_like(q)
+    a = _lib.AttnPrefillArgs()
+    a.q, a.k, a.v, a.out = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr()
+    a.lse = lse.data_ptr() if lse is not None else None
+    a.num_qo_heads, a.num_kv_heads, a.q_len, a.kv_len, a.head_dim = hq, hkv, sq, skv, d
+    a.dtype, a.causal, a.sm_scale = _dtype_code(q), int(bool(causal)), float(sm_scale)
+    need = _lib.lib().cb200_attn_prefill_workspace_bytes(C.byref(a))
+    if need == 0:
+        _lib.check(_lib.lib().cb200_attn_prefill(C.byref(a), _stream()))  # reports why the plan is refused
+    ws = workspace("attn_prefill", need, q.device)
+    a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+    _lib.check(_lib.lib().cb200_attn_prefill(C.byref(a), _stream()))
+    return out
+
+
 def gqa_paged_decode_static_scratch(q, k_cache, v_cache, kv_indptr, kv_indices, kv_last_page_len, sm_scale,
                                     *, out, lse, max_ctas=0):
     """Paged decode for hosts that may not allocate device memory (a server that gave this

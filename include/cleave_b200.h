@@ -185,6 +185,36 @@ size_t cb200_mla_decode_workspace_bytes(const cb200_mla_decode_args* a);
 int cb200_mla_decode(const cb200_mla_decode_args* a, void* stream);
 
 /* ------------------------------------------------------------------------------------------
+ * Unsplit attention with many query rows (the "prefill" shapes), tcgen05/TMEM kernel.
+ *   O = softmax(sm_scale * Q K^T [+ causal mask]) V; query head h reads kv head h / (HQ / HKV).
+ * Replaces the static unsplit attention kernels of demo/{mha,gqa,mqa}_prefill.py
+ * (tests/graph/handwritten/expected_kernels/mha_bhsd.py); `causal` applies the end-aligned mask of
+ * python/cleave/dynamic/reference.py:129-133 (query row r sees keys <= r + kv_len - q_len), the
+ * mask of the paged and ragged prefill operators. head_dim 64 or 128. The workspace holds only the
+ * status word (cb200_workspace_status).
+ * ---------------------------------------------------------------------------------------- */
+typedef struct {
+  const void* q;   /* (num_qo_heads, q_len, head_dim) */
+  const void* k;   /* (num_kv_heads, kv_len, head_dim) */
+  const void* v;   /* (num_kv_heads, kv_len, head_dim) */
+  void* out;       /* (num_qo_heads, q_len, head_dim) */
+  float* lse;      /* (num_qo_heads, q_len) base 2, may be NULL */
+  void* workspace;
+  size_t workspace_bytes;
+  int32_t num_qo_heads;
+  int32_t num_kv_heads;
+  int32_t q_len;
+  int32_t kv_len;
+  int32_t head_dim; /* 64 or 128 */
+  int32_t dtype;    /* cb200_dtype */
+  int32_t causal;   /* 0 = no mask, 1 = end-aligned causal mask (needs q_len <= kv_len) */
+  float sm_scale;
+} cb200_attn_prefill_args;
+
+size_t cb200_attn_prefill_workspace_bytes(const cb200_attn_prefill_args* a);
+int cb200_attn_prefill(const cb200_attn_prefill_args* a, void* stream);
+
+/* ------------------------------------------------------------------------------------------
  * Decode attention for callers that cannot allocate device memory. (No counterpart in the
  * reference, whose wrappers always own a torch-allocated scratch buffer.)
  *

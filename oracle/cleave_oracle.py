@@ -149,6 +149,24 @@ def attention(q, k, v, dtype: str = "f16", scale: float | None = None) -> np.nda
     return round_to(pp @ vv, dtype)
 
 
+def attention_masked(q, k, v, scale: float, causal: bool, dtype: str = "bf16"):
+    """Attention with the end-aligned causal mask of the paged and ragged prefill operators
+    (python/cleave/dynamic/reference.py:85-133: keep ``kv_pos <= kv_len - q_len + q_pos``, fp32
+    softmax through ``_finish``, base-2 lse). q (HQ, SQ, D); k, v (HKV, SKV, D).
+    Returns (out (HQ, SQ, D), lse (HQ, SQ))."""
+    q, k, v = f32(q), f32(k), f32(v)
+    hq, sq, _ = q.shape
+    hkv, skv, _ = k.shape
+    g = hq // hkv
+    kk, vv = np.repeat(k, g, axis=0), np.repeat(v, g, axis=0)
+    logits = np.einsum("hqd,hkd->hqk", q, kk, optimize=True).astype(np.float32) * np.float32(scale)
+    if causal:
+        keep = np.arange(skv)[None, :] <= (skv - sq) + np.arange(sq)[:, None]
+        logits = np.where(keep[None], logits, -np.inf).astype(np.float32)
+    w, l = _finish(logits)
+    return round_to(np.einsum("hqk,hkd->hqd", w, vv, optimize=True), dtype), l
+
+
 def mla_decode(q, kv, q_pe, k_pe, scale: float, dtype: str = "bf16") -> np.ndarray:
     """Absorbed-latent MLA decode: ``S = (Q KV^T + Qpe Kpe^T) * scale``; ``O = softmax(S) KV``.
     q (B,H,D), kv (B,SKV,D), q_pe (B,H,PE), k_pe (B,SKV,PE)."""

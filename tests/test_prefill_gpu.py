@@ -1,0 +1,119 @@
+"""GPU parity of the tcgen05 unsplit-attention ("prefill") kernel, through the C ABI, against the
+oracle: the reference's fixed-shift static attention without a mask, and the end-aligned causal
+mask of its paged / ragged prefill definitions."""
+
+import numpy as np
+import pytest
+import torch
+
+import cases
+from _util import assert_close, assert_lse_close, dev, host
+from oracle import cleave_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+
+def _ops():
+    from cleave_b200 import ops
+
+    return ops
+
+
+def _check_ws():
+    ops = _ops()
+    ops.check_workspace(ops.workspace("attn_prefill", 0, "cuda"))
+
+
+SHAPES = [  # hq, hkv, sq, skv, d
+    (4, 4, 256, 256, 64),     # MHA, whole tiles
+    (8, 2, 300, 517, 128),    # GQA, ragged in both lengths
+    (4, 1, 130, 1000, 64),    # MQA
+    (2, 2, 128, 128, 128),    # a single tile
+    (3, 3, 1, 77, 64),        # one query row
+    (2, 1, 640, 640, 128),    # five KV tiles: both S and P buffers wrap
+]
+
+
+@pytest.mark.parametrize("dt", ["f16", "bf16"])
+@pytest.mark.parametrize("hq,hkv,sq,skv,d", SHAPES)
+def test_unmasked_attention_vs_oracle(hq, hkv, sq, skv, d, dt):
+    """Reference: demo/attention.py:5-8 (exp(s/sqrt(d) - 50/sqrt(d)) / rowsum)."""
+    inp = cases.attention_inputs(hq * 1000 + sq, hq, hkv, sq, skv, d, dt)
+    got = _ops().attention_prefill(dev(inp["q"], dt), dev(inp["k"], dt), dev(inp["v"], dt))
+    _check_ws()
+    assert_close(host(got), orc.attention(inp["q"], inp["k"], inp["v"], dt))
+
+
+@pytest.mark.parametrize("dt", ["bf16", "f16"])
+@pytest.mark.parametrize("hq,hkv,sq,skv,d", [s for s in SHAPES if s[2] <= s[3]])
+def test_causal_attention_vs_oracle(hq, hkv, sq, skv, d, dt):
+    """Reference: python/cleave/dynamic/reference.py:85-133 (end-aligned causal mask, base-2 lse)."""
+    inp = cases.attention_inputs(hq * 1000 + skv, hq, hkv, sq, skv, d, dt)
+    scale = d ** -0.5
+    lse = torch.empty(hq, sq, dtype=torch.float32, device="cuda")
+    got = _ops().attention_prefill(dev(inp["q"], dt), dev(inp["k"], dt), dev(inp["v"], dt), scale, causal=True, lse=lse)
+    _check_ws()
+    want, want_lse = orc.attention_masked(inp["q"], inp["k"], inp["v"], scale, True, dt)
+    assert_close(host(got), want)
+    assert_lse_close(host(lse), want_lse)
+
+
+def test_large_logits_take_the_rescale_path():
+    """Keys whose norm grows along the sequence push the running maximum up by more than 2^8
+    between tiles, so O is rescaled in tensor memory."""
+    rng = np.random.default_rng(5)
+    hq, sq, skv, d = 2, 128, 512, 64
+    q = cases.round_to(rng.standard_normal((hq, sq, d), dtype=np.float32), "bf16")
+    step = (1.0 + 3.0 * (np.arange(skv) // 128))[None, :, None].astype(np.float32)
+    k = cases.round_to(rng.standard_normal((hq, skv, d), dtype=np.float32) * step, "bf16")
+    v = cases.round_to(rng.standard_normal((hq, skv, d), dtype=np.float32), "bf16")
+    lse = torch.empty(hq, sq, dtype=torch.float32, device="cuda")
+    got = _ops().attention_prefill(dev(q, "bf16"), dev(k, "bf16"), dev(v, "bf16"), 1.0, lse=lse)
+    _check_ws()
+    want, want_lse = orc.attention_masked(q, k, v, 1.0, False, "bf16")
+    assert_close(host(got), want)
+    assert_lse_close(host(lse), want_lse)
+
+
+def test_repeat_launches_are_bit_identical():
+    inp = cases.attention_inputs(9, 8, 2, 300, 517, 128, "f16")
+    q, k, v = (dev(inp[n], "f16") for n in ("q", "k", "v"))
+    a = host(_ops().attention_prefill(q, k, v, causal=True))
+    b = host(_ops().attention_prefill(q, k, v, causal=True))
+    assert np.array_equal(a, b)
+
+
+def test_full_demo_shape_properties():
+    """demo/gqa_prefill.py at full size (32 / 8 heads, S_Q = S_KV = 4096, D 64, fp16): with V = 1 every
+    output is 1 (the weights of a row sum to one), and sampled rows match the oracle."""
+    g = torch.Generator(device="cpu").manual_seed(0)
+    hq, hkv, s, d = 32, 8, 4096, 64
+    q = torch.randn(hq, s, d, generator=g).half()
+    k = torch.randn(hkv, s, d, generator=g).half()
+    v = torch.randn(hkv, s, d, generator=g).half()
+    ops = _ops()
+    ones = ops.attention_prefill(q.cuda(), k.cuda(), torch.ones_like(v).cuda(), causal=True)
+    np.testing.assert_allclose(host(ones), 1.0, rtol=0, atol=4e-3)
+    out = host(ops.attention_prefill(q.cuda(), k.cuda(), v.cuda(), causal=True))
+    _check_ws()
+    rows = np.array([0, 1, 127, 128, 2047, 3000, 4095])
+    for h in (0, 13, 31):
+        hk = h // (hq // hkv)
+        logits = (q[h, rows].float() @ k[hk].float().T).numpy() * np.float32(d ** -0.5)
+        logits = np.where(np.arange(s)[None, :] <= rows[:, None], logits, -np.inf).astype(np.float32)
+        w, _ = orc._finish(logits)
+        assert_close(out[h, rows], cases.round_to(w @ v[hk].float().numpy(), "f16"))
+
+
+def test_prefill_bad_arguments():
+    from cleave_b200 import Cb200Error
+
+    ops = _ops()
+    q = torch.zeros(2, 64, 96, dtype=torch.float16, device="cuda")
+    k = torch.zeros(2, 64, 96, dtype=torch.float16, device="cuda")
+    with pytest.raises(Cb200Error):
+        ops.attention_prefill(q, k, k)  # head_dim 96
+    q = torch.zeros(2, 64, 64, dtype=torch.float16, device="cuda")
+    k = torch.zeros(2, 32, 64, dtype=torch.float16, device="cuda")
+    with pytest.raises(Cb200Error):
+        ops.attention_prefill(q, k, k, causal=True)  # more query rows than keys under the causal mask

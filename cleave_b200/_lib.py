@@ -70,6 +70,16 @@ class AttnPrefillArgs(C.Structure):
     ]
 
 
+class AttnPrefillRaggedArgs(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("qo_indptr", C.c_void_p), ("kv_indptr", C.c_void_p),
+        ("out", C.c_void_p), ("lse", C.c_void_p), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("batch", C.c_int32), ("total_q", C.c_int32), ("total_kv", C.c_int32),
+        ("num_qo_heads", C.c_int32), ("num_kv_heads", C.c_int32), ("head_dim", C.c_int32), ("dtype", C.c_int32),
+        ("causal", C.c_int32), ("sm_scale", C.c_float),
+    ]
+
+
 MLA_IMPL = {"auto": 0, "mma_sync": 1, "tcgen05": 2}
 
 _lib = None
@@ -112,6 +122,10 @@ def lib() -> C.CDLL:
         L.cb200_attn_prefill_workspace_bytes.argtypes = [C.POINTER(AttnPrefillArgs)]
         L.cb200_attn_prefill.restype = C.c_int
         L.cb200_attn_prefill.argtypes = [C.POINTER(AttnPrefillArgs), C.c_void_p]
+        L.cb200_attn_prefill_ragged_workspace_bytes.restype = C.c_size_t
+        L.cb200_attn_prefill_ragged_workspace_bytes.argtypes = [C.POINTER(AttnPrefillRaggedArgs)]
+        L.cb200_attn_prefill_ragged.restype = C.c_int
+        L.cb200_attn_prefill_ragged.argtypes = [C.POINTER(AttnPrefillRaggedArgs), C.c_void_p]
         _lib = L
     return _lib
 

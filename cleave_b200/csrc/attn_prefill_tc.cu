@@ -45,11 +45,17 @@ struct Params {
   void* out;
   float* lse;
   int* status;
+  const int* qo_indptr;  // ragged: (batch + 1) query-row offsets
+  const int* kv_indptr;  // ragged: (batch + 1) key offsets
+  int batch;             // ragged: requests
   int hq, hkv, sq, skv, q_tiles, causal;
   float scale_log2;
 };
 
-template <typename T, int D>
+// RAGGED: q (total_q, HQ, D), k / v (total_kv, HKV, D) with one (query range, key range) per request;
+// a CTA finds its (request, query tile) by scanning the query offsets (the device-side work list of
+// the reference's IndptrTileScan, python/cleave/dynamic/paging/stages.py:288-328).
+template <typename T, int D, bool RAGGED>
 __global__ void __launch_bounds__(kThreads, 1)
 attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                     const __grid_constant__ CUtensorMap tm_v, const Params p) {
@@ -74,16 +80,34 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(o_done + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  // heads of one query tile are neighbours (they share K/V in L2); late query tiles, which see the
-  // most keys under the causal mask, come first
+  // heads of one query tile are neighbours (they share K/V in L2)
   const int h = blockIdx.x % p.hq;
-  const int qt = p.q_tiles - 1 - blockIdx.x / p.hq;
   const int hk = h / (p.hq / p.hkv);
-  const int q0 = qt * kBM;
-  const int off = p.skv - p.sq;  // end-aligned causal mask: row r sees keys <= r + off
-  int nt = ceil_div(p.skv, kBN);
+  int q0, sq, skv, q_base = 0, kv_base = 0;
+  if constexpr (RAGGED) {
+    int t = blockIdx.x / p.hq, r = 0, lo = __ldg(p.qo_indptr);
+    bool found = false;
+    for (; r < p.batch; ++r) {
+      const int hi = __ldg(p.qo_indptr + r + 1);
+      const int tiles = hi > lo ? ceil_div(hi - lo, kBM) : 0;
+      if (t < tiles) { found = true; q_base = lo; sq = hi - lo; break; }
+      t -= tiles;
+      lo = hi;
+    }
+    if (!found) return;  // the grid is an upper bound on the number of query tiles
+    kv_base = __ldg(p.kv_indptr + r);
+    skv = max(__ldg(p.kv_indptr + r + 1) - kv_base, 0);
+    q0 = t * kBM;
+  } else {
+    // late query tiles, which see the most keys under the causal mask, come first
+    q0 = (p.q_tiles - 1 - blockIdx.x / p.hq) * kBM;
+    sq = p.sq;
+    skv = p.skv;
+  }
+  const int off = skv - sq;  // end-aligned causal mask: row r sees keys <= r + off
+  int nt = ceil_div(skv, kBN);
   if (p.causal) {
-    const int last_key = min(p.sq, q0 + kBM) - 1 + off;
+    const int last_key = min(sq, q0 + kBM) - 1 + off;
     nt = last_key < 0 ? 0 : min(nt, last_key / kBN + 1);
   }
 
@@ -121,7 +145,10 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     if (lane == 0 && nt > 0) {
       mbar_arrive_expect_tx(q_full, C::kTileBytes);
 #pragma unroll
-      for (int c = 0; c < C::kChunks; ++c) tma_load_3d(q_smem + c * C::kChunkBytes, &tm_q, q_full, c * 64, q0, h);
+      for (int c = 0; c < C::kChunks; ++c) {
+        if constexpr (RAGGED) tma_load_3d(q_smem + c * C::kChunkBytes, &tm_q, q_full, c * 64, h, q_base + q0);
+        else tma_load_3d(q_smem + c * C::kChunkBytes, &tm_q, q_full, c * 64, q0, h);
+      }
     }
     __syncwarp();
     int st = 0, ph = 0;
@@ -130,8 +157,11 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       if (lane == 0) {
         mbar_arrive_expect_tx(&k_full[st], C::kTileBytes);
 #pragma unroll
-        for (int c = 0; c < C::kChunks; ++c)
-          tma_load_3d(k_smem + st * C::kTileBytes + c * C::kChunkBytes, &tm_k, &k_full[st], c * 64, j * kBN, hk);
+        for (int c = 0; c < C::kChunks; ++c) {
+          uint8_t* dst = k_smem + st * C::kTileBytes + c * C::kChunkBytes;
+          if constexpr (RAGGED) tma_load_3d(dst, &tm_k, &k_full[st], c * 64, hk, kv_base + j * kBN);
+          else tma_load_3d(dst, &tm_k, &k_full[st], c * 64, j * kBN, hk);
+        }
       }
       __syncwarp();
       if (++st == kStages) { st = 0; ph ^= 1; }
@@ -144,8 +174,11 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       if (lane == 0) {
         mbar_arrive_expect_tx(&v_full[st], C::kTileBytes);
 #pragma unroll
-        for (int c = 0; c < C::kChunks; ++c)
-          tma_load_3d(v_smem + st * C::kTileBytes + c * C::kChunkBytes, &tm_v, &v_full[st], c * 64, j * kBN, hk);
+        for (int c = 0; c < C::kChunks; ++c) {
+          uint8_t* dst = v_smem + st * C::kTileBytes + c * C::kChunkBytes;
+          if constexpr (RAGGED) tma_load_3d(dst, &tm_v, &v_full[st], c * 64, hk, kv_base + j * kBN);
+          else tma_load_3d(dst, &tm_v, &v_full[st], c * 64, j * kBN, hk);
+        }
       }
       __syncwarp();
       if (++st == kStages) { st = 0; ph ^= 1; }
@@ -210,7 +243,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     const int row = quarter * 32 + lane;  // query row inside the tile = TMEM lane
     const int qrow = q0 + row;
     const uint32_t lane_field = static_cast<uint32_t>(quarter * 32) << 16;
-    const int key_limit = p.causal ? min(p.skv - 1, qrow + off) : p.skv - 1;  // last key this row sees
+    const int key_limit = p.causal ? min(skv - 1, qrow + off) : skv - 1;  // last key this row sees
     float m_ref = 0.f, l_run = 0.f;
     for (int j = 0; j < nt; ++j) {
       const int sb = j & 1, pb = j & 1;
@@ -298,9 +331,10 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       mbar_wait(o_done, 0, p.status, kFaultMmaBarrier);
       tc_fence_after();
     }
-    const bool live = qrow < p.sq;
+    const bool live = qrow < sq;
     const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-    T* outp = reinterpret_cast<T*>(p.out) + (static_cast<size_t>(h) * p.sq + qrow) * D;
+    const size_t orow = RAGGED ? static_cast<size_t>(q_base + qrow) * p.hq + h : static_cast<size_t>(h) * sq + qrow;
+    T* outp = reinterpret_cast<T*>(p.out) + orow * D;
 #pragma unroll 1
     for (int c0 = 0; c0 < D; c0 += 32) {
       uint32_t o[32];
@@ -324,7 +358,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         }
       }
     }
-    if (live && p.lse) p.lse[static_cast<size_t>(h) * p.sq + qrow] = l_run > 0.f ? m_ref + fast_log2(l_run) : -INFINITY;
+    if (live && p.lse) p.lse[orow] = l_run > 0.f ? m_ref + fast_log2(l_run) : -INFINITY;
   }
 
   tc_fence_before();
@@ -346,7 +380,6 @@ int plan_prefill(const cb200_attn_prefill_args* a) {
   if (a->num_qo_heads % a->num_kv_heads) return CB200_ERR_BAD_ARG;
   if (a->head_dim != 64 && a->head_dim != 128) return CB200_ERR_UNSUPPORTED;
   if (a->dtype != CB200_F16 && a->dtype != CB200_BF16) return CB200_ERR_UNSUPPORTED;
-  if (a->causal && a->q_len > a->kv_len) return CB200_ERR_UNSUPPORTED;  // rows that see no key at all
   const long long ctas = static_cast<long long>(a->num_qo_heads) * ceil_div(a->q_len, fa::kBM);
   if (ctas >= (1LL << 31)) return CB200_ERR_UNSUPPORTED;
   return CB200_OK;
@@ -380,9 +413,60 @@ int launch_prefill(const cb200_attn_prefill_args* a, cudaStream_t stream) {
         !encode_tensor_map(&tm_v, dt, 3, const_cast<void*>(a->v), dk, sk, box, sw))
       return CB200_ERR_CUDA;
   }
-  auto kern = attn_prefill_kernel<T, D>;
+  auto kern = attn_prefill_kernel<T, D, false>;
   CB200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<D>::kSmemBytes));
   const unsigned grid = static_cast<unsigned>(p.hq) * p.q_tiles;
+  kern<<<grid, kThreads, Cfg<D>::kSmemBytes, stream>>>(tm_q, tm_k, tm_v, p);
+  CB200_CUDA_TRY(cudaGetLastError());
+  return CB200_OK;
+}
+
+int plan_prefill_ragged(const cb200_attn_prefill_ragged_args* a) {
+  if (!a) return CB200_ERR_BAD_ARG;
+  if (a->num_qo_heads <= 0 || a->num_kv_heads <= 0 || a->batch <= 0 || a->total_q <= 0 || a->total_kv <= 0)
+    return CB200_ERR_BAD_ARG;
+  if (a->num_qo_heads % a->num_kv_heads) return CB200_ERR_BAD_ARG;
+  if (a->head_dim != 64 && a->head_dim != 128) return CB200_ERR_UNSUPPORTED;
+  if (a->dtype != CB200_F16 && a->dtype != CB200_BF16) return CB200_ERR_UNSUPPORTED;
+  const long long ctas = static_cast<long long>(a->num_qo_heads) * (ceil_div(a->total_q, fa::kBM) + a->batch);
+  if (ctas >= (1LL << 31)) return CB200_ERR_UNSUPPORTED;
+  return CB200_OK;
+}
+
+template <typename T, int D>
+int launch_prefill_ragged(const cb200_attn_prefill_ragged_args* a, cudaStream_t stream) {
+  using namespace fa;
+  Params p{};
+  p.out = a->out;
+  p.lse = a->lse;
+  p.status = reinterpret_cast<int*>(a->workspace);
+  p.qo_indptr = a->qo_indptr;
+  p.kv_indptr = a->kv_indptr;
+  p.batch = a->batch;
+  p.hq = a->num_qo_heads;
+  p.hkv = a->num_kv_heads;
+  p.causal = a->causal ? 1 : 0;
+  p.scale_log2 = a->sm_scale * kLog2e;
+  const CUtensorMapDataType dt = a->dtype == CB200_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  CUtensorMap tm_q, tm_k, tm_v;
+  {
+    // a box is 64 columns of one head for 128 consecutive tokens: the same shared-memory image as the
+    // static layout's (64 columns x 128 rows)
+    uint32_t box[3] = {64u, 1u, 128u};
+    uint64_t dq[3] = {static_cast<uint64_t>(D), static_cast<uint64_t>(a->num_qo_heads), static_cast<uint64_t>(a->total_q)};
+    uint64_t sq[2] = {static_cast<uint64_t>(D) * 2, static_cast<uint64_t>(a->num_qo_heads) * D * 2};
+    uint64_t dk[3] = {static_cast<uint64_t>(D), static_cast<uint64_t>(a->num_kv_heads), static_cast<uint64_t>(a->total_kv)};
+    uint64_t sk[2] = {static_cast<uint64_t>(D) * 2, static_cast<uint64_t>(a->num_kv_heads) * D * 2};
+    const CUtensorMapSwizzle sw = CU_TENSOR_MAP_SWIZZLE_128B;
+    if (!encode_tensor_map(&tm_q, dt, 3, const_cast<void*>(a->q), dq, sq, box, sw) ||
+        !encode_tensor_map(&tm_k, dt, 3, const_cast<void*>(a->k), dk, sk, box, sw) ||
+        !encode_tensor_map(&tm_v, dt, 3, const_cast<void*>(a->v), dk, sk, box, sw))
+      return CB200_ERR_CUDA;
+  }
+  auto kern = attn_prefill_kernel<T, D, true>;
+  CB200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<D>::kSmemBytes));
+  // every request has at most ceil(q_len / 128) <= q_len / 128 + 1 query tiles
+  const unsigned grid = static_cast<unsigned>(p.hq) * static_cast<unsigned>(ceil_div(a->total_q, kBM) + a->batch);
   kern<<<grid, kThreads, Cfg<D>::kSmemBytes, stream>>>(tm_q, tm_k, tm_v, p);
   CB200_CUDA_TRY(cudaGetLastError());
   return CB200_OK;
@@ -409,4 +493,24 @@ extern "C" int cb200_attn_prefill(const cb200_attn_prefill_args* a, void* stream
   if (a->head_dim == 64)
     return f16 ? launch_prefill<__half, 64>(a, st) : launch_prefill<__nv_bfloat16, 64>(a, st);
   return f16 ? launch_prefill<__half, 128>(a, st) : launch_prefill<__nv_bfloat16, 128>(a, st);
+}
+
+extern "C" size_t cb200_attn_prefill_ragged_workspace_bytes(const cb200_attn_prefill_ragged_args* a) {
+  return cb200::plan_prefill_ragged(a) == CB200_OK ? cb200::kWsHeaderBytes : 0;
+}
+
+extern "C" int cb200_attn_prefill_ragged(const cb200_attn_prefill_ragged_args* a, void* stream) {
+  using namespace cb200;
+  const int rc = plan_prefill_ragged(a);
+  if (rc != CB200_OK) return rc;
+  if (!a->q || !a->k || !a->v || !a->out || !a->qo_indptr || !a->kv_indptr) return CB200_ERR_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(a->q) | reinterpret_cast<uintptr_t>(a->k) | reinterpret_cast<uintptr_t>(a->v) |
+       reinterpret_cast<uintptr_t>(a->out)) & 15)
+    return CB200_ERR_ALIGNMENT;
+  if (!a->workspace || a->workspace_bytes < kWsHeaderBytes) return CB200_ERR_WORKSPACE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const bool f16 = a->dtype == CB200_F16;
+  if (a->head_dim == 64)
+    return f16 ? launch_prefill_ragged<__half, 64>(a, st) : launch_prefill_ragged<__nv_bfloat16, 64>(a, st);
+  return f16 ? launch_prefill_ragged<__half, 128>(a, st) : launch_prefill_ragged<__nv_bfloat16, 128>(a, st);
 }

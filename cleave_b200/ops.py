@@ -164,6 +164,37 @@ def attention_prefill(q, k, v, sm_scale=None, *, causal=False, out=None, lse=Non
     return out
 
 
+def gqa_ragged_prefill(q, k, v, qo_indptr, kv_indptr, sm_scale, *, causal=True, out=None, lse=None):
+    """Ragged causal prefill (reference: python/cleave/dynamic/reference.py:244-278, builders/ragged.py).
+    ``q`` (total_q, HQ, D); ``k``, ``v`` (total_kv, HKV, D); ``qo_indptr`` / ``kv_indptr`` (batch + 1)
+    int32 on the device. Returns ``(out, lse)``: out (total_q, HQ, D), lse (total_q, HQ) fp32 base 2;
+    rows of requests without queries or keys are 0 / -inf."""
+    q, k, v = _cuda(q, "q"), _cuda(k, "k"), _cuda(v, "v")
+    total_q, hq, d = q.shape
+    total_kv, hkv, d2 = k.shape
+    if d2 != d or v.shape != k.shape or hq % hkv:
+        raise ValueError("shapes: q (total_q,HQ,D), k/v (total_kv,HKV,D), HQ a multiple of HKV")
+    if qo_indptr.dtype != torch.int32 or kv_indptr.dtype != torch.int32 or qo_indptr.numel() != kv_indptr.numel():
+        raise ValueError("qo_indptr and kv_indptr: int32 tensors of batch + 1 entries")
+    if out is None:
+        out = torch.zeros_like(q)
+    if lse is None:
+        lse = torch.full((total_q, hq), float("-inf"), dtype=torch.float32, device=q.device)
+    a = _lib.AttnPrefillRaggedArgs()
+    a.q, a.k, a.v, a.out, a.lse = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr()
+    a.qo_indptr, a.kv_indptr = _cuda(qo_indptr, "qo_indptr").data_ptr(), _cuda(kv_indptr, "kv_indptr").data_ptr()
+    a.batch, a.total_q, a.total_kv = qo_indptr.numel() - 1, total_q, total_kv
+    a.num_qo_heads, a.num_kv_heads, a.head_dim = hq, hkv, d
+    a.dtype, a.causal, a.sm_scale = _dtype_code(q), int(bool(causal)), float(sm_scale)
+    need = _lib.lib().cb200_attn_prefill_ragged_workspace_bytes(C.byref(a))
+    if need == 0:
+        _lib.check(_lib.lib().cb200_attn_prefill_ragged(C.byref(a), _stream()))  # reports why the plan is refused
+    ws = workspace("attn_prefill", need, q.device)
+    a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+    _lib.check(_lib.lib().cb200_attn_prefill_ragged(C.byref(a), _stream()))
+    return out, lse
+
+
 def gqa_paged_decode_static_scratch(q, k_cache, v_cache, kv_indptr, kv_indices, kv_last_page_len, sm_scale,
                                     *, out, lse, max_ctas=0):
     """Paged decode for hosts that may not allocate device memory (a server that gave this

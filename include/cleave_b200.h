@@ -207,12 +207,41 @@ typedef struct {
   int32_t kv_len;
   int32_t head_dim; /* 64 or 128 */
   int32_t dtype;    /* cb200_dtype */
-  int32_t causal;   /* 0 = no mask, 1 = end-aligned causal mask (needs q_len <= kv_len) */
+  int32_t causal;   /* 0 = no mask, 1 = end-aligned causal mask (a row left without keys gives 0 and lse -inf) */
   float sm_scale;
 } cb200_attn_prefill_args;
 
 size_t cb200_attn_prefill_workspace_bytes(const cb200_attn_prefill_args* a);
 int cb200_attn_prefill(const cb200_attn_prefill_args* a, void* stream);
+
+/* Ragged causal prefill: one (query range, key range) per request in token-major tensors.
+ * Replaces gqa_ragged_prefill_causal_* (python/cleave/dynamic/paging/builders/ragged.py); argument
+ * order and meaning follow python/cleave/dynamic/reference.py:244-278. A request with no query rows
+ * or no keys leaves its rows of `out` zero and of `lse` -inf, as the reference's preallocation does;
+ * so does a row that the mask leaves without keys. */
+typedef struct {
+  const void* q;             /* (total_q, num_qo_heads, head_dim) */
+  const void* k;             /* (total_kv, num_kv_heads, head_dim) */
+  const void* v;             /* (total_kv, num_kv_heads, head_dim) */
+  const int32_t* qo_indptr;  /* (batch + 1) device */
+  const int32_t* kv_indptr;  /* (batch + 1) device */
+  void* out;                 /* (total_q, num_qo_heads, head_dim) */
+  float* lse;                /* (total_q, num_qo_heads) base 2, may be NULL */
+  void* workspace;
+  size_t workspace_bytes;
+  int32_t batch;
+  int32_t total_q;
+  int32_t total_kv;
+  int32_t num_qo_heads;
+  int32_t num_kv_heads;
+  int32_t head_dim; /* 64 or 128 */
+  int32_t dtype;    /* cb200_dtype */
+  int32_t causal;   /* 1 = end-aligned causal mask per request */
+  float sm_scale;
+} cb200_attn_prefill_ragged_args;
+
+size_t cb200_attn_prefill_ragged_workspace_bytes(const cb200_attn_prefill_ragged_args* a);
+int cb200_attn_prefill_ragged(const cb200_attn_prefill_ragged_args* a, void* stream);
 
 /* ------------------------------------------------------------------------------------------
  * Decode attention for callers that cannot allocate device memory. (No counterpart in the

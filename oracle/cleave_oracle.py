@@ -167,6 +167,26 @@ def attention_masked(q, k, v, scale: float, causal: bool, dtype: str = "bf16"):
     return round_to(np.einsum("hqk,hkd->hqd", w, vv, optimize=True), dtype), l
 
 
+def gqa_ragged_prefill(q, k, v, qo_indptr, kv_indptr, scale: float, dtype: str = "bf16", causal: bool = True):
+    """Ragged causal prefill (python/cleave/dynamic/reference.py:244-278): per request r, rows
+    ``qo_indptr[r]:qo_indptr[r+1]`` of q (total_q, HQ, D) attend keys ``kv_indptr[r]:kv_indptr[r+1]`` of
+    k, v (total_kv, HKV, D) under the end-aligned causal mask; requests without queries or keys keep the
+    preallocated 0 / -inf. Returns (out (total_q, HQ, D), lse (total_q, HQ))."""
+    q, k, v = f32(q), f32(k), f32(v)
+    total_q, hq, d = q.shape
+    out = np.zeros((total_q, hq, d), dtype=np.float32)
+    lse = np.full((total_q, hq), NEG_INF, dtype=np.float32)
+    for r in range(len(qo_indptr) - 1):
+        qs, qe, ks, ke = int(qo_indptr[r]), int(qo_indptr[r + 1]), int(kv_indptr[r]), int(kv_indptr[r + 1])
+        if qe <= qs or ke <= ks:
+            continue
+        o, l = attention_masked(q[qs:qe].transpose(1, 0, 2), k[ks:ke].transpose(1, 0, 2), v[ks:ke].transpose(1, 0, 2),
+                                scale, causal, dtype)
+        out[qs:qe] = o.transpose(1, 0, 2)
+        lse[qs:qe] = l.T
+    return out, lse
+
+
 def mla_decode(q, kv, q_pe, k_pe, scale: float, dtype: str = "bf16") -> np.ndarray:
     """Absorbed-latent MLA decode: ``S = (Q KV^T + Qpe Kpe^T) * scale``; ``O = softmax(S) KV``.
     q (B,H,D), kv (B,SKV,D), q_pe (B,H,PE), k_pe (B,SKV,PE)."""

@@ -75,6 +75,28 @@ def test_large_logits_take_the_rescale_path():
     assert_lse_close(host(lse), want_lse)
 
 
+@pytest.mark.parametrize("hq,hkv,d,dt", [(8, 2, 128, "bf16"), (4, 4, 64, "f16"), (16, 1, 64, "bf16")])
+def test_ragged_causal_prefill_vs_oracle(hq, hkv, d, dt):
+    """Reference: python/cleave/dynamic/reference.py:244-278. Requests without queries, without keys,
+    with more queries than keys (rows the mask leaves empty), and with several query tiles."""
+    q_lens = [100, 0, 128, 5, 257, 30, 1]
+    kv_lens = [300, 50, 128, 0, 1000, 20, 129]
+    rng = np.random.default_rng(hq * 10 + d)
+    tq, tk = sum(q_lens), sum(kv_lens)
+    q = cases.round_to(rng.standard_normal((tq, hq, d), dtype=np.float32), dt)
+    k = cases.round_to(rng.standard_normal((tk, hkv, d), dtype=np.float32), dt)
+    v = cases.round_to(rng.standard_normal((tk, hkv, d), dtype=np.float32), dt)
+    qo = np.concatenate([[0], np.cumsum(q_lens)]).astype(np.int32)
+    kv = np.concatenate([[0], np.cumsum(kv_lens)]).astype(np.int32)
+    scale = d ** -0.5
+    out, lse = _ops().gqa_ragged_prefill(dev(q, dt), dev(k, dt), dev(v, dt), torch.from_numpy(qo).cuda(),
+                                         torch.from_numpy(kv).cuda(), scale)
+    _check_ws()
+    want, want_lse = orc.gqa_ragged_prefill(q, k, v, qo, kv, scale, dt)
+    assert_close(host(out), want)
+    assert_lse_close(host(lse), want_lse)
+
+
 def test_repeat_launches_are_bit_identical():
     inp = cases.attention_inputs(9, 8, 2, 300, 517, 128, "f16")
     q, k, v = (dev(inp[n], "f16") for n in ("q", "k", "v"))
@@ -113,7 +135,6 @@ def test_prefill_bad_arguments():
     k = torch.zeros(2, 64, 96, dtype=torch.float16, device="cuda")
     with pytest.raises(Cb200Error):
         ops.attention_prefill(q, k, k)  # head_dim 96
-    q = torch.zeros(2, 64, 64, dtype=torch.float16, device="cuda")
-    k = torch.zeros(2, 32, 64, dtype=torch.float16, device="cuda")
-    with pytest.raises(Cb200Error):
-        ops.attention_prefill(q, k, k, causal=True)  # more query rows than keys under the causal mask
+    q = torch.zeros(2, 64, 64, dtype=torch.float32, device="cuda")
+    with pytest.raises((Cb200Error, ValueError, TypeError)):
+        ops.attention_prefill(q, q, q)  # fp32 inputs

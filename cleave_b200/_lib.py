@@ -73,6 +73,7 @@ class AttnPrefillArgs(C.Structure):
 class AttnPrefillRaggedArgs(C.Structure):
     _fields_ = [
         ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("qo_indptr", C.c_void_p), ("kv_indptr", C.c_void_p),
+        ("kv_indices", C.c_void_p),
         ("out", C.c_void_p), ("lse", C.c_void_p), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("batch", C.c_int32), ("total_q", C.c_int32), ("total_kv", C.c_int32),
         ("num_qo_heads", C.c_int32), ("num_kv_heads", C.c_int32), ("head_dim", C.c_int32), ("dtype", C.c_int32),

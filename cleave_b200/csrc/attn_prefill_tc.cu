@@ -26,7 +26,8 @@ namespace cb200 {
 namespace fa {
 
 constexpr int kBM = 128, kBN = 128;
-constexpr int kThreads = 224;
+constexpr int kThreads = 224;       // static and ragged layouts
+constexpr int kThreadsPaged = 352;  // + four gather warps
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.f;  // log2 units
 // TMEM columns: S0 | S1 | O | P0 | P1
@@ -46,8 +47,12 @@ struct Params {
   float* lse;
   int* status;
   const int* qo_indptr;  // ragged: (batch + 1) query-row offsets
-  const int* kv_indptr;  // ragged: (batch + 1) key offsets
-  int batch;             // ragged: requests
+  const int* kv_indptr;  // ragged: (batch + 1) key offsets; paged: offsets into kv_indices
+  const int* kv_indices; // paged: one page id per token (page size 1)
+  const void* k_cache;   // paged: (num_pages, 1, HKV, D)
+  const void* v_cache;
+  int num_pages;
+  int batch;             // ragged / paged: requests
   int hq, hkv, sq, skv, q_tiles, causal;
   float scale_log2;
 };
@@ -55,12 +60,16 @@ struct Params {
 // RAGGED: q (total_q, HQ, D), k / v (total_kv, HKV, D) with one (query range, key range) per request;
 // a CTA finds its (request, query tile) by scanning the query offsets (the device-side work list of
 // the reference's IndptrTileScan, python/cleave/dynamic/paging/stages.py:288-328).
-template <typename T, int D, bool RAGGED>
-__global__ void __launch_bounds__(kThreads, 1)
+// MODE 2 (paged): q as in the ragged layout; K and V rows are gathered from page-size-1 caches through
+// kv_indices by four extra warps (one token row per thread, 16-byte cp.async into the swizzled tile;
+// a thread's arrival on the full barrier fires when its copies have landed).
+template <typename T, int D, int MODE>
+__global__ void __launch_bounds__(MODE == 2 ? kThreadsPaged : kThreads, 1)
 attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                     const __grid_constant__ CUtensorMap tm_v, const Params p) {
   using C = Cfg<D>;
   constexpr int kStages = C::kStages;
+  constexpr bool RAGGED = MODE != 0;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* q_smem = smem;
@@ -113,9 +122,9 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(&k_full[s], 1);
+      mbar_init(&k_full[s], MODE == 2 ? 128 : 1);
       mbar_init(&k_empty[s], 1);
-      mbar_init(&v_full[s], 1);
+      mbar_init(&v_full[s], MODE == 2 ? 128 : 1);
       mbar_init(&v_empty[s], 1);
     }
     for (int s = 0; s < 2; ++s) {
@@ -152,7 +161,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     }
     __syncwarp();
     int st = 0, ph = 0;
-    for (int j = 0; j < nt; ++j) {
+    for (int j = 0; MODE != 2 && j < nt; ++j) {
       mbar_wait(&k_empty[st], ph ^ 1, p.status, kFaultEmptyBarrier);
       if (lane == 0) {
         mbar_arrive_expect_tx(&k_full[st], C::kTileBytes);
@@ -169,7 +178,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   } else if (warp == 6) {
     // ================================================================ TMA producer: V tiles
     int st = 0, ph = 0;
-    for (int j = 0; j < nt; ++j) {
+    for (int j = 0; MODE != 2 && j < nt; ++j) {
       mbar_wait(&v_empty[st], ph ^ 1, p.status, kFaultEmptyBarrier);
       if (lane == 0) {
         mbar_arrive_expect_tx(&v_full[st], C::kTileBytes);
@@ -182,6 +191,40 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       }
       __syncwarp();
       if (++st == kStages) { st = 0; ph ^= 1; }
+    }
+  } else if (warp >= 7) {
+    // ================================================================ paged: K / V row gather
+    if constexpr (MODE == 2) {
+      const int row = tid - 7 * 32;  // token row of the tile, 0..127
+      const T* kc = reinterpret_cast<const T*>(p.k_cache);
+      const T* vc = reinterpret_cast<const T*>(p.v_cache);
+      auto page_of = [&](int j) {
+        const int tok = min(j * kBN + row, skv - 1);  // rows past the end repeat the last token; they are masked
+        return __ldg(p.kv_indices + kv_base + tok);
+      };
+      int pg = nt > 0 ? page_of(0) : 0;
+      int st = 0, ph = 0;
+      for (int j = 0; j < nt; ++j) {
+        const long long page = min(max(pg, 0), p.num_pages - 1);
+        if (j + 1 < nt) pg = page_of(j + 1);  // one tile ahead: the index latency stays off the critical path
+        const long long src = (page * p.hkv + hk) * D;
+        const uint32_t kdst = smem_u32(k_smem + st * C::kTileBytes), vdst = smem_u32(v_smem + st * C::kTileBytes);
+        mbar_wait(&k_empty[st], ph ^ 1, p.status, kFaultEmptyBarrier);
+#pragma unroll
+        for (int c = 0; c < D / 8; ++c) {
+          const uint32_t o = (c >> 3) * C::kChunkBytes + row * 128 + (((c & 7) ^ (row & 7)) << 4);
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(kdst + o), "l"(kc + src + c * 8) : "memory");
+        }
+        asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&k_full[st])) : "memory");
+        mbar_wait(&v_empty[st], ph ^ 1, p.status, kFaultEmptyBarrier);
+#pragma unroll
+        for (int c = 0; c < D / 8; ++c) {
+          const uint32_t o = (c >> 3) * C::kChunkBytes + row * 128 + (((c & 7) ^ (row & 7)) << 4);
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(vdst + o), "l"(vc + src + c * 8) : "memory");
+        }
+        asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&v_full[st])) : "memory");
+        if (++st == kStages) { st = 0; ph ^= 1; }
+      }
     }
   } else if (warp == 1) {
     // ================================================================ MMA issuer
@@ -413,7 +456,7 @@ int launch_prefill(const cb200_attn_prefill_args* a, cudaStream_t stream) {
         !encode_tensor_map(&tm_v, dt, 3, const_cast<void*>(a->v), dk, sk, box, sw))
       return CB200_ERR_CUDA;
   }
-  auto kern = attn_prefill_kernel<T, D, false>;
+  auto kern = attn_prefill_kernel<T, D, 0>;
   CB200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<D>::kSmemBytes));
   const unsigned grid = static_cast<unsigned>(p.hq) * p.q_tiles;
   kern<<<grid, kThreads, Cfg<D>::kSmemBytes, stream>>>(tm_q, tm_k, tm_v, p);
@@ -442,6 +485,10 @@ int launch_prefill_ragged(const cb200_attn_prefill_ragged_args* a, cudaStream_t 
   p.status = reinterpret_cast<int*>(a->workspace);
   p.qo_indptr = a->qo_indptr;
   p.kv_indptr = a->kv_indptr;
+  p.kv_indices = a->kv_indices;
+  p.k_cache = a->k;
+  p.v_cache = a->v;
+  p.num_pages = a->total_kv;
   p.batch = a->batch;
   p.hq = a->num_qo_heads;
   p.hkv = a->num_kv_heads;
@@ -463,11 +510,17 @@ int launch_prefill_ragged(const cb200_attn_prefill_ragged_args* a, cudaStream_t 
         !encode_tensor_map(&tm_v, dt, 3, const_cast<void*>(a->v), dk, sk, box, sw))
       return CB200_ERR_CUDA;
   }
-  auto kern = attn_prefill_kernel<T, D, true>;
-  CB200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<D>::kSmemBytes));
   // every request has at most ceil(q_len / 128) <= q_len / 128 + 1 query tiles
   const unsigned grid = static_cast<unsigned>(p.hq) * static_cast<unsigned>(ceil_div(a->total_q, kBM) + a->batch);
-  kern<<<grid, kThreads, Cfg<D>::kSmemBytes, stream>>>(tm_q, tm_k, tm_v, p);
+  if (a->kv_indices) {
+    auto kern = attn_prefill_kernel<T, D, 2>;
+    CB200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<D>::kSmemBytes));
+    kern<<<grid, kThreadsPaged, Cfg<D>::kSmemBytes, stream>>>(tm_q, tm_k, tm_v, p);
+  } else {
+    auto kern = attn_prefill_kernel<T, D, 1>;
+    CB200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<D>::kSmemBytes));
+    kern<<<grid, kThreads, Cfg<D>::kSmemBytes, stream>>>(tm_q, tm_k, tm_v, p);
+  }
   CB200_CUDA_TRY(cudaGetLastError());
   return CB200_OK;
 }

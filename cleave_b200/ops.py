@@ -164,7 +164,7 @@ def attention_prefill(q, k, v, sm_scale=None, *, causal=False, out=None, lse=Non
     return out
 
 
-def gqa_ragged_prefill(q, k, v, qo_indptr, kv_indptr, sm_scale, *, causal=True, out=None, lse=None):
+def gqa_ragged_prefill(q, k, v, qo_indptr, kv_indptr, sm_scale, *, causal=True, out=None, lse=None, kv_indices=None):
     """Ragged causal prefill (reference: python/cleave/dynamic/reference.py:244-278, builders/ragged.py).
     ``q`` (total_q, HQ, D); ``k``, ``v`` (total_kv, HKV, D); ``qo_indptr`` / ``kv_indptr`` (batch + 1)
     int32 on the device. Returns ``(out, lse)``: out (total_q, HQ, D), lse (total_q, HQ) fp32 base 2;
@@ -183,6 +183,7 @@ def gqa_ragged_prefill(q, k, v, qo_indptr, kv_indptr, sm_scale, *, causal=True, 
     a = _lib.AttnPrefillRaggedArgs()
     a.q, a.k, a.v, a.out, a.lse = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr()
     a.qo_indptr, a.kv_indptr = _cuda(qo_indptr, "qo_indptr").data_ptr(), _cuda(kv_indptr, "kv_indptr").data_ptr()
+    a.kv_indices = kv_indices.data_ptr() if kv_indices is not None else None
     a.batch, a.total_q, a.total_kv = qo_indptr.numel() - 1, total_q, total_kv
     a.num_qo_heads, a.num_kv_heads, a.head_dim = hq, hkv, d
     a.dtype, a.causal, a.sm_scale = _dtype_code(q), int(bool(causal)), float(sm_scale)
@@ -193,6 +194,20 @@ def gqa_ragged_prefill(q, k, v, qo_indptr, kv_indptr, sm_scale, *, causal=True, 
     a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
     _lib.check(_lib.lib().cb200_attn_prefill_ragged(C.byref(a), _stream()))
     return out, lse
+
+
+def gqa_paged_prefill(q, k_cache, v_cache, qo_indptr, kv_indptr, kv_indices, sm_scale, *, causal=True, out=None,
+                      lse=None):
+    """Paged causal prefill over page-size-1 caches (reference: python/cleave/dynamic/reference.py:204-241,
+    builders/prefill.py). ``q`` (total_q, HQ, D); caches (num_pages, 1, HKV, D); request r attends the
+    tokens ``kv_indices[kv_indptr[r] : kv_indptr[r+1]]``. Returns ``(out, lse)`` as gqa_ragged_prefill."""
+    k_cache, v_cache = _cuda(k_cache, "k_cache"), _cuda(v_cache, "v_cache")
+    if k_cache.dim() != 4 or k_cache.shape[1] != 1 or v_cache.shape != k_cache.shape:
+        raise ValueError("caches: (num_pages, 1, HKV, D), one token per page")
+    if kv_indices.dtype != torch.int32:
+        raise ValueError("kv_indices: int32")
+    return gqa_ragged_prefill(q, k_cache[:, 0], v_cache[:, 0], qo_indptr, kv_indptr, sm_scale, causal=causal, out=out,
+                              lse=lse, kv_indices=_cuda(kv_indices, "kv_indices"))
 
 
 def gqa_paged_decode_static_scratch(q, k_cache, v_cache, kv_indptr, kv_indices, kv_last_page_len, sm_scale,

@@ -214,24 +214,26 @@ typedef struct {
 size_t cb200_attn_prefill_workspace_bytes(const cb200_attn_prefill_args* a);
 int cb200_attn_prefill(const cb200_attn_prefill_args* a, void* stream);
 
-/* Ragged causal prefill: one (query range, key range) per request in token-major tensors.
- * Replaces gqa_ragged_prefill_causal_* (python/cleave/dynamic/paging/builders/ragged.py); argument
- * order and meaning follow python/cleave/dynamic/reference.py:244-278. A request with no query rows
- * or no keys leaves its rows of `out` zero and of `lse` -inf, as the reference's preallocation does;
- * so does a row that the mask leaves without keys. */
+/* Ragged and paged causal prefill: one (query range, key range) per request, token-major tensors.
+ * Replaces gqa_ragged_prefill_causal_* (python/cleave/dynamic/paging/builders/ragged.py) and, with
+ * kv_indices set, gqa_paged_prefill_causal_* (builders/prefill.py); argument order and meaning follow
+ * python/cleave/dynamic/reference.py:204-278. A request with no query rows or no keys leaves its rows
+ * of `out` zero and of `lse` -inf, as the reference's preallocation does; so does a row that the mask
+ * leaves without keys. */
 typedef struct {
   const void* q;             /* (total_q, num_qo_heads, head_dim) */
-  const void* k;             /* (total_kv, num_kv_heads, head_dim) */
-  const void* v;             /* (total_kv, num_kv_heads, head_dim) */
+  const void* k;             /* ragged: (total_kv, num_kv_heads, head_dim); paged: cache (num_pages, 1, num_kv_heads, head_dim) */
+  const void* v;             /* same shape as k */
   const int32_t* qo_indptr;  /* (batch + 1) device */
-  const int32_t* kv_indptr;  /* (batch + 1) device */
+  const int32_t* kv_indptr;  /* (batch + 1) device: key offsets (ragged) or offsets into kv_indices (paged) */
+  const int32_t* kv_indices; /* NULL = ragged; paged: page id of every key (one token per page), device */
   void* out;                 /* (total_q, num_qo_heads, head_dim) */
   float* lse;                /* (total_q, num_qo_heads) base 2, may be NULL */
   void* workspace;
   size_t workspace_bytes;
   int32_t batch;
   int32_t total_q;
-  int32_t total_kv;
+  int32_t total_kv;          /* ragged: rows of k; paged: num_pages */
   int32_t num_qo_heads;
   int32_t num_kv_heads;
   int32_t head_dim; /* 64 or 128 */

@@ -187,6 +187,25 @@ def gqa_ragged_prefill(q, k, v, qo_indptr, kv_indptr, scale: float, dtype: str =
     return out, lse
 
 
+def gqa_paged_prefill(q, k_cache, v_cache, qo_indptr, kv_indptr, kv_indices, scale: float, dtype: str = "bf16"):
+    """Paged causal prefill over page-size-1 caches (python/cleave/dynamic/reference.py:204-241): request r
+    attends the rows ``kv_indices[kv_indptr[r]:kv_indptr[r+1]]`` of caches (num_pages, 1, HKV, D)."""
+    q, kc, vc = f32(q), f32(k_cache), f32(v_cache)
+    total_q, hq, d = q.shape
+    out = np.zeros((total_q, hq, d), dtype=np.float32)
+    lse = np.full((total_q, hq), NEG_INF, dtype=np.float32)
+    for r in range(len(qo_indptr) - 1):
+        qs, qe, ks, ke = int(qo_indptr[r]), int(qo_indptr[r + 1]), int(kv_indptr[r]), int(kv_indptr[r + 1])
+        if qe <= qs or ke <= ks:
+            continue
+        pages = np.asarray(kv_indices[ks:ke], dtype=np.int64)
+        o, l = attention_masked(q[qs:qe].transpose(1, 0, 2), kc[pages, 0].transpose(1, 0, 2),
+                                vc[pages, 0].transpose(1, 0, 2), scale, True, dtype)
+        out[qs:qe] = o.transpose(1, 0, 2)
+        lse[qs:qe] = l.T
+    return out, lse
+
+
 def mla_decode(q, kv, q_pe, k_pe, scale: float, dtype: str = "bf16") -> np.ndarray:
     """Absorbed-latent MLA decode: ``S = (Q KV^T + Qpe Kpe^T) * scale``; ``O = softmax(S) KV``.
     q (B,H,D), kv (B,SKV,D), q_pe (B,H,PE), k_pe (B,SKV,PE)."""

@@ -72,6 +72,26 @@ def mla_paged_inputs(seed, kv_lens, h, ckv, kpe, dtype, scale):
             "kv_indptr": kv_indptr, "kv_indices": kv_indices, "sm_scale": float(scale)}
 
 
+def gqa_prefill_inputs(seed, q_lens, kv_lens, hq, hkv, d, dtype, paged):
+    """Ragged (``paged=False``) or page-size-1 paged causal prefill, argument for argument as
+    python/cleave/dynamic/reference.py:204-258 lays them out."""
+    rng = np.random.default_rng(seed)
+    tq, tk = sum(q_lens), sum(kv_lens)
+    out = {"q": _randn(rng, (tq, hq, d), dtype),
+           "qo_indptr": np.concatenate([[0], np.cumsum(q_lens)]).astype(np.int32),
+           "kv_indptr": np.concatenate([[0], np.cumsum(kv_lens)]).astype(np.int32),
+           "sm_scale": float(d) ** -0.5}
+    if paged:
+        num_pages = tk + 5
+        out["k_cache"] = _randn(rng, (num_pages, 1, hkv, d), dtype)
+        out["v_cache"] = _randn(rng, (num_pages, 1, hkv, d), dtype)
+        out["kv_indices"] = rng.permutation(num_pages)[:tk].astype(np.int32)
+    else:
+        out["k"] = _randn(rng, (tk, hkv, d), dtype)
+        out["v"] = _randn(rng, (tk, hkv, d), dtype)
+    return out
+
+
 MLA_SM_SCALE = 0.1352337747812271
 
 # name -> (family, builder kwargs)
@@ -105,6 +125,14 @@ CASES = {
                                                        page_size=1, dtype="bf16")),
     "gqa_paged_ps16_f16": ("gqa_paged", dict(seed=34, kv_lens=[100, 33, 16, 250], hq=32, hkv=8, d=128,
                                              page_size=16, dtype="f16")),
+    # unsplit static attention with many query rows (demo/{mha,gqa}_prefill.py at test size)
+    "gqa_prefill_d64_f16": ("attention", dict(seed=14, hq=8, hkv=2, sq=130, skv=130, d=64, dtype="f16")),
+    "mha_prefill_d128_bf16": ("attention", dict(seed=15, hq=2, hkv=2, sq=200, skv=333, d=128, dtype="bf16")),
+    # ragged / paged causal prefill (requests without queries, without keys, with several query tiles)
+    "gqa_ragged_prefill_bf16": ("gqa_prefill", dict(seed=50, q_lens=[100, 0, 128, 5, 257], kv_lens=[300, 50, 128, 0, 600],
+                                                    hq=8, hkv=2, d=128, dtype="bf16", paged=False)),
+    "gqa_paged_prefill_bf16": ("gqa_prefill", dict(seed=51, q_lens=[100, 0, 128, 5, 257], kv_lens=[300, 50, 128, 0, 600],
+                                                   hq=8, hkv=2, d=64, dtype="bf16", paged=True)),
     # paged MLA decode
     "mla_paged_bf16": ("mla_paged", dict(seed=40, kv_lens=[5, 0, 7, 300], h=16, ckv=512, kpe=64,
                                          dtype="bf16", scale=MLA_SM_SCALE)),
@@ -126,6 +154,9 @@ def build(name):
                                                     kv_lens=kw["kv_lens"])
     if family == "mla_paged":
         return family, mla_paged_inputs(**kw), dict(extra, dtype=kw["dtype"], kv_lens=kw["kv_lens"])
+    if family == "gqa_prefill":
+        return family, gqa_prefill_inputs(**kw), dict(extra, dtype=kw["dtype"], q_lens=kw["q_lens"],
+                                                      kv_lens=kw["kv_lens"], paged=kw["paged"])
     raise KeyError(family)
 
 

@@ -113,6 +113,20 @@ def main(ref_root):
             res = ref(_t(inp["q_nope"], dt), _t(inp["q_pe"], dt), _t(inp["ckv_cache"], dt),
                       _t(inp["kpe_cache"], dt), _t(inp["kv_indptr"], dt), _t(inp["kv_indices"], dt),
                       inp["sm_scale"])
+        elif family == "gqa_prefill":
+            tq, hq, d = inp["q"].shape
+            if opt["paged"]:
+                num_pages, _, hkv, _ = inp["k_cache"].shape
+                dims = (hq, hkv, d, num_pages, inp["kv_indices"].size, tq)
+                ref = dyn.gqa_paged_prefill_reference(dims, opt["q_lens"], opt["kv_lens"])
+                res = ref(_t(inp["q"], dt), _t(inp["k_cache"], dt), _t(inp["v_cache"], dt), _t(inp["qo_indptr"], dt),
+                          _t(inp["kv_indptr"], dt), _t(inp["kv_indices"], dt), inp["sm_scale"])
+            else:
+                tk, hkv, _ = inp["k"].shape
+                dims = (hq, hkv, d, tq, tk)
+                ref = dyn.gqa_ragged_prefill_reference(dims, opt["q_lens"], opt["kv_lens"])
+                res = ref(_t(inp["q"], dt), _t(inp["k"], dt), _t(inp["v"], dt), _t(inp["qo_indptr"], dt),
+                          _t(inp["kv_indptr"], dt), inp["sm_scale"])
         else:
             raise KeyError(family)
         for i, r in enumerate(res):

@@ -38,7 +38,7 @@ def test_paged_decode_matches_reference_golden(name):
     assert_lse_close(lse, want_lse)
 
 
-@pytest.mark.parametrize("name", [n for n, c in cases.CASES.items() if c[0] == "attention"])
+@pytest.mark.parametrize("name", [n for n, c in cases.CASES.items() if c[0] == "attention" and c[1]["sq"] == 1])
 def test_static_decode_matches_reference_golden(name):
     _, inp, opt = cases.build(name)
     dt = opt["dtype"]

@@ -24,6 +24,36 @@ def _check_ws():
     ops.check_workspace(ops.workspace("attn_prefill", 0, "cuda"))
 
 
+GOLDEN = cases.load_golden()
+
+
+@pytest.mark.parametrize("name", [n for n, c in cases.CASES.items() if c[0] == "attention" and c[1]["sq"] > 1])
+def test_static_prefill_matches_reference_golden(name):
+    """Golden outputs of the reference's own torch path (cleave.trace(...).reference) on the seeded case."""
+    _, inp, opt = cases.build(name)
+    dt = opt["dtype"]
+    got = _ops().attention_prefill(dev(inp["q"], dt), dev(inp["k"], dt), dev(inp["v"], dt))
+    _check_ws()
+    assert_close(host(got), GOLDEN[name][0])
+
+
+@pytest.mark.parametrize("name", [n for n, c in cases.CASES.items() if c[0] == "gqa_prefill"])
+def test_dynamic_prefill_matches_reference_golden(name):
+    """Golden outputs of python/cleave/dynamic/reference.py's ragged / paged prefill definitions."""
+    _, inp, opt = cases.build(name)
+    dt = opt["dtype"]
+    qo, kv = torch.from_numpy(inp["qo_indptr"]).cuda(), torch.from_numpy(inp["kv_indptr"]).cuda()
+    if opt["paged"]:
+        out, lse = _ops().gqa_paged_prefill(dev(inp["q"], dt), dev(inp["k_cache"], dt), dev(inp["v_cache"], dt), qo, kv,
+                                            torch.from_numpy(inp["kv_indices"]).cuda(), inp["sm_scale"])
+    else:
+        out, lse = _ops().gqa_ragged_prefill(dev(inp["q"], dt), dev(inp["k"], dt), dev(inp["v"], dt), qo, kv,
+                                             inp["sm_scale"])
+    _check_ws()
+    assert_close(host(out), GOLDEN[name][0])
+    assert_lse_close(host(lse), GOLDEN[name][1])
+
+
 SHAPES = [  # hq, hkv, sq, skv, d
     (4, 4, 256, 256, 64),     # MHA, whole tiles
     (8, 2, 300, 517, 128),    # GQA, ragged in both lengths

@@ -127,7 +127,12 @@ class B200Kernel:
         elif f == "swiglu":
             ops.swiglu(ins[0], ins[1], ins[2], split_k=split, out=outs[0].view(ins[0].shape[0], -1), max_ctas=mc)
         elif f == "attention_decode":
-            ops.attention_decode(ins[0], ins[1], ins[2], s.attrs.get("scale"), out=outs[0], max_ctas=mc)
+            # the same static attention family: few query rows stream KV through the split-KV decode kernel,
+            # a query tile's worth of rows (the "prefill" shapes) runs QK^T and PV on tcgen05
+            if s.dims["SQ"] >= 64 and s.dims["D"] in (64, 128) and split <= 1:
+                ops.attention_prefill(ins[0], ins[1], ins[2], s.attrs.get("scale"), out=outs[0])
+            else:
+                ops.attention_decode(ins[0], ins[1], ins[2], s.attrs.get("scale"), out=outs[0], max_ctas=mc)
         elif f == "mla_decode":
             ops.mla_decode(ins[0], ins[1], ins[2], ins[3], float(s.attrs["scale"]), out=outs[0], max_ctas=mc)
         elif f == "gqa_paged_decode":

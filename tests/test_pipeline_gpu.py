@@ -84,6 +84,10 @@ def test_compile_rmsnorm_gamma_swiglu_attention_and_mla():
     q, kk, v = rnd(32, 1, 128), rnd(8, 777, 128), rnd(8, 777, 128)
     torch.testing.assert_close(k3(q, kk, v).float(), R.attention(q, kk, v), rtol=2e-2, atol=2e-2)
     assert set(k3.report.variants()) == {"solo"}
+    # the same program at a prefill shape (demo/gqa_prefill.py) runs on the tcgen05 attention kernel
+    k3p = cleave.compile(att, shapes=dict(HQ=8, HKV=2, SQ=300, SKV=300, D=64), eval=_fast(), cache_kernels=False)
+    q, kk, v = rnd(8, 300, 64), rnd(2, 300, 64), rnd(2, 300, 64)
+    torch.testing.assert_close(k3p(q, kk, v).float(), R.attention(q, kk, v), rtol=2e-2, atol=2e-2)
     k4 = cleave.compile(mla, shapes=dict(B=2, H=32, SKV=300, D=512, PE=64), dtype=cl.bf16, eval=_fast(),
                         cache_kernels=False)
     bf = torch.bfloat16

@@ -80,14 +80,25 @@ def test_swiglu_vs_oracle(m, n, k, split_k):
     ("matmul", 2048, 4864, 1032, "bf16"),  # 17 K blocks: the stage ring wraps inside a tile
     ("swiglu", 2100, 2504, 136, "bf16"),
     ("swiglu", 1024, 4736, 520, "f16"),
+    ("rmsnorm_matmul", 2048, 4864, 1032, "f16"),
+    ("rmsnorm_gamma", 3000, 3336, 200, "bf16"),
+    ("rmsnorm_gamma", 1024, 9728, 712, "f16"),
 ])
 def test_large_gemms_on_cta_pairs(family, m, n, k, dt):
     """Shapes with at least one 256 x 256 tile per CTA pair take the cta_group::2 kernel."""
-    inp = cases.gemm_inputs(m + k, m, n, k, dt, n_w=2 if family == "swiglu" else 1)
-    got = _run(family, inp, {"dtype": dt})
-    want = orc.swiglu(inp["x"], inp["w0"], inp["w1"], dt) if family == "swiglu" else orc.matmul(inp["x"], inp["w0"], dt)
+    gamma = family == "rmsnorm_gamma"
+    fam = "rmsnorm_matmul" if gamma else family
+    inp = cases.gemm_inputs(m + k, m, n, k, dt, n_w=2 if family == "swiglu" else 1, gamma=gamma)
+    opt = {"dtype": dt, "eps": 1e-6}
+    got = _run(fam, inp, opt)
+    if family == "swiglu":
+        want = orc.swiglu(inp["x"], inp["w0"], inp["w1"], dt)
+    elif fam == "rmsnorm_matmul":
+        want = orc.rmsnorm_matmul(inp["x"], inp["w0"], 1e-6, inp.get("gamma"), dt)
+    else:
+        want = orc.matmul(inp["x"], inp["w0"], dt)
     assert_close(got, want)
-    assert np.array_equal(got, _run(family, inp, {"dtype": dt}))
+    assert np.array_equal(got, _run(fam, inp, opt))
 
 
 def test_split_k_partials_sum_like_the_unsplit_product():

@@ -3,15 +3,14 @@
 // HALF of B's columns (the hardware feeds both halves to both SMs), so a CTA moves 32 KB of operands
 // per K block where the single-CTA kernel moves 48 KB for the same 128 x 256 x 64 of work per SM.
 //   MODE 0  Y = X @ W                    B half of CTA r: columns [256 tn + 128 r, +128) of W
-//   MODE 1  Y = RMSNorm(X) @ W (no gamma) as MODE 0; eight statistics warps per CTA take sum(x^2) of the CTA's own A rows
-//                                        from shared memory (two groups on alternate K blocks) AFTER the
-//                                        MMAs of the stage have completed - the commit that would free the
-//                                        stage wakes them instead, and they free it - so the statistics
-//                                        are never ahead of the MMA on the critical path; the epilogue
-//                                        scales rows by rsqrt(sum / K + eps). (With gamma the A tile must
-//                                        be rewritten before the MMA reads it; that chain does not hide
-//                                        behind six stages across a pair, and the single-CTA kernel keeps
-//                                        that variant.)
+//   RMSNorm(X)[* gamma] @ W                MODE 0 after one pass over X (rmsnorm_prepass_kernel) that computes the row
+//                                        factors rsqrt(sum(x^2) / K + eps) and, with gamma, writes X * gamma as
+//                                        the A operand; the epilogue applies the factors. Statistics warps
+//                                        inside the pair pipeline were measured slower in both forms: reading
+//                                        A tiles beside the MMA costs shared-memory bandwidth (1.26 PFLOP/s),
+//                                        and rewriting them ahead of the MMA adds a land -> scale -> fence ->
+//                                        remote arrive chain that six stages do not hide (0.69); the pass
+//                                        moves 2 - 4 M K bytes, about 2 % of the GEMM's time (1.35 - 1.39).
 //   MODE 2  Y = silu(X @ W0) * (X @ W1)  B half of CTA 0: 128 columns of W0; of CTA 1: the same columns of W1,
 //                                        so every CTA's accumulator is gate | up for its own rows
 // Used for whole tiles only (no split-K); small or skinny problems stay with gemm_tcgen05.cu.
@@ -19,7 +18,7 @@
 // Every CTA loads its own operands (TMA without multicast; the transaction bytes of both CTAs are
 // counted on the first CTA's barrier); the first CTA's MMA thread issues for the pair; one commit
 // arrives on the barriers of both CTAs. Warp roles per CTA: 0 = TMA producer, 1 = MMA issuer
-// (first CTA only) and TMEM owner, 2..5 = epilogue for the CTA's own 128 rows, 6..13 = statistics (MODE 1).
+// (first CTA only) and TMEM owner, 2..5 = epilogue for the CTA's own 128 rows.
 //
 // Replaces the same reference kernels as gemm_tcgen05.cu (expected_kernels/matmul.py, rmsnorm_matmul.py,
 // swiglu.py).
@@ -40,15 +39,14 @@ constexpr int kStageBytes = kABytes + kBHalfChunks * kBChunkBytes;  // 32 KB
 constexpr int kStages = 6;
 constexpr int kUmmaN = 256;
 constexpr int kThreads = 192;
-constexpr int kThreadsNorm = 448;  // MODE 1: + eight statistics warps
-constexpr int kSmemBytes = kStages * kStageBytes + 4096 /*barriers, row sums*/ + 1024 /*alignment*/;
+constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 1024;
 constexpr uint32_t kTmemCols = 512;  // two accumulators of 256 columns
 
 struct Params {
   void* y;
+  const float* row_scale;  // MODE 0: optional per-row factor applied in the epilogue (RMSNorm)
   int* status;
   int M, N, K, tiles_m, tiles_n, kblocks;
-  float eps;
 };
 
 // Tile order: bands of kGroupM tile rows, column-major inside a band, so the tiles that the resident
@@ -64,7 +62,7 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
 }
 
 template <int MODE, typename T>
-__global__ void __launch_bounds__(MODE == 1 ? kThreadsNorm : kThreads, 1)
+__global__ void __launch_bounds__(kThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b0,
                  const __grid_constant__ CUtensorMap tm_b1, const Params p) {
   extern __shared__ uint8_t smem_raw[];
@@ -74,11 +72,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   uint64_t* empty_bar = full_bar + kStages;
   uint64_t* acc_full = empty_bar + kStages;   // [2]
   uint64_t* acc_empty = acc_full + 2;         // [2] used on the first CTA: both CTAs' epilogue warps arrive
-  uint64_t* mma_done = acc_empty + 2;         // [kStages] MODE 1: the MMAs have read the stage (statistics may)
-  uint64_t* rs_full = mma_done + kStages;     // [2] MODE 1: row sums published
-  uint64_t* rs_empty = rs_full + 2;           // [2]
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(rs_empty + 2);
-  float* rowsum_smem = reinterpret_cast<float*>(smem + kStages * kStageBytes + 1024);  // [2 accumulators][2 groups][128]
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_empty + 2);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t rank = cluster_ctarank();  // 0 = first CTA of the pair (issues the MMAs)
@@ -86,14 +80,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&full_bar[s], 1);
-      mbar_init(&empty_bar[s], MODE == 1 ? 4 : 1);  // MMA commit, or the four statistics warps of the stage's group
-      mbar_init(&mma_done[s], 1);
+      mbar_init(&empty_bar[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&acc_full[b], 1);
       mbar_init(&acc_empty[b], 8);  // four epilogue warps of each CTA
-      mbar_init(&rs_full[b], 8);
-      mbar_init(&rs_empty[b], 4);
     }
     mbar_fence_init();
     tma_prefetch_desc(&tm_a);
@@ -159,7 +150,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
               const uint64_t bdesc = umma_smem_desc(b_addr + k * 16 * 128, kBChunkBytes, 8 * 128);
               umma_f16_pair(d_tmem, adesc, bdesc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
             }
-            umma_commit_pair(MODE == 1 ? &mma_done[stage] : &empty_bar[stage]);
+            umma_commit_pair(&empty_bar[stage]);
           }
           __syncwarp();
           if (++stage == kStages) { stage = 0; phase ^= 1; }
@@ -168,52 +159,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         __syncwarp();
         if (++buf == 2) { buf = 0; acc_phase ^= 1; }
       }
-    }
-  } else if (MODE == 1 && warp >= 6) {
-    // ================================================================ RMSNorm statistics, own rows
-    // Thread r owns row r of the CTA's A tile. Two groups of four warps take alternate K blocks; the
-    // number of stages is even, so a stage always belongs to the same group.
-    const int group = (warp - 6) >> 2;
-    const int row = ((warp - 6) & 3) * 32 + lane;
-    int stage = 0, phase = 0, buf = 0, acc_phase = 0, kb_count = 0;
-    for (int t = pair_id; t < tiles; t += n_pairs) {
-      int tm, tn;
-      tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
-      const bool row_live = tm * 256 + static_cast<int>(rank) * kBM + row < p.M;  // padded rows are all zero
-      float sumsq = 0.f;
-      for (int kb = 0; kb < p.kblocks; ++kb, ++kb_count) {
-        if ((kb_count & 1) != group) {
-          if (++stage == kStages) { stage = 0; phase ^= 1; }
-          continue;
-        }
-        mbar_wait(&mma_done[stage], phase, p.status, kFaultMmaBarrier);  // the tile has landed and been multiplied
-        if (row_live) {
-          const uint8_t* a_row = stages + stage * kStageBytes + row * 128;
-          // logical 16-byte chunk lc of row r sits at physical chunk lc ^ (r & 7) (128-byte swizzle)
-          uint4 raw[8];
-#pragma unroll
-          for (int lc = 0; lc < 8; ++lc) raw[lc] = *reinterpret_cast<const uint4*>(a_row + ((lc ^ (row & 7)) << 4));
-          float part[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-          for (int lc = 0; lc < 8; ++lc) {
-            const T* e = reinterpret_cast<const T*>(&raw[lc]);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const float f = static_cast<float>(e[j]);
-              part[j & 3] += f * f;
-            }
-          }
-          sumsq += (part[0] + part[1]) + (part[2] + part[3]);
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&empty_bar[stage]);  // the producer may refill the stage
-        if (++stage == kStages) { stage = 0; phase ^= 1; }
-      }
-      mbar_wait(&rs_empty[buf], acc_phase ^ 1, p.status, kFaultTmemBarrier);
-      rowsum_smem[(buf * 2 + group) * kBM + row] = sumsq;
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&rs_full[buf]);
-      if (++buf == 2) { buf = 0; acc_phase ^= 1; }
     }
   } else {
     // ================================================================ epilogue (both CTAs, own rows)
@@ -228,12 +173,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       mbar_wait(&acc_full[buf], acc_phase, p.status, kFaultMmaBarrier);
       tc_fence_after();
       float row_scale = 1.f;
-      if constexpr (MODE == 1) {
-        mbar_wait(&rs_full[buf], acc_phase, p.status, kFaultTmemBarrier);
-        const float rs = rowsum_smem[(buf * 2) * kBM + row] + rowsum_smem[(buf * 2 + 1) * kBM + row];
-        row_scale = rsqrtf(rs / static_cast<float>(p.K) + p.eps);
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&rs_empty[buf]);
+      if constexpr (MODE == 0) {
+        if (p.row_scale != nullptr && gr < p.M) row_scale = __ldg(p.row_scale + gr);
       }
       const uint32_t t_acc = tmem_base + buf * kUmmaN + (static_cast<uint32_t>(quarter * 32) << 16);
 #pragma unroll 1
@@ -247,7 +188,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             const float v = __uint_as_float(r[j]);
-            o[j] = MODE == 2 ? v / (1.f + __expf(-v)) * __uint_as_float(r2[j]) : (MODE == 1 ? v * row_scale : v);
+            o[j] = MODE == 2 ? v / (1.f + __expf(-v)) * __uint_as_float(r2[j]) : (MODE == 2 ? v : v * row_scale);
           }
           const int gc0 = tn * kTileN + c0;
           T* dst = yout + static_cast<size_t>(gr) * p.N + gc0;
@@ -280,12 +221,51 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   }
 }
 
+// RMSNorm at pair-kernel sizes: one pass over X computes the row factors rsqrt(sum(x^2) / K + eps) and, with
+// gamma (SCALE), writes X * gamma as the MMA's A operand; the matmul kernel applies the factors in its
+// epilogue. One CTA of 128 threads per row.
+template <typename T, bool SCALE>
+__global__ void __launch_bounds__(128) rmsnorm_prepass_kernel(const T* __restrict__ x, const T* __restrict__ gamma,
+                                                              T* __restrict__ xs, float* __restrict__ row_scale,
+                                                              int M, int K, float eps) {
+  __shared__ float red[4];
+  const int row = blockIdx.x;
+  if (row >= M) return;
+  const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * K);
+  const uint4* gsrc = reinterpret_cast<const uint4*>(gamma);
+  uint4* dst = reinterpret_cast<uint4*>(xs + static_cast<size_t>(row) * K);
+  float part[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int i = threadIdx.x; i < K / 8; i += 128) {
+    const uint4 v = __ldg(src + i);
+    if constexpr (SCALE) {
+      const uint4 g = __ldg(gsrc + i);
+      uint4 o;
+      o.x = mul2<T>(v.x, g.x);
+      o.y = mul2<T>(v.y, g.y);
+      o.z = mul2<T>(v.z, g.z);
+      o.w = mul2<T>(v.w, g.w);
+      dst[i] = o;
+    }
+    const T* e = reinterpret_cast<const T*>(&v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float f = static_cast<float>(e[j]);
+      part[j & 3] += f * f;
+    }
+  }
+  float sum = (part[0] + part[1]) + (part[2] + part[3]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sum;
+  __syncthreads();
+  if (threadIdx.x == 0) row_scale[row] = rsqrtf(((red[0] + red[1]) + (red[2] + red[3])) / static_cast<float>(K) + eps);
+}
+
 }  // namespace pair
 
 // ------------------------------------------------------------------------------------- host side
 bool gemm_pair_supported(const cb200_gemm_args* a, int sms) {
   if (a->split_k > 1 || a->max_ctas != 0) return false;
-  if (a->op == CB200_GEMM_RMSNORM && a->gamma != nullptr) return false;  // gamma rewrites A ahead of the MMA: single-CTA kernel
   if (a->m < 512) return false;
   const long long tiles = static_cast<long long>(ceil_div(a->m, 256)) * ceil_div(a->n, a->op == CB200_GEMM_SWIGLU ? 128 : 256);
   return tiles >= 2LL * (sms / 2);  // enough whole tiles to keep every pair busy
@@ -297,7 +277,7 @@ static int launch_pair_kernel(const pair::Params& p, const CUtensorMap& ta, cons
   auto kern = pair::gemm_pair_kernel<MODE, T>;
   CB200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, pair::kSmemBytes));
   cudaLaunchConfig_t cfg = {};
-  cfg.blockDim = dim3(MODE == 1 ? pair::kThreadsNorm : pair::kThreads, 1, 1);
+  cfg.blockDim = dim3(pair::kThreads, 1, 1);
   cfg.dynamicSmemBytes = pair::kSmemBytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -327,13 +307,18 @@ static int launch_pair_kernel(const pair::Params& p, const CUtensorMap& ta, cons
   return CB200_OK;
 }
 
-int launch_gemm_pair(const cb200_gemm_args* a, int* status, const CUtensorMap& tm_a, const CUtensorMap& tm_b0,
-                     const CUtensorMap& tm_b1, cudaStream_t stream) {
+size_t gemm_pair_prepass_bytes(const cb200_gemm_args* a) {
+  if (a->op != CB200_GEMM_RMSNORM) return 0;
+  return (a->gamma ? align_up(static_cast<size_t>(a->m) * a->k * 2, 256) : 0) + align_up(static_cast<size_t>(a->m) * 4, 256);
+}
+
+// `scratch`: gemm_pair_prepass_bytes(a) bytes of the caller's workspace (RMSNorm only).
+int launch_gemm_pair(const cb200_gemm_args* a, int* status, void* scratch, const CUtensorMap& tm_a,
+                     const CUtensorMap& tm_b0, const CUtensorMap& tm_b1, cudaStream_t stream) {
   const int sms = sm_count();
   if (sms <= 0) return CB200_ERR_CUDA;
   pair::Params p{};
   p.y = a->y;
-  p.eps = a->eps;
   p.status = status;
   p.M = a->m; p.N = a->n; p.K = a->k;
   p.tiles_m = ceil_div(a->m, 256);
@@ -343,9 +328,35 @@ int launch_gemm_pair(const cb200_gemm_args* a, int* status, const CUtensorMap& t
   if (a->op == CB200_GEMM_SWIGLU)
     return f16 ? launch_pair_kernel<2, __half>(p, tm_a, tm_b0, tm_b1, stream)
                : launch_pair_kernel<2, __nv_bfloat16>(p, tm_a, tm_b0, tm_b1, stream);
-  if (a->op == CB200_GEMM_RMSNORM)
-    return f16 ? launch_pair_kernel<1, __half>(p, tm_a, tm_b0, tm_b1, stream)
-               : launch_pair_kernel<1, __nv_bfloat16>(p, tm_a, tm_b0, tm_b1, stream);
+  if (a->op == CB200_GEMM_RMSNORM) {
+    // the row factors (and with gamma the scaled copy of X) in one pass over X, then the plain matmul
+    const bool scale = a->gamma != nullptr;
+    uint8_t* xs = static_cast<uint8_t*>(scratch);
+    float* rscale = reinterpret_cast<float*>(xs + (scale ? align_up(static_cast<size_t>(a->m) * a->k * 2, 256) : 0));
+    if (f16) {
+      auto pre = scale ? pair::rmsnorm_prepass_kernel<__half, true> : pair::rmsnorm_prepass_kernel<__half, false>;
+      pre<<<a->m, 128, 0, stream>>>(static_cast<const __half*>(a->x), static_cast<const __half*>(a->gamma),
+                                    reinterpret_cast<__half*>(xs), rscale, a->m, a->k, a->eps);
+    } else {
+      auto pre = scale ? pair::rmsnorm_prepass_kernel<__nv_bfloat16, true> : pair::rmsnorm_prepass_kernel<__nv_bfloat16, false>;
+      pre<<<a->m, 128, 0, stream>>>(static_cast<const __nv_bfloat16*>(a->x), static_cast<const __nv_bfloat16*>(a->gamma),
+                                    reinterpret_cast<__nv_bfloat16*>(xs), rscale, a->m, a->k, a->eps);
+    }
+    CB200_CUDA_TRY(cudaGetLastError());
+    p.row_scale = rscale;
+    if (!scale)
+      return f16 ? launch_pair_kernel<0, __half>(p, tm_a, tm_b0, tm_b1, stream)
+                 : launch_pair_kernel<0, __nv_bfloat16>(p, tm_a, tm_b0, tm_b1, stream);
+    CUtensorMap tm_xs;
+    uint64_t dims[2] = {static_cast<uint64_t>(a->k), static_cast<uint64_t>(a->m)};
+    uint64_t strides[1] = {static_cast<uint64_t>(a->k) * 2};
+    uint32_t box[2] = {pair::kBK, pair::kBM};
+    if (!encode_tensor_map(&tm_xs, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, xs, dims,
+                           strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
+      return CB200_ERR_CUDA;
+    return f16 ? launch_pair_kernel<0, __half>(p, tm_xs, tm_b0, tm_b1, stream)
+               : launch_pair_kernel<0, __nv_bfloat16>(p, tm_xs, tm_b0, tm_b1, stream);
+  }
   return f16 ? launch_pair_kernel<0, __half>(p, tm_a, tm_b0, tm_b1, stream)
              : launch_pair_kernel<0, __nv_bfloat16>(p, tm_a, tm_b0, tm_b1, stream);
 }

@@ -592,8 +592,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
 
 // ------------------------------------------------------------------------------------- host side
 bool gemm_pair_supported(const cb200_gemm_args* a, int sms);
-int launch_gemm_pair(const cb200_gemm_args* a, int* status, const CUtensorMap& tm_a, const CUtensorMap& tm_b0,
-                     const CUtensorMap& tm_b1, cudaStream_t stream);
+size_t gemm_pair_prepass_bytes(const cb200_gemm_args* a);
+int launch_gemm_pair(const cb200_gemm_args* a, int* status, void* scratch, const CUtensorMap& tm_a,
+                     const CUtensorMap& tm_b0, const CUtensorMap& tm_b1, cudaStream_t stream);
 
 namespace {
 
@@ -612,7 +613,7 @@ struct GemmSetup {
   int mode, nbw, grid;
   bool cluster;  // split-K inside a thread-block cluster (tiny outputs)
   bool pair;     // whole 256 x 256 tiles on CTA pairs (gemm_pair.cu)
-  size_t ws_needed, partials_off, counters_off;
+  size_t ws_needed, partials_off, counters_off, prepass_off;
   CUtensorMap tm_a, tm_b0, tm_b1;
 };
 
@@ -690,7 +691,8 @@ int plan_gemm(const cb200_gemm_args* a, GemmSetup* s, bool need_maps) {
   }
   s->partials_off = kWsHeaderBytes;
   s->counters_off = align_up(s->partials_off + static_cast<size_t>(sms) * 2 * kGemmSlotBytesMax, 256);
-  s->ws_needed = s->counters_off + static_cast<size_t>(tiles) * 4;
+  s->prepass_off = align_up(s->counters_off + static_cast<size_t>(tiles) * 4, 256);
+  s->ws_needed = s->prepass_off + (s->pair ? gemm_pair_prepass_bytes(a) : 0);
   if (!need_maps) return CB200_OK;
 
   if (!a->x || !a->w || !a->y) return CB200_ERR_BAD_ARG;
@@ -793,6 +795,7 @@ extern "C" int cb200_gemm(const cb200_gemm_args* a, void* stream) {
   const int rc = plan_gemm(a, &s, true);
   if (rc != CB200_OK) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (s.pair) return launch_gemm_pair(a, s.p.status, s.tm_a, s.tm_b0, s.tm_b1, st);
+  if (s.pair)
+    return launch_gemm_pair(a, s.p.status, static_cast<uint8_t*>(a->workspace) + s.prepass_off, s.tm_a, s.tm_b0, s.tm_b1, st);
   return a->dtype == CB200_F16 ? dispatch_gemm<__half>(s, st) : dispatch_gemm<__nv_bfloat16>(s, st);
 }

@@ -61,6 +61,9 @@ SHAPES = [  # hq, hkv, sq, skv, d
     (2, 2, 128, 128, 128),    # a single tile
     (3, 3, 1, 77, 64),        # one query row
     (2, 1, 640, 640, 128),    # five KV tiles: both S and P buffers wrap
+    (160, 160, 300, 300, 64),   # more CTAs than SMs; last query tile partly filled
+    (152, 8, 300, 517, 128),    # the same with grouped heads and more keys than queries
+    (160, 32, 129, 260, 64),    # last query tile holds a single row
 ]
 
 
@@ -88,11 +91,12 @@ def test_causal_attention_vs_oracle(hq, hkv, sq, skv, d, dt):
     assert_lse_close(host(lse), want_lse)
 
 
-def test_large_logits_take_the_rescale_path():
+@pytest.mark.parametrize("heads,sq_", [(2, 128), (160, 256)])
+def test_large_logits_take_the_rescale_path(heads, sq_):
     """Keys whose norm grows along the sequence push the running maximum up by more than 2^8
     between tiles, so O is rescaled in tensor memory."""
     rng = np.random.default_rng(5)
-    hq, sq, skv, d = 2, 128, 512, 64
+    hq, sq, skv, d = heads, sq_, 512, 64
     q = cases.round_to(rng.standard_normal((hq, sq, d), dtype=np.float32), "bf16")
     step = (1.0 + 3.0 * (np.arange(skv) // 128))[None, :, None].astype(np.float32)
     k = cases.round_to(rng.standard_normal((hq, skv, d), dtype=np.float32) * step, "bf16")
@@ -153,6 +157,26 @@ def test_paged_causal_prefill_vs_oracle(hq, hkv, d, dt):
     out2, lse2 = _ops().gqa_ragged_prefill(dev(q, dt), dev(kc[idx, 0], dt), dev(vc[idx, 0], dt),
                                            torch.from_numpy(qo).cuda(), torch.from_numpy(kv).cuda(), scale)
     assert np.array_equal(host(out), host(out2)) and np.array_equal(host(lse), host(lse2))
+
+
+def test_ragged_long_requests():
+    """Requests of several hundred query rows on 32 heads: several query tiles per request, more CTAs than SMs."""
+    q_lens, kv_lens = [300, 700, 256, 513], [300, 1000, 600, 513]
+    hq, hkv, d, dt = 32, 8, 128, "bf16"
+    rng = np.random.default_rng(77)
+    tq, tk = sum(q_lens), sum(kv_lens)
+    q = cases.round_to(rng.standard_normal((tq, hq, d), dtype=np.float32), dt)
+    k = cases.round_to(rng.standard_normal((tk, hkv, d), dtype=np.float32), dt)
+    v = cases.round_to(rng.standard_normal((tk, hkv, d), dtype=np.float32), dt)
+    qo = np.concatenate([[0], np.cumsum(q_lens)]).astype(np.int32)
+    kv = np.concatenate([[0], np.cumsum(kv_lens)]).astype(np.int32)
+    scale = d ** -0.5
+    out, lse = _ops().gqa_ragged_prefill(dev(q, dt), dev(k, dt), dev(v, dt), torch.from_numpy(qo).cuda(),
+                                         torch.from_numpy(kv).cuda(), scale)
+    _check_ws()
+    want, want_lse = orc.gqa_ragged_prefill(q, k, v, qo, kv, scale, dt)
+    assert_close(host(out), want)
+    assert_lse_close(host(lse), want_lse)
 
 
 def test_repeat_launches_are_bit_identical():

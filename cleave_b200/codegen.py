@@ -13,7 +13,7 @@ from dataclasses import dataclass, field
 from .core.errors import CodegenError
 
 FAMILIES = ("matmul", "rmsnorm_matmul", "swiglu", "attention_decode", "mla_decode",
-            "gqa_paged_decode", "mla_paged_decode")
+            "gqa_paged_decode", "mla_paged_decode", "gqa_ragged_prefill", "gqa_paged_prefill")
 FORMAT = 1
 
 
@@ -109,6 +109,20 @@ def default_params(family: str, dtype: str, dims: dict, attrs: dict) -> tuple:
                 P(_ph("kv_indices"), "int32", ("num_kv_indices",), "input"),
                 P("sm_scale", "float32", (), "scalar"), P("OutputNode", dtype, ("batch", h, c), "output"),
                 P("OutputNode_1", "float32", ("batch", h), "output"))
+    if family in ("gqa_ragged_prefill", "gqa_paged_prefill"):
+        hq, hkv, d = g("num_qo_heads"), g("num_kv_heads"), g("head_dim")
+        out = [P(_ph("q"), dtype, ("total_q", hq, d), "input")]
+        if family == "gqa_paged_prefill":
+            out += [P(_ph("k_cache"), dtype, ("num_pages", 1, hkv, d), "input"),
+                    P(_ph("v_cache"), dtype, ("num_pages", 1, hkv, d), "input")]
+        else:
+            out += [P(_ph("k"), dtype, ("total_kv", hkv, d), "input"), P(_ph("v"), dtype, ("total_kv", hkv, d), "input")]
+        out += [P(_ph("qo_indptr"), "int32", ("len_indptr",), "input"), P(_ph("kv_indptr"), "int32", ("len_indptr",), "input")]
+        if family == "gqa_paged_prefill":
+            out.append(P(_ph("kv_indices"), "int32", ("num_kv_indices",), "input"))
+        out += [P("sm_scale", "float32", (), "scalar"), P("OutputNode", dtype, ("total_q", hq, d), "output"),
+                P("OutputNode_1", "float32", ("total_q", hq), "output")]
+        return tuple(out)
     raise CodegenError(f"unknown kernel family {family!r}")
 
 

@@ -29,7 +29,14 @@ OPERATORS = {
     "mla_paged_decode": ("mla_paged_decode",
                          ("q_nope", "q_pe", "ckv_cache", "kpe_cache", "kv_indptr", "kv_indices", "sm_scale"),
                          ("num_qo_heads", "head_dim_ckv", "head_dim_kpe")),
+    "gqa_ragged_prefill_causal": ("gqa_ragged_prefill",
+                                  ("q", "k", "v", "qo_indptr", "kv_indptr", "sm_scale"),
+                                  ("num_qo_heads", "num_kv_heads", "head_dim")),
+    "gqa_paged_prefill_causal": ("gqa_paged_prefill",
+                                 ("q", "k_cache", "v_cache", "qo_indptr", "kv_indptr", "kv_indices", "sm_scale"),
+                                 ("num_qo_heads", "num_kv_heads", "head_dim")),
 }
+PREFILL_FAMILIES = ("gqa_ragged_prefill", "gqa_paged_prefill")
 
 
 def paged_decode_workloads(batches=(1, 7, 64), kv_points=6, kv_max=8192, seed=0):
@@ -50,6 +57,25 @@ def paged_decode_workloads(batches=(1, 7, 64), kv_points=6, kv_max=8192, seed=0)
     return out
 
 
+def paged_prefill_workloads(batches=(1, 5), kv_points=4, kv_max=2048, seed=0):
+    """``[(key, (q_lens, kv_lens))]``: whole-prompt prefill (q_len = kv_len) and chunked prefill (a query
+    suffix of an existing context), with an empty request in every batch larger than one - the lengths
+    python/cleave/dynamic/workloads.py draws for the prefill operators, generated here."""
+    import random
+
+    rnd = random.Random(seed)
+    out = []
+    for b in batches:
+        for i in range(kv_points):
+            centre = max(2, round(kv_max ** ((i + 1) / kv_points)))
+            kv = [max(1, round(centre * rnd.uniform(0.5, 1.0))) for _ in range(b)]
+            ql = [n if rnd.random() < 0.5 else max(1, n // rnd.choice((2, 3, 8))) for n in kv]
+            if b > 1:
+                ql[rnd.randrange(b)] = 0
+            out.append((f"b{b}_kv{centre}", (ql, kv)))
+    return out
+
+
 def make_inputs(family, dims, kv_lens, dtype, device="cuda", seed=0):
     """The operator's tensors in its declared order (reference: python/cleave/dynamic/reference.py:156-177,
     282-294): random permutation page table, N(0,1) tensors, pool three pages larger than needed."""
@@ -59,6 +85,18 @@ def make_inputs(family, dims, kv_lens, dtype, device="cuda", seed=0):
 
     dt = torch_dtype(dtype)
     g = torch.Generator(device="cpu").manual_seed(seed)
+    if family in PREFILL_FAMILIES:
+        q_lens, kv_lens = kv_lens
+        hq, hkv, d = dims["num_qo_heads"], dims["num_kv_heads"], dims["head_dim"]
+        rn = lambda *s: torch.randn(*s, generator=g).to(dt).to(device)  # noqa: E731
+        ptr = lambda ls: torch.tensor([0] + list(torch.tensor(ls).cumsum(0).tolist()), dtype=torch.int32, device=device)  # noqa: E731
+        tq, tk = max(1, sum(q_lens)), sum(kv_lens)
+        if family == "gqa_ragged_prefill":
+            return [rn(tq, hq, d), rn(tk, hkv, d), rn(tk, hkv, d), ptr(q_lens), ptr(kv_lens), float(d) ** -0.5]
+        num_pages = tk + 3
+        idx = torch.randperm(num_pages, generator=g)[:tk].to(torch.int32).to(device)
+        return [rn(tq, hq, d), rn(num_pages, 1, hkv, d), rn(num_pages, 1, hkv, d), ptr(q_lens), ptr(kv_lens), idx,
+                float(d) ** -0.5]
     batch = len(kv_lens)
     ps = int(dims.get("page_size", 1))
     pages = [-(-n // ps) for n in kv_lens]
@@ -81,7 +119,9 @@ def make_inputs(family, dims, kv_lens, dtype, device="cuda", seed=0):
 def reference(family, args):
     from ..runtime import reference as R
 
-    return (R.gqa_paged_decode if family == "gqa_paged_decode" else R.mla_paged_decode)(*args)
+    fn = {"gqa_paged_decode": R.gqa_paged_decode, "mla_paged_decode": R.mla_paged_decode,
+          "gqa_ragged_prefill": R.gqa_ragged_prefill, "gqa_paged_prefill": R.gqa_paged_prefill}[family]
+    return fn(*args)
 
 
 @dataclass
@@ -225,7 +265,7 @@ def compile_dynamic(op_name, *, dtype=None, preset="default", eval=None, workloa
         raise TypeError(f"{op_name}: missing dims {missing}")
     dt = getattr(dtype, "name", dtype) or "bfloat16"
     dims = {k: int(v) for k, v in dims.items()}
-    if family == "gqa_paged_decode":
+    if family in ("gqa_paged_decode",) + PREFILL_FAMILIES:
         if dims["head_dim"] not in (64, 128):
             raise PagingRefusal(f"{op_name}: head_dim {dims['head_dim']} is not built (64 or 128)")
         if dims["num_qo_heads"] % dims["num_kv_heads"]:
@@ -239,9 +279,11 @@ def compile_dynamic(op_name, *, dtype=None, preset="default", eval=None, workloa
     from ..runtime.compile import _compile, _load_main_kernel_from_code
     from ..runtime.timer import min_launch_us
 
-    cand = WorkloadCandidate(label=f"{op_name} persistent tile-stream", source=source)
+    cand = WorkloadCandidate(label=f"{op_name} " + ("tcgen05 query-tile" if family in PREFILL_FAMILIES else "persistent tile-stream"),
+                             source=source)
     cand.kernel = _compile(_load_main_kernel_from_code(source), None)
-    wls = list(workloads) if workloads is not None else paged_decode_workloads()
+    wls = list(workloads) if workloads is not None else (
+        paged_prefill_workloads() if family in PREFILL_FAMILIES else paged_decode_workloads())
     errors, t0 = [], time.perf_counter()
     cand.correct = True
     for key, lens in wls:

@@ -142,6 +142,10 @@ class B200Kernel:
         elif f == "mla_paged_decode":
             ops.mla_paged_decode(ins[0], ins[1], ins[2], ins[3], ins[4], ins[5], float(ins[6]), out=outs[0],
                                  lse=outs[1], max_ctas=mc)
+        elif f == "gqa_ragged_prefill":
+            ops.gqa_ragged_prefill(ins[0], ins[1], ins[2], ins[3], ins[4], float(ins[5]), out=outs[0], lse=outs[1])
+        elif f == "gqa_paged_prefill":
+            ops.gqa_paged_prefill(ins[0], ins[1], ins[2], ins[3], ins[4], ins[5], float(ins[6]), out=outs[0], lse=outs[1])
         else:  # pragma: no cover - from_dict rejects unknown families
             raise CompileError(f"unknown kernel family {f!r}")
         if self.out_idx is None:

@@ -132,6 +132,51 @@ def mla_paged_decode(q_nope, q_pe, ckv_cache, kpe_cache, kv_indptr, kv_indices, 
     return out.to(q_nope.dtype), lse
 
 
+def _causal_attend(q, k, v, sm_scale):
+    """One request: q (n_q, HQ, D), k / v (n_kv, HKV, D); end-aligned causal mask
+    (python/cleave/dynamic/reference.py:85-133). Returns (out fp32, lse base 2)."""
+    n_q, hq, d = q.shape
+    n_kv, hkv, _ = k.shape
+    group = hq // hkv
+    qg = q.float().reshape(n_q, hkv, group, d)
+    logits = torch.einsum("qhgd,khd->hgqk", qg, k.float()) * sm_scale
+    keep = torch.arange(n_kv, device=q.device)[None, :] <= (n_kv - n_q) + torch.arange(n_q, device=q.device)[:, None]
+    logits = logits.masked_fill(~keep[None, None], float("-inf"))
+    w, l = _finish(logits)
+    out = torch.einsum("hgqk,khd->qhgd", w, v.float()).reshape(n_q, hq, d)
+    return out, l.permute(2, 0, 1).reshape(n_q, hq)
+
+
+def gqa_ragged_prefill(q, k, v, qo_indptr, kv_indptr, sm_scale):
+    """``(out, lse)`` of the ragged causal prefill (python/cleave/dynamic/reference.py:244-278)."""
+    total_q, hq, d = q.shape
+    out = torch.zeros(total_q, hq, d, device=q.device, dtype=torch.float32)
+    lse = torch.full((total_q, hq), float("-inf"), device=q.device, dtype=torch.float32)
+    qo, kv = qo_indptr.tolist(), kv_indptr.tolist()
+    for r in range(len(qo) - 1):
+        if qo[r + 1] <= qo[r] or kv[r + 1] <= kv[r]:
+            continue
+        o, l = _causal_attend(q[qo[r]:qo[r + 1]], k[kv[r]:kv[r + 1]], v[kv[r]:kv[r + 1]], sm_scale)
+        out[qo[r]:qo[r + 1]], lse[qo[r]:qo[r + 1]] = o, l
+    return out.to(q.dtype), lse
+
+
+def gqa_paged_prefill(q, k_cache, v_cache, qo_indptr, kv_indptr, kv_indices, sm_scale):
+    """``(out, lse)`` of the paged causal prefill over page-size-1 caches
+    (python/cleave/dynamic/reference.py:204-241)."""
+    total_q, hq, d = q.shape
+    out = torch.zeros(total_q, hq, d, device=q.device, dtype=torch.float32)
+    lse = torch.full((total_q, hq), float("-inf"), device=q.device, dtype=torch.float32)
+    qo, kv = qo_indptr.tolist(), kv_indptr.tolist()
+    for r in range(len(qo) - 1):
+        if qo[r + 1] <= qo[r] or kv[r + 1] <= kv[r]:
+            continue
+        pages = kv_indices[kv[r]:kv[r + 1]].long()
+        o, l = _causal_attend(q[qo[r]:qo[r + 1]], k_cache[pages, 0], v_cache[pages, 0], sm_scale)
+        out[qo[r]:qo[r + 1]], lse[qo[r]:qo[r + 1]] = o, l
+    return out.to(q.dtype), lse
+
+
 def order_inputs_for_kernel(inputs_by_name: dict, kernel) -> list:
     """The tensors of ``inputs_by_name`` in the kernel's parameter order (by buffer name), as the
     reference orders them (python/cleave/runtime/reference.py:448-479)."""

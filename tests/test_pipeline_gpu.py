@@ -145,6 +145,30 @@ def test_compile_paged_mla_decode_and_refusals():
         cleave.compile("mla_paged_decode", num_qo_heads=16, head_dim_ckv=256, head_dim_kpe=64)
 
 
+@pytest.mark.parametrize("op", ["gqa_ragged_prefill_causal", "gqa_paged_prefill_causal"])
+def test_compile_causal_prefill_operators(tmp_path, op):
+    """The ragged and paged causal prefill operators of the reference's registry
+    (python/cleave/dynamic/registry.py) through the same compile / call / save / load path."""
+    import cleave_b200 as cleave
+    from cleave_b200.pipeline.dynamic import OPERATORS, make_inputs, reference
+
+    family = OPERATORS[op][0]
+    dims = dict(num_qo_heads=8, num_kv_heads=2, head_dim=64)
+    wl = [("a", ([100, 0, 300], [300, 50, 300])), ("b", ([1], [129])), ("c", ([257, 5], [600, 5]))]
+    k = cleave.compile(op, dtype="bfloat16", workloads=wl, **dims)
+    assert k.report.n_workloads == 3 and k.report.best() is not None
+    args = make_inputs(family, dims, ([200, 17, 0, 128], [333, 17, 9, 128]), "bfloat16", seed=3)
+    want_out, want_lse = reference(family, args)
+    out, lse = k(*args)
+    torch.testing.assert_close(out.float(), want_out.float(), rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(lse, want_lse, rtol=1e-2, atol=1e-2)
+    out2, lse2 = k(**dict(zip(OPERATORS[op][1], args)))
+    assert torch.equal(out, out2) and torch.equal(lse, lse2)
+    loaded = cleave.load(k.save(tmp_path / op))
+    out3, lse3 = loaded(*args)
+    assert torch.equal(out, out3) and torch.equal(lse, lse3)
+
+
 def test_check_code_in_a_spawned_worker(tmp_path):
     """The default check function is picklable and runs in a spawned worker with its own CUDA context,
     reading the parent-built reference file (reference: python/cleave/runtime/workers.py:104-122)."""

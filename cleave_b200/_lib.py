@@ -57,7 +57,7 @@ class MlaDecodeArgs(C.Structure):
         ("batch", C.c_int32), ("num_heads", C.c_int32), ("ckv_dim", C.c_int32), ("kpe_dim", C.c_int32),
         ("page_size", C.c_int32), ("num_pages", C.c_int32), ("num_kv_indices", C.c_int32),
         ("kv_len", C.c_int32), ("dtype", C.c_int32), ("max_ctas", C.c_int32), ("impl", C.c_int32),
-        ("sm_scale", C.c_float),
+        ("sm_scale", C.c_float), ("kv_start", C.c_void_p), ("kv_lens", C.c_void_p),
     ]
 
 

@@ -16,6 +16,12 @@ namespace cb200 {
 // The first 256 bytes of every workspace: word 0 is the device status (0 = ok, otherwise the
 // code of the first bounded wait that gave up).
 constexpr size_t kWsHeaderBytes = 256;
+// Workspace rule: the arrival counters sit at an offset that does not depend on the problem and reset
+// themselves after every launch; everything else may hold garbage between launches. Scratch that is
+// placed BEHIND the counters therefore starts beyond a fixed number of counter slots, so that no later
+// launch of another shape finds a previous launch's scratch where it expects zeroed counters; a problem
+// that needs more counters than that takes a path without trailing scratch.
+constexpr size_t kWsCounterSlots = size_t(1) << 18;
 enum DeviceFault : int {
   kFaultNone = 0,
   kFaultFullBarrier = 1,   // consumer waited for a TMA-filled stage

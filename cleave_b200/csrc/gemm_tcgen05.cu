@@ -691,7 +691,9 @@ int plan_gemm(const cb200_gemm_args* a, GemmSetup* s, bool need_maps) {
   }
   s->partials_off = kWsHeaderBytes;
   s->counters_off = align_up(s->partials_off + static_cast<size_t>(sms) * 2 * kGemmSlotBytesMax, 256);
-  s->prepass_off = align_up(s->counters_off + static_cast<size_t>(tiles) * 4, 256);
+  if (s->pair && a->op == CB200_GEMM_RMSNORM && static_cast<size_t>(tiles) > kWsCounterSlots)
+    s->pair = false;  // the pre-pass scratch would start inside the counters
+  s->prepass_off = align_up(s->counters_off + (static_cast<size_t>(tiles) > kWsCounterSlots ? static_cast<size_t>(tiles) : kWsCounterSlots) * 4, 256);
   s->ws_needed = s->prepass_off + (s->pair ? gemm_pair_prepass_bytes(a) : 0);
   if (!need_maps) return CB200_OK;
 

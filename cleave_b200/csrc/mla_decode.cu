@@ -48,6 +48,8 @@ struct Params {
   const void* kpe;
   const int* kv_indptr;
   const int* kv_indices;
+  const int* kv_start;  // optional: request b reads kv_indices[kv_start[b] .. + kv_lens[b]) (ranges may overlap)
+  const int* kv_lens;
   void* out;
   float* lse;
   int* status;
@@ -56,6 +58,15 @@ struct Params {
   int batch, heads, head_blocks, kv_len, paged, num_pages;
   float scale_log2;
 };
+
+// Token range of a paged request: from the (batch + 1) offsets, or from explicit per-request start and
+// length arrays (causal prefill runs one request per query token over a prefix of its sequence's pages).
+__device__ __forceinline__ int req_len(const Params& p, int b) {
+  return p.kv_lens ? max(__ldg(p.kv_lens + b), 0) : max(p.kv_indptr[b + 1] - p.kv_indptr[b], 0);
+}
+__device__ __forceinline__ int req_base(const Params& p, int b) {
+  return p.kv_start ? __ldg(p.kv_start + b) : p.kv_indptr[b];
+}
 
 template <int NHB, bool GATHER>
 struct Smem {
@@ -104,7 +115,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_ckv, const __grid_const
     const int per = ceil_div(p.batch, nthreads);
     const int i0 = min(tid * per, p.batch), i1 = min(i0 + per, p.batch);
     int sum = 0;
-    for (int i = i0; i < i1; ++i) sum += ceil_div(max(p.kv_indptr[i + 1] - p.kv_indptr[i], 0), kTile);
+    for (int i = i0; i < i1; ++i) sum += ceil_div(req_len(p, i), kTile);
     scratch[tid] = sum;
     __syncthreads();
     if (tid == 0) {
@@ -120,7 +131,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_ckv, const __grid_const
     int run = scratch[tid];
     for (int i = i0; i < i1; ++i) {
       P[i] = run;
-      run += ceil_div(max(p.kv_indptr[i + 1] - p.kv_indptr[i], 0), kTile);
+      run += ceil_div(req_len(p, i), kTile);
     }
   } else {
     tiles_per_req = ceil_div(p.kv_len, kTile);
@@ -151,8 +162,8 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_ckv, const __grid_const
     int stage = 0, phase = 0;
     for (int u = u0; u < u1;) {
       const Piece pc = walker.at(u, u1);
-      const int valid = p.paged ? max(p.kv_indptr[pc.b + 1] - p.kv_indptr[pc.b], 0) : p.kv_len;
-      const int base = p.paged ? p.kv_indptr[pc.b] : 0;
+      const int valid = p.paged ? req_len(p, pc.b) : p.kv_len;
+      const int base = p.paged ? req_base(p, pc.b) : 0;
       int pg0 = 0, pg1 = 0;
       auto page_of = [&](int t, int i) {
         const int tok = min(t * kTile + lane + 32 * i, valid - 1);
@@ -225,7 +236,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_ckv, const __grid_const
   int stage = 0, phase = 0;
   for (int u = u0; u < u1;) {
     const Piece pc = walker.at(u, u1);
-    const int valid = p.paged ? max(p.kv_indptr[pc.b + 1] - p.kv_indptr[pc.b], 0) : p.kv_len;
+    const int valid = p.paged ? req_len(p, pc.b) : p.kv_len;
     const int head0 = pc.hv * L::kRows;  // first head of the item
 
     // ---- stage Q (nope | pe) of the item's heads in shared memory; rows past the last head are zero
@@ -561,7 +572,7 @@ int plan_mla(const cb200_mla_decode_args* a, MlaSetup* s, bool need_maps) {
   s->gather = paged;
   const long long tiles_ub = paged ? (static_cast<long long>(a->num_kv_indices) + kTile - 1) / kTile + a->batch
                                    : static_cast<long long>(a->batch) * ceil_div(a->kv_len, kTile);
-  const long long units_ub = tiles_ub * p.head_blocks;
+  const long long units_ub = (a->kv_lens ? (1LL << 20) : tiles_ub) * p.head_blocks;  // explicit ranges may overlap: no bound from the index count
   if (units_ub >= (1LL << 31)) return CB200_ERR_UNSUPPORTED;
   const int sms = sm_count();
   if (sms <= 0) return CB200_ERR_CUDA;
@@ -585,7 +596,11 @@ int plan_mla(const cb200_mla_decode_args* a, MlaSetup* s, bool need_maps) {
   if (a->impl == CB200_MLA_IMPL_TCGEN05 && !s->use_tc) return CB200_ERR_UNSUPPORTED;
   const size_t n_counters = static_cast<size_t>(a->batch) * (p.head_blocks > 2 * ceil_div(a->num_heads, 128)
                                                                 ? p.head_blocks : 2 * ceil_div(a->num_heads, 128));
-  s->tc_partials_off = align_up(s->counters_off + n_counters * 4, 256);
+  if (n_counters > kWsCounterSlots) {  // the scratch of the tcgen05 kernels would start inside the counters
+    if (a->impl == CB200_MLA_IMPL_TCGEN05) return CB200_ERR_UNSUPPORTED;
+    s->use_tc = false;
+  }
+  s->tc_partials_off = align_up(s->counters_off + (n_counters > kWsCounterSlots ? n_counters : kWsCounterSlots) * 4, 256);
   s->ws_needed = s->tc_partials_off + (s->use_tc ? mla_tc_partial_bytes(a, sms) : 0);
   s->grid = static_cast<int>(units_ub < grid ? (units_ub > 0 ? units_ub : 1) : grid);
   if (!need_maps) return CB200_OK;
@@ -604,6 +619,8 @@ int plan_mla(const cb200_mla_decode_args* a, MlaSetup* s, bool need_maps) {
   p.kpe = a->kpe_cache;
   p.kv_indptr = a->kv_indptr;
   p.kv_indices = a->kv_indices;
+  p.kv_start = paged ? a->kv_start : nullptr;
+  p.kv_lens = paged ? a->kv_lens : nullptr;
   p.out = a->out;
   p.lse = a->lse;
   uint8_t* ws = static_cast<uint8_t*>(a->workspace);

@@ -120,6 +120,25 @@ def attn_prefill_case(hq=32, hkv=32, s=4096, d=64, dtype=torch.float16, causal=F
     return fn, flops, byts
 
 
+def mla_prefill_case(batch=4, q_len=512, heads=16, dtype=torch.bfloat16):
+    """Paged causal MLA prefill, whole prompts (q_len = kv_len), one token per page."""
+    g = _gen()
+    tq = batch * q_len
+    num_pages = tq + 8
+    qn = torch.randn(tq, heads, 512, generator=g).to(dtype).cuda()
+    qp = torch.randn(tq, heads, 64, generator=g).to(dtype).cuda()
+    ckv = torch.randn(num_pages, 1, 512, generator=g).to(dtype).cuda()
+    kpe = torch.randn(num_pages, 1, 64, generator=g).to(dtype).cuda()
+    ptr = (torch.arange(batch + 1, dtype=torch.int32) * q_len).cuda()
+    idx = torch.randperm(num_pages, generator=g)[:tq].to(torch.int32).cuda()
+    out = torch.empty_like(qn)
+    lse = torch.empty(tq, heads, dtype=torch.float32, device="cuda")
+    flops = 2 * batch * heads * (q_len * (q_len + 1) // 2) * (576 + 512)
+    byts = (qn.numel() + qp.numel() + ckv.numel() + kpe.numel() + out.numel()) * 2
+    fn = lambda: ops.mla_paged_prefill(qn, qp, ckv, kpe, ptr, ptr, idx, 0.1352337747812271, out=out, lse=lse)  # noqa: E731
+    return fn, flops, byts
+
+
 CONFIGS = {
     "cfg1_matmul_128x128x4096": lambda: gemm_case("matmul", 128, 128, 4096),
     "cfg2_rmsnorm_matmul_64x11008x4096": lambda: gemm_case("rmsnorm_matmul", 64, 11008, 4096),
@@ -132,6 +151,7 @@ CONFIGS = {
     "demo_gqa_prefill_h32_kv8_s4096_d64": lambda: attn_prefill_case(32, 8, 4096, 64),
     "gqa_prefill_causal_h32_kv8_s4096_d128": lambda: attn_prefill_case(32, 8, 4096, 128, torch.bfloat16, True),
     "gqa_prefill_h32_kv8_s4096_d128": lambda: attn_prefill_case(32, 8, 4096, 128, torch.bfloat16, False),
+    "mla_paged_prefill_causal_h16_b4_q512": lambda: mla_prefill_case(),
 }
 
 

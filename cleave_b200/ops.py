@@ -275,7 +275,7 @@ def swiglu(x, w0, w1, *, split_k=0, out=None, max_ctas=0):
 
 
 def _mla(q_nope, q_pe, ckv, kpe, sm_scale, *, kv_indptr=None, kv_indices=None, out=None, lse=None, max_ctas=0,
-         impl="auto"):
+         impl="auto", kv_start=None, kv_lens=None):
     q_nope, q_pe, ckv, kpe = _cuda(q_nope, "q_nope"), _cuda(q_pe, "q_pe"), _cuda(ckv, "ckv"), _cuda(kpe, "kpe")
     batch, heads, dc = q_nope.shape
     dp = q_pe.shape[2]
@@ -295,6 +295,8 @@ def _mla(q_nope, q_pe, ckv, kpe, sm_scale, *, kv_indptr=None, kv_indices=None, o
             raise TypeError("kv_indptr / kv_indices must be int32")
         a.kv_indptr, a.kv_indices = kv_indptr.data_ptr(), kv_indices.data_ptr()
         a.page_size, a.num_pages, a.num_kv_indices = ckv.shape[1], ckv.shape[0], kv_indices.numel()
+        if kv_start is not None:
+            a.kv_start, a.kv_lens = kv_start.data_ptr(), kv_lens.data_ptr()
     else:
         a.kv_len = ckv.shape[1]
     need = _lib.lib().cb200_mla_decode_workspace_bytes(C.byref(a))
@@ -323,4 +325,29 @@ def mla_paged_decode(q_nope, q_pe, ckv_cache, kpe_cache, kv_indptr, kv_indices, 
         lse = torch.empty((batch, heads), dtype=torch.float32, device=q_nope.device)
     out = _mla(q_nope, q_pe, ckv_cache, kpe_cache, sm_scale, kv_indptr=kv_indptr, kv_indices=kv_indices,
                out=out, lse=lse, max_ctas=max_ctas)
+    return out, lse
+
+
+def mla_paged_prefill(q_nope, q_pe, ckv_cache, kpe_cache, qo_indptr, kv_indptr, kv_indices, sm_scale, *, out=None,
+                      lse=None):
+    """Paged causal MLA prefill (reference: python/cleave/dynamic/reference.py:324-365, builders/mla.py):
+    q_nope (total_q, H, 512), q_pe (total_q, H, 64), caches (num_pages, 1, 512 / 64), per-request query
+    and key offsets. Every query token runs as one request of the paged MLA decode kernel over the
+    prefix of its sequence's pages that the end-aligned causal mask lets it see; a functional first
+    version (the prefix is re-read per token), not a query-tile kernel. Returns ``(out, lse)``; rows
+    without visible keys are 0 / -inf."""
+    q_nope, qo_indptr, kv_indptr = _cuda(q_nope, "q_nope"), _cuda(qo_indptr, "qo_indptr"), _cuda(kv_indptr, "kv_indptr")
+    total_q, heads, _ = q_nope.shape
+    batch = qo_indptr.numel() - 1
+    dev = q_nope.device
+    q_lens = (qo_indptr[1:] - qo_indptr[:-1]).long().clamp(min=0)
+    kv_lens = (kv_indptr[1:] - kv_indptr[:-1]).long().clamp(min=0)
+    req = torch.repeat_interleave(torch.arange(batch, device=dev), q_lens, output_size=total_q)
+    pos = torch.arange(total_q, device=dev) - qo_indptr.long()[req]
+    seen = torch.minimum((kv_lens[req] - q_lens[req] + pos + 1).clamp(min=0), kv_lens[req]).to(torch.int32)
+    start = kv_indptr[:-1][req].to(torch.int32).contiguous()
+    if lse is None:
+        lse = torch.empty(total_q, heads, dtype=torch.float32, device=dev)
+    out = _mla(q_nope, q_pe, ckv_cache, kpe_cache, sm_scale, kv_indptr=start, kv_indices=_cuda(kv_indices, "kv_indices"),
+               out=out, lse=lse, impl="mma_sync", kv_start=start, kv_lens=seen.contiguous())
     return out, lse

@@ -179,6 +179,12 @@ typedef struct {
   int32_t impl;           /* cb200_mla_impl: 0 = choose (tcgen05 kernels for contiguous caches with at least 64
                              heads and 512 tokens), 1 = mma.sync kernel, 2 = tcgen05 kernels (contiguous caches) */
   float sm_scale;
+  /* Optional, paged only (NULL otherwise): request b reads kv_indices[kv_start[b] .. kv_start[b] + kv_lens[b])
+   * instead of the range kv_indptr gives. Ranges may overlap: causal prefill
+   * (mla_paged_prefill_causal_*, python/cleave/dynamic/reference.py:324-365) runs one request per query
+   * token over the prefix of its sequence's pages that the end-aligned mask lets it see. */
+  const int32_t* kv_start;
+  const int32_t* kv_lens;
 } cb200_mla_decode_args;
 
 size_t cb200_mla_decode_workspace_bytes(const cb200_mla_decode_args* a);

@@ -318,6 +318,31 @@ def mla_paged_decode(q_nope, q_pe, ckv_cache, kpe_cache, kv_indptr, kv_indices, 
     return out, lse
 
 
+def mla_paged_prefill(q_nope, q_pe, ckv_cache, kpe_cache, qo_indptr, kv_indptr, kv_indices, scale: float,
+                      dtype: str = "bf16"):
+    """Paged causal MLA prefill (python/cleave/dynamic/reference.py:324-365): per request, rows
+    ``qo_indptr[r]:qo_indptr[r+1]`` attend the latent rows ``kv_indices[kv_indptr[r]:kv_indptr[r+1]]`` under the
+    end-aligned causal mask; ``S = (Qn CKV^T + Qp KPE^T) scale``, ``O = softmax(S) CKV``."""
+    qn, qp, ckv, kpe = f32(q_nope), f32(q_pe), f32(ckv_cache), f32(kpe_cache)
+    total_q, h, c = qn.shape
+    out = np.zeros((total_q, h, c), dtype=np.float32)
+    lse = np.full((total_q, h), NEG_INF, dtype=np.float32)
+    for r in range(len(qo_indptr) - 1):
+        qs, qe, ks, ke = int(qo_indptr[r]), int(qo_indptr[r + 1]), int(kv_indptr[r]), int(kv_indptr[r + 1])
+        if qe <= qs or ke <= ks:
+            continue
+        pages = np.asarray(kv_indices[ks:ke], dtype=np.int64)
+        kv, kp = ckv[pages, 0], kpe[pages, 0]
+        logits = (np.einsum("qhc,kc->qhk", qn[qs:qe], kv, optimize=True) +
+                  np.einsum("qhp,kp->qhk", qp[qs:qe], kp, optimize=True)).astype(np.float32) * np.float32(scale)
+        keep = np.arange(ke - ks)[None, :] <= (ke - ks) - (qe - qs) + np.arange(qe - qs)[:, None]
+        logits = np.where(keep[:, None, :], logits, -np.inf).astype(np.float32)
+        w, l = _finish(logits)
+        out[qs:qe] = round_to(np.einsum("qhk,kc->qhc", w, kv, optimize=True), dtype)
+        lse[qs:qe] = l
+    return out, lse
+
+
 def attention_lse(q, k, v, scale: float, dtype: str = "f16"):
     """Decode attention plus base-2 lse for contiguous caches, used to check the split-KV
     log-sum-exp combine: q (B,HQ,D), k/v (B,HKV,SKV,D)."""

@@ -92,6 +92,18 @@ def gqa_prefill_inputs(seed, q_lens, kv_lens, hq, hkv, d, dtype, paged):
     return out
 
 
+def mla_prefill_inputs(seed, q_lens, kv_lens, h, ckv, kpe, dtype, scale):
+    """Paged causal MLA prefill, argument for argument as python/cleave/dynamic/reference.py:323-338."""
+    rng = np.random.default_rng(seed)
+    tq, tk = sum(q_lens), sum(kv_lens)
+    num_pages = tk + 4
+    return {"q_nope": _randn(rng, (tq, h, ckv), dtype), "q_pe": _randn(rng, (tq, h, kpe), dtype),
+            "ckv_cache": _randn(rng, (num_pages, 1, ckv), dtype), "kpe_cache": _randn(rng, (num_pages, 1, kpe), dtype),
+            "qo_indptr": np.concatenate([[0], np.cumsum(q_lens)]).astype(np.int32),
+            "kv_indptr": np.concatenate([[0], np.cumsum(kv_lens)]).astype(np.int32),
+            "kv_indices": rng.permutation(num_pages)[:tk].astype(np.int32), "sm_scale": float(scale)}
+
+
 MLA_SM_SCALE = 0.1352337747812271
 
 # name -> (family, builder kwargs)
@@ -133,6 +145,8 @@ CASES = {
                                                     hq=8, hkv=2, d=128, dtype="bf16", paged=False)),
     "gqa_paged_prefill_bf16": ("gqa_prefill", dict(seed=51, q_lens=[100, 0, 128, 5, 257], kv_lens=[300, 50, 128, 0, 600],
                                                    hq=8, hkv=2, d=64, dtype="bf16", paged=True)),
+    "mla_paged_prefill_bf16": ("mla_prefill", dict(seed=52, q_lens=[20, 0, 30, 5, 1], kv_lens=[70, 30, 30, 0, 129], h=16,
+                                                  ckv=512, kpe=64, dtype="bf16", scale=MLA_SM_SCALE)),
     # paged MLA decode
     "mla_paged_bf16": ("mla_paged", dict(seed=40, kv_lens=[5, 0, 7, 300], h=16, ckv=512, kpe=64,
                                          dtype="bf16", scale=MLA_SM_SCALE)),
@@ -154,6 +168,8 @@ def build(name):
                                                     kv_lens=kw["kv_lens"])
     if family == "mla_paged":
         return family, mla_paged_inputs(**kw), dict(extra, dtype=kw["dtype"], kv_lens=kw["kv_lens"])
+    if family == "mla_prefill":
+        return family, mla_prefill_inputs(**kw), dict(extra, dtype=kw["dtype"], q_lens=kw["q_lens"], kv_lens=kw["kv_lens"])
     if family == "gqa_prefill":
         return family, gqa_prefill_inputs(**kw), dict(extra, dtype=kw["dtype"], q_lens=kw["q_lens"],
                                                       kv_lens=kw["kv_lens"], paged=kw["paged"])

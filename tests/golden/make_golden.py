@@ -113,6 +113,12 @@ def main(ref_root):
             res = ref(_t(inp["q_nope"], dt), _t(inp["q_pe"], dt), _t(inp["ckv_cache"], dt),
                       _t(inp["kpe_cache"], dt), _t(inp["kv_indptr"], dt), _t(inp["kv_indices"], dt),
                       inp["sm_scale"])
+        elif family == "mla_prefill":
+            tq, h, ckv = inp["q_nope"].shape
+            dims = (h, ckv, inp["q_pe"].shape[2], inp["ckv_cache"].shape[0], inp["kv_indices"].size, tq)
+            ref = dyn.mla_paged_prefill_reference(dims, opt["q_lens"], opt["kv_lens"])
+            res = ref(_t(inp["q_nope"], dt), _t(inp["q_pe"], dt), _t(inp["ckv_cache"], dt), _t(inp["kpe_cache"], dt),
+                      _t(inp["qo_indptr"], dt), _t(inp["kv_indptr"], dt), _t(inp["kv_indices"], dt), inp["sm_scale"])
         elif family == "gqa_prefill":
             tq, hq, d = inp["q"].shape
             if opt["paged"]:

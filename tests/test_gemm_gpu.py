@@ -101,6 +101,17 @@ def test_large_gemms_on_cta_pairs(family, m, n, k, dt):
     assert np.array_equal(got, _run(fam, inp, opt))
 
 
+def test_scratch_behind_the_counters_never_lands_in_another_shape_s_counters():
+    """A launch that parks scratch behind the arrival counters (the RMSNorm pre-pass of the pair kernel)
+    followed, on the same workspace, by a split launch of another shape with more tiles than the first:
+    its counters must still read zero."""
+    g = cases.gemm_inputs(21, 1024, 9728, 712, "f16", gamma=True)
+    _run("rmsnorm_matmul", g, {"dtype": "f16", "eps": 1e-6})
+    inp = cases.gemm_inputs(22, 2048, 2048, 256, "f16")
+    got = _run("matmul", inp, {"dtype": "f16"}, split_k=4, max_ctas=5)
+    assert_close(got, orc.matmul(inp["x"], inp["w0"], "f16"))
+
+
 def test_split_k_partials_sum_like_the_unsplit_product():
     """Reference: tests/pipeline_api/test_e2e.py:58-81 (the split-K chain equals x.float() @ w.float());
     here every split factor and every grid size must agree with the unsplit launch to fp32 round-off."""

@@ -111,3 +111,27 @@ def test_mla_full_config_properties():
     want = orc.mla_decode(q[3:4].float().numpy(), kv[3:4].float().numpy(), qp[3:4].float().numpy(),
                           kp[3:4].float().numpy(), scale, "bf16")
     assert_close(host(out[3:4]), want)
+
+
+def test_paged_causal_mla_prefill_matches_reference_golden_and_oracle():
+    """Reference: python/cleave/dynamic/reference.py:324-365 (mla_paged_prefill_causal_h16_ckv512_kpe64_ps1):
+    the golden case from the reference's own definition, and a second seeded case against the oracle with
+    requests without queries, without keys, and with more queries than keys."""
+    ops = _ops()
+    _, inp, opt = cases.build("mla_paged_prefill_bf16")
+    i32 = lambda a: torch.from_numpy(a).cuda()  # noqa: E731
+    out, lse = ops.mla_paged_prefill(dev(inp["q_nope"], "bf16"), dev(inp["q_pe"], "bf16"), dev(inp["ckv_cache"], "bf16"),
+                                     dev(inp["kpe_cache"], "bf16"), i32(inp["qo_indptr"]), i32(inp["kv_indptr"]),
+                                     i32(inp["kv_indices"]), inp["sm_scale"])
+    _check_ws()
+    assert_close(host(out), GOLDEN["mla_paged_prefill_bf16"][0])
+    assert_lse_close(host(lse), GOLDEN["mla_paged_prefill_bf16"][1])
+    inp = cases.mla_prefill_inputs(9, [33, 200, 0, 7, 20], [64, 260, 5, 0, 12], 16, 512, 64, "bf16", cases.MLA_SM_SCALE)
+    out, lse = ops.mla_paged_prefill(dev(inp["q_nope"], "bf16"), dev(inp["q_pe"], "bf16"), dev(inp["ckv_cache"], "bf16"),
+                                     dev(inp["kpe_cache"], "bf16"), i32(inp["qo_indptr"]), i32(inp["kv_indptr"]),
+                                     i32(inp["kv_indices"]), inp["sm_scale"])
+    _check_ws()
+    want, want_lse = orc.mla_paged_prefill(inp["q_nope"], inp["q_pe"], inp["ckv_cache"], inp["kpe_cache"], inp["qo_indptr"],
+                                           inp["kv_indptr"], inp["kv_indices"], inp["sm_scale"])
+    assert_close(host(out), want)
+    assert_lse_close(host(lse), want_lse)

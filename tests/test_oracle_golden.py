@@ -38,6 +38,9 @@ def _run(name):
     if family == "mla_paged":
         return list(orc.mla_paged_decode(inp["q_nope"], inp["q_pe"], inp["ckv_cache"], inp["kpe_cache"],
                                          inp["kv_indptr"], inp["kv_indices"], inp["sm_scale"]))
+    if family == "mla_prefill":
+        return list(orc.mla_paged_prefill(inp["q_nope"], inp["q_pe"], inp["ckv_cache"], inp["kpe_cache"], inp["qo_indptr"],
+                                          inp["kv_indptr"], inp["kv_indices"], inp["sm_scale"]))
     if family == "gqa_prefill":
         if opt["paged"]:
             return list(orc.gqa_paged_prefill(inp["q"], inp["k_cache"], inp["v_cache"], inp["qo_indptr"],
@@ -53,7 +56,7 @@ def test_oracle_matches_reference_golden(name):
     got = _run(name)
     want = GOLDEN[name]
     assert len(got) == len(want)
-    out_dt = "bf16" if family in ("gqa_paged", "mla_paged", "gqa_prefill") else opt["dtype"]
+    out_dt = "bf16" if family in ("gqa_paged", "mla_paged", "gqa_prefill", "mla_prefill") else opt["dtype"]
     _close(got[0].reshape(want[0].shape), want[0], out_dt)
     if len(want) > 1:  # base-2 lse, fp32
         assert np.array_equal(np.isneginf(got[1]), np.isneginf(want[1]))

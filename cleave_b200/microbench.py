@@ -120,6 +120,20 @@ def attn_prefill_case(hq=32, hkv=32, s=4096, d=64, dtype=torch.float16, causal=F
     return fn, flops, byts
 
 
+def paged_decode_case(page_size=1, batch=64, hi=8192):
+    """Paged GQA decode (32 / 8 heads, d 128, bf16) over a cache far larger than L2; page size 1 takes
+    the row-gather path."""
+    from .workloads import paged_decode_workload
+
+    w = paged_decode_workload(batch=batch, page_size=page_size, lo=512, hi=hi, dtype=torch.bfloat16)
+    out = torch.empty_like(w.q)
+    lse = torch.empty(w.q.shape[0], w.q.shape[1], dtype=torch.float32, device="cuda")
+    last = None if page_size == 1 else w.kv_last_page_len
+    fn = lambda: ops.gqa_paged_decode(w.q, w.k_cache, w.v_cache, w.kv_indptr, w.kv_indices, last, w.sm_scale,  # noqa: E731
+                                      out=out, lse=lse)
+    return fn, w.flops(), w.algorithmic_bytes()
+
+
 def mla_prefill_case(batch=4, q_len=512, heads=16, dtype=torch.bfloat16):
     """Paged causal MLA prefill, whole prompts (q_len = kv_len), one token per page."""
     g = _gen()
@@ -152,6 +166,10 @@ CONFIGS = {
     "gqa_prefill_causal_h32_kv8_s4096_d128": lambda: attn_prefill_case(32, 8, 4096, 128, torch.bfloat16, True),
     "gqa_prefill_h32_kv8_s4096_d128": lambda: attn_prefill_case(32, 8, 4096, 128, torch.bfloat16, False),
     "mla_paged_prefill_causal_h16_b4_q512": lambda: mla_prefill_case(),
+    "gqa_paged_decode_ps1_b64_kv512_8192": lambda: paged_decode_case(1),
+    "gqa_paged_decode_ps16_b64_kv512_8192": lambda: paged_decode_case(16),
+    "gqa_paged_decode_ps32_b64_kv512_8192": lambda: paged_decode_case(32),
+    "gqa_paged_decode_ps64_b64_kv512_8192": lambda: paged_decode_case(64),
 }
 
 

@@ -61,7 +61,7 @@ struct Params {
 // a CTA finds its (request, query tile) by scanning the query offsets (the device-side work list of
 // the reference's IndptrTileScan, python/cleave/dynamic/paging/stages.py:288-328).
 // MODE 2 (paged): q as in the ragged layout; K and V rows are gathered from page-size-1 caches through
-// kv_indices by four extra warps (one token row per thread, 16-byte cp.async into the swizzled tile;
+// kv_indices by four extra warps (16-byte cp.async into the swizzled tile, whole rows per warp instruction;
 // a thread's arrival on the full barrier fires when its copies have landed).
 template <typename T, int D, int MODE>
 __global__ void __launch_bounds__(MODE == 2 ? kThreadsPaged : kThreads, 1)
@@ -94,7 +94,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   const int hk = h / (p.hq / p.hkv);
   int q0, sq, skv, q_base = 0, kv_base = 0;
   if constexpr (RAGGED) {
-    int t = blockIdx.x / p.hq, r = 0, lo = __ldg(p.qo_indptr);
+    // late query tiles, which see the most keys under the causal mask, are scheduled first
+    int t = static_cast<int>(gridDim.x / p.hq) - 1 - static_cast<int>(blockIdx.x / p.hq), r = 0, lo = __ldg(p.qo_indptr);
     bool found = false;
     for (; r < p.batch; ++r) {
       const int hi = __ldg(p.qo_indptr + r + 1);
@@ -195,32 +196,46 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   } else if (warp >= 7) {
     // ================================================================ paged: K / V row gather
     if constexpr (MODE == 2) {
-      const int row = tid - 7 * 32;  // token row of the tile, 0..127
+      // Consecutive lanes copy consecutive 16-byte chunks of a row, so one warp instruction moves whole
+      // rows as full 128-byte lines; the 128 threads cover kRowsPerRound rows at once.
+      const int gtid = tid - 7 * 32;  // 0..127
+      constexpr int kChunksPerRow = D / 8;
+      constexpr int kRowsPerRound = 128 / kChunksPerRow;
+      constexpr int kRounds = kBN / kRowsPerRound;
+      const int c = gtid % kChunksPerRow, r_in = gtid / kChunksPerRow;
       const T* kc = reinterpret_cast<const T*>(p.k_cache);
       const T* vc = reinterpret_cast<const T*>(p.v_cache);
-      auto page_of = [&](int j) {
-        const int tok = min(j * kBN + row, skv - 1);  // rows past the end repeat the last token; they are masked
-        return __ldg(p.kv_indices + kv_base + tok);
+      auto load_pages = [&](int j, int (&pg)[kRounds]) {
+#pragma unroll
+        for (int r = 0; r < kRounds; ++r) {
+          const int tok = min(j * kBN + r * kRowsPerRound + r_in, skv - 1);  // rows past the end repeat the last token; they are masked
+          pg[r] = __ldg(p.kv_indices + kv_base + tok);
+        }
       };
-      int pg = nt > 0 ? page_of(0) : 0;
+      int pg[kRounds];
+      if (nt > 0) load_pages(0, pg);
       int st = 0, ph = 0;
       for (int j = 0; j < nt; ++j) {
-        const long long page = min(max(pg, 0), p.num_pages - 1);
-        if (j + 1 < nt) pg = page_of(j + 1);  // one tile ahead: the index latency stays off the critical path
-        const long long src = (page * p.hkv + hk) * D;
+        long long src[kRounds];
+#pragma unroll
+        for (int r = 0; r < kRounds; ++r)
+          src[r] = (static_cast<long long>(min(max(pg[r], 0), p.num_pages - 1)) * p.hkv + hk) * D + c * 8;
+        if (j + 1 < nt) load_pages(j + 1, pg);  // one tile ahead: the index latency stays off the critical path
         const uint32_t kdst = smem_u32(k_smem + st * C::kTileBytes), vdst = smem_u32(v_smem + st * C::kTileBytes);
         mbar_wait(&k_empty[st], ph ^ 1, p.status, kFaultEmptyBarrier);
 #pragma unroll
-        for (int c = 0; c < D / 8; ++c) {
+        for (int r = 0; r < kRounds; ++r) {
+          const int row = r * kRowsPerRound + r_in;
           const uint32_t o = (c >> 3) * C::kChunkBytes + row * 128 + (((c & 7) ^ (row & 7)) << 4);
-          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(kdst + o), "l"(kc + src + c * 8) : "memory");
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(kdst + o), "l"(kc + src[r]) : "memory");
         }
         asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&k_full[st])) : "memory");
         mbar_wait(&v_empty[st], ph ^ 1, p.status, kFaultEmptyBarrier);
 #pragma unroll
-        for (int c = 0; c < D / 8; ++c) {
+        for (int r = 0; r < kRounds; ++r) {
+          const int row = r * kRowsPerRound + r_in;
           const uint32_t o = (c >> 3) * C::kChunkBytes + row * 128 + (((c & 7) ^ (row & 7)) << 4);
-          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(vdst + o), "l"(vc + src + c * 8) : "memory");
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(vdst + o), "l"(vc + src[r]) : "memory");
         }
         asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&v_full[st])) : "memory");
         if (++st == kStages) { st = 0; ph ^= 1; }

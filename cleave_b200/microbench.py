@@ -134,6 +134,30 @@ def paged_decode_case(page_size=1, batch=64, hi=8192):
     return fn, w.flops(), w.algorithmic_bytes()
 
 
+def gqa_dynamic_prefill_case(paged, batch=8, q_len=2048, hq=32, hkv=8, d=128, dtype=torch.bfloat16):
+    """Ragged or paged (one token per page) causal prefill of whole prompts."""
+    g = _gen()
+    tq = batch * q_len
+    q = torch.randn(tq, hq, d, generator=g).to(dtype).cuda()
+    ptr = (torch.arange(batch + 1, dtype=torch.int32) * q_len).cuda()
+    out = torch.empty_like(q)
+    lse = torch.empty(tq, hq, dtype=torch.float32, device="cuda")
+    flops = 4 * batch * hq * (q_len * (q_len + 1) // 2) * d
+    if paged:
+        num_pages = tq + 8
+        kc = torch.randn(num_pages, 1, hkv, d, generator=g).to(dtype).cuda()
+        vc = torch.randn(num_pages, 1, hkv, d, generator=g).to(dtype).cuda()
+        idx = torch.randperm(num_pages, generator=g)[:tq].to(torch.int32).cuda()
+        fn = lambda: ops.gqa_paged_prefill(q, kc, vc, ptr, ptr, idx, d ** -0.5, out=out, lse=lse)  # noqa: E731
+        byts = (2 * q.numel() + 2 * kc.numel()) * 2
+    else:
+        k = torch.randn(tq, hkv, d, generator=g).to(dtype).cuda()
+        v = torch.randn(tq, hkv, d, generator=g).to(dtype).cuda()
+        fn = lambda: ops.gqa_ragged_prefill(q, k, v, ptr, ptr, d ** -0.5, out=out, lse=lse)  # noqa: E731
+        byts = (2 * q.numel() + 2 * k.numel()) * 2
+    return fn, flops, byts
+
+
 def mla_prefill_case(batch=4, q_len=512, heads=16, dtype=torch.bfloat16):
     """Paged causal MLA prefill, whole prompts (q_len = kv_len), one token per page."""
     g = _gen()
@@ -165,6 +189,8 @@ CONFIGS = {
     "demo_gqa_prefill_h32_kv8_s4096_d64": lambda: attn_prefill_case(32, 8, 4096, 64),
     "gqa_prefill_causal_h32_kv8_s4096_d128": lambda: attn_prefill_case(32, 8, 4096, 128, torch.bfloat16, True),
     "gqa_prefill_h32_kv8_s4096_d128": lambda: attn_prefill_case(32, 8, 4096, 128, torch.bfloat16, False),
+    "gqa_ragged_prefill_causal_h32_kv8_d128_b8_q2048": lambda: gqa_dynamic_prefill_case(False),
+    "gqa_paged_prefill_causal_h32_kv8_d128_ps1_b8_q2048": lambda: gqa_dynamic_prefill_case(True),
     "mla_paged_prefill_causal_h16_b4_q512": lambda: mla_prefill_case(),
     "gqa_paged_decode_ps1_b64_kv512_8192": lambda: paged_decode_case(1),
     "gqa_paged_decode_ps16_b64_kv512_8192": lambda: paged_decode_case(16),

@@ -24,7 +24,6 @@
 
 #include "common.cuh"
 
-#include <cstdlib>
 #include <cstring>
 #include <type_traits>
 
@@ -598,14 +597,6 @@ int launch_gemm_pair(const cb200_gemm_args* a, int* status, void* scratch, const
 
 namespace {
 
-bool gemm_pair_enabled() {
-  static const bool on = [] {
-    const char* e = getenv("CB200_GEMM_PAIR");
-    return !(e && e[0] == '0');
-  }();
-  return on;
-}
-
 constexpr size_t kGemmSlotBytesMax = (static_cast<size_t>(kBM) * 256 + kBM) * 4;
 
 struct GemmSetup {
@@ -683,7 +674,7 @@ int plan_gemm(const cb200_gemm_args* a, GemmSetup* s, bool need_maps) {
   const int S = p.chunks_per_tile;
   s->cluster = S >= 2 && (S <= 8 || S == 16) && chunks <= grid_max && a->max_ctas == 0;
   if (s->cluster) s->grid = static_cast<int>(chunks);
-  s->pair = gemm_pair_supported(a, sms) && gemm_pair_enabled();
+  s->pair = gemm_pair_supported(a, sms);
   if (s->pair) {
     s->cluster = false;
     p.chunk_kblocks = p.kblocks;

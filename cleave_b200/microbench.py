@@ -158,6 +158,25 @@ def gqa_dynamic_prefill_case(paged, batch=8, q_len=2048, hq=32, hkv=8, d=128, dt
     return fn, flops, byts
 
 
+def mla_paged_decode_case(batch=64, heads=16, lo=512, hi=8192, dtype=torch.bfloat16):
+    """Paged MLA decode (one token per page, 16 heads as the reference's shipped operator)."""
+    g = _gen()
+    lens = torch.randint(lo, hi + 1, (batch,), generator=g)
+    total = int(lens.sum())
+    num_pages = total + 8
+    qn = torch.randn(batch, heads, 512, generator=g).to(dtype).cuda()
+    qp = torch.randn(batch, heads, 64, generator=g).to(dtype).cuda()
+    ckv = torch.randn(num_pages, 1, 512, dtype=dtype, device="cuda")
+    kpe = torch.randn(num_pages, 1, 64, dtype=dtype, device="cuda")
+    ptr = torch.cat([torch.zeros(1, dtype=torch.int64), lens.cumsum(0)]).to(torch.int32).cuda()
+    idx = torch.randperm(num_pages, generator=g)[:total].to(torch.int32).cuda()
+    out = torch.empty_like(qn)
+    flops = 2 * heads * total * (576 + 512)
+    byts = total * 576 * 2 + (qn.numel() + qp.numel() + out.numel()) * 2
+    fn = lambda: ops.mla_paged_decode(qn, qp, ckv, kpe, ptr, idx, 0.1352337747812271, out=out)  # noqa: E731
+    return fn, flops, byts
+
+
 def mla_prefill_case(batch=4, q_len=512, heads=16, dtype=torch.bfloat16):
     """Paged causal MLA prefill, whole prompts (q_len = kv_len), one token per page."""
     g = _gen()
@@ -191,6 +210,7 @@ CONFIGS = {
     "gqa_prefill_h32_kv8_s4096_d128": lambda: attn_prefill_case(32, 8, 4096, 128, torch.bfloat16, False),
     "gqa_ragged_prefill_causal_h32_kv8_d128_b8_q2048": lambda: gqa_dynamic_prefill_case(False),
     "gqa_paged_prefill_causal_h32_kv8_d128_ps1_b8_q2048": lambda: gqa_dynamic_prefill_case(True),
+    "mla_paged_decode_h16_ps1_b64_kv512_8192": lambda: mla_paged_decode_case(),
     "mla_paged_prefill_causal_h16_b4_q512": lambda: mla_prefill_case(),
     "gqa_paged_decode_ps1_b64_kv512_8192": lambda: paged_decode_case(1),
     "gqa_paged_decode_ps16_b64_kv512_8192": lambda: paged_decode_case(16),

@@ -81,9 +81,10 @@ struct Smem {
   static constexpr int kPPitch = kTile * 2 + 16;         // padded P row (64 tokens)
   static constexpr int kPBytes = kRows * kPPitch;
   static constexpr int kExchFloats = 4 * kRows;          // per-warp row maxima / row sums
-  static constexpr int kFixed = kStages * kStageBytes + kQBytes + kPBytes + 2 * kExchFloats * 4 + 256;
+  static constexpr int kFixed = kStages * kStageBytes + kQBytes + kPBytes + 2 * kExchFloats * 4 + 1024;  // barriers, flags, page ids
   static constexpr int kSlotFloats = kRows * kCkv + 2 * kRows;  // partial O, m, l
-  static constexpr int kThreads = (4 + 1) * 32;          // four consumer warps and the producer
+  static constexpr int kProducerWarps = GATHER ? 4 : 1;  // one TMA warp, or four row-gather warps
+  static constexpr int kThreads = (4 + kProducerWarps) * 32;
 };
 
 template <typename T, int NHB, bool GATHER>
@@ -103,6 +104,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_ckv, const __grid_const
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(sum_exch + L::kExchFloats);
   uint64_t* empty_bar = full_bar + kStages;
   int* flags = reinterpret_cast<int*>(empty_bar + kStages);
+  int* pg_smem = flags + 32;  // gather: page ids of the current and the next tile, 2 x 64
   int* P = reinterpret_cast<int*>(smem + L::kFixed);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -138,7 +140,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_ckv, const __grid_const
   }
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(&full_bar[s], 1);
+      mbar_init(&full_bar[s], GATHER ? L::kProducerWarps * 32 : 1);  // gather: one arrival per copying thread
       mbar_init(&empty_bar[s], kConsumerWarps);
     }
     mbar_fence_init();
@@ -157,34 +159,18 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_ckv, const __grid_const
   const int u1 = min(u0 + span, total);
   Walker walker{p.paged ? P : nullptr, p.batch, hb_count, tiles_per_req};
 
-  if (warp == kConsumerWarps) {
-    // ================================================================= producer warp
+  if (warp >= kConsumerWarps) {
+    // ================================================================= producer warp(s)
     int stage = 0, phase = 0;
     for (int u = u0; u < u1;) {
       const Piece pc = walker.at(u, u1);
       const int valid = p.paged ? req_len(p, pc.b) : p.kv_len;
       const int base = p.paged ? req_base(p, pc.b) : 0;
-      int pg0 = 0, pg1 = 0;
-      auto page_of = [&](int t, int i) {
-        const int tok = min(t * kTile + lane + 32 * i, valid - 1);
-        return __ldg(p.kv_indices + base + tok);
-      };
-      if constexpr (GATHER) {
-        pg0 = page_of(pc.tile0, 0);
-        pg1 = page_of(pc.tile0, 1);
-      }
-      for (int t = pc.tile0; t < pc.tile0 + pc.count; ++t) {
-        int cur0 = pg0, cur1 = pg1;
-        if constexpr (GATHER) {
-          if (t + 1 < pc.tile0 + pc.count) {  // page ids one tile ahead
-            pg0 = page_of(t + 1, 0);
-            pg1 = page_of(t + 1, 1);
-          }
-        }
-        mbar_wait(&empty_bar[stage], phase ^ 1, p.status, kFaultEmptyBarrier);
-        uint8_t* ckv_dst = stages + stage * L::kStageBytes;
-        uint8_t* kpe_dst = ckv_dst + L::kCkvBytes;
-        if constexpr (!GATHER) {
+      if constexpr (!GATHER) {
+        for (int t = pc.tile0; t < pc.tile0 + pc.count; ++t) {
+          mbar_wait(&empty_bar[stage], phase ^ 1, p.status, kFaultEmptyBarrier);
+          uint8_t* ckv_dst = stages + stage * L::kStageBytes;
+          uint8_t* kpe_dst = ckv_dst + L::kCkvBytes;
           if (lane == 0) {
             mbar_arrive_expect_tx(&full_bar[stage], kTile * kQk * 2);
 #pragma unroll
@@ -193,20 +179,52 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_ckv, const __grid_const
             tma_load_3d(kpe_dst, &tm_kpe, &full_bar[stage], 0, t * kTile, pc.b);
           }
           __syncwarp();
-        } else {
-          const T* ckv = reinterpret_cast<const T*>(p.ckv);
-          const T* kpe = reinterpret_cast<const T*>(p.kpe);
-          if (lane == 0) mbar_arrive_expect_tx(&full_bar[stage], kTile * kQk * 2);
-          __syncwarp();
-#pragma unroll
-          for (int i = 0; i < 2; ++i) {
-            const int row = lane + 32 * i;
-            const long long page = min(max(i ? cur1 : cur0, 0), p.num_pages - 1);
-            bulk_load_1d(ckv_dst + row * L::kCkvPitch, ckv + page * kCkv, kCkv * 2, &full_bar[stage]);
-            bulk_load_1d(kpe_dst + row * L::kKpePitch, kpe + page * kKpe, kKpe * 2, &full_bar[stage]);
-          }
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
-        if (++stage == kStages) { stage = 0; phase ^= 1; }
+      } else {
+        // Row gather (one token per page): four warps copy the 64 latent rows (1024 + 128 bytes each) of a
+        // tile with 16-byte cp.async into padded rows; consecutive lanes copy consecutive chunks of a row,
+        // so a warp instruction moves 512 contiguous bytes. (One bulk copy per row was measured first:
+        // 128 small bulk copies per tile kept the copy engine, not the memory, busy.) The page ids of the
+        // next tile are staged in shared memory while the current one is copied.
+        constexpr int kPThreads = L::kProducerWarps * 32;
+        const int ptid = tid - kCThreads;
+        const T* ckv = reinterpret_cast<const T*>(p.ckv);
+        const T* kpe = reinterpret_cast<const T*>(p.kpe);
+        auto stage_ids = [&](int t, int buf) {
+          if (ptid < kTile) {
+            const int tok = min(t * kTile + ptid, valid - 1);
+            pg_smem[buf * kTile + ptid] = min(max(__ldg(p.kv_indices + base + tok), 0), p.num_pages - 1);
+          }
+        };
+        named_bar_sync(3, kPThreads);  // the previous piece's last tile no longer reads the id buffers
+        stage_ids(pc.tile0, 0);
+        named_bar_sync(3, kPThreads);
+        for (int t = pc.tile0; t < pc.tile0 + pc.count; ++t) {
+          const int buf = (t - pc.tile0) & 1;
+          if (t + 1 < pc.tile0 + pc.count) stage_ids(t + 1, buf ^ 1);
+          mbar_wait(&empty_bar[stage], phase ^ 1, p.status, kFaultEmptyBarrier);
+          const uint32_t ckv_dst = smem_u32(stages + stage * L::kStageBytes);
+          const uint32_t kpe_dst = ckv_dst + L::kCkvBytes;
+          constexpr int kCkvChunks = kCkv / 8, kKpeChunks = kKpe / 8;  // 16-byte chunks per row: 64 and 8
+#pragma unroll 4
+          for (int i = ptid; i < kTile * kCkvChunks; i += kPThreads) {
+            const int row = i / kCkvChunks, c = i - row * kCkvChunks;
+            const long long page = pg_smem[buf * kTile + row];
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(ckv_dst + row * L::kCkvPitch + c * 16),
+                         "l"(ckv + page * kCkv + c * 8) : "memory");
+          }
+#pragma unroll
+          for (int i = ptid; i < kTile * kKpeChunks; i += kPThreads) {
+            const int row = i / kKpeChunks, c = i - row * kKpeChunks;
+            const long long page = pg_smem[buf * kTile + row];
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(kpe_dst + row * L::kKpePitch + c * 16),
+                         "l"(kpe + page * kKpe + c * 8) : "memory");
+          }
+          asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&full_bar[stage])) : "memory");
+          named_bar_sync(3, kPThreads);  // ids of tile t + 1 are in place; buffer `buf` may be rewritten
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
       }
       u += pc.count;
     }

@@ -630,23 +630,37 @@ int plan_gemm(const cb200_gemm_args* a, GemmSetup* s, bool need_maps) {
   s->nbw = 2;
   if (a->op != CB200_GEMM_SWIGLU && static_cast<long long>(p.tiles_m) * ceil_div(a->n, 256) >= 2LL * grid_max) s->nbw = 4;
   p.kblocks = ceil_div(a->k, kBK);
-  // One row of tiles (M <= 128, the decode-sized GEMMs): W is streamed once, so the plan is the
-  // (tile width, cluster split) pair that puts the most SMs on it, with at least four K blocks per CTA.
-  int skinny_split = 0;
-  if (a->split_k <= 0 && a->max_ctas == 0 && p.tiles_m == 1) {
-    long long best_ctas = 0, best_pad = 0;
+  // Automatic plan: whole tiles, or the K parts of a tile as one thread-block cluster (reduced through
+  // distributed shared memory), whichever a small cost model says finishes first. Per CTA and K block
+  // the MMAs take about 684 clocks for a 256-column tile and 400 for a 128-column one (measured
+  // instruction costs) or the time to pull the block's operands, whichever is longer; a cluster reduce moves
+  // (S - 1) / S of an fp32 tile at about 25 KB/us; tiles beyond one wave of SMs queue up. The stream-K walk with a workspace fix-up stays for explicit split factors
+  // and CTA limits: its last-arriver reduce costs several microseconds per cut tile.
+  int auto_split = 0;
+  if (a->split_k <= 0 && a->max_ctas == 0) {
+    double best = 0.0;
+    const int rows_live = a->m < kBM ? a->m : kBM;
     for (int nbw = 2; nbw <= (a->op == CB200_GEMM_SWIGLU ? 2 : 4); nbw *= 2) {
-      const int tn = ceil_div(a->n, nbw * kChunkN);
-      int smax = grid_max / tn;
+      const long long tl = static_cast<long long>(p.tiles_m) * ceil_div(a->n, nbw * kChunkN);
+      const double kb_us = ((nbw == 4 || a->op == CB200_GEMM_SWIGLU) ? 684.0 : 400.0) / 1900.0;
+      const int umma_n = nbw * kChunkN * (a->op == CB200_GEMM_SWIGLU ? 2 : 1);
+      int smax = tl <= grid_max ? static_cast<int>(grid_max / tl) : 1;
       if (smax > 8) smax = 8;
       if (smax > p.kblocks / 4) smax = p.kblocks / 4;
-      if (smax < 1) continue;
-      const long long ctas = static_cast<long long>(tn) * smax, pad = static_cast<long long>(tn) * nbw * kChunkN - a->n;
-      if (ctas > best_ctas || (ctas == best_ctas && pad < best_pad)) {
-        best_ctas = ctas;
-        best_pad = pad;
-        s->nbw = nbw;
-        skinny_split = smax;
+      if (smax < 1) smax = 1;
+      // operand bytes a CTA pulls per K block (A rows that exist + B chunks) at about 70 KB/us per SM
+      const double kb_mem_us = (rows_live * kBK * 2.0 + umma_n * kBK * 2.0) / 70000.0;
+      const double kb_cost = kb_us > kb_mem_us ? kb_us : kb_mem_us;
+      for (int sp = 1; sp <= smax; ++sp) {
+        const long long waves = (tl * sp + grid_max - 1) / grid_max;
+        double t = static_cast<double>(waves) * ceil_div(p.kblocks, sp) * kb_cost;
+        // park + reduce, and half a microsecond per extra cluster member (measured: wide clusters start late)
+        if (sp > 1) t += rows_live * umma_n * 4.0 * (sp - 1) / sp / 25000.0 + 1.0 + 0.5 * (sp - 1);
+        if (best == 0.0 || t < best * 0.97) {  // ties go to the earlier (narrower, less split) candidate
+          best = t;
+          s->nbw = nbw;
+          auto_split = sp;
+        }
       }
     }
   }
@@ -654,9 +668,9 @@ int plan_gemm(const cb200_gemm_args* a, GemmSetup* s, bool need_maps) {
   const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
   if (tiles >= (1LL << 24)) return CB200_ERR_UNSUPPORTED;
   int split = a->split_k;
-  if (split <= 0 && skinny_split > 0) {
-    split = skinny_split;
-  } else if (split <= 0) {  // pick the K split that gives every CTA several chunks
+  if (split <= 0 && auto_split > 0) {
+    split = auto_split;
+  } else if (split <= 0) {  // a CTA limit: pick the K split that gives every CTA several chunks
     split = 1;
     if (tiles * 8 <= grid_max && p.kblocks >= 16) {
       split = 8;  // tiny output: an 8-CTA cluster per tile (portable cluster size)

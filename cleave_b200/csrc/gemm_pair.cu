@@ -264,11 +264,17 @@ __global__ void __launch_bounds__(128) rmsnorm_prepass_kernel(const T* __restric
 }  // namespace pair
 
 // ------------------------------------------------------------------------------------- host side
-bool gemm_pair_supported(const cb200_gemm_args* a, int sms) {
-  if (a->split_k > 1 || a->max_ctas != 0) return false;
-  if (a->m < 512) return false;
+// Estimated time (us) of the pair kernel on this problem, or a negative value when it does not apply.
+// One 256 x 256 x 64 block of MMAs costs a pair about 0.44 us (sustained rate of full-size runs);
+// tiles beyond one wave of pairs queue up; RMSNorm adds its pass over X.
+double gemm_pair_estimate_us(const cb200_gemm_args* a, int sms) {
+  if (a->split_k > 1 || a->max_ctas != 0 || a->m < 256) return -1.0;
   const long long tiles = static_cast<long long>(ceil_div(a->m, 256)) * ceil_div(a->n, a->op == CB200_GEMM_SWIGLU ? 128 : 256);
-  return tiles >= 2LL * (sms / 2);  // enough whole tiles to keep every pair busy
+  const int pairs = sms / 2;
+  const long long waves = (tiles + pairs - 1) / pairs;
+  double t = static_cast<double>(waves) * ceil_div(a->k, pair::kBK) * 0.44 + 2.0;
+  if (a->op == CB200_GEMM_RMSNORM) t += 2.5 + static_cast<double>(a->m) * a->k * (a->gamma ? 4.0 : 2.0) / 6.5e6;
+  return t;
 }
 
 template <int MODE, typename T>

@@ -590,7 +590,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
 }
 
 // ------------------------------------------------------------------------------------- host side
-bool gemm_pair_supported(const cb200_gemm_args* a, int sms);
+double gemm_pair_estimate_us(const cb200_gemm_args* a, int sms);
 size_t gemm_pair_prepass_bytes(const cb200_gemm_args* a);
 int launch_gemm_pair(const cb200_gemm_args* a, int* status, void* scratch, const CUtensorMap& tm_a,
                      const CUtensorMap& tm_b0, const CUtensorMap& tm_b1, cudaStream_t stream);
@@ -607,6 +607,10 @@ struct GemmSetup {
   size_t ws_needed, partials_off, counters_off, prepass_off;
   CUtensorMap tm_a, tm_b0, tm_b1;
 };
+
+// How many clusters of `size` CTAs of the cluster GEMM variant can be resident at once (they must fit
+// inside GPCs, so it is less than SMs / size for the larger sizes); cached per variant, size and device.
+int cluster_capacity(int mode, bool f16, int nbw, int size);
 
 int plan_gemm(const cb200_gemm_args* a, GemmSetup* s, bool need_maps) {
   if (!a) return CB200_ERR_BAD_ARG;
@@ -632,30 +636,35 @@ int plan_gemm(const cb200_gemm_args* a, GemmSetup* s, bool need_maps) {
   p.kblocks = ceil_div(a->k, kBK);
   // Automatic plan: whole tiles, or the K parts of a tile as one thread-block cluster (reduced through
   // distributed shared memory), whichever a small cost model says finishes first. Per CTA and K block
-  // the MMAs take about 684 clocks for a 256-column tile and 400 for a 128-column one (measured
-  // instruction costs) or the time to pull the block's operands, whichever is longer; a cluster reduce moves
+  // the MMAs take about 0.56 us for a 256-column tile and 0.33 us for a 128-column one (sustained rates
+  // measured on full-size runs, clocks under the power cap included) or the time to pull the block's
+  // operands, whichever is longer; a cluster reduce moves
   // (S - 1) / S of an fp32 tile at about 25 KB/us; tiles beyond one wave of SMs queue up. The stream-K walk with a workspace fix-up stays for explicit split factors
   // and CTA limits: its last-arriver reduce costs several microseconds per cut tile.
   int auto_split = 0;
+  double best = 0.0;  // the cost model's estimate for the single-CTA kernel, us
   if (a->split_k <= 0 && a->max_ctas == 0) {
-    double best = 0.0;
     const int rows_live = a->m < kBM ? a->m : kBM;
     for (int nbw = 2; nbw <= (a->op == CB200_GEMM_SWIGLU ? 2 : 4); nbw *= 2) {
       const long long tl = static_cast<long long>(p.tiles_m) * ceil_div(a->n, nbw * kChunkN);
-      const double kb_us = ((nbw == 4 || a->op == CB200_GEMM_SWIGLU) ? 684.0 : 400.0) / 1900.0;
+      const double kb_us = (nbw == 4 || a->op == CB200_GEMM_SWIGLU) ? 0.56 : 0.33;
       const int umma_n = nbw * kChunkN * (a->op == CB200_GEMM_SWIGLU ? 2 : 1);
       int smax = tl <= grid_max ? static_cast<int>(grid_max / tl) : 1;
       if (smax > 8) smax = 8;
       if (smax > p.kblocks / 4) smax = p.kblocks / 4;
       if (smax < 1) smax = 1;
-      // operand bytes a CTA pulls per K block (A rows that exist + B chunks) at about 70 KB/us per SM
-      const double kb_mem_us = (rows_live * kBK * 2.0 + umma_n * kBK * 2.0) / 70000.0;
+      // operand bytes a CTA pulls per K block (A rows that exist + B chunks) at about 90 KB/us per SM
+      const double kb_mem_us = (rows_live * kBK * 2.0 + umma_n * kBK * 2.0) / 90000.0;
       const double kb_cost = kb_us > kb_mem_us ? kb_us : kb_mem_us;
       for (int sp = 1; sp <= smax; ++sp) {
-        const long long waves = (tl * sp + grid_max - 1) / grid_max;
+        long long waves = (tl * sp + grid_max - 1) / grid_max;
+        if (sp > 1) {  // clusters that do not all fit at once run in waves
+          const int cap = cluster_capacity(a->op, a->dtype == CB200_F16, nbw, sp);
+          if (cap <= 0) continue;
+          waves = (tl + cap - 1) / cap;
+        }
         double t = static_cast<double>(waves) * ceil_div(p.kblocks, sp) * kb_cost;
-        // park + reduce, and half a microsecond per extra cluster member (measured: wide clusters start late)
-        if (sp > 1) t += rows_live * umma_n * 4.0 * (sp - 1) / sp / 25000.0 + 1.0 + 0.5 * (sp - 1);
+        if (sp > 1) t += rows_live * umma_n * 4.0 * (sp - 1) / sp / 25000.0 + 1.0;  // park + reduce
         if (best == 0.0 || t < best * 0.97) {  // ties go to the earlier (narrower, less split) candidate
           best = t;
           s->nbw = nbw;
@@ -688,7 +697,14 @@ int plan_gemm(const cb200_gemm_args* a, GemmSetup* s, bool need_maps) {
   const int S = p.chunks_per_tile;
   s->cluster = S >= 2 && (S <= 8 || S == 16) && chunks <= grid_max && a->max_ctas == 0;
   if (s->cluster) s->grid = static_cast<int>(chunks);
-  s->pair = gemm_pair_supported(a, sms);
+  {
+    // CTA pairs when the same model says they finish first (split_k == 1 asks for whole tiles: compare
+    // against the whole-tile plan's waves)
+    const double t_pair = gemm_pair_estimate_us(a, sms);
+    double t_single = best;
+    if (t_single == 0.0) t_single = static_cast<double>((tiles + grid_max - 1) / grid_max) * p.kblocks * (s->nbw == 4 || a->op == CB200_GEMM_SWIGLU ? 0.56 : 0.33);
+    s->pair = t_pair > 0.0 && t_pair < t_single;
+  }
   if (s->pair) {
     s->cluster = false;
     p.chunk_kblocks = p.kblocks;
@@ -779,6 +795,50 @@ int dispatch_gemm(const GemmSetup& s, cudaStream_t st) {
     case CB200_GEMM_RMSNORM: return s.nbw == 4 ? launch_gemm<1, T, 4>(s, st) : launch_gemm<1, T, 2>(s, st);
     default: return launch_gemm<2, T, 2>(s, st);
   }
+}
+
+template <int MODE, typename T, int NBW>
+int query_cluster_capacity(int size) {
+  using Plan = GemmPlan<MODE, NBW>;
+  auto kern = gemm_kernel<MODE, T, NBW, true>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Plan::kSmemBytes) != cudaSuccess) return 0;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(size * 64, 1, 1);
+  cfg.blockDim = dim3(Plan::kThreads, 1, 1);
+  cfg.dynamicSmemBytes = Plan::kSmemBytes;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = size;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return 0;
+  }
+  return n;
+}
+
+int cluster_capacity(int mode, bool f16, int nbw, int size) {
+  static int cache[16][3][2][2][9] = {};  // device, mode, dtype, width, size; 0 = not asked yet, -1 = none
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16 || size < 2 || size > 8) return 0;
+  int& c = cache[dev][mode][f16 ? 0 : 1][nbw == 4 ? 1 : 0][size];
+  if (c == 0) {
+    int n = 0;
+    if (mode == CB200_GEMM_MATMUL)
+      n = f16 ? (nbw == 4 ? query_cluster_capacity<0, __half, 4>(size) : query_cluster_capacity<0, __half, 2>(size))
+              : (nbw == 4 ? query_cluster_capacity<0, __nv_bfloat16, 4>(size) : query_cluster_capacity<0, __nv_bfloat16, 2>(size));
+    else if (mode == CB200_GEMM_RMSNORM)
+      n = f16 ? (nbw == 4 ? query_cluster_capacity<1, __half, 4>(size) : query_cluster_capacity<1, __half, 2>(size))
+              : (nbw == 4 ? query_cluster_capacity<1, __nv_bfloat16, 4>(size) : query_cluster_capacity<1, __nv_bfloat16, 2>(size));
+    else
+      n = f16 ? query_cluster_capacity<2, __half, 2>(size) : query_cluster_capacity<2, __nv_bfloat16, 2>(size);
+    c = n > 0 ? n : -1;
+  }
+  return c;
 }
 
 }  // namespace

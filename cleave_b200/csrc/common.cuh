@@ -198,11 +198,12 @@ __device__ __forceinline__ void umma_f16_pair(uint32_t d_tmem, uint64_t adesc, u
       : "memory");
 }
 // Arrives on the barrier at the same shared-memory offset in both CTAs of the pair.
-__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+// `mask`: the cluster ranks of the two CTAs (3 for a cluster that is one pair).
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar, uint16_t mask = 3) {
   asm volatile(
       "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
           smem_u32(bar)),
-      "h"(static_cast<uint16_t>(3))
+      "h"(mask)
       : "memory");
 }
 __device__ __forceinline__ void mbar_arrive_remote(uint64_t* local_bar, uint32_t rank) {

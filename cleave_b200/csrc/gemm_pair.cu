@@ -61,7 +61,11 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
   tm = first + (r - tn * rows);
 }
 
-template <int MODE, typename T>
+// KS > 1: the K dimension of a tile is split over KS pairs that form one cluster of 2 KS CTAs (ranks 2 k and
+// 2 k + 1 are pair k); every pair accumulates its K part, parks the accumulator in its idle pipeline
+// stages, and CTA (k, half) sums rows [k, k + 1) * 128 / KS of its half over the pairs through distributed
+// shared memory, in pair order, before the epilogue. One tile per cluster (the grid is tiles x 2 KS).
+template <int MODE, typename T, int KS>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b0,
                  const __grid_constant__ CUtensorMap tm_b1, const Params p) {
@@ -75,7 +79,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_empty + 2);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const uint32_t rank = cluster_ctarank();  // 0 = first CTA of the pair (issues the MMAs)
+  const uint32_t crank = cluster_ctarank();
+  const uint32_t rank = crank & 1;          // 0 = first CTA of the pair (issues the MMAs)
+  const uint32_t kpart = crank >> 1;        // which K part this pair accumulates (KS > 1)
+  const uint32_t lead = crank & ~1u;        // cluster rank of the pair's first CTA
+  const uint16_t pair_mask = static_cast<uint16_t>(3u << lead);
 
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -101,8 +109,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_holder);
 
-  const int pair_id = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  const int pair_id = blockIdx.x / (2 * KS), n_pairs = gridDim.x / (2 * KS);
   const int tiles = p.tiles_m * p.tiles_n;
+  const int kb_per = ceil_div(p.kblocks, KS);
+  const int kb0 = static_cast<int>(kpart) * kb_per, kb1 = min(p.kblocks, kb0 + kb_per);
   constexpr int kTileN = MODE == 2 ? 128 : 256;  // output columns per tile
 
   if (warp == 0) {
@@ -114,7 +124,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
       const int row0 = tm * 256 + static_cast<int>(rank) * kBM;
       const int col0 = MODE == 2 ? tn * 128 : tn * 256 + static_cast<int>(rank) * 128;
-      for (int kb = 0; kb < p.kblocks; ++kb) {
+      for (int kb = kb0; kb < kb1; ++kb) {
         mbar_wait(&empty_bar[stage], phase ^ 1, p.status, kFaultEmptyBarrier);
         if (lane == 0) {
           uint8_t* a_dst = stages + stage * kStageBytes;
@@ -129,6 +139,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         if (++stage == kStages) { stage = 0; phase ^= 1; }
       }
     }
+    if constexpr (KS > 1) {  // the two meetings of the split-K combine
+      cluster_sync();
+      cluster_sync();
+    }
   } else if (warp == 1) {
     // ================================================================ MMA issuer (first CTA only)
     if (rank == 0) {
@@ -138,7 +152,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         mbar_wait(&acc_empty[buf], acc_phase ^ 1, p.status, kFaultTmemBarrier);
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * kUmmaN;
-        for (int kb = 0; kb < p.kblocks; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           mbar_wait(&full_bar[stage], phase, p.status, kFaultFullBarrier);
           tc_fence_after();
           if (lane == 0) {
@@ -148,17 +162,21 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             for (int k = 0; k < kBK / 16; ++k) {
               const uint64_t adesc = umma_smem_desc(a_addr + k * 32, 16, 8 * 128);
               const uint64_t bdesc = umma_smem_desc(b_addr + k * 16 * 128, kBChunkBytes, 8 * 128);
-              umma_f16_pair(d_tmem, adesc, bdesc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+              umma_f16_pair(d_tmem, adesc, bdesc, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
             }
-            umma_commit_pair(&empty_bar[stage]);
+            umma_commit_pair(&empty_bar[stage], pair_mask);
           }
           __syncwarp();
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
-        if (lane == 0) umma_commit_pair(&acc_full[buf]);
+        if (lane == 0) umma_commit_pair(&acc_full[buf], pair_mask);
         __syncwarp();
         if (++buf == 2) { buf = 0; acc_phase ^= 1; }
       }
+    }
+    if constexpr (KS > 1) {
+      cluster_sync();
+      cluster_sync();
     }
   } else {
     // ================================================================ epilogue (both CTAs, own rows)
@@ -177,6 +195,64 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         if (p.row_scale != nullptr && gr < p.M) row_scale = __ldg(p.row_scale + gr);
       }
       const uint32_t t_acc = tmem_base + buf * kUmmaN + (static_cast<uint32_t>(quarter * 32) << 16);
+      if constexpr (KS > 1) {
+        // ---- park this pair's partial accumulator: [column group of 32][row][8 pieces of 16 bytes], piece i of
+        // row r at i ^ (r & 7) (conflict-free stores); the stages are idle: every MMA of the tile has completed
+        float* stg = reinterpret_cast<float*>(stages);
+#pragma unroll 1
+        for (int c0 = 0; c0 < kUmmaN; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32(t_acc + c0, r);
+          tmem_ld_wait();
+          float4* dst = reinterpret_cast<float4*>(stg + (static_cast<size_t>(c0 >> 5) * kBM + row) * 32);
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            dst[j ^ (row & 7)] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                             __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+        }
+        cluster_sync();
+        {
+          // CTA (kpart, half) owns rows [kpart, kpart + 1) * 128 / KS of its half; a warp reads 512 contiguous
+          // bytes of a peer per load (four rows of one column group); pairs are added in order
+          constexpr int kGroupsOut = kTileN / 32, kRowsMine = kBM / KS;
+          const int r_lo = static_cast<int>(kpart) * kRowsMine;
+          const uint32_t stg_u32 = smem_u32(stg);
+          const int ewarp = (tid - 64) >> 5;
+          for (int wi = ewarp; wi < (kRowsMine / 4) * kGroupsOut; wi += 4) {
+            const int g = wi % kGroupsOut, rl = r_lo + (wi / kGroupsOut) * 4 + (lane >> 3);
+            const uint32_t off = ((static_cast<uint32_t>(g) * kBM + rl) * 32) * 4 + (lane & 7) * 16;
+            float v[4] = {0.f, 0.f, 0.f, 0.f}, up[4] = {0.f, 0.f, 0.f, 0.f};
+            float4 a[KS], bq[KS];
+#pragma unroll
+            for (int kp = 0; kp < KS; ++kp) {
+              const uint32_t base = dsmem_addr(stg_u32, rank + 2 * kp);
+              a[kp] = dsmem_ld_v4(base + off);
+              if constexpr (MODE == 2) bq[kp] = dsmem_ld_v4(base + off + kGroupsOut * kBM * 32 * 4);
+            }
+#pragma unroll
+            for (int kp = 0; kp < KS; ++kp) {
+              v[0] += a[kp].x; v[1] += a[kp].y; v[2] += a[kp].z; v[3] += a[kp].w;
+              if constexpr (MODE == 2) { up[0] += bq[kp].x; up[1] += bq[kp].y; up[2] += bq[kp].z; up[3] += bq[kp].w; }
+            }
+            const int grow = tm * 256 + static_cast<int>(rank) * kBM + rl;
+            const int gcol = tn * kTileN + g * 32 + (((lane & 7) ^ (rl & 7)) << 2);  // undo the swizzle
+            if (grow < p.M && gcol < p.N) {
+              float sc = 1.f;
+              if constexpr (MODE == 0) {
+                if (p.row_scale != nullptr) sc = __ldg(p.row_scale + grow);
+              }
+              float o[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) o[j] = MODE == 2 ? v[j] / (1.f + __expf(-v[j])) * up[j] : v[j] * sc;
+              uint2 pk;
+              pk.x = pack2<T>(o[0], o[1]);
+              pk.y = pack2<T>(o[2], o[3]);
+              *reinterpret_cast<uint2*>(yout + static_cast<size_t>(grow) * p.N + gcol) = pk;
+            }
+          }
+        }
+        cluster_sync();  // nobody leaves while a peer still reads its shared memory (one tile per cluster)
+      } else {
 #pragma unroll 1
       for (int c0 = 0; c0 < kTileN; c0 += 32) {
         uint32_t r[32], r2[32];
@@ -207,7 +283,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive_remote(&acc_empty[buf], 0);  // the first CTA's MMA thread waits for all eight warps
+      if (lane == 0) mbar_arrive_remote(&acc_empty[buf], lead);  // the first CTA's MMA thread waits for all eight warps
+      }
       if (++buf == 2) { buf = 0; acc_phase ^= 1; }
     }
   }
@@ -264,23 +341,81 @@ __global__ void __launch_bounds__(128) rmsnorm_prepass_kernel(const T* __restric
 }  // namespace pair
 
 // ------------------------------------------------------------------------------------- host side
-// Estimated time (us) of the pair kernel on this problem, or a negative value when it does not apply.
-// One 256 x 256 x 64 block of MMAs costs a pair about 0.44 us (sustained rate of full-size runs);
-// tiles beyond one wave of pairs queue up; RMSNorm adds its pass over X.
-double gemm_pair_estimate_us(const cb200_gemm_args* a, int sms) {
-  if (a->split_k > 1 || a->max_ctas != 0 || a->m < 256) return -1.0;
-  const long long tiles = static_cast<long long>(ceil_div(a->m, 256)) * ceil_div(a->n, a->op == CB200_GEMM_SWIGLU ? 128 : 256);
-  const int pairs = sms / 2;
-  const long long waves = (tiles + pairs - 1) / pairs;
-  double t = static_cast<double>(waves) * ceil_div(a->k, pair::kBK) * 0.44 + 2.0;
-  if (a->op == CB200_GEMM_RMSNORM) t += 2.5 + static_cast<double>(a->m) * a->k * (a->gamma ? 4.0 : 2.0) / 6.5e6;
-  return t;
+template <int MODE, typename T, int KS>
+static int query_pair_capacity() {
+  auto kern = pair::gemm_pair_kernel<MODE, T, KS>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, pair::kSmemBytes) != cudaSuccess) return 0;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * KS * 64, 1, 1);
+  cfg.blockDim = dim3(pair::kThreads, 1, 1);
+  cfg.dynamicSmemBytes = pair::kSmemBytes;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2 * KS;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return 0;
+  }
+  return n;
 }
 
-template <int MODE, typename T>
-static int launch_pair_kernel(const pair::Params& p, const CUtensorMap& ta, const CUtensorMap& tb0,
-                              const CUtensorMap& tb1, cudaStream_t stream) {
-  auto kern = pair::gemm_pair_kernel<MODE, T>;
+// Clusters of 2 KS CTAs of the pair kernel that can be resident at once; cached per device.
+static int pair_capacity(bool swiglu, bool f16, int ks) {
+  static int cache[16][2][2][3] = {};  // 0 = not asked yet, -1 = none
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16) return 0;
+  const int ki = ks == 1 ? 0 : ks == 2 ? 1 : 2;
+  int& c = cache[dev][swiglu ? 1 : 0][f16 ? 0 : 1][ki];
+  if (c == 0) {
+    int n = 0;
+    if (swiglu) {
+      if (f16) n = ks == 1 ? query_pair_capacity<2, __half, 1>() : ks == 2 ? query_pair_capacity<2, __half, 2>() : query_pair_capacity<2, __half, 4>();
+      else n = ks == 1 ? query_pair_capacity<2, __nv_bfloat16, 1>() : ks == 2 ? query_pair_capacity<2, __nv_bfloat16, 2>() : query_pair_capacity<2, __nv_bfloat16, 4>();
+    } else {
+      if (f16) n = ks == 1 ? query_pair_capacity<0, __half, 1>() : ks == 2 ? query_pair_capacity<0, __half, 2>() : query_pair_capacity<0, __half, 4>();
+      else n = ks == 1 ? query_pair_capacity<0, __nv_bfloat16, 1>() : ks == 2 ? query_pair_capacity<0, __nv_bfloat16, 2>() : query_pair_capacity<0, __nv_bfloat16, 4>();
+    }
+    c = n > 0 ? n : -1;
+  }
+  return c;
+}
+
+// Estimated time (us) of the pair kernel on this problem and the K split (pairs per cluster) that gives it, or
+// a negative value when the kernel does not apply. One 256 x 256 x 64 block of MMAs costs a pair about
+// 0.44 us (sustained rate of full-size runs); tiles beyond one wave of clusters queue up; a split adds parking
+// the accumulator and a reduce at about 25 KB/us; RMSNorm adds its pass over X.
+double gemm_pair_estimate_us(const cb200_gemm_args* a, int sms, int* ks_out) {
+  (void)sms;
+  if (a->split_k > 1 || a->max_ctas != 0 || a->m < 256) return -1.0;
+  const bool swiglu = a->op == CB200_GEMM_SWIGLU, f16 = a->dtype == CB200_F16;
+  const long long tiles = static_cast<long long>(ceil_div(a->m, 256)) * ceil_div(a->n, swiglu ? 128 : 256);
+  const int kblocks = ceil_div(a->k, pair::kBK);
+  double best = -1.0;
+  for (int ks = 1; ks <= 4; ks *= 2) {
+    if (ks > 1 && (a->split_k == 1 || kblocks / ks < 8)) break;  // split_k == 1 asks for whole tiles
+    const int cap = pair_capacity(swiglu, f16, ks);
+    if (cap <= 0) continue;
+    const long long waves = (tiles + cap - 1) / cap;
+    double t = static_cast<double>(waves) * ceil_div(kblocks, ks) * 0.44 + 2.0;
+    if (ks > 1) t += 1.0 + (128.0 / ks) * 256.0 * 4.0 * (ks - 1) / 25000.0;
+    if (best < 0.0 || t < best * 0.97) {
+      best = t;
+      *ks_out = ks;
+    }
+  }
+  if (best > 0.0 && a->op == CB200_GEMM_RMSNORM) best += 2.5 + static_cast<double>(a->m) * a->k * (a->gamma ? 4.0 : 2.0) / 6.5e6;
+  return best;
+}
+
+template <int MODE, typename T, int KS>
+static int launch_pair_kernel_ks(const pair::Params& p, const CUtensorMap& ta, const CUtensorMap& tb0,
+                                 const CUtensorMap& tb1, cudaStream_t stream) {
+  auto kern = pair::gemm_pair_kernel<MODE, T, KS>;
   CB200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, pair::kSmemBytes));
   cudaLaunchConfig_t cfg = {};
   cfg.blockDim = dim3(pair::kThreads, 1, 1);
@@ -288,29 +423,33 @@ static int launch_pair_kernel(const pair::Params& p, const CUtensorMap& ta, cons
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.x = 2 * KS;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  // The tiles are dealt round-robin to the pairs, so the grid must be exactly the number of pairs
-  // that are resident at once (SMs that cannot form a pair inside their GPC stay idle).
-  static int resident_pairs[16] = {};
-  int dev = 0;
-  CB200_CUDA_TRY(cudaGetDevice(&dev));
-  int pairs = (dev >= 0 && dev < 16) ? resident_pairs[dev] : 0;
-  if (pairs == 0) {
-    cfg.gridDim = dim3((sm_count() / 2) * 2, 1, 1);
-    CB200_CUDA_TRY(cudaOccupancyMaxActiveClusters(&pairs, kern, &cfg));
-    if (pairs <= 0) return CB200_ERR_CUDA;
-    if (dev >= 0 && dev < 16) resident_pairs[dev] = pairs;
-  }
   const int tiles = p.tiles_m * p.tiles_n;
-  if (pairs > tiles) pairs = tiles;
-  cfg.gridDim = dim3(2 * pairs, 1, 1);
+  if (KS == 1) {
+    // The tiles are dealt round-robin to the pairs, so the grid must be exactly the number of pairs
+    // that are resident at once (SMs that cannot form a pair inside their GPC stay idle).
+    int pairs = pair_capacity(MODE == 2, std::is_same<T, __half>::value, 1);
+    if (pairs <= 0) return CB200_ERR_CUDA;
+    if (pairs > tiles) pairs = tiles;
+    cfg.gridDim = dim3(2 * pairs, 1, 1);
+  } else {
+    cfg.gridDim = dim3(static_cast<unsigned>(tiles) * 2 * KS, 1, 1);  // one tile per cluster
+  }
   CB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, ta, tb0, tb1, p));
   CB200_CUDA_TRY(cudaGetLastError());
   return CB200_OK;
+}
+
+template <int MODE, typename T>
+static int launch_pair_kernel(const pair::Params& p, int ks, const CUtensorMap& ta, const CUtensorMap& tb0,
+                              const CUtensorMap& tb1, cudaStream_t stream) {
+  if (ks == 4) return launch_pair_kernel_ks<MODE, T, 4>(p, ta, tb0, tb1, stream);
+  if (ks == 2) return launch_pair_kernel_ks<MODE, T, 2>(p, ta, tb0, tb1, stream);
+  return launch_pair_kernel_ks<MODE, T, 1>(p, ta, tb0, tb1, stream);
 }
 
 size_t gemm_pair_prepass_bytes(const cb200_gemm_args* a) {
@@ -319,7 +458,7 @@ size_t gemm_pair_prepass_bytes(const cb200_gemm_args* a) {
 }
 
 // `scratch`: gemm_pair_prepass_bytes(a) bytes of the caller's workspace (RMSNorm only).
-int launch_gemm_pair(const cb200_gemm_args* a, int* status, void* scratch, const CUtensorMap& tm_a,
+int launch_gemm_pair(const cb200_gemm_args* a, int* status, void* scratch, int ks, const CUtensorMap& tm_a,
                      const CUtensorMap& tm_b0, const CUtensorMap& tm_b1, cudaStream_t stream) {
   const int sms = sm_count();
   if (sms <= 0) return CB200_ERR_CUDA;
@@ -332,8 +471,8 @@ int launch_gemm_pair(const cb200_gemm_args* a, int* status, void* scratch, const
   p.kblocks = ceil_div(a->k, pair::kBK);
   const bool f16 = a->dtype == CB200_F16;
   if (a->op == CB200_GEMM_SWIGLU)
-    return f16 ? launch_pair_kernel<2, __half>(p, tm_a, tm_b0, tm_b1, stream)
-               : launch_pair_kernel<2, __nv_bfloat16>(p, tm_a, tm_b0, tm_b1, stream);
+    return f16 ? launch_pair_kernel<2, __half>(p, ks, tm_a, tm_b0, tm_b1, stream)
+               : launch_pair_kernel<2, __nv_bfloat16>(p, ks, tm_a, tm_b0, tm_b1, stream);
   if (a->op == CB200_GEMM_RMSNORM) {
     // the row factors (and with gamma the scaled copy of X) in one pass over X, then the plain matmul
     const bool scale = a->gamma != nullptr;
@@ -351,8 +490,8 @@ int launch_gemm_pair(const cb200_gemm_args* a, int* status, void* scratch, const
     CB200_CUDA_TRY(cudaGetLastError());
     p.row_scale = rscale;
     if (!scale)
-      return f16 ? launch_pair_kernel<0, __half>(p, tm_a, tm_b0, tm_b1, stream)
-                 : launch_pair_kernel<0, __nv_bfloat16>(p, tm_a, tm_b0, tm_b1, stream);
+      return f16 ? launch_pair_kernel<0, __half>(p, ks, tm_a, tm_b0, tm_b1, stream)
+                 : launch_pair_kernel<0, __nv_bfloat16>(p, ks, tm_a, tm_b0, tm_b1, stream);
     CUtensorMap tm_xs;
     uint64_t dims[2] = {static_cast<uint64_t>(a->k), static_cast<uint64_t>(a->m)};
     uint64_t strides[1] = {static_cast<uint64_t>(a->k) * 2};
@@ -360,11 +499,11 @@ int launch_gemm_pair(const cb200_gemm_args* a, int* status, void* scratch, const
     if (!encode_tensor_map(&tm_xs, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, xs, dims,
                            strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
       return CB200_ERR_CUDA;
-    return f16 ? launch_pair_kernel<0, __half>(p, tm_xs, tm_b0, tm_b1, stream)
-               : launch_pair_kernel<0, __nv_bfloat16>(p, tm_xs, tm_b0, tm_b1, stream);
+    return f16 ? launch_pair_kernel<0, __half>(p, ks, tm_xs, tm_b0, tm_b1, stream)
+               : launch_pair_kernel<0, __nv_bfloat16>(p, ks, tm_xs, tm_b0, tm_b1, stream);
   }
-  return f16 ? launch_pair_kernel<0, __half>(p, tm_a, tm_b0, tm_b1, stream)
-             : launch_pair_kernel<0, __nv_bfloat16>(p, tm_a, tm_b0, tm_b1, stream);
+  return f16 ? launch_pair_kernel<0, __half>(p, ks, tm_a, tm_b0, tm_b1, stream)
+             : launch_pair_kernel<0, __nv_bfloat16>(p, ks, tm_a, tm_b0, tm_b1, stream);
 }
 
 }  // namespace cb200

@@ -590,9 +590,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
 }
 
 // ------------------------------------------------------------------------------------- host side
-double gemm_pair_estimate_us(const cb200_gemm_args* a, int sms);
+double gemm_pair_estimate_us(const cb200_gemm_args* a, int sms, int* ks_out);
 size_t gemm_pair_prepass_bytes(const cb200_gemm_args* a);
-int launch_gemm_pair(const cb200_gemm_args* a, int* status, void* scratch, const CUtensorMap& tm_a,
+int launch_gemm_pair(const cb200_gemm_args* a, int* status, void* scratch, int ks, const CUtensorMap& tm_a,
                      const CUtensorMap& tm_b0, const CUtensorMap& tm_b1, cudaStream_t stream);
 
 namespace {
@@ -604,6 +604,7 @@ struct GemmSetup {
   int mode, nbw, grid;
   bool cluster;  // split-K inside a thread-block cluster (tiny outputs)
   bool pair;     // whole 256 x 256 tiles on CTA pairs (gemm_pair.cu)
+  int pair_ks;   // pairs per cluster: the K split of the pair kernel
   size_t ws_needed, partials_off, counters_off, prepass_off;
   CUtensorMap tm_a, tm_b0, tm_b1;
 };
@@ -700,7 +701,8 @@ int plan_gemm(const cb200_gemm_args* a, GemmSetup* s, bool need_maps) {
   {
     // CTA pairs when the same model says they finish first (split_k == 1 asks for whole tiles: compare
     // against the whole-tile plan's waves)
-    const double t_pair = gemm_pair_estimate_us(a, sms);
+    s->pair_ks = 1;
+    const double t_pair = gemm_pair_estimate_us(a, sms, &s->pair_ks);
     double t_single = best;
     if (t_single == 0.0) t_single = static_cast<double>((tiles + grid_max - 1) / grid_max) * p.kblocks * (s->nbw == 4 || a->op == CB200_GEMM_SWIGLU ? 0.56 : 0.33);
     s->pair = t_pair > 0.0 && t_pair < t_single;
@@ -863,6 +865,6 @@ extern "C" int cb200_gemm(const cb200_gemm_args* a, void* stream) {
   if (rc != CB200_OK) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (s.pair)
-    return launch_gemm_pair(a, s.p.status, static_cast<uint8_t*>(a->workspace) + s.prepass_off, s.tm_a, s.tm_b0, s.tm_b1, st);
+    return launch_gemm_pair(a, s.p.status, static_cast<uint8_t*>(a->workspace) + s.prepass_off, s.pair_ks, s.tm_a, s.tm_b0, s.tm_b1, st);
   return a->dtype == CB200_F16 ? dispatch_gemm<__half>(s, st) : dispatch_gemm<__nv_bfloat16>(s, st);
 }

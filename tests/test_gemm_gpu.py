@@ -83,6 +83,13 @@ def test_swiglu_vs_oracle(m, n, k, split_k):
     ("rmsnorm_matmul", 2048, 4864, 1032, "f16"),
     ("rmsnorm_gamma", 3000, 3336, 200, "bf16"),
     ("rmsnorm_gamma", 1024, 9728, 712, "f16"),
+    # few 256 x 256 tiles and a long K: the K dimension is split over the pairs of one cluster
+    ("matmul", 512, 4096, 4096, "f16"),
+    ("matmul", 256, 4096, 4096, "bf16"),
+    ("matmul", 300, 3336, 2056, "f16"),
+    ("swiglu", 512, 2048, 4096, "bf16"),
+    ("rmsnorm_gamma", 512, 4096, 2048, "f16"),
+    ("rmsnorm_matmul", 257, 4096, 4096, "bf16"),
 ])
 def test_large_gemms_on_cta_pairs(family, m, n, k, dt):
     """Shapes with at least one 256 x 256 tile per CTA pair take the cta_group::2 kernel."""

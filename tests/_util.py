@@ -4,7 +4,7 @@ import numpy as np
 import torch
 
 TORCH_DT = {"f16": torch.float16, "bf16": torch.bfloat16}
-# north-star tolerance for 16-bit outputs against the fp32 reference
+# required tolerance for 16-bit outputs against the fp32 reference
 RTOL, ATOL = 2e-2, 2e-2
 
 

@@ -110,7 +110,7 @@ def test_static_decode_vs_oracle(hq, hkv, sq):
 
 
 def test_static_gqa_decode_full_config_properties():
-    """BASELINE config 3 at full size (batch 8, 32/8 heads, d 128, KV 8192, fp16): compared with
+    """Benchmark configuration 3 at full size (batch 8, 32/8 heads, d 128, KV 8192, fp16): compared with
     the oracle on a sample of kv heads, and invariant under a permutation of the KV positions."""
     g = torch.Generator(device="cpu").manual_seed(0)
     q = torch.randn(8 * 32, 1, 128, generator=g).half()

@@ -137,7 +137,7 @@ def test_repeat_launches_are_bit_identical():
 
 
 def test_linearity_at_full_rmsnorm_config():
-    """BASELINE config 2 at full size (M 64, K 4096, N 11008, fp16): compared with the oracle, and
+    """Benchmark configuration 2 at full size (M 64, K 4096, N 11008, fp16): compared with the oracle, and
     scaling X by 2 leaves RMSNorm(X) @ W unchanged (the norm is scale-invariant when eps is tiny)."""
     g = torch.Generator(device="cpu").manual_seed(0)
     x = torch.randn(64, 4096, generator=g).half()

@@ -91,7 +91,7 @@ def test_static_mla_large_logits_rescale_path():
 
 
 def test_mla_full_config_properties():
-    """BASELINE config 4 at full size (batch 16, 128 heads, 512 + 64, KV 4096, bf16): compared with
+    """Benchmark configuration 4 at full size (batch 16, 128 heads, 512 + 64, KV 4096, bf16): compared with
     the oracle on one request, invariant under a permutation of the KV positions, and repeat
     launches are bit-identical."""
     g = torch.Generator(device="cpu").manual_seed(0)

@@ -231,7 +231,8 @@ def measure(name, build):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default=None, choices=["matmul", "rmsnorm_matmul", "swiglu", "gqa_decode", "mla_decode", "attn_prefill"])
+    ap.add_argument("--op", default=None, choices=["matmul", "rmsnorm_matmul", "swiglu", "gqa_decode", "mla_decode", "attn_prefill", "gqa_paged_ps1",
+                                             "mla_paged_decode"])
     ap.add_argument("--m", type=int, default=4096)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
@@ -245,6 +246,10 @@ def main():
             build = gqa_decode_case
         elif a.op == "mla_decode":
             build = mla_decode_case
+        elif a.op == "gqa_paged_ps1":
+            build = lambda: paged_decode_case(1)  # noqa: E731
+        elif a.op == "mla_paged_decode":
+            build = mla_paged_decode_case
         elif a.op == "attn_prefill":
             build = lambda: attn_prefill_case(32, 8, a.m, a.k if a.k in (64, 128) else 128, torch.bfloat16, False)  # noqa: E731
         else:

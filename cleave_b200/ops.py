@@ -45,7 +45,7 @@ def workspace(kind: str, nbytes: int, device) -> torch.Tensor:
     key = (kind, index, _stream())
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
-        ws = torch.zeros(max(nbytes, 1), dtype=torch.uint8, device=device)
+        ws = torch.zeros(max(nbytes, 256), dtype=torch.uint8, device=device)  # never smaller than the status header
         _workspaces[key] = ws
     return ws
 

@@ -206,3 +206,45 @@ def test_paged_workload_generator_is_seeded_and_ragged():
     assert a == b and len(a) == 18
     assert min(min(l) for _, l in a) >= 1 and max(max(l) for _, l in a) == 8192
     assert any(len(set(l)) > 1 for _, l in a)
+
+
+def test_prefill_operators_in_the_dynamic_registry_and_kernel_text():
+    """The ragged and paged causal prefill operators carry the reference's argument order
+    (python/cleave/dynamic/reference.py:204-258), their kernel text round-trips, and their workload
+    generator is seeded, causal (q_len <= kv_len) and includes a request without queries."""
+    from cleave_b200.codegen import B200CodeGen, make_spec
+    from cleave_b200.pipeline.dynamic import OPERATORS, paged_prefill_workloads
+    from cleave_b200.runtime.compile import _load_main_kernel_from_code
+
+    assert OPERATORS["gqa_ragged_prefill_causal"][1] == ("q", "k", "v", "qo_indptr", "kv_indptr", "sm_scale")
+    assert OPERATORS["gqa_paged_prefill_causal"][1] == ("q", "k_cache", "v_cache", "qo_indptr", "kv_indptr", "kv_indices",
+                                                        "sm_scale")
+    for family in ("gqa_ragged_prefill", "gqa_paged_prefill"):
+        spec = make_spec(family, "bfloat16", dict(num_qo_heads=32, num_kv_heads=8, head_dim=128))
+        text = B200CodeGen().gen(spec)
+        assert text == B200CodeGen().gen(spec)
+        again = _load_main_kernel_from_code(text)
+        assert again.family == family and [p.name for p in again.outputs] == ["OutputNode", "OutputNode_1"]
+        assert again.outputs[1].dtype == "float32" and again.outputs[0].dims == ("total_q", 32, 128)
+    a, b = paged_prefill_workloads(), paged_prefill_workloads()
+    assert a == b and len(a) == 8
+    assert all(q <= k for _, (ql, kl) in a for q, k in zip(ql, kl))
+    assert any(0 in ql for _, (ql, _) in a)
+
+
+def test_oracle_causal_mask_is_end_aligned():
+    """python/cleave/dynamic/reference.py:129-133: query row r of q_len rows sees keys <= kv_len - q_len + r;
+    with one query row the result equals unmasked attention over all keys."""
+    import numpy as np
+
+    from oracle import cleave_oracle as orc
+
+    rng = np.random.default_rng(0)
+    q = rng.standard_normal((2, 3, 16), dtype=np.float32)
+    k = rng.standard_normal((2, 7, 16), dtype=np.float32)
+    v = rng.standard_normal((2, 7, 16), dtype=np.float32)
+    out, lse = orc.attention_masked(q, k, v, 0.25, True, "f16")
+    for r in range(3):
+        want, want_lse = orc.attention_masked(q[:, r:r + 1], k[:, :5 + r], v[:, :5 + r], 0.25, False, "f16")
+        np.testing.assert_allclose(out[:, r:r + 1], want, rtol=1e-3, atol=1e-3)
+        np.testing.assert_allclose(lse[:, r:r + 1], want_lse, rtol=1e-5, atol=1e-5)

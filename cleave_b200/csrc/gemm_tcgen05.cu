@@ -9,7 +9,10 @@
 // fall to the same CTA accumulate in TMEM; a tile finished inside one CTA goes straight through
 // the fused epilogue; a tile cut across CTAs leaves fp32 partials in the workspace and the last
 // CTA to arrive sums them in a fixed order and runs the epilogue (no second launch, nobody
-// waits, bit-stable results).
+// waits, bit-stable results). That walk serves explicit split factors and CTA limits. When the
+// caller leaves the split to the library, plan_gemm picks whole tiles, or the K parts of a tile as
+// one thread-block cluster whose CTAs combine through distributed shared memory (CLUSTER), or the
+// CTA-pair kernel of gemm_pair.cu, from a small cost model.
 //
 // Warp roles: 0 = TMA producer, 1 = MMA issuer (one elected thread) and TMEM owner,
 // 2..5 = epilogue (TMEM -> registers -> global), 6..13 = RMSNorm statistics / gamma scaling of the

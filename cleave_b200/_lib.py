@@ -42,7 +42,22 @@ class GemmArgs(C.Structure):
         ("x", C.c_void_p), ("w", C.c_void_p), ("w1", C.c_void_p), ("gamma", C.c_void_p), ("y", C.c_void_p),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("m", C.c_int32), ("n", C.c_int32), ("k", C.c_int32), ("op", C.c_int32), ("dtype", C.c_int32),
-        ("split_k", C.c_int32), ("max_ctas", C.c_int32), ("eps", C.c_float),
+        ("split_k", C.c_int32), ("max_ctas", C.c_int32), ("eps", C.c_float), ("addend", C.c_void_p),
+    ]
+
+
+class MatmulRowsumArgs(C.Structure):
+    _fields_ = [
+        ("x", C.c_void_p), ("w", C.c_void_p), ("y", C.c_void_p), ("workspace", C.c_void_p),
+        ("workspace_bytes", C.c_size_t), ("m", C.c_int32), ("n", C.c_int32), ("k", C.c_int32), ("dtype", C.c_int32),
+    ]
+
+
+class LoraArgs(C.Structure):
+    _fields_ = [
+        ("x", C.c_void_p), ("w", C.c_void_p), ("a", C.c_void_p), ("b", C.c_void_p), ("y", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("m", C.c_int32), ("n", C.c_int32), ("k", C.c_int32), ("r", C.c_int32), ("dtype", C.c_int32),
     ]
 
 
@@ -67,7 +82,11 @@ class AttnPrefillArgs(C.Structure):
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("num_qo_heads", C.c_int32), ("num_kv_heads", C.c_int32), ("q_len", C.c_int32), ("kv_len", C.c_int32),
         ("head_dim", C.c_int32), ("dtype", C.c_int32), ("causal", C.c_int32), ("sm_scale", C.c_float),
+        ("score_mode", C.c_int32), ("qk_norm", C.c_int32), ("norm_eps", C.c_float),
     ]
+
+
+SCORE_SOFTMAX, SCORE_LINEAR = 0, 1
 
 
 class AttnPrefillRaggedArgs(C.Structure):
@@ -115,6 +134,14 @@ def lib() -> C.CDLL:
         L.cb200_gemm_effective_split.argtypes = [C.POINTER(GemmArgs)]
         L.cb200_gemm.restype = C.c_int
         L.cb200_gemm.argtypes = [C.POINTER(GemmArgs), C.c_void_p]
+        L.cb200_matmul_rowsum_workspace_bytes.restype = C.c_size_t
+        L.cb200_matmul_rowsum_workspace_bytes.argtypes = [C.POINTER(MatmulRowsumArgs)]
+        L.cb200_matmul_rowsum.restype = C.c_int
+        L.cb200_matmul_rowsum.argtypes = [C.POINTER(MatmulRowsumArgs), C.c_void_p]
+        L.cb200_lora_workspace_bytes.restype = C.c_size_t
+        L.cb200_lora_workspace_bytes.argtypes = [C.POINTER(LoraArgs)]
+        L.cb200_lora.restype = C.c_int
+        L.cb200_lora.argtypes = [C.POINTER(LoraArgs), C.c_void_p]
         L.cb200_mla_decode_workspace_bytes.restype = C.c_size_t
         L.cb200_mla_decode_workspace_bytes.argtypes = [C.POINTER(MlaDecodeArgs)]
         L.cb200_mla_decode.restype = C.c_int

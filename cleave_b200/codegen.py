@@ -13,7 +13,8 @@ from dataclasses import dataclass, field
 from .core.errors import CodegenError
 
 FAMILIES = ("matmul", "rmsnorm_matmul", "swiglu", "attention_decode", "mla_decode",
-            "gqa_paged_decode", "mla_paged_decode", "gqa_ragged_prefill", "gqa_paged_prefill")
+            "gqa_paged_decode", "mla_paged_decode", "gqa_ragged_prefill", "gqa_paged_prefill",
+            "matmul_matmul", "qknorm_attention", "matmul_rowsum", "lora")
 FORMAT = 1
 
 
@@ -78,7 +79,14 @@ def default_params(family: str, dtype: str, dims: dict, attrs: dict) -> tuple:
     if family == "swiglu":
         return (P(_ph("x"), dtype, (g("M"), g("K")), "input"), P(_ph("w0"), dtype, (g("K"), g("N")), "input"),
                 P(_ph("w1"), dtype, (g("K"), g("N")), "input"), P("OutputNode", dtype, (g("M"), g("N")), "output"))
-    if family == "attention_decode":
+    if family == "matmul_rowsum":
+        return (P(_ph("x"), dtype, (g("M"), g("K")), "input"), P(_ph("w"), dtype, (g("K"), g("N")), "input"),
+                P("OutputNode", dtype, (g("M"), 1), "output"))
+    if family == "lora":
+        return (P(_ph("x"), dtype, (g("M"), g("K")), "input"), P(_ph("w"), dtype, (g("K"), g("N")), "input"),
+                P(_ph("a"), dtype, (g("K"), g("R")), "input"), P(_ph("b"), dtype, (g("R"), g("N")), "input"),
+                P("OutputNode", dtype, (g("M"), g("N")), "output"))
+    if family in ("attention_decode", "matmul_matmul", "qknorm_attention"):
         return (P(_ph("q"), dtype, (g("HQ"), g("SQ"), g("D")), "input"),
                 P(_ph("k"), dtype, (g("HKV"), g("SKV"), g("D")), "input"),
                 P(_ph("v"), dtype, (g("HKV"), g("SKV"), g("D")), "input"),
@@ -183,8 +191,9 @@ def recognise(obj) -> KernelSpec:
     """Classify a scheduled plan by the op pattern of its flat graph and read the shapes off its
     placeholders. Patterns (op class names of python/cleave/ir/ops): ``{Matmul}`` -> matmul;
     ``{Matmul, Mul, ReduceSum, Div, RSqrt|Sqrt}`` -> rmsnorm_matmul; ``{Matmul x2, Silu, Mul}`` ->
-    swiglu; ``{Matmul x2, Exp, ReduceSum, Div}`` -> attention_decode, with a third score matmul and an
-    ``Add`` -> mla_decode. Leading ``SplitView`` nodes carry the split factor. Tile shapes and
+    swiglu; ``{Matmul x2, Exp, ReduceSum, Div}`` -> attention_decode (with ``RSqrt`` -> qknorm_attention,
+    without ``Exp`` -> matmul_matmul), with a third score matmul and an ``Add`` -> mla_decode;
+    ``{Matmul, ReduceSum}`` -> matmul_rowsum; ``{Matmul x3, Add}`` over four placeholders -> lora. Leading ``SplitView`` nodes carry the split factor. Tile shapes and
     thread counts in the plan are hints scored for another architecture and are not used."""
     if isinstance(obj, (list, tuple)):  # [partial, combine]: the partial carries the structure
         if not obj:
@@ -209,6 +218,8 @@ def recognise(obj) -> KernelSpec:
         if k != k2:
             raise CodegenError(f"matmul placeholders do not chain: {shapes}")
         fam = "rmsnorm_matmul" if "ReduceSum" in kinds and ("RSqrt" in kinds or "Sqrt" in kinds) else "matmul"
+        if fam == "matmul" and "ReduceSum" in kinds:
+            return make_spec("matmul_rowsum", dtype, {"M": m, "N": n, "K": k}, split=split)
         attrs = {}
         if fam == "rmsnorm_matmul":
             eps = [getattr(getattr(n, "op", None), "value", None) for n, kd in zip(nodes, kinds) if kd == "Add"]
@@ -217,9 +228,20 @@ def recognise(obj) -> KernelSpec:
     if n_mm == 2 and "Silu" in kinds:
         (m, k), (_, n) = shapes[0][-2:], shapes[1][-2:]
         return make_spec("swiglu", dtype, {"M": m, "N": n, "K": k}, split=split)
-    if "Exp" in kinds and n_mm == 2 and len(shapes) == 3:
+    if n_mm == 2 and len(shapes) == 3 and all(len(sh) >= 3 for sh in shapes):
         (hq, sq, d), (hkv, skv, _) = shapes[0][-3:], shapes[1][-3:]
-        return make_spec("attention_decode", dtype, {"HQ": hq, "HKV": hkv, "SQ": sq, "SKV": skv, "D": d}, split=split)
+        dims = {"HQ": hq, "HKV": hkv, "SQ": sq, "SKV": skv, "D": d}
+        if "Exp" not in kinds:
+            return make_spec("matmul_matmul", dtype, dims, split=split)
+        if "RSqrt" in kinds or "Sqrt" in kinds:
+            eps = [getattr(getattr(n, "op", None), "value", None) for n, kd in zip(nodes, kinds) if kd == "Add"]
+            return make_spec("qknorm_attention", dtype, dims, split=split,
+                             attrs={"eps": float(next((e for e in eps if e is not None), 0.0))})
+        return make_spec("attention_decode", dtype, dims, split=split)
+    if n_mm == 3 and "Exp" not in kinds and len(shapes) == 4:
+        (m, k), (_, n) = shapes[0][-2:], shapes[1][-2:]
+        r = min(s_[-1] for s_ in shapes)
+        return make_spec("lora", dtype, {"M": m, "N": n, "K": k, "R": r}, split=split)
     if "Exp" in kinds and n_mm == 3 and len(shapes) == 4:
         by_rank = sorted(shapes, key=lambda s: (s[-1], s[-2]))
         (b, h, pe), (_, skv, _), (_, _, d) = by_rank[0], by_rank[1], by_rank[2]

@@ -19,6 +19,7 @@
 
 #include "common.cuh"
 
+#include <algorithm>
 #include <cstring>
 #include <type_traits>
 
@@ -55,6 +56,10 @@ struct Params {
   int batch;             // ragged / paged: requests
   int hq, hkv, sq, skv, q_tiles, causal;
   float scale_log2;
+  int linear;      // 1: no softmax, P = scale * S (the operator (Q K^T) V of demo/matmul_matmul.py)
+  float scale;     // linear mode: the plain factor
+  int q_norm;      // 1: query rows are RMS-normalised (demo/qknorm.py); the row factor is folded into the scale
+  float norm_eps;
 };
 
 // RAGGED: q (total_q, HQ, D), k / v (total_kv, HKV, D) with one (query range, key range) per request;
@@ -303,6 +308,26 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     const uint32_t lane_field = static_cast<uint32_t>(quarter * 32) << 16;
     const int key_limit = p.causal ? min(skv - 1, qrow + off) : skv - 1;  // last key this row sees
     float m_ref = 0.f, l_run = 0.f;
+    // scores are scale_row * (q . k): the softmax scale in log2 units (the plain factor in linear mode)
+    // times, for RMS-normalised queries, rsqrt(mean(q^2) + eps) of this thread's row, taken from the
+    // resident Q tile (K arrives normalised)
+    float scale_row = p.linear ? p.scale : p.scale_log2;
+    if (p.q_norm && nt > 0) {
+      mbar_wait(q_full, 0, p.status, kFaultFullBarrier);
+      float ss = 0.f;
+#pragma unroll
+      for (int c = 0; c < D / 8; ++c) {
+        const uint4 u = *reinterpret_cast<const uint4*>(q_smem + (c >> 3) * C::kChunkBytes + row * 128 +
+                                                         (((c & 7) ^ (row & 7)) << 4));
+        const T* e = reinterpret_cast<const T*>(&u);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float f = static_cast<float>(e[i]);
+          ss = fmaf(f, f, ss);
+        }
+      }
+      scale_row = qrow < sq ? scale_row * rsqrtf(ss * (1.f / D) + p.norm_eps) : 0.f;
+    }
     for (int j = 0; j < nt; ++j) {
       const int sb = j & 1, pb = j & 1;
       mbar_wait(&s_full[sb], (j >> 1) & 1, p.status, kFaultMmaBarrier);
@@ -315,13 +340,36 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_empty[sb]);
       const int k0 = j * kBN;
+      if (p.linear) {
+        // no softmax: P = scale * S rounded to the storage type; keys past the end are zero rows of K
+        mbar_wait(&p_empty[pb], ((j >> 1) & 1) ^ 1, p.status, kFaultMmaBarrier);
+        tc_fence_after();
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          uint32_t pk[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int c = hh * 64 + 2 * i;
+            const float p0 = k0 + c <= key_limit ? __uint_as_float(r[c >> 5][c & 31]) * scale_row : 0.f;
+            const float p1 = k0 + c + 1 <= key_limit ? __uint_as_float(r[(c + 1) >> 5][(c + 1) & 31]) * scale_row : 0.f;
+            pk[i] = pack2<T>(p0, p1);
+          }
+          tmem_st_32x32(tmem_base + lane_field + kColP + pb * 64 + hh * 32, pk);
+        }
+        l_run = 1.f;
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p_full[pb]);
+        continue;
+      }
       float mx = -INFINITY;
       if (k0 + kBN - 1 <= key_limit) {  // whole tile visible to this row
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
-            const float v = __uint_as_float(r[q][i]) * p.scale_log2;
+            const float v = __uint_as_float(r[q][i]) * scale_row;
             r[q][i] = __float_as_uint(v);
             mx = fmaxf(mx, v);
           }
@@ -331,7 +379,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         for (int q = 0; q < 4; ++q) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
-            const float v = k0 + q * 32 + i <= key_limit ? __uint_as_float(r[q][i]) * p.scale_log2 : -INFINITY;
+            const float v = k0 + q * 32 + i <= key_limit ? __uint_as_float(r[q][i]) * scale_row : -INFINITY;
             r[q][i] = __float_as_uint(v);
             mx = fmaxf(mx, v);
           }
@@ -416,7 +464,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         }
       }
     }
-    if (live && p.lse) p.lse[orow] = l_run > 0.f ? m_ref + fast_log2(l_run) : -INFINITY;
+    if (live && p.lse && !p.linear) p.lse[orow] = l_run > 0.f ? m_ref + fast_log2(l_run) : -INFINITY;
   }
 
   tc_fence_before();
@@ -424,6 +472,34 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// RMS-normalises rows of D elements, one warp per row: y = x * rsqrt(mean(x^2) + eps), fp32 statistics,
+// result in the storage type. Used on K ahead of the attention kernel for demo/qknorm.py (K is the small
+// operand: it is read by every query tile, so it is normalised once instead of per tile).
+template <typename T, int D>
+__global__ void __launch_bounds__(256) rms_rows_kernel(const T* __restrict__ x, T* __restrict__ y, long long rows, float eps) {
+  constexpr int kPer = D / 32;  // 2 or 4 elements per lane
+  const int lane = threadIdx.x & 31;
+  const long long stride = static_cast<long long>(gridDim.x) * (blockDim.x >> 5);
+  for (long long r = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); r < rows; r += stride) {
+    T e[kPer];
+    if constexpr (kPer == 4) *reinterpret_cast<uint2*>(e) = *reinterpret_cast<const uint2*>(x + r * D + lane * 4);
+    else *reinterpret_cast<uint32_t*>(e) = *reinterpret_cast<const uint32_t*>(x + r * D + lane * 2);
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < kPer; ++i) {
+      const float f = static_cast<float>(e[i]);
+      ss = fmaf(f, f, ss);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float f = rsqrtf(ss * (1.f / D) + eps);
+#pragma unroll
+    for (int i = 0; i < kPer; ++i) e[i] = static_cast<T>(static_cast<float>(e[i]) * f);
+    if constexpr (kPer == 4) *reinterpret_cast<uint2*>(y + r * D + lane * 4) = *reinterpret_cast<const uint2*>(e);
+    else *reinterpret_cast<uint32_t*>(y + r * D + lane * 2) = *reinterpret_cast<const uint32_t*>(e);
   }
 }
 
@@ -440,7 +516,15 @@ int plan_prefill(const cb200_attn_prefill_args* a) {
   if (a->dtype != CB200_F16 && a->dtype != CB200_BF16) return CB200_ERR_UNSUPPORTED;
   const long long ctas = static_cast<long long>(a->num_qo_heads) * ceil_div(a->q_len, fa::kBM);
   if (ctas >= (1LL << 31)) return CB200_ERR_UNSUPPORTED;
+  if (a->score_mode != CB200_SCORE_SOFTMAX && a->score_mode != CB200_SCORE_LINEAR) return CB200_ERR_BAD_ARG;
+  if (a->qk_norm && !(a->norm_eps >= 0.f)) return CB200_ERR_BAD_ARG;
   return CB200_OK;
+}
+
+// bytes of the normalised copy of K that follows the status header when qk_norm is set
+size_t prefill_knorm_bytes(const cb200_attn_prefill_args* a) {
+  if (!a->qk_norm) return 0;
+  return static_cast<size_t>(a->num_kv_heads) * a->kv_len * a->head_dim * 2;
 }
 
 template <typename T, int D>
@@ -457,6 +541,19 @@ int launch_prefill(const cb200_attn_prefill_args* a, cudaStream_t stream) {
   p.q_tiles = ceil_div(a->q_len, kBM);
   p.causal = a->causal ? 1 : 0;
   p.scale_log2 = a->sm_scale * kLog2e;
+  p.linear = a->score_mode == CB200_SCORE_LINEAR ? 1 : 0;
+  p.scale = a->sm_scale;
+  p.q_norm = a->qk_norm ? 1 : 0;
+  p.norm_eps = a->norm_eps;
+  const void* k_src = a->k;
+  if (a->qk_norm) {
+    T* kn = reinterpret_cast<T*>(static_cast<uint8_t*>(a->workspace) + kWsHeaderBytes);
+    const long long rows = static_cast<long long>(a->num_kv_heads) * a->kv_len;
+    const int blocks = static_cast<int>(std::min<long long>((rows + 7) / 8, 148LL * 8));
+    rms_rows_kernel<T, D><<<blocks, 256, 0, stream>>>(reinterpret_cast<const T*>(a->k), kn, rows, a->norm_eps);
+    CB200_CUDA_TRY(cudaGetLastError());
+    k_src = kn;
+  }
   const CUtensorMapDataType dt = a->dtype == CB200_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   CUtensorMap tm_q, tm_k, tm_v;
   {
@@ -467,7 +564,7 @@ int launch_prefill(const cb200_attn_prefill_args* a, cudaStream_t stream) {
     uint64_t sk[2] = {static_cast<uint64_t>(D) * 2, static_cast<uint64_t>(a->kv_len) * D * 2};
     const CUtensorMapSwizzle sw = CU_TENSOR_MAP_SWIZZLE_128B;
     if (!encode_tensor_map(&tm_q, dt, 3, const_cast<void*>(a->q), dq, sq, box, sw) ||
-        !encode_tensor_map(&tm_k, dt, 3, const_cast<void*>(a->k), dk, sk, box, sw) ||
+        !encode_tensor_map(&tm_k, dt, 3, const_cast<void*>(k_src), dk, sk, box, sw) ||
         !encode_tensor_map(&tm_v, dt, 3, const_cast<void*>(a->v), dk, sk, box, sw))
       return CB200_ERR_CUDA;
   }
@@ -544,7 +641,7 @@ int launch_prefill_ragged(const cb200_attn_prefill_ragged_args* a, cudaStream_t 
 }  // namespace cb200
 
 extern "C" size_t cb200_attn_prefill_workspace_bytes(const cb200_attn_prefill_args* a) {
-  return cb200::plan_prefill(a) == CB200_OK ? cb200::kWsHeaderBytes : 0;
+  return cb200::plan_prefill(a) == CB200_OK ? cb200::kWsHeaderBytes + cb200::prefill_knorm_bytes(a) : 0;
 }
 
 extern "C" int cb200_attn_prefill(const cb200_attn_prefill_args* a, void* stream) {
@@ -555,7 +652,7 @@ extern "C" int cb200_attn_prefill(const cb200_attn_prefill_args* a, void* stream
   if ((reinterpret_cast<uintptr_t>(a->q) | reinterpret_cast<uintptr_t>(a->k) | reinterpret_cast<uintptr_t>(a->v) |
        reinterpret_cast<uintptr_t>(a->out)) & 15)
     return CB200_ERR_ALIGNMENT;
-  if (!a->workspace || a->workspace_bytes < kWsHeaderBytes) return CB200_ERR_WORKSPACE;
+  if (!a->workspace || a->workspace_bytes < kWsHeaderBytes + prefill_knorm_bytes(a)) return CB200_ERR_WORKSPACE;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const bool f16 = a->dtype == CB200_F16;
   if (a->head_dim == 64)

@@ -469,23 +469,37 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
 #pragma unroll
         for (int c = 0; c < kColsPerThread; ++c) oc[c] = 0.f;
         if (mrow < rows_here) {
-          for (int cta = c_first; cta <= c_last; ++cta) {
-            const float* src = p.partials + (static_cast<size_t>(cta) * 2 + (cta == c_first ? 1 : 0)) * slot_floats;
-            const float mi_ = __ldcg(src + kRowsMax * D + mrow);
-            const float li_ = __ldcg(src + kRowsMax * D + kRowsMax + mrow);
-            const float Mn = fmaxf(Mc, mi_);
-            const float Mu = Mn == -INFINITY ? 0.f : Mn;
-            const float a = fast_exp2(Mc - Mu), bb = fast_exp2(mi_ - Mu);
-            Lc = a * Lc + bb * li_;
+          // the partials of up to four CTAs are fetched together: one L2 round trip per group instead of
+          // one per CTA (an item of a long request can span every CTA of the grid)
+          constexpr int kGroup = 4, kVec = kColsPerThread / 4;
+          for (int cta0 = c_first; cta0 <= c_last; cta0 += kGroup) {
+            float mi_[kGroup], li_[kGroup];
+            float4 x[kGroup][kVec];
 #pragma unroll
-            for (int c = 0; c < kColsPerThread; c += 4) {
-              const float4 x = __ldcg(reinterpret_cast<const float4*>(src + mrow * D + mcol + c));
-              oc[c] = a * oc[c] + bb * x.x;
-              oc[c + 1] = a * oc[c + 1] + bb * x.y;
-              oc[c + 2] = a * oc[c + 2] + bb * x.z;
-              oc[c + 3] = a * oc[c + 3] + bb * x.w;
+            for (int g = 0; g < kGroup; ++g) {
+              const int cta = min(cta0 + g, c_last);  // a repeated slot is given weight zero below
+              const float* src = p.partials + (static_cast<size_t>(cta) * 2 + (cta == c_first ? 1 : 0)) * slot_floats;
+              mi_[g] = __ldcg(src + kRowsMax * D + mrow);
+              li_[g] = __ldcg(src + kRowsMax * D + kRowsMax + mrow);
+#pragma unroll
+              for (int c = 0; c < kVec; ++c) x[g][c] = __ldcg(reinterpret_cast<const float4*>(src + mrow * D + mcol + 4 * c));
             }
-            Mc = Mn;
+#pragma unroll
+            for (int g = 0; g < kGroup; ++g) {
+              if (cta0 + g > c_last) continue;
+              const float Mn = fmaxf(Mc, mi_[g]);
+              const float Mu = Mn == -INFINITY ? 0.f : Mn;
+              const float a = fast_exp2(Mc - Mu), bb = fast_exp2(mi_[g] - Mu);
+              Lc = a * Lc + bb * li_[g];
+#pragma unroll
+              for (int c = 0; c < kVec; ++c) {
+                oc[4 * c] = a * oc[4 * c] + bb * x[g][c].x;
+                oc[4 * c + 1] = a * oc[4 * c + 1] + bb * x[g][c].y;
+                oc[4 * c + 2] = a * oc[4 * c + 2] + bb * x[g][c].z;
+                oc[4 * c + 3] = a * oc[4 * c + 3] + bb * x[g][c].w;
+              }
+              Mc = Mn;
+            }
           }
         }
         store_final(Mc, Lc, oc);

@@ -51,6 +51,7 @@ struct GemmParams {
   int chunks_per_tile; // S
   float eps;
   int a_rows;  // rows of the A box: 128, or M rounded up to 8 when M is smaller
+  const void* addend;  // MODE 0, may be null: (M, N) in the storage type, added in the epilogue
 };
 
 template <int MODE, int NBW>
@@ -307,6 +308,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
       } else {
 #pragma unroll
         for (int j = 0; j < 32; ++j) o[j] = v[j];
+        if (p.addend) {
+          const T* add = reinterpret_cast<const T*>(p.addend) + static_cast<size_t>(gr) * p.N + gc0;
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            if (gc0 + j < p.N) {
+              const uint4 u = *reinterpret_cast<const uint4*>(add + j);
+              const T* e = reinterpret_cast<const T*>(&u);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) o[j + i] += static_cast<float>(e[i]);
+            }
+          }
+        }
       }
       T* dst = yout + static_cast<size_t>(gr) * p.N + gc0;
 #pragma unroll
@@ -425,6 +438,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
               } else {
 #pragma unroll
                 for (int j = 0; j < 4; ++j) o[j] = v[j];
+                if (p.addend) {
+                  const uint2 u = *reinterpret_cast<const uint2*>(reinterpret_cast<const T*>(p.addend) +
+                                                                  static_cast<size_t>(tm * kBM + r) * p.N + gcol);
+                  const T* e = reinterpret_cast<const T*>(&u);
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) o[j] += static_cast<float>(e[j]);
+                }
               }
               uint2 pk;
               pk.x = pack2<T>(o[0], o[1]);
@@ -559,6 +579,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
               } else {
 #pragma unroll
                 for (int j = 0; j < 8; ++j) o[j] = v[u][j];
+                if (p.addend) {
+                  const uint4 q = *reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(p.addend) +
+                                                                  static_cast<size_t>(tm * kBM + r) * p.N + gcol);
+                  const T* e = reinterpret_cast<const T*>(&q);
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) o[j] += static_cast<float>(e[j]);
+                }
               }
               uint4 pk;
               pk.x = pack2<T>(o[0], o[1]);
@@ -622,6 +649,7 @@ int plan_gemm(const cb200_gemm_args* a, GemmSetup* s, bool need_maps) {
   if (a->op < CB200_GEMM_MATMUL || a->op > CB200_GEMM_SWIGLU) return CB200_ERR_BAD_ARG;
   if (a->dtype != CB200_F16 && a->dtype != CB200_BF16) return CB200_ERR_UNSUPPORTED;
   if (a->k % 8 || a->n % 8) return CB200_ERR_UNSUPPORTED;  // TMA strides are multiples of 16 bytes
+  if (a->addend && a->op != CB200_GEMM_MATMUL) return CB200_ERR_UNSUPPORTED;
   const int sms = sm_count();
   if (sms <= 0) return CB200_ERR_CUDA;
   int grid_max = sms;
@@ -708,7 +736,7 @@ int plan_gemm(const cb200_gemm_args* a, GemmSetup* s, bool need_maps) {
     const double t_pair = gemm_pair_estimate_us(a, sms, &s->pair_ks);
     double t_single = best;
     if (t_single == 0.0) t_single = static_cast<double>((tiles + grid_max - 1) / grid_max) * p.kblocks * (s->nbw == 4 || a->op == CB200_GEMM_SWIGLU ? 0.56 : 0.33);
-    s->pair = t_pair > 0.0 && t_pair < t_single;
+    s->pair = t_pair > 0.0 && t_pair < t_single && !a->addend;  // the pair kernel's epilogue has no addend
   }
   if (s->pair) {
     s->cluster = false;
@@ -727,12 +755,13 @@ int plan_gemm(const cb200_gemm_args* a, GemmSetup* s, bool need_maps) {
   if (a->op == CB200_GEMM_SWIGLU && !a->w1) return CB200_ERR_BAD_ARG;
   uintptr_t bits = reinterpret_cast<uintptr_t>(a->x) | reinterpret_cast<uintptr_t>(a->w) |
                    reinterpret_cast<uintptr_t>(a->y) | reinterpret_cast<uintptr_t>(a->w1) |
-                   reinterpret_cast<uintptr_t>(a->gamma);
+                   reinterpret_cast<uintptr_t>(a->gamma) | reinterpret_cast<uintptr_t>(a->addend);
   if (bits & 15) return CB200_ERR_ALIGNMENT;
   if (!a->workspace || a->workspace_bytes < s->ws_needed) return CB200_ERR_WORKSPACE;
   if (reinterpret_cast<uintptr_t>(a->workspace) & 255) return CB200_ERR_ALIGNMENT;
   p.y = a->y;
   p.gamma = a->op == CB200_GEMM_RMSNORM ? a->gamma : nullptr;
+  p.addend = a->addend;
   uint8_t* ws = static_cast<uint8_t*>(a->workspace);
   p.status = reinterpret_cast<int*>(ws);
   p.partials = reinterpret_cast<float*>(ws + s->partials_off);

@@ -74,12 +74,40 @@ class Tensor:
     def __radd__(self, other):
         return self._bin("add", other, swap=True)
 
+    def _last_axis(self, dim, what):
+        if dim not in (-1, len(self.shape) - 1):
+            raise ValueError(f"{what} is taken along the last axis")
+
+    def sum(self, dim: int = -1, keepdim: bool = False):  # noqa: A003
+        self._last_axis(dim, "sum")
+        return Tensor(("sum", self.expr), self.shape[:-1] + ((1,) if keepdim else ()))
+
+    def mean(self, dim: int = -1, keepdim: bool = False):
+        """``sum / extent`` as the reference defines it (python/cleave/frontend/tensor.py:273-274)."""
+        self._last_axis(dim, "mean")
+        return Tensor(("mean", self.expr), self.shape[:-1] + ((1,) if keepdim else ()))
+
+    def rsqrt(self):
+        return Tensor(("rsqrt", self.expr), self.shape)
+
 
 def rms_norm(x, dim: int = -1, eps: float = 0.0):
     """``x * rsqrt(mean(x*x) + eps)`` along the last axis, without weight."""
     if dim not in (-1, len(x.shape) - 1):
         raise ValueError("rms_norm is taken along the last axis")
     return Tensor(("rms_norm", x.expr, float(eps)), x.shape)
+
+
+def rsqrt(x):
+    return x.rsqrt()
+
+
+def sum(x, dim: int = -1, keepdim: bool = False):  # noqa: A001
+    return x.sum(dim, keepdim)
+
+
+def mean(x, dim: int = -1, keepdim: bool = False):
+    return x.mean(dim, keepdim)
 
 
 def silu(x):

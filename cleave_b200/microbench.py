@@ -120,6 +120,54 @@ def attn_prefill_case(hq=32, hkv=32, s=4096, d=64, dtype=torch.float16, causal=F
     return fn, flops, byts
 
 
+def fused_attn_case(kind, hq, hkv, s, d, dtype=torch.float16):
+    """(Q K^T) V without softmax (demo/matmul_matmul.py) or QK-norm attention (demo/qknorm.py) at demo size."""
+    g = _gen()
+    q = torch.randn(hq, s, d, generator=g).to(dtype).cuda()
+    k = torch.randn(hkv, s, d, generator=g).to(dtype).cuda()
+    v = (torch.randn(hkv, s, d, generator=g) / (s * d) ** 0.5 if kind == "matmul_matmul" else torch.randn(hkv, s, d, generator=g)).to(dtype).cuda()
+    out = torch.empty_like(q)
+    byts = (2 * q.numel() + 2 * k.numel()) * 2
+    if kind == "matmul_matmul":
+        fn = _rotating(lambda t: (lambda: ops.matmul_matmul(t[0], t[1], t[2], out=t[3])), [q, k, v, out])
+    else:
+        fn = _rotating(lambda t: (lambda: ops.qknorm_attention(t[0], t[1], t[2], eps=1e-6, out=t[3])), [q, k, v, out])
+    return fn, 4 * hq * s * s * d, byts
+
+
+def rowsum_case(m=4096, n=4096, k=64, dtype=torch.float16):
+    """rowsum(X @ W) (demo/matmul_rowsum.py); FLOPs are the operator's nominal 2 M N K, bytes X + W + y."""
+    g = _gen()
+    x = torch.randn(m, k, generator=g).to(dtype).cuda()
+    w = (torch.randn(k, n, generator=g) / k ** 0.5).to(dtype).cuda()
+    out = torch.empty(m, 1, dtype=dtype, device="cuda")
+    fn = _rotating(lambda t: (lambda: ops.matmul_rowsum(t[0], t[1], out=t[2])), [x, w, out], max_sets=16)
+    return fn, 2 * m * n * k, (m * k + k * n + m) * 2
+
+
+def lora_case(m=16, n=4096, k=4096, r=16, dtype=torch.float16):
+    """LoRA (demo/lora.py): bytes X + W + A + B + Y, FLOPs 2 M K N + 2 M K R + 2 M R N."""
+    g = _gen()
+    x = torch.randn(m, k, generator=g).to(dtype).cuda()
+    w = (torch.randn(k, n, generator=g) / k ** 0.5).to(dtype).cuda()
+    a = (torch.randn(k, r, generator=g) / k ** 0.5).to(dtype).cuda()
+    b = (torch.randn(r, n, generator=g) / r ** 0.5).to(dtype).cuda()
+    out = torch.empty(m, n, dtype=dtype, device="cuda")
+    fn = _rotating(lambda t: (lambda: ops.lora(t[0], t[1], t[2], t[3], out=t[4])), [x, w, a, b, out])
+    return fn, 2 * m * k * n + 2 * m * k * r + 2 * m * r * n, (m * k + k * n + k * r + r * n + m * n) * 2
+
+
+def attn_prefill_case_rect(hq, hkv, sq, skv, d, dtype=torch.float16):
+    """Unsplit attention with S_Q != S_KV (demo/mha_decode_exact.py: 64 query rows over 256 keys)."""
+    g = _gen()
+    q = torch.randn(hq, sq, d, generator=g).to(dtype).cuda()
+    k = torch.randn(hkv, skv, d, generator=g).to(dtype).cuda()
+    v = torch.randn(hkv, skv, d, generator=g).to(dtype).cuda()
+    out = torch.empty_like(q)
+    fn = _rotating(lambda t: (lambda: ops.attention_prefill(t[0], t[1], t[2], out=t[3])), [q, k, v, out], max_sets=16)
+    return fn, 4 * hq * sq * skv * d, (2 * q.numel() + 2 * k.numel()) * 2
+
+
 def paged_decode_case(page_size=1, batch=64, hi=8192):
     """Paged GQA decode (32 / 8 heads, d 128, bf16) over a cache far larger than L2; page size 1 takes
     the row-gather path."""
@@ -208,6 +256,11 @@ CONFIGS = {
     "demo_gqa_prefill_h32_kv8_s4096_d64": lambda: attn_prefill_case(32, 8, 4096, 64),
     "gqa_prefill_causal_h32_kv8_s4096_d128": lambda: attn_prefill_case(32, 8, 4096, 128, torch.bfloat16, True),
     "gqa_prefill_h32_kv8_s4096_d128": lambda: attn_prefill_case(32, 8, 4096, 128, torch.bfloat16, False),
+    "demo_matmul_matmul_bh32_s4096_d64": lambda: fused_attn_case("matmul_matmul", 32, 32, 4096, 64),
+    "demo_qknorm_h64_kv8_s4096_d128": lambda: fused_attn_case("qknorm", 64, 8, 4096, 128),
+    "demo_mha_decode_exact_h32_sq64_skv256_d64": lambda: attn_prefill_case_rect(32, 32, 64, 256, 64),
+    "demo_matmul_rowsum_4096x4096x64": lambda: rowsum_case(),
+    "demo_lora_16x4096x4096_r16": lambda: lora_case(),
     "gqa_ragged_prefill_causal_h32_kv8_d128_b8_q2048": lambda: gqa_dynamic_prefill_case(False),
     "gqa_paged_prefill_causal_h32_kv8_d128_ps1_b8_q2048": lambda: gqa_dynamic_prefill_case(True),
     "mla_paged_decode_h16_ps1_b64_kv512_8192": lambda: mla_paged_decode_case(),

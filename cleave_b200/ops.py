@@ -135,12 +135,14 @@ def attention_decode(q, k, v, sm_scale=None, *, out=None, lse=None, max_ctas=0):
     return out
 
 
-def attention_prefill(q, k, v, sm_scale=None, *, causal=False, out=None, lse=None):
+def attention_prefill(q, k, v, sm_scale=None, *, causal=False, out=None, lse=None, linear=False, qk_norm_eps=None):
     """Unsplit attention with many query rows (reference: demo/attention.py:5-8 at the shapes of
     demo/{mha,gqa,mqa}_prefill.py). ``q`` (HQ, SQ, D); ``k``, ``v`` (HKV, SKV, D); D 64 or 128; query
     head h reads kv head h // (HQ/HKV). ``causal`` applies the end-aligned mask of the paged and
     ragged prefill operators (python/cleave/dynamic/reference.py:129-133). Returns ``out``
-    (HQ, SQ, D); pass ``lse`` (HQ, SQ) fp32 to also get the base-2 log-sum-exp."""
+    (HQ, SQ, D); pass ``lse`` (HQ, SQ) fp32 to also get the base-2 log-sum-exp. ``linear`` drops the
+    softmax (``O = (sm_scale * Q K^T) V``, see :func:`matmul_matmul`); ``qk_norm_eps`` RMS-normalises the
+    rows of q and k first (see :func:`qknorm_attention`)."""
     q, k, v = _cuda(q, "q"), _cuda(k, "k"), _cuda(v, "v")
     hq, sq, d = q.shape
     hkv, skv, d2 = k.shape
@@ -151,6 +153,9 @@ def attention_prefill(q, k, v, sm_scale=None, *, causal=False, out=None, lse=Non
     if out is None:
         out = torch.empty_like(q)
     a = _lib.AttnPrefillArgs()
+    a.score_mode = _lib.SCORE_LINEAR if linear else _lib.SCORE_SOFTMAX
+    if qk_norm_eps is not None:
+        a.qk_norm, a.norm_eps = 1, float(qk_norm_eps)
     a.q, a.k, a.v, a.out = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr()
     a.lse = lse.data_ptr() if lse is not None else None
     a.num_qo_heads, a.num_kv_heads, a.q_len, a.kv_len, a.head_dim = hq, hkv, sq, skv, d
@@ -161,6 +166,66 @@ def attention_prefill(q, k, v, sm_scale=None, *, causal=False, out=None, lse=Non
     ws = workspace("attn_prefill", need, q.device)
     a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
     _lib.check(_lib.lib().cb200_attn_prefill(C.byref(a), _stream()))
+    return out
+
+
+def matmul_matmul(q, k, v, *, out=None):
+    """``O = (Q K^T) V`` without softmax (reference operator: demo/matmul_matmul.py:11-13): q (HQ, SQ, D);
+    k, v (HKV, SKV, D); D 64 or 128. Runs on the tcgen05 attention kernel with the scores passed through:
+    they are rounded to the storage dtype before the second product."""
+    return attention_prefill(q, k, v, 1.0, out=out, linear=True)
+
+
+def qknorm_attention(q, k, v, sm_scale=None, *, eps=1e-6, out=None, lse=None):
+    """Attention over RMS-normalised queries and keys (reference operator: demo/qknorm.py:17-24):
+    ``softmax(rms(q) rms(k)^T * scale) v`` with ``rms(x) = x * rsqrt(mean(x^2) + eps)`` along D, fp32
+    statistics. The query factor is folded into the score scale inside the kernel; K is normalised once."""
+    return attention_prefill(q, k, v, sm_scale, out=out, lse=lse, qk_norm_eps=eps)
+
+
+def matmul_rowsum(x, w, *, out=None):
+    """``Y = rowsum(X @ W)``, shape (M, 1) (reference operator: demo/matmul_rowsum.py:6-8), computed as
+    ``X @ rowsum(W)``: every input byte is read once and the (M, N) product is never formed."""
+    x, w = _cuda(x, "x"), _cuda(w, "w")
+    m, k = x.shape
+    k2, n = w.shape
+    if k2 != k or w.dtype != x.dtype:
+        raise ValueError(f"shapes/dtypes: x {tuple(x.shape)} {x.dtype}, w {tuple(w.shape)} {w.dtype}")
+    if out is None:
+        out = torch.empty((m, 1), dtype=x.dtype, device=x.device)
+    if out.numel() != m or not out.is_contiguous():
+        raise ValueError("out must hold M contiguous values")
+    a = _lib.MatmulRowsumArgs()
+    a.x, a.w, a.y = x.data_ptr(), w.data_ptr(), out.data_ptr()
+    a.m, a.n, a.k, a.dtype = m, n, k, _dtype_code(x)
+    need = _lib.lib().cb200_matmul_rowsum_workspace_bytes(C.byref(a))
+    if need == 0:
+        _lib.check(_lib.lib().cb200_matmul_rowsum(C.byref(a), _stream()))  # raises the real status
+    ws = workspace("matmul_rowsum", need, x.device)
+    a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+    _lib.check(_lib.lib().cb200_matmul_rowsum(C.byref(a), _stream()))
+    return out
+
+
+def lora(x, w, a, b, *, out=None):
+    """``Y = X @ W + (X @ A) @ B`` (reference operator: demo/lora.py:11-18): x (M, K), w (K, N), a (K, R),
+    b (R, N). Three tcgen05 GEMM launches; the low-rank term is added in the epilogue of the last."""
+    x, w, a, b = _cuda(x, "x"), _cuda(w, "w"), _cuda(a, "a"), _cuda(b, "b")
+    m, k = x.shape
+    n, r = w.shape[1], a.shape[1]
+    if w.shape[0] != k or a.shape[0] != k or tuple(b.shape) != (r, n) or len({x.dtype, w.dtype, a.dtype, b.dtype}) != 1:
+        raise ValueError("shapes: x (M,K), w (K,N), a (K,R), b (R,N), one storage dtype")
+    if out is None:
+        out = torch.empty((m, n), dtype=x.dtype, device=x.device)
+    g = _lib.LoraArgs()
+    g.x, g.w, g.a, g.b, g.y = x.data_ptr(), w.data_ptr(), a.data_ptr(), b.data_ptr(), out.data_ptr()
+    g.m, g.n, g.k, g.r, g.dtype = m, n, k, r, _dtype_code(x)
+    need = _lib.lib().cb200_lora_workspace_bytes(C.byref(g))
+    if need == 0:
+        _lib.check(_lib.lib().cb200_lora(C.byref(g), _stream()))  # raises the real status
+    ws = workspace("lora", need, x.device)
+    g.workspace, g.workspace_bytes = ws.data_ptr(), ws.numel()
+    _lib.check(_lib.lib().cb200_lora(C.byref(g), _stream()))
     return out
 
 

@@ -133,6 +133,15 @@ class B200Kernel:
                 ops.attention_prefill(ins[0], ins[1], ins[2], s.attrs.get("scale"), out=outs[0])
             else:
                 ops.attention_decode(ins[0], ins[1], ins[2], s.attrs.get("scale"), out=outs[0], max_ctas=mc)
+        elif f == "matmul_matmul":
+            ops.matmul_matmul(ins[0], ins[1], ins[2], out=outs[0])
+        elif f == "qknorm_attention":
+            ops.qknorm_attention(ins[0], ins[1], ins[2], s.attrs.get("scale"), eps=float(s.attrs.get("eps", 0.0)),
+                                 out=outs[0])
+        elif f == "matmul_rowsum":
+            ops.matmul_rowsum(ins[0], ins[1], out=outs[0])
+        elif f == "lora":
+            ops.lora(ins[0], ins[1], ins[2], ins[3], out=outs[0])
         elif f == "mla_decode":
             ops.mla_decode(ins[0], ins[1], ins[2], ins[3], float(s.attrs["scale"]), out=outs[0], max_ctas=mc)
         elif f == "gqa_paged_decode":
@@ -183,6 +192,7 @@ def build_inputs_and_reference(spec: KernelSpec, device="cuda", seed=None):
     dt = R.torch_dtype(spec.dtype)
     g = torch.Generator(device="cpu").manual_seed(R.fingerprint_seed(spec) if seed is None else seed)
     d = spec.dims
+    f_ = spec.family
     inputs = {}
     for p in spec.inputs:
         shape = [int(x) for x in p.dims]
@@ -191,6 +201,12 @@ def build_inputs_and_reference(spec: KernelSpec, device="cuda", seed=None):
             t = 1 + 0.1 * torch.randn(shape, generator=g)
         elif base in ("w", "w0", "w1"):
             t = torch.randn(shape, generator=g) / d["K"] ** 0.5
+        elif f_ == "lora" and base == "b":
+            t = torch.randn(shape, generator=g) / d["R"] ** 0.5
+        elif f_ == "matmul_matmul" and base == "v":
+            # 16-bit scores feed the second product: keep the output O(1) so that their rounding stays
+            # inside the absolute tolerance (with N(0,1) values the output has magnitude sqrt(SKV * D))
+            t = torch.randn(shape, generator=g) / (d["SKV"] * d["D"]) ** 0.5
         else:
             t = torch.randn(shape, generator=g)
         inputs[p.name] = t.to(dt).to(device)
@@ -207,6 +223,14 @@ def build_inputs_and_reference(spec: KernelSpec, device="cuda", seed=None):
         ref = R.attention(v("q"), v("k"), v("v"), spec.attrs.get("scale"))
     elif f == "mla_decode":
         ref = R.mla_decode(v("q"), v("kv"), v("q_pe"), v("k_pe"), float(spec.attrs["scale"]))
+    elif f == "matmul_matmul":
+        ref = R.matmul_matmul(v("q"), v("k"), v("v"))
+    elif f == "qknorm_attention":
+        ref = R.qknorm_attention(v("q"), v("k"), v("v"), float(spec.attrs.get("eps", 0.0)), spec.attrs.get("scale"))
+    elif f == "matmul_rowsum":
+        ref = R.matmul_rowsum(v("x"), v("w"))
+    elif f == "lora":
+        ref = R.lora(v("x"), v("w"), v("a"), v("b"))
     else:
         raise CompileError(f"{f}: dynamic operators are validated over workloads, not one static reference")
     return inputs, [ref.to(dt)], graph_out_indices(spec)

@@ -67,6 +67,35 @@ def attention(q, k, v, scale=None):
     return pp @ vv
 
 
+def matmul_matmul(q, k, v):
+    """``(q @ k.mT) @ v`` (demo/matmul_matmul.py), grouped heads broadcast like the attention operators."""
+    q, k, v = q.float(), k.float(), v.float()
+    qq, kk = _grouped(q, k)
+    s = qq @ kk.mT
+    ss, vv = _grouped(s, v)
+    return ss @ vv
+
+
+def _rms(x, eps):
+    return x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps)
+
+
+def qknorm_attention(q, k, v, eps=0.0, scale=None):
+    """Attention over RMS-normalised q and k (demo/qknorm.py)."""
+    return attention(_rms(q.float(), eps), _rms(k.float(), eps), v, scale)
+
+
+def matmul_rowsum(x, w):
+    """``(x @ w).sum(-1, keepdim=True)`` (demo/matmul_rowsum.py)."""
+    return (x.float() @ w.float()).sum(-1, keepdim=True)
+
+
+def lora(x, w, a, b):
+    """``x @ w + (x @ a) @ b`` (demo/lora.py)."""
+    x = x.float()
+    return x @ w.float() + (x @ a.float()) @ b.float()
+
+
 def mla_decode(q, kv, q_pe, k_pe, scale):
     q, kv, q_pe, k_pe = q.float(), kv.float(), q_pe.float(), k_pe.float()
     p = torch.softmax((q @ kv.mT + q_pe @ k_pe.mT) * scale, dim=-1)

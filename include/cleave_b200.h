@@ -137,6 +137,8 @@ typedef struct {
   int32_t split_k;  /* 0 = auto */
   int32_t max_ctas; /* 0 = one CTA per SM */
   float eps;        /* RMSNorm only */
+  const void* addend; /* CB200_GEMM_MATMUL only, may be NULL: (m, n) in the storage dtype, Y = X @ W + addend
+                         (added in fp32 in the epilogue; the low-rank term of cb200_lora) */
 } cb200_gemm_args;
 
 size_t cb200_gemm_workspace_bytes(const cb200_gemm_args* a);
@@ -196,9 +198,11 @@ int cb200_mla_decode(const cb200_mla_decode_args* a, void* stream);
  * Replaces the static unsplit attention kernels of demo/{mha,gqa,mqa}_prefill.py
  * (tests/graph/handwritten/expected_kernels/mha_bhsd.py); `causal` applies the end-aligned mask of
  * python/cleave/dynamic/reference.py:129-133 (query row r sees keys <= r + kv_len - q_len), the
- * mask of the paged and ragged prefill operators. head_dim 64 or 128. The workspace holds only the
- * status word (cb200_workspace_status).
+ * mask of the paged and ragged prefill operators. head_dim 64 or 128. The workspace holds the status
+ * word (cb200_workspace_status) and, with qk_norm, the normalised copy of K.
  * ---------------------------------------------------------------------------------------- */
+typedef enum { CB200_SCORE_SOFTMAX = 0, CB200_SCORE_LINEAR = 1 } cb200_score_mode;
+
 typedef struct {
   const void* q;   /* (num_qo_heads, q_len, head_dim) */
   const void* k;   /* (num_kv_heads, kv_len, head_dim) */
@@ -215,6 +219,18 @@ typedef struct {
   int32_t dtype;    /* cb200_dtype */
   int32_t causal;   /* 0 = no mask, 1 = end-aligned causal mask (a row left without keys gives 0 and lse -inf) */
   float sm_scale;
+  /* The fields below select two more operators of the same kernel; zero gives plain attention.
+   * score_mode CB200_SCORE_LINEAR: O = (sm_scale * Q K^T) V without softmax - the operator
+   *   (q @ k.mT) @ v of demo/matmul_matmul.py (sm_scale 1). The scores are rounded to the storage type
+   *   before the second product, as a 16-bit tensor-core operand must be; lse is not written.
+   * qk_norm 1: Q and K rows are RMS-normalised first, x * rsqrt(mean_d(x^2) + norm_eps) with fp32
+   *   statistics - the operator of demo/qknorm.py. The query factor is taken from the resident query tile
+   *   and folded into the score scale; K is normalised once by a pre-pass into the workspace, which
+   *   then holds num_kv_heads * kv_len * head_dim * 2 more bytes (cb200_attn_prefill_workspace_bytes
+   *   accounts for it). */
+  int32_t score_mode; /* cb200_score_mode */
+  int32_t qk_norm;
+  float norm_eps;
 } cb200_attn_prefill_args;
 
 size_t cb200_attn_prefill_workspace_bytes(const cb200_attn_prefill_args* a);
@@ -250,6 +266,46 @@ typedef struct {
 
 size_t cb200_attn_prefill_ragged_workspace_bytes(const cb200_attn_prefill_ragged_args* a);
 int cb200_attn_prefill_ragged(const cb200_attn_prefill_ragged_args* a, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Y = rowsum(X @ W): y[m] = sum_n (X @ W)[m, n]; X (m, k), W (k, n) row-major, y (m) = (m, 1); k and n
+ * multiples of 8. Replaces the fused matmul + reduce kernel of demo/matmul_rowsum.py
+ * ((x @ w).sum(-1, keepdim=True)). Computed as X @ (W 1): one pass over W for its fp32 row sums (k
+ * floats in the workspace), one pass over X; the (m, n) product is never formed.
+ * ---------------------------------------------------------------------------------------- */
+typedef struct {
+  const void* x; /* (m, k) */
+  const void* w; /* (k, n) */
+  void* y;       /* (m) */
+  void* workspace;
+  size_t workspace_bytes;
+  int32_t m, n, k;
+  int32_t dtype; /* cb200_dtype */
+} cb200_matmul_rowsum_args;
+
+size_t cb200_matmul_rowsum_workspace_bytes(const cb200_matmul_rowsum_args* a);
+int cb200_matmul_rowsum(const cb200_matmul_rowsum_args* a, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * LoRA: Y = X @ W + (X @ A) @ B; X (m, k), W (k, n), A (k, r), B (r, n), Y (m, n), all row-major in the
+ * storage dtype; k, n and r multiples of 8. Replaces the fused kernel of demo/lora.py
+ * (x @ w + (x @ a) @ b). Three launches of cb200_gemm on `stream`: T = X @ A, Z = T @ B, then
+ * Y = X @ W with Z added in the epilogue; T and Z are kept in the workspace in the storage dtype.
+ * ---------------------------------------------------------------------------------------- */
+typedef struct {
+  const void* x; /* (m, k) */
+  const void* w; /* (k, n) */
+  const void* a; /* (k, r) */
+  const void* b; /* (r, n) */
+  void* y;       /* (m, n) */
+  void* workspace;
+  size_t workspace_bytes;
+  int32_t m, n, k, r;
+  int32_t dtype; /* cb200_dtype */
+} cb200_lora_args;
+
+size_t cb200_lora_workspace_bytes(const cb200_lora_args* a);
+int cb200_lora(const cb200_lora_args* a, void* stream);
 
 /* ------------------------------------------------------------------------------------------
  * Decode attention for callers that cannot allocate device memory. (No counterpart in the

@@ -17,6 +17,11 @@ project root):
                           shift ``-50/sqrt(d)``) and the grouped batch broadcast of
                           ``frontend/program.py:351-363`` (``repeat_interleave``).
 * ``mla_decode``        - ``demo/mla_decode.py:8-13`` with a caller-chosen scale.
+* ``attention_exact``   - ``demo/attention.py:11-13`` (``exp(s - max(s)) / sum``; ``demo/mha_decode_exact.py``).
+* ``matmul_matmul``     - ``demo/matmul_matmul.py:11-13`` (``(q @ k.mT) @ v``).
+* ``qknorm_attention``  - ``demo/qknorm.py:17-24`` (``x * rsqrt(mean(x*x) + eps)`` on q and k, then ``attention``).
+* ``matmul_rowsum``     - ``demo/matmul_rowsum.py:6-8`` (``(x @ w).sum(-1, keepdim=True)``).
+* ``lora``              - ``demo/lora.py:11-18`` (``x @ w + (x @ a) @ b``).
 * ``gqa_paged_decode``  - ``python/cleave/dynamic/reference.py:180-200`` (+ ``_paged_tokens`` ``:143-152``,
                           ``_attend`` ``:85-105``, ``_finish`` ``:68-82``).
 * ``mla_paged_decode``  - ``python/cleave/dynamic/reference.py:297-320`` (+ ``_mla_attend_rows`` ``:108-128``).
@@ -147,6 +152,49 @@ def attention(q, k, v, dtype: str = "f16", scale: float | None = None) -> np.nda
     p = e / e.sum(axis=-1, keepdims=True, dtype=np.float32)
     pp, vv = _grouped(p, v)
     return round_to(pp @ vv, dtype)
+
+
+def attention_exact(q, k, v, dtype: str = "f16") -> np.ndarray:
+    """``softmax(Q K^T / sqrt(d)) V`` with the exact row maximum (demo/attention.py:11-13;
+    ``composites.softmax`` without a shift subtracts ``max`` along the axis)."""
+    q, k, v = f32(q), f32(k), f32(v)
+    qq, kk = _grouped(q, k)
+    s = (qq @ np.swapaxes(kk, -1, -2)) / np.float32(q.shape[-1] ** 0.5)
+    e = np.exp(s - s.max(axis=-1, keepdims=True))
+    p = e / e.sum(axis=-1, keepdims=True, dtype=np.float32)
+    pp, vv = _grouped(p, v)
+    return round_to(pp @ vv, dtype)
+
+
+def matmul_matmul(q, k, v, dtype: str = "f16") -> np.ndarray:
+    """``(Q K^T) V`` in fp32, no softmax and no scale (demo/matmul_matmul.py:11-13); grouped heads
+    broadcast as in ``attention``."""
+    q, k, v = f32(q), f32(k), f32(v)
+    qq, kk = _grouped(q, k)
+    s = qq @ np.swapaxes(kk, -1, -2)
+    ss, vv = _grouped(s, v)
+    return round_to(ss @ vv, dtype)
+
+
+def qknorm_attention(q, k, v, eps: float = 1e-6, dtype: str = "f16") -> np.ndarray:
+    """``attention(rms(q), rms(k), v)`` with ``rms(x) = x * rsqrt(mean(x*x, -1) + eps)`` written out in
+    primitives as demo/qknorm.py:17-24 does (mean = sum / extent, python/cleave/frontend/tensor.py:273-274)."""
+    q, k = f32(q), f32(k)
+    d = np.float32(q.shape[-1])
+    qn = q * (np.float32(1) / np.sqrt((q * q).sum(-1, keepdims=True, dtype=np.float32) / d + np.float32(eps)))
+    kn = k * (np.float32(1) / np.sqrt((k * k).sum(-1, keepdims=True, dtype=np.float32) / d + np.float32(eps)))
+    return attention(qn.astype(np.float32), kn.astype(np.float32), v, dtype)
+
+
+def matmul_rowsum(x, w, dtype: str = "f16") -> np.ndarray:
+    """``(X @ W).sum(-1, keepdim=True)`` in fp32 (demo/matmul_rowsum.py:6-8); shape (M, 1)."""
+    return round_to((f32(x) @ f32(w)).sum(-1, keepdims=True, dtype=np.float32), dtype)
+
+
+def lora(x, w, a, b, dtype: str = "f16") -> np.ndarray:
+    """``X @ W + (X @ A) @ B`` in fp32 (demo/lora.py:11-18)."""
+    x = f32(x)
+    return round_to(x @ f32(w) + (x @ f32(a)) @ f32(b), dtype)
 
 
 def attention_masked(q, k, v, scale: float, causal: bool, dtype: str = "bf16"):

@@ -36,6 +36,21 @@ def attention_inputs(seed, hq, hkv, sq, skv, d, dtype):
             "v": _randn(rng, (hkv, skv, d), dtype)}
 
 
+def matmul_matmul_inputs(seed, hq, hkv, sq, skv, d, dtype):
+    """v is scaled by 1/sqrt(SKV * D) so that the output is O(1): the scores (magnitude sqrt(D)) are a
+    16-bit operand of the second product on the GPU and their rounding must stay inside the absolute
+    tolerance of the comparison."""
+    rng = np.random.default_rng(seed)
+    return {"q": _randn(rng, (hq, sq, d), dtype), "k": _randn(rng, (hkv, skv, d), dtype),
+            "v": _randn(rng, (hkv, skv, d), dtype, 1.0 / np.sqrt(skv * d))}
+
+
+def lora_inputs(seed, m, n, k, r, dtype):
+    rng = np.random.default_rng(seed)
+    return {"x": _randn(rng, (m, k), dtype), "w": _randn(rng, (k, n), dtype, 1.0 / np.sqrt(k)),
+            "a": _randn(rng, (k, r), dtype, 1.0 / np.sqrt(k)), "b": _randn(rng, (r, n), dtype, 1.0 / np.sqrt(r))}
+
+
 def mla_inputs(seed, b, h, skv, d, pe, dtype):
     rng = np.random.default_rng(seed)
     return {"q": _randn(rng, (b, h, d), dtype), "kv": _randn(rng, (b, skv, d), dtype),
@@ -147,6 +162,16 @@ CASES = {
                                                    hq=8, hkv=2, d=64, dtype="bf16", paged=True)),
     "mla_paged_prefill_bf16": ("mla_prefill", dict(seed=52, q_lens=[20, 0, 30, 5, 1], kv_lens=[70, 30, 30, 0, 129], h=16,
                                                   ckv=512, kpe=64, dtype="bf16", scale=MLA_SM_SCALE)),
+    # the remaining fused operators of the reference's demo set
+    "mha_decode_exact_f16": ("attention_exact", dict(seed=60, hq=4, hkv=4, sq=64, skv=256, d=64, dtype="f16")),
+    "matmul_matmul_f16": ("matmul_matmul", dict(seed=61, hq=4, hkv=4, sq=130, skv=300, d=64, dtype="f16")),
+    "matmul_matmul_gqa_bf16": ("matmul_matmul", dict(seed=62, hq=4, hkv=2, sq=64, skv=256, d=128, dtype="bf16")),
+    "qknorm_f16": ("qknorm", dict(seed=63, hq=8, hkv=2, sq=200, skv=333, d=128, dtype="f16"), dict(eps=1e-6)),
+    "qknorm_d64_bf16": ("qknorm", dict(seed=64, hq=4, hkv=4, sq=128, skv=128, d=64, dtype="bf16"), dict(eps=1e-6)),
+    "matmul_rowsum_f16": ("matmul_rowsum", dict(seed=65, m=200, n=512, k=64, dtype="f16")),
+    "matmul_rowsum_bf16": ("matmul_rowsum", dict(seed=66, m=33, n=72, k=320, dtype="bf16")),
+    "lora_f16": ("lora", dict(seed=67, m=16, n=512, k=1024, r=16, dtype="f16")),
+    "lora_bf16": ("lora", dict(seed=68, m=200, n=264, k=320, r=8, dtype="bf16")),
     # paged MLA decode
     "mla_paged_bf16": ("mla_paged", dict(seed=40, kv_lens=[5, 0, 7, 300], h=16, ckv=512, kpe=64,
                                          dtype="bf16", scale=MLA_SM_SCALE)),
@@ -159,8 +184,14 @@ def build(name):
     extra = entry[2] if len(entry) > 2 else {}
     if family in ("matmul", "rmsnorm_matmul", "swiglu"):
         return family, gemm_inputs(**kw), dict(extra, dtype=kw["dtype"])
-    if family == "attention":
+    if family in ("attention", "attention_exact", "qknorm"):
         return family, attention_inputs(**kw), dict(extra, dtype=kw["dtype"])
+    if family == "matmul_matmul":
+        return family, matmul_matmul_inputs(**kw), dict(extra, dtype=kw["dtype"])
+    if family == "matmul_rowsum":
+        return family, gemm_inputs(**kw), dict(extra, dtype=kw["dtype"])
+    if family == "lora":
+        return family, lora_inputs(**kw), dict(extra, dtype=kw["dtype"])
     if family == "mla":
         return family, mla_inputs(**kw), dict(extra, dtype=kw["dtype"])
     if family == "gqa_paged":

@@ -84,6 +84,47 @@ def main(ref_root):
             hkv, skv, _ = inp["k"].shape
             prog = cleave.trace(attention, shapes=dict(HQ=hq, HKV=hkv, SQ=sq, SKV=skv, D=d), dtype=cdt[dt])
             res = prog.reference(_t(inp["q"], dt), _t(inp["k"], dt), _t(inp["v"], dt))
+        elif family == "attention_exact":
+            def fn(q: cl.Tensor["H", "SQ", "D"], k: cl.Tensor["H", "SKV", "D"], v: cl.Tensor["H", "SKV", "D"]):
+                return cl.softmax((q @ k.mT) / q.shape[-1] ** 0.5, dim=-1) @ v
+            h, sq, d = inp["q"].shape
+            prog = cleave.trace(fn, shapes=dict(H=h, SQ=sq, SKV=inp["k"].shape[1], D=d), dtype=cdt[dt])
+            res = prog.reference(_t(inp["q"], dt), _t(inp["k"], dt), _t(inp["v"], dt))
+        elif family == "matmul_matmul":
+            def fn(q: cl.Tensor["HQ", "SQ", "D"], k: cl.Tensor["HKV", "SKV", "D"], v: cl.Tensor["HKV", "SKV", "D"]):
+                return (q @ k.mT) @ v
+            hq, sq, d = inp["q"].shape
+            hkv, skv, _ = inp["k"].shape
+            prog = cleave.trace(fn, shapes=dict(HQ=hq, HKV=hkv, SQ=sq, SKV=skv, D=d), dtype=cdt[dt])
+            res = prog.reference(_t(inp["q"], dt), _t(inp["k"], dt), _t(inp["v"], dt))
+        elif family == "qknorm":
+            eps = opt["eps"]
+
+            def fn(q: cl.Tensor["HQ", "SQ", "D"], k: cl.Tensor["HKV", "SKV", "D"], v: cl.Tensor["HKV", "SKV", "D"]):
+                q_sq, k_sq = q * q, k * k
+                q_ms, k_ms = q_sq.mean(-1, keepdim=True), k_sq.mean(-1, keepdim=True)
+                qn = q * cl.rsqrt(q_ms + eps)
+                kn = k * cl.rsqrt(k_ms + eps)
+                n = qn.shape[-1] ** 0.5
+                return cl.softmax((qn @ kn.mT) / n, dim=-1, shift=-50 / n) @ v
+            hq, sq, d = inp["q"].shape
+            hkv, skv, _ = inp["k"].shape
+            prog = cleave.trace(fn, shapes=dict(HQ=hq, HKV=hkv, SQ=sq, SKV=skv, D=d), dtype=cdt[dt])
+            res = prog.reference(_t(inp["q"], dt), _t(inp["k"], dt), _t(inp["v"], dt))
+        elif family == "matmul_rowsum":
+            def fn(x: cl.Tensor["M", "K"], w: cl.Tensor["K", "N"]):
+                return (x @ w).sum(-1, keepdim=True)
+            m, k = inp["x"].shape
+            prog = cleave.trace(fn, shapes=dict(M=m, K=k, N=inp["w0"].shape[1]), dtype=cdt[dt])
+            res = prog.reference(_t(inp["x"], dt), _t(inp["w0"], dt))
+        elif family == "lora":
+            m, k = inp["x"].shape
+            prog = cleave.Program("lora", dtype=cdt[dt])
+            M, K, N, R = prog.dims(M=m, K=k, N=inp["w"].shape[1], R=inp["a"].shape[1])
+            x, w = prog.input("x", (M, K)), prog.input("w", (K, N))
+            a, b = prog.input("a", (K, R)), prog.input("b", (R, N))
+            prog.output(x @ w + (x @ a) @ b, name="y")
+            res = prog.reference(*[_t(inp[n], dt) for n in ("x", "w", "a", "b")])
         elif family == "mla":
             scale = opt["scale"]
 

@@ -83,6 +83,20 @@ def test_plan_recognition_from_flat_graph_patterns():
     assert a.family == "attention_decode" and a.dims["HKV"] == 64 and a.dims["SKV"] == 8192
     with pytest.raises(Exception):
         recognise(_plan([N("PlaceHolderNode", (4, 4)), N("Exp"), N("OutputNode")]))
+    # the remaining demo operators
+    qkv = [N("PlaceHolderNode", (32, 4096, 64)), N("PlaceHolderNode", (32, 4096, 64)), N("PlaceHolderNode", (32, 4096, 64))]
+    mmm = recognise(_plan(qkv + [N("Matmul"), N("Matmul"), N("OutputNode")]))
+    assert mmm.family == "matmul_matmul" and mmm.dims == {"HQ": 32, "HKV": 32, "SQ": 4096, "SKV": 4096, "D": 64}
+    qkn = recognise(_plan(qkv + [N("Mul"), N("ReduceSum"), N("Div"), N("Add"), N("RSqrt"), N("Mul"), N("Matmul"), N("Div"),
+                                 N("Add"), N("Exp"), N("ReduceSum"), N("Matmul"), N("Div"), N("OutputNode")]))
+    assert qkn.family == "qknorm_attention"
+    rs = recognise(_plan([N("PlaceHolderNode", (4096, 64)), N("PlaceHolderNode", (64, 4096)), N("Matmul"), N("ReduceSum"),
+                          N("OutputNode")]))
+    assert rs.family == "matmul_rowsum" and rs.params[-1].dims == (4096, 1)
+    lo = recognise(_plan([N("PlaceHolderNode", (16, 4096)), N("PlaceHolderNode", (4096, 4096)),
+                          N("PlaceHolderNode", (4096, 16)), N("PlaceHolderNode", (16, 4096)), N("Matmul"), N("Matmul"),
+                          N("Matmul"), N("Add"), N("OutputNode")]))
+    assert lo.family == "lora" and lo.dims == {"M": 16, "N": 4096, "K": 4096, "R": 16}
 
 
 def test_trace_matches_the_demo_operators():
@@ -104,6 +118,52 @@ def test_trace_matches_the_demo_operators():
 
     p = trace(attention, dict(HQ=32, HKV=8, SQ=1, SKV=4096, D=128))
     assert p.family == "attention_decode" and abs(p.attrs["scale"] - 128 ** -0.5) < 1e-9
+
+    # the remaining demo operators (demo/matmul_matmul.py, matmul_rowsum.py, qknorm.py, mha_decode_exact.py, lora.py)
+    @jit
+    def matmul_matmul(q: cl.Tensor["BH", "SQ", "D"], k: cl.Tensor["BH", "SKV", "D"], v: cl.Tensor["BH", "SKV", "D"]):
+        return (q @ k.mT) @ v
+
+    p = trace(matmul_matmul, dict(BH=32, SQ=4096, SKV=4096, D=64))
+    assert p.family == "matmul_matmul" and p.output_shapes == [(32, 4096, 64)]
+
+    @jit
+    def matmul_rowsum(x: cl.Tensor["M", "K"], w: cl.Tensor["K", "N"]):
+        return (x @ w).sum(-1, keepdim=True)
+
+    p = trace(matmul_rowsum, dict(M=4096, N=4096, K=64))
+    assert p.family == "matmul_rowsum" and p.output_shapes == [(4096, 1)]
+
+    @jit
+    def qknorm(q: cl.Tensor["HQ", "SQ", "D"], k: cl.Tensor["HKV", "SKV", "D"], v: cl.Tensor["HKV", "SKV", "D"]):
+        q_sq, k_sq = q * q, k * k
+        q_ms, k_ms = q_sq.mean(-1, keepdim=True), k_sq.mean(-1, keepdim=True)
+        qn = q * cl.rsqrt(q_ms + 1e-6)
+        kn = k * cl.rsqrt(k_ms + 1e-6)
+        n = qn.shape[-1] ** 0.5
+        return cl.softmax((qn @ kn.mT) / n, dim=-1, shift=-50 / n) @ v
+
+    p = trace(qknorm, dict(HQ=64, HKV=8, SQ=4096, SKV=4096, D=128))
+    assert p.family == "qknorm_attention" and p.attrs["eps"] == 1e-6 and abs(p.attrs["scale"] - 128 ** -0.5) < 1e-9
+
+    @jit
+    def mha_decode_exact(q: cl.Tensor["H", "SQ", "D"], k: cl.Tensor["H", "SKV", "D"], v: cl.Tensor["H", "SKV", "D"]):
+        return cl.softmax((q @ k.mT) / q.shape[-1] ** 0.5, dim=-1) @ v
+
+    assert trace(mha_decode_exact, dict(H=32, SQ=64, SKV=256, D=64)).family == "attention_decode"
+
+    from cleave_b200.frontend import Program
+
+    prog = Program("lora", dtype=cl.f16)
+    M, K, N, R = prog.dims(M=16, K=4096, N=4096, R=16)
+    x, w = prog.input("x", (M, K)), prog.input("w", (K, N))
+    a, b = prog.input("a", (K, R)), prog.input("b", (R, N))
+    prog.output(x @ w + (x @ a) @ b, name="y")
+    assert (prog.family, prog.dims, prog.input_names) == ("lora", {"M": 16, "N": 4096, "K": 4096, "R": 16},
+                                                         ["x", "w", "a", "b"])
+    assert prog.dtype == "float16" and prog.output_shapes == [(16, 4096)]
+    with pytest.raises(SpecError):
+        prog.input("late", (1, 1))
 
     @jit
     def unknown(x: cl.Tensor["M", "K"]):

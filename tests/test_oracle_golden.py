@@ -29,6 +29,16 @@ def _run(name):
         return [orc.swiglu(inp["x"], inp["w0"], inp["w1"], dt)]
     if family == "attention":
         return [orc.attention(inp["q"], inp["k"], inp["v"], dt)]
+    if family == "attention_exact":
+        return [orc.attention_exact(inp["q"], inp["k"], inp["v"], dt)]
+    if family == "matmul_matmul":
+        return [orc.matmul_matmul(inp["q"], inp["k"], inp["v"], dt)]
+    if family == "qknorm":
+        return [orc.qknorm_attention(inp["q"], inp["k"], inp["v"], opt["eps"], dt)]
+    if family == "matmul_rowsum":
+        return [orc.matmul_rowsum(inp["x"], inp["w0"], dt)]
+    if family == "lora":
+        return [orc.lora(inp["x"], inp["w"], inp["a"], inp["b"], dt)]
     if family == "mla":
         return [orc.mla_decode(inp["q"], inp["kv"], inp["q_pe"], inp["k_pe"], opt["scale"], dt)]
     if family == "gqa_paged":

@@ -19,7 +19,7 @@ _LAZY = {
     "CleaveError": ".core.errors",
 }
 _SUBMODULES = {"ops", "lang", "codegen", "runtime", "pipeline", "frontend", "core", "workloads", "sharding",
-               "microbench"}
+               "microbench", "arch"}
 
 __all__ = sorted(["Cb200Error", *_LAZY, *_SUBMODULES])
 

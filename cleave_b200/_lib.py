@@ -53,6 +53,18 @@ class MatmulRowsumArgs(C.Structure):
     ]
 
 
+class MatmulMatmulArgs(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("out", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("num_qo_heads", C.c_int32), ("num_kv_heads", C.c_int32), ("q_len", C.c_int32), ("kv_len", C.c_int32),
+        ("head_dim", C.c_int32), ("dtype", C.c_int32), ("impl", C.c_int32),
+    ]
+
+
+MM_IMPL = {"auto": 0, "scores_first": 1, "chain": 2}
+
+
 class LoraArgs(C.Structure):
     _fields_ = [
         ("x", C.c_void_p), ("w", C.c_void_p), ("a", C.c_void_p), ("b", C.c_void_p), ("y", C.c_void_p),
@@ -138,6 +150,12 @@ def lib() -> C.CDLL:
         L.cb200_matmul_rowsum_workspace_bytes.argtypes = [C.POINTER(MatmulRowsumArgs)]
         L.cb200_matmul_rowsum.restype = C.c_int
         L.cb200_matmul_rowsum.argtypes = [C.POINTER(MatmulRowsumArgs), C.c_void_p]
+        L.cb200_matmul_matmul_workspace_bytes.restype = C.c_size_t
+        L.cb200_matmul_matmul_workspace_bytes.argtypes = [C.POINTER(MatmulMatmulArgs)]
+        L.cb200_matmul_matmul_uses_chain.restype = C.c_int
+        L.cb200_matmul_matmul_uses_chain.argtypes = [C.POINTER(MatmulMatmulArgs)]
+        L.cb200_matmul_matmul.restype = C.c_int
+        L.cb200_matmul_matmul.argtypes = [C.POINTER(MatmulMatmulArgs), C.c_void_p]
         L.cb200_lora_workspace_bytes.restype = C.c_size_t
         L.cb200_lora_workspace_bytes.argtypes = [C.POINTER(LoraArgs)]
         L.cb200_lora.restype = C.c_int

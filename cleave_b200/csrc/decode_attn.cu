@@ -85,9 +85,13 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
   const int nthreads = blockDim.x;
   const int hkvv = p.hkv * p.vblk;
 
+  // The launch carries the programmatic-serialization attribute: this CTA may start while the kernel
+  // before it in the stream is still draining. Nothing that kernel may have written (page tables, the
+  // caches, Q, the workspace) is touched before pdl_wait(); what precedes it is shared-memory set-up.
   // ---- tile prefix over requests (every CTA computes the same table)
   int tiles_per_req = 0;
   if (p.paged) {
+    pdl_wait();
     int* scratch = reinterpret_cast<int*>(merge);  // merge buffer is free at this point
     const int per = ceil_div(p.batch, nthreads);
     const int i0 = min(tid * per, p.batch), i1 = min(i0 + per, p.batch);
@@ -125,6 +129,8 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
     }
   }
   __syncthreads();
+  if (!p.paged) pdl_wait();
+  pdl_launch_dependents();  // the next kernel's CTAs may take SMs as this grid's CTAs retire
 
   const int total_per_head = p.paged ? P[p.batch] : p.batch * tiles_per_req;
   const int total = hkvv * total_per_head;
@@ -637,7 +643,19 @@ int launch_decode(const DecodeSetup& s, cudaStream_t stream) {
   } else if (dev >= 16) {
     CB200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
   }
-  kern<<<s.grid, SmemPlan<D, GATHER>::kThreads, s.smem_bytes, stream>>>(s.tm_k, s.tm_v, s.p);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(s.grid, 1, 1);
+  cfg.blockDim = dim3(SmemPlan<D, GATHER>::kThreads, 1, 1);
+  cfg.dynamicSmemBytes = s.smem_bytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  // the grid may be scheduled while the preceding kernel of the stream drains; it waits (griddepcontrol.wait)
+  // before its first global access
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  CB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, s.tm_k, s.tm_v, s.p));
   CB200_CUDA_TRY(cudaGetLastError());
   return CB200_OK;
 }

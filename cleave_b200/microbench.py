@@ -120,7 +120,7 @@ def attn_prefill_case(hq=32, hkv=32, s=4096, d=64, dtype=torch.float16, causal=F
     return fn, flops, byts
 
 
-def fused_attn_case(kind, hq, hkv, s, d, dtype=torch.float16):
+def fused_attn_case(kind, hq, hkv, s, d, dtype=torch.float16, impl="auto"):
     """(Q K^T) V without softmax (demo/matmul_matmul.py) or QK-norm attention (demo/qknorm.py) at demo size."""
     g = _gen()
     q = torch.randn(hq, s, d, generator=g).to(dtype).cuda()
@@ -129,7 +129,7 @@ def fused_attn_case(kind, hq, hkv, s, d, dtype=torch.float16):
     out = torch.empty_like(q)
     byts = (2 * q.numel() + 2 * k.numel()) * 2
     if kind == "matmul_matmul":
-        fn = _rotating(lambda t: (lambda: ops.matmul_matmul(t[0], t[1], t[2], out=t[3])), [q, k, v, out])
+        fn = _rotating(lambda t: (lambda: ops.matmul_matmul(t[0], t[1], t[2], out=t[3], impl=impl)), [q, k, v, out])
     else:
         fn = _rotating(lambda t: (lambda: ops.qknorm_attention(t[0], t[1], t[2], eps=1e-6, out=t[3])), [q, k, v, out])
     return fn, 4 * hq * s * s * d, byts
@@ -257,6 +257,7 @@ CONFIGS = {
     "gqa_prefill_causal_h32_kv8_s4096_d128": lambda: attn_prefill_case(32, 8, 4096, 128, torch.bfloat16, True),
     "gqa_prefill_h32_kv8_s4096_d128": lambda: attn_prefill_case(32, 8, 4096, 128, torch.bfloat16, False),
     "demo_matmul_matmul_bh32_s4096_d64": lambda: fused_attn_case("matmul_matmul", 32, 32, 4096, 64),
+    "demo_matmul_matmul_scores_first_bh32_s4096_d64": lambda: fused_attn_case("matmul_matmul", 32, 32, 4096, 64, impl="scores_first"),
     "demo_qknorm_h64_kv8_s4096_d128": lambda: fused_attn_case("qknorm", 64, 8, 4096, 128),
     "demo_mha_decode_exact_h32_sq64_skv256_d64": lambda: attn_prefill_case_rect(32, 32, 64, 256, 64),
     "demo_matmul_rowsum_4096x4096x64": lambda: rowsum_case(),
@@ -285,7 +286,7 @@ def measure(name, build):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--op", default=None, choices=["matmul", "rmsnorm_matmul", "swiglu", "gqa_decode", "mla_decode", "attn_prefill", "gqa_paged_ps1",
-                                             "mla_paged_decode"])
+                                             "mla_paged_decode", "matmul_matmul", "qknorm", "matmul_rowsum", "lora"])
     ap.add_argument("--m", type=int, default=4096)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
@@ -303,6 +304,14 @@ def main():
             build = lambda: paged_decode_case(1)  # noqa: E731
         elif a.op == "mla_paged_decode":
             build = mla_paged_decode_case
+        elif a.op == "matmul_matmul":
+            build = lambda: fused_attn_case("matmul_matmul", 32, 32, 4096, 64)  # noqa: E731
+        elif a.op == "qknorm":
+            build = lambda: fused_attn_case("qknorm", 64, 8, 4096, 128)  # noqa: E731
+        elif a.op == "matmul_rowsum":
+            build = rowsum_case
+        elif a.op == "lora":
+            build = lora_case
         elif a.op == "attn_prefill":
             build = lambda: attn_prefill_case(32, 8, a.m, a.k if a.k in (64, 128) else 128, torch.bfloat16, False)  # noqa: E731
         else:

@@ -169,11 +169,32 @@ def attention_prefill(q, k, v, sm_scale=None, *, causal=False, out=None, lse=Non
     return out
 
 
-def matmul_matmul(q, k, v, *, out=None):
+def matmul_matmul(q, k, v, *, out=None, impl="auto"):
     """``O = (Q K^T) V`` without softmax (reference operator: demo/matmul_matmul.py:11-13): q (HQ, SQ, D);
-    k, v (HKV, SKV, D); D 64 or 128. Runs on the tcgen05 attention kernel with the scores passed through:
-    they are rounded to the storage dtype before the second product."""
-    return attention_prefill(q, k, v, 1.0, out=out, linear=True)
+    k, v (HKV, SKV, D); D 64 or 128. ``impl``: "scores_first" evaluates (Q K^T) V on the tcgen05 attention
+    kernel (scores rounded to the storage dtype before the second product); "chain" evaluates Q (K^T V),
+    a D x D intermediate per kv head and one pass over every input; "auto" takes the chain when it saves
+    at least four times the FLOPs (32 times at the demo's S = 4096, D = 64)."""
+    q, k, v = _cuda(q, "q"), _cuda(k, "k"), _cuda(v, "v")
+    hq, sq, d = q.shape
+    hkv, skv, d2 = k.shape
+    if d2 != d or v.shape != k.shape or hq % hkv:
+        raise ValueError("shapes: q (HQ,SQ,D), k/v (HKV,SKV,D), HQ a multiple of HKV")
+    if out is None:
+        out = torch.empty_like(q)
+    a = _lib.MatmulMatmulArgs()
+    a.q, a.k, a.v, a.out = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr()
+    a.num_qo_heads, a.num_kv_heads, a.q_len, a.kv_len, a.head_dim = hq, hkv, sq, skv, d
+    a.dtype, a.impl = _dtype_code(q), _lib.MM_IMPL[impl]
+    need = _lib.lib().cb200_matmul_matmul_workspace_bytes(C.byref(a))
+    if need == 0:
+        _lib.check(_lib.lib().cb200_matmul_matmul(C.byref(a), _stream()))  # reports why the plan is refused
+    # the scores-first order shares the attention kernel's workspace (its status word)
+    chain = bool(_lib.lib().cb200_matmul_matmul_uses_chain(C.byref(a)))
+    ws = workspace("matmul_chain" if chain else "attn_prefill", need, q.device)
+    a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+    _lib.check(_lib.lib().cb200_matmul_matmul(C.byref(a), _stream()))
+    return out
 
 
 def qknorm_attention(q, k, v, sm_scale=None, *, eps=1e-6, out=None, lse=None):

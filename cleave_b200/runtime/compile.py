@@ -199,7 +199,8 @@ def build_inputs_and_reference(spec: KernelSpec, device="cuda", seed=None):
         base = p.name.replace("PlaceHolder_", "")
         if base == "gamma":
             t = 1 + 0.1 * torch.randn(shape, generator=g)
-        elif base in ("w", "w0", "w1"):
+        elif base in ("w", "w0", "w1") or (f_ == "lora" and base == "a"):
+            # weights scaled so that products stay O(1): intermediates (LoRA's X @ A) are 16-bit on the GPU
             t = torch.randn(shape, generator=g) / d["K"] ** 0.5
         elif f_ == "lora" and base == "b":
             t = torch.randn(shape, generator=g) / d["R"] ** 0.5

@@ -268,6 +268,41 @@ size_t cb200_attn_prefill_ragged_workspace_bytes(const cb200_attn_prefill_ragged
 int cb200_attn_prefill_ragged(const cb200_attn_prefill_ragged_args* a, void* stream);
 
 /* ------------------------------------------------------------------------------------------
+ * O = (Q K^T) V without softmax or scale; q (num_qo_heads, q_len, head_dim), k / v (num_kv_heads, kv_len,
+ * head_dim), query head h uses kv head h / (HQ / HKV); head_dim 64 or 128. Replaces the fused kernel of
+ * demo/matmul_matmul.py ((q @ k.mT) @ v). Two evaluation orders:
+ *   CB200_MM_SCORES_FIRST  (Q K^T) V on the tcgen05 attention kernel (cb200_attn_prefill, linear scores);
+ *   CB200_MM_CHAIN         Q (K^T V): T = K^T V (head_dim x head_dim per kv head, fp32 accumulation over
+ *                          token chunks summed in a fixed order, stored in the storage dtype), then O = Q T.
+ *                          2 (kv_len + g q_len) D^2 FLOPs per kv head instead of 4 g q_len kv_len D, every
+ *                          input byte read once;
+ *   CB200_MM_AUTO          the chain when it saves at least four times the FLOPs.
+ * Both orders round one intermediate to the storage dtype (the scores, or T).
+ * ---------------------------------------------------------------------------------------- */
+typedef enum { CB200_MM_AUTO = 0, CB200_MM_SCORES_FIRST = 1, CB200_MM_CHAIN = 2 } cb200_mm_impl;
+
+typedef struct {
+  const void* q;
+  const void* k;
+  const void* v;
+  void* out; /* (num_qo_heads, q_len, head_dim) */
+  void* workspace;
+  size_t workspace_bytes;
+  int32_t num_qo_heads;
+  int32_t num_kv_heads;
+  int32_t q_len;
+  int32_t kv_len;
+  int32_t head_dim;
+  int32_t dtype; /* cb200_dtype */
+  int32_t impl;  /* cb200_mm_impl */
+} cb200_matmul_matmul_args;
+
+size_t cb200_matmul_matmul_workspace_bytes(const cb200_matmul_matmul_args* a);
+/* 1 when the launch will use the chain order, 0 otherwise. */
+int cb200_matmul_matmul_uses_chain(const cb200_matmul_matmul_args* a);
+int cb200_matmul_matmul(const cb200_matmul_matmul_args* a, void* stream);
+
+/* ------------------------------------------------------------------------------------------
  * Y = rowsum(X @ W): y[m] = sum_n (X @ W)[m, n]; X (m, k), W (k, n) row-major, y (m) = (m, 1); k and n
  * multiples of 8. Replaces the fused matmul + reduce kernel of demo/matmul_rowsum.py
  * ((x @ w).sum(-1, keepdim=True)). Computed as X @ (W 1): one pass over W for its fp32 row sums (k

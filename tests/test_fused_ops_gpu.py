@@ -60,13 +60,34 @@ def test_matches_reference_golden(name):
 @pytest.mark.parametrize("dt", ["f16", "bf16"])
 @pytest.mark.parametrize("hq,hkv,sq,skv,d", [(4, 4, 256, 256, 64), (8, 2, 300, 517, 128), (4, 1, 130, 1000, 64),
                                              (3, 3, 1, 77, 64), (2, 1, 640, 640, 128), (160, 32, 129, 260, 64)])
-def test_matmul_matmul_vs_oracle(hq, hkv, sq, skv, d, dt):
-    """Reference: demo/matmul_matmul.py:11-13. Key counts that are not multiples of the 128-key tile check
-    that rows past the end contribute nothing (they are zero rows of K and V, not masked scores)."""
+@pytest.mark.parametrize("impl", ["scores_first", "chain"])
+def test_matmul_matmul_vs_oracle(hq, hkv, sq, skv, d, dt, impl):
+    """Reference: demo/matmul_matmul.py:11-13, in both evaluation orders. Key counts that are not multiples
+    of the tile sizes check that rows past the end contribute nothing (they are zero rows of K and V)."""
     inp = cases.matmul_matmul_inputs(hq * 1000 + sq, hq, hkv, sq, skv, d, dt)
-    got = _ops().matmul_matmul(dev(inp["q"], dt), dev(inp["k"], dt), dev(inp["v"], dt))
+    got = _ops().matmul_matmul(dev(inp["q"], dt), dev(inp["k"], dt), dev(inp["v"], dt), impl=impl)
     _check("attn_prefill")
     assert_close(host(got), orc.matmul_matmul(inp["q"], inp["k"], inp["v"], dt))
+
+
+def test_matmul_matmul_chain_is_bit_stable_and_picked_for_long_sequences():
+    """The token chunks of K^T V are summed in a fixed order by the last CTA to arrive: repeat launches give
+    the same bits. The automatic choice takes the chain at the demo shape and keeps (Q K^T) V where the
+    chain saves little (demo/matmul_matmul.py's split preset, S_Q = 64)."""
+    import ctypes as C
+
+    from cleave_b200 import _lib
+
+    inp = cases.matmul_matmul_inputs(3, 8, 4, 1000, 3000, 64, "f16")
+    q, k, v = dev(inp["q"], "f16"), dev(inp["k"], "f16"), dev(inp["v"], "f16")
+    first = _ops().matmul_matmul(q, k, v, impl="chain")
+    for _ in range(3):
+        assert torch.equal(_ops().matmul_matmul(q, k, v, impl="chain"), first)
+    a = _lib.MatmulMatmulArgs()
+    a.num_qo_heads, a.num_kv_heads, a.q_len, a.kv_len, a.head_dim, a.dtype = 32, 32, 4096, 4096, 64, _lib.F16
+    assert _lib.lib().cb200_matmul_matmul_uses_chain(C.byref(a)) == 1
+    a.q_len = 64
+    assert _lib.lib().cb200_matmul_matmul_uses_chain(C.byref(a)) == 0
 
 
 @pytest.mark.parametrize("dt", ["f16", "bf16"])
@@ -153,9 +174,10 @@ def test_demo_sizes_against_oracle_slices():
     run on their slices (the whole problem is minutes of CPU work)."""
     ops = _ops()
     inp = cases.matmul_matmul_inputs(1, 32, 32, 4096, 4096, 64, "f16")
-    got = host(ops.matmul_matmul(dev(inp["q"], "f16"), dev(inp["k"], "f16"), dev(inp["v"], "f16")))
-    for h in (0, 31):
-        assert_close(got[h:h + 1], orc.matmul_matmul(inp["q"][h:h + 1], inp["k"][h:h + 1], inp["v"][h:h + 1], "f16"))
+    for impl in ("chain", "scores_first"):
+        got = host(ops.matmul_matmul(dev(inp["q"], "f16"), dev(inp["k"], "f16"), dev(inp["v"], "f16"), impl=impl))
+        for h in (0, 31):
+            assert_close(got[h:h + 1], orc.matmul_matmul(inp["q"][h:h + 1], inp["k"][h:h + 1], inp["v"][h:h + 1], "f16"))
     inp = cases.attention_inputs(2, 64, 8, 4096, 4096, 128, "f16")
     got = host(ops.qknorm_attention(dev(inp["q"], "f16"), dev(inp["k"], "f16"), dev(inp["v"], "f16"), eps=1e-6))
     _check("attn_prefill")

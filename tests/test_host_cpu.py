@@ -308,3 +308,26 @@ def test_oracle_causal_mask_is_end_aligned():
         want, want_lse = orc.attention_masked(q[:, r:r + 1], k[:, :5 + r], v[:, :5 + r], 0.25, False, "f16")
         np.testing.assert_allclose(out[:, r:r + 1], want, rtol=1e-3, atol=1e-3)
         np.testing.assert_allclose(lse[:, r:r + 1], want_lse, rtol=1e-5, atol=1e-5)
+
+
+def test_arch_description_and_tile_snapping():
+    """The sm_100 row in the reference's format (python/cleave/arch/cuda.py:120-186) and the mapping of a
+    scheduler's tile hints onto the kernels' tiles."""
+    from cleave_b200 import arch
+
+    dev = arch.B200()
+    for name in ("reg_cap", "smem_cap", "compute_max_core", "warp_size", "sm_partition", "transaction_size",
+                 "max_smem_usage", "bandwidth", "platform", "compute_capability", "l2_cache_size_bytes"):
+        assert getattr(dev, name)  # every field of the reference's Arch is present and filled in
+    assert dev.compute_max_core == arch.OFFLINE_DEVICES[100]["sms"] == 148
+    assert [128, 256] in dev.get_avaliable_tensorintrin_shapes()
+    assert dev.is_tensorcore_supported_precision("bfloat16", "float32")
+    assert not dev.is_tensorcore_supported_precision("int8", "int32")
+    assert arch.snap_tile(64, 32) == (128, 128)            # the split-K matmul partial's Hopper hint
+    assert arch.snap_tile(128, 256) == (128, 256)
+    assert arch.snap_tile(256, 128, m=4096) == (256, 256)
+    assert arch.snap_tile(256, 128, m=64) == (128, 256)    # no pair tile for a 64-row problem
+    assert arch.snap_tile(64, 512, n=128) == (128, 128)    # the problem has 128 columns only
+    assert arch.tmem_columns_needed((128, 256)) == dev.tmem_columns
+    with pytest.raises(ValueError):
+        arch.snap_tile(0, 8)

@@ -4,13 +4,13 @@
 //
 // when the sequence lengths dwarf the head dimension: 2 * (SKV + SQ) * D * D FLOPs per head instead of
 // 4 * SQ * SKV * D (32 times fewer at the demo's S = 4096, D = 64), and every input byte is read once, so
-// the operator becomes HBM-bound. Two kernels on warp-level MMAs (m16n8k16; at 30 FLOP per byte the
+// the operator becomes HBM-bound. Three kernels, the products on warp-level MMAs (m16n8k16; at 30 FLOP per byte the
 // tensor pipe is not the limit):
 //   ktv_kernel   a CTA owns (kv head, chunk of tokens): T_part = K_chunk^T V_chunk in fp32. K and V tiles of
-//                64 tokens are staged by cp.async (double-buffered, padded rows); both operands are read
+//                64 tokens are staged by cp.async (four stages, padded rows); both operands are read
 //                with transposing ldmatrix (the token axis is the contraction axis of both). Partials go
-//                to the workspace; the last CTA of a head to arrive sums them in chunk order (bit-stable)
-//                and stores T in the storage type.
+//                to the workspace.
+//   tsum_kernel  sums the partials of a head in chunk order (bit-stable) and stores T in the storage type.
 //   qt_kernel    a CTA owns (query head, 128 query rows): O_tile = Q_tile T, T (D x D, 16-bit) resident in
 //                shared memory.
 // The (Q K^T) V order (scores rounded to 16 bits, then the second product) stays available on the tcgen05
@@ -32,7 +32,8 @@ struct Cfg {
   static constexpr int kThreads = kWarps * 32;
   static constexpr int kRowBytes = D * 2 + 16;   // padded: 8 consecutive rows fall in distinct bank groups
   static constexpr int kMatBytes = kTok * kRowBytes;
-  static constexpr int kKtvSmem = 2 * 2 * kMatBytes;  // two stages of (K, V)
+  static constexpr int kStages = 4;
+  static constexpr int kKtvSmem = kStages * 2 * kMatBytes;  // stages of (K, V)
   static constexpr int kQtRows = 128;
   static constexpr int kQtSmem = (kQtRows + D) * kRowBytes;  // Q tile + T
 };
@@ -44,7 +45,6 @@ struct Params {
   void* out;
   float* partials;  // [chunk][hkv][D][D]
   void* t16;        // [hkv][D][D] storage type
-  int* counters;    // [hkv], zero between launches
   int hq, hkv, sq, skv, chunks, chunk_tokens;
 };
 
@@ -61,7 +61,6 @@ template <typename T, int D>
 __global__ void __launch_bounds__(Cfg<D>::kThreads) ktv_kernel(const Params p) {
   using C = Cfg<D>;
   extern __shared__ __align__(16) uint8_t smem[];
-  __shared__ int last_flag;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int chunk = blockIdx.x, hk = blockIdx.y;
   const int t_begin = chunk * p.chunk_tokens, t_end = min(t_begin + p.chunk_tokens, p.skv);
@@ -89,16 +88,20 @@ __global__ void __launch_bounds__(Cfg<D>::kThreads) ktv_kernel(const Params p) {
 #pragma unroll
   for (int n = 0; n < D / 8; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
 
-  if (n_tiles > 0) stage_tile(0, 0);
+  // kStages - 1 tiles in flight; one commit group per iteration (an empty one past the end) keeps the
+  // wait count fixed
+  constexpr int kStages = C::kStages;
+#pragma unroll
+  for (int s = 0; s < kStages - 1; ++s) {
+    if (s < n_tiles) stage_tile(s, s);
+    else cp_async_commit();
+  }
   for (int j = 0; j < n_tiles; ++j) {
-    const int st = j & 1;
-    if (j + 1 < n_tiles) {
-      stage_tile(j + 1, st ^ 1);
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
-    }
-    __syncthreads();
+    const int st = j % kStages;
+    cp_async_wait<kStages - 2>();
+    __syncthreads();  // tile j has landed for everyone, and everyone is done with tile j - 1
+    if (j + kStages - 1 < n_tiles) stage_tile(j + kStages - 1, (j + kStages - 1) % kStages);
+    else cp_async_commit();
     const uint32_t ks = smem_base + st * 2 * C::kMatBytes, vs = ks + C::kMatBytes;
 #pragma unroll
     for (int kk = 0; kk < kTok / 16; ++kk) {
@@ -124,10 +127,10 @@ __global__ void __launch_bounds__(Cfg<D>::kThreads) ktv_kernel(const Params p) {
         mma_16816<T>(acc[2 * nb + 1], a, b[2], b[3]);
       }
     }
-    __syncthreads();  // the stage is refilled by the next iteration's copies
   }
+  cp_async_wait<0>();
 
-  // ---- partial to the workspace, last arriver of the head sums the chunks in order
+  // ---- partial to the workspace; tsum_kernel adds the chunks of a head in order
   const int g = lane >> 2, t2 = (lane & 3) * 2;
   float* part = p.partials + (static_cast<size_t>(chunk) * p.hkv + hk) * D * D;
 #pragma unroll
@@ -136,25 +139,35 @@ __global__ void __launch_bounds__(Cfg<D>::kThreads) ktv_kernel(const Params p) {
     *reinterpret_cast<float2*>(part + row * D + col) = make_float2(acc[n][0], acc[n][1]);
     *reinterpret_cast<float2*>(part + (row + 8) * D + col) = make_float2(acc[n][2], acc[n][3]);
   }
-  __threadfence();
-  __syncthreads();
-  if (tid == 0) last_flag = atomicAdd(p.counters + hk, 1) == p.chunks - 1 ? 1 : 0;
-  __syncthreads();
-  if (!last_flag) return;
-  __threadfence();
-  T* t16 = reinterpret_cast<T*>(p.t16) + static_cast<size_t>(hk) * D * D;
-  for (int i = tid * 4; i < D * D; i += C::kThreads * 4) {
-    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int c = 0; c < p.chunks; ++c) {
-      const float4 x = __ldcg(reinterpret_cast<const float4*>(p.partials + (static_cast<size_t>(c) * p.hkv + hk) * D * D + i));
-      s.x += x.x; s.y += x.y; s.z += x.z; s.w += x.w;
+}
+
+// Sums the chunk partials of T in chunk order (bit-stable) and stores T in the storage type: one thread
+// per four consecutive elements, all of its loads in flight at once. A last-arriver sum inside ktv_kernel
+// was measured first: one CTA per head walking 16 partials is a chain of dependent L2 round trips
+// that took as long as the products themselves.
+template <typename T>
+__global__ void __launch_bounds__(256) tsum_kernel(const Params p, int dd) {
+  const int per_head = dd / 4;
+  const int idx = blockIdx.x * 256 + threadIdx.x;
+  if (idx >= p.hkv * per_head) return;
+  const int hk = idx / per_head, i = (idx - hk * per_head) * 4;
+  float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int c0 = 0; c0 < p.chunks; c0 += 8) {
+    float4 x[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int c = min(c0 + u, p.chunks - 1);
+      x[u] = __ldcg(reinterpret_cast<const float4*>(p.partials + (static_cast<size_t>(c) * p.hkv + hk) * dd + i));
     }
-    uint2 pk;
-    pk.x = pack2<T>(s.x, s.y);
-    pk.y = pack2<T>(s.z, s.w);
-    *reinterpret_cast<uint2*>(t16 + i) = pk;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      if (c0 + u < p.chunks) { s.x += x[u].x; s.y += x[u].y; s.z += x[u].z; s.w += x[u].w; }
+    }
   }
-  if (tid == 0) p.counters[hk] = 0;  // ready for the next launch
+  uint2 pk;
+  pk.x = pack2<T>(s.x, s.y);
+  pk.y = pack2<T>(s.z, s.w);
+  *reinterpret_cast<uint2*>(reinterpret_cast<T*>(p.t16) + static_cast<size_t>(hk) * dd + i) = pk;
 }
 
 // ------------------------------------------------------------------------------------------ Q T
@@ -212,12 +225,24 @@ __global__ void __launch_bounds__(128) qt_kernel(const Params p) {
         mma_16816<T>(acc[2 * nb + 1], a, b[2], b[3]);
       }
     }
-    const int row_a = q0 + r0 + g, row_b = row_a + 8;
+    // stage the 16 x D block over this warp's own rows of the Q tile (no other warp reads them), then
+    // store whole 16-byte pieces: a row leaves as full 128-byte lines
+    __syncwarp();
 #pragma unroll
     for (int n = 0; n < D / 8; ++n) {
       const int col = n * 8 + t2;
-      if (row_a < p.sq) *reinterpret_cast<uint32_t*>(obase + static_cast<size_t>(row_a) * D + col) = pack2<T>(acc[n][0], acc[n][1]);
-      if (row_b < p.sq) *reinterpret_cast<uint32_t*>(obase + static_cast<size_t>(row_b) * D + col) = pack2<T>(acc[n][2], acc[n][3]);
+      *reinterpret_cast<uint32_t*>(smem + (r0 + g) * C::kRowBytes + col * 2) = pack2<T>(acc[n][0], acc[n][1]);
+      *reinterpret_cast<uint32_t*>(smem + (r0 + g + 8) * C::kRowBytes + col * 2) = pack2<T>(acc[n][2], acc[n][3]);
+    }
+    __syncwarp();
+    constexpr int kChunks = D / 8;
+#pragma unroll
+    for (int i = lane; i < 16 * kChunks; i += 32) {
+      const int r = i / kChunks, c = i - r * kChunks;
+      const int row = q0 + r0 + r;
+      if (row < p.sq)
+        *reinterpret_cast<uint4*>(obase + static_cast<size_t>(row) * D + c * 8) =
+            *reinterpret_cast<const uint4*>(smem + (r0 + r) * C::kRowBytes + c * 16);
     }
   }
 }
@@ -230,7 +255,7 @@ namespace {
 struct ChainPlan {
   bool chain;
   int chunks, chunk_tokens;
-  size_t counters_off, partials_off, t16_off, total;
+  size_t partials_off, t16_off, total;
 };
 
 int plan_chain(const cb200_matmul_matmul_args* a, ChainPlan* pl) {
@@ -244,19 +269,18 @@ int plan_chain(const cb200_matmul_matmul_args* a, ChainPlan* pl) {
   // FLOPs per kv head: scores first 4 g SQ SKV D, chain 2 (SKV + g SQ) D D
   const double ratio = 2.0 * group * a->q_len * static_cast<double>(a->kv_len) / (d * (a->kv_len + group * a->q_len));
   pl->chain = a->impl == CB200_MM_CHAIN || (a->impl == CB200_MM_AUTO && ratio >= 4.0);
-  // chunks of whole 64-token tiles, enough CTAs for about two per SM
+  // chunks of whole 64-token tiles, enough CTAs for about four per SM
   const int sms = sm_count();
   if (sms <= 0) return CB200_ERR_CUDA;
   const int tiles = ceil_div(a->kv_len, chain::kTok);
-  int chunks = ceil_div(2 * sms, a->num_kv_heads);
+  int chunks = ceil_div(4 * sms, a->num_kv_heads);
   if (chunks > tiles) chunks = tiles;
   if (chunks > 64) chunks = 64;
   if (chunks < 1) chunks = 1;
   pl->chunk_tokens = ceil_div(tiles, chunks) * chain::kTok;
   pl->chunks = ceil_div(a->kv_len, pl->chunk_tokens);
   const size_t dd = static_cast<size_t>(a->head_dim) * a->head_dim;
-  pl->counters_off = kWsHeaderBytes;
-  pl->partials_off = align_up(pl->counters_off + static_cast<size_t>(a->num_kv_heads) * 4, 256);
+  pl->partials_off = kWsHeaderBytes;
   pl->t16_off = align_up(pl->partials_off + static_cast<size_t>(pl->chunks) * a->num_kv_heads * dd * 4, 256);
   pl->total = align_up(pl->t16_off + static_cast<size_t>(a->num_kv_heads) * dd * 2, 256);
   return CB200_OK;
@@ -268,7 +292,6 @@ int launch_chain(const cb200_matmul_matmul_args* a, const ChainPlan& pl, cudaStr
   chain::Params p{};
   uint8_t* ws = static_cast<uint8_t*>(a->workspace);
   p.q = a->q; p.k = a->k; p.v = a->v; p.out = a->out;
-  p.counters = reinterpret_cast<int*>(ws + pl.counters_off);
   p.partials = reinterpret_cast<float*>(ws + pl.partials_off);
   p.t16 = ws + pl.t16_off;
   p.hq = a->num_qo_heads; p.hkv = a->num_kv_heads; p.sq = a->q_len; p.skv = a->kv_len;
@@ -278,6 +301,9 @@ int launch_chain(const cb200_matmul_matmul_args* a, const ChainPlan& pl, cudaStr
   CB200_CUDA_TRY(cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kKtvSmem));
   CB200_CUDA_TRY(cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kQtSmem));
   k1<<<dim3(pl.chunks, a->num_kv_heads), C::kThreads, C::kKtvSmem, st>>>(p);
+  CB200_CUDA_TRY(cudaGetLastError());
+  const int dd = D * D;
+  chain::tsum_kernel<T><<<ceil_div(a->num_kv_heads * (dd / 4), 256), 256, 0, st>>>(p, dd);
   CB200_CUDA_TRY(cudaGetLastError());
   k2<<<dim3(ceil_div(a->q_len, C::kQtRows), a->num_qo_heads), 128, C::kQtSmem, st>>>(p);
   CB200_CUDA_TRY(cudaGetLastError());

@@ -9,7 +9,9 @@
 //   lora            Y = X @ W + (X @ A) @ B                          (demo/lora.py)
 //       Three launches of the tcgen05 GEMM of this library on one stream: T = X @ A (rank R columns),
 //       Z = T @ B, Y = X @ W + Z with Z added in the epilogue of the last product. T and Z live in the
-//       workspace in the storage type (the reference's kernels round intermediates the same way).
+//       workspace in the storage type (the reference's kernels round intermediates the same way). The
+//       launches are dependent launches: the big product streams W beside the two small ones and only
+//       its epilogue waits for Z.
 
 #include "common.cuh"
 
@@ -98,6 +100,8 @@ int plan_lora(const cb200_lora_args* a, LoraLayout* L) {
   L->z = g; L->z.m = a->m; L->z.n = a->n; L->z.k = a->r;
   L->y = g; L->y.m = a->m; L->y.n = a->n; L->y.k = a->k;
   L->y.addend = reinterpret_cast<const void*>(16);  // planned as the launch will be: with an addend
+  L->y.dependent_launch = 2;
+  L->z.dependent_launch = 1;
   size_t ws = 0;
   for (const cb200_gemm_args* p : {&L->t, &L->z, &L->y}) {
     const size_t need = cb200_gemm_workspace_bytes(p);
@@ -105,7 +109,7 @@ int plan_lora(const cb200_lora_args* a, LoraLayout* L) {
     if (need > ws) ws = need;
   }
   L->gemm_ws = align_up(ws, 256);
-  L->t_off = L->gemm_ws;
+  L->t_off = 3 * L->gemm_ws;  // one GEMM scratch per product: they overlap on the GPU
   L->z_off = align_up(L->t_off + static_cast<size_t>(a->m) * a->r * 2, 256);
   L->total = align_up(L->z_off + static_cast<size_t>(a->m) * a->n * 2, 256);
   return CB200_OK;
@@ -146,11 +150,15 @@ extern "C" int cb200_lora(const cb200_lora_args* a, void* stream) {
   uint8_t* ws = static_cast<uint8_t*>(a->workspace);
   void* t = ws + L.t_off;
   void* z = ws + L.z_off;
-  // the three products share the GEMM scratch at the head of the workspace: they run in order on one stream
+  // Z waits for T before it reads anything; Y runs its whole main loop beside T and Z and waits for Z only
+  // in its epilogue, where Z is added (dependent launches). Each product has its own GEMM scratch.
+  int slot = 0;
   for (cb200_gemm_args* g : {&L.t, &L.z, &L.y}) {
-    g->workspace = ws;
+    g->workspace = ws + static_cast<size_t>(slot++) * L.gemm_ws;
     g->workspace_bytes = L.gemm_ws;
   }
+  L.z.dependent_launch = 1;
+  L.y.dependent_launch = 2;
   L.t.x = a->x; L.t.w = a->a; L.t.y = t;
   L.z.x = t;    L.z.w = a->b; L.z.y = z;
   L.y.x = a->x; L.y.w = a->w; L.y.y = a->y; L.y.addend = z;

@@ -52,6 +52,7 @@ struct GemmParams {
   float eps;
   int a_rows;  // rows of the A box: 128, or M rounded up to 8 when M is smaller
   const void* addend;  // MODE 0, may be null: (M, N) in the storage type, added in the epilogue
+  int pdl;             // cb200_gemm_args.dependent_launch
 };
 
 template <int MODE, int NBW>
@@ -126,6 +127,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_holder);
+  // Dependent launch (the grid may have started while the preceding kernel of the stream still runs):
+  // mode 1 waits for that kernel here, before any operand is read; mode 2 lets the main loop run and waits
+  // in the epilogue warps only, before the addend - the one operand the preceding kernel wrote - is read.
+  pdl_launch_dependents();  // before the wait: a dependent of this grid waits for this grid's completion itself
+  if (p.pdl == 1) pdl_wait();
 
   // ---- this CTA's share of the (tile, chunk) list
   const int S = p.chunks_per_tile;
@@ -293,6 +299,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     T* yout = reinterpret_cast<T*>(p.y);
     const float inv_k = 1.f / static_cast<float>(p.K);
     int buf = 0, acc_phase = 0;
+    if (p.pdl == 2) pdl_wait();
 
     // v: 32 consecutive accumulator columns starting at tile column c0 (for MODE 2: gate and up)
     auto finish_and_store = [&](const float* v, const float* up, int gr, int gc0, float rs) {
@@ -650,6 +657,7 @@ int plan_gemm(const cb200_gemm_args* a, GemmSetup* s, bool need_maps) {
   if (a->dtype != CB200_F16 && a->dtype != CB200_BF16) return CB200_ERR_UNSUPPORTED;
   if (a->k % 8 || a->n % 8) return CB200_ERR_UNSUPPORTED;  // TMA strides are multiples of 16 bytes
   if (a->addend && a->op != CB200_GEMM_MATMUL) return CB200_ERR_UNSUPPORTED;
+  if (a->dependent_launch < 0 || a->dependent_launch > 2) return CB200_ERR_BAD_ARG;
   const int sms = sm_count();
   if (sms <= 0) return CB200_ERR_CUDA;
   int grid_max = sms;
@@ -736,7 +744,7 @@ int plan_gemm(const cb200_gemm_args* a, GemmSetup* s, bool need_maps) {
     const double t_pair = gemm_pair_estimate_us(a, sms, &s->pair_ks);
     double t_single = best;
     if (t_single == 0.0) t_single = static_cast<double>((tiles + grid_max - 1) / grid_max) * p.kblocks * (s->nbw == 4 || a->op == CB200_GEMM_SWIGLU ? 0.56 : 0.33);
-    s->pair = t_pair > 0.0 && t_pair < t_single && !a->addend;  // the pair kernel's epilogue has no addend
+    s->pair = t_pair > 0.0 && t_pair < t_single && !a->addend && !a->dependent_launch;  // the pair kernel has neither an addend nor the dependent-launch waits
   }
   if (s->pair) {
     s->cluster = false;
@@ -762,6 +770,7 @@ int plan_gemm(const cb200_gemm_args* a, GemmSetup* s, bool need_maps) {
   p.y = a->y;
   p.gamma = a->op == CB200_GEMM_RMSNORM ? a->gamma : nullptr;
   p.addend = a->addend;
+  p.pdl = a->dependent_launch;
   uint8_t* ws = static_cast<uint8_t*>(a->workspace);
   p.status = reinterpret_cast<int*>(ws);
   p.partials = reinterpret_cast<float*>(ws + s->partials_off);
@@ -793,25 +802,30 @@ int launch_gemm_variant(const GemmSetup& s, cudaStream_t stream) {
   using Plan = GemmPlan<MODE, NBW>;
   auto kern = gemm_kernel<MODE, T, NBW, CLUSTER>;
   CB200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Plan::kSmemBytes));
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(s.grid, 1, 1);
+  cfg.blockDim = dim3(Plan::kThreads, 1, 1);
+  cfg.dynamicSmemBytes = Plan::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  int n_attr = 0;
   if constexpr (CLUSTER) {
     if (s.p.chunks_per_tile > 8)
       CB200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(s.grid, 1, 1);
-    cfg.blockDim = dim3(Plan::kThreads, 1, 1);
-    cfg.dynamicSmemBytes = Plan::kSmemBytes;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = s.p.chunks_per_tile;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    CB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, s.tm_a, s.tm_b0, s.tm_b1, s.p));
-  } else {
-    kern<<<s.grid, Plan::kThreads, Plan::kSmemBytes, stream>>>(s.tm_a, s.tm_b0, s.tm_b1, s.p);
+    attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+    attr[n_attr].val.clusterDim.x = s.p.chunks_per_tile;
+    attr[n_attr].val.clusterDim.y = 1;
+    attr[n_attr].val.clusterDim.z = 1;
+    ++n_attr;
   }
+  if (s.p.pdl) {
+    attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+    ++n_attr;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = n_attr;
+  CB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, s.tm_a, s.tm_b0, s.tm_b1, s.p));
   CB200_CUDA_TRY(cudaGetLastError());
   return CB200_OK;
 }

@@ -139,6 +139,11 @@ typedef struct {
   float eps;        /* RMSNorm only */
   const void* addend; /* CB200_GEMM_MATMUL only, may be NULL: (m, n) in the storage dtype, Y = X @ W + addend
                          (added in fp32 in the epilogue; the low-rank term of cb200_lora) */
+  int32_t dependent_launch; /* 0: the launch is ordered after the preceding kernel of the stream, as usual.
+                               1: it may start while that kernel still runs and waits for it before reading any
+                                  operand (set-up overlaps). 2: it waits only before reading `addend`; X and W must
+                                  not be outputs of the preceding kernel. Used by cb200_lora to run the big product
+                                  beside the two rank-r products. */
 } cb200_gemm_args;
 
 size_t cb200_gemm_workspace_bytes(const cb200_gemm_args* a);

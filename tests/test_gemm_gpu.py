@@ -120,7 +120,7 @@ def test_scratch_behind_the_counters_never_lands_in_another_shape_s_counters():
 
 
 def test_automatic_plans_for_the_benchmark_shapes():
-    """What the planner's cost model picks when the caller leaves the split to it: one cluster of 8 for
+    """What the planner's cost model picks when the caller leaves the split to it: one cluster of 16 for
     the 128 x 128 x 4096 matmul, clusters of 3 for the 64 x 11008 x 4096 RMSNorm GEMM, whole tiles for a
     large square; an explicit factor is honoured."""
     import ctypes as C
@@ -132,7 +132,7 @@ def test_automatic_plans_for_the_benchmark_shapes():
         a.m, a.n, a.k, a.op, a.dtype, a.split_k = m, n, k, op, 0, split_k
         return _lib.lib().cb200_gemm_effective_split(C.byref(a))
 
-    assert split(128, 128, 4096) == 8
+    assert split(128, 128, 4096) == 16
     assert split(64, 11008, 4096, op=1) == 3
     assert split(8192, 8192, 4096) == 1
     assert split(128, 128, 4096, split_k=4) == 4

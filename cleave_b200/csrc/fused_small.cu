@@ -7,11 +7,11 @@
 //       2*M*N*K. Bound by HBM (and, at the demo's 1 MB, by two launch latencies).
 //
 //   lora            Y = X @ W + (X @ A) @ B                          (demo/lora.py)
-//       Three launches of the tcgen05 GEMM of this library on one stream: T = X @ A (rank R columns),
-//       Z = T @ B, Y = X @ W + Z with Z added in the epilogue of the last product. T and Z live in the
-//       workspace in the storage type (the reference's kernels round intermediates the same way). The
-//       launches are dependent launches: the big product streams W beside the two small ones and only
-//       its epilogue waits for Z.
+//       Two launches of the tcgen05 GEMM of this library on one stream: T = X @ A (rank R columns, kept
+//       in the workspace in the storage type - the reference's kernels round intermediates the same way),
+//       then Y = [X | T] @ [W ; B]: one product whose last K block comes from a second operand pair, so the
+//       low-rank term lands in the same accumulator. The second launch is a dependent launch: it streams W
+//       while T is computed and waits for T only before that last K block.
 
 #include "common.cuh"
 
@@ -84,8 +84,8 @@ int launch_rowsum(const cb200_matmul_rowsum_args* a, cudaStream_t st) {
 
 // ---------------------------------------------------------------------------------------- LoRA
 struct LoraLayout {
-  cb200_gemm_args t, z, y;  // the three products
-  size_t gemm_ws, t_off, z_off, total;
+  cb200_gemm_args t, y;  // the two launches
+  size_t gemm_ws, t_off, total;
 };
 
 int plan_lora(const cb200_lora_args* a, LoraLayout* L) {
@@ -97,21 +97,18 @@ int plan_lora(const cb200_lora_args* a, LoraLayout* L) {
   g.op = CB200_GEMM_MATMUL;
   g.dtype = a->dtype;
   L->t = g; L->t.m = a->m; L->t.n = a->r; L->t.k = a->k;
-  L->z = g; L->z.m = a->m; L->z.n = a->n; L->z.k = a->r;
   L->y = g; L->y.m = a->m; L->y.n = a->n; L->y.k = a->k;
-  L->y.addend = reinterpret_cast<const void*>(16);  // planned as the launch will be: with an addend
-  L->y.dependent_launch = 2;
-  L->z.dependent_launch = 1;
+  L->y.k2 = a->r;              // planned as the launch will be: with the second operand pair
+  L->y.dependent_launch = 3;
   size_t ws = 0;
-  for (const cb200_gemm_args* p : {&L->t, &L->z, &L->y}) {
+  for (const cb200_gemm_args* p : {&L->t, &L->y}) {
     const size_t need = cb200_gemm_workspace_bytes(p);
     if (need == 0) return CB200_ERR_UNSUPPORTED;
     if (need > ws) ws = need;
   }
   L->gemm_ws = align_up(ws, 256);
-  L->t_off = 3 * L->gemm_ws;  // one GEMM scratch per product: they overlap on the GPU
-  L->z_off = align_up(L->t_off + static_cast<size_t>(a->m) * a->r * 2, 256);
-  L->total = align_up(L->z_off + static_cast<size_t>(a->m) * a->n * 2, 256);
+  L->t_off = 2 * L->gemm_ws;  // one GEMM scratch per launch: they overlap on the GPU
+  L->total = align_up(L->t_off + static_cast<size_t>(a->m) * a->r * 2, 256);
   return CB200_OK;
 }
 
@@ -149,20 +146,16 @@ extern "C" int cb200_lora(const cb200_lora_args* a, void* stream) {
   if (reinterpret_cast<uintptr_t>(a->workspace) & 255) return CB200_ERR_ALIGNMENT;
   uint8_t* ws = static_cast<uint8_t*>(a->workspace);
   void* t = ws + L.t_off;
-  void* z = ws + L.z_off;
-  // Z waits for T before it reads anything; Y runs its whole main loop beside T and Z and waits for Z only
-  // in its epilogue, where Z is added (dependent launches). Each product has its own GEMM scratch.
-  int slot = 0;
-  for (cb200_gemm_args* g : {&L.t, &L.z, &L.y}) {
-    g->workspace = ws + static_cast<size_t>(slot++) * L.gemm_ws;
-    g->workspace_bytes = L.gemm_ws;
-  }
-  L.z.dependent_launch = 1;
-  L.y.dependent_launch = 2;
+  // T = X @ A, then Y = X @ W + T @ B as ONE product over the concatenated K of [X | T] and [W ; B]. The
+  // second launch is a dependent launch: it streams W while T is still being computed and waits for T only
+  // before it loads the rank-r K block. Each launch has its own GEMM scratch.
+  L.t.workspace = ws;
+  L.y.workspace = ws + L.gemm_ws;
+  L.t.workspace_bytes = L.y.workspace_bytes = L.gemm_ws;
   L.t.x = a->x; L.t.w = a->a; L.t.y = t;
-  L.z.x = t;    L.z.w = a->b; L.z.y = z;
-  L.y.x = a->x; L.y.w = a->w; L.y.y = a->y; L.y.addend = z;
-  for (const cb200_gemm_args* g : {&L.t, &L.z, &L.y}) {
+  L.y.x = a->x; L.y.w = a->w; L.y.y = a->y;
+  L.y.x2 = t;   L.y.w2 = a->b;
+  for (const cb200_gemm_args* g : {&L.t, &L.y}) {
     const int rc2 = cb200_gemm(g, stream);
     if (rc2 != CB200_OK) return rc2;
   }

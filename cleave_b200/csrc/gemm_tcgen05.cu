@@ -53,6 +53,7 @@ struct GemmParams {
   int a_rows;  // rows of the A box: 128, or M rounded up to 8 when M is smaller
   const void* addend;  // MODE 0, may be null: (M, N) in the storage type, added in the epilogue
   int pdl;             // cb200_gemm_args.dependent_launch
+  int kblocks_main;    // K blocks of X / W; blocks beyond come from the second operand pair (x2, w2)
 };
 
 template <int MODE, int NBW>
@@ -78,7 +79,8 @@ __device__ __forceinline__ int cta_of_chunk(long long x, long long C, long long 
 template <int MODE, typename T, int NBW, bool CLUSTER>
 __global__ void __launch_bounds__(GemmPlan<MODE, NBW>::kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b0,
-            const __grid_constant__ CUtensorMap tm_b1, const GemmParams p) {
+            const __grid_constant__ CUtensorMap tm_b1, const __grid_constant__ CUtensorMap tm_a2,
+            const GemmParams p) {
   using Plan = GemmPlan<MODE, NBW>;
   constexpr int kStages = Plan::kStages;
   constexpr int kUmmaN = Plan::kUmmaN;
@@ -129,7 +131,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_holder);
   // Dependent launch (the grid may have started while the preceding kernel of the stream still runs):
   // mode 1 waits for that kernel here, before any operand is read; mode 2 lets the main loop run and waits
-  // in the epilogue warps only, before the addend - the one operand the preceding kernel wrote - is read.
+  // in the epilogue warps only, before the addend - the one operand the preceding kernel wrote - is read;
+  // mode 3 waits in the producer warp before the first load of the second operand pair.
   pdl_launch_dependents();  // before the wait: a dependent of this grid waits for this grid's completion itself
   if (p.pdl == 1) pdl_wait();
 
@@ -144,6 +147,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
   if (warp == 0) {
     // ================================================================ TMA producer
     int stage = 0, phase = 0;
+    bool waited2 = false;
     for (long long x = x0; x < x1;) {
       const int tile = static_cast<int>(x / S), s0 = static_cast<int>(x - static_cast<long long>(tile) * S);
       const int nseg = static_cast<int>(min(static_cast<long long>(S - s0), x1 - x));
@@ -151,16 +155,29 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
       const int kb0 = s0 * p.chunk_kblocks, kb1 = min((s0 + nseg) * p.chunk_kblocks, p.kblocks);
       for (int kb = kb0; kb < kb1; ++kb) {
         mbar_wait(&empty_bar[stage], phase ^ 1, p.status, kFaultEmptyBarrier);
+        if (MODE == 0 && p.pdl == 3 && kb >= p.kblocks_main && !waited2) {
+          pdl_wait();  // the second operand pair is the preceding kernel's output; everything before streamed beside it
+          waited2 = true;
+        }
         if (lane == 0) {
           uint8_t* a_dst = stages + stage * Plan::kStageBytes;
           uint8_t* b_dst = a_dst + kABytes;
           // rows of the A tile beyond a_rows are never fetched; the MMA reads whatever is there,
           // and the rows of D they produce are never stored
           mbar_arrive_expect_tx(&full_bar[stage], Plan::kStageBytes - (kBM - p.a_rows) * kBK * 2);
-          tma_load_2d(a_dst, &tm_a, &full_bar[stage], kb * kBK, tm * kBM);
+          if (MODE == 0 && kb >= p.kblocks_main) {
+            // K blocks past the end of X / W: the second operand pair, Y = X W + X2 W2 (tm_b1 is W2 here)
+            const int k2 = (kb - p.kblocks_main) * kBK;
+            tma_load_2d(a_dst, &tm_a2, &full_bar[stage], k2, tm * kBM);
 #pragma unroll
-          for (int j = 0; j < NBW; ++j)
-            tma_load_2d(b_dst + j * kBChunkBytes, &tm_b0, &full_bar[stage], tn * Plan::kTileN + j * kChunkN, kb * kBK);
+            for (int j = 0; j < NBW; ++j)
+              tma_load_2d(b_dst + j * kBChunkBytes, &tm_b1, &full_bar[stage], tn * Plan::kTileN + j * kChunkN, k2);
+          } else {
+            tma_load_2d(a_dst, &tm_a, &full_bar[stage], kb * kBK, tm * kBM);
+#pragma unroll
+            for (int j = 0; j < NBW; ++j)
+              tma_load_2d(b_dst + j * kBChunkBytes, &tm_b0, &full_bar[stage], tn * Plan::kTileN + j * kChunkN, kb * kBK);
+          }
           if constexpr (MODE == 2) {
 #pragma unroll
             for (int j = 0; j < NBW; ++j)
@@ -643,7 +660,7 @@ struct GemmSetup {
   bool pair;     // whole 256 x 256 tiles on CTA pairs (gemm_pair.cu)
   int pair_ks;   // pairs per cluster: the K split of the pair kernel
   size_t ws_needed, partials_off, counters_off, prepass_off;
-  CUtensorMap tm_a, tm_b0, tm_b1;
+  CUtensorMap tm_a, tm_b0, tm_b1, tm_a2;
 };
 
 // How many clusters of `size` CTAs of the cluster GEMM variant can be resident at once (they must fit
@@ -657,7 +674,10 @@ int plan_gemm(const cb200_gemm_args* a, GemmSetup* s, bool need_maps) {
   if (a->dtype != CB200_F16 && a->dtype != CB200_BF16) return CB200_ERR_UNSUPPORTED;
   if (a->k % 8 || a->n % 8) return CB200_ERR_UNSUPPORTED;  // TMA strides are multiples of 16 bytes
   if (a->addend && a->op != CB200_GEMM_MATMUL) return CB200_ERR_UNSUPPORTED;
-  if (a->dependent_launch < 0 || a->dependent_launch > 2) return CB200_ERR_BAD_ARG;
+  if (a->dependent_launch < 0 || a->dependent_launch > 3) return CB200_ERR_BAD_ARG;
+  const bool ext = a->k2 > 0;
+  if (ext && (a->op != CB200_GEMM_MATMUL || a->k2 % 8)) return CB200_ERR_UNSUPPORTED;
+  if (a->k2 < 0 || (a->dependent_launch == 3 && !ext)) return CB200_ERR_BAD_ARG;
   const int sms = sm_count();
   if (sms <= 0) return CB200_ERR_CUDA;
   int grid_max = sms;
@@ -673,7 +693,8 @@ int plan_gemm(const cb200_gemm_args* a, GemmSetup* s, bool need_maps) {
   // pairs two 128-column accumulators).
   s->nbw = 2;
   if (a->op != CB200_GEMM_SWIGLU && static_cast<long long>(p.tiles_m) * ceil_div(a->n, 256) >= 2LL * grid_max) s->nbw = 4;
-  p.kblocks = ceil_div(a->k, kBK);
+  p.kblocks_main = ceil_div(a->k, kBK);
+  p.kblocks = p.kblocks_main + (ext ? ceil_div(a->k2, kBK) : 0);
   // Automatic plan: whole tiles, or the K parts of a tile as one thread-block cluster (reduced through
   // distributed shared memory), whichever a small cost model says finishes first. Per CTA and K block
   // the MMAs take about 0.56 us for a 256-column tile and 0.33 us for a 128-column one (sustained rates
@@ -749,7 +770,7 @@ int plan_gemm(const cb200_gemm_args* a, GemmSetup* s, bool need_maps) {
     const double t_pair = gemm_pair_estimate_us(a, sms, &s->pair_ks);
     double t_single = best;
     if (t_single == 0.0) t_single = static_cast<double>((tiles + grid_max - 1) / grid_max) * p.kblocks * (s->nbw == 4 || a->op == CB200_GEMM_SWIGLU ? 0.56 : 0.33);
-    s->pair = t_pair > 0.0 && t_pair < t_single && !a->addend && !a->dependent_launch;  // the pair kernel has neither an addend nor the dependent-launch waits
+    s->pair = t_pair > 0.0 && t_pair < t_single && !a->addend && !a->dependent_launch && !ext;  // the pair kernel has no addend, no dependent-launch waits, no second operand pair
   }
   if (s->pair) {
     s->cluster = false;
@@ -766,6 +787,8 @@ int plan_gemm(const cb200_gemm_args* a, GemmSetup* s, bool need_maps) {
 
   if (!a->x || !a->w || !a->y) return CB200_ERR_BAD_ARG;
   if (a->op == CB200_GEMM_SWIGLU && !a->w1) return CB200_ERR_BAD_ARG;
+  if (ext && (!a->x2 || !a->w2)) return CB200_ERR_BAD_ARG;
+  if (ext && ((reinterpret_cast<uintptr_t>(a->x2) | reinterpret_cast<uintptr_t>(a->w2)) & 15)) return CB200_ERR_ALIGNMENT;
   uintptr_t bits = reinterpret_cast<uintptr_t>(a->x) | reinterpret_cast<uintptr_t>(a->w) |
                    reinterpret_cast<uintptr_t>(a->y) | reinterpret_cast<uintptr_t>(a->w1) |
                    reinterpret_cast<uintptr_t>(a->gamma) | reinterpret_cast<uintptr_t>(a->addend);
@@ -796,7 +819,20 @@ int plan_gemm(const cb200_gemm_args* a, GemmSetup* s, bool need_maps) {
     if (!encode_tensor_map(&s->tm_b0, dt, 2, const_cast<void*>(a->w), dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
       return CB200_ERR_CUDA;
     const void* w1 = a->op == CB200_GEMM_SWIGLU ? a->w1 : a->w;
-    if (!encode_tensor_map(&s->tm_b1, dt, 2, const_cast<void*>(w1), dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
+    if (ext) {  // tm_b1 carries W2 (k2, n)
+      uint64_t dims2[2] = {static_cast<uint64_t>(a->n), static_cast<uint64_t>(a->k2)};
+      if (!encode_tensor_map(&s->tm_b1, dt, 2, const_cast<void*>(a->w2), dims2, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
+        return CB200_ERR_CUDA;
+    } else if (!encode_tensor_map(&s->tm_b1, dt, 2, const_cast<void*>(w1), dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) {
+      return CB200_ERR_CUDA;
+    }
+  }
+  s->tm_a2 = s->tm_a;
+  if (ext) {
+    uint64_t dims[2] = {static_cast<uint64_t>(a->k2), static_cast<uint64_t>(a->m)};
+    uint64_t strides[1] = {static_cast<uint64_t>(a->k2) * 2};
+    uint32_t box[2] = {kBK, static_cast<uint32_t>(p.a_rows)};
+    if (!encode_tensor_map(&s->tm_a2, dt, 2, const_cast<void*>(a->x2), dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
       return CB200_ERR_CUDA;
   }
   return CB200_OK;
@@ -830,7 +866,7 @@ int launch_gemm_variant(const GemmSetup& s, cudaStream_t stream) {
   }
   cfg.attrs = attr;
   cfg.numAttrs = n_attr;
-  CB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, s.tm_a, s.tm_b0, s.tm_b1, s.p));
+  CB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, s.tm_a, s.tm_b0, s.tm_b1, s.tm_a2, s.p));
   CB200_CUDA_TRY(cudaGetLastError());
   return CB200_OK;
 }

@@ -230,7 +230,8 @@ def matmul_rowsum(x, w, *, out=None):
 
 def lora(x, w, a, b, *, out=None):
     """``Y = X @ W + (X @ A) @ B`` (reference operator: demo/lora.py:11-18): x (M, K), w (K, N), a (K, R),
-    b (R, N). Three tcgen05 GEMM launches; the low-rank term is added in the epilogue of the last."""
+    b (R, N). Two tcgen05 GEMM launches: ``T = X @ A``, then ``[X | T] @ [W ; B]`` as one product that streams
+    W while T is computed."""
     x, w, a, b = _cuda(x, "x"), _cuda(w, "w"), _cuda(a, "a"), _cuda(b, "b")
     m, k = x.shape
     n, r = w.shape[1], a.shape[1]
@@ -317,7 +318,7 @@ def gqa_paged_decode_static_scratch(q, k_cache, v_cache, kv_indptr, kv_indices, 
     return out, lse
 
 
-def _gemm(op, x, w, w1=None, gamma=None, eps=0.0, split_k=0, out=None, max_ctas=0):
+def _gemm(op, x, w, w1=None, gamma=None, eps=0.0, split_k=0, out=None, max_ctas=0, addend=None, x2=None, w2=None):
     x, w = _cuda(x, "x"), _cuda(w, "w")
     m, k = x.shape
     k2, n = w.shape
@@ -335,6 +336,16 @@ def _gemm(op, x, w, w1=None, gamma=None, eps=0.0, split_k=0, out=None, max_ctas=
     a.gamma = None if gamma is None else gamma.data_ptr()
     a.m, a.n, a.k, a.op, a.dtype = m, n, k, op, _dtype_code(x)
     a.split_k, a.max_ctas, a.eps = int(split_k), int(max_ctas), float(eps)
+    if addend is not None:
+        if tuple(_cuda(addend, "addend").shape) != (m, n) or addend.dtype != x.dtype:
+            raise ValueError("addend must be (M, N) of x's dtype")
+        a.addend = addend.data_ptr()
+    if (x2 is None) != (w2 is None):
+        raise ValueError("x2 and w2 go together")
+    if x2 is not None:
+        if _cuda(x2, "x2").shape[0] != m or tuple(_cuda(w2, "w2").shape) != (x2.shape[1], n) or x2.dtype != x.dtype or w2.dtype != x.dtype:
+            raise ValueError("x2 must be (M, K2) and w2 (K2, N), of x's dtype")
+        a.x2, a.w2, a.k2 = x2.data_ptr(), w2.data_ptr(), x2.shape[1]
     need = _lib.lib().cb200_gemm_workspace_bytes(C.byref(a))
     if need == 0:
         _lib.check(_lib.lib().cb200_gemm(C.byref(a), _stream()))  # raises the real status
@@ -344,9 +355,11 @@ def _gemm(op, x, w, w1=None, gamma=None, eps=0.0, split_k=0, out=None, max_ctas=
     return out
 
 
-def matmul(x, w, *, split_k=0, out=None, max_ctas=0):
-    """``Y = X @ W`` (reference operator: demo/matmul.py:11-13); ``split_k`` is the plan's K split."""
-    return _gemm(_lib.GEMM_MATMUL, x, w, split_k=split_k, out=out, max_ctas=max_ctas)
+def matmul(x, w, *, split_k=0, out=None, max_ctas=0, addend=None, x2=None, w2=None):
+    """``Y = X @ W`` (reference operator: demo/matmul.py:11-13); ``split_k`` is the plan's K split.
+    ``addend`` (M, N) is added in the epilogue; ``x2`` (M, K2) and ``w2`` (K2, N) extend the contraction:
+    ``Y = X @ W + X2 @ W2`` in one accumulator (the low-rank term of LoRA)."""
+    return _gemm(_lib.GEMM_MATMUL, x, w, split_k=split_k, out=out, max_ctas=max_ctas, addend=addend, x2=x2, w2=w2)
 
 
 def rmsnorm_matmul(x, w, *, eps=0.0, gamma=None, split_k=0, out=None, max_ctas=0):

@@ -142,8 +142,14 @@ typedef struct {
   int32_t dependent_launch; /* 0: the launch is ordered after the preceding kernel of the stream, as usual.
                                1: it may start while that kernel still runs and waits for it before reading any
                                   operand (set-up overlaps). 2: it waits only before reading `addend`; X and W must
-                                  not be outputs of the preceding kernel. Used by cb200_lora to run the big product
-                                  beside the two rank-r products. */
+                                  not be outputs of the preceding kernel. 3: it waits only before the first read of
+                                  the second operand pair (x2, w2 below); X and W must not be outputs of the
+                                  preceding kernel. cb200_lora streams W beside the rank-r product this way. */
+  /* Optional second operand pair, CB200_GEMM_MATMUL only (k2 = 0: none): Y = X @ W + X2 @ W2 [+ addend] in one
+   * accumulator - the K blocks of X2 (m, k2) / W2 (k2, n) follow those of X / W. k2 a multiple of 8. */
+  const void* x2;
+  const void* w2;
+  int32_t k2;
 } cb200_gemm_args;
 
 size_t cb200_gemm_workspace_bytes(const cb200_gemm_args* a);
@@ -329,8 +335,9 @@ int cb200_matmul_rowsum(const cb200_matmul_rowsum_args* a, void* stream);
 /* ------------------------------------------------------------------------------------------
  * LoRA: Y = X @ W + (X @ A) @ B; X (m, k), W (k, n), A (k, r), B (r, n), Y (m, n), all row-major in the
  * storage dtype; k, n and r multiples of 8. Replaces the fused kernel of demo/lora.py
- * (x @ w + (x @ a) @ b). Three launches of cb200_gemm on `stream`: T = X @ A, Z = T @ B, then
- * Y = X @ W with Z added in the epilogue; T and Z are kept in the workspace in the storage dtype.
+ * (x @ w + (x @ a) @ b). Two launches of cb200_gemm on `stream`: T = X @ A (kept in the workspace in the
+ * storage dtype), then Y = X @ W + T @ B as one product over the concatenated K (x2 / w2 of cb200_gemm_args),
+ * launched so that it streams W while T is computed.
  * ---------------------------------------------------------------------------------------- */
 typedef struct {
   const void* x; /* (m, k) */

@@ -148,14 +148,33 @@ def test_lora_vs_oracle(m, n, k, r, dt):
     assert_close(host(got), orc.lora(inp["x"], inp["w"], inp["a"], inp["b"], dt))
 
 
-def test_lora_with_zero_adapter_equals_matmul_bitwise():
-    """B = 0 makes the low-rank term exactly zero: the result must be the plain product's bits (the addend
-    path of the GEMM epilogue adds 0.0 in fp32 before the one rounding)."""
+def test_lora_with_zero_adapter_equals_matmul():
+    """B = 0 makes the low-rank K block contribute exact zeros to the accumulator: the result is the plain
+    product up to the order of the fp32 sum (the K split of a product with one more K block may differ)."""
     inp = cases.lora_inputs(5, 48, 520, 1024, 16, "f16")
     ops = _ops()
     x, w, a = dev(inp["x"], "f16"), dev(inp["w"], "f16"), dev(inp["a"], "f16")
     got = ops.lora(x, w, a, torch.zeros(16, 520, dtype=torch.float16, device="cuda"))
-    assert torch.equal(got, ops.matmul(x, w))
+    assert_close(host(got), host(ops.matmul(x, w)), rtol=2.0 ** -9, atol=2.0 ** -9)
+
+
+@pytest.mark.parametrize("dt", ["f16", "bf16"])
+@pytest.mark.parametrize("m,n,k,k2,split_k", [(16, 4096, 4096, 16, 0), (128, 256, 512, 64, 0), (200, 264, 320, 8, 0),
+                                              (64, 512, 1024, 72, 4), (600, 2048, 1024, 136, 0), (1024, 2048, 1024, 16, 0),
+                                              (40, 72, 64, 200, 2)])
+def test_matmul_with_a_second_operand_pair_and_an_addend(m, n, k, k2, split_k, dt):
+    """``Y = X @ W + X2 @ W2 + C`` in one launch: the K blocks of the second pair follow those of the first
+    in the same accumulator, C is added in the epilogue. Cluster plans, the stream-K walk (explicit split)
+    and sizes the CTA-pair kernel would otherwise take."""
+    rng = np.random.default_rng(m + n + k2)
+    r = lambda shape, sc: orc.round_to(rng.standard_normal(shape, dtype=np.float32) * np.float32(sc), dt)  # noqa: E731
+    x, w = r((m, k), 1.0), r((k, n), k ** -0.5)
+    x2, w2, c = r((m, k2), 1.0), r((k2, n), k2 ** -0.5), r((m, n), 1.0)
+    got = _ops().matmul(dev(x, dt), dev(w, dt), split_k=split_k, addend=dev(c, dt), x2=dev(x2, dt), w2=dev(w2, dt))
+    _check("gemm")
+    assert_close(host(got), orc.round_to(x @ w + x2 @ w2 + c, dt))
+    only_pair = _ops().matmul(dev(x, dt), dev(w, dt), split_k=split_k, x2=dev(x2, dt), w2=dev(w2, dt))
+    assert_close(host(only_pair), orc.round_to(x @ w + x2 @ w2, dt))
 
 
 def test_gemm_addend_rejected_outside_plain_matmul():
@@ -166,6 +185,11 @@ def test_gemm_addend_rejected_outside_plain_matmul():
     a = _lib.GemmArgs()
     a.m, a.n, a.k, a.op, a.dtype, a.addend = 64, 64, 64, _lib.GEMM_SWIGLU, _lib.F16, 16
     assert _lib.lib().cb200_gemm_workspace_bytes(C.byref(a)) == 0
+    b = _lib.GemmArgs()
+    b.m, b.n, b.k, b.op, b.dtype, b.k2 = 64, 64, 64, _lib.GEMM_RMSNORM, _lib.F16, 16
+    assert _lib.lib().cb200_gemm_workspace_bytes(C.byref(b)) == 0  # the second operand pair is plain-matmul only
+    b.op, b.k2, b.dependent_launch = _lib.GEMM_MATMUL, 0, 3
+    assert _lib.lib().cb200_gemm_workspace_bytes(C.byref(b)) == 0  # mode 3 waits on a second pair that is not there
 
 
 def test_demo_sizes_against_oracle_slices():

@@ -7,7 +7,7 @@
 // the operator becomes HBM-bound. Three kernels, the products on warp-level MMAs (m16n8k16; at 30 FLOP per byte the
 // tensor pipe is not the limit):
 //   ktv_kernel   a CTA owns (kv head, chunk of tokens): T_part = K_chunk^T V_chunk in fp32. K and V tiles of
-//                64 tokens are staged by cp.async (four stages, padded rows); both operands are read
+//                64 tokens are staged by cp.async (three stages, padded rows); both operands are read
 //                with transposing ldmatrix (the token axis is the contraction axis of both). Partials go
 //                to the workspace.
 //   tsum_kernel  sums the partials of a head in chunk order (bit-stable) and stores T in the storage type.
@@ -32,7 +32,7 @@ struct Cfg {
   static constexpr int kThreads = kWarps * 32;
   static constexpr int kRowBytes = D * 2 + 16;   // padded: 8 consecutive rows fall in distinct bank groups
   static constexpr int kMatBytes = kTok * kRowBytes;
-  static constexpr int kStages = 4;
+  static constexpr int kStages = 3;
   static constexpr int kKtvSmem = kStages * 2 * kMatBytes;  // stages of (K, V)
   static constexpr int kQtRows = 128;
   static constexpr int kQtSmem = (kQtRows + D) * kRowBytes;  // Q tile + T

@@ -68,6 +68,7 @@ __global__ void __launch_bounds__(Cfg<D>::kThreads) ktv_kernel(const Params p) {
   const T* kbase = reinterpret_cast<const T*>(p.k) + static_cast<size_t>(hk) * p.skv * D;
   const T* vbase = reinterpret_cast<const T*>(p.v) + static_cast<size_t>(hk) * p.skv * D;
   const uint32_t smem_base = smem_u32(smem);
+  pdl_launch_dependents();  // tsum_kernel's grid may be scheduled as this grid's CTAs retire
 
   constexpr int kChunksPerRow = D / 8;                    // 16-byte pieces per row
   constexpr int kPieces = kTok * kChunksPerRow;           // per matrix
@@ -149,6 +150,8 @@ template <typename T>
 __global__ void __launch_bounds__(256) tsum_kernel(const Params p, int dd) {
   const int per_head = dd / 4;
   const int idx = blockIdx.x * 256 + threadIdx.x;
+  pdl_launch_dependents();
+  pdl_wait();  // the partials are the preceding kernel's output
   if (idx >= p.hkv * per_head) return;
   const int hk = idx / per_head, i = (idx - hk * per_head) * 4;
   float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -182,14 +185,16 @@ __global__ void __launch_bounds__(128) qt_kernel(const Params p) {
   const T* qbase = reinterpret_cast<const T*>(p.q) + static_cast<size_t>(h) * p.sq * D;
   const T* tbase = reinterpret_cast<const T*>(p.t16) + static_cast<size_t>(hk) * D * D;
   constexpr int kChunksPerRow = D / 8;
-  for (int i = tid; i < (C::kQtRows + D) * kChunksPerRow; i += 128) {
+  // Q does not depend on the kernels before this one: its copies are in flight while they finish
+  for (int i = tid; i < C::kQtRows * kChunksPerRow; i += 128) {
     const int r = i / kChunksPerRow, c = i - r * kChunksPerRow;
-    if (r < C::kQtRows) {
-      const bool ok = q0 + r < p.sq;
-      cp_async16(qs + r * C::kRowBytes + c * 16, qbase + static_cast<size_t>(ok ? q0 + r : 0) * D + c * 8, ok);
-    } else {
-      cp_async16(ts + (r - C::kQtRows) * C::kRowBytes + c * 16, tbase + static_cast<size_t>(r - C::kQtRows) * D + c * 8, true);
-    }
+    const bool ok = q0 + r < p.sq;
+    cp_async16(qs + r * C::kRowBytes + c * 16, qbase + static_cast<size_t>(ok ? q0 + r : 0) * D + c * 8, ok);
+  }
+  pdl_wait();  // T is the preceding kernel's output
+  for (int i = tid; i < D * kChunksPerRow; i += 128) {
+    const int r = i / kChunksPerRow, c = i - r * kChunksPerRow;
+    cp_async16(ts + r * C::kRowBytes + c * 16, tbase + static_cast<size_t>(r) * D + c * 8, true);
   }
   cp_async_commit();
   cp_async_wait<0>();
@@ -302,11 +307,24 @@ int launch_chain(const cb200_matmul_matmul_args* a, const ChainPlan& pl, cudaStr
   CB200_CUDA_TRY(cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kQtSmem));
   k1<<<dim3(pl.chunks, a->num_kv_heads), C::kThreads, C::kKtvSmem, st>>>(p);
   CB200_CUDA_TRY(cudaGetLastError());
+  // the two kernels that follow are dependent launches: each is scheduled while its predecessor drains and
+  // waits (griddepcontrol.wait) before it reads what the predecessor wrote
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
   const int dd = D * D;
-  chain::tsum_kernel<T><<<ceil_div(a->num_kv_heads * (dd / 4), 256), 256, 0, st>>>(p, dd);
-  CB200_CUDA_TRY(cudaGetLastError());
-  k2<<<dim3(ceil_div(a->q_len, C::kQtRows), a->num_qo_heads), 128, C::kQtSmem, st>>>(p);
-  CB200_CUDA_TRY(cudaGetLastError());
+  cudaLaunchConfig_t cfg = {};
+  cfg.stream = st;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cfg.gridDim = dim3(ceil_div(a->num_kv_heads * (dd / 4), 256), 1, 1);
+  cfg.blockDim = dim3(256, 1, 1);
+  cfg.dynamicSmemBytes = 0;
+  CB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, chain::tsum_kernel<T>, p, dd));
+  cfg.gridDim = dim3(ceil_div(a->q_len, C::kQtRows), a->num_qo_heads, 1);
+  cfg.blockDim = dim3(128, 1, 1);
+  cfg.dynamicSmemBytes = C::kQtSmem;
+  CB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, k2, p));
   return CB200_OK;
 }
 

@@ -22,6 +22,7 @@ template <typename T>
 __global__ void __launch_bounds__(128) w_rowsum_kernel(const T* __restrict__ w, float* __restrict__ s, int n) {
   __shared__ float part[4];
   const int k = blockIdx.x, tid = threadIdx.x;
+  pdl_launch_dependents();
   const T* row = w + static_cast<size_t>(k) * n;
   float acc = 0.f;
   for (int c = tid * 8; c < n; c += 128 * 8) {
@@ -43,11 +44,18 @@ __global__ void __launch_bounds__(256) x_dot_kernel(const T* __restrict__ x, con
                                                     T* __restrict__ y, int m, int k) {
   const int lane = threadIdx.x & 31;
   const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (r >= m) return;
+  if (r >= m) {
+    pdl_wait();
+    return;
+  }
   const T* row = x + static_cast<size_t>(r) * k;
   float acc = 0.f;
+  // dependent launch: this row's first piece of X is fetched while w_rowsum_kernel finishes; s is its output
+  uint4 first = make_uint4(0u, 0u, 0u, 0u);
+  if (lane * 8 < k) first = *reinterpret_cast<const uint4*>(row + lane * 8);
+  pdl_wait();
   for (int c = lane * 8; c < k; c += 32 * 8) {
-    const uint4 u = *reinterpret_cast<const uint4*>(row + c);
+    const uint4 u = c == lane * 8 ? first : *reinterpret_cast<const uint4*>(row + c);
     const T* e = reinterpret_cast<const T*>(&u);
     const float4 s0 = *reinterpret_cast<const float4*>(s + c), s1 = *reinterpret_cast<const float4*>(s + c + 4);
     acc = fmaf(static_cast<float>(e[0]), s0.x, acc);
@@ -77,8 +85,17 @@ int launch_rowsum(const cb200_matmul_rowsum_args* a, cudaStream_t st) {
   float* s = reinterpret_cast<float*>(static_cast<uint8_t*>(a->workspace) + kWsHeaderBytes);
   w_rowsum_kernel<T><<<a->k, 128, 0, st>>>(reinterpret_cast<const T*>(a->w), s, a->n);
   CB200_CUDA_TRY(cudaGetLastError());
-  x_dot_kernel<T><<<ceil_div(a->m, 8), 256, 0, st>>>(reinterpret_cast<const T*>(a->x), s, reinterpret_cast<T*>(a->y), a->m, a->k);
-  CB200_CUDA_TRY(cudaGetLastError());
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(ceil_div(a->m, 8), 1, 1);
+  cfg.blockDim = dim3(256, 1, 1);
+  cfg.stream = st;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  CB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, x_dot_kernel<T>, reinterpret_cast<const T*>(a->x), const_cast<const float*>(s),
+                                    reinterpret_cast<T*>(a->y), a->m, a->k));
   return CB200_OK;
 }
 

@@ -770,7 +770,7 @@ int plan_gemm(const cb200_gemm_args* a, GemmSetup* s, bool need_maps) {
     const double t_pair = gemm_pair_estimate_us(a, sms, &s->pair_ks);
     double t_single = best;
     if (t_single == 0.0) t_single = static_cast<double>((tiles + grid_max - 1) / grid_max) * p.kblocks * (s->nbw == 4 || a->op == CB200_GEMM_SWIGLU ? 0.56 : 0.33);
-    s->pair = t_pair > 0.0 && t_pair < t_single && !a->addend && !a->dependent_launch && !ext;  // the pair kernel has no addend, no dependent-launch waits, no second operand pair
+    s->pair = t_pair > 0.0 && t_pair < t_single && !a->addend && a->dependent_launch <= 1 && !ext;  // the pair kernel has no addend and no second operand pair; mode 1 is only a permission, the pair launch stays an ordinary one
   }
   if (s->pair) {
     s->cluster = false;

@@ -130,6 +130,8 @@ def fused_attn_case(kind, hq, hkv, s, d, dtype=torch.float16, impl="auto"):
     byts = (2 * q.numel() + 2 * k.numel()) * 2
     if kind == "matmul_matmul":
         fn = _rotating(lambda t: (lambda: ops.matmul_matmul(t[0], t[1], t[2], out=t[3], impl=impl)), [q, k, v, out])
+        if impl != "scores_first":  # the chain order Q (K^T V) does 2 (HKV SKV + HQ SQ) D^2 FLOPs, not 4 HQ SQ SKV D
+            return fn, 2 * (hkv * s + hq * s) * d * d, byts
     else:
         fn = _rotating(lambda t: (lambda: ops.qknorm_attention(t[0], t[1], t[2], eps=1e-6, out=t[3])), [q, k, v, out])
     return fn, 4 * hq * s * s * d, byts

@@ -118,6 +118,10 @@ mla_scores_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_consta
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_holder);
   pdl_launch_dependents();  // the values kernel may set up and prefetch V while this grid drains
+  // This grid is itself a dependent launch: it was scheduled while the preceding kernel of the stream (in a
+  // decode loop, the values kernel of the step before, which still reads the P buffer) drains. Everything up
+  // to here was set-up; nothing in global memory is read or written before the wait.
+  pdl_wait();
 
   if (warp == 0) {
     // ================================================================ TMA producer
@@ -309,6 +313,7 @@ mla_values_kernel(const __grid_constant__ CUtensorMap tm_ckv, const Params p) {
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_holder);
+  pdl_launch_dependents();  // the next kernel of the stream may be scheduled as this grid's CTAs retire
 
   if (warp == 0) {
     // ================================================================ TMA producer
@@ -646,7 +651,20 @@ int launch_mla_tc_kernels(int dv, long long grid1, long long grid2, const CUtens
   // set on every launch: the attribute is per function and per device, and the call is cheap
   CB200_CUDA_TRY(cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, mlatc::kScoreSmem));
   CB200_CUDA_TRY(cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, mlatc::kValueSmem));
-  k1<<<static_cast<unsigned>(grid1), mlatc::kScoreThreads, mlatc::kScoreSmem, stream>>>(tm_qn, tm_qp, tm_ckv_k, tm_kpe, p);
+  {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(grid1), 1, 1);
+    cfg.blockDim = dim3(mlatc::kScoreThreads, 1, 1);
+    cfg.dynamicSmemBytes = mlatc::kScoreSmem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    // scheduled while the preceding kernel of the stream drains; waits before its first global access
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    CB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, k1, tm_qn, tm_qp, tm_ckv_k, tm_kpe, p));
+  }
   CB200_CUDA_TRY(cudaGetLastError());
   {
     cudaLaunchConfig_t cfg = {};

@@ -154,6 +154,11 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_holder);
+  // The static launch is a dependent launch: the grid may have been scheduled while the preceding kernel of
+  // the stream drains. Up to here only shared and tensor memory were set up (the index reads of the ragged
+  // modes above belong to launches without the attribute); global memory is touched after the wait.
+  pdl_launch_dependents();
+  pdl_wait();
 
   if (warp == 0) {
     // ================================================================ TMA producer: Q, then K tiles
@@ -571,7 +576,18 @@ int launch_prefill(const cb200_attn_prefill_args* a, cudaStream_t stream) {
   auto kern = attn_prefill_kernel<T, D, 0>;
   CB200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<D>::kSmemBytes));
   const unsigned grid = static_cast<unsigned>(p.hq) * p.q_tiles;
-  kern<<<grid, kThreads, Cfg<D>::kSmemBytes, stream>>>(tm_q, tm_k, tm_v, p);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = Cfg<D>::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  // scheduled while the preceding kernel of the stream drains; the kernel waits before its first global access
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  CB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, tm_q, tm_k, tm_v, p));
   CB200_CUDA_TRY(cudaGetLastError());
   return CB200_OK;
 }

@@ -331,3 +331,38 @@ def test_arch_description_and_tile_snapping():
     assert arch.tmem_columns_needed((128, 256)) == dev.tmem_columns
     with pytest.raises(ValueError):
         arch.snap_tile(0, 8)
+
+
+def test_new_operators_refuse_cpu_tensors_and_bad_shapes():
+    """There is no CPU path: every operator refuses host tensors before anything is launched, and shape
+    errors are reported as ValueError like the reference's kernel binding does (python/cleave/pipeline/kernel.py:67-82)."""
+    import torch
+
+    from cleave_b200 import ops
+
+    h = lambda *s: torch.zeros(*s, dtype=torch.float16)  # noqa: E731
+    with pytest.raises(ValueError, match="CUDA"):
+        ops.matmul_matmul(h(2, 8, 64), h(2, 8, 64), h(2, 8, 64))
+    with pytest.raises(ValueError, match="CUDA"):
+        ops.qknorm_attention(h(2, 8, 64), h(2, 8, 64), h(2, 8, 64))
+    with pytest.raises(ValueError, match="CUDA"):
+        ops.matmul_rowsum(h(8, 16), h(16, 8))
+    with pytest.raises(ValueError, match="CUDA"):
+        ops.lora(h(8, 16), h(16, 8), h(16, 8), h(8, 8))
+
+
+def test_kernel_text_of_the_remaining_demo_operators_round_trips():
+    from cleave_b200.codegen import B200CodeGen, make_spec
+    from cleave_b200.runtime.compile import _load_main_kernel_from_code
+
+    for family, dims, attrs in (("matmul_matmul", {"HQ": 32, "HKV": 32, "SQ": 4096, "SKV": 4096, "D": 64}, {}),
+                                ("qknorm_attention", {"HQ": 64, "HKV": 8, "SQ": 4096, "SKV": 4096, "D": 128}, {"eps": 1e-6}),
+                                ("matmul_rowsum", {"M": 4096, "N": 4096, "K": 64}, {}),
+                                ("lora", {"M": 16, "N": 4096, "K": 4096, "R": 16}, {})):
+        spec = make_spec(family, "float16", dims, attrs=attrs)
+        text = B200CodeGen().gen(spec)
+        assert "main_kernel" in text and text == B200CodeGen().gen(make_spec(family, "float16", dims, attrs=attrs))
+        back = _load_main_kernel_from_code(text)
+        assert back.family == family and back.dims == dims and [p.name for p in back.params] == [p.name for p in spec.params]
+    assert [p.name for p in make_spec("lora", "float16", {"M": 16, "N": 4096, "K": 4096, "R": 16}).params] == [
+        "PlaceHolder_x", "PlaceHolder_w", "PlaceHolder_a", "PlaceHolder_b", "OutputNode"]

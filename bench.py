@@ -68,7 +68,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", self.sel, f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._pump, daemon=True)
             self.thread.start()
         except Exception:  # noqa: BLE001
@@ -143,6 +143,8 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--sustained-steps", type=int, default=300,
+                    help="steps of the extra long region reported under \"sustained\" (0 skips it)")
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--e2e-steps", type=int, default=3, help="steps of the host-buffer end-to-end leg")
@@ -233,6 +235,23 @@ def main():
     all_bytes = sum_over_ranks(float(my_bytes))
     ms_per_step = total_ms / args.steps
     value = all_bytes / (ms_per_step * 1e-3) / 1e12
+
+    # A second, longer region: 20 steps are a 25 ms burst (the protocol of the measured copy bandwidth the
+    # roofline divides by); a third of a second of back-to-back steps shows what the part sustains once
+    # its power cap engages, with enough clock samples to say so.
+    sustained = None
+    if args.sustained_steps > 0 and not args.kernel_only:
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(local_rank) as clocks_long:
+            barrier()
+            ev0.record()
+            for _ in range(args.sustained_steps):
+                step()
+            ev1.record()
+            barrier()
+        long_ms = max_over_ranks(ev0.elapsed_time(ev1)) / args.sustained_steps
+        sustained = {"value": all_bytes / (long_ms * 1e-3) / 1e12, "unit": UNIT, "steps": args.sustained_steps,
+                     "ms_per_step": long_ms, "clocks": clocks_long.summary()}
 
     if args.kernel_only:
         if rank == 0:
@@ -350,7 +369,7 @@ def main():
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f16", "data": "synthetic", "config": dict(WORKLOAD, batch_per_gpu=args.batch, tokens_rank0=w.tokens),
-        "clocks": clocks.summary(), "e2e": e2e, "e2e_kv_resident": e2e_resident, "gpu_launches": args.steps,
+        "clocks": clocks.summary(), "sustained": sustained, "e2e": e2e, "e2e_kv_resident": e2e_resident, "gpu_launches": args.steps,
         "roofline": roofline, "cpu_baseline": cpu, "other_configs": others}))
     if dist is not None:
         dist.destroy_process_group()

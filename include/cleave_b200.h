@@ -32,7 +32,10 @@
 extern "C" {
 #endif
 
-#define CB200_VERSION 1
+/* 2: cb200_gemm_args and cb200_attn_prefill_args gained trailing fields (zero = the behaviour of version 1);
+ *    new entry points cb200_matmul_matmul, cb200_matmul_rowsum, cb200_lora. A binding written against
+ *    version 1 must zero-fill the longer structs. */
+#define CB200_VERSION 2
 
 typedef enum {
   CB200_OK = 0,

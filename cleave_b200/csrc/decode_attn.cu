@@ -26,6 +26,7 @@ namespace cb200 {
 constexpr int kTile = 64;          // tokens per KV tile
 constexpr int kRowsMax = 16;       // query rows one item carries (M of the MMA tile)
 constexpr int kConsumerWarps = 4;  // each owns 16 tokens of every tile
+constexpr int kPrefetchTiles = 16; // tiles a CTA asks into L2 while it waits for the preceding kernel (contiguous caches)
 constexpr float kLog2e = 1.4426950408889634f;
 
 struct DecodeParams {
@@ -129,8 +130,6 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
     }
   }
   __syncthreads();
-  if (!p.paged) pdl_wait();
-  pdl_launch_dependents();  // the next kernel's CTAs may take SMs as this grid's CTAs retire
 
   const int total_per_head = p.paged ? P[p.batch] : p.batch * tiles_per_req;
   const int total = hkvv * total_per_head;
@@ -139,6 +138,25 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
   const int u0 = min(static_cast<int>(blockIdx.x) * span, total);
   const int u1 = min(u0 + span, total);
   Walker walker{p.paged ? P : nullptr, p.batch, hkvv, tiles_per_req};
+  if (!p.paged) {
+    // Contiguous caches: where this CTA's first tiles lie follows from the launch parameters alone, so
+    // while the preceding kernel still runs the TMA unit is asked to bring them into L2 (a hint: nothing
+    // reaches the SM, and L2 is where that kernel's writes land too). The first ring fill then comes from
+    // L2 with warm address translations instead of paying the cold 2.3 us.
+    if (!GATHER && warp == kConsumerWarps && lane == 0 && u0 < u1) {
+      const Piece pc = walker.at(u0, u1);
+      const int h = pc.hv / p.vblk;
+      for (int t = pc.tile0; t < pc.tile0 + min(pc.count, kPrefetchTiles); ++t) {
+#pragma unroll
+        for (int hf = 0; hf < D / 64; ++hf) {
+          tma_prefetch_4d(&tm_k, hf * 64, 0, t * kTile, pc.b * p.hkv + h);
+          tma_prefetch_4d(&tm_v, hf * 64, 0, t * kTile, pc.b * p.hkv + h);
+        }
+      }
+    }
+    pdl_wait();
+  }
+  pdl_launch_dependents();  // the next kernel's CTAs may take SMs as this grid's CTAs retire
 
   if (warp >= kConsumerWarps) {
     // ================================================================= producer warp(s)

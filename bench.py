@@ -3,10 +3,12 @@ page 64, lengths uniform in [512, 32768], fp16), one step = one pass over one ba
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-N > 1 is launched by ``python -m torch.distributed.run``; the batch is sharded by request with no
-collective on the data path: every rank decodes its own 128-request batch (weak scaling), the
-time is the maximum over ranks and the value is the whole job's algorithmic KV bandwidth.
-Prints ONE JSON line on rank 0.
+N > 1 is launched by ``python -m torch.distributed.run``: ONE global batch of 128 * N requests is split
+by request over the ranks (longest first over KV tile counts, ``cleave_b200.sharding``), every rank
+holds only its requests' pages, and there is no collective on the data path (weak scaling: the work per
+GPU stays that of 128 requests). The time is the maximum over ranks and the value is the whole job's
+algorithmic KV bandwidth. Rank 0 checks a sample of its requests (the longest and the shortest among
+them) against the CPU reference and the run fails on a mismatch. Prints ONE JSON line on rank 0.
 """
 
 from __future__ import annotations
@@ -29,11 +31,14 @@ UNIT = "TB/s"
 WORKLOAD = dict(workload="paged GQA decode: batch 128 per GPU, 32 q / 8 kv heads, head_dim 128, page 64, "
                          "kv_len ~ U[512, 32768], block table = seeded permutation, fp16",
                 batch_per_gpu=128, num_qo_heads=32, num_kv_heads=8, head_dim=128, page_size=64,
-                kv_len_range=[512, 32768], sharding="by request, no collective",
+                kv_len_range=[512, 32768],
+                sharding="one global batch of 128 * n_gpus requests, split by request (longest first over KV "
+                         "tiles), no collective",
                 l2="inputs (about 8 GB per GPU) are far larger than the 126 MB L2; no flush needed")
 FALLBACK_HBM_GBS = 6650.0
-# DRAM bytes the kernel moves per algorithmic byte, from the committed ncu capture
-# (profiles/decode_attn_paged_ps64.md); None until a capture exists.
+# DRAM bytes the kernel moved per algorithmic byte in an ncu capture of this kernel on a batch of 32
+# requests of the same length distribution (every KV tile is read once, so traffic scales with the
+# live tokens). A constant from that capture, not a measurement of this run.
 TRAFFIC_PER_ALGORITHMIC_BYTE = 1.0046
 CPU_SAMPLE_REQUESTS = 8
 
@@ -49,7 +54,9 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while a region runs."""
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi. The sampler is started early
+    (nvidia-smi takes longer to start than a short timed region lasts, most of all on an 8-GPU box);
+    ``mark()`` opens a region and ``summary()`` reports the samples taken since the mark."""
 
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
@@ -62,7 +69,7 @@ class ClockSampler:
             self.sel = uuid if uuid.startswith("GPU-") else "GPU-" + uuid
         except Exception:  # noqa: BLE001
             self.sel = str(device_index)
-        self.proc, self.lines = None, []
+        self.proc, self.lines, self.start = None, [], 0
 
     def __enter__(self):
         try:
@@ -71,6 +78,9 @@ class ClockSampler:
                  "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._pump, daemon=True)
             self.thread.start()
+            deadline = time.time() + 10.0
+            while not self.lines and time.time() < deadline and self.proc.poll() is None:
+                time.sleep(0.02)
         except Exception:  # noqa: BLE001
             self.proc = None
         return self
@@ -79,19 +89,24 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.lines.append(line.strip())
 
+    def mark(self):
+        self.start = len(self.lines)
+
     def __exit__(self, *exc):
         if self.proc is not None:
-            time.sleep(0.15)
             self.proc.terminate()
             try:
                 self.proc.wait(timeout=5)
             except Exception:  # noqa: BLE001
                 self.proc.kill()
 
-    def summary(self):
+    def summary(self, settle=0.12):
+        """Samples since ``mark()``; waits ``settle`` seconds first so that a sample taken just after a
+        short region (its clocks are still the region's) is included."""
+        time.sleep(settle)
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
+        for line in self.lines[self.start:]:
             parts = [x.strip() for x in line.split(",")]
             if len(parts) < 6:
                 continue
@@ -109,34 +124,120 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
-def cpu_baseline_run(sample, steps, warmup):
-    """Times the CPU oracle (numpy port of the reference's torch path) on ``sample``; returns
-    (TB/s, seconds per step, thread count)."""
+REF_COPY = os.path.join(ROOT, "oracle", "_ref", "dynamic_reference.py")
+
+
+def cpu_reference():
+    """The CPU implementation both CPU legs time and the parity check compares with: the reference's own
+    torch code for this operator (python/cleave/dynamic/reference.py:180-200), loaded by file path from
+    the git-ignored copy the build step leaves under oracle/_ref/ when the reference tree is present
+    (``kind`` "reference"); else its numpy restatement under oracle/ (``kind`` "port").
+    Returns ``(kind, threads, run)`` with ``run(sample) -> (out, lse)`` as fp32 numpy arrays."""
+    import numpy as np
+    import torch
+
+    torch.set_num_threads(max(torch.get_num_threads(), os.cpu_count() or 1))
+    if os.path.exists(REF_COPY):
+        import importlib.util
+
+        spec = importlib.util.spec_from_file_location("cleave_dynamic_reference", REF_COPY)
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+
+        def run(sample):
+            batch, hq, d = sample.q.shape
+            num_pages, page, hkv, _ = sample.k_cache.shape
+            dims = (batch, hq, hkv, d, num_pages, sample.kv_indices.numel())
+            fn = mod.gqa_paged_decode_reference(dims, [int(x) for x in sample.kv_lens], page_size=page)
+            out, lse = fn(sample.q, sample.k_cache, sample.v_cache, sample.kv_indptr, sample.kv_indices,
+                          sample.kv_last_page_len, sample.sm_scale)
+            return out.float().numpy(), lse.float().numpy()
+
+        return "reference", torch.get_num_threads(), run
+
     from oracle import cleave_oracle as orc
 
-    try:
-        from threadpoolctl import threadpool_info
-
-        threads = max([p.get("num_threads", 1) for p in threadpool_info()] or [1])
-    except Exception:  # noqa: BLE001
-        threads = os.cpu_count() or 1
+    threads = os.cpu_count() or 1
     try:  # a launcher may have pinned OMP_NUM_THREADS to 1: give the BLAS pool every host core back
-        from threadpoolctl import threadpool_limits
+        from threadpoolctl import threadpool_info, threadpool_limits
 
         threadpool_limits(limits=os.cpu_count())
         threads = max([p.get("num_threads", 1) for p in threadpool_info()] or [threads])
     except Exception:  # noqa: BLE001
         pass
-    a = [sample.q.float().numpy(), sample.k_cache.float().numpy(), sample.v_cache.float().numpy(),
-         sample.kv_indptr.numpy(), sample.kv_indices.numpy(), sample.kv_last_page_len.numpy()]
-    times = []
+
+    def run(sample):
+        out, lse = orc.gqa_paged_decode(sample.q.float().numpy(), sample.k_cache.float().numpy(),
+                                        sample.v_cache.float().numpy(), sample.kv_indptr.numpy(),
+                                        sample.kv_indices.numpy(), sample.kv_last_page_len.numpy(),
+                                        sample.sm_scale, out_dtype="f16")
+        return np.asarray(out, dtype=np.float32), np.asarray(lse, dtype=np.float32)
+
+    return "port", threads, run
+
+
+def cpu_baseline_run(sample, steps, warmup):
+    """Times the CPU implementation on ``sample``: ``(TB/s, seconds per step, threads, kind, (out, lse))``."""
+    kind, threads, run = cpu_reference()
+    times, res = [], None
     for i in range(warmup + steps):
         t0 = time.perf_counter()
-        orc.gqa_paged_decode(*a, sample.sm_scale, out_dtype="f16")
+        res = run(sample)
         if i >= warmup:
             times.append(time.perf_counter() - t0)
     per = sum(times) / len(times)
-    return sample.algorithmic_bytes() / per / 1e12, per, threads
+    return sample.algorithmic_bytes() / per / 1e12, per, threads, kind, res
+
+
+def parity_sample(kv_lens, n):
+    """``n`` request indices: the longest, the shortest, and the rest spread evenly over the batch."""
+    lens = [int(x) for x in kv_lens]
+    picks = [max(range(len(lens)), key=lens.__getitem__), min(range(len(lens)), key=lens.__getitem__)]
+    step = max(1, len(lens) // max(1, n - 2))
+    for i in range(0, len(lens), step):
+        if len(picks) >= n:
+            break
+        if i not in picks:
+            picks.append(i)
+    return sorted(set(picks))
+
+
+def nshard_gemm_rows(dist, rank, world, torch):
+    """Strong-scaling reading of the N-sharded fused GEMM (RMSNorm(X) @ W, 4096 x 14336 x 4096, fp16): W is
+    split along N, every rank recomputes the row statistics, one NCCL all-gather reassembles Y. Device
+    time, maximum over ranks, with and without the all-gather."""
+    from cleave_b200 import ops, sharding
+
+    m, n, k = 4096, 14336, 4096
+    g = torch.Generator(device="cpu").manual_seed(0)
+    x = torch.randn(m, k, generator=g).to(torch.float16).cuda()
+    lo, hi = sharding.n_shard(n, rank, world)
+    gw = torch.Generator(device="cuda").manual_seed(1 + rank)
+    w = (torch.randn(k, hi - lo, generator=gw, device="cuda") / k ** 0.5).to(torch.float16)
+    local = lambda xx, ww: ops.rmsnorm_matmul(xx, ww, eps=1e-6)  # noqa: E731
+    rows = []
+    for gather in (False, True):
+        fn = lambda: sharding.gemm_n_sharded(local, x, (w,), n, gather=gather)  # noqa: E731
+        for _ in range(3):
+            fn()
+        dist.barrier()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 10
+        a.record()
+        for _ in range(reps):
+            fn()
+        b.record()
+        dist.barrier()
+        torch.cuda.synchronize()
+        t = torch.tensor([a.elapsed_time(b) / reps], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        us = float(t.item()) * 1e3
+        rows.append({"config": f"rmsnorm_matmul_{m}x{n}x{k}_n_sharded_over_{world}" + ("_allgather" if gather else ""),
+                     "us": round(us, 2), "TFLOP/s": round(2 * m * n * k / us / 1e6, 1), "scaling": "strong",
+                     "allgather": gather})
+    rows[1]["allgather_us"] = round(rows[1]["us"] - rows[0]["us"], 2)
+    return rows
 
 
 def main():
@@ -155,9 +256,10 @@ def main():
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
+    import numpy as np
     import torch
 
-    from cleave_b200.workloads import paged_decode_workload, sub_workload
+    from cleave_b200.workloads import paged_decode_workload, sharded_paged_decode_workload, sub_workload
 
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -165,19 +267,19 @@ def main():
 
     if args.impl == "reference":
         # The reference's own implementation of this path is its torch CPU code
-        # (python/cleave/dynamic/reference.py:180-200); its numpy port under oracle/ is what can
-        # travel to the benchmark box. Rank 0 alone runs it, on a bounded sample per step.
+        # (python/cleave/dynamic/reference.py:180-200). Rank 0 alone runs it, on a bounded sample per step.
         if rank != 0:
             return
         w = paged_decode_workload(seed=0, device="cpu", batch=CPU_SAMPLE_REQUESTS)
-        tbs, per, threads = cpu_baseline_run(w, args.steps, args.warmup)
-        sample = (f"{CPU_SAMPLE_REQUESTS} requests of the workload's length distribution "
+        tbs, per, threads, kind, _ = cpu_baseline_run(w, args.steps, args.warmup)
+        sample = (f"{CPU_SAMPLE_REQUESTS} requests drawn from the workload's length distribution "
                   f"({w.tokens} tokens, {w.algorithmic_bytes() / 1e9:.2f} GB of KV) per step")
         print(json.dumps({
             "impl": "reference", "metric": METRIC, "value": tbs, "unit": UNIT, "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": per * 1e3, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": WORKLOAD,
-            "cpu_baseline": {"value": tbs, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+            "sample_requests": CPU_SAMPLE_REQUESTS,
+            "cpu_baseline": {"value": tbs, "unit": UNIT, "cores": threads, "kind": kind, "sample": sample},
             "e2e": {"value": tbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}))
         return
@@ -212,46 +314,50 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.SUM)
         return float(t.item())
 
-    w = paged_decode_workload(seed=rank, device="cuda", batch=args.batch)
+    w, my_requests, tiles_per_rank = sharded_paged_decode_workload(world, rank, batch_per_gpu=args.batch, seed=0)
     out = torch.empty_like(w.q)
     lse = torch.empty(w.q.shape[:2], dtype=torch.float32, device="cuda")
     step = lambda: ops.gqa_paged_decode(*w.args(), out=out, lse=lse)  # noqa: E731
 
-    for _ in range(args.warmup):
-        step()
-    barrier()
-    events = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
     with ClockSampler(local_rank) as clocks:
+        for _ in range(args.warmup):
+            step()
+        barrier()
+        events = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+        clocks.mark()
         barrier()
         events[0].record()
         for i in range(args.steps):
             step()
             events[i + 1].record()
         barrier()
-    ops.check_workspace(ops.workspace("attn_decode", 0, "cuda"))
-    total_ms = max_over_ranks(events[0].elapsed_time(events[-1]))
-    launch_ms = [events[i].elapsed_time(events[i + 1]) for i in range(args.steps)]
-    my_bytes = w.algorithmic_bytes()
-    all_bytes = sum_over_ranks(float(my_bytes))
-    ms_per_step = total_ms / args.steps
-    value = all_bytes / (ms_per_step * 1e-3) / 1e12
+        clocks_burst = clocks.summary()
+        ops.check_workspace(ops.workspace("attn_decode", 0, "cuda"))
+        total_ms = max_over_ranks(events[0].elapsed_time(events[-1]))
+        launch_ms = [events[i].elapsed_time(events[i + 1]) for i in range(args.steps)]
+        my_bytes = w.algorithmic_bytes()
+        all_bytes = sum_over_ranks(float(my_bytes))
+        ms_per_step = total_ms / args.steps
+        value = all_bytes / (ms_per_step * 1e-3) / 1e12
 
-    # A second, longer region: 20 steps are a 25 ms burst (the protocol of the measured copy bandwidth the
-    # roofline divides by); a third of a second of back-to-back steps shows what the part sustains once
-    # its power cap engages, with enough clock samples to say so.
-    sustained = None
-    if args.sustained_steps > 0 and not args.kernel_only:
-        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        with ClockSampler(local_rank) as clocks_long:
+        # A second, longer region: 20 steps are a 25 ms burst (the protocol of the measured copy bandwidth the
+        # roofline divides by); a third of a second of back-to-back steps shows what the part sustains once
+        # its power cap engages, with enough clock samples to say so.
+        sustained = None
+        if args.sustained_steps > 0 and not args.kernel_only:
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            clocks.mark()
             barrier()
             ev0.record()
             for _ in range(args.sustained_steps):
                 step()
             ev1.record()
             barrier()
-        long_ms = max_over_ranks(ev0.elapsed_time(ev1)) / args.sustained_steps
-        sustained = {"value": all_bytes / (long_ms * 1e-3) / 1e12, "unit": UNIT, "steps": args.sustained_steps,
-                     "ms_per_step": long_ms, "clocks": clocks_long.summary()}
+            long_ms = max_over_ranks(ev0.elapsed_time(ev1)) / args.sustained_steps
+            sustained = {"value": all_bytes / (long_ms * 1e-3) / 1e12, "unit": UNIT, "steps": args.sustained_steps,
+                         "ms_per_step": long_ms, "clocks": clocks.summary()}
+    if clocks_burst["samples"] == 0 and sustained is not None:  # a 25 ms region can fall between two samples
+        clocks_burst = dict(sustained["clocks"], note="no sample fell inside the short region; these are the long region's")
 
     if args.kernel_only:
         if rank == 0:
@@ -331,6 +437,14 @@ def main():
     if e2e is None:
         e2e = dict(e2e_resident, note="host memory too small to stage the KV cache; cache kept resident")
 
+    # the N-sharded fused GEMM with its one collective (every rank takes part; rank 0 reports)
+    sharded_gemm = None
+    if dist is not None and not args.no_other_configs:
+        try:
+            sharded_gemm = nshard_gemm_rows(dist, rank, world, torch)
+        except Exception as exc:  # noqa: BLE001 - the headline line must still be printed
+            sharded_gemm = [{"error": f"{type(exc).__name__}: {exc}"}]
+
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
@@ -345,18 +459,29 @@ def main():
                 "traffic": None if TRAFFIC_PER_ALGORITHMIC_BYTE is None else my_bytes * TRAFFIC_PER_ALGORITHMIC_BYTE,
                 "frac_of_nominal_8TBs": achieved / 8000.0}
 
-    sample = sub_workload(w, range(CPU_SAMPLE_REQUESTS))
-    cpu_tbs, cpu_s, threads = cpu_baseline_run(sample, 2, 1)
-    cpu = {"value": cpu_tbs, "unit": UNIT, "cores": threads, "kind": "port",
-           "sample": f"first {CPU_SAMPLE_REQUESTS} requests of rank 0's batch ({sample.tokens} tokens, "
-                     f"{sample.algorithmic_bytes() / 1e9:.2f} GB of KV), {cpu_s:.2f} s per pass, 2 passes after 1 warm-up"}
+    # ---- CPU leg on a sample of rank 0's requests; its result is the checker of the timed output
+    picks = parity_sample(w.kv_lens, CPU_SAMPLE_REQUESTS)
+    sample = sub_workload(w, picks)
+    cpu_tbs, cpu_s, threads, kind, (want_out, want_lse) = cpu_baseline_run(sample, 2, 1)
+    cpu = {"value": cpu_tbs, "unit": UNIT, "cores": threads, "kind": kind,
+           "sample": f"{len(picks)} requests of rank 0's batch, the longest and the shortest included "
+                     f"({sample.tokens} tokens, {sample.algorithmic_bytes() / 1e9:.2f} GB of KV), "
+                     f"{cpu_s:.2f} s per pass, 2 passes after 1 warm-up"}
+    sel = torch.tensor(picks, device="cuda")
+    got_out, got_lse = out[sel].float().cpu().numpy(), lse[sel].cpu().numpy()
+    err_out = float(np.max(np.abs(got_out - want_out)))
+    err_lse = float(np.max(np.abs(got_lse - want_lse)))
+    ok = bool(np.allclose(got_out, want_out, rtol=2e-2, atol=2e-2) and np.allclose(got_lse, want_lse, rtol=1e-3, atol=2e-3))
+    parity = {"checked": len(picks), "requests": picks, "kv_lens": [int(w.kv_lens[i]) for i in picks],
+              "max_abs_err": err_out, "max_abs_err_lse": err_lse, "tolerance": "out rtol 2e-2 atol 2e-2; lse rtol 1e-3 atol 2e-3",
+              "against": kind, "ok": ok}
 
     # The other benchmark configurations (parity-test cases, not the headline): one CUDA-graph-timed
     # reading each, with its fraction of the measured HBM / tensor peaks.
     others = []
     if world == 1 and not args.no_other_configs:
         try:
-            from cleave_b200 import microbench
+            import microbench
 
             for name, build in microbench.CONFIGS.items():
                 r = microbench.measure(name, build)
@@ -364,15 +489,21 @@ def main():
                 torch.cuda.empty_cache()
         except Exception as exc:  # noqa: BLE001 - the headline line must still be printed
             others.append({"error": f"{type(exc).__name__}: {exc}"})
+    if sharded_gemm:
+        others.extend(sharded_gemm)
 
     print(json.dumps({
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "f16", "data": "synthetic", "config": dict(WORKLOAD, batch_per_gpu=args.batch, tokens_rank0=w.tokens),
-        "clocks": clocks.summary(), "sustained": sustained, "e2e": e2e, "e2e_kv_resident": e2e_resident, "gpu_launches": args.steps,
+        "vs_baseline": None, "dtype": "f16", "data": "synthetic", "config": WORKLOAD,
+        "requests_rank0": len(my_requests), "tokens_rank0": w.tokens, "kv_tiles_per_rank": tiles_per_rank,
+        "clocks": clocks_burst, "sustained": sustained, "e2e": e2e, "e2e_kv_resident": e2e_resident,
+        "gpu_launches": args.steps, "parity": parity,
         "roofline": roofline, "cpu_baseline": cpu, "other_configs": others}))
     if dist is not None:
         dist.destroy_process_group()
+    if not ok:
+        raise SystemExit("bench.py: the timed output does not match the CPU reference")
 
 
 if __name__ == "__main__":

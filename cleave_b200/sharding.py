@@ -32,16 +32,29 @@ def partition_requests(kv_lens, world: int, tile: int = 64, balance: bool = True
     return [sorted(x) for x in out]
 
 
-def shard_paged_tables(kv_indptr, kv_indices, kv_last_page_len, requests):
+def shard_paged_tables(kv_indptr, kv_indices, kv_last_page_len, requests, keep_order: bool = False):
     """Page tables of one rank's requests over a private pool: ``(indptr, indices, last, pages)``
-    where ``pages`` lists the global page ids the rank must hold, in its local numbering."""
+    where ``pages`` lists the global page ids the rank must hold, in its local numbering (local page
+    ``i`` holds global page ``pages[i]``). By default local ids follow the walk of the requests (page
+    tables become sequential); ``keep_order=True`` numbers the rank's pages by the rank of their global
+    id instead, so that a scattered global table stays as scattered on the rank (a subset of a random
+    permutation, order kept, is again a random permutation)."""
     ptr = [int(x) for x in kv_indptr]
-    new_ptr, new_idx, pages = [0], [], []
+    new_ptr, walk = [0], []
     for b in requests:
-        mine = [int(x) for x in kv_indices[ptr[b]:ptr[b + 1]]]
-        new_idx.extend(range(len(pages), len(pages) + len(mine)))
-        pages.extend(mine)
-        new_ptr.append(new_ptr[-1] + len(mine))
+        walk.extend(int(x) for x in kv_indices[ptr[b]:ptr[b + 1]])
+        new_ptr.append(len(walk))
+    if keep_order:
+        pages = sorted(set(walk))
+        local = {g: i for i, g in enumerate(pages)}
+        new_idx = [local[g] for g in walk]
+    else:
+        pages, local, new_idx = [], {}, []
+        for g in walk:  # a page shared by two requests is held once
+            if g not in local:
+                local[g] = len(pages)
+                pages.append(g)
+            new_idx.append(local[g])
     last = None if kv_last_page_len is None else [int(kv_last_page_len[b]) for b in requests]
     return new_ptr, new_idx, last, pages
 

@@ -97,3 +97,39 @@ def sub_workload(w: PagedDecodeWorkload, requests) -> PagedDecodeWorkload:
     return PagedDecodeWorkload(w.q.cpu()[req], kc, vc, torch.tensor(new_ptr, dtype=torch.int32),
                                torch.cat(new_idx).to(torch.int32) if new_idx else torch.zeros(0, dtype=torch.int32),
                                w.kv_last_page_len.cpu()[req], w.sm_scale, w.kv_lens[req])
+
+
+def sharded_paged_decode_workload(world, rank, batch_per_gpu=128, hq=32, hkv=8, d=128, page_size=64, lo=512,
+                                  hi=32768, seed=0, dtype=torch.float16, device="cuda"):
+    """Rank ``rank``'s share of ONE global batch of ``world * batch_per_gpu`` requests, split by request
+    with :func:`cleave_b200.sharding.partition_requests` (longest first over KV tile counts) and held in
+    a private pool (:func:`cleave_b200.sharding.shard_paged_tables` with the global table's scatter kept).
+    Returns ``(workload, requests, tiles_per_rank)``: the rank's workload, the global indices of its
+    requests and every rank's KV tile count. Lengths, tables and Q of the global batch are drawn on the
+    CPU generator exactly as :func:`paged_decode_workload` draws them (``world = 1`` gives that
+    workload's tables and Q); a rank's cache pages are drawn on its own device."""
+    from . import sharding
+
+    batch = world * batch_per_gpu
+    kv_lens, kv_indptr, kv_indices, last, _ = paged_decode_tables(batch, page_size, lo, hi, seed)
+    parts = sharding.partition_requests(kv_lens.tolist(), world, tile=64)
+    tiles = [sum(max(1, -(-int(kv_lens[i]) // 64)) for i in p) for p in parts]
+    mine = parts[rank]
+    lptr, lidx, llast, held = sharding.shard_paged_tables(kv_indptr.tolist(), kv_indices.tolist(), last.tolist(),
+                                                          mine, keep_order=True)
+    g = torch.Generator(device="cpu").manual_seed(seed + 1)
+    q = torch.randn(batch, hq, d, generator=g).to(dtype)[torch.tensor(mine, dtype=torch.long)]
+    dev = torch.device(device)
+    shape = (len(held), page_size, hkv, d)
+    if dev.type == "cuda":
+        gd = torch.Generator(device=dev).manual_seed(seed + 2 + rank)
+        k_cache = torch.randn(shape, generator=gd, device=dev, dtype=dtype)
+        v_cache = torch.randn(shape, generator=gd, device=dev, dtype=dtype)
+    else:
+        k_cache = torch.randn(shape, generator=g).to(dtype)
+        v_cache = torch.randn(shape, generator=g).to(dtype)
+    w = PagedDecodeWorkload(q.to(dev), k_cache, v_cache, torch.tensor(lptr, dtype=torch.int32, device=dev),
+                            torch.tensor(lidx, dtype=torch.int32, device=dev),
+                            torch.tensor(llast, dtype=torch.int32, device=dev), float(d) ** -0.5,
+                            kv_lens[torch.tensor(mine, dtype=torch.long)])
+    return w, mine, tiles

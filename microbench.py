@@ -1,7 +1,7 @@
 """Per-operator timing of the kernel library on the benchmark configurations.
 
-    python -m cleave_b200.microbench                      # every configuration, one line each
-    python -m cleave_b200.microbench --op rmsnorm_matmul --m 4096 --n 14336 --k 4096 --launches 3
+    python microbench.py                      # every configuration, one line each
+    python microbench.py --op rmsnorm_matmul --m 4096 --n 14336 --k 4096 --launches 3
 
 Timing follows the reference's protocol (python/cleave/runtime/timer.py:76-108,
 python/cleave/runtime/autotune.py:36-43): CUDA events around CUDA-graph replays, minimum over
@@ -16,17 +16,22 @@ from __future__ import annotations
 import argparse
 import json
 import os
+import sys
 
 import torch
 
-from . import ops
-from .runtime.timer import min_launch_us
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from cleave_b200 import ops  # noqa: E402
+from cleave_b200.runtime.timer import min_launch_us  # noqa: E402
 
 NOMINAL_HBM_GBS, NOMINAL_TFLOPS = 8000.0, 2250.0
 
 
 def _peaks():
-    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     try:
         with open(path) as f:
             d = json.load(f)
@@ -173,7 +178,7 @@ def attn_prefill_case_rect(hq, hkv, sq, skv, d, dtype=torch.float16):
 def paged_decode_case(page_size=1, batch=64, hi=8192):
     """Paged GQA decode (32 / 8 heads, d 128, bf16) over a cache far larger than L2; page size 1 takes
     the row-gather path."""
-    from .workloads import paged_decode_workload
+    from cleave_b200.workloads import paged_decode_workload
 
     w = paged_decode_workload(batch=batch, page_size=page_size, lo=512, hi=hi, dtype=torch.bfloat16)
     out = torch.empty_like(w.q)

@@ -154,3 +154,31 @@ def test_workspace_shared_by_launches_of_different_shapes():
                                                   inp["kv_indices"], inp["kv_last_page_len"], inp["sm_scale"])
         assert_close(out, want_out)
         assert_lse_close(lse, want_lse)
+
+
+@pytest.mark.parametrize("seed,dtype", [(0, torch.float16), (7, torch.float16), (7, torch.bfloat16)])
+def test_paged_decode_full_benchmark_config(seed, dtype):
+    """Benchmark configuration 5 at full size (batch 128, 32/8 heads, d 128, page 64, lengths uniform in
+    [512, 32768]; the seed-0 draw is the one bench.py times, the seed-7 draw holds 2.33 M tokens: a page pool of
+    more than 2^31 elements). A request spans up to 512 tiles and every CTA of the grid, and the combine
+    merges up to 148 partials. Six requests, the longest and the shortest among them, are compared with the
+    oracle over a private pool holding only their pages
+    (operator semantics: python/cleave/dynamic/reference.py:180-200)."""
+    from cleave_b200.workloads import paged_decode_workload, sub_workload
+
+    ops = _ops()
+    w = paged_decode_workload(seed=seed, dtype=dtype)
+    out, lse = ops.gqa_paged_decode(*w.args())
+    ops.check_workspace(ops.workspace("attn_decode", 0, "cuda"))
+    lens = w.kv_lens.tolist()
+    picks = sorted({lens.index(max(lens)), lens.index(min(lens)), 0, 41, 86, 127})
+    s = sub_workload(w, picks)
+    dt = "f16" if dtype == torch.float16 else "bf16"
+    want_out, want_lse = orc.gqa_paged_decode(s.q.float().numpy(), s.k_cache.float().numpy(), s.v_cache.float().numpy(),
+                                              s.kv_indptr.numpy(), s.kv_indices.numpy(), s.kv_last_page_len.numpy(),
+                                              s.sm_scale, out_dtype=dt)
+    sel = torch.tensor(picks, device="cuda")
+    assert_close(host(out[sel]), want_out)
+    assert_lse_close(host(lse[sel]), want_lse)
+    del w, out, lse
+    torch.cuda.empty_cache()

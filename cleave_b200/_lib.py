@@ -141,6 +141,10 @@ def lib() -> C.CDLL:
         L.cb200_attn_decode_static_scratch_max_bytes.restype = C.c_size_t
         L.cb200_attn_decode_static_scratch.restype = C.c_int
         L.cb200_attn_decode_static_scratch.argtypes = [C.POINTER(AttnDecodeArgs), C.c_void_p]
+        L.cb200_attn_decode_static_scratch_status.restype = C.c_int
+        L.cb200_attn_decode_static_scratch_status.argtypes = [C.c_void_p]
+        L.cb200_workspace_reset.restype = C.c_int
+        L.cb200_workspace_reset.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p]
         L.cb200_gemm_workspace_bytes.restype = C.c_size_t
         L.cb200_gemm_workspace_bytes.argtypes = [C.POINTER(GemmArgs)]
         L.cb200_gemm_effective_split.restype = C.c_int

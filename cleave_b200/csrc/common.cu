@@ -94,5 +94,18 @@ extern "C" int cb200_workspace_status(const void* workspace, void* stream) {
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   CB200_CUDA_TRY(cudaMemcpyAsync(&word, workspace, sizeof(int), cudaMemcpyDeviceToHost, st));
   CB200_CUDA_TRY(cudaStreamSynchronize(st));
-  return word == 0 ? CB200_OK : CB200_ERR_DEVICE_TIMEOUT;
+  if (word == 0) return CB200_OK;
+  // A launch whose wait gave up leaves the status word set, which would make every later launch on this
+  // workspace abandon its waits at the first check. The word is cleared here so that the fault is reported
+  // once; the arrival counters of the items that launch did not finish are still dirty, so the caller must
+  // zero the whole workspace (cb200_workspace_reset) before the next launch.
+  CB200_CUDA_TRY(cudaMemsetAsync(const_cast<void*>(workspace), 0, cb200::kWsHeaderBytes, st));
+  CB200_CUDA_TRY(cudaStreamSynchronize(st));
+  return CB200_ERR_DEVICE_TIMEOUT;
+}
+
+extern "C" int cb200_workspace_reset(void* workspace, size_t workspace_bytes, void* stream) {
+  if (!workspace || workspace_bytes < cb200::kWsHeaderBytes) return CB200_ERR_BAD_ARG;
+  CB200_CUDA_TRY(cudaMemsetAsync(workspace, 0, workspace_bytes, static_cast<cudaStream_t>(stream)));
+  return CB200_OK;
 }

@@ -59,10 +59,18 @@ struct SmemPlan {
   static constexpr int kFixedBytes = kStages * kStageBytes + kMergeBytes + 256;  // + barriers/flags
 };
 
+// Pages of request b that the page table really holds: kv_indptr is caller data, so the range it names is
+// clipped to [0, n_idx) and every later read of kv_indices stays inside the array whatever it says.
+__device__ __forceinline__ int item_pages(const DecodeParams& p, int b) {
+  const int base = p.kv_indptr[b];
+  if (base < 0 || base >= p.n_idx) return 0;
+  return max(min(p.kv_indptr[b + 1] - base, p.n_idx - base), 0);
+}
+
 __device__ __forceinline__ int item_valid_len(const DecodeParams& p, int b) {
   if (!p.paged) return p.kv_len;
-  const int n_pages = p.kv_indptr[b + 1] - p.kv_indptr[b];
-  if (p.page_size == 1 || p.kv_last == nullptr) return max(n_pages, 0) * p.page_size;
+  const int n_pages = item_pages(p, b);
+  if (p.page_size == 1 || p.kv_last == nullptr) return n_pages * p.page_size;
   const int v = max(n_pages - 1, 0) * p.page_size + max(p.kv_last[b], 0);
   return max(min(v, n_pages * p.page_size), 0);
 }
@@ -585,7 +593,11 @@ int plan_decode(const cb200_attn_decode_args* a, DecodeSetup* s, bool need_maps)
     tiles_ub = static_cast<long long>(a->batch) * ceil_div(a->kv_len, kTile);
   }
   const long long units_ub = tiles_ub * p.hkv * p.vblk;
-  if (units_ub >= (1LL << 31)) return CB200_ERR_UNSUPPORTED;
+  // The kernel counts tiles in 32 bits. Requests may share pages (overlapping kv_indptr ranges), so the
+  // bound for that count is every request spanning the whole table, not the table's own size.
+  const long long tiles_max = paged ? static_cast<long long>(a->batch) * ((static_cast<long long>(a->num_kv_indices) * a->page_size + kTile - 1) / kTile + 1)
+                                    : tiles_ub;
+  if (tiles_max * p.hkv * p.vblk >= (1LL << 31)) return CB200_ERR_UNSUPPORTED;
   const int sms = sm_count();
   if (sms <= 0) return CB200_ERR_CUDA;
   int grid = sms;
@@ -740,6 +752,13 @@ extern "C" int cb200_attn_decode_static_scratch(const cb200_attn_decode_args* a,
   }
   if (s.gather) return f16 ? launch_decode<__half, 64, true>(s, st) : launch_decode<__nv_bfloat16, 64, true>(s, st);
   return f16 ? launch_decode<__half, 64, false>(s, st) : launch_decode<__nv_bfloat16, 64, false>(s, st);
+}
+
+extern "C" int cb200_attn_decode_static_scratch_status(void* stream) {
+  unsigned char* scratch = nullptr;
+  const int rc = cb200::static_scratch_address(&scratch);
+  if (rc != CB200_OK) return rc;
+  return cb200_workspace_status(scratch, stream);
 }
 
 extern "C" size_t cb200_attn_decode_workspace_bytes(const cb200_attn_decode_args* a) {

@@ -117,11 +117,13 @@ mla_scores_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_holder);
-  pdl_launch_dependents();  // the values kernel may set up and prefetch V while this grid drains
   // This grid is itself a dependent launch: it was scheduled while the preceding kernel of the stream (in a
-  // decode loop, the values kernel of the step before, which still reads the P buffer) drains. Everything up
-  // to here was set-up; nothing in global memory is read or written before the wait.
+  // decode loop, the kernel that appended this step's rows to the caches) drains. Everything up to here
+  // was set-up; nothing in global memory is read or written before the wait.
   pdl_wait();
+  // Only now may the values kernel start: it fetches cache tiles before its own wait, so it must never
+  // run beside a kernel older than this one (one that may still be writing the caches).
+  pdl_launch_dependents();
 
   if (warp == 0) {
     // ================================================================ TMA producer

@@ -51,8 +51,15 @@ def workspace(kind: str, nbytes: int, device) -> torch.Tensor:
 
 
 def check_workspace(ws: torch.Tensor) -> None:
-    """Synchronise and raise if a kernel recorded a bounded-wait timeout in ``ws``."""
-    _lib.check(_lib.lib().cb200_workspace_status(ws.data_ptr(), _stream()))
+    """Synchronise and raise ``Cb200Error`` (status 6) if a kernel recorded a bounded-wait timeout in
+    ``ws``. The launch that gave up left arrival counters behind, so the workspace is zero-filled again
+    before the error is raised: the next launch on it starts clean."""
+    try:
+        _lib.check(_lib.lib().cb200_workspace_status(ws.data_ptr(), _stream()))
+    except _lib.Cb200Error as exc:
+        if exc.status == _lib.ERR_DEVICE_TIMEOUT:
+            _lib.check(_lib.lib().cb200_workspace_reset(ws.data_ptr(), ws.numel(), _stream()))
+        raise
 
 
 def _attn_args(q, k_cache, v_cache, out, lse, ws, *, batch, hq, hkv, d, sm_scale, q_rows=1,
@@ -75,31 +82,51 @@ def _attn_args(q, k_cache, v_cache, out, lse, ws, *, batch, hq, hkv, d, sm_scale
     return a
 
 
+def _paged_decode_args(q, k_cache, v_cache, kv_indptr, kv_indices, kv_last_page_len, sm_scale, out, lse, max_ctas):
+    """Argument checks shared by the two paged decode entry points; returns the filled argument struct.
+    The kernel trusts nothing in the tables (page ids and ranges are clipped on the device), but shapes,
+    dtypes and devices are the caller's contract and are refused here."""
+    q, k_cache, v_cache = _cuda(q, "q"), _cuda(k_cache, "k_cache"), _cuda(v_cache, "v_cache")
+    if q.dim() != 3 or k_cache.dim() != 4:
+        raise ValueError("q must be (batch, HQ, D) and the caches (num_pages, page_size, HKV, D)")
+    batch, hq, d = q.shape
+    num_pages, page_size, hkv, d2 = k_cache.shape
+    if d2 != d or v_cache.shape != k_cache.shape:
+        raise ValueError("k_cache / v_cache must be (num_pages, page_size, HKV, D) with q's D")
+    if k_cache.dtype != q.dtype or v_cache.dtype != q.dtype:
+        raise TypeError("q and the caches must share one storage dtype")
+    if kv_indptr.dtype != torch.int32 or kv_indices.dtype != torch.int32:
+        raise TypeError("kv_indptr / kv_indices must be int32")
+    if kv_indptr.numel() != batch + 1:
+        raise ValueError("kv_indptr must have batch + 1 entries")
+    _cuda(kv_indptr, "kv_indptr"), _cuda(kv_indices, "kv_indices")
+    if page_size != 1 and kv_last_page_len is None:
+        raise TypeError("missing input 'kv_last_page_len'")
+    if kv_last_page_len is not None:
+        if _cuda(kv_last_page_len, "kv_last_page_len").dtype != torch.int32 or kv_last_page_len.numel() != batch:
+            raise TypeError("kv_last_page_len must hold batch int32 values")
+    if tuple(_cuda(out, "out").shape) != tuple(q.shape) or out.dtype != q.dtype or out.device != q.device:
+        raise ValueError("out must have q's shape, dtype and device")
+    if tuple(_cuda(lse, "lse").shape) != (batch, hq) or lse.dtype != torch.float32 or lse.device != q.device:
+        raise ValueError("lse must be (batch, HQ) float32 on q's device")
+    return _attn_args(q, k_cache, v_cache, out, lse, None, batch=batch, hq=hq, hkv=hkv, d=d,
+                      sm_scale=sm_scale, kv_indptr=kv_indptr, kv_indices=kv_indices,
+                      kv_last_page_len=kv_last_page_len, page_size=page_size, num_pages=num_pages,
+                      max_ctas=max_ctas)
+
+
 def gqa_paged_decode(q, k_cache, v_cache, kv_indptr, kv_indices, kv_last_page_len, sm_scale, *,
                      out=None, lse=None, max_ctas=0):
     """Paged GQA/MHA/MQA decode. Argument order and meaning follow the reference's operator
     (python/cleave/dynamic/reference.py:156-200): q (batch, HQ, D); caches
     (num_pages, page_size, HKV, D); ``kv_indptr`` in pages; ``kv_last_page_len`` may be None
     when page_size is 1. Returns ``(out, lse)`` with ``lse`` base 2."""
-    q, k_cache, v_cache = _cuda(q, "q"), _cuda(k_cache, "k_cache"), _cuda(v_cache, "v_cache")
-    batch, hq, d = q.shape
-    num_pages, page_size, hkv, d2 = k_cache.shape
-    if d2 != d or v_cache.shape != k_cache.shape:
-        raise ValueError("k_cache / v_cache must be (num_pages, page_size, HKV, D) with q's D")
-    if kv_indptr.dtype != torch.int32 or kv_indices.dtype != torch.int32:
-        raise TypeError("kv_indptr / kv_indices must be int32")
-    if kv_indptr.numel() != batch + 1:
-        raise ValueError("kv_indptr must have batch + 1 entries")
-    if page_size != 1 and kv_last_page_len is None:
-        raise TypeError("missing input 'kv_last_page_len'")
     if out is None:
         out = torch.empty_like(q)
     if lse is None:
-        lse = torch.empty((batch, hq), dtype=torch.float32, device=q.device)
-    probe = _attn_args(q, k_cache, v_cache, out, lse, None, batch=batch, hq=hq, hkv=hkv, d=d,
-                       sm_scale=sm_scale, kv_indptr=kv_indptr, kv_indices=kv_indices,
-                       kv_last_page_len=kv_last_page_len, page_size=page_size, num_pages=num_pages,
-                       max_ctas=max_ctas)
+        lse = torch.empty(tuple(q.shape[:2]), dtype=torch.float32, device=q.device)
+    probe = _paged_decode_args(q, k_cache, v_cache, kv_indptr, kv_indices, kv_last_page_len, sm_scale, out, lse,
+                               max_ctas)
     need = _lib.lib().cb200_attn_decode_workspace_bytes(C.byref(probe))
     if need == 0:
         _lib.check(_lib.lib().cb200_attn_decode(C.byref(probe), _stream()))  # raises the real status
@@ -307,15 +334,15 @@ def gqa_paged_decode_static_scratch(q, k_cache, v_cache, kv_indptr, kv_indices, 
     than the array holds raise ``Cb200Error`` (status 7). All calls on a device share the array:
     keep them on one stream, or order them, or they race. The first call on a device resolves
     the array's address; make it before any stream capture."""
-    q, k_cache, v_cache = _cuda(q, "q"), _cuda(k_cache, "k_cache"), _cuda(v_cache, "v_cache")
-    batch, hq, d = q.shape
-    num_pages, page_size, hkv, _ = k_cache.shape
-    a = _attn_args(q, k_cache, v_cache, out, lse, None, batch=batch, hq=hq, hkv=hkv, d=d,
-                   sm_scale=sm_scale, kv_indptr=kv_indptr, kv_indices=kv_indices,
-                   kv_last_page_len=kv_last_page_len, page_size=page_size, num_pages=num_pages,
-                   max_ctas=max_ctas)
+    a = _paged_decode_args(q, k_cache, v_cache, kv_indptr, kv_indices, kv_last_page_len, sm_scale, out, lse, max_ctas)
     _lib.check(_lib.lib().cb200_attn_decode_static_scratch(C.byref(a), _stream()))
     return out, lse
+
+
+def check_static_scratch() -> None:
+    """Synchronise and raise ``Cb200Error`` (status 6) if a bounded wait of the most recent
+    :func:`gqa_paged_decode_static_scratch` call on the current device gave up."""
+    _lib.check(_lib.lib().cb200_attn_decode_static_scratch_status(_stream()))
 
 
 def _gemm(op, x, w, w1=None, gamma=None, eps=0.0, split_k=0, out=None, max_ctas=0, addend=None, x2=None, w2=None,

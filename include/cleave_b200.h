@@ -35,7 +35,9 @@ extern "C" {
 /* 2: cb200_gemm_args and cb200_attn_prefill_args gained trailing fields (zero = the behaviour of version 1);
  *    new entry points cb200_matmul_matmul, cb200_matmul_rowsum, cb200_lora. A binding written against
  *    version 1 must zero-fill the longer structs. */
-#define CB200_VERSION 2
+/* 3: cb200_workspace_status clears a reported fault; new cb200_workspace_reset and
+ *    cb200_attn_decode_static_scratch_status. */
+#define CB200_VERSION 3
 
 typedef enum {
   CB200_OK = 0,
@@ -57,8 +59,13 @@ int cb200_last_cuda_error(void);
 /* Number of SMs of the current device (grid sizing is a multiple of it). */
 int cb200_sm_count(void);
 /* Copies the status word of `workspace` to the host after synchronising `stream`.
- * Returns CB200_OK, CB200_ERR_DEVICE_TIMEOUT or CB200_ERR_CUDA. */
+ * Returns CB200_OK, CB200_ERR_DEVICE_TIMEOUT or CB200_ERR_CUDA. A fault is reported once: the status word is
+ * cleared before the function returns. The launch that faulted did not finish its items, so their arrival
+ * counters are still dirty: zero the workspace (cb200_workspace_reset) before launching on it again. */
 int cb200_workspace_status(const void* workspace, void* stream);
+/* Zero-fills `workspace_bytes` bytes of `workspace` on `stream` (a cudaMemsetAsync; no synchronisation): the
+ * state a workspace must be in before its first use and after a reported fault. */
+int cb200_workspace_reset(void* workspace, size_t workspace_bytes, void* stream);
 
 /* ------------------------------------------------------------------------------------------
  * Decode attention, one query token per request: O = softmax(Q K^T * scale) V, plus the base-2
@@ -144,10 +151,16 @@ typedef struct {
                          (added in fp32 in the epilogue; the low-rank term of cb200_lora) */
   int32_t dependent_launch; /* 0: the launch is ordered after the preceding kernel of the stream, as usual.
                                1: it may start while that kernel still runs and waits for it before reading any
-                                  operand (set-up overlaps). 2: it waits only before reading `addend`; X and W must
-                                  not be outputs of the preceding kernel. 3: it waits only before the first read of
-                                  the second operand pair (x2, w2 below); X and W must not be outputs of the
-                                  preceding kernel. cb200_lora streams W beside the rank-r product this way. */
+                                  operand (set-up overlaps). 2: it waits only before reading `addend`. 3: it waits
+                                  only before the first read of the second operand pair (x2, w2 below); a CTA whose
+                                  share holds no K block of that pair never waits. cb200_lora streams W beside the
+                                  rank-r product this way.
+                               Contract of modes 2 and 3: every kernel of this library lets its successor start
+                               before it has itself waited, so such a launch can run beside ANY kernel still in
+                               flight on the stream, not only the one directly before it. X, W, Y's other inputs
+                               and the workspace must therefore not be written, and the workspace not used at all,
+                               by any kernel that may still be running when the launch is made; put an ordinary
+                               launch (mode 0) before it, as cb200_lora does, and give it a workspace of its own. */
   /* Optional second operand pair, CB200_GEMM_MATMUL only (k2 = 0: none): Y = X @ W + X2 @ W2 [+ addend] in one
    * accumulator - the K blocks of X2 (m, k2) / W2 (k2, n) follow those of X / W. k2 a multiple of 8. */
   const void* x2;
@@ -382,6 +395,11 @@ int cb200_lora(const cb200_lora_args* a, void* stream);
  * ---------------------------------------------------------------------------------------- */
 size_t cb200_attn_decode_static_scratch_max_bytes(void);
 int cb200_attn_decode_static_scratch(const cb200_attn_decode_args* a, void* stream);
+/* The status word of the built-in array after synchronising `stream` (the caller has no pointer to hand to
+ * cb200_workspace_status): CB200_OK, or CB200_ERR_DEVICE_TIMEOUT if a bounded wait of the most recent call on
+ * the current device gave up, in which case that call's outputs are not valid. Ask before the next call: every
+ * call clears the word. Allocates nothing. */
+int cb200_attn_decode_static_scratch_status(void* stream);
 
 #ifdef __cplusplus
 }

@@ -182,3 +182,74 @@ def test_paged_decode_full_benchmark_config(seed, dtype):
     assert_lse_close(host(lse[sel]), want_lse)
     del w, out, lse
     torch.cuda.empty_cache()
+
+
+def test_kv_indptr_beyond_the_page_table_is_clipped():
+    """A kv_indptr whose ranges run past the end of kv_indices (caller error, or tables of the wrong width)
+    must not make the kernel read outside the table: the range of every request is clipped to the
+    ``num_kv_indices`` entries that exist. Requests that lie inside the table are unaffected; the clipped
+    one attends over the pages that are really there."""
+    lens = [700, 129, 5000, 3000]
+    inp = cases.gqa_paged_inputs(31, lens, 32, 8, 128, 64, "bf16")
+    full_idx = inp["kv_indices"]
+    keep = int(inp["kv_indptr"][3]) + 10           # the last request keeps 10 of its 47 pages
+    inp["kv_indices"] = np.ascontiguousarray(full_idx[:keep])
+    out, lse = _run_paged(inp, "bf16", 64)
+    assert np.isfinite(out).all()
+    clipped = dict(inp)
+    clipped["kv_indptr"] = np.minimum(inp["kv_indptr"], keep).astype(np.int32)
+    want_out, want_lse = orc.gqa_paged_decode(clipped["q"], clipped["k_cache"], clipped["v_cache"], clipped["kv_indptr"],
+                                              clipped["kv_indices"], clipped["kv_last_page_len"], clipped["sm_scale"])
+    assert_close(out, want_out)
+    assert_lse_close(lse, want_lse)
+    # a table that claims pages although none exist: every request is empty
+    inp["kv_indices"] = np.zeros(0, dtype=np.int32)
+    ops = _ops()
+    o, l = ops.gqa_paged_decode(dev(inp["q"], "bf16"), dev(inp["k_cache"], "bf16"), dev(inp["v_cache"], "bf16"),
+                                dev(inp["kv_indptr"]), torch.zeros(0, dtype=torch.int32, device="cuda"),
+                                dev(inp["kv_last_page_len"]), inp["sm_scale"])
+    ops.check_workspace(ops.workspace("attn_decode", 0, "cuda"))
+    assert (host(o) == 0).all() and np.isneginf(host(l)).all()
+
+
+def test_wrong_output_buffers_are_refused():
+    ops = _ops()
+    inp = cases.gqa_paged_inputs(32, [100, 64], 32, 8, 128, 64, "f16")
+    args = (dev(inp["q"], "f16"), dev(inp["k_cache"], "f16"), dev(inp["v_cache"], "f16"), dev(inp["kv_indptr"]),
+            dev(inp["kv_indices"]), dev(inp["kv_last_page_len"]), inp["sm_scale"])
+    good_out = torch.empty_like(args[0])
+    good_lse = torch.empty(2, 32, dtype=torch.float32, device="cuda")
+    for fn in (ops.gqa_paged_decode, ops.gqa_paged_decode_static_scratch):
+        with pytest.raises(ValueError):
+            fn(*args, out=torch.empty(2, 32, 64, dtype=torch.float16, device="cuda"), lse=good_lse)
+        with pytest.raises(ValueError):
+            fn(*args, out=good_out.bfloat16(), lse=good_lse)
+        with pytest.raises(ValueError):
+            fn(*args, out=good_out, lse=torch.empty(2, 32, dtype=torch.float16, device="cuda"))
+        with pytest.raises(TypeError):
+            fn(args[0], args[1], args[2], args[3].long(), args[4], args[5], args[6], out=good_out, lse=good_lse)
+
+
+def test_fault_code_in_a_workspace_reaches_the_host_once():
+    """A kernel whose bounded wait gives up writes a fault code into the first word of its workspace. No
+    wait is made to run out here: the code is written from the host, which is all the host path can see.
+    The check raises status 6, leaves the workspace zero-filled, and the next launch on it is clean."""
+    from cleave_b200 import Cb200Error
+
+    ops = _ops()
+    inp = cases.gqa_paged_inputs(33, [5000, 300], 32, 8, 128, 64, "bf16")
+    _run_paged(inp, "bf16", 64)
+    ws = ops.workspace("attn_decode", 0, "cuda")
+    ws[:4] = torch.tensor([2, 0, 0, 0], dtype=torch.uint8, device="cuda")   # kFaultEmptyBarrier
+    ws[-8:] = 7                                                             # and a dirty arrival counter
+    with pytest.raises(Cb200Error) as e:
+        ops.check_workspace(ws)
+    assert e.value.status == 6
+    torch.cuda.synchronize()
+    assert int(ws.count_nonzero()) == 0
+    ops.check_workspace(ws)
+    out, lse = _run_paged(inp, "bf16", 64)
+    want_out, want_lse = orc.gqa_paged_decode(inp["q"], inp["k_cache"], inp["v_cache"], inp["kv_indptr"],
+                                              inp["kv_indices"], inp["kv_last_page_len"], inp["sm_scale"])
+    assert_close(out, want_out)
+    assert_lse_close(lse, want_lse)

@@ -113,6 +113,32 @@ def test_mla_full_config_properties():
     assert_close(host(out[3:4]), want)
 
 
+@pytest.mark.parametrize("impl", ["tcgen05", "mma_sync"])
+def test_static_mla_after_a_kernel_that_appends_to_the_caches(impl):
+    """A decode loop appends the step's rows to the caches right before it calls the operator, on the same
+    stream. The operator's launches may be scheduled while that kernel still runs (dependent launches) and
+    must not read the caches before it has finished: the result has to see the appended rows."""
+    b, h, skv = 4, 128, 2048
+    inp = cases.mla_inputs(123, b, h, skv, 512, 64, "bf16")
+    new = cases.mla_inputs(124, b, h, skv, 512, 64, "bf16")
+    scale = 192 ** -0.5
+    q, qp = dev(inp["q"], "bf16"), dev(inp["q_pe"], "bf16")
+    kv, kp = dev(inp["kv"], "bf16"), dev(inp["k_pe"], "bf16")
+    kv_new, kp_new = dev(new["kv"], "bf16"), dev(new["k_pe"], "bf16")
+    ops = _ops()
+    ops.mla_decode(q, kv, qp, kp, scale, impl=impl)           # warm: modules loaded, workspace allocated
+    torch.cuda.synchronize()
+    for _ in range(3):
+        kv.copy_(kv_new)                                      # the "append": rewrites every row of both caches
+        kp.copy_(kp_new)
+        out = ops.mla_decode(q, kv, qp, kp, scale, impl=impl)
+        _check_ws()
+        assert_close(host(out), orc.mla_decode(inp["q"], new["kv"], inp["q_pe"], new["k_pe"], scale, "bf16"))
+        kv.copy_(dev(inp["kv"], "bf16"))
+        kp.copy_(dev(inp["k_pe"], "bf16"))
+        torch.cuda.synchronize()
+
+
 def test_paged_causal_mla_prefill_matches_reference_golden_and_oracle():
     """Reference: python/cleave/dynamic/reference.py:324-365 (mla_paged_prefill_causal_h16_ckv512_kpe64_ps1):
     the golden case from the reference's own definition, and a second seeded case against the oracle with

@@ -5,7 +5,7 @@ all device memory into its own arena at start-up and hands out only slices of it
 host that forbids allocation once it is running, a GPU whose memory is already committed to
 the KV cache. For them ``cb200_attn_decode_static_scratch`` keeps the split-KV workspace in a
 fixed array inside the library. This file checks, through the C ABI, that it gives the same
-answer as the entry point with a caller-owned workspace, twice in a row (the array keeps the
+answer as the entry point with a caller-owned workspace and as the CPU oracle, twice in a row (the array keeps the
 previous call's contents), and that it refuses a problem that does not fit.
 
 The file name sorts last on purpose: a run that stops at the first failure has then already
@@ -20,6 +20,7 @@ import torch
 
 import cases
 from _util import ATOL, RTOL, dev, host
+from oracle import cleave_oracle as orc
 
 pytestmark = pytest.mark.gpu
 
@@ -35,8 +36,13 @@ def _both(inp, dt, page_size):
     got_lse = torch.full_like(want_lse, float("nan"))
     before = torch.cuda.memory_allocated()
     ops.gqa_paged_decode_static_scratch(*args, out=got_out, lse=got_lse)
-    torch.cuda.synchronize()
+    ops.check_static_scratch()  # synchronises; raises if a bounded wait of that launch gave up
     assert torch.cuda.memory_allocated() == before  # the call itself allocated nothing through torch
+    # and against the CPU oracle, not only against the sibling entry point
+    last_np = inp["kv_last_page_len"] if page_size != 1 else None
+    orc_out, orc_lse = orc.gqa_paged_decode(inp["q"], inp["k_cache"], inp["v_cache"], inp["kv_indptr"],
+                                            inp["kv_indices"], last_np, inp["sm_scale"], out_dtype=dt)
+    _check(host(got_out), host(got_lse), orc_out, orc_lse)
     return host(got_out), host(got_lse), host(want_out), host(want_lse)
 
 

@@ -14,7 +14,7 @@ from .core.errors import CodegenError
 
 FAMILIES = ("matmul", "rmsnorm_matmul", "swiglu", "attention_decode", "mla_decode",
             "gqa_paged_decode", "mla_paged_decode", "gqa_ragged_prefill", "gqa_paged_prefill",
-            "matmul_matmul", "qknorm_attention", "matmul_rowsum", "lora")
+            "matmul_matmul", "qknorm_attention", "matmul_rowsum", "lora", "split_combine")
 FORMAT = 1
 
 
@@ -34,7 +34,7 @@ class KernelSpec:
     dtype: str                       # storage dtype: "float16" | "bfloat16"
     dims: dict = field(default_factory=dict)    # static extents (M, N, K, HQ, ...)
     split: int = 1                   # K / KV split factor the plan asked for (1 = solo)
-    role: str = "main"               # "main" (fused split, one launch) - the only role emitted
+    role: str = "main"               # "main" (fused: one launch whatever the split), "partial" or "combine"
     attrs: dict = field(default_factory=dict)   # eps, scale, gamma, max_ctas ...
     params: tuple = ()               # KernelParam, inputs in call order then outputs
 
@@ -56,6 +56,16 @@ class KernelSpec:
     @property
     def inputs(self):
         return [p for p in self.params if p.role != "output"]
+
+    def input_roles(self) -> list:
+        """The library's name for each input, in call order (``x``, ``w``, ``q`` ...). A spec made from a
+        reference plan keeps the plan's placeholder names on its parameters and lists which of them plays
+        which part in ``attrs["bind"]``; otherwise the part is the parameter name without ``PlaceHolder_``."""
+        bind = {v: k for k, v in (self.attrs.get("bind") or {}).items()}
+        return [bind.get(p.name, p.name.replace("PlaceHolder_", "", 1)) for p in self.inputs]
+
+    def by_role(self, args) -> dict:
+        return dict(zip(self.input_roles(), args))
 
     @property
     def outputs(self):
@@ -160,7 +170,20 @@ class B200CodeGen:
 
 
 # ----------------------------------------------------------------------------- plan recogniser
-def _nodes_of(obj):
+# A scheduled plan of the reference (python/cleave/pipeline/plans.py:16-41) carries a tiled flat graph:
+# ``plan.tile.flat_graph.nodes`` in topological order, each node an instance of one of the classes of
+# python/cleave/ir/ops (``PlaceHolderNode``, ``Matmul``, ``SplitView``, ``Div`` ...), with ``name``,
+# ``get_shape(0)``, ``get_dtype(0)`` and ``inputs`` (edges with ``src_node``). Element-wise nodes with a scalar
+# operand hold it in ``const`` (python/cleave/ir/ops/elementwise.py:90-101; ``const_on_left`` for ``c / x``).
+# The recogniser reads the dataflow, not the node order: which placeholder feeds which matmul operand decides
+# its role, the constants on the way to ``Exp`` give the score scale, those between the sum of squares and
+# ``RSqrt`` give eps. Tile shapes and thread counts in the plan were scored for another architecture; the
+# kernels pick their own (``cleave_b200.arch.snap_tile`` maps the hints onto what exists).
+
+_VIEWS = ("SplitView", "Reshape", "View", "Transpose", "Broadcast", "Cast")
+
+
+def _graph_of(obj):
     graph = getattr(getattr(obj, "tile", None), "flat_graph", None) or getattr(obj, "flat_graph", None) or obj
     nodes = getattr(graph, "nodes", None)
     if nodes is None:
@@ -169,14 +192,13 @@ def _nodes_of(obj):
 
 
 def _kind(node) -> str:
-    op = getattr(node, "op", None)
-    return type(op).__name__ if op is not None else type(node).__name__
+    return type(node).__name__
 
 
 def _shape(node) -> tuple:
     try:
         return tuple(int(s) for s in node.get_shape(0))
-    except Exception:  # noqa: BLE001 - fakes and placeholders expose .shape
+    except Exception:  # noqa: BLE001
         return tuple(int(s) for s in getattr(node, "shape", ()))
 
 
@@ -187,65 +209,434 @@ def _dtype_of(node, default="float16") -> str:
         return str(getattr(node, "dtype", default))
 
 
+class _Flow:
+    """Dataflow view of a flat graph."""
+
+    def __init__(self, obj):
+        self.nodes = _graph_of(obj)
+        self.pos = {id(n): i for i, n in enumerate(self.nodes)}
+        self._anc = {}
+
+    def preds(self, n):
+        return [e.src_node for e in (getattr(n, "inputs", None) or []) if getattr(e, "src_node", None) is not None]
+
+    def of(self, *kinds):
+        return [n for n in self.nodes if _kind(n) in kinds]
+
+    def ancestors(self, n):
+        key = id(n)
+        if key not in self._anc:
+            seen, stack = {}, list(self.preds(n))
+            while stack:
+                m = stack.pop()
+                if id(m) not in seen:
+                    seen[id(m)] = m
+                    stack.extend(self.preds(m))
+            self._anc[key] = seen
+        return self._anc[key]
+
+    def below(self, n, m) -> bool:
+        """True when ``m`` is an ancestor of ``n``."""
+        return id(m) in self.ancestors(n)
+
+    def root(self, n):
+        """The placeholder ``n`` is a plain view of, or None when it is computed."""
+        while n is not None and not _kind(n).startswith("PlaceHolder"):
+            ps = self.preds(n)
+            if _kind(n) not in _VIEWS or len(ps) != 1:
+                return None
+            n = ps[0]
+        return n
+
+    def scalar_ops(self, target, stop=None):
+        """The element-wise nodes with a scalar operand among the ancestors of ``target`` (and ``target``
+        itself), in graph order; with ``stop`` only those computed from ``stop``."""
+        cand = list(self.ancestors(target).values()) + [target]
+        out = [n for n in cand if getattr(n, "const", None) is not None and (stop is None or self.below(n, stop))]
+        return sorted(out, key=lambda n: self.pos[id(n)])
+
+
+def _score_scale(flow, exp_node) -> float:
+    """Product of the constant factors applied between the inputs and ``Exp``: ``s / c`` and ``s * c`` nodes
+    (softmax is invariant under the constant shifts, which are skipped)."""
+    scale = 1.0
+    for n in flow.scalar_ops(exp_node):
+        k, c = _kind(n), float(n.const)
+        if k == "Div":
+            if getattr(n, "const_on_left", False):
+                raise CodegenError("a constant divided by the scores is not an attention score scale")
+            scale /= c
+        elif k == "Mul":
+            scale *= c
+        elif k in ("Add", "Sub"):
+            continue
+        else:
+            raise CodegenError(f"unexpected scalar operation {k} before Exp")
+    return scale
+
+
+def _rms_eps(flow, rsqrt_node, k_extent) -> float:
+    """eps of ``rsqrt(mean(x^2) + eps)``: the scalar operations between the sum of squares and ``RSqrt`` are
+    composed into ``a * sum + b``; the form is an RMS norm over ``k_extent`` values when ``a * k_extent = 1``,
+    and then eps = ``b``."""
+    sums = [n for n in flow.ancestors(rsqrt_node).values() if _kind(n) == "ReduceSum"]
+    if len(sums) != 1:
+        raise CodegenError("RSqrt without exactly one sum of squares below it")
+    a, b = 1.0, 0.0
+    for n in flow.scalar_ops(rsqrt_node, stop=sums[0]):
+        k, c = _kind(n), float(n.const)
+        if k == "Div" and not getattr(n, "const_on_left", False):
+            a, b = a / c, b / c
+        elif k == "Mul":
+            a, b = a * c, b * c
+        elif k == "Add":
+            b += c
+        elif k == "Sub" and not getattr(n, "const_on_left", False):
+            b -= c
+        else:
+            raise CodegenError(f"unexpected scalar operation {k} inside an RMS norm")
+    if abs(a * k_extent - 1.0) > 1e-3:
+        raise CodegenError(f"the normalisation divides the sum of squares by {1.0 / a:g}, not by the row length {k_extent}")
+    return b
+
+
+def _split_factor(flow) -> int:
+    s = 1
+    for n in flow.of("SplitView"):
+        src = flow.preds(n)[0] if flow.preds(n) else None
+        shp, axis = _shape(n), getattr(n, "axis", None)
+        if src is not None and axis is not None and len(shp) == len(_shape(src)) + 1:
+            s = max(s, shp[int(axis)])      # the split axis is inserted in front of the axis it cuts
+        elif shp:
+            s = max(s, shp[0])
+    return s
+
+
+class _Axes:
+    """Which tensor axes a graph identifies with one another. Every placeholder axis gets a label; a matmul
+    merges the labels of the two axes it contracts, an element-wise node those of equal extents it lines up.
+    The resulting classes do not depend on how the search re-associated a product chain or which operands
+    it transposed, so the part an input plays can be read off them: ``x @ w`` contracts the LAST axis of x
+    with the FIRST axis of w however the plan writes it."""
+
+    def __init__(self, flow: _Flow):
+        self.flow, self.parent, self.labels, self.contractions = flow, {}, {}, []
+        for n in flow.nodes:
+            self.labels[id(n)] = self._visit(n)
+
+    def find(self, a):
+        while self.parent.setdefault(a, a) != a:
+            self.parent[a] = self.parent[self.parent[a]]
+            a = self.parent[a]
+        return a
+
+    def union(self, a, b):
+        ra, rb = self.find(a), self.find(b)
+        if ra != rb:
+            self.parent[max(ra, rb, key=str)] = min(ra, rb, key=str)
+
+    def _visit(self, n):
+        k, shp, ps = _kind(n), _shape(n), self.flow.preds(n)
+        if k.startswith("PlaceHolder"):
+            return [(n.name, i) for i in range(len(shp))]
+        ins = [self.labels[id(p)] for p in ps]
+        if k == "Matmul":
+            (la, lb) = ins
+            if len(la) == 1:      # a vector operand (a reduced matrix) is a single row or column
+                ar, ac = (n.name, "unit_a"), la[0]
+            else:
+                ar, ac = (la[-1], la[-2]) if getattr(n, "transpose_A", False) else (la[-2], la[-1])
+            if len(lb) == 1:
+                br, bc = lb[0], (n.name, "unit_b")
+            else:
+                br, bc = (lb[-1], lb[-2]) if getattr(n, "transpose_B", False) else (lb[-2], lb[-1])
+            self.union(ac, br)
+            self.contractions.append((n, ac))
+            return [(n.name, "b", i) for i in range(len(shp) - 2)] + [ar, bc]
+        if k == "SplitView":
+            axis = int(getattr(n, "axis", 0))
+            return ins[0][:axis] + [(n.name, "split")] + ins[0][axis:]
+        if k in ("ReduceSum", "ReduceMax", "ReduceMin"):
+            axis = int(getattr(n, "axis", len(ins[0]) - 1))
+            if len(shp) == len(ins[0]):          # keepdims
+                return ins[0][:axis] + [(n.name, "unit")] + ins[0][axis + 1:]
+            return ins[0][:axis] + ins[0][axis + 1:]
+        if len(ins) == 2 and len(ins[0]) == len(ins[1]):
+            sa, sb = _shape(ps[0]), _shape(ps[1])
+            for i, (x, y) in enumerate(zip(ins[0], ins[1])):
+                if sa[i] == sb[i] and sa[i] != 1:
+                    self.union(x, y)
+            return list(ins[0] if sa >= sb else ins[1])
+        if ins:
+            best = max(ins, key=len)
+            return list(best) if len(best) == len(shp) or not shp else list(best)[:len(shp)]
+        return [(n.name, i) for i in range(len(shp))]
+
+    def cls(self, node, axis):
+        labs = self.labels[id(node)]
+        return self.find(labs[axis])
+
+    def contracted(self, mm):
+        return next(self.find(c) for m, c in self.contractions if m is mm)
+
+
+def _leaves(flow, node):
+    """The placeholders ``node`` is computed from."""
+    if _kind(node).startswith("PlaceHolder"):
+        return [node]
+    seen = [p for p in flow.ancestors(node).values() if _kind(p).startswith("PlaceHolder")]
+    return sorted(seen, key=lambda n: flow.pos[id(n)])
+
+
+def _axis_in(axes, ph, cls):
+    """Position (counted from the end: -1 last, -2 second to last) of the axis of ``ph`` that lies in ``cls``."""
+    rank = len(_shape(ph))
+    for i in range(rank):
+        if axes.cls(ph, i) == cls:
+            return i - rank
+    return None
+
+
+def _plan_params(flow, dtype, roles: dict) -> tuple:
+    """Inputs = the placeholders in graph order under their own names (the order and the names the
+    reference's generated kernels use, python/cleave/runtime/reference.py:63-75), and the graph's output nodes
+    with their physical shapes."""
+    P = KernelParam
+    ins = [P(n.name, _dtype_of(n, dtype), _shape(n), "input") for n in flow.nodes if _kind(n).startswith("PlaceHolder")]
+    missing = set(roles.values()) - {p.name for p in ins}
+    if missing:
+        raise CodegenError(f"placeholders {sorted(missing)} are not in the graph")
+    outs = [P(n.name, _dtype_of(n, dtype), _shape(n), "output") for n in flow.of("OutputNode")]
+    return tuple(ins), tuple(outs)
+
+
 def recognise(obj) -> KernelSpec:
-    """Classify a scheduled plan by the op pattern of its flat graph and read the shapes off its
-    placeholders. Patterns (op class names of python/cleave/ir/ops): ``{Matmul}`` -> matmul;
-    ``{Matmul, Mul, ReduceSum, Div, RSqrt|Sqrt}`` -> rmsnorm_matmul; ``{Matmul x2, Silu, Mul}`` ->
-    swiglu; ``{Matmul x2, Exp, ReduceSum, Div}`` -> attention_decode (with ``RSqrt`` -> qknorm_attention,
-    without ``Exp`` -> matmul_matmul), with a third score matmul and an ``Add`` -> mla_decode;
-    ``{Matmul, ReduceSum}`` -> matmul_rowsum; ``{Matmul x3, Add}`` over four placeholders -> lora. Leading ``SplitView`` nodes carry the split factor. Tile shapes and
-    thread counts in the plan are hints scored for another architecture and are not used."""
-    if isinstance(obj, (list, tuple)):  # [partial, combine]: the partial carries the structure
+    """The kernel a scheduled plan asks for. ``obj`` is a reference ``Plan``, its ``TileDict`` (anything with
+    ``flat_graph``), a tiled graph, or a ``[partial, combine]`` pair, which becomes ONE fused kernel with the
+    pair's split factor. A lone graph with ``SplitView`` nodes is a split partial (``role = "partial"``: it
+    writes the per-split partial results the reference's two-stage form passes on), a lone graph that only
+    sums placeholders along a split axis is its combine (family ``split_combine``).
+
+    Families by op pattern: one ``Matmul`` -> matmul, with a sum of squares and ``RSqrt`` -> rmsnorm_matmul,
+    with a ``ReduceSum`` over the product's columns -> matmul_rowsum; two with ``Silu`` -> swiglu; two around
+    ``Exp`` -> attention_decode (``RSqrt`` below ``Exp`` -> qknorm_attention), two without -> matmul_matmul;
+    three around ``Exp`` -> mla_decode; three without -> lora. The search also emits re-associated and
+    transposed forms of a product chain (``q (k^T v)``, ``x @ rowsum(w)``, ``x (a b)``): they compute the same
+    operator and give the same kernel."""
+    fused = False
+    if isinstance(obj, (list, tuple)):
         if not obj:
             raise CodegenError("empty plan list")
-        return recognise(obj[0])
-    nodes = _nodes_of(obj)
-    kinds = [_kind(n) for n in nodes]
-    phs = [n for n, k in zip(nodes, kinds) if k.startswith("PlaceHolder")]
-    count = lambda k: sum(1 for x in kinds if x == k)  # noqa: E731
-    split = 1
-    for n, k in zip(nodes, kinds):
-        if k == "SplitView":
-            split = max(split, _shape(n)[0])
+        obj, fused = obj[0], True
+    flow = _Flow(obj)
+    phs = [n for n in flow.nodes if _kind(n).startswith("PlaceHolder")]
+    if not phs:
+        raise CodegenError("the plan has no placeholders")
+    dtype = _dtype_of(phs[0])
+    mms, exps = flow.of("Matmul"), flow.of("Exp")
+    split = _split_factor(flow)
     declared = getattr(obj, "split_factor", None)
     if declared:
         split = int(declared)
-    dtype = _dtype_of(phs[0]) if phs else "float16"
-    n_mm = count("Matmul")
-    shapes = [_shape(n) for n in phs]
-    if n_mm == 1 and "Exp" not in kinds:
-        (m, k), (k2, n) = shapes[0][-2:], shapes[1][-2:]
-        if k != k2:
-            raise CodegenError(f"matmul placeholders do not chain: {shapes}")
-        fam = "rmsnorm_matmul" if "ReduceSum" in kinds and ("RSqrt" in kinds or "Sqrt" in kinds) else "matmul"
-        if fam == "matmul" and "ReduceSum" in kinds:
-            return make_spec("matmul_rowsum", dtype, {"M": m, "N": n, "K": k}, split=split)
-        attrs = {}
-        if fam == "rmsnorm_matmul":
-            eps = [getattr(getattr(n, "op", None), "value", None) for n, kd in zip(nodes, kinds) if kd == "Add"]
-            attrs["eps"] = float(next((e for e in eps if e is not None), 0.0))
-        return make_spec(fam, dtype, {"M": m, "N": n, "K": k}, split=split, attrs=attrs)
-    if n_mm == 2 and "Silu" in kinds:
-        (m, k), (_, n) = shapes[0][-2:], shapes[1][-2:]
-        return make_spec("swiglu", dtype, {"M": m, "N": n, "K": k}, split=split)
-    if n_mm == 2 and len(shapes) == 3 and all(len(sh) >= 3 for sh in shapes):
-        (hq, sq, d), (hkv, skv, _) = shapes[0][-3:], shapes[1][-3:]
+    role = "main" if fused or split == 1 else "partial"
+    if not mms:
+        return _recognise_combine(flow, dtype, obj)
+    axes = _Axes(flow)
+    name = lambda n: n.name  # noqa: E731
+
+    def finish(family, dims, attrs, roles):
+        attrs = dict(attrs)
+        ins, outs = _plan_params(flow, dtype, roles)
+        default = default_params(family, dtype, dims, attrs)
+        if all(_ph(r) == roles[r] for r in roles):       # already under the library's own names
+            params = default if role == "main" else tuple(ins) + tuple(outs)
+        else:
+            attrs["bind"] = {r: roles[r] for r in sorted(roles)}
+            final = [p for p in default if p.role == "output"]
+            params = tuple(ins) + (tuple(final) if role == "main" else tuple(outs))
+        return KernelSpec(family, dtype, dict(dims), int(split), role, attrs, params)
+
+    def two_d(ph, what):
+        shp = _shape(ph)
+        if len(shp) < 2:
+            raise CodegenError(f"{what} {name(ph)} must be a matrix, got shape {shp}")
+        return shp[-2], shp[-1]
+
+    def left_right(mm, cands, what):
+        """Of two inputs joined by the contraction of ``mm``: (the one contracted on its last axis, the one
+        contracted on its second-to-last axis) - ``x`` and ``w`` of ``x @ w`` in whatever form it was written."""
+        c = axes.contracted(mm)
+        pos = {id(p): _axis_in(axes, p, c) for p in cands}
+        left = [p for p in cands if pos[id(p)] == -1]
+        right = [p for p in cands if pos[id(p)] == -2]
+        if len(left) != 1 or len(right) != 1:
+            raise CodegenError(f"{what}: the inputs are not laid out as (rows, contraction) @ (contraction, columns)")
+        return left[0], right[0]
+
+    if len(mms) == 1 and not exps:
+        mm = mms[0]
+        rs = flow.of("RSqrt", "Sqrt")
+        sums = flow.of("ReduceSum")
+        if rs:
+            stat = rs[0]
+            stat_in = _leaves(flow, stat)
+            if len(stat_in) != 1:
+                raise CodegenError("the norm statistics must come from one input")
+            x = stat_in[0]
+            rest = [p for p in phs if p is not x]
+            w = next((p for p in rest if _axis_in(axes, p, axes.contracted(mm)) == -2), None)
+            if w is None or _axis_in(axes, x, axes.contracted(mm)) != -1:
+                raise CodegenError("rms_norm(x) @ w: x must be (M, K) and w (K, N)")
+            (m, k), (_, n) = two_d(x, "x"), two_d(w, "w")
+            roles = {"x": name(x), "w": name(w)}
+            attrs = {"eps": _rms_eps(flow, stat, k)}
+            others = [p for p in rest if p is not w]
+            if others:
+                if len(others) > 1 or _shape(others[0])[-1] != k:
+                    raise CodegenError("unexpected extra inputs beside x, w and the norm weight")
+                attrs["gamma"] = True
+                roles["gamma"] = name(others[0])
+            return finish("rmsnorm_matmul", {"M": m, "N": n, "K": k}, attrs, roles)
+        if len(phs) != 2:
+            raise CodegenError(f"one product over {len(phs)} inputs")
+        x, w = left_right(mm, phs, "x @ w")
+        (m, k), (_, n) = two_d(x, "x"), two_d(w, "w")
+        roles = {"x": name(x), "w": name(w)}
+        if sums and role == "main":
+            # rowsum(x @ w) sums over w's columns, before the product (x @ rowsum(w)) or after it
+            s_ = sums[0]
+            src = flow.preds(s_)[0]
+            dropped = axes.find(axes.labels[id(src)][int(getattr(s_, "axis", len(_shape(src)) - 1))])
+            if dropped != axes.cls(w, len(_shape(w)) - 1) or len(sums) > 1:
+                raise CodegenError("a product followed by a sum that is not over the product's columns")
+            return finish("matmul_rowsum", {"M": m, "N": n, "K": k}, {}, roles)
+        return finish("matmul", {"M": m, "N": n, "K": k}, {}, roles)
+
+    if len(mms) == 2 and flow.of("Silu") and not exps:
+        silu = flow.of("Silu")[0]
+        gate = next((mm for mm in mms if flow.below(silu, mm)), None)
+        up = next((mm for mm in mms if mm is not gate), None)
+        if gate is None or up is None or len(phs) != 3:
+            raise CodegenError("silu(x @ w0) * (x @ w1): Silu must be applied to one of two products of three inputs")
+        gl, ul = _leaves(flow, gate), _leaves(flow, up)
+        shared = [p for p in gl if p in ul]
+        if len(shared) != 1 or len(gl) != 2 or len(ul) != 2:
+            raise CodegenError("swiglu: both products must read one shared input and one weight each")
+        x, w0 = left_right(gate, gl, "x @ w0")
+        x2, w1 = left_right(up, ul, "x @ w1")
+        if x is not shared[0] or x2 is not x:
+            raise CodegenError("swiglu: the shared input must be the left operand of both products")
+        (m, k), (_, n) = two_d(x, "x"), two_d(w0, "w0")
+        return finish("swiglu", {"M": m, "N": n, "K": k}, {}, {"x": name(x), "w0": name(w0), "w1": name(w1)})
+
+    if len(mms) == 2 and len(exps) == 1 and len(phs) == 3:
+        e = exps[0]
+        score = next((mm for mm in mms if flow.below(e, mm)), None)
+        value = next((mm for mm in mms if flow.below(mm, e)), None)
+        if score is None or value is None or score is value:
+            raise CodegenError("attention: Exp must sit between the score product and the value product")
+        qk = _leaves(flow, score)
+        v = next((p for p in phs if p not in qk), None)
+        if v is None or len(qk) != 2:
+            raise CodegenError("attention: q, k and v must be three inputs")
+        # k shares its sequence axis with v: the value product contracts the score columns with v's rows
+        c = axes.contracted(value)
+        k = next((p for p in qk if _axis_in(axes, p, c) is not None), None)
+        q = next((p for p in qk if p is not k), None)
+        if k is None or q is None or _axis_in(axes, v, c) != -2 or _axis_in(axes, k, c) != -2:
+            raise CodegenError("attention: k and v must be (kv heads, kv length, d)")
+        (hq, sq, d), (hkv, skv, _) = _shape(q)[-3:], _shape(k)[-3:]
         dims = {"HQ": hq, "HKV": hkv, "SQ": sq, "SKV": skv, "D": d}
-        if "Exp" not in kinds:
-            return make_spec("matmul_matmul", dtype, dims, split=split)
-        if "RSqrt" in kinds or "Sqrt" in kinds:
-            eps = [getattr(getattr(n, "op", None), "value", None) for n, kd in zip(nodes, kinds) if kd == "Add"]
-            return make_spec("qknorm_attention", dtype, dims, split=split,
-                             attrs={"eps": float(next((e for e in eps if e is not None), 0.0))})
-        return make_spec("attention_decode", dtype, dims, split=split)
-    if n_mm == 3 and "Exp" not in kinds and len(shapes) == 4:
-        (m, k), (_, n) = shapes[0][-2:], shapes[1][-2:]
-        r = min(s_[-1] for s_ in shapes)
-        return make_spec("lora", dtype, {"M": m, "N": n, "K": k, "R": r}, split=split)
-    if "Exp" in kinds and n_mm == 3 and len(shapes) == 4:
-        by_rank = sorted(shapes, key=lambda s: (s[-1], s[-2]))
-        (b, h, pe), (_, skv, _), (_, _, d) = by_rank[0], by_rank[1], by_rank[2]
-        h = min(s[-2] for s in shapes)
-        skv = max(s[-2] for s in shapes)
-        return make_spec("mla_decode", dtype, {"B": b, "H": h, "SKV": skv, "D": d, "PE": pe}, split=split)
-    raise CodegenError(f"no kernel family matches the plan's op pattern {sorted(set(kinds))}")
+        attrs = {"scale": _score_scale(flow, e)}
+        roles = {"q": name(q), "k": name(k), "v": name(v)}
+        rs = [r for r in flow.of("RSqrt", "Sqrt") if flow.below(e, r)]
+        if rs:
+            attrs["eps"] = _rms_eps(flow, rs[0], d)
+            return finish("qknorm_attention", dims, attrs, roles)
+        return finish("attention_decode", dims, attrs, roles)
+
+    if len(mms) == 2 and not exps and len(phs) == 3:
+        # (q k^T) v in either association: q and k are contracted on their last axes, k and v on their rows
+        pairs = {}
+        for mm in mms:
+            c = axes.contracted(mm)
+            pairs[id(mm)] = [(p, _axis_in(axes, p, c)) for p in phs if _axis_in(axes, p, c) is not None]
+        d_pair = next((pr for pr in pairs.values() if len(pr) == 2 and all(a == -1 for _, a in pr)), None)
+        s_pair = next((pr for pr in pairs.values() if len(pr) == 2 and all(a == -2 for _, a in pr)), None)
+        if d_pair is None or s_pair is None:
+            raise CodegenError("two products that are not (q k^T) v")
+        k = next((p for p, _ in d_pair if any(p is p2 for p2, _ in s_pair)), None)
+        q = next((p for p, _ in d_pair if p is not k), None)
+        v = next((p for p, _ in s_pair if p is not k), None)
+        if k is None or q is None or v is None:
+            raise CodegenError("(q k^T) v: k must take part in both products")
+        (hq, sq, d), (hkv, skv, _) = _shape(q)[-3:], _shape(k)[-3:]
+        return finish("matmul_matmul", {"HQ": hq, "HKV": hkv, "SQ": sq, "SKV": skv, "D": d}, {},
+                      {"q": name(q), "k": name(k), "v": name(v)})
+
+    if len(mms) == 3 and len(exps) == 1 and len(phs) == 4:
+        e = exps[0]
+        scores = [mm for mm in mms if flow.below(e, mm)]
+        value = next((mm for mm in mms if flow.below(mm, e)), None)
+        if len(scores) != 2 or value is None:
+            raise CodegenError("MLA decode: two score products below Exp and one value product above it")
+        cv = axes.contracted(value)
+        kv = next((p for p in phs if flow.below(value, p) and not flow.below(e, p)), None)
+        if kv is None:      # the latent cache feeds a score product too, so it IS below Exp: take the value operand
+            kv = next((p for p in _leaves(flow, value) if _axis_in(axes, p, cv) == -2 and
+                       any(p in _leaves(flow, mm) for mm in scores) and len(_shape(p)) >= 2 and
+                       _shape(p)[-1] == _shape(flow.of("OutputNode")[0])[-1]), None)
+        main = next((mm for mm in scores if kv in _leaves(flow, mm)), None)
+        rope = next((mm for mm in scores if mm is not main), None)
+        if kv is None or main is None or rope is None:
+            raise CodegenError("MLA decode: the latent cache must feed one score product and the value product")
+        q = next((p for p in _leaves(flow, main) if p is not kv), None)
+        rl = _leaves(flow, rope)
+        k_pe = next((p for p in rl if _axis_in(axes, p, cv) is not None), None)   # shares the kv-length axis
+        q_pe = next((p for p in rl if p is not k_pe), None)
+        if q is None or k_pe is None or q_pe is None:
+            raise CodegenError("MLA decode: q, q_pe and k_pe must be inputs")
+        b_, h, d = _shape(q)[-3:]
+        dims = {"B": b_, "H": h, "SKV": _shape(kv)[-2], "D": d, "PE": _shape(q_pe)[-1]}
+        return finish("mla_decode", dims, {"scale": _score_scale(flow, e)},
+                      {"q": name(q), "kv": name(kv), "q_pe": name(q_pe), "k_pe": name(k_pe)})
+
+    if len(mms) == 3 and not exps and len(phs) == 4:
+        # x @ w + (x @ a) @ b in any association: x is contracted (last axis) with the rows of both w and a,
+        # a's columns with b's rows; w and b end in the output's columns
+        cls_last = {id(p): axes.cls(p, len(_shape(p)) - 1) for p in phs}
+        cls_first = {id(p): axes.cls(p, len(_shape(p)) - 2) for p in phs}
+        x = next((p for p in phs if sum(1 for o in phs if o is not p and cls_first[id(o)] == cls_last[id(p)]) == 2), None)
+        if x is None:
+            raise CodegenError("x @ w + (x @ a) @ b: no input is contracted with two others")
+        wa = [o for o in phs if o is not x and cls_first[id(o)] == cls_last[id(x)]]
+        b = next((p for p in phs if p is not x and p not in wa), None)
+        a = next((p for p in wa if cls_last[id(p)] == cls_first[id(b)]), None) if b is not None else None
+        w = next((p for p in wa if p is not a), None)
+        if a is None or w is None or cls_last[id(w)] != cls_last[id(b)]:
+            raise CodegenError("x @ w + (x @ a) @ b: the low-rank pair does not line up with w")
+        (m, k), (_, n), (_, r) = two_d(x, "x"), two_d(w, "w"), two_d(a, "a")
+        return finish("lora", {"M": m, "N": n, "K": k, "R": r}, {},
+                      {"x": name(x), "w": name(w), "a": name(a), "b": name(b)})
+
+    kinds = sorted({_kind(n) for n in flow.nodes})
+    raise CodegenError(f"no kernel family matches the plan's op pattern {kinds}")
+
+
+def _recognise_combine(flow, dtype, obj) -> KernelSpec:
+    """The combine stage of a split pair: every placeholder carries a split axis that a ``ReduceSum`` removes;
+    an optional ``Div`` divides the first sum by the second, row by row (the split softmax denominator)."""
+    phs = [n for n in flow.nodes if _kind(n).startswith("PlaceHolder")]
+    sums = flow.of("ReduceSum")
+    if not sums or len(sums) != len(phs) or any(flow.root(flow.preds(s)[0]) is None for s in sums):
+        kinds = sorted({_kind(n) for n in flow.nodes})
+        raise CodegenError(f"no kernel family matches the plan's op pattern {kinds}")
+    extra = [n for n in flow.nodes if _kind(n) not in ("ReduceSum", "OutputNode", "Div") and not _kind(n).startswith("PlaceHolder")]
+    if extra or len(flow.of("Div")) > 1 or len(sums) > 2:
+        raise CodegenError("a combine stage with operations other than sums and one division")
+    axis = int(getattr(sums[0], "axis", 0))
+    split = _shape(flow.preds(sums[0])[0])[axis]
+    declared = getattr(obj, "split_factor", None)
+    attrs = {"axes": [int(getattr(s, "axis", 0)) for s in sums], "divide": bool(flow.of("Div"))}
+    ins, outs = _plan_params(flow, dtype, {})
+    return KernelSpec("split_combine", dtype, {}, int(declared or split), "combine", attrs, tuple(ins) + tuple(outs))

@@ -107,6 +107,9 @@ class B200Kernel:
 
         s = self.spec
         n_in = len(s.inputs)
+        if s.role != "main" and not hasattr(self, "_two_stage"):
+            raise CompileError(f"{s.family}: the {s.role} stage of a two-stage split has no kernel; pass the "
+                               "[partial, combine] pair to the code generator for one fused launch")
         if self.out_idx is None:
             if len(args) != n_in + len(s.outputs):
                 raise TypeError(f"{s.family}: expected {n_in} inputs and {len(s.outputs)} outputs, got {len(args)}")
@@ -118,32 +121,35 @@ class B200Kernel:
             outs = self._alloc_outputs([a for a, p in zip(ins, s.inputs) if p.role == "input"])
         split, mc = (s.split if s.split > 1 else 0), int(s.attrs.get("max_ctas", 0))
         f = s.family
+        if s.role != "main":
+            self._two_stage(ins, outs)
+            return None if self.out_idx is None else (outs[0] if len(outs) == 1 else outs)
+        a = s.by_role(ins)   # the library's name for every input, whatever the parameters are called
         if f == "matmul":
-            ops.matmul(ins[0], ins[1], split_k=split, out=outs[0].view(ins[0].shape[0], -1), max_ctas=mc)
+            ops.matmul(a["x"], a["w"], split_k=split, out=outs[0].view(a["x"].shape[0], -1), max_ctas=mc)
         elif f == "rmsnorm_matmul":
-            gamma = ins[1] if s.attrs.get("gamma") else None
-            ops.rmsnorm_matmul(ins[0], ins[-1], eps=float(s.attrs.get("eps", 0.0)), gamma=gamma, split_k=split,
-                               out=outs[0].view(ins[0].shape[0], -1), max_ctas=mc)
+            ops.rmsnorm_matmul(a["x"], a["w"], eps=float(s.attrs.get("eps", 0.0)), gamma=a.get("gamma"), split_k=split,
+                               out=outs[0].view(a["x"].shape[0], -1), max_ctas=mc)
         elif f == "swiglu":
-            ops.swiglu(ins[0], ins[1], ins[2], split_k=split, out=outs[0].view(ins[0].shape[0], -1), max_ctas=mc)
+            ops.swiglu(a["x"], a["w0"], a["w1"], split_k=split, out=outs[0].view(a["x"].shape[0], -1), max_ctas=mc)
         elif f == "attention_decode":
             # the same static attention family: few query rows stream KV through the split-KV decode kernel,
             # a query tile's worth of rows (the "prefill" shapes) runs QK^T and PV on tcgen05
             if s.dims["SQ"] >= 64 and s.dims["D"] in (64, 128) and split <= 1:
-                ops.attention_prefill(ins[0], ins[1], ins[2], s.attrs.get("scale"), out=outs[0])
+                ops.attention_prefill(a["q"], a["k"], a["v"], s.attrs.get("scale"), out=outs[0])
             else:
-                ops.attention_decode(ins[0], ins[1], ins[2], s.attrs.get("scale"), out=outs[0], max_ctas=mc)
+                ops.attention_decode(a["q"], a["k"], a["v"], s.attrs.get("scale"), out=outs[0], max_ctas=mc)
         elif f == "matmul_matmul":
-            ops.matmul_matmul(ins[0], ins[1], ins[2], out=outs[0])
+            ops.matmul_matmul(a["q"], a["k"], a["v"], out=outs[0])
         elif f == "qknorm_attention":
-            ops.qknorm_attention(ins[0], ins[1], ins[2], s.attrs.get("scale"), eps=float(s.attrs.get("eps", 0.0)),
+            ops.qknorm_attention(a["q"], a["k"], a["v"], s.attrs.get("scale"), eps=float(s.attrs.get("eps", 0.0)),
                                  out=outs[0])
         elif f == "matmul_rowsum":
-            ops.matmul_rowsum(ins[0], ins[1], out=outs[0])
+            ops.matmul_rowsum(a["x"], a["w"], out=outs[0])
         elif f == "lora":
-            ops.lora(ins[0], ins[1], ins[2], ins[3], out=outs[0])
+            ops.lora(a["x"], a["w"], a["a"], a["b"], out=outs[0])
         elif f == "mla_decode":
-            ops.mla_decode(ins[0], ins[1], ins[2], ins[3], float(s.attrs["scale"]), out=outs[0], max_ctas=mc)
+            ops.mla_decode(a["q"], a["kv"], a["q_pe"], a["k_pe"], float(s.attrs["scale"]), out=outs[0], max_ctas=mc)
         elif f == "gqa_paged_decode":
             last = ins[5] if s.dims["page_size"] != 1 else None
             ops.gqa_paged_decode(ins[0], ins[1], ins[2], ins[3], ins[4], last, float(ins[-1]), out=outs[0],
@@ -193,10 +199,9 @@ def build_inputs_and_reference(spec: KernelSpec, device="cuda", seed=None):
     g = torch.Generator(device="cpu").manual_seed(R.fingerprint_seed(spec) if seed is None else seed)
     d = spec.dims
     f_ = spec.family
-    inputs = {}
-    for p in spec.inputs:
+    inputs, by_role = {}, {}
+    for p, base in zip(spec.inputs, spec.input_roles()):
         shape = [int(x) for x in p.dims]
-        base = p.name.replace("PlaceHolder_", "")
         if base == "gamma":
             t = 1 + 0.1 * torch.randn(shape, generator=g)
         elif base in ("w", "w0", "w1") or (f_ == "lora" and base == "a"):
@@ -210,14 +215,13 @@ def build_inputs_and_reference(spec: KernelSpec, device="cuda", seed=None):
             t = torch.randn(shape, generator=g) / (d["SKV"] * d["D"]) ** 0.5
         else:
             t = torch.randn(shape, generator=g)
-        inputs[p.name] = t.to(dt).to(device)
-    v = lambda n: inputs[f"PlaceHolder_{n}"]  # noqa: E731
+        inputs[p.name] = by_role[base] = t.to(dt).to(device)
+    v = by_role.__getitem__
     f = spec.family
     if f == "matmul":
         ref = R.matmul(v("x"), v("w"))
     elif f == "rmsnorm_matmul":
-        ref = R.rmsnorm_matmul(v("x"), v("w"), float(spec.attrs.get("eps", 0.0)),
-                               v("gamma") if spec.attrs.get("gamma") else None)
+        ref = R.rmsnorm_matmul(v("x"), v("w"), float(spec.attrs.get("eps", 0.0)), by_role.get("gamma"))
     elif f == "swiglu":
         ref = R.swiglu(v("x"), v("w0"), v("w1"))
     elif f == "attention_decode":

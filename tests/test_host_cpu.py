@@ -41,64 +41,6 @@ def test_kernel_text_is_deterministic_and_round_trips():
     assert [p.name for p in a.params] == ["PlaceHolder_x", "PlaceHolder_w", "OutputNode"]
 
 
-class _Node:
-    def __init__(self, kind, shape=(), dtype="float16"):
-        self.op = None if kind in ("PlaceHolderNode", "OutputNode") else type(kind, (), {})()
-        self._kind, self._shape, self._dtype = kind, shape, dtype
-        if self.op is None:
-            self.__class__ = type(kind, (_Node,), {})
-
-    def get_shape(self, _):
-        return self._shape
-
-    def get_dtype(self, _):
-        return self._dtype
-
-
-def _plan(nodes, split=None):
-    return SimpleNamespace(tile=SimpleNamespace(flat_graph=SimpleNamespace(nodes=nodes)), split_factor=split)
-
-
-def test_plan_recognition_from_flat_graph_patterns():
-    """Node patterns as the reference's scheduler emits them for the split-K matmul partial
-    (python/cleave/lower/split.py, observed: PlaceHolder, SplitView, PlaceHolder, SplitView, Matmul, Output)."""
-    from cleave_b200.codegen import recognise
-
-    N = _Node
-    mm = _plan([N("PlaceHolderNode", (128, 4096)), N("SplitView", (4, 128, 1024)), N("PlaceHolderNode", (4096, 128)),
-                N("SplitView", (4, 1024, 128)), N("Matmul", (4, 128, 128)), N("OutputNode", (4, 128, 128))])
-    s = recognise(mm)
-    assert (s.family, s.split, s.dims) == ("matmul", 4, {"M": 128, "N": 128, "K": 4096})
-    assert recognise([mm, _plan([N("ReduceSum")])]).split == 4  # [partial, combine] -> one fused kernel
-    rms = _plan([N("PlaceHolderNode", (64, 4096)), N("PlaceHolderNode", (4096, 11008)), N("Mul"), N("ReduceSum"),
-                 N("Div"), N("RSqrt"), N("Matmul"), N("Mul"), N("OutputNode")])
-    assert recognise(rms).family == "rmsnorm_matmul"
-    sw = _plan([N("PlaceHolderNode", (8, 32)), N("PlaceHolderNode", (32, 16)), N("PlaceHolderNode", (32, 16)),
-                N("Matmul"), N("Matmul"), N("Silu"), N("Mul"), N("OutputNode")])
-    assert recognise(sw).family == "swiglu"
-    att = _plan([N("PlaceHolderNode", (256, 1, 128)), N("PlaceHolderNode", (64, 8192, 128)),
-                 N("PlaceHolderNode", (64, 8192, 128)), N("Matmul"), N("Div"), N("Add"), N("Exp"), N("ReduceSum"),
-                 N("Matmul"), N("Div"), N("OutputNode")])
-    a = recognise(att)
-    assert a.family == "attention_decode" and a.dims["HKV"] == 64 and a.dims["SKV"] == 8192
-    with pytest.raises(Exception):
-        recognise(_plan([N("PlaceHolderNode", (4, 4)), N("Exp"), N("OutputNode")]))
-    # the remaining demo operators
-    qkv = [N("PlaceHolderNode", (32, 4096, 64)), N("PlaceHolderNode", (32, 4096, 64)), N("PlaceHolderNode", (32, 4096, 64))]
-    mmm = recognise(_plan(qkv + [N("Matmul"), N("Matmul"), N("OutputNode")]))
-    assert mmm.family == "matmul_matmul" and mmm.dims == {"HQ": 32, "HKV": 32, "SQ": 4096, "SKV": 4096, "D": 64}
-    qkn = recognise(_plan(qkv + [N("Mul"), N("ReduceSum"), N("Div"), N("Add"), N("RSqrt"), N("Mul"), N("Matmul"), N("Div"),
-                                 N("Add"), N("Exp"), N("ReduceSum"), N("Matmul"), N("Div"), N("OutputNode")]))
-    assert qkn.family == "qknorm_attention"
-    rs = recognise(_plan([N("PlaceHolderNode", (4096, 64)), N("PlaceHolderNode", (64, 4096)), N("Matmul"), N("ReduceSum"),
-                          N("OutputNode")]))
-    assert rs.family == "matmul_rowsum" and rs.params[-1].dims == (4096, 1)
-    lo = recognise(_plan([N("PlaceHolderNode", (16, 4096)), N("PlaceHolderNode", (4096, 4096)),
-                          N("PlaceHolderNode", (4096, 16)), N("PlaceHolderNode", (16, 4096)), N("Matmul"), N("Matmul"),
-                          N("Matmul"), N("Add"), N("OutputNode")]))
-    assert lo.family == "lora" and lo.dims == {"M": 16, "N": 4096, "K": 4096, "R": 16}
-
-
 def test_trace_matches_the_demo_operators():
     import cleave_b200.lang as cl
     from cleave_b200.core.errors import SpecError

@@ -43,7 +43,22 @@ class GemmArgs(C.Structure):
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("m", C.c_int32), ("n", C.c_int32), ("k", C.c_int32), ("op", C.c_int32), ("dtype", C.c_int32),
         ("split_k", C.c_int32), ("max_ctas", C.c_int32), ("eps", C.c_float), ("addend", C.c_void_p), ("dependent_launch", C.c_int32),
-        ("x2", C.c_void_p), ("w2", C.c_void_p), ("k2", C.c_int32),
+        ("x2", C.c_void_p), ("w2", C.c_void_p), ("k2", C.c_int32), ("ldx", C.c_int32),
+    ]
+
+
+class SplitCombineArgs(C.Structure):
+    _fields_ = [
+        ("num", C.c_void_p), ("den", C.c_void_p), ("out", C.c_void_p), ("outer", C.c_int64), ("inner", C.c_int64),
+        ("splits", C.c_int32), ("den_inner", C.c_int32), ("dtype", C.c_int32),
+    ]
+
+
+class AttnUnnormaliseArgs(C.Structure):
+    _fields_ = [
+        ("out", C.c_void_p), ("lse", C.c_void_p), ("o_part", C.c_void_p), ("l_part", C.c_void_p),
+        ("kv_heads", C.c_int32), ("group", C.c_int32), ("splits", C.c_int32), ("head_dim", C.c_int32),
+        ("dtype", C.c_int32), ("shift", C.c_float),
     ]
 
 
@@ -151,6 +166,10 @@ def lib() -> C.CDLL:
         L.cb200_gemm_effective_split.argtypes = [C.POINTER(GemmArgs)]
         L.cb200_gemm.restype = C.c_int
         L.cb200_gemm.argtypes = [C.POINTER(GemmArgs), C.c_void_p]
+        L.cb200_split_combine.restype = C.c_int
+        L.cb200_split_combine.argtypes = [C.POINTER(SplitCombineArgs), C.c_void_p]
+        L.cb200_attn_unnormalise.restype = C.c_int
+        L.cb200_attn_unnormalise.argtypes = [C.POINTER(AttnUnnormaliseArgs), C.c_void_p]
         L.cb200_matmul_rowsum_workspace_bytes.restype = C.c_size_t
         L.cb200_matmul_rowsum_workspace_bytes.argtypes = [C.POINTER(MatmulRowsumArgs)]
         L.cb200_matmul_rowsum.restype = C.c_int

@@ -149,6 +149,37 @@ def make_spec(family: str, dtype: str, dims: dict, *, split: int = 1, attrs: dic
     return KernelSpec(family, dtype, dict(dims), int(split), "main", attrs, default_params(family, dtype, dims, attrs))
 
 
+def make_two_stage_specs(family: str, dtype: str, dims: dict, split: int, attrs: dict | None = None):
+    """``(partial, combine)`` specs of the two-stage form of a split (the reference's partial + combine kernel
+    pairs, python/cleave/codegen/split.py:13-123): the partial kernel writes one result per split, the combine
+    kernel sums them. Built for the split-K matmul and for split-KV decode attention with one query row."""
+    P = KernelParam
+    attrs = dict(attrs or {})
+    split = int(split)
+    ins = tuple(p for p in default_params(family, dtype, dims, attrs) if p.role != "output")
+    if family == "matmul":
+        m, n = dims["M"], dims["N"]
+        part_out = (P("OutputNode", dtype, (split, m, n), "output"),)
+        comb_in = (P("PlaceHolder_partial", dtype, (split, m, n), "input"),)
+        comb_attrs = {"axes": [0], "divide": False}
+        final = (P("OutputNode", dtype, (m, n), "output"),)
+    elif family == "attention_decode" and dims["SQ"] == 1:
+        hq, d = dims["HQ"], dims["D"]
+        scale = float(attrs.get("scale", d ** -0.5))
+        attrs.setdefault("scale", scale)
+        attrs.setdefault("shift", -50.0 * scale)
+        part_out = (P("OutputNode", dtype, (hq, split, 1, d), "output"), P("OutputNode_1", dtype, (hq, split, 1), "output"))
+        comb_in = (P("PlaceHolder_o_partial", dtype, (hq, split, 1, d), "input"),
+                   P("PlaceHolder_l_partial", dtype, (hq, split, 1), "input"))
+        comb_attrs = {"axes": [1, 1], "divide": True, "num": 0, "den": 1}
+        final = (P("OutputNode", dtype, (hq, 1, d), "output"),)
+    else:
+        raise CodegenError(f"no two-stage form of {family} {dims}")
+    partial = KernelSpec(family, dtype, dict(dims), split, "partial", attrs, ins + part_out)
+    combine = KernelSpec("split_combine", dtype, {}, split, "combine", comb_attrs, comb_in + final)
+    return partial, combine
+
+
 _HEADER = ("# cleave_b200 kernel spec: selects and parameterises a hand-written sm_100a kernel.\n"
            "# Loaded by cleave_b200.runtime.compile._load_main_kernel_from_code; no code is generated.\n"
            "import json\n\nfrom cleave_b200.codegen import KernelSpec\n\n")
@@ -256,23 +287,30 @@ class _Flow:
         return sorted(out, key=lambda n: self.pos[id(n)])
 
 
-def _score_scale(flow, exp_node) -> float:
-    """Product of the constant factors applied between the inputs and ``Exp``: ``s / c`` and ``s * c`` nodes
-    (softmax is invariant under the constant shifts, which are skipped)."""
-    scale = 1.0
+def _score_affine(flow, exp_node):
+    """``(scale, shift)`` of the scalar operations between the score product and ``Exp``, composed into
+    ``exp(scale * s + shift)``. The fused kernels use the scale only (softmax does not depend on a constant
+    shift); the two-stage partial kernels reproduce the shift, which is part of what they emit."""
+    a, b = 1.0, 0.0
     for n in flow.scalar_ops(exp_node):
         k, c = _kind(n), float(n.const)
         if k == "Div":
             if getattr(n, "const_on_left", False):
                 raise CodegenError("a constant divided by the scores is not an attention score scale")
-            scale /= c
+            a, b = a / c, b / c
         elif k == "Mul":
-            scale *= c
-        elif k in ("Add", "Sub"):
-            continue
+            a, b = a * c, b * c
+        elif k == "Add":
+            b += c
+        elif k == "Sub" and not getattr(n, "const_on_left", False):
+            b -= c
         else:
             raise CodegenError(f"unexpected scalar operation {k} before Exp")
-    return scale
+    return a, b
+
+
+def _score_scale(flow, exp_node) -> float:
+    return _score_affine(flow, exp_node)[0]
 
 
 def _rms_eps(flow, rsqrt_node, k_extent) -> float:
@@ -547,7 +585,10 @@ def recognise(obj) -> KernelSpec:
             raise CodegenError("attention: k and v must be (kv heads, kv length, d)")
         (hq, sq, d), (hkv, skv, _) = _shape(q)[-3:], _shape(k)[-3:]
         dims = {"HQ": hq, "HKV": hkv, "SQ": sq, "SKV": skv, "D": d}
-        attrs = {"scale": _score_scale(flow, e)}
+        scale, shift = _score_affine(flow, e)
+        attrs = {"scale": scale}
+        if role == "partial":
+            attrs["shift"] = shift
         roles = {"q": name(q), "k": name(k), "v": name(v)}
         rs = [r for r in flow.of("RSqrt", "Sqrt") if flow.below(e, r)]
         if rs:
@@ -637,6 +678,11 @@ def _recognise_combine(flow, dtype, obj) -> KernelSpec:
     axis = int(getattr(sums[0], "axis", 0))
     split = _shape(flow.preds(sums[0])[0])[axis]
     declared = getattr(obj, "split_factor", None)
-    attrs = {"axes": [int(getattr(s, "axis", 0)) for s in sums], "divide": bool(flow.of("Div"))}
+    axis_of = {id(flow.root(flow.preds(s)[0])): int(getattr(s, "axis", 0)) for s in sums}
+    attrs = {"axes": [axis_of[id(p)] for p in phs], "divide": bool(flow.of("Div"))}
+    if attrs["divide"]:      # which input is divided by which
+        num, den = (flow.root(flow.preds(x)[0]) for x in flow.preds(flow.of("Div")[0]))
+        order = [id(p) for p in phs]
+        attrs["num"], attrs["den"] = order.index(id(num)), order.index(id(den))
     ins, outs = _plan_params(flow, dtype, {})
     return KernelSpec("split_combine", dtype, {}, int(declared or split), "combine", attrs, tuple(ins) + tuple(outs))

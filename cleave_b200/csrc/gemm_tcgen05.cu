@@ -144,6 +144,85 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
   const long long x0 = CLUSTER ? static_cast<long long>(blockIdx.x) : static_cast<long long>(blockIdx.x) * C / G;
   const long long x1 = CLUSTER ? x0 + 1 : static_cast<long long>(blockIdx.x + 1) * C / G;
 
+  // Split-K inside a cluster, second half: once every CTA of the cluster has parked its accumulator
+  // (first cluster barrier), ALL warps of the CTA - the producer, the MMA issuer and the statistics warps
+  // are idle by then - take part in the reduce through distributed shared memory: it is bound by the
+  // latency of remote loads, so the number of loads in flight is what sets its duration.
+  constexpr int kReduceWarps = Plan::kThreads / 32;
+  auto cluster_reduce = [&](int slot_in) {
+    if constexpr (CLUSTER) {
+      // epilogue warps pass 0..3; the other warps take the remaining slots
+      const int slot = slot_in;
+      const int tile = static_cast<int>(x0 / S);
+      const int tm = tile / p.tiles_n, tn = tile - tm * p.tiles_n;
+      const int rows_live = min(kBM, p.M - tm * kBM);
+      const float inv_k = 1.f / static_cast<float>(p.K);
+      T* yout = reinterpret_cast<T*>(p.y);
+      float* stg = reinterpret_cast<float*>(stages);
+      // CTA `rank` owns rows [r_lo, r_hi). A warp reads 512 contiguous bytes of a peer per load:
+      // four rows of one column group, lane = (row, 16-byte piece); peers are added in rank order.
+      const int rank = static_cast<int>(cluster_ctarank());
+      constexpr int kGroups = Plan::kTileN / 32;
+      const int per = ceil_div(rows_live, S);
+      const int r_lo = min(rank * per, rows_live), r_hi = min(r_lo + per, rows_live);
+      const int quads = (r_hi - r_lo + 3) >> 2, n_items = quads * kGroups;
+      const uint32_t stg_u32 = smem_u32(stg);
+      for (int wi = slot; wi < n_items; wi += kReduceWarps) {
+        const int g = wi % kGroups, r = r_lo + (wi / kGroups) * 4 + (lane >> 3);
+        const int rc = min(r, r_hi - 1);  // clamped for the loads; rows past the end are not stored
+        const uint32_t off = ((static_cast<uint32_t>(g) * kBM + rc) * 32) * 4 + (lane & 7) * 16;
+        float v[4] = {0.f, 0.f, 0.f, 0.f}, up[4] = {0.f, 0.f, 0.f, 0.f}, rs_all = 0.f;
+        for (int q0 = 0; q0 < S; q0 += 4) {  // four peers' loads in flight
+          float4 a[4], bq[4];
+          float rq[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            a[u] = bq[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            rq[u] = 0.f;
+            if (q0 + u < S) {
+              const uint32_t base = dsmem_addr(stg_u32, q0 + u);
+              a[u] = dsmem_ld_v4(base + off);
+              if constexpr (MODE == 2) bq[u] = dsmem_ld_v4(base + off + kGroups * kBM * 32 * 4);
+              if constexpr (MODE == 1) rq[u] = dsmem_ld_f32(base + (kBM * kUmmaN + rc) * 4);
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            v[0] += a[u].x; v[1] += a[u].y; v[2] += a[u].z; v[3] += a[u].w;
+            if constexpr (MODE == 2) { up[0] += bq[u].x; up[1] += bq[u].y; up[2] += bq[u].z; up[3] += bq[u].w; }
+            rs_all += rq[u];
+          }
+        }
+        const int gcol = tn * Plan::kTileN + g * 32 + (((lane & 7) ^ (rc & 7)) << 2);  // undo the swizzle
+        if (r < r_hi && gcol < p.N) {
+          float o[4];
+          if constexpr (MODE == 1) {
+            const float sc = rsqrtf(rs_all * inv_k + p.eps);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) o[j] = v[j] * sc;
+          } else if constexpr (MODE == 2) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) o[j] = v[j] / (1.f + __expf(-v[j])) * up[j];
+          } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) o[j] = v[j];
+            if (p.addend) {
+              const uint2 u = *reinterpret_cast<const uint2*>(reinterpret_cast<const T*>(p.addend) +
+                                                              static_cast<size_t>(tm * kBM + r) * p.N + gcol);
+              const T* e = reinterpret_cast<const T*>(&u);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) o[j] += static_cast<float>(e[j]);
+            }
+          }
+          uint2 pk;
+          pk.x = pack2<T>(o[0], o[1]);
+          pk.y = pack2<T>(o[2], o[3]);
+          *reinterpret_cast<uint2*>(yout + static_cast<size_t>(tm * kBM + r) * p.N + gcol) = pk;
+        }
+      }
+    }
+  };
+
   if (warp == 0) {
     // ================================================================ TMA producer
     int stage = 0, phase = 0;
@@ -413,70 +492,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         }
         if constexpr (MODE == 1) stg[kBM * kUmmaN + row] = rs;
         cluster_sync();
-        {
-          // CTA `rank` owns rows [r_lo, r_hi). A warp reads 512 contiguous bytes of a peer per load:
-          // four rows of one column group, lane = (row, 16-byte piece); peers are added in rank order.
-          const int rank = static_cast<int>(cluster_ctarank());
-          constexpr int kGroups = Plan::kTileN / 32;
-          const int per = ceil_div(rows_live, S);
-          const int r_lo = min(rank * per, rows_live), r_hi = min(r_lo + per, rows_live);
-          const int quads = (r_hi - r_lo + 3) >> 2, n_items = quads * kGroups;
-          const uint32_t stg_u32 = smem_u32(stg);
-          const int ewarp = etid >> 5;
-          for (int wi = ewarp; wi < n_items; wi += 4) {
-            const int g = wi % kGroups, r = r_lo + (wi / kGroups) * 4 + (lane >> 3);
-            const int rc = min(r, r_hi - 1);  // clamped for the loads; rows past the end are not stored
-            const uint32_t off = ((static_cast<uint32_t>(g) * kBM + rc) * 32) * 4 + (lane & 7) * 16;
-            float v[4] = {0.f, 0.f, 0.f, 0.f}, up[4] = {0.f, 0.f, 0.f, 0.f}, rs_all = 0.f;
-            for (int q0 = 0; q0 < S; q0 += 4) {  // four peers' loads in flight
-              float4 a[4], bq[4];
-              float rq[4];
-#pragma unroll
-              for (int u = 0; u < 4; ++u) {
-                a[u] = bq[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-                rq[u] = 0.f;
-                if (q0 + u < S) {
-                  const uint32_t base = dsmem_addr(stg_u32, q0 + u);
-                  a[u] = dsmem_ld_v4(base + off);
-                  if constexpr (MODE == 2) bq[u] = dsmem_ld_v4(base + off + kGroups * kBM * 32 * 4);
-                  if constexpr (MODE == 1) rq[u] = dsmem_ld_f32(base + (kBM * kUmmaN + rc) * 4);
-                }
-              }
-#pragma unroll
-              for (int u = 0; u < 4; ++u) {
-                v[0] += a[u].x; v[1] += a[u].y; v[2] += a[u].z; v[3] += a[u].w;
-                if constexpr (MODE == 2) { up[0] += bq[u].x; up[1] += bq[u].y; up[2] += bq[u].z; up[3] += bq[u].w; }
-                rs_all += rq[u];
-              }
-            }
-            const int gcol = tn * Plan::kTileN + g * 32 + (((lane & 7) ^ (rc & 7)) << 2);  // undo the swizzle
-            if (r < r_hi && gcol < p.N) {
-              float o[4];
-              if constexpr (MODE == 1) {
-                const float sc = rsqrtf(rs_all * inv_k + p.eps);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) o[j] = v[j] * sc;
-              } else if constexpr (MODE == 2) {
-#pragma unroll
-                for (int j = 0; j < 4; ++j) o[j] = v[j] / (1.f + __expf(-v[j])) * up[j];
-              } else {
-#pragma unroll
-                for (int j = 0; j < 4; ++j) o[j] = v[j];
-                if (p.addend) {
-                  const uint2 u = *reinterpret_cast<const uint2*>(reinterpret_cast<const T*>(p.addend) +
-                                                                  static_cast<size_t>(tm * kBM + r) * p.N + gcol);
-                  const T* e = reinterpret_cast<const T*>(&u);
-#pragma unroll
-                  for (int j = 0; j < 4; ++j) o[j] += static_cast<float>(e[j]);
-                }
-              }
-              uint2 pk;
-              pk.x = pack2<T>(o[0], o[1]);
-              pk.y = pack2<T>(o[2], o[3]);
-              *reinterpret_cast<uint2*>(yout + static_cast<size_t>(tm * kBM + r) * p.N + gcol) = pk;
-            }
-          }
-        }
+        cluster_reduce(warp - 2);
         cluster_sync();  // nobody leaves while a peer still reads its shared memory
       } else {
         // Partial layout: [column group of 32][row][32 floats], so that a warp (32 consecutive
@@ -632,6 +648,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     // the epilogue warps met the cluster twice inside their branch; everyone else does so here
     if (!(warp >= 2 && warp < 6)) {
       cluster_sync();
+      if (p.pdl >= 2) pdl_wait();  // the reduce reads the addend and writes Y: the preceding kernel must be done
+      cluster_reduce(warp < 2 ? 4 + warp : warp);  // slots 4, 5 and 6 .. 13
       cluster_sync();
     }
   }
@@ -678,6 +696,8 @@ int plan_gemm(const cb200_gemm_args* a, GemmSetup* s, bool need_maps) {
   const bool ext = a->k2 > 0;
   if (ext && (a->op != CB200_GEMM_MATMUL || a->k2 % 8)) return CB200_ERR_UNSUPPORTED;
   if (a->k2 < 0 || (a->dependent_launch == 3 && !ext)) return CB200_ERR_BAD_ARG;
+  if (a->ldx != 0 && (a->ldx < a->k || a->ldx % 8)) return CB200_ERR_BAD_ARG;
+  if (a->ldx != 0 && a->op != CB200_GEMM_MATMUL) return CB200_ERR_UNSUPPORTED;
   const int sms = sm_count();
   if (sms <= 0) return CB200_ERR_CUDA;
   int grid_max = sms;
@@ -807,7 +827,7 @@ int plan_gemm(const cb200_gemm_args* a, GemmSetup* s, bool need_maps) {
   const CUtensorMapDataType dt = a->dtype == CB200_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   {
     uint64_t dims[2] = {static_cast<uint64_t>(a->k), static_cast<uint64_t>(a->m)};
-    uint64_t strides[1] = {static_cast<uint64_t>(a->k) * 2};
+    uint64_t strides[1] = {static_cast<uint64_t>(a->ldx ? a->ldx : a->k) * 2};  // a K slice of a wider X keeps X's row pitch
     uint32_t box[2] = {kBK, static_cast<uint32_t>(p.a_rows)};
     if (!encode_tensor_map(&s->tm_a, dt, 2, const_cast<void*>(a->x), dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
       return CB200_ERR_CUDA;

@@ -347,7 +347,14 @@ def check_static_scratch() -> None:
 
 def _gemm(op, x, w, w1=None, gamma=None, eps=0.0, split_k=0, out=None, max_ctas=0, addend=None, x2=None, w2=None,
           dependent_launch=1):
-    x, w = _cuda(x, "x"), _cuda(w, "w")
+    if not x.is_cuda or not w.is_cuda:
+        raise ValueError("x and w must be CUDA tensors (there is no CPU path)")
+    ldx = 0
+    if op == _lib.GEMM_MATMUL and x.dim() == 2 and not x.is_contiguous() and x.stride(1) == 1:
+        ldx = x.stride(0)   # a K slice of a wider matrix: the kernel reads it in place with X's row pitch
+    else:
+        x = _cuda(x, "x")
+    w = _cuda(w, "w")
     m, k = x.shape
     k2, n = w.shape
     if k2 != k or w.dtype != x.dtype:
@@ -365,6 +372,7 @@ def _gemm(op, x, w, w1=None, gamma=None, eps=0.0, split_k=0, out=None, max_ctas=
     a.m, a.n, a.k, a.op, a.dtype = m, n, k, op, _dtype_code(x)
     a.split_k, a.max_ctas, a.eps = int(split_k), int(max_ctas), float(eps)
     a.dependent_launch = int(dependent_launch)
+    a.ldx = int(ldx)
     if addend is not None:
         if tuple(_cuda(addend, "addend").shape) != (m, n) or addend.dtype != x.dtype:
             raise ValueError("addend must be (M, N) of x's dtype")
@@ -485,3 +493,80 @@ def mla_paged_prefill(q_nope, q_pe, ckv_cache, kpe_cache, qo_indptr, kv_indptr, 
     out = _mla(q_nope, q_pe, ckv_cache, kpe_cache, sm_scale, kv_indptr=start, kv_indices=_cuda(kv_indices, "kv_indices"),
                out=out, lse=lse, impl="mma_sync", kv_start=start, kv_lens=seen.contiguous())
     return out, lse
+
+
+# ---------------------------------------------------------------------------- two-stage split (compatibility)
+def split_combine(num, den=None, *, axis, out=None):
+    """The combine stage of a split pair (reference kernels: tests/graph/handwritten/expected_kernels/
+    matmul_splitk_combine.py, mha_split_combine.py): ``out = sum(num, axis)`` in fp32, divided row by row by
+    ``sum(den, axis)`` when ``den`` is given (``den`` has ``num``'s leading axes up to and including ``axis``
+    and then either nothing, unit axes, or ``num``'s trailing axes)."""
+    num = _cuda(num, "num")
+    axis = axis % num.dim()
+    outer = int(torch.tensor(num.shape[:axis]).prod()) if axis else 1
+    inner = int(torch.tensor(num.shape[axis + 1:]).prod()) if axis + 1 < num.dim() else 1
+    splits = num.shape[axis]
+    if out is None:
+        out = torch.empty(tuple(num.shape[:axis]) + tuple(num.shape[axis + 1:]), dtype=num.dtype, device=num.device)
+    if out.numel() != outer * inner or out.dtype != num.dtype or not out.is_contiguous():
+        raise ValueError("out must hold the reduced tensor, contiguous, in num's dtype")
+    a = _lib.SplitCombineArgs()
+    a.num, a.out, a.outer, a.inner, a.splits, a.dtype = num.data_ptr(), out.data_ptr(), outer, inner, splits, _dtype_code(num)
+    if den is not None:
+        den = _cuda(den, "den")
+        if den.dtype != num.dtype or den.numel() not in (outer * splits, outer * splits * inner):
+            raise ValueError("den must be (outer, splits) or (outer, splits, inner) in num's dtype")
+        a.den, a.den_inner = den.data_ptr(), 1 if den.numel() == outer * splits else inner
+    _lib.check(_lib.lib().cb200_split_combine(C.byref(a), _stream()))
+    return out
+
+
+def matmul_split_partial(x, w, split, *, out=None):
+    """The partial stage of a split-K matmul (reference kernel: tests/graph/handwritten/expected_kernels/
+    matmul_splitk_partial.py): ``out[s] = x[:, s K/S : (s+1) K/S] @ w[s K/S : (s+1) K/S, :]`` for every split,
+    (S, M, N) in the storage dtype. One tcgen05 GEMM launch per split, reading the K slices in place."""
+    x, w = _cuda(x, "x"), _cuda(w, "w")
+    m, k = x.shape
+    n = w.shape[1]
+    if k % split or (k // split) % 8:
+        raise ValueError(f"K = {k} does not cut into {split} slices of a multiple of 8 columns")
+    kc = k // split
+    if out is None:
+        out = torch.empty((split, m, n), dtype=x.dtype, device=x.device)
+    flat = out.view(split, m, n)
+    for s in range(split):
+        _gemm(_lib.GEMM_MATMUL, x[:, s * kc:(s + 1) * kc], w[s * kc:(s + 1) * kc], out=flat[s], split_k=1, dependent_launch=0)
+    return out
+
+
+def attention_split_partial(q, k, v, split, sm_scale=None, *, shift=None, o_part=None, l_part=None):
+    """The partial stage of a split-KV decode (reference kernels: tests/graph/handwritten/expected_kernels/
+    {gqa,mha,mqa}_split_partial.py): for every split s of the KV axis ``o_part[h, s] = sum_j e_j v_j`` and
+    ``l_part[h, s] = sum_j e_j`` with ``e_j = exp(q_h . k_j * scale + shift)`` over the split's tokens
+    (``shift`` defaults to the demos' -50 * scale). q (HQ, 1, D), k / v (HKV, SKV, D). The decode kernel runs
+    once over the cache viewed as HKV * S requests; a second small kernel rescales its normalised results."""
+    q, k, v = _cuda(q, "q"), _cuda(k, "k"), _cuda(v, "v")
+    hq, sq, d = q.shape
+    hkv, skv, _ = k.shape
+    if sq != 1:
+        raise ValueError("the two-stage partial is built for decode (one query row per head)")
+    if skv % split:
+        raise ValueError(f"KV length {skv} does not cut into {split} equal splits")
+    g = hq // hkv
+    scale = float(d) ** -0.5 if sm_scale is None else float(sm_scale)
+    shift = -50.0 * scale if shift is None else float(shift)
+    # query head (hkv, j) attends every split of its kv head: one copy of its row per split
+    q_rep = q.view(hkv, 1, g, 1, d).expand(hkv, split, g, 1, d).reshape(hkv * split * g, 1, d).contiguous()
+    k_view, v_view = k.view(hkv * split, skv // split, d), v.view(hkv * split, skv // split, d)
+    out = torch.empty_like(q_rep)
+    lse = torch.empty((hkv * split * g, 1), dtype=torch.float32, device=q.device)
+    attention_decode(q_rep, k_view, v_view, scale, out=out, lse=lse)
+    if o_part is None:
+        o_part = torch.empty((hq, split, d), dtype=q.dtype, device=q.device)
+    if l_part is None:
+        l_part = torch.empty((hq, split), dtype=q.dtype, device=q.device)
+    a = _lib.AttnUnnormaliseArgs()
+    a.out, a.lse, a.o_part, a.l_part = out.data_ptr(), lse.data_ptr(), o_part.data_ptr(), l_part.data_ptr()
+    a.kv_heads, a.group, a.splits, a.head_dim, a.dtype, a.shift = hkv, g, split, d, _dtype_code(q), shift
+    _lib.check(_lib.lib().cb200_attn_unnormalise(C.byref(a), _stream()))
+    return o_part, l_part

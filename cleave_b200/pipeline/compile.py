@@ -46,7 +46,9 @@ def build(planset, cfg, progress=None) -> Report:
     gen = B200CodeGen()
     runs = _evaluate.run_candidates(
         plans, build_fn=lambda plan: gen.gen(plan.spec),
-        reference_fn=(lambda d: publish_reference(d, plans[0].spec)[0]) if plans else None,
+        # fused candidates compute the same function and share one published reference; partial and combine
+        # stages compute different things and are each checked against their own spec
+        reference_fn=(lambda d: publish_reference(d, plans[0].spec)[0]) if plans and all(p.role == "main" for p in plans) else None,
         pool=cfg.pool, max_parallel=cfg.max_parallel, timeout_s=cfg.timeout_s, tolerance=cfg.tolerance,
         benchmark=BenchOptions(cfg.warmup, cfg.iters), labels=[p.label for p in plans], progress=progress)
     results = [Result(p, r, BuiltKernel.from_plan(p, r.code) if r.code else None) for p, r in zip(plans, runs)]
@@ -54,11 +56,12 @@ def build(planset, cfg, progress=None) -> Report:
 
 
 def compile(fn, shapes=None, dtype=None, *, split=None, preset="default", eval=None, cache_kernels=True,  # noqa: A001,A002
-            progress=None, **attrs):
+            progress=None, two_stage=False, **attrs):
     """Compile an operator for fixed shapes and return the fastest validated :class:`Kernel`; its
     ``report`` holds every candidate. ``fn`` is a ``@cleave_b200.jit`` function, a traced
     ``Program``, or the name of a paged operator (``"gqa_paged_decode"``, ``"mla_paged_decode"``; these
-    go to :func:`cleave_b200.pipeline.dynamic.compile_dynamic`)."""
+    go to :func:`cleave_b200.pipeline.dynamic.compile_dynamic`). ``two_stage`` also schedules the reference's
+    partial + combine kernel pairs (variant ``split-k=N/two-stage``) beside the fused split kernels."""
     if isinstance(fn, str):
         from .dynamic import compile_dynamic
 
@@ -72,7 +75,7 @@ def compile(fn, shapes=None, dtype=None, *, split=None, preset="default", eval=N
     splits = program.split if program.split else (DEFAULT_SPLITS if split is None else ())
     if split is False:
         splits = ()
-    path = _cache_dir(program, cfg, splits)
+    path = _cache_dir(program, cfg, tuple(splits) + (("two-stage",) if two_stage else ()))
     if cache_kernels and os.path.isfile(os.path.join(path, "kernel.json")):
         from .kernel import load
 
@@ -80,7 +83,7 @@ def compile(fn, shapes=None, dtype=None, *, split=None, preset="default", eval=N
         kernel.meta["cache_hit"] = True
         return kernel
     t0 = time.perf_counter()
-    planset = _plans.schedule(program, splits)
+    planset = _plans.schedule(program, splits, two_stage=two_stage)
     report = build(planset, cfg, progress)
     report.timings["schedule"] = 0.0
     report.timings["total"] = time.perf_counter() - t0

@@ -92,8 +92,9 @@ class Report(Sequence):
         return [r for r in self.results if r.ok and r.latency_ms is not None]
 
     def variants(self) -> dict:
-        """Best latency per variant: solo = best main; split-k=N = best main (fused, one launch)
-        or, where a plan set holds them, best partial + best combine."""
+        """Best latency per variant: solo = best main; split-k=N = best main (the fused kernel, one launch);
+        split-k=N/two-stage = best partial + best combine (the reference's pairing rule,
+        python/cleave/pipeline/report.py:123-136)."""
         best = {}
         for r in self.timed:
             key = (r.variant, r.role)
@@ -146,17 +147,11 @@ class Report(Sequence):
 
 
 def _make_kernel(win: VariantResult, report: Report):
-    from .kernel import Kernel, Param, Stage
+    from .kernel import Kernel, stages_for
 
     program = report.program
-    stages = []
-    for r in win.members:
-        spec = r.plan.spec
-        bind = {name: i for i, name in enumerate(r.plan.inputs)}
-        params = [Param(p.name, "input", bind[p.name], tuple(p.dims)) for p in spec.inputs]
-        n_out = len(spec.outputs)
-        stages.append(Stage(r.role, r.source, list(range(-n_out, 0)), params, r.label, r.latency_us, r.kernel))
+    stages, problem = stages_for([(r.plan, r.run, r.kernel) for r in win.members], program)
     return Kernel(stages, name=program.name, input_names=program.input_names, input_shapes=program.input_shapes,
                   output_shapes=program.output_shapes, variant=win.variant,
                   label=" + ".join(m.label for m in win.members), latency_us=win.latency_us, report=report,
-                  plans=[m.plan for m in win.members])
+                  plans=[m.plan for m in win.members], unrunnable=problem)

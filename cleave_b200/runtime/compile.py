@@ -102,14 +102,38 @@ class B200Kernel:
         return [torch.empty([bound[d] if isinstance(d, str) else int(d) for d in p.dims],
                             dtype=torch_dtype(p.dtype), device=device) for p in self.spec.outputs]
 
+    def _two_stage(self, ins, outs):
+        """One stage of the two-stage form of a split (the reference's partial / combine kernels)."""
+        from .. import ops
+
+        s = self.spec
+        if s.family == "split_combine":
+            axes = s.attrs["axes"]
+            if s.attrs.get("divide"):
+                num, den = ins[s.attrs["num"]], ins[s.attrs["den"]]
+                ops.split_combine(num, den, axis=axes[s.attrs["num"]], out=outs[0])
+            else:
+                ops.split_combine(ins[0], axis=axes[0], out=outs[0])
+            return
+        a = s.by_role(ins)
+        if s.family == "matmul":
+            ops.matmul_split_partial(a["x"], a["w"], s.split, out=outs[0])
+        elif s.family == "attention_decode" and s.dims["SQ"] == 1:
+            d, hq = s.dims["D"], s.dims["HQ"]
+            # the two outputs in the plan's own order: the weighted values (D per row) and the weight sums
+            o_out = next(o for o in outs if o.numel() == hq * s.split * d)
+            l_out = next(o for o in outs if o.numel() == hq * s.split)
+            ops.attention_split_partial(a["q"], a["k"], a["v"], s.split, s.attrs.get("scale"), shift=s.attrs.get("shift"),
+                                        o_part=o_out.view(hq, s.split, d), l_part=l_out.view(hq, s.split))
+        else:
+            raise CompileError(f"{s.family}: the partial stage of a two-stage split has no kernel; pass the "
+                               "[partial, combine] pair to the code generator for one fused launch")
+
     def __call__(self, *args):
         from .. import ops
 
         s = self.spec
         n_in = len(s.inputs)
-        if s.role != "main" and not hasattr(self, "_two_stage"):
-            raise CompileError(f"{s.family}: the {s.role} stage of a two-stage split has no kernel; pass the "
-                               "[partial, combine] pair to the code generator for one fused launch")
         if self.out_idx is None:
             if len(args) != n_in + len(s.outputs):
                 raise TypeError(f"{s.family}: expected {n_in} inputs and {len(s.outputs)} outputs, got {len(args)}")
@@ -199,6 +223,8 @@ def build_inputs_and_reference(spec: KernelSpec, device="cuda", seed=None):
     g = torch.Generator(device="cpu").manual_seed(R.fingerprint_seed(spec) if seed is None else seed)
     d = spec.dims
     f_ = spec.family
+    if spec.role != "main":
+        return _two_stage_inputs_and_reference(spec, dt, g, device)
     inputs, by_role = {}, {}
     for p, base in zip(spec.inputs, spec.input_roles()):
         shape = [int(x) for x in p.dims]
@@ -239,6 +265,63 @@ def build_inputs_and_reference(spec: KernelSpec, device="cuda", seed=None):
     else:
         raise CompileError(f"{f}: dynamic operators are validated over workloads, not one static reference")
     return inputs, [ref.to(dt)], graph_out_indices(spec)
+
+
+def _two_stage_inputs_and_reference(spec: KernelSpec, dt, g, device):
+    """Inputs and torch fp32 references of a partial or combine stage. A partial stage is checked against the
+    per-split results themselves (as the reference checks its partial kernels, against the partial graph's own
+    outputs), a combine stage on random partials."""
+    import torch
+
+    from . import reference as R
+
+    inputs, by_role = {}, {}
+    d = spec.dims
+    if spec.family == "split_combine":
+        for i, p in enumerate(spec.inputs):
+            t = torch.randn([int(x) for x in p.dims], generator=g)
+            if spec.attrs.get("divide") and i == spec.attrs["den"]:
+                t = t.abs() + 0.5      # denominators bounded away from zero, as the reference draws divisors
+            inputs[p.name] = t.to(dt).to(device)
+        vals = list(inputs.values())
+        axes = spec.attrs["axes"]
+        if spec.attrs.get("divide"):
+            ni, di = spec.attrs["num"], spec.attrs["den"]
+            outer = int(torch.tensor(vals[ni].shape[:axes[ni]]).prod()) if axes[ni] else 1
+            num = vals[ni].float().sum(axes[ni]).reshape(outer, -1)
+            den = vals[di].float().sum(axes[di]).reshape(outer, -1)   # one value per row, or one per element
+            ref = num / den
+        else:
+            ref = vals[0].float().sum(axes[0])
+        out = spec.outputs[0]
+        return inputs, [ref.reshape([int(x) for x in out.dims]).to(dt)], graph_out_indices(spec)
+    for p, base in zip(spec.inputs, spec.input_roles()):
+        t = torch.randn([int(x) for x in p.dims], generator=g)
+        if base == "w":
+            t = t / d["K"] ** 0.5
+        inputs[p.name] = by_role[base] = t.to(dt).to(device)
+    S = spec.split
+    if spec.family == "matmul":
+        x, w = by_role["x"].float(), by_role["w"].float()
+        kc = d["K"] // S
+        ref = torch.stack([x[:, s * kc:(s + 1) * kc] @ w[s * kc:(s + 1) * kc] for s in range(S)])
+        refs = [ref.reshape([int(v) for v in spec.outputs[0].dims]).to(dt)]
+    elif spec.family == "attention_decode":
+        q, k, v = (by_role[n].float() for n in ("q", "k", "v"))
+        hq, hkv, skv, dd = d["HQ"], d["HKV"], d["SKV"], d["D"]
+        scale, shift = float(spec.attrs.get("scale", dd ** -0.5)), float(spec.attrs.get("shift", 0.0))
+        kk = k.repeat_interleave(hq // hkv, 0).view(hq, S, skv // S, dd)
+        vv = v.repeat_interleave(hq // hkv, 0).view(hq, S, skv // S, dd)
+        e = torch.exp(torch.einsum("hd,hstd->hst", q[:, 0], kk) * scale + shift)
+        o_part, l_part = torch.einsum("hst,hstd->hsd", e, vv), e.sum(-1)
+        refs = []
+        for o in spec.outputs:
+            src = o_part if int(torch.tensor([int(x) for x in o.dims]).prod()) == o_part.numel() else l_part
+            refs.append(src.reshape([int(x) for x in o.dims]).to(dt))
+    else:
+        raise CompileError(f"{spec.family}: no two-stage form")
+    del R
+    return inputs, refs, graph_out_indices(spec)
 
 
 def check_code(code_str, *, graph=None, dtype=None, out_idx=None, reference_cache_dir=None,

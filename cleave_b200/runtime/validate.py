@@ -1,5 +1,12 @@
-"""Tolerances, the on-disk reference a worker validates against, and the check itself
-(mirrors python/cleave/runtime/validate.py of the reference)."""
+"""The validate and bench stages of one candidate.
+
+Contract shared with the reference (python/cleave/runtime/validate.py): a candidate is checked against a
+reference that the parent process published once as ``<dir>/reference.pt`` = ``{"inputs_by_name",
+"reference"}``; the check raises, and whatever escapes carries ``_cleave_stage`` in {"compile", "validate",
+"bench"} so that the farm can type the failure; timing follows ``cleave_b200.runtime.timer``. The default
+tolerance here is the 2e-2 / 2e-2 this library's 16-bit outputs are held to against fp32 (the reference's own
+default, 0.5 / 0.5 at python/cleave/runtime/validate.py:27, is looser).
+"""
 
 from __future__ import annotations
 
@@ -19,8 +26,6 @@ class Tolerance:
     equal_nan: bool = False
 
 
-# The reference's loose default is 0.5 / 0.5 (python/cleave/runtime/validate.py:27); every kernel
-# of this library is held to the tighter bound its 16-bit outputs allow against fp32.
 DEFAULT_TOLERANCE = Tolerance(rtol=2e-2, atol=2e-2)
 PAGED_TOLERANCE = Tolerance(rtol=1e-2, atol=1e-2)  # python/cleave/dynamic/registry.py:29
 
@@ -31,89 +36,96 @@ class BenchOptions:
     iters: int = 1000
 
 
-@contextlib.contextmanager
-def _stage(name):
-    """Tag an escaping exception with the pipeline stage it came from."""
-    try:
-        yield
-    except BaseException as exc:
-        if getattr(exc, "_cleave_stage", None) is None:
-            try:
-                exc._cleave_stage = name
-            except Exception:  # noqa: BLE001 - some builtins reject attributes
-                pass
-        raise
-
-
 _BENCHMARK_GRAPH_BATCH = 100
 _REFERENCE_FILE_NAME = "reference.pt"
 
 
+@contextlib.contextmanager
+def _stage(name):
+    """Whatever escapes the block is labelled with the stage it came from, unless an inner block
+    already labelled it."""
+    try:
+        yield
+    except BaseException as exc:
+        if getattr(exc, "_cleave_stage", None) is None:
+            with contextlib.suppress(Exception):  # a few builtin exception types take no attributes
+                exc._cleave_stage = name
+        raise
+
+
+class ReferenceStore:
+    """The published reference of one build: a single file in a directory the workers can read."""
+
+    def __init__(self, directory):
+        self.path = Path(directory) / _REFERENCE_FILE_NAME
+
+    def publish(self, inputs_by_name: dict, reference: list) -> int:
+        """Writes the payload so that a reader never sees half a file; returns the bytes of all tensors."""
+        import torch
+
+        self.path.parent.mkdir(parents=True, exist_ok=True)
+        scratch = self.path.with_name(f"{self.path.name}.tmp.{os.getpid()}")
+        torch.save({"inputs_by_name": dict(inputs_by_name), "reference": list(reference)}, scratch)
+        os.replace(scratch, self.path)
+        tensors = [*inputs_by_name.values(), *reference]
+        return sum(t.numel() * t.element_size() for t in tensors if hasattr(t, "numel"))
+
+    def read(self, device="cuda"):
+        import torch
+
+        blob = torch.load(self.path, map_location=device, weights_only=True)
+        return dict(blob["inputs_by_name"]), list(blob["reference"])
+
+
+def publish_reference(reference_cache_dir, spec, device="cuda"):
+    """Build inputs and reference for ``spec`` once, in the parent, and persist them for the workers.
+    Returns ``(out_idx, io_bytes)``."""
+    from .compile import build_inputs_and_reference
+
+    inputs_by_name, reference, out_idx = build_inputs_and_reference(spec, device=device)
+    return out_idx, ReferenceStore(reference_cache_dir).publish(inputs_by_name, reference)
+
+
+def _load_reference(reference_cache_dir, device="cuda"):
+    return ReferenceStore(reference_cache_dir).read(device)
+
+
 def benchmark_compiled_kernel(kernel, input_tensors, *, warmup_iters=0, profile_iters=1):
-    """Mean milliseconds per launch, CUDA events around CUDA-graph replays."""
+    """Mean milliseconds per launch (CUDA events around CUDA-graph replays)."""
     return mean_launch_ms(kernel, input_tensors, warmup=warmup_iters, iters=profile_iters,
                           batch=_BENCHMARK_GRAPH_BATCH)
 
 
-def _reference_cache_file(reference_cache_dir):
-    return Path(reference_cache_dir) / _REFERENCE_FILE_NAME
-
-
-def publish_reference(reference_cache_dir, spec, device="cuda"):
-    """Build (inputs, reference) once in the parent and persist them for the workers.
-    Returns ``(out_idx, io_bytes)``."""
-    import torch
-
-    from .compile import build_inputs_and_reference
-
-    inputs_by_name, reference, out_idx = build_inputs_and_reference(spec, device=device)
-    path = _reference_cache_file(reference_cache_dir)
-    tmp = path.with_name(f"{path.name}.tmp.{os.getpid()}")
-    os.makedirs(reference_cache_dir, exist_ok=True)
-    torch.save({"inputs_by_name": inputs_by_name, "reference": list(reference)}, tmp)
-    os.replace(tmp, path)
-    io_bytes = sum(t.element_size() * t.nelement() for t in list(inputs_by_name.values()) + list(reference)
-                   if hasattr(t, "nelement"))
-    return out_idx, io_bytes
-
-
-def _load_reference(reference_cache_dir, device="cuda"):
-    import torch
-
-    payload = torch.load(_reference_cache_file(reference_cache_dir), map_location=device, weights_only=True)
-    return dict(payload["inputs_by_name"]), list(payload["reference"])
-
-
-def _as_list(x):
-    return list(x) if isinstance(x, (tuple, list)) else [x]
-
-
 def _validate_kernel_outputs(kernel, inputs, reference, *, tolerance: Tolerance = DEFAULT_TOLERANCE):
-    """Run ``kernel(*inputs)`` and assert it matches ``reference`` within ``tolerance``."""
+    """Launch once and compare every output with its reference in fp32; raises ``AssertionError`` naming
+    the output that is off."""
     import torch
 
-    actual = _as_list(kernel(*inputs))
-    assert len(actual) == len(reference), (
-        f"Kernel returned {len(actual)} outputs but the reference has {len(reference)}.")
-    reference = [reconcile_output_layout(r, a.shape) for r, a in zip(reference, actual)]
-    actual = [a.float() for a in actual]
-    reference = [r.float() for r in reference]
-    torch.testing.assert_close(actual, reference, rtol=tolerance.rtol, atol=tolerance.atol,
-                               equal_nan=tolerance.equal_nan)
-    if actual and actual[0].is_cuda:
-        torch.cuda.synchronize()
+    produced = kernel(*inputs)
+    produced = list(produced) if isinstance(produced, (list, tuple)) else [produced]
+    if len(produced) != len(reference):
+        raise AssertionError(f"Kernel returned {len(produced)} outputs but the reference has {len(reference)}.")
+    for i, (got, want) in enumerate(zip(produced, reference)):
+        want = reconcile_output_layout(want, got.shape)   # the kernel may keep unit axes the reference drops
+        try:
+            torch.testing.assert_close(got.float(), want.float(), rtol=tolerance.rtol, atol=tolerance.atol,
+                                       equal_nan=tolerance.equal_nan)
+        except AssertionError as exc:
+            raise AssertionError(f"output {i}: {exc}") from None
+    if produced and produced[0].is_cuda:
+        torch.cuda.synchronize()  # a fault in the launch surfaces here, inside the validate stage
 
 
 def _check_kernel(kernel, *, spec=None, reference_cache_dir=None, tolerance: Tolerance = DEFAULT_TOLERANCE,
                   benchmark: BenchOptions | None = None):
-    """Validate ``kernel`` against the reference, then optionally time it; returns mean ms or None."""
-    from .compile import build_inputs_and_reference
-
+    """Validate, then (with ``benchmark``) time: mean milliseconds per launch, or None."""
     with _stage("validate"):
-        if reference_cache_dir is not None:
-            inputs_by_name, reference = _load_reference(reference_cache_dir)
-        else:
+        if reference_cache_dir is None:
+            from .compile import build_inputs_and_reference
+
             inputs_by_name, reference, _ = build_inputs_and_reference(spec)
+        else:
+            inputs_by_name, reference = _load_reference(reference_cache_dir)
         inputs = order_inputs_for_kernel(inputs_by_name, kernel)
         _validate_kernel_outputs(kernel, inputs, reference, tolerance=tolerance)
     if benchmark is None:

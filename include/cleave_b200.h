@@ -35,8 +35,9 @@ extern "C" {
 /* 2: cb200_gemm_args and cb200_attn_prefill_args gained trailing fields (zero = the behaviour of version 1);
  *    new entry points cb200_matmul_matmul, cb200_matmul_rowsum, cb200_lora. A binding written against
  *    version 1 must zero-fill the longer structs. */
-/* 3: cb200_workspace_status clears a reported fault; new cb200_workspace_reset and
- *    cb200_attn_decode_static_scratch_status. */
+/* 3: cb200_workspace_status clears a reported fault; new cb200_workspace_reset,
+ *    cb200_attn_decode_static_scratch_status, cb200_split_combine, cb200_attn_unnormalise; cb200_gemm_args gained
+ *    the trailing field ldx (zero = the behaviour of version 2). */
 #define CB200_VERSION 3
 
 typedef enum {
@@ -166,6 +167,9 @@ typedef struct {
   const void* x2;
   const void* w2;
   int32_t k2;
+  int32_t ldx; /* CB200_GEMM_MATMUL only: elements between consecutive rows of X (0 = k, a dense matrix). A
+                  multiple of 8. Lets a K slice of a wider matrix be the operand: the per-split products of the
+                  two-stage split-K form are X[:, s K/S : (s+1) K/S] @ W[s K/S : (s+1) K/S, :]. */
 } cb200_gemm_args;
 
 size_t cb200_gemm_workspace_bytes(const cb200_gemm_args* a);
@@ -369,6 +373,51 @@ typedef struct {
 
 size_t cb200_lora_workspace_bytes(const cb200_lora_args* a);
 int cb200_lora(const cb200_lora_args* a, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * The two-stage form of a split (compatibility with the reference's partial + combine kernel pairs; the
+ * entry points above fuse the combine into the one launch and are what performance work should call).
+ *
+ * cb200_split_combine replaces the combine kernels
+ *   tests/graph/handwritten/expected_kernels/matmul_splitk_combine.py   (Y = sum_s P[s])
+ *   tests/graph/handwritten/expected_kernels/mha_split_combine.py       (O = sum_s O[s] / sum_s L[s], per row)
+ * `num` is (outer, splits, inner) in the storage dtype, contiguous; `out` (outer, inner) receives the sum over
+ * `splits` in fp32, rounded once. With `den` (den_outer rows of `splits` values, den_outer * den_inner = the
+ * rows the quotient is taken over; den_inner is 1 for a per-row denominator) every sum is divided by the
+ * matching denominator sum: element (o, i) by den row o (den_inner == 1) or by element (o, i) (den_inner ==
+ * inner). No workspace.
+ *
+ * cb200_attn_unnormalise turns the normalised per-split results of cb200_attn_decode (out, base-2 lse) into
+ * the partial results the reference's split partial kernels emit
+ *   tests/graph/handwritten/expected_kernels/{gqa,mha,mqa}_split_partial.py:
+ *   O[s] = sum_j exp(score_j + shift) v_j and L[s] = sum_j exp(score_j + shift) with the operator's fixed shift
+ *   (demo/attention.py:5-8), i.e. O[s] = out * L[s], L[s] = 2^lse * e^shift. `out`, `lse` are laid out
+ *   (kv_heads, splits, group) rows (the order cb200_attn_decode produces for a cache viewed as
+ *   kv_heads * splits requests); o_part is (kv_heads * group, splits, head_dim), l_part (kv_heads * group, splits).
+ * ---------------------------------------------------------------------------------------- */
+typedef struct {
+  const void* num;
+  const void* den; /* may be NULL */
+  void* out;
+  int64_t outer, inner;
+  int32_t splits;
+  int32_t den_inner; /* 1 or inner; ignored without den */
+  int32_t dtype;     /* cb200_dtype of num, den and out */
+} cb200_split_combine_args;
+
+int cb200_split_combine(const cb200_split_combine_args* a, void* stream);
+
+typedef struct {
+  const void* out;  /* (kv_heads * splits * group, head_dim), storage dtype */
+  const float* lse; /* (kv_heads * splits * group), base 2 */
+  void* o_part;     /* (kv_heads * group, splits, head_dim), storage dtype */
+  void* l_part;     /* (kv_heads * group, splits), storage dtype */
+  int32_t kv_heads, group, splits, head_dim;
+  int32_t dtype;
+  float shift; /* natural-log shift added to every score before exp (the demos use -50 / sqrt(d)) */
+} cb200_attn_unnormalise_args;
+
+int cb200_attn_unnormalise(const cb200_attn_unnormalise_args* a, void* stream);
 
 /* ------------------------------------------------------------------------------------------
  * Decode attention for callers that cannot allocate device memory. (No counterpart in the

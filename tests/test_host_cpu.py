@@ -190,12 +190,12 @@ def test_kernel_binding_errors_and_save_load_roundtrip(tmp_path):
                variant="solo", latency_us=1.5)
     x, w = SimpleNamespace(shape=(4, 64)), SimpleNamespace(shape=(64, 8))
     with pytest.raises(TypeError):
-        k._bind((x,), {})
+        k._arguments((x,), {})
     with pytest.raises(TypeError):
-        k._bind((x,), {"w": w})
+        k._arguments((x,), {"w": w})
     with pytest.raises(ValueError):
-        k._bind((w, x), {})
-    assert k._bind((), {"w": w, "x": x}) == [x, w]
+        k._arguments((w, x), {})
+    assert k._arguments((), {"w": w, "x": x}) == [x, w]
     back = load(k.save(tmp_path / "k"))
     assert back.source == k.source and back.variant == "solo" and back.stages[0].params[1].shape == (64, 8)
     assert (tmp_path / "k" / "kernel.json").exists() and (tmp_path / "k" / "kernel.py").read_text() == src

@@ -181,3 +181,121 @@ def test_check_code_in_a_spawned_worker(tmp_path):
                          max_parallel=1, timeout_s=240, benchmark=BenchOptions(2, 10))
     assert [r.status for r in res] == ["ok", "ok"], [str(r.error) for r in res]
     assert all(r.latency_ms and r.latency_ms > 0 for r in res)
+
+
+def test_two_stage_split_k_chain_and_fused_kernel_agree(tmp_path, monkeypatch):
+    """Reference: tests/pipeline_api/test_e2e.py:58-81 - a split-K variant whose partial and combine plans are
+    built and timed separately runs as ONE Kernel of two chained stages, its latency the sum of its members',
+    and equals x.float() @ w.float(). Here that form is scheduled beside the fused split kernel on request."""
+    import cleave_b200 as cleave
+    import cleave_b200.lang as cl
+
+    monkeypatch.setenv("CLEAVE_CACHE_ROOT", str(tmp_path / "cache"))
+
+    @cleave.jit
+    def matmul(x: cl.Tensor["M", "K"], w: cl.Tensor["K", "N"]):
+        return x @ w
+
+    k = cleave.compile(matmul, shapes=dict(M=128, N=128, K=4096), dtype=cl.f16, split=cl.Split("K", (4, 8)),
+                       eval=_fast(), two_stage=True)
+    rep = k.report
+    assert {"solo", "split-k=4", "split-k=8", "split-k=4/two-stage", "split-k=8/two-stage"} == set(rep.variants())
+    assert not rep.failures, rep.summary()
+    pair = rep.best("split-k=4/two-stage")
+    assert [s.role for s in pair.stages] == ["partial", "combine"] and pair.unrunnable is None
+    members = rep.variants()["split-k=4/two-stage"].members
+    assert pair.latency_us == pytest.approx(sum(m.latency_us for m in members))
+    x = torch.randn(128, 4096, device="cuda").half()
+    w = (torch.randn(4096, 128, device="cuda") / 64).half()
+    want = x.float() @ w.float()
+    torch.testing.assert_close(pair(x, w).float(), want, rtol=2e-2, atol=5e-2)
+    torch.testing.assert_close(rep.best("split-k=4")(x, w).float(), want, rtol=2e-2, atol=5e-2)
+    loaded = cleave.load(pair.save(tmp_path / "pair"))
+    assert [s.role for s in loaded.stages] == ["partial", "combine"] and torch.equal(loaded(x, w), pair(x, w))
+    assert (tmp_path / "pair" / "kernel_0_partial.py").exists() and (tmp_path / "pair" / "kernel_1_combine.py").exists()
+
+
+def test_two_stage_split_kv_decode_attention():
+    """The split-KV partial + combine pair of decode attention (reference kernels:
+    tests/graph/handwritten/expected_kernels/gqa_split_partial.py + mha_split_combine.py) against the unsplit
+    fp32 reference, and the partial stage alone against the per-split sums it is defined to emit."""
+    import cleave_b200 as cleave
+    import cleave_b200.lang as cl
+    from cleave_b200.runtime import reference as R
+
+    @cleave.jit
+    def att(q: cl.Tensor["HQ", "SQ", "D"], k: cl.Tensor["HKV", "SKV", "D"], v: cl.Tensor["HKV", "SKV", "D"]):
+        n = q.shape[-1] ** 0.5
+        return cl.softmax((q @ k.mT) / n, dim=-1, shift=-50 / n) @ v
+
+    kern = cleave.compile(att, shapes=dict(HQ=32, HKV=8, SQ=1, SKV=4096, D=128), dtype=cl.f16, split=cl.Split("SKV", (4, 8)),
+                          eval=_fast(), two_stage=True, cache_kernels=False)
+    rep = kern.report
+    assert not rep.failures, rep.summary()
+    assert {"solo", "split-k=4/two-stage", "split-k=8/two-stage"} <= set(rep.variants())
+    g = torch.Generator(device="cuda").manual_seed(3)
+    q = torch.randn(32, 1, 128, device="cuda", generator=g).half()
+    k = torch.randn(8, 4096, 128, device="cuda", generator=g).half()
+    v = torch.randn(8, 4096, 128, device="cuda", generator=g).half()
+    want = R.attention(q, k, v, 128 ** -0.5)
+    for variant in ("solo", "split-k=8/two-stage"):
+        torch.testing.assert_close(rep.best(variant)(q, k, v).float(), want.float(), rtol=2e-2, atol=2e-2)
+
+
+def test_real_reference_split_plans_run_as_two_stages():
+    """The partial and combine plans the reference's scheduler really emits (recorded in tests/golden/plans.json)
+    go through the code generator one by one, as the reference's build does (python/cleave/pipeline/build.py:165),
+    and the two kernels chained give the operator's result: split-K matmul, split-KV GQA decode."""
+    import plans as plan_fixtures
+    from cleave_b200.codegen import B200CodeGen
+    from cleave_b200.runtime.compile import _compile, _load_main_kernel_from_code
+    from cleave_b200.runtime.reference import order_inputs_for_kernel
+
+    data = plan_fixtures.load()
+    gen = B200CodeGen()
+
+    def bind(plan):
+        spec = _load_main_kernel_from_code(gen.gen(plan))
+        return spec, _compile(spec, list(range(-len(spec.outputs), 0)))
+
+    g = torch.Generator(device="cuda").manual_seed(5)
+    # ---- configuration 1, split-K 8
+    c = data["cfg1_matmul"]
+    partial = next(p for p in c["plans"] if p.role == "partial" and p.split_factor == 8)
+    combine = next(p for p in c["plans"] if p.role == "combine" and p.split_factor == 8)
+    (ps, pk), (cs, ck) = bind(partial), bind(combine)
+    x = torch.randn(128, 4096, device="cuda", generator=g).half()
+    w = (torch.randn(4096, 128, device="cuda", generator=g) / 64).half()
+    roles = dict(zip(ps.input_roles(), [p.name for p in ps.inputs]))
+    parts = pk(*order_inputs_for_kernel({roles["x"]: x, roles["w"]: w}, pk))
+    assert tuple(parts.shape) == (8, 128, 128)
+    torch.testing.assert_close(parts.float(), torch.stack([x[:, i * 512:(i + 1) * 512].float() @ w[i * 512:(i + 1) * 512].float()
+                                                           for i in range(8)]), rtol=2e-2, atol=2e-2)
+    y = ck(parts)
+    torch.testing.assert_close(y.float(), x.float() @ w.float(), rtol=2e-2, atol=5e-2)
+    # ---- configuration 3, split-KV 8 (both output orders the search emits)
+    c = data["cfg3_gqa_decode"]
+    q = torch.randn(256, 1, 128, device="cuda", generator=g).half()
+    k = torch.randn(64, 8192, 128, device="cuda", generator=g).half()
+    v = torch.randn(64, 8192, 128, device="cuda", generator=g).half()
+    from cleave_b200.runtime import reference as R
+
+    want = R.attention(q, k, v, 128 ** -0.5).float()
+    combine = next(p for p in c["plans"] if p.role == "combine" and p.split_factor == 8)
+    cs, ck = bind(combine)
+    seen = set()
+    for partial in (p for p in c["plans"] if p.role == "partial" and p.split_factor == 8):
+        ps, pk = bind(partial)
+        order = tuple(tuple(o.dims) for o in ps.outputs)
+        if order in seen:
+            continue
+        seen.add(order)
+        roles = dict(zip(ps.input_roles(), [p.name for p in ps.inputs]))
+        outs = pk(*order_inputs_for_kernel({roles["q"]: q, roles["k"]: k, roles["v"]: v}, pk))
+        by_size = sorted(outs, key=lambda t: -t.numel())          # weighted values, then weight sums
+        feed = [None, None]
+        feed[cs.attrs["num"]], feed[cs.attrs["den"]] = by_size[0], by_size[1]
+        shaped = [t.reshape([int(d) for d in p.dims]) for t, p in zip(feed, cs.inputs)]
+        out = ck(*shaped)
+        torch.testing.assert_close(out.float().reshape(256, 1, 128), want, rtol=2e-2, atol=2e-2)
+    assert len(seen) >= 1

@@ -47,6 +47,17 @@ class GemmArgs(C.Structure):
     ]
 
 
+class MlaPrefillArgs(C.Structure):
+    _fields_ = [
+        ("q_nope", C.c_void_p), ("q_pe", C.c_void_p), ("ckv_cache", C.c_void_p), ("kpe_cache", C.c_void_p),
+        ("qo_indptr", C.c_void_p), ("kv_indptr", C.c_void_p), ("kv_indices", C.c_void_p), ("out", C.c_void_p),
+        ("lse", C.c_void_p), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("batch", C.c_int32), ("total_q", C.c_int32), ("num_heads", C.c_int32), ("ckv_dim", C.c_int32),
+        ("kpe_dim", C.c_int32), ("num_pages", C.c_int32), ("num_kv_indices", C.c_int32), ("dtype", C.c_int32),
+        ("sm_scale", C.c_float),
+    ]
+
+
 class SplitCombineArgs(C.Structure):
     _fields_ = [
         ("num", C.c_void_p), ("den", C.c_void_p), ("out", C.c_void_p), ("outer", C.c_int64), ("inner", C.c_int64),
@@ -166,6 +177,10 @@ def lib() -> C.CDLL:
         L.cb200_gemm_effective_split.argtypes = [C.POINTER(GemmArgs)]
         L.cb200_gemm.restype = C.c_int
         L.cb200_gemm.argtypes = [C.POINTER(GemmArgs), C.c_void_p]
+        L.cb200_mla_prefill_workspace_bytes.restype = C.c_size_t
+        L.cb200_mla_prefill_workspace_bytes.argtypes = [C.POINTER(MlaPrefillArgs)]
+        L.cb200_mla_prefill.restype = C.c_int
+        L.cb200_mla_prefill.argtypes = [C.POINTER(MlaPrefillArgs), C.c_void_p]
         L.cb200_split_combine.restype = C.c_int
         L.cb200_split_combine.argtypes = [C.POINTER(SplitCombineArgs), C.c_void_p]
         L.cb200_attn_unnormalise.restype = C.c_int

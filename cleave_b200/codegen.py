@@ -14,7 +14,7 @@ from .core.errors import CodegenError
 
 FAMILIES = ("matmul", "rmsnorm_matmul", "swiglu", "attention_decode", "mla_decode",
             "gqa_paged_decode", "mla_paged_decode", "gqa_ragged_prefill", "gqa_paged_prefill",
-            "matmul_matmul", "qknorm_attention", "matmul_rowsum", "lora", "split_combine")
+            "matmul_matmul", "qknorm_attention", "matmul_rowsum", "lora", "split_combine", "mla_paged_prefill")
 FORMAT = 1
 
 
@@ -127,6 +127,15 @@ def default_params(family: str, dtype: str, dims: dict, attrs: dict) -> tuple:
                 P(_ph("kv_indices"), "int32", ("num_kv_indices",), "input"),
                 P("sm_scale", "float32", (), "scalar"), P("OutputNode", dtype, ("batch", h, c), "output"),
                 P("OutputNode_1", "float32", ("batch", h), "output"))
+    if family == "mla_paged_prefill":
+        h, c, k = g("num_qo_heads"), g("head_dim_ckv"), g("head_dim_kpe")
+        return (P(_ph("q_nope"), dtype, ("total_q", h, c), "input"), P(_ph("q_pe"), dtype, ("total_q", h, k), "input"),
+                P(_ph("ckv_cache"), dtype, ("num_pages", 1, c), "input"),
+                P(_ph("kpe_cache"), dtype, ("num_pages", 1, k), "input"),
+                P(_ph("qo_indptr"), "int32", ("len_indptr",), "input"), P(_ph("kv_indptr"), "int32", ("len_indptr",), "input"),
+                P(_ph("kv_indices"), "int32", ("num_kv_indices",), "input"),
+                P("sm_scale", "float32", (), "scalar"), P("OutputNode", dtype, ("total_q", h, c), "output"),
+                P("OutputNode_1", "float32", ("total_q", h), "output"))
     if family in ("gqa_ragged_prefill", "gqa_paged_prefill"):
         hq, hkv, d = g("num_qo_heads"), g("num_kv_heads"), g("head_dim")
         out = [P(_ph("q"), dtype, ("total_q", hq, d), "input")]

@@ -1,0 +1,454 @@
+// Paged causal MLA prefill (absorbed latent) on the tcgen05 tensor cores: a query-tile kernel.
+//
+//   S = (Q_nope CKV^T + Q_pe KPE^T) * scale under the end-aligned causal mask, O = softmax(S) CKV
+//   q_nope (total_q, H, 512), q_pe (total_q, H, 64); caches (num_pages, 1, 512 / 64), one token per page;
+//   request r owns the query rows qo_indptr[r] .. qo_indptr[r + 1] and the keys
+//   kv_indices[kv_indptr[r] .. kv_indptr[r + 1]).
+//
+// The 128 rows of every MMA are (query token, head) pairs: a block of 128 / H consecutive query tokens of
+// one request times its H heads. Those rows are contiguous in q_nope / q_pe viewed as (total_q * H, 512 / 64)
+// matrices, so a Q chunk is one TMA box; each row has its own causal limit. An item is (request, query block);
+// two CTAs work on an item, one per half of the 512 output columns (blockIdx.x & 1), each computing the
+// scores it needs itself - the score product is 576 / 512 of the value product, and repeating it costs less
+// than moving P between SMs or holding a 128 x 512 fp32 accumulator, which alone would fill tensor memory.
+//
+//   S = Q K^T    A = Q chunk, B = cache chunk (64 of the 576 columns x 128 tokens), both K-major in shared
+//                memory; nine chunk pairs stream through one ring per KV tile (the Q chunks by TMA, the cache
+//                rows gathered through kv_indices by four warps with 16-byte cp.async into the 128-byte
+//                swizzled layout); D = S in tensor memory, two buffers of 128 columns
+//   O += P V     A = P (16-bit pairs the softmax warps store over the first 64 columns of the S buffer they
+//                just read), B = the CTA's 256 latent columns of the same 128 tokens, MN-major in shared
+//                memory (gathered by four more warps), D = O in tensor memory (256 columns)
+// Tensor memory: S/P 0 | S/P 1 | O = 128 + 128 + 256 columns. MMAs of one thread execute in order, so the
+// score product of tile j + 2, which overwrites the buffer P(j) lives in, cannot pass the value product that
+// reads it. The softmax keeps a reference maximum per row and rescales O only when the running maximum grew
+// by more than 2^8 (exact), as the GQA prefill kernel does.
+//
+// Warp roles: 0 = Q-chunk TMA producer, 1 = MMA issuer and TMEM owner, 2..5 = softmax / epilogue (thread =
+// row = TMEM lane), 6..9 = cache-row gather for the score chunks, 10..13 = gather of the value tile.
+//
+// Reference semantics: python/cleave/dynamic/reference.py:324-365; replaces
+// tests/graph/handwritten/expected_kernels/mla_paged_prefill_causal_h16_ckv512_kpe64_ps1.py
+// (python/cleave/dynamic/paging/builders/mla.py:393).
+
+#include "common.cuh"
+
+#include <cstring>
+#include <type_traits>
+
+namespace cb200 {
+namespace mlapf {
+
+constexpr int kCkv = 512, kKpe = 64;
+constexpr int kChunks = (kCkv + kKpe) / 64;  // 9 score chunks of 64 columns
+constexpr int kBM = 128, kBN = 128;          // rows per item, tokens per KV tile
+constexpr int kDV = 256;                     // output columns per CTA
+constexpr int kChunkBytes = 128 * 128;       // 128 rows x 128 bytes
+constexpr int kStageBytes = 2 * kChunkBytes; // Q chunk + cache chunk
+constexpr int kStages = 5;        // 160 KB of chunk pairs in flight: the tile loop is bound by the latency of its loads
+constexpr int kVBytes = (kDV / 64) * kChunkBytes;  // 64 KB
+constexpr int kSmemBytes = kStages * kStageBytes + kVBytes + 1024 /*barriers*/ + 1024 /*alignment*/;
+constexpr int kThreads = 14 * 32;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kRescaleThreshold = 8.f;     // log2 units
+constexpr uint32_t kColS = 0, kColO = 256;
+
+struct Params {
+  const void* ckv;
+  const void* kpe;
+  const int* qo_indptr;
+  const int* kv_indptr;
+  const int* kv_indices;
+  void* out;
+  float* lse;
+  int* status;
+  int batch, heads, qb;  // qb = 128 / heads query tokens per item
+  int num_pages, n_idx;
+  float scale_log2;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 1)
+mla_prefill_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_constant__ CUtensorMap tm_qp, const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* ring = smem;
+  uint8_t* v_smem = ring + kStages * kStageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(v_smem + kVBytes);
+  uint64_t* k_full = bars;              // [kStages] Q chunk landed (TMA) and cache rows landed (128 gather threads)
+  uint64_t* k_empty = k_full + kStages; // [kStages] the score MMAs have read the stage
+  uint64_t* v_full = k_empty + kStages; // value tile gathered
+  uint64_t* v_empty = v_full + 1;       // the value MMAs have read it
+  uint64_t* s_full = v_empty + 1;       // [2] S complete in tensor memory
+  uint64_t* p_full = s_full + 2;        // [2] P stored (and O rescaled if needed)
+  uint64_t* pv_done = p_full + 2;       // [2] the value MMAs of a tile have completed
+  uint64_t* o_done = pv_done + 2;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(o_done + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int dh = blockIdx.x & 1;  // which half of the output columns
+  // ---- which (request, query block) this CTA works on: late blocks, which see the most keys, come first
+  int t = static_cast<int>(gridDim.x >> 1) - 1 - static_cast<int>(blockIdx.x >> 1), r = 0, lo = __ldg(p.qo_indptr);
+  int q_len = 0;
+  bool found = false;
+  for (; r < p.batch; ++r) {
+    const int hi = __ldg(p.qo_indptr + r + 1);
+    const int blocks = hi > lo ? ceil_div(hi - lo, p.qb) : 0;
+    if (t < blocks) { found = true; q_len = hi - lo; break; }
+    t -= blocks;
+    lo = hi;
+  }
+  if (!found) return;  // the grid is an upper bound on the number of query blocks
+  const int q_base = lo;                 // first query token of the request
+  const int q0 = t * p.qb;               // first query token of this block, inside the request
+  int kv_base = __ldg(p.kv_indptr + r);
+  int kv_len = __ldg(p.kv_indptr + r + 1) - kv_base;
+  if (kv_base < 0 || kv_base >= p.n_idx) kv_len = 0;   // the table is caller data: stay inside it
+  kv_len = max(min(kv_len, p.n_idx - kv_base), 0);
+  const int off = kv_len - q_len;        // end-aligned causal mask: query i sees keys <= i + off
+  const int live_q = min(p.qb, q_len - q0);
+  const int last_key = min(kv_len - 1, q0 + live_q - 1 + off);
+  const int nt = last_key < 0 ? 0 : last_key / kBN + 1;
+
+  if (tid == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&k_full[s], 129);  // 128 gather threads + the TMA thread's expect-tx arrival
+      mbar_init(&k_empty[s], 1);
+    }
+    mbar_init(v_full, 128);
+    mbar_init(v_empty, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&s_full[s], 1);
+      mbar_init(&p_full[s], 4);
+      mbar_init(&pv_done[s], 1);
+    }
+    mbar_init(o_done, 1);
+    mbar_fence_init();
+    tma_prefetch_desc(&tm_qn);
+    tma_prefetch_desc(&tm_qp);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_holder, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_holder);
+
+  // page id of token `tok` of this request (clamped: rows past the end repeat the last token and are masked)
+  auto page_of = [&](int tok) {
+    const int i = kv_base + min(tok, kv_len - 1);
+    return min(max(__ldg(p.kv_indices + i), 0), p.num_pages - 1);
+  };
+
+  if (warp == 0) {
+    // ================================================================ Q chunks by TMA
+    const int row0 = (q_base + q0) * p.heads;  // first row of the block in the (total_q * H, .) view
+    int st = 0, ph = 0;
+    for (int j = 0; j < nt; ++j) {
+      for (int c = 0; c < kChunks; ++c) {
+        mbar_wait(&k_empty[st], ph ^ 1, p.status, kFaultEmptyBarrier);
+        if (lane == 0) {
+          mbar_arrive_expect_tx(&k_full[st], kChunkBytes);
+          if (c < kCkv / 64) tma_load_2d(ring + st * kStageBytes, &tm_qn, &k_full[st], c * 64, row0);
+          else tma_load_2d(ring + st * kStageBytes, &tm_qp, &k_full[st], 0, row0);
+        }
+        __syncwarp();
+        if (++st == kStages) { st = 0; ph ^= 1; }
+      }
+    }
+  } else if (warp >= 6 && warp < 10) {
+    // ================================================================ cache rows of the score chunks
+    // eight lanes copy the eight 16-byte pieces of one row's chunk: a warp instruction moves four whole
+    // 128-byte lines; the 128 threads cover 16 rows per round
+    const int gtid = tid - 6 * 32, piece = gtid & 7, r_in = gtid >> 3;
+    const T* ckv = reinterpret_cast<const T*>(p.ckv);
+    const T* kpe = reinterpret_cast<const T*>(p.kpe);
+    int st = 0, ph = 0;
+    for (int j = 0; j < nt; ++j) {
+      int pg[8];
+#pragma unroll
+      for (int rr = 0; rr < 8; ++rr) pg[rr] = page_of(j * kBN + rr * 16 + r_in);
+      for (int c = 0; c < kChunks; ++c) {
+        mbar_wait(&k_empty[st], ph ^ 1, p.status, kFaultEmptyBarrier);
+        const uint32_t dst = smem_u32(ring + st * kStageBytes + kChunkBytes);
+#pragma unroll
+        for (int rr = 0; rr < 8; ++rr) {
+          const int row = rr * 16 + r_in;
+          const T* src = c < kCkv / 64 ? ckv + static_cast<long long>(pg[rr]) * kCkv + c * 64 + piece * 8
+                                       : kpe + static_cast<long long>(pg[rr]) * kKpe + piece * 8;
+          const uint32_t o = row * 128 + ((piece ^ (row & 7)) << 4);
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + o), "l"(src) : "memory");
+        }
+        asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&k_full[st])) : "memory");
+        if (++st == kStages) { st = 0; ph ^= 1; }
+      }
+    }
+  } else if (warp >= 10) {
+    // ================================================================ value tile: 128 tokens x this CTA's 256 columns
+    // a row's 512 bytes are 32 pieces: the 128 threads cover 4 rows per round
+    const int gtid = tid - 10 * 32, piece = gtid & 31, r_in = gtid >> 5;
+    const T* ckv = reinterpret_cast<const T*>(p.ckv) + dh * kDV;
+    const uint32_t dst = smem_u32(v_smem);
+    for (int j = 0; j < nt; ++j) {
+      mbar_wait(v_empty, (j & 1) ^ 1, p.status, kFaultEmptyBarrier);
+#pragma unroll 1
+      for (int r0 = 0; r0 < kBN; r0 += 32) {
+        int pg[8];
+#pragma unroll
+        for (int rr = 0; rr < 8; ++rr) pg[rr] = page_of(j * kBN + r0 + rr * 4 + r_in);
+#pragma unroll
+        for (int rr = 0; rr < 8; ++rr) {
+          const int row = r0 + rr * 4 + r_in;
+          const T* src = ckv + static_cast<long long>(pg[rr]) * kCkv + piece * 8;
+          const uint32_t o = (piece >> 3) * kChunkBytes + row * 128 + (((piece & 7) ^ (row & 7)) << 4);
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + o), "l"(src) : "memory");
+        }
+      }
+      asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(v_full)) : "memory");
+    }
+  } else if (warp == 1) {
+    // ================================================================ MMA issuer
+    constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
+    constexpr uint32_t idesc_s = umma_idesc(kBf16, /*b_mn_major=*/false, kBM, kBN);
+    constexpr uint32_t idesc_pv = umma_idesc(kBf16, /*b_mn_major=*/true, kBM, kDV);
+    const uint32_t ring_addr = smem_u32(ring), v_addr = smem_u32(v_smem);
+    int st = 0, ph = 0;
+    auto issue_s = [&](int j) {
+      const uint32_t d = tmem_base + kColS + (j & 1) * kBN;
+      for (int c = 0; c < kChunks; ++c) {
+        mbar_wait(&k_full[st], ph, p.status, kFaultFullBarrier);
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t a = ring_addr + st * kStageBytes;
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            const uint64_t adesc = umma_smem_desc(a + kk * 32, 16, 8 * 128);
+            const uint64_t bdesc = umma_smem_desc(a + kChunkBytes + kk * 32, 16, 8 * 128);
+            umma_f16(d, adesc, bdesc, idesc_s, (c > 0 || kk > 0) ? 1u : 0u);
+          }
+          umma_commit(&k_empty[st]);
+        }
+        __syncwarp();
+        if (++st == kStages) { st = 0; ph ^= 1; }
+      }
+      if (lane == 0) umma_commit(&s_full[j & 1]);
+      __syncwarp();
+    };
+    if (nt > 0) issue_s(0);
+    for (int j = 0; j < nt; ++j) {
+      if (j + 1 < nt) issue_s(j + 1);
+      const int pb = j & 1;
+      mbar_wait(v_full, j & 1, p.status, kFaultFullBarrier);
+      mbar_wait(&p_full[pb], (j >> 1) & 1, p.status, kFaultTmemBarrier);
+      tc_fence_after();
+      if (lane == 0) {
+#pragma unroll
+        for (int ks = 0; ks < kBN / 16; ++ks) {
+          // B: MN-major, 16 token rows of 128 bytes per step; 64-column chunks are kChunkBytes apart
+          const uint64_t bdesc = umma_smem_desc(v_addr + ks * 16 * 128, kChunkBytes, 8 * 128);
+          umma_f16_ts(tmem_base + kColO, tmem_base + kColS + pb * kBN + ks * 8, bdesc, idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+        }
+        umma_commit(v_empty);
+        umma_commit(&pv_done[pb]);
+        if (j == nt - 1) umma_commit(o_done);
+      }
+      __syncwarp();
+    }
+  } else if (warp >= 2 && warp < 6) {
+    // ================================================================ softmax / epilogue
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;       // (token, head) pair inside the block = TMEM lane
+    const int qi = row / p.heads, head = row - qi * p.heads;
+    const bool live = qi < live_q;
+    const uint32_t lane_field = static_cast<uint32_t>(quarter * 32) << 16;
+    const int key_limit = live ? min(kv_len - 1, q0 + qi + off) : -1;  // last key this row sees
+    float m_ref = 0.f, l_run = 0.f;
+    for (int j = 0; j < nt; ++j) {
+      const int sb = j & 1;
+      mbar_wait(&s_full[sb], (j >> 1) & 1, p.status, kFaultMmaBarrier);
+      tc_fence_after();
+      uint32_t rg[4][32];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) tmem_ld_32x32(tmem_base + lane_field + kColS + sb * kBN + q * 32, rg[q]);
+      tmem_ld_wait();
+      const int k0 = j * kBN;
+      float mx = -INFINITY;
+      if (k0 + kBN - 1 <= key_limit) {  // whole tile visible to this row
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float v = __uint_as_float(rg[q][i]) * p.scale_log2;
+            rg[q][i] = __float_as_uint(v);
+            mx = fmaxf(mx, v);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float v = k0 + q * 32 + i <= key_limit ? __uint_as_float(rg[q][i]) * p.scale_log2 : -INFINITY;
+            rg[q][i] = __float_as_uint(v);
+            mx = fmaxf(mx, v);
+          }
+        }
+      }
+      float alpha = 1.f;
+      bool rescale = false;
+      if (j == 0) {
+        m_ref = mx == -INFINITY ? 0.f : mx;
+      } else if (mx > m_ref + kRescaleThreshold) {
+        alpha = fast_exp2(m_ref - mx);
+        m_ref = mx;
+        rescale = true;
+      }
+      if (__any_sync(0xffffffffu, rescale)) {  // rare: the running maximum grew by more than 2^8
+        // O may only be touched when no value MMA is in flight: tile j - 1 is the last one issued
+        mbar_wait(&pv_done[sb ^ 1], ((j - 1) >> 1) & 1, p.status, kFaultMmaBarrier);
+        tc_fence_after();
+#pragma unroll 1
+        for (int c0 = 0; c0 < kDV; c0 += 32) {
+          uint32_t o[32];
+          tmem_ld_32x32(tmem_base + lane_field + kColO + c0, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st_32x32(tmem_base + lane_field + kColO + c0, o);
+        }
+        tmem_st_wait();
+      }
+      // P goes over the first 64 columns of the S buffer this thread has just read into registers
+      float psum = 0.f;
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        uint32_t pk[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int c = hh * 64 + 2 * i;
+          const float p0 = fast_exp2(__uint_as_float(rg[c >> 5][c & 31]) - m_ref);
+          const float p1 = fast_exp2(__uint_as_float(rg[(c + 1) >> 5][(c + 1) & 31]) - m_ref);
+          psum += p0 + p1;
+          pk[i] = pack2<T>(p0, p1);
+        }
+        tmem_st_32x32(tmem_base + lane_field + kColS + sb * kBN + hh * 32, pk);
+      }
+      l_run = l_run * alpha + psum;
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[sb]);
+    }
+    // ---- epilogue: O / l
+    if (nt > 0) {
+      mbar_wait(o_done, 0, p.status, kFaultMmaBarrier);
+      tc_fence_after();
+    }
+    const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+    const size_t orow = static_cast<size_t>(q_base + q0 + qi) * p.heads + head;
+    T* outp = reinterpret_cast<T*>(p.out) + orow * kCkv + dh * kDV;
+#pragma unroll 1
+    for (int c0 = 0; c0 < kDV; c0 += 32) {
+      uint32_t o[32];
+      if (nt > 0) {
+        tmem_ld_32x32(tmem_base + lane_field + kColO + c0, o);
+        tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[i] = 0u;
+      }
+      if (live) {
+        const float* v = reinterpret_cast<const float*>(o);
+#pragma unroll
+        for (int i = 0; i < 32; i += 8) {
+          uint4 q4;
+          q4.x = pack2<T>(v[i] * inv, v[i + 1] * inv);
+          q4.y = pack2<T>(v[i + 2] * inv, v[i + 3] * inv);
+          q4.z = pack2<T>(v[i + 4] * inv, v[i + 5] * inv);
+          q4.w = pack2<T>(v[i + 6] * inv, v[i + 7] * inv);
+          *reinterpret_cast<uint4*>(outp + c0 + i) = q4;
+        }
+      }
+    }
+    if (live && dh == 0 && p.lse) p.lse[orow] = l_run > 0.f ? m_ref + fast_log2(l_run) : -INFINITY;
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <typename T>
+int launch(const cb200_mla_prefill_args* a, cudaStream_t stream) {
+  Params p{};
+  p.ckv = a->ckv_cache;
+  p.kpe = a->kpe_cache;
+  p.qo_indptr = a->qo_indptr;
+  p.kv_indptr = a->kv_indptr;
+  p.kv_indices = a->kv_indices;
+  p.out = a->out;
+  p.lse = a->lse;
+  p.status = reinterpret_cast<int*>(a->workspace);
+  p.batch = a->batch;
+  p.heads = a->num_heads;
+  p.qb = kBM / a->num_heads;
+  p.num_pages = a->num_pages;
+  p.n_idx = a->num_kv_indices;
+  p.scale_log2 = a->sm_scale * kLog2e;
+  const CUtensorMapDataType dt = a->dtype == CB200_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  CUtensorMap tm_qn, tm_qp;
+  {
+    // the (total_q, H, 512 / 64) query tensors as matrices of total_q * H rows: a block of 128 / H tokens is 128 rows
+    const uint64_t rows = static_cast<uint64_t>(a->total_q) * a->num_heads;
+    uint32_t box[2] = {64u, 128u};
+    uint64_t dn[2] = {kCkv, rows}, sn[1] = {kCkv * 2};
+    uint64_t dp[2] = {kKpe, rows}, sp[1] = {kKpe * 2};
+    if (!encode_tensor_map(&tm_qn, dt, 2, const_cast<void*>(a->q_nope), dn, sn, box, CU_TENSOR_MAP_SWIZZLE_128B) ||
+        !encode_tensor_map(&tm_qp, dt, 2, const_cast<void*>(a->q_pe), dp, sp, box, CU_TENSOR_MAP_SWIZZLE_128B))
+      return CB200_ERR_CUDA;
+  }
+  auto kern = mla_prefill_kernel<T>;
+  CB200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+  // every request has at most ceil(q_len / qb) <= q_len / qb + 1 query blocks; two CTAs per block
+  const long long blocks = static_cast<long long>(ceil_div(a->total_q, p.qb)) + a->batch;
+  kern<<<static_cast<unsigned>(2 * blocks), kThreads, kSmemBytes, stream>>>(tm_qn, tm_qp, p);
+  CB200_CUDA_TRY(cudaGetLastError());
+  return CB200_OK;
+}
+
+int plan(const cb200_mla_prefill_args* a) {
+  if (!a) return CB200_ERR_BAD_ARG;
+  if (a->batch <= 0 || a->total_q <= 0 || a->num_heads <= 0 || a->num_pages <= 0 || a->num_kv_indices < 0) return CB200_ERR_BAD_ARG;
+  if (a->ckv_dim != kCkv || a->kpe_dim != kKpe) return CB200_ERR_UNSUPPORTED;
+  if (a->num_heads > kBM || kBM % a->num_heads) return CB200_ERR_UNSUPPORTED;  // a block of whole tokens fills the 128 MMA rows
+  if (a->dtype != CB200_F16 && a->dtype != CB200_BF16) return CB200_ERR_UNSUPPORTED;
+  const long long blocks = static_cast<long long>(ceil_div(a->total_q, kBM / a->num_heads)) + a->batch;
+  if (2 * blocks >= (1LL << 31) || static_cast<long long>(a->total_q) * a->num_heads >= (1LL << 31)) return CB200_ERR_UNSUPPORTED;
+  return CB200_OK;
+}
+
+}  // namespace mlapf
+}  // namespace cb200
+
+extern "C" size_t cb200_mla_prefill_workspace_bytes(const cb200_mla_prefill_args* a) {
+  return cb200::mlapf::plan(a) == CB200_OK ? cb200::kWsHeaderBytes : 0;
+}
+
+extern "C" int cb200_mla_prefill(const cb200_mla_prefill_args* a, void* stream) {
+  using namespace cb200;
+  const int rc = mlapf::plan(a);
+  if (rc != CB200_OK) return rc;
+  if (!a->q_nope || !a->q_pe || !a->ckv_cache || !a->kpe_cache || !a->qo_indptr || !a->kv_indptr || !a->out) return CB200_ERR_BAD_ARG;
+  if (!a->kv_indices && a->num_kv_indices > 0) return CB200_ERR_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(a->q_nope) | reinterpret_cast<uintptr_t>(a->q_pe) | reinterpret_cast<uintptr_t>(a->ckv_cache) |
+       reinterpret_cast<uintptr_t>(a->kpe_cache) | reinterpret_cast<uintptr_t>(a->out)) & 15)
+    return CB200_ERR_ALIGNMENT;
+  if (!a->workspace || a->workspace_bytes < kWsHeaderBytes) return CB200_ERR_WORKSPACE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  return a->dtype == CB200_F16 ? mlapf::launch<__half>(a, st) : mlapf::launch<__nv_bfloat16>(a, st);
+}

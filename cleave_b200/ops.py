@@ -471,25 +471,50 @@ def mla_paged_decode(q_nope, q_pe, ckv_cache, kpe_cache, kv_indptr, kv_indices, 
 
 
 def mla_paged_prefill(q_nope, q_pe, ckv_cache, kpe_cache, qo_indptr, kv_indptr, kv_indices, sm_scale, *, out=None,
-                      lse=None):
+                      lse=None, impl="auto"):
     """Paged causal MLA prefill (reference: python/cleave/dynamic/reference.py:324-365, builders/mla.py):
     q_nope (total_q, H, 512), q_pe (total_q, H, 64), caches (num_pages, 1, 512 / 64), per-request query
-    and key offsets. Every query token runs as one request of the paged MLA decode kernel over the
-    prefix of its sequence's pages that the end-aligned causal mask lets it see; a functional first
-    version (the prefix is re-read per token), not a query-tile kernel. Returns ``(out, lse)``; rows
-    without visible keys are 0 / -inf."""
+    and key offsets. ``impl`` "tile" is the tcgen05 query-tile kernel (128 / H query tokens times their heads
+    are the rows of every MMA; H must divide 128), "per_token" runs every query token as one request of the
+    paged MLA decode kernel over the prefix the mask lets it see (any H; the prefix is re-read per token);
+    "auto" takes the tile kernel whenever H divides 128. Returns ``(out, lse)``; rows without visible keys
+    are 0 / -inf."""
     q_nope, qo_indptr, kv_indptr = _cuda(q_nope, "q_nope"), _cuda(qo_indptr, "qo_indptr"), _cuda(kv_indptr, "kv_indptr")
-    total_q, heads, _ = q_nope.shape
+    q_pe, ckv_cache, kpe_cache = _cuda(q_pe, "q_pe"), _cuda(ckv_cache, "ckv_cache"), _cuda(kpe_cache, "kpe_cache")
+    total_q, heads, dc = q_nope.shape
     batch = qo_indptr.numel() - 1
     dev = q_nope.device
+    if qo_indptr.dtype != torch.int32 or kv_indptr.dtype != torch.int32 or kv_indices.dtype != torch.int32:
+        raise TypeError("qo_indptr / kv_indptr / kv_indices must be int32")
+    if kv_indptr.numel() != batch + 1:
+        raise ValueError("qo_indptr and kv_indptr must both hold batch + 1 entries")
+    if lse is None:
+        lse = torch.empty(total_q, heads, dtype=torch.float32, device=dev)
+    tile_ok = heads <= 128 and 128 % heads == 0 and dc == 512 and q_pe.shape[2] == 64
+    if impl == "tile" and not tile_ok:
+        raise ValueError("the tile kernel needs a head count that divides 128 and the 512 + 64 latent layout")
+    if impl == "tile" or (impl == "auto" and tile_ok):
+        if out is None:
+            out = torch.empty_like(q_nope)
+        a = _lib.MlaPrefillArgs()
+        a.q_nope, a.q_pe, a.ckv_cache, a.kpe_cache = q_nope.data_ptr(), q_pe.data_ptr(), ckv_cache.data_ptr(), kpe_cache.data_ptr()
+        a.qo_indptr, a.kv_indptr, a.kv_indices = qo_indptr.data_ptr(), kv_indptr.data_ptr(), _cuda(kv_indices, "kv_indices").data_ptr()
+        a.out, a.lse = out.data_ptr(), lse.data_ptr()
+        a.batch, a.total_q, a.num_heads, a.ckv_dim, a.kpe_dim = batch, total_q, heads, dc, q_pe.shape[2]
+        a.num_pages, a.num_kv_indices, a.dtype, a.sm_scale = ckv_cache.shape[0], kv_indices.numel(), _dtype_code(q_nope), float(sm_scale)
+        need = _lib.lib().cb200_mla_prefill_workspace_bytes(C.byref(a))
+        if need == 0:
+            _lib.check(_lib.lib().cb200_mla_prefill(C.byref(a), _stream()))  # raises the real status
+        ws = workspace("mla_prefill", need, dev)
+        a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+        _lib.check(_lib.lib().cb200_mla_prefill(C.byref(a), _stream()))
+        return out, lse
     q_lens = (qo_indptr[1:] - qo_indptr[:-1]).long().clamp(min=0)
     kv_lens = (kv_indptr[1:] - kv_indptr[:-1]).long().clamp(min=0)
     req = torch.repeat_interleave(torch.arange(batch, device=dev), q_lens, output_size=total_q)
     pos = torch.arange(total_q, device=dev) - qo_indptr.long()[req]
     seen = torch.minimum((kv_lens[req] - q_lens[req] + pos + 1).clamp(min=0), kv_lens[req]).to(torch.int32)
     start = kv_indptr[:-1][req].to(torch.int32).contiguous()
-    if lse is None:
-        lse = torch.empty(total_q, heads, dtype=torch.float32, device=dev)
     out = _mla(q_nope, q_pe, ckv_cache, kpe_cache, sm_scale, kv_indptr=start, kv_indices=_cuda(kv_indices, "kv_indices"),
                out=out, lse=lse, impl="mma_sync", kv_start=start, kv_lens=seen.contiguous())
     return out, lse

@@ -4,8 +4,10 @@
 The reference searches tilings of a dense attention body, wraps each in a paged access layer,
 validates every candidate on every workload and calibrates a split-vs-single dispatch
 threshold. Here one persistent kernel deals KV tiles evenly to the SMs whatever the length
-distribution, so there is a single candidate per operator and no dispatch table: ``dispatch``
-stays ``None`` and the report says why.
+distribution. ``calibrate_dispatch`` still measures the reference's question on it - does a
+workload with short requests run better on a small grid whose CTAs keep whole items than on
+the full grid that cuts them - and the report carries the answer with the reference's field
+names; the threshold is applied only if the hybrid beats the full grid by a margin.
 """
 
 from __future__ import annotations
@@ -35,8 +37,11 @@ OPERATORS = {
     "gqa_paged_prefill_causal": ("gqa_paged_prefill",
                                  ("q", "k_cache", "v_cache", "qo_indptr", "kv_indptr", "kv_indices", "sm_scale"),
                                  ("num_qo_heads", "num_kv_heads", "head_dim")),
+    "mla_paged_prefill_causal": ("mla_paged_prefill",
+                                 ("q_nope", "q_pe", "ckv_cache", "kpe_cache", "qo_indptr", "kv_indptr", "kv_indices", "sm_scale"),
+                                 ("num_qo_heads", "head_dim_ckv", "head_dim_kpe")),
 }
-PREFILL_FAMILIES = ("gqa_ragged_prefill", "gqa_paged_prefill")
+PREFILL_FAMILIES = ("gqa_ragged_prefill", "gqa_paged_prefill", "mla_paged_prefill")
 
 
 def paged_decode_workloads(batches=(1, 7, 64), kv_points=6, kv_max=8192, seed=0):
@@ -87,10 +92,16 @@ def make_inputs(family, dims, kv_lens, dtype, device="cuda", seed=0):
     g = torch.Generator(device="cpu").manual_seed(seed)
     if family in PREFILL_FAMILIES:
         q_lens, kv_lens = kv_lens
-        hq, hkv, d = dims["num_qo_heads"], dims["num_kv_heads"], dims["head_dim"]
         rn = lambda *s: torch.randn(*s, generator=g).to(dt).to(device)  # noqa: E731
         ptr = lambda ls: torch.tensor([0] + list(torch.tensor(ls).cumsum(0).tolist()), dtype=torch.int32, device=device)  # noqa: E731
         tq, tk = max(1, sum(q_lens)), sum(kv_lens)
+        if family == "mla_paged_prefill":
+            h, c, k = dims["num_qo_heads"], dims["head_dim_ckv"], dims["head_dim_kpe"]
+            num_pages = tk + 3
+            idx = torch.randperm(num_pages, generator=g)[:tk].to(torch.int32).to(device)
+            return [rn(tq, h, c), rn(tq, h, k), rn(num_pages, 1, c), rn(num_pages, 1, k), ptr(q_lens), ptr(kv_lens), idx,
+                    0.1352337747812271]
+        hq, hkv, d = dims["num_qo_heads"], dims["num_kv_heads"], dims["head_dim"]
         if family == "gqa_ragged_prefill":
             return [rn(tq, hq, d), rn(tk, hkv, d), rn(tk, hkv, d), ptr(q_lens), ptr(kv_lens), float(d) ** -0.5]
         num_pages = tk + 3
@@ -120,7 +131,8 @@ def reference(family, args):
     from ..runtime import reference as R
 
     fn = {"gqa_paged_decode": R.gqa_paged_decode, "mla_paged_decode": R.mla_paged_decode,
-          "gqa_ragged_prefill": R.gqa_ragged_prefill, "gqa_paged_prefill": R.gqa_paged_prefill}[family]
+          "gqa_ragged_prefill": R.gqa_ragged_prefill, "gqa_paged_prefill": R.gqa_paged_prefill,
+          "mla_paged_prefill": R.mla_paged_prefill}[family]
     return fn(*args)
 
 
@@ -143,12 +155,48 @@ class WorkloadCandidate:
         return math.exp(sum(math.log(v) for v in vals) / len(vals)) if vals else None
 
 
+SMALL_GRID_CTAS = 32        # the "single" candidate of the dispatch question: a grid that rarely cuts a short item
+DISPATCH_MARGIN = 0.05      # the hybrid must beat the full grid's geomean by this much to be applied
+
+
+def calibrate_dispatch(pair, solo, tiles: dict, *, kv_tile: int = 64, page_size: int = 1, indptr_index: int = 3) -> dict:
+    """The smallest ``min_tiles`` threshold with the best hybrid geomean: a workload whose longest request
+    has at least ``min_tiles`` KV tiles runs ``pair`` (here: the full grid, items cut across CTAs and
+    combined), a shorter one runs ``solo`` (here: a small grid). Same rule, tie-break and result fields as
+    the reference (python/cleave/pipeline/dynamic.py:209-242); ``pair`` / ``solo`` are candidates whose
+    ``latency_us`` maps workload key -> microseconds, ``tiles`` maps workload key -> KV tiles of its longest
+    request. ``applied`` says whether the hybrid beats ``pair`` alone by ``DISPATCH_MARGIN``."""
+    keys = [k for k in tiles if pair.latency_us.get(k) and solo.latency_us.get(k)]
+    if not keys:
+        raise CleaveError("calibrate_dispatch: no workload was timed on both candidates")
+
+    def geomean(vals):
+        return math.exp(sum(math.log(v) for v in vals) / len(vals))
+
+    def hybrid(t):
+        return geomean([(pair if tiles[k] >= t else solo).latency_us[k] for k in keys])
+
+    thresholds = sorted({tiles[k] for k in keys} | {1, max(tiles[k] for k in keys) + 1})
+    best_us, min_tiles = min((hybrid(t), t) for t in thresholds)   # ties go to the smallest threshold
+    split_us = geomean([pair.latency_us[k] for k in keys])
+    return {
+        "split_label": pair.label, "single_label": solo.label, "min_tiles": int(min_tiles),
+        "kv_tile": int(kv_tile), "page_size": int(page_size), "indptr_index": int(indptr_index),
+        "geomean_us": {"hybrid": best_us, "split": split_us, "single": geomean([solo.latency_us[k] for k in keys])},
+        "n_workloads": len(keys), "split_runs": sum(tiles[k] >= min_tiles for k in keys),
+        "applied": bool(best_us < split_us * (1.0 - DISPATCH_MARGIN)),
+        "rule": "run the full grid when the longest request has at least min_tiles KV tiles "
+                "(indptr units x page_size tokens / kv_tile), else the small grid",
+    }
+
+
 class DynamicReport:
     def __init__(self, candidates, errors, *, workloads, timings, dispatch=None):
         self.candidates, self.errors = list(candidates), list(errors)
         self.n_workloads, self.timings, self.dispatch = workloads, dict(timings), dispatch
         self.dispatch_note = ("one persistent kernel splits the KV tile stream evenly over the SMs for every "
-                              "length distribution: there is no split/single pair to dispatch between")
+                              "length distribution; the measured split / single threshold is recorded and "
+                              "applied only when it pays")
 
     correct = property(lambda self: [c for c in self.candidates if c.correct])
     timed = property(lambda self: [c for c in self.correct if c.latency_us])
@@ -165,7 +213,13 @@ class DynamicReport:
         b = self.best()
         if b is not None:
             rows.append(f"benchmark     best {b.geomean_us:.2f} us geomean  {b.label}  {self.timings.get('benchmark', 0):.2f} s")
-        rows.append(f"dispatch      none: {self.dispatch_note}")
+        if self.dispatch:
+            d = self.dispatch
+            rows.append(f"dispatch      min_tiles {d['min_tiles']}  hybrid {d['geomean_us']['hybrid']:.2f} us, full grid "
+                        f"{d['geomean_us']['split']:.2f} us, small grid {d['geomean_us']['single']:.2f} us  "
+                        f"({'applied' if d['applied'] else 'not applied: within the margin of the full grid'})")
+        else:
+            rows.append(f"dispatch      none: {self.dispatch_note}")
         return "\n".join(rows)
 
     def to_dict(self) -> dict:
@@ -188,6 +242,10 @@ class PagedKernel(Kernel):
         self.dispatch, self.dispatch_sources = None, {}
         super().__init__([Stage("main", source, [], [], kw.get("label", ""), kw.get("latency_us"))],
                          name=op_name, input_names=self.param_names, input_shapes=[], **kw)
+        if compiled is not None:
+            from ..runtime.scratch import with_scratch
+
+            compiled = with_scratch(compiled)
         self._compiled = compiled
 
     def compile(self) -> "PagedKernel":
@@ -203,6 +261,8 @@ class PagedKernel(Kernel):
         meta = json.loads((p / "kernel.json").read_text())
         meta["paged"] = self.op_name
         (p / "kernel.json").write_text(json.dumps(meta, indent=1, default=str))
+        if self.dispatch:   # the reference keeps the calibrated threshold beside the kernel (dispatch.json)
+            (p / "dispatch.json").write_text(json.dumps(self.dispatch, indent=1, default=str))
         return p
 
     @classmethod
@@ -211,8 +271,11 @@ class PagedKernel(Kernel):
 
         source = (p / m["stages"][0]["file"]).read_text()
         spec = _load_main_kernel_from_code(source)
-        return cls(m["paged"], spec, source, label=m["label"], variant=m["variant"], latency_us=m["latency_us"],
-                   meta=dict(m.get("meta") or {}, loaded_from=str(p)))
+        kernel = cls(m["paged"], spec, source, label=m["label"], variant=m["variant"], latency_us=m["latency_us"],
+                     meta=dict(m.get("meta") or {}, loaded_from=str(p)))
+        if (p / "dispatch.json").exists():
+            kernel.dispatch = json.loads((p / "dispatch.json").read_text())
+        return kernel
 
     def __call__(self, *args, **named):
         import torch
@@ -265,7 +328,7 @@ def compile_dynamic(op_name, *, dtype=None, preset="default", eval=None, workloa
         raise TypeError(f"{op_name}: missing dims {missing}")
     dt = getattr(dtype, "name", dtype) or "bfloat16"
     dims = {k: int(v) for k, v in dims.items()}
-    if family in ("gqa_paged_decode",) + PREFILL_FAMILIES:
+    if family in ("gqa_paged_decode", "gqa_ragged_prefill", "gqa_paged_prefill"):
         if dims["head_dim"] not in (64, 128):
             raise PagingRefusal(f"{op_name}: head_dim {dims['head_dim']} is not built (64 or 128)")
         if dims["num_qo_heads"] % dims["num_kv_heads"]:
@@ -308,8 +371,27 @@ def compile_dynamic(op_name, *, dtype=None, preset="default", eval=None, workloa
             kept = [a for a in args if a is not None]
             outs = [torch.empty_like(w) for w in reference(family, args)]
             cand.latency_us[key] = min_launch_us(cand.kernel, [*kept, *outs], batch=20, repeats=5)
+    dispatch, cands = None, [cand]
+    if cand.correct and family in ("gqa_paged_decode", "mla_paged_decode"):
+        # the reference's dispatch question on this kernel: full grid against a small grid, per workload
+        small_spec = make_spec(family, dt, dims, attrs={"max_ctas": SMALL_GRID_CTAS})
+        small = WorkloadCandidate(label=f"{op_name} persistent tile-stream, {SMALL_GRID_CTAS} CTAs",
+                                  source=B200CodeGen().gen(small_spec), eligible=False, correct=True)
+        small.kernel = _compile(_load_main_kernel_from_code(small.source), None)
+        tiles = {}
+        ps = int(dims.get("page_size", 1))
+        for key, lens in wls[::step][:max_workloads]:
+            args = make_inputs(family, dims, lens, dt)
+            kept = [a for a in args if a is not None]
+            outs = [torch.empty_like(w) for w in reference(family, args)]
+            small.latency_us[key] = min_launch_us(small.kernel, [*kept, *outs], batch=20, repeats=5)
+            tiles[key] = -(-max(-(-n // ps) for n in lens) * ps // 64)
+        dispatch = calibrate_dispatch(cand, small, tiles, kv_tile=64, page_size=ps,
+                                      indptr_index=OPERATORS[op_name][1].index("kv_indptr"))
+        cands.append(small)
     t2 = time.perf_counter()
-    report = DynamicReport([cand], errors, workloads=cand.checked, timings={"validate": t1 - t0, "benchmark": t2 - t1})
+    report = DynamicReport(cands, errors, workloads=cand.checked, timings={"validate": t1 - t0, "benchmark": t2 - t1},
+                           dispatch=dispatch)
     if progress:
         progress("evaluate", report)
     best = report.best()
@@ -317,5 +399,7 @@ def compile_dynamic(op_name, *, dtype=None, preset="default", eval=None, workloa
         err = CleaveError(f"{op_name}: the kernel is not correct over its workloads: {cand.failure}")
         err.report = report
         raise err
-    return PagedKernel(op_name, spec, source, best.kernel, label=best.label, variant="solo",
-                       latency_us=best.geomean_us, report=report)
+    kernel = PagedKernel(op_name, spec, source, best.kernel, label=best.label, variant="solo",
+                         latency_us=best.geomean_us, report=report)
+    kernel.dispatch = dispatch
+    return kernel

@@ -181,6 +181,9 @@ class B200Kernel:
         elif f == "mla_paged_decode":
             ops.mla_paged_decode(ins[0], ins[1], ins[2], ins[3], ins[4], ins[5], float(ins[6]), out=outs[0],
                                  lse=outs[1], max_ctas=mc)
+        elif f == "mla_paged_prefill":
+            ops.mla_paged_prefill(ins[0], ins[1], ins[2], ins[3], ins[4], ins[5], ins[6], float(ins[7]), out=outs[0],
+                                  lse=outs[1])
         elif f == "gqa_ragged_prefill":
             ops.gqa_ragged_prefill(ins[0], ins[1], ins[2], ins[3], ins[4], float(ins[5]), out=outs[0], lse=outs[1])
         elif f == "gqa_paged_prefill":

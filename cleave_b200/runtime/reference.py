@@ -206,6 +206,29 @@ def gqa_paged_prefill(q, k_cache, v_cache, qo_indptr, kv_indptr, kv_indices, sm_
     return out.to(q.dtype), lse
 
 
+def mla_paged_prefill(q_nope, q_pe, ckv_cache, kpe_cache, qo_indptr, kv_indptr, kv_indices, sm_scale):
+    """``(out, lse)`` of the paged causal MLA prefill (python/cleave/dynamic/reference.py:324-365): per request
+    the latent rows are both keys (with the rope part) and values, under the end-aligned causal mask."""
+    total_q, h, c = q_nope.shape
+    out = torch.zeros(total_q, h, c, device=q_nope.device, dtype=torch.float32)
+    lse = torch.full((total_q, h), float("-inf"), device=q_nope.device, dtype=torch.float32)
+    qo, kv = qo_indptr.tolist(), kv_indptr.tolist()
+    for r in range(len(qo) - 1):
+        n_q, n_kv = qo[r + 1] - qo[r], kv[r + 1] - kv[r]
+        if n_q <= 0 or n_kv <= 0:
+            continue
+        pages = kv_indices[kv[r]:kv[r + 1]].long()
+        kc, kp = ckv_cache[pages, 0].float(), kpe_cache[pages, 0].float()
+        qn, qp = q_nope[qo[r]:qo[r + 1]].float(), q_pe[qo[r]:qo[r + 1]].float()
+        logits = (torch.einsum("qhc,kc->qhk", qn, kc) + torch.einsum("qhp,kp->qhk", qp, kp)) * sm_scale
+        keep = torch.arange(n_kv, device=logits.device)[None, :] <= (n_kv - n_q) + torch.arange(n_q, device=logits.device)[:, None]
+        logits = logits.masked_fill(~keep[:, None, :], float("-inf"))
+        w, l = _finish(logits)
+        out[qo[r]:qo[r + 1]] = torch.einsum("qhk,kc->qhc", w, kc)
+        lse[qo[r]:qo[r + 1]] = l
+    return out.to(q_nope.dtype), lse
+
+
 def order_inputs_for_kernel(inputs_by_name: dict, kernel) -> list:
     """The tensors of ``inputs_by_name`` in the kernel's parameter order (by buffer name), as the
     reference orders them (python/cleave/runtime/reference.py:448-479)."""

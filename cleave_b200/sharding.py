@@ -100,10 +100,18 @@ def gemm_n_sharded(local_gemm, x, w_shards, n_total, *, gather=True, group=None)
         return y_local
     world, rank = dist.get_world_size(group), dist.get_rank(group)
     bounds = [n_shard(n_total, r, world) for r in range(world)]
-    width = max(hi - lo for lo, hi in bounds)
+    assert bounds[rank][1] - bounds[rank][0] == y_local.shape[1]
+    widths = {hi - lo for lo, hi in bounds}
+    if len(widths) == 1:
+        # equal shards (the usual case): one collective straight from the kernel's output into a
+        # (world, M, N / world) buffer, then one strided copy into the row-major (M, N) result
+        m = y_local.shape[0]
+        stacked = torch.empty((world, m, y_local.shape[1]), dtype=y_local.dtype, device=y_local.device)
+        dist.all_gather_into_tensor(stacked, y_local.contiguous(), group=group)
+        return stacked.permute(1, 0, 2).reshape(m, n_total)
+    width = max(widths)
     pad = torch.zeros((y_local.shape[0], width), dtype=y_local.dtype, device=y_local.device)
     pad[:, :y_local.shape[1]] = y_local
     bufs = [torch.empty_like(pad) for _ in range(world)]
     dist.all_gather(bufs, pad, group=group)
-    assert bounds[rank][1] - bounds[rank][0] == y_local.shape[1]
     return torch.cat([b[:, :hi - lo] for b, (lo, hi) in zip(bufs, bounds)], dim=1)

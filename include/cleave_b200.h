@@ -36,7 +36,8 @@ extern "C" {
  *    new entry points cb200_matmul_matmul, cb200_matmul_rowsum, cb200_lora. A binding written against
  *    version 1 must zero-fill the longer structs. */
 /* 3: cb200_workspace_status clears a reported fault; new cb200_workspace_reset,
- *    cb200_attn_decode_static_scratch_status, cb200_split_combine, cb200_attn_unnormalise; cb200_gemm_args gained
+ *    cb200_attn_decode_static_scratch_status, cb200_split_combine, cb200_attn_unnormalise, cb200_mla_prefill;
+ *    cb200_gemm_args gained
  *    the trailing field ldx (zero = the behaviour of version 2). */
 #define CB200_VERSION 3
 
@@ -373,6 +374,38 @@ typedef struct {
 
 size_t cb200_lora_workspace_bytes(const cb200_lora_args* a);
 int cb200_lora(const cb200_lora_args* a, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Paged causal MLA prefill (absorbed latent), one token per page:
+ *   S = (Q_nope CKV^T + Q_pe KPE^T) * scale under the end-aligned causal mask (query i of a request with q_len
+ *   queries and kv_len keys sees keys <= i + kv_len - q_len), O = softmax(S) CKV, plus the base-2 log-sum-exp.
+ * Rows without a visible key give 0 and -inf.
+ *
+ * Replaces tests/graph/handwritten/expected_kernels/mla_paged_prefill_causal_h16_ckv512_kpe64_ps1.py
+ * (python/cleave/dynamic/paging/builders/mla.py:393); argument order and meaning follow
+ * python/cleave/dynamic/reference.py:324-365. A query-tile kernel on tcgen05: 128 / num_heads consecutive query
+ * tokens times their heads are the 128 rows of every MMA, so num_heads must divide 128. The workspace holds the
+ * status word only (cb200_workspace_status).
+ * ---------------------------------------------------------------------------------------- */
+typedef struct {
+  const void* q_nope;    /* (total_q, num_heads, 512) */
+  const void* q_pe;      /* (total_q, num_heads, 64) */
+  const void* ckv_cache; /* (num_pages, 1, 512) */
+  const void* kpe_cache; /* (num_pages, 1, 64) */
+  const int32_t* qo_indptr;  /* (batch + 1) query-row offsets */
+  const int32_t* kv_indptr;  /* (batch + 1) offsets into kv_indices */
+  const int32_t* kv_indices; /* (num_kv_indices) page id per token */
+  void* out;             /* (total_q, num_heads, 512) */
+  float* lse;            /* (total_q, num_heads), may be NULL */
+  void* workspace;
+  size_t workspace_bytes;
+  int32_t batch, total_q, num_heads, ckv_dim, kpe_dim, num_pages, num_kv_indices;
+  int32_t dtype;         /* cb200_dtype */
+  float sm_scale;
+} cb200_mla_prefill_args;
+
+size_t cb200_mla_prefill_workspace_bytes(const cb200_mla_prefill_args* a);
+int cb200_mla_prefill(const cb200_mla_prefill_args* a, void* stream);
 
 /* ------------------------------------------------------------------------------------------
  * The two-stage form of a split (compatibility with the reference's partial + combine kernel pairs; the

@@ -232,7 +232,7 @@ def mla_paged_decode_case(batch=64, heads=16, lo=512, hi=8192, dtype=torch.bfloa
     return fn, flops, byts
 
 
-def mla_prefill_case(batch=4, q_len=512, heads=16, dtype=torch.bfloat16):
+def mla_prefill_case(batch=4, q_len=512, heads=16, dtype=torch.bfloat16, impl="auto"):
     """Paged causal MLA prefill, whole prompts (q_len = kv_len), one token per page."""
     g = _gen()
     tq = batch * q_len
@@ -247,7 +247,7 @@ def mla_prefill_case(batch=4, q_len=512, heads=16, dtype=torch.bfloat16):
     lse = torch.empty(tq, heads, dtype=torch.float32, device="cuda")
     flops = 2 * batch * heads * (q_len * (q_len + 1) // 2) * (576 + 512)
     byts = (qn.numel() + qp.numel() + ckv.numel() + kpe.numel() + out.numel()) * 2
-    fn = lambda: ops.mla_paged_prefill(qn, qp, ckv, kpe, ptr, ptr, idx, 0.1352337747812271, out=out, lse=lse)  # noqa: E731
+    fn = lambda: ops.mla_paged_prefill(qn, qp, ckv, kpe, ptr, ptr, idx, 0.1352337747812271, out=out, lse=lse, impl=impl)  # noqa: E731
     return fn, flops, byts
 
 
@@ -273,6 +273,8 @@ CONFIGS = {
     "gqa_paged_prefill_causal_h32_kv8_d128_ps1_b8_q2048": lambda: gqa_dynamic_prefill_case(True),
     "mla_paged_decode_h16_ps1_b64_kv512_8192": lambda: mla_paged_decode_case(),
     "mla_paged_prefill_causal_h16_b4_q512": lambda: mla_prefill_case(),
+    "mla_paged_prefill_causal_h16_b4_q512_per_token": lambda: mla_prefill_case(impl="per_token"),
+    "mla_paged_prefill_causal_h16_b8_q2048": lambda: mla_prefill_case(batch=8, q_len=2048),
     "gqa_paged_decode_ps1_b64_kv512_8192": lambda: paged_decode_case(1),
     "gqa_paged_decode_ps16_b64_kv512_8192": lambda: paged_decode_case(16),
     "gqa_paged_decode_ps32_b64_kv512_8192": lambda: paged_decode_case(32),

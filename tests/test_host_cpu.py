@@ -308,3 +308,24 @@ def test_kernel_text_of_the_remaining_demo_operators_round_trips():
         assert back.family == family and back.dims == dims and [p.name for p in back.params] == [p.name for p in spec.params]
     assert [p.name for p in make_spec("lora", "float16", {"M": 16, "N": 4096, "K": 4096, "R": 16}).params] == [
         "PlaceHolder_x", "PlaceHolder_w", "PlaceHolder_a", "PlaceHolder_b", "OutputNode"]
+
+
+def test_calibrate_dispatch_threshold_rule():
+    """The reference's rule (python/cleave/pipeline/dynamic.py:209-242): the threshold with the best hybrid
+    geomean over the observed tile counts, the smallest one on a tie, result fields kept."""
+    from cleave_b200.core.errors import CleaveError
+    from cleave_b200.pipeline.dynamic import WorkloadCandidate, calibrate_dispatch
+
+    tiles = {"a": 1, "b": 4, "c": 32, "d": 128}
+    pair = WorkloadCandidate("full grid", "", latency_us={"a": 9.0, "b": 9.0, "c": 10.0, "d": 20.0})
+    solo = WorkloadCandidate("small grid", "", latency_us={"a": 5.0, "b": 6.0, "c": 30.0, "d": 200.0})
+    d = calibrate_dispatch(pair, solo, tiles, kv_tile=64, page_size=16, indptr_index=3)
+    assert d["min_tiles"] == 32 and d["split_runs"] == 2 and d["n_workloads"] == 4 and d["applied"]
+    assert d["geomean_us"]["hybrid"] == pytest.approx((5.0 * 6.0 * 10.0 * 20.0) ** 0.25)
+    assert (d["split_label"], d["single_label"], d["page_size"], d["kv_tile"]) == ("full grid", "small grid", 16, 64)
+    # the full grid wins everywhere: threshold 1 (ties go to the smallest), nothing to apply
+    never = WorkloadCandidate("small grid", "", latency_us={k: 50.0 for k in tiles})
+    d2 = calibrate_dispatch(pair, never, tiles)
+    assert d2["min_tiles"] == 1 and d2["split_runs"] == 4 and not d2["applied"]
+    with pytest.raises(CleaveError):
+        calibrate_dispatch(pair, WorkloadCandidate("x", ""), tiles)

@@ -139,25 +139,53 @@ def test_static_mla_after_a_kernel_that_appends_to_the_caches(impl):
         torch.cuda.synchronize()
 
 
-def test_paged_causal_mla_prefill_matches_reference_golden_and_oracle():
+@pytest.mark.parametrize("impl", ["tile", "per_token"])
+def test_paged_causal_mla_prefill_matches_reference_golden_and_oracle(impl):
     """Reference: python/cleave/dynamic/reference.py:324-365 (mla_paged_prefill_causal_h16_ckv512_kpe64_ps1):
     the golden case from the reference's own definition, and a second seeded case against the oracle with
-    requests without queries, without keys, and with more queries than keys."""
+    requests without queries, without keys, and with more queries than keys. Both implementations: the
+    tcgen05 query-tile kernel and the per-token form on the paged decode kernel."""
     ops = _ops()
     _, inp, opt = cases.build("mla_paged_prefill_bf16")
     i32 = lambda a: torch.from_numpy(a).cuda()  # noqa: E731
     out, lse = ops.mla_paged_prefill(dev(inp["q_nope"], "bf16"), dev(inp["q_pe"], "bf16"), dev(inp["ckv_cache"], "bf16"),
                                      dev(inp["kpe_cache"], "bf16"), i32(inp["qo_indptr"]), i32(inp["kv_indptr"]),
-                                     i32(inp["kv_indices"]), inp["sm_scale"])
+                                     i32(inp["kv_indices"]), inp["sm_scale"], impl=impl)
     _check_ws()
+    ops.check_workspace(ops.workspace("mla_prefill", 0, "cuda"))
     assert_close(host(out), GOLDEN["mla_paged_prefill_bf16"][0])
     assert_lse_close(host(lse), GOLDEN["mla_paged_prefill_bf16"][1])
     inp = cases.mla_prefill_inputs(9, [33, 200, 0, 7, 20], [64, 260, 5, 0, 12], 16, 512, 64, "bf16", cases.MLA_SM_SCALE)
     out, lse = ops.mla_paged_prefill(dev(inp["q_nope"], "bf16"), dev(inp["q_pe"], "bf16"), dev(inp["ckv_cache"], "bf16"),
                                      dev(inp["kpe_cache"], "bf16"), i32(inp["qo_indptr"]), i32(inp["kv_indptr"]),
-                                     i32(inp["kv_indices"]), inp["sm_scale"])
+                                     i32(inp["kv_indices"]), inp["sm_scale"], impl=impl)
     _check_ws()
+    ops.check_workspace(ops.workspace("mla_prefill", 0, "cuda"))
     want, want_lse = orc.mla_paged_prefill(inp["q_nope"], inp["q_pe"], inp["ckv_cache"], inp["kpe_cache"], inp["qo_indptr"],
                                            inp["kv_indptr"], inp["kv_indices"], inp["sm_scale"])
     assert_close(host(out), want)
     assert_lse_close(host(lse), want_lse)
+
+
+@pytest.mark.parametrize("heads,dt", [(16, "f16"), (32, "bf16"), (128, "bf16"), (8, "bf16")])
+def test_mla_prefill_tile_kernel_vs_oracle(heads, dt):
+    """The query-tile kernel over head counts that pack 8, 4, 1 and 16 query tokens into the 128 MMA rows, with
+    query lengths that are not multiples of the block, prefixes longer than a KV tile, chunked prefill
+    (fewer queries than keys) and the two implementations agreeing with each other."""
+    ops = _ops()
+    q_lens, kv_lens = [130, 1, 257, 40, 0], [130, 300, 257, 1000, 9]
+    inp = cases.mla_prefill_inputs(40 + heads, q_lens, kv_lens, heads, 512, 64, dt, cases.MLA_SM_SCALE)
+    i32 = lambda a: torch.from_numpy(a).cuda()  # noqa: E731
+    args = (dev(inp["q_nope"], dt), dev(inp["q_pe"], dt), dev(inp["ckv_cache"], dt), dev(inp["kpe_cache"], dt),
+            i32(inp["qo_indptr"]), i32(inp["kv_indptr"]), i32(inp["kv_indices"]), inp["sm_scale"])
+    out, lse = ops.mla_paged_prefill(*args, impl="tile")
+    ops.check_workspace(ops.workspace("mla_prefill", 0, "cuda"))
+    want, want_lse = orc.mla_paged_prefill(inp["q_nope"], inp["q_pe"], inp["ckv_cache"], inp["kpe_cache"], inp["qo_indptr"],
+                                           inp["kv_indptr"], inp["kv_indices"], inp["sm_scale"], dtype=dt)
+    assert_close(host(out), want)
+    assert_lse_close(host(lse), want_lse)
+    out2, lse2 = ops.mla_paged_prefill(*args, impl="per_token")
+    _check_ws()
+    assert_close(host(out), host(out2))
+    out3, _ = ops.mla_paged_prefill(*args, impl="tile")
+    assert torch.equal(out, out3)   # repeat launches are bit-identical

@@ -1,6 +1,8 @@
 """End-to-end ``compile`` on the GPU: candidates are validated and timed, the best becomes a
 callable Kernel that can be saved, loaded and cached; paged operators return a PagedKernel."""
 
+import json
+
 import numpy as np
 import pytest
 import torch
@@ -106,7 +108,14 @@ def test_compile_paged_gqa_decode(tmp_path, page_size):
     dims = dict(num_qo_heads=32, num_kv_heads=8, head_dim=128, page_size=page_size)
     wl = [("a", [700, 1, 129, 64]), ("b", [5, 0, 7]), ("c", [3000] * 3)]
     k = cleave.compile("gqa_paged_decode", dtype="bfloat16", workloads=wl, **dims)
-    assert k.report.n_workloads == 3 and k.report.best() is not None and k.dispatch is None
+    assert k.report.n_workloads == 3 and k.report.best() is not None
+    # the split / single question of the reference's calibrate_dispatch, measured on the persistent kernel
+    # (reference: python/cleave/pipeline/dynamic.py:209-242; persisted as in tests/frontend_dynamic/test_paged_trace.py:281-328)
+    d = k.dispatch
+    assert d is k.report.dispatch and d["n_workloads"] == 3 and 1 <= d["min_tiles"] <= 48
+    assert set(d["geomean_us"]) == {"hybrid", "split", "single"} and d["geomean_us"]["hybrid"] <= d["geomean_us"]["split"] + 1e-9
+    assert d["page_size"] == page_size and d["kv_tile"] == 64 and d["indptr_index"] == 3 and isinstance(d["applied"], bool)
+    assert "dispatch" in k.report.summary()
     args = make_inputs("gqa_paged_decode", dims, [700, 1, 129, 64], "bfloat16", seed=5)
     want_out, want_lse = reference("gqa_paged_decode", args)
     out, lse = k(*args)
@@ -125,6 +134,19 @@ def test_compile_paged_gqa_decode(tmp_path, page_size):
     loaded = cleave.load(k.save(tmp_path / "paged"))
     out3, lse3 = loaded(*args)
     assert torch.equal(out, out3) and torch.equal(lse, lse3)
+    assert (tmp_path / "paged" / "dispatch.json").exists() and loaded.dispatch == json.loads(json.dumps(d))
+    # scratch is owned by the compiled kernel's wrapper and allocated once: a further call allocates nothing
+    # (reference: tests/graph/handwritten/test_splitkv_decode.py:85-111)
+    owner = k.compile()._compiled
+    assert owner.scratch_bytes > 0 and len(owner.workspaces) >= 1
+    outs = [torch.empty_like(out), torch.empty_like(lse)]
+    kept = [a for a in args if a is not None]
+    owner(*kept, *outs)
+    torch.cuda.synchronize()
+    before = torch.cuda.memory_allocated()
+    owner(*kept, *outs)
+    torch.cuda.synchronize()
+    assert torch.cuda.memory_allocated() == before and torch.equal(outs[0], out)
 
 
 def test_compile_paged_mla_decode_and_refusals():
@@ -145,7 +167,7 @@ def test_compile_paged_mla_decode_and_refusals():
         cleave.compile("mla_paged_decode", num_qo_heads=16, head_dim_ckv=256, head_dim_kpe=64)
 
 
-@pytest.mark.parametrize("op", ["gqa_ragged_prefill_causal", "gqa_paged_prefill_causal"])
+@pytest.mark.parametrize("op", ["gqa_ragged_prefill_causal", "gqa_paged_prefill_causal", "mla_paged_prefill_causal"])
 def test_compile_causal_prefill_operators(tmp_path, op):
     """The ragged and paged causal prefill operators of the reference's registry
     (python/cleave/dynamic/registry.py) through the same compile / call / save / load path."""
@@ -154,6 +176,8 @@ def test_compile_causal_prefill_operators(tmp_path, op):
 
     family = OPERATORS[op][0]
     dims = dict(num_qo_heads=8, num_kv_heads=2, head_dim=64)
+    if family == "mla_paged_prefill":
+        dims = dict(num_qo_heads=16, head_dim_ckv=512, head_dim_kpe=64)
     wl = [("a", ([100, 0, 300], [300, 50, 300])), ("b", ([1], [129])), ("c", ([257, 5], [600, 5]))]
     k = cleave.compile(op, dtype="bfloat16", workloads=wl, **dims)
     assert k.report.n_workloads == 3 and k.report.best() is not None

@@ -47,6 +47,11 @@ class GemmArgs(C.Structure):
     ]
 
 
+class GemmPlanInfo(C.Structure):
+    _fields_ = [("tile_m", C.c_int32), ("tile_n", C.c_int32), ("split", C.c_int32), ("kind", C.c_int32),
+                ("grid", C.c_int32), ("estimate_us", C.c_float)]
+
+
 class MlaPrefillArgs(C.Structure):
     _fields_ = [
         ("q_nope", C.c_void_p), ("q_pe", C.c_void_p), ("ckv_cache", C.c_void_p), ("kpe_cache", C.c_void_p),
@@ -175,6 +180,8 @@ def lib() -> C.CDLL:
         L.cb200_gemm_workspace_bytes.argtypes = [C.POINTER(GemmArgs)]
         L.cb200_gemm_effective_split.restype = C.c_int
         L.cb200_gemm_effective_split.argtypes = [C.POINTER(GemmArgs)]
+        L.cb200_gemm_plan.restype = C.c_int
+        L.cb200_gemm_plan.argtypes = [C.POINTER(GemmArgs), C.POINTER(GemmPlanInfo)]
         L.cb200_gemm.restype = C.c_int
         L.cb200_gemm.argtypes = [C.POINTER(GemmArgs), C.c_void_p]
         L.cb200_mla_prefill_workspace_bytes.restype = C.c_size_t

@@ -91,3 +91,33 @@ def tmem_columns_needed(tile: tuple, accumulators: int = 2) -> int:
     GEMM kernels double-buffer the accumulator so that the epilogue of one tile overlaps the main loop of
     the next; 2 x 256 columns fills the 512 columns of an SM."""
     return accumulators * tile[1]
+
+
+class TCPolicyB200:
+    """Scores GEMM-family plans for sm_100 with the cost model the kernels themselves plan by (the role of the
+    reference's ``TCPolicy``, python/cleave/schedule/policy/default.py:1015-1110, which scores tilings for sm_90).
+    A candidate here is what the backend honours of a plan: operator, extents and split factor; the score is the
+    model's estimate in microseconds for the tile, cluster or pair plan the library would run for it. It needs the
+    built library and a visible GPU (the plan depends on the SM count and on how many clusters fit at once)."""
+
+    KIND = {0: "tiles", 1: "cluster split-K", 2: "CTA pairs"}
+    OPS = {"matmul": 0, "rmsnorm_matmul": 1, "swiglu": 2}
+
+    def plan(self, family: str, dims: dict, dtype: str = "float16", split: int = 0) -> dict:
+        import ctypes as C
+
+        from . import _lib
+
+        a, info = _lib.GemmArgs(), _lib.GemmPlanInfo()
+        a.m, a.n, a.k, a.op = int(dims["M"]), int(dims["N"]), int(dims["K"]), self.OPS[family]
+        a.dtype, a.split_k = (_lib.F16 if dtype in ("float16", "f16") else _lib.BF16), int(split if split > 1 else 0)
+        _lib.check(_lib.lib().cb200_gemm_plan(C.byref(a), C.byref(info)))
+        return {"tile": (info.tile_m, info.tile_n), "split": info.split, "kind": self.KIND[info.kind], "grid": info.grid,
+                "estimate_us": float(info.estimate_us)}
+
+    def rank(self, specs) -> list:
+        """``[(estimate_us, spec)]`` for kernel specs of the GEMM family, best first: the order a scheduler should
+        offer its candidates in, instead of the order an sm_90 policy scored them in."""
+        scored = [(self.plan(s.family, s.dims, s.dtype, s.split)["estimate_us"], i, s) for i, s in enumerate(specs)
+                  if s.family in self.OPS]
+        return [(us, s) for us, _, s in sorted(scored)]

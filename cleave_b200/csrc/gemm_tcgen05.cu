@@ -678,6 +678,7 @@ struct GemmSetup {
   bool pair;     // whole 256 x 256 tiles on CTA pairs (gemm_pair.cu)
   int pair_ks;   // pairs per cluster: the K split of the pair kernel
   size_t ws_needed, partials_off, counters_off, prepass_off;
+  double estimate_us;  // the cost model's estimate for the plan that was chosen
   CUtensorMap tm_a, tm_b0, tm_b1, tm_a2;
 };
 
@@ -792,10 +793,21 @@ int plan_gemm(const cb200_gemm_args* a, GemmSetup* s, bool need_maps) {
     if (t_single == 0.0) t_single = static_cast<double>((tiles + grid_max - 1) / grid_max) * p.kblocks * (s->nbw == 4 || a->op == CB200_GEMM_SWIGLU ? 0.56 : 0.33);
     s->pair = t_pair > 0.0 && t_pair < t_single && !a->addend && a->dependent_launch <= 1 && !ext;  // the pair kernel has no addend and no second operand pair; mode 1 is only a permission, the pair launch stays an ordinary one
   }
+  {
+    // the estimate of the plan that runs: the model's own for automatic plans; for an explicit split factor the
+    // same per-block costs plus the workspace fix-up of every cut tile (a few microseconds, once per wave)
+    const double kb_us = (s->nbw == 4 || a->op == CB200_GEMM_SWIGLU) ? 0.56 : 0.33;
+    const int rows_live = a->m < kBM ? a->m : kBM;
+    const double kb_mem_us = (rows_live * kBK * 2.0 + s->nbw * kChunkN * (a->op == CB200_GEMM_SWIGLU ? 2 : 1) * kBK * 2.0) / 90000.0;
+    const double per_cta_blocks = static_cast<double>(chunks) * p.chunk_kblocks / s->grid;
+    s->estimate_us = best > 0.0 && split == auto_split ? best
+                                                       : per_cta_blocks * (kb_us > kb_mem_us ? kb_us : kb_mem_us) + (S > 1 ? 3.0 : 0.0);
+  }
   if (s->pair) {
     s->cluster = false;
     p.chunk_kblocks = p.kblocks;
     p.chunks_per_tile = 1;
+    s->estimate_us = gemm_pair_estimate_us(a, sms, &s->pair_ks);
   }
   s->partials_off = kWsHeaderBytes;
   s->counters_off = align_up(s->partials_off + static_cast<size_t>(sms) * 2 * kGemmSlotBytesMax, 256);
@@ -964,6 +976,20 @@ extern "C" int cb200_gemm_effective_split(const cb200_gemm_args* a) {
   cb200::GemmSetup s;
   if (cb200::plan_gemm(a, &s, false) != CB200_OK) return 0;
   return s.p.chunks_per_tile;
+}
+
+extern "C" int cb200_gemm_plan(const cb200_gemm_args* a, cb200_gemm_plan_info* out) {
+  cb200::GemmSetup s;
+  if (!out) return CB200_ERR_BAD_ARG;
+  const int rc = cb200::plan_gemm(a, &s, false);
+  if (rc != CB200_OK) return rc;
+  out->tile_m = s.pair ? 256 : cb200::kBM;
+  out->tile_n = s.pair ? 256 : s.nbw * cb200::kChunkN;
+  out->split = s.pair ? s.pair_ks : s.p.chunks_per_tile;
+  out->kind = s.pair ? 2 : (s.cluster ? 1 : 0);
+  out->grid = s.grid;
+  out->estimate_us = static_cast<float>(s.estimate_us);
+  return CB200_OK;
 }
 
 extern "C" int cb200_gemm(const cb200_gemm_args* a, void* stream) {

@@ -17,15 +17,19 @@
 //                rows gathered through kv_indices by four warps with 16-byte cp.async into the 128-byte
 //                swizzled layout); D = S in tensor memory, two buffers of 128 columns
 //   O += P V     A = P (16-bit pairs the softmax warps store over the first 64 columns of the S buffer they
-//                just read), B = the CTA's 256 latent columns of the same 128 tokens, MN-major in shared
-//                memory (gathered by four more warps), D = O in tensor memory (256 columns)
+//                just read), B = the CTA's 256 latent columns of the same 128 tokens, D = O in tensor memory
+//                (256 columns). Those columns are four of the nine score chunks, and a K-major chunk of 128
+//                token rows x 128 bytes is byte for byte the MN-major value operand: the four chunks are
+//                gathered into a value buffer (two buffers, one per tile in flight) instead of the ring, serve
+//                the score product first and the value product afterwards, and are fetched once
 // Tensor memory: S/P 0 | S/P 1 | O = 128 + 128 + 256 columns. MMAs of one thread execute in order, so the
 // score product of tile j + 2, which overwrites the buffer P(j) lives in, cannot pass the value product that
 // reads it. The softmax keeps a reference maximum per row and rescales O only when the running maximum grew
 // by more than 2^8 (exact), as the GQA prefill kernel does.
 //
 // Warp roles: 0 = Q-chunk TMA producer, 1 = MMA issuer and TMEM owner, 2..5 = softmax / epilogue (thread =
-// row = TMEM lane), 6..9 = cache-row gather for the score chunks, 10..13 = gather of the value tile.
+// row = TMEM lane), 6..9 = cache-row gather. The tile loop is bound by what an SM can pull from L2 (the Q
+// chunks are streamed again for every KV tile: Q, a tile and the accumulators do not fit on one SM together).
 //
 // Reference semantics: python/cleave/dynamic/reference.py:324-365; replaces
 // tests/graph/handwritten/expected_kernels/mla_paged_prefill_causal_h16_ckv512_kpe64_ps1.py
@@ -45,10 +49,11 @@ constexpr int kBM = 128, kBN = 128;          // rows per item, tokens per KV til
 constexpr int kDV = 256;                     // output columns per CTA
 constexpr int kChunkBytes = 128 * 128;       // 128 rows x 128 bytes
 constexpr int kStageBytes = 2 * kChunkBytes; // Q chunk + cache chunk
-constexpr int kStages = 5;        // 160 KB of chunk pairs in flight: the tile loop is bound by the latency of its loads
-constexpr int kVBytes = (kDV / 64) * kChunkBytes;  // 64 KB
-constexpr int kSmemBytes = kStages * kStageBytes + kVBytes + 1024 /*barriers*/ + 1024 /*alignment*/;
-constexpr int kThreads = 14 * 32;
+constexpr int kStages = 3;
+constexpr int kVChunks = kDV / 64;           // the score chunks that are this CTA's value columns
+constexpr int kVBytes = kVChunks * kChunkBytes;    // 64 KB, two buffers
+constexpr int kSmemBytes = kStages * kStageBytes + 2 * kVBytes + 1024 /*barriers*/ + 1024 /*alignment*/;
+constexpr int kThreads = 10 * 32;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.f;     // log2 units
 constexpr uint32_t kColS = 0, kColO = 256;
@@ -74,12 +79,10 @@ mla_prefill_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_const
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* ring = smem;
   uint8_t* v_smem = ring + kStages * kStageBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(v_smem + kVBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(v_smem + 2 * kVBytes);
   uint64_t* k_full = bars;              // [kStages] Q chunk landed (TMA) and cache rows landed (128 gather threads)
   uint64_t* k_empty = k_full + kStages; // [kStages] the score MMAs have read the stage
-  uint64_t* v_full = k_empty + kStages; // value tile gathered
-  uint64_t* v_empty = v_full + 1;       // the value MMAs have read it
-  uint64_t* s_full = v_empty + 1;       // [2] S complete in tensor memory
+  uint64_t* s_full = k_empty + kStages; // [2] S complete in tensor memory
   uint64_t* p_full = s_full + 2;        // [2] P stored (and O rescaled if needed)
   uint64_t* pv_done = p_full + 2;       // [2] the value MMAs of a tile have completed
   uint64_t* o_done = pv_done + 2;
@@ -115,8 +118,6 @@ mla_prefill_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_const
       mbar_init(&k_full[s], 129);  // 128 gather threads + the TMA thread's expect-tx arrival
       mbar_init(&k_empty[s], 1);
     }
-    mbar_init(v_full, 128);
-    mbar_init(v_empty, 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(&s_full[s], 1);
       mbar_init(&p_full[s], 4);
@@ -142,12 +143,19 @@ mla_prefill_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_const
     return min(max(__ldg(p.kv_indices + i), 0), p.num_pages - 1);
   };
 
+  // The nine score chunks of a tile in the order they are streamed: the five that are only keys first, then
+  // the four that are also this CTA's value columns (their buffer is free once the value product of the tile
+  // two back has completed, which the later they come the more surely has happened).
+  auto chunk_at = [&](int i) { return i < kChunks - kVChunks ? (dh == 0 ? kVChunks + i : (i < kVChunks ? i : kChunks - 1))
+                                                             : dh * kVChunks + (i - (kChunks - kVChunks)); };
+
   if (warp == 0) {
     // ================================================================ Q chunks by TMA
     const int row0 = (q_base + q0) * p.heads;  // first row of the block in the (total_q * H, .) view
     int st = 0, ph = 0;
     for (int j = 0; j < nt; ++j) {
-      for (int c = 0; c < kChunks; ++c) {
+      for (int i = 0; i < kChunks; ++i) {
+        const int c = chunk_at(i);
         mbar_wait(&k_empty[st], ph ^ 1, p.status, kFaultEmptyBarrier);
         if (lane == 0) {
           mbar_arrive_expect_tx(&k_full[st], kChunkBytes);
@@ -166,13 +174,28 @@ mla_prefill_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_const
     const T* ckv = reinterpret_cast<const T*>(p.ckv);
     const T* kpe = reinterpret_cast<const T*>(p.kpe);
     int st = 0, ph = 0;
-    for (int j = 0; j < nt; ++j) {
-      int pg[8];
+    int pg[8], pg_next[8];
+    if (nt > 0) {
 #pragma unroll
-      for (int rr = 0; rr < 8; ++rr) pg[rr] = page_of(j * kBN + rr * 16 + r_in);
-      for (int c = 0; c < kChunks; ++c) {
+      for (int rr = 0; rr < 8; ++rr) pg_next[rr] = page_of(rr * 16 + r_in);
+    }
+    for (int j = 0; j < nt; ++j) {
+#pragma unroll
+      for (int rr = 0; rr < 8; ++rr) pg[rr] = pg_next[rr];
+      if (j + 1 < nt) {  // one tile ahead: the latency of the index loads stays off the stream
+#pragma unroll
+        for (int rr = 0; rr < 8; ++rr) pg_next[rr] = page_of((j + 1) * kBN + rr * 16 + r_in);
+      }
+      for (int i = 0; i < kChunks; ++i) {
+        const int c = chunk_at(i);
         mbar_wait(&k_empty[st], ph ^ 1, p.status, kFaultEmptyBarrier);
-        const uint32_t dst = smem_u32(ring + st * kStageBytes + kChunkBytes);
+        uint32_t dst = smem_u32(ring + st * kStageBytes + kChunkBytes);
+        if (i >= kChunks - kVChunks) {
+          // a chunk that is also value columns goes to the tile's value buffer, which the value product of
+          // tile j - 2 must have finished reading
+          if (i == kChunks - kVChunks && j >= 2) mbar_wait(&pv_done[j & 1], ((j >> 1) - 1) & 1, p.status, kFaultMmaBarrier);
+          dst = smem_u32(v_smem + (j & 1) * kVBytes + (i - (kChunks - kVChunks)) * kChunkBytes);
+        }
 #pragma unroll
         for (int rr = 0; rr < 8; ++rr) {
           const int row = rr * 16 + r_in;
@@ -185,29 +208,6 @@ mla_prefill_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_const
         if (++st == kStages) { st = 0; ph ^= 1; }
       }
     }
-  } else if (warp >= 10) {
-    // ================================================================ value tile: 128 tokens x this CTA's 256 columns
-    // a row's 512 bytes are 32 pieces: the 128 threads cover 4 rows per round
-    const int gtid = tid - 10 * 32, piece = gtid & 31, r_in = gtid >> 5;
-    const T* ckv = reinterpret_cast<const T*>(p.ckv) + dh * kDV;
-    const uint32_t dst = smem_u32(v_smem);
-    for (int j = 0; j < nt; ++j) {
-      mbar_wait(v_empty, (j & 1) ^ 1, p.status, kFaultEmptyBarrier);
-#pragma unroll 1
-      for (int r0 = 0; r0 < kBN; r0 += 32) {
-        int pg[8];
-#pragma unroll
-        for (int rr = 0; rr < 8; ++rr) pg[rr] = page_of(j * kBN + r0 + rr * 4 + r_in);
-#pragma unroll
-        for (int rr = 0; rr < 8; ++rr) {
-          const int row = r0 + rr * 4 + r_in;
-          const T* src = ckv + static_cast<long long>(pg[rr]) * kCkv + piece * 8;
-          const uint32_t o = (piece >> 3) * kChunkBytes + row * 128 + (((piece & 7) ^ (row & 7)) << 4);
-          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + o), "l"(src) : "memory");
-        }
-      }
-      asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(v_full)) : "memory");
-    }
   } else if (warp == 1) {
     // ================================================================ MMA issuer
     constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
@@ -217,16 +217,18 @@ mla_prefill_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_const
     int st = 0, ph = 0;
     auto issue_s = [&](int j) {
       const uint32_t d = tmem_base + kColS + (j & 1) * kBN;
-      for (int c = 0; c < kChunks; ++c) {
+      for (int i = 0; i < kChunks; ++i) {
         mbar_wait(&k_full[st], ph, p.status, kFaultFullBarrier);
         tc_fence_after();
         if (lane == 0) {
           const uint32_t a = ring_addr + st * kStageBytes;
+          const uint32_t b = i < kChunks - kVChunks ? a + kChunkBytes
+                                                    : v_addr + (j & 1) * kVBytes + (i - (kChunks - kVChunks)) * kChunkBytes;
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) {
             const uint64_t adesc = umma_smem_desc(a + kk * 32, 16, 8 * 128);
-            const uint64_t bdesc = umma_smem_desc(a + kChunkBytes + kk * 32, 16, 8 * 128);
-            umma_f16(d, adesc, bdesc, idesc_s, (c > 0 || kk > 0) ? 1u : 0u);
+            const uint64_t bdesc = umma_smem_desc(b + kk * 32, 16, 8 * 128);
+            umma_f16(d, adesc, bdesc, idesc_s, (i > 0 || kk > 0) ? 1u : 0u);
           }
           umma_commit(&k_empty[st]);
         }
@@ -240,17 +242,16 @@ mla_prefill_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_const
     for (int j = 0; j < nt; ++j) {
       if (j + 1 < nt) issue_s(j + 1);
       const int pb = j & 1;
-      mbar_wait(v_full, j & 1, p.status, kFaultFullBarrier);
       mbar_wait(&p_full[pb], (j >> 1) & 1, p.status, kFaultTmemBarrier);
       tc_fence_after();
       if (lane == 0) {
 #pragma unroll
         for (int ks = 0; ks < kBN / 16; ++ks) {
           // B: MN-major, 16 token rows of 128 bytes per step; 64-column chunks are kChunkBytes apart
-          const uint64_t bdesc = umma_smem_desc(v_addr + ks * 16 * 128, kChunkBytes, 8 * 128);
+          // the value chunks of this tile landed before its score product was issued
+          const uint64_t bdesc = umma_smem_desc(v_addr + pb * kVBytes + ks * 16 * 128, kChunkBytes, 8 * 128);
           umma_f16_ts(tmem_base + kColO, tmem_base + kColS + pb * kBN + ks * 8, bdesc, idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
         }
-        umma_commit(v_empty);
         umma_commit(&pv_done[pb]);
         if (j == nt - 1) umma_commit(o_done);
       }
@@ -269,32 +270,20 @@ mla_prefill_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_const
       const int sb = j & 1;
       mbar_wait(&s_full[sb], (j >> 1) & 1, p.status, kFaultMmaBarrier);
       tc_fence_after();
-      uint32_t rg[4][32];
-#pragma unroll
-      for (int q = 0; q < 4; ++q) tmem_ld_32x32(tmem_base + lane_field + kColS + sb * kBN + q * 32, rg[q]);
-      tmem_ld_wait();
+      // Two passes over the 128 scores of the row, 32 at a time from tensor memory (reads are cheap, registers
+      // are not): the maximum first, then exp2 and the 16-bit P values.
+      const uint32_t t_s = tmem_base + lane_field + kColS + sb * kBN;
       const int k0 = j * kBN;
+      const bool whole = k0 + kBN - 1 <= key_limit;  // the whole tile is visible to this row
       float mx = -INFINITY;
-      if (k0 + kBN - 1 <= key_limit) {  // whole tile visible to this row
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
+      for (int q = 0; q < 4; ++q) {
+        uint32_t rg[32];
+        tmem_ld_32x32(t_s + q * 32, rg);
+        tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const float v = __uint_as_float(rg[q][i]) * p.scale_log2;
-            rg[q][i] = __float_as_uint(v);
-            mx = fmaxf(mx, v);
-          }
-        }
-      } else {
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const float v = k0 + q * 32 + i <= key_limit ? __uint_as_float(rg[q][i]) * p.scale_log2 : -INFINITY;
-            rg[q][i] = __float_as_uint(v);
-            mx = fmaxf(mx, v);
-          }
-        }
+        for (int i = 0; i < 32; ++i)
+          if (whole || k0 + q * 32 + i <= key_limit) mx = fmaxf(mx, __uint_as_float(rg[i]) * p.scale_log2);
       }
       float alpha = 1.f;
       bool rescale = false;
@@ -320,20 +309,27 @@ mla_prefill_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_const
         }
         tmem_st_wait();
       }
-      // P goes over the first 64 columns of the S buffer this thread has just read into registers
+      // P goes over the first 64 columns of this S buffer: the 64 scores a half of P is made from are in
+      // registers before the 32 columns it lands on are overwritten (columns 0-31 come from scores 0-63,
+      // columns 32-63 from scores 64-127, which the first store does not touch)
       float psum = 0.f;
 #pragma unroll
       for (int hh = 0; hh < 2; ++hh) {
-        uint32_t pk[32];
+        uint32_t ra[32], rb[32], pk[32];
+        tmem_ld_32x32(t_s + hh * 64, ra);
+        tmem_ld_32x32(t_s + hh * 64 + 32, rb);
+        tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          const int c = hh * 64 + 2 * i;
-          const float p0 = fast_exp2(__uint_as_float(rg[c >> 5][c & 31]) - m_ref);
-          const float p1 = fast_exp2(__uint_as_float(rg[(c + 1) >> 5][(c + 1) & 31]) - m_ref);
+          const int c = 2 * i;  // scores c and c + 1 of this half
+          const uint32_t u0 = c < 32 ? ra[c] : rb[c - 32], u1 = c + 1 < 32 ? ra[c + 1] : rb[c + 1 - 32];
+          const int key = k0 + hh * 64 + c;
+          const float p0 = (whole || key <= key_limit) ? fast_exp2(__uint_as_float(u0) * p.scale_log2 - m_ref) : 0.f;
+          const float p1 = (whole || key + 1 <= key_limit) ? fast_exp2(__uint_as_float(u1) * p.scale_log2 - m_ref) : 0.f;
           psum += p0 + p1;
           pk[i] = pack2<T>(p0, p1);
         }
-        tmem_st_32x32(tmem_base + lane_field + kColS + sb * kBN + hh * 32, pk);
+        tmem_st_32x32(t_s + hh * 32, pk);
       }
       l_run = l_run * alpha + psum;
       tmem_st_wait();

@@ -36,7 +36,8 @@ extern "C" {
  *    new entry points cb200_matmul_matmul, cb200_matmul_rowsum, cb200_lora. A binding written against
  *    version 1 must zero-fill the longer structs. */
 /* 3: cb200_workspace_status clears a reported fault; new cb200_workspace_reset,
- *    cb200_attn_decode_static_scratch_status, cb200_split_combine, cb200_attn_unnormalise, cb200_mla_prefill;
+ *    cb200_attn_decode_static_scratch_status, cb200_split_combine, cb200_attn_unnormalise, cb200_mla_prefill,
+ *    cb200_gemm_plan;
  *    cb200_gemm_args gained
  *    the trailing field ldx (zero = the behaviour of version 2). */
 #define CB200_VERSION 3
@@ -174,6 +175,19 @@ typedef struct {
 } cb200_gemm_args;
 
 size_t cb200_gemm_workspace_bytes(const cb200_gemm_args* a);
+/* The plan the library would run for `a` (pointers are not read) and its cost model's estimate: the sm_100
+ * counterpart of the score the reference's tile policy gives a candidate
+ * (python/cleave/schedule/policy/default.py:1015-1110 scores tilings for sm_90 shared memory and wmma shapes).
+ * A scheduler can rank split factors with it before anything is built. */
+typedef struct {
+  int32_t tile_m, tile_n; /* output tile of one CTA (128 x 128 / 128 x 256) or of a CTA pair (256 x 256) */
+  int32_t split;          /* K parts per output tile that will really be used */
+  int32_t kind;           /* 0 = whole tiles or a stream-K walk with a workspace fix-up, 1 = the K parts of a tile are
+                             one thread-block cluster (reduced through distributed shared memory), 2 = CTA pairs */
+  int32_t grid;           /* CTAs */
+  float estimate_us;      /* the model's estimate for this plan */
+} cb200_gemm_plan_info;
+int cb200_gemm_plan(const cb200_gemm_args* a, cb200_gemm_plan_info* out);
 /* K chunks per output tile the launch will use (the requested split clamped to the K extent). */
 int cb200_gemm_effective_split(const cb200_gemm_args* a);
 int cb200_gemm(const cb200_gemm_args* a, void* stream);

@@ -295,7 +295,7 @@ def measure(name, build):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--op", default=None, choices=["matmul", "rmsnorm_matmul", "swiglu", "gqa_decode", "mla_decode", "attn_prefill", "gqa_paged_ps1",
-                                             "mla_paged_decode", "matmul_matmul", "qknorm", "matmul_rowsum", "lora"])
+                                             "mla_paged_decode", "mla_prefill", "matmul_matmul", "qknorm", "matmul_rowsum", "lora"])
     ap.add_argument("--m", type=int, default=4096)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
@@ -313,6 +313,8 @@ def main():
             build = lambda: paged_decode_case(1)  # noqa: E731
         elif a.op == "mla_paged_decode":
             build = mla_paged_decode_case
+        elif a.op == "mla_prefill":
+            build = lambda: mla_prefill_case(batch=8, q_len=2048)  # noqa: E731
         elif a.op == "matmul_matmul":
             build = lambda: fused_attn_case("matmul_matmul", 32, 32, 4096, 64)  # noqa: E731
         elif a.op == "qknorm":

@@ -138,6 +138,27 @@ def test_automatic_plans_for_the_benchmark_shapes():
     assert split(128, 128, 4096, split_k=4) == 4
 
 
+def test_sm100_policy_scores_and_ranks_gemm_candidates():
+    """The sm_100 counterpart of the reference's tile policy (python/cleave/schedule/policy/default.py:1015-1110):
+    the plan the kernels would run for a candidate and the cost model's estimate for it, and candidates ranked
+    by that estimate - a split of 16 beats no split on the 128 x 128 x 4096 product, whole CTA-pair tiles win
+    on a large square."""
+    from cleave_b200.arch import TCPolicyB200
+    from cleave_b200.codegen import make_spec
+
+    pol = TCPolicyB200()
+    small = pol.plan("matmul", {"M": 128, "N": 128, "K": 4096})
+    assert small["kind"] == "cluster split-K" and small["split"] == 16 and small["grid"] == 16 and small["estimate_us"] > 0
+    cfg2 = pol.plan("rmsnorm_matmul", {"M": 64, "N": 11008, "K": 4096})
+    assert (cfg2["kind"], cfg2["split"], cfg2["tile"], cfg2["grid"]) == ("cluster split-K", 3, (128, 256), 129)
+    big = pol.plan("matmul", {"M": 8192, "N": 8192, "K": 4096})
+    assert big["kind"] == "CTA pairs" and big["tile"] == (256, 256)
+    dims = {"M": 128, "N": 128, "K": 4096}
+    specs = [make_spec("matmul", "float16", dims, split=s) for s in (1, 4, 16)]
+    ranked = pol.rank(specs)
+    assert [s.split for _, s in ranked][0] == 16 and ranked[0][0] <= ranked[-1][0]
+
+
 def test_split_k_partials_sum_like_the_unsplit_product():
     """Reference: tests/pipeline_api/test_e2e.py:58-81 (the split-K chain equals x.float() @ w.float());
     here every split factor and every grid size must agree with the unsplit launch to fp32 round-off."""

@@ -19,8 +19,8 @@ import time
 import traceback
 from dataclasses import dataclass
 
-from ..core.errors import (BenchmarkError, CandidateTimeout, CleaveError, CodegenError, CompileError,
-                           ValidationError, WorkerCrash)
+from ..core.errors import (BenchmarkError, CandidateTimeout, CleaveError, CodegenError, CompileError,  # noqa: F401
+                           ValidationError, WorkerCrash, for_stage)
 
 _TRACEBACK_LINES = 20
 
@@ -50,7 +50,7 @@ def _short_traceback(text):
 
 def _typed_error(stage, label, exc_type, message, tb):
     text = "\n".join(x for x in (f"{label} failed with {exc_type}", message, _short_traceback(tb)) if x)
-    cls = {"validate": ValidationError, "bench": BenchmarkError, "codegen": CodegenError}.get(stage, CompileError)
+    cls = for_stage(stage)
     return cls(text)
 
 

@@ -140,7 +140,7 @@ class AttnPrefillRaggedArgs(C.Structure):
         ("out", C.c_void_p), ("lse", C.c_void_p), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("batch", C.c_int32), ("total_q", C.c_int32), ("total_kv", C.c_int32),
         ("num_qo_heads", C.c_int32), ("num_kv_heads", C.c_int32), ("head_dim", C.c_int32), ("dtype", C.c_int32),
-        ("causal", C.c_int32), ("sm_scale", C.c_float),
+        ("causal", C.c_int32), ("sm_scale", C.c_float), ("num_kv_indices", C.c_int32),
     ]
 
 

@@ -53,6 +53,7 @@ struct Params {
   const void* k_cache;   // paged: (num_pages, 1, HKV, D)
   const void* v_cache;
   int num_pages;
+  int n_idx;             // paged: entries of kv_indices (0 = not stated, ranges are trusted)
   int batch;             // ragged / paged: requests
   int hq, hkv, sq, skv, q_tiles, causal;
   float scale_log2;
@@ -112,6 +113,13 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     if (!found) return;  // the grid is an upper bound on the number of query tiles
     kv_base = __ldg(p.kv_indptr + r);
     skv = max(__ldg(p.kv_indptr + r + 1) - kv_base, 0);
+    if constexpr (MODE == 2) {
+      // the page table is caller data: a range that runs past its stated length is read as a shorter request
+      if (p.n_idx > 0) {
+        kv_base = min(max(kv_base, 0), p.n_idx);
+        skv = min(skv, p.n_idx - kv_base);
+      }
+    }
     q0 = t * kBM;
   } else {
     // late query tiles, which see the most keys under the causal mask, come first
@@ -617,6 +625,7 @@ int launch_prefill_ragged(const cb200_attn_prefill_ragged_args* a, cudaStream_t 
   p.k_cache = a->k;
   p.v_cache = a->v;
   p.num_pages = a->total_kv;
+  p.n_idx = a->kv_indices ? a->num_kv_indices : 0;
   p.batch = a->batch;
   p.hq = a->num_qo_heads;
   p.hkv = a->num_kv_heads;

@@ -55,17 +55,22 @@ struct Params {
   int* status;
   int* counters;
   float* partials;
-  int batch, heads, head_blocks, kv_len, paged, num_pages;
+  int batch, heads, head_blocks, kv_len, paged, num_pages, n_idx;
   float scale_log2;
 };
 
 // Token range of a paged request: from the (batch + 1) offsets, or from explicit per-request start and
 // length arrays (causal prefill runs one request per query token over a prefix of its sequence's pages).
-__device__ __forceinline__ int req_len(const Params& p, int b) {
-  return p.kv_lens ? max(__ldg(p.kv_lens + b), 0) : max(p.kv_indptr[b + 1] - p.kv_indptr[b], 0);
-}
+// The range is clipped to the n_idx entries kv_indices holds, so that offsets that run past the array are
+// read as a shorter request, never as memory beyond it.
 __device__ __forceinline__ int req_base(const Params& p, int b) {
-  return p.kv_start ? __ldg(p.kv_start + b) : p.kv_indptr[b];
+  const int base = p.kv_start ? __ldg(p.kv_start + b) : p.kv_indptr[b];
+  return min(max(base, 0), p.n_idx);
+}
+__device__ __forceinline__ int req_len(const Params& p, int b) {
+  const int base = p.kv_start ? __ldg(p.kv_start + b) : p.kv_indptr[b];
+  const int end = p.kv_lens ? base + max(__ldg(p.kv_lens + b), 0) : p.kv_indptr[b + 1];
+  return max(min(end, p.n_idx) - min(max(base, 0), p.n_idx), 0);
 }
 
 template <int NHB, bool GATHER>
@@ -586,6 +591,7 @@ int plan_mla(const cb200_mla_decode_args* a, MlaSetup* s, bool need_maps) {
   p.kv_len = a->kv_len;
   p.paged = paged ? 1 : 0;
   p.num_pages = a->num_pages;
+  p.n_idx = a->num_kv_indices;
   p.scale_log2 = a->sm_scale * kLog2e;
   s->gather = paged;
   const long long tiles_ub = paged ? (static_cast<long long>(a->num_kv_indices) + kTile - 1) / kTile + a->batch

@@ -298,6 +298,10 @@ def gqa_ragged_prefill(q, k, v, qo_indptr, kv_indptr, sm_scale, *, causal=True, 
     a.q, a.k, a.v, a.out, a.lse = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr()
     a.qo_indptr, a.kv_indptr = _cuda(qo_indptr, "qo_indptr").data_ptr(), _cuda(kv_indptr, "kv_indptr").data_ptr()
     a.kv_indices = kv_indices.data_ptr() if kv_indices is not None else None
+    if kv_indices is not None:
+        if kv_indices.dtype != torch.int32 or not kv_indices.is_contiguous() or kv_indices.device != q.device:
+            raise ValueError("kv_indices: a contiguous int32 tensor on q's device")
+        a.num_kv_indices = kv_indices.numel()  # ranges of kv_indptr are clipped to it on the device
     a.batch, a.total_q, a.total_kv = qo_indptr.numel() - 1, total_q, total_kv
     a.num_qo_heads, a.num_kv_heads, a.head_dim = hq, hkv, d
     a.dtype, a.causal, a.sm_scale = _dtype_code(q), int(bool(causal)), float(sm_scale)

@@ -40,7 +40,9 @@ extern "C" {
  *    cb200_gemm_plan;
  *    cb200_gemm_args gained
  *    the trailing field ldx (zero = the behaviour of version 2). */
-#define CB200_VERSION 3
+/* 4: cb200_attn_prefill_ragged_args gained the trailing field num_kv_indices (zero = the behaviour of
+ *    version 3); the paged MLA decode clips request ranges to num_kv_indices. */
+#define CB200_VERSION 4
 
 typedef enum {
   CB200_OK = 0,
@@ -308,6 +310,7 @@ typedef struct {
   int32_t dtype;    /* cb200_dtype */
   int32_t causal;   /* 1 = end-aligned causal mask per request */
   float sm_scale;
+  int32_t num_kv_indices; /* paged: entries of kv_indices; ranges of kv_indptr are clipped to it (0 = not stated, no clipping) */
 } cb200_attn_prefill_ragged_args;
 
 size_t cb200_attn_prefill_ragged_workspace_bytes(const cb200_attn_prefill_ragged_args* a);

@@ -77,6 +77,22 @@ def test_paged_mla_vs_oracle(h, max_ctas):
     assert_lse_close(lse, want_lse)
 
 
+def test_paged_mla_ranges_beyond_the_page_table_are_clipped():
+    """kv_indptr is caller data: ranges that run past the ``num_kv_indices`` entries of kv_indices are read as
+    shorter requests (the entries that exist), never as memory behind the table."""
+    lens = [300, 65, 2000, 900]
+    inp = cases.mla_paged_inputs(78, lens, 16, 512, 64, "bf16", cases.MLA_SM_SCALE)
+    keep = int(inp["kv_indptr"][2]) + 130   # request 2 keeps 130 of its tokens, request 3 none
+    inp["kv_indices"] = np.ascontiguousarray(inp["kv_indices"][:keep])
+    out, lse = _run_paged(inp, "bf16")
+    clipped = np.minimum(inp["kv_indptr"], keep).astype(np.int32)
+    want_out, want_lse = orc.mla_paged_decode(inp["q_nope"], inp["q_pe"], inp["ckv_cache"], inp["kpe_cache"],
+                                              clipped, inp["kv_indices"], inp["sm_scale"])
+    assert_close(out, want_out)
+    assert_lse_close(lse, want_lse)
+    assert (out[3] == 0).all() and np.isneginf(lse[3]).all()
+
+
 def test_static_mla_large_logits_rescale_path():
     """Logits that jump half-way along the sequence force the tensor-memory kernel through its
     rescale of the accumulator (the running maximum grows by far more than 2^8 between two tiles)."""

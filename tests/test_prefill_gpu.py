@@ -159,6 +159,29 @@ def test_paged_causal_prefill_vs_oracle(hq, hkv, d, dt):
     assert np.array_equal(host(out), host(out2)) and np.array_equal(host(lse), host(lse2))
 
 
+def test_paged_prefill_ranges_beyond_the_page_table_are_clipped():
+    """Ranges of kv_indptr that run past the entries kv_indices holds are read as shorter requests."""
+    hq, hkv, d, dt = 8, 2, 128, "bf16"
+    q_lens, kv_lens = [64, 130, 20], [200, 400, 300]
+    rng = np.random.default_rng(91)
+    tq, tk = sum(q_lens), sum(kv_lens)
+    q = cases.round_to(rng.standard_normal((tq, hq, d), dtype=np.float32), dt)
+    kc = cases.round_to(rng.standard_normal((tk, 1, hkv, d), dtype=np.float32), dt)
+    vc = cases.round_to(rng.standard_normal((tk, 1, hkv, d), dtype=np.float32), dt)
+    keep = 200 + 150                       # request 1 keeps 150 of its 400 keys, request 2 none
+    idx = rng.permutation(tk)[:keep].astype(np.int32)
+    qo = np.concatenate([[0], np.cumsum(q_lens)]).astype(np.int32)
+    kv = np.concatenate([[0], np.cumsum(kv_lens)]).astype(np.int32)
+    scale = d ** -0.5
+    out, lse = _ops().gqa_paged_prefill(dev(q, dt), dev(kc, dt), dev(vc, dt), torch.from_numpy(qo).cuda(),
+                                        torch.from_numpy(kv).cuda(), torch.from_numpy(idx).cuda(), scale)
+    _check_ws()
+    want, want_lse = orc.gqa_paged_prefill(q, kc, vc, qo, np.minimum(kv, keep).astype(np.int32), idx, scale, dt)
+    assert_close(host(out), want)
+    assert_lse_close(host(lse), want_lse)
+    assert (host(out)[qo[2]:] == 0).all() and np.isneginf(host(lse)[qo[2]:]).all()
+
+
 def test_ragged_long_requests():
     """Requests of several hundred query rows on 32 heads: several query tiles per request, more CTAs than SMs."""
     q_lens, kv_lens = [300, 700, 256, 513], [300, 1000, 600, 513]

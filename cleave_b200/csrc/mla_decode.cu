@@ -31,6 +31,10 @@ namespace cb200 {
 bool mla_tc_supported(const cb200_mla_decode_args* a);
 size_t mla_tc_partial_bytes(const cb200_mla_decode_args* a, int sms);
 int launch_mla_tc(const cb200_mla_decode_args* a, int* status, void* scratch, cudaStream_t stream);
+// mla_paged_tc.cu: the paged form with at most 16 heads on tcgen05 (tokens as MMA rows).
+bool mla_paged_tc_supported(const cb200_mla_decode_args* a);
+int launch_mla_paged_tc(const cb200_mla_decode_args* a, int* status, float* partials, int* counters, int grid,
+                        cudaStream_t stream);
 
 namespace mla {
 
@@ -566,7 +570,8 @@ namespace {
 struct MlaSetup {
   mla::Params p;
   int nhb, grid, smem_bytes;
-  bool gather, use_tc;
+  bool gather, use_tc, use_paged_tc;
+  int paged_tc_grid;
   size_t ws_needed, partials_off, counters_off, tc_partials_off;
   CUtensorMap tm_ckv, tm_kpe;
 };
@@ -617,7 +622,13 @@ int plan_mla(const cb200_mla_decode_args* a, MlaSetup* s, bool need_maps) {
   s->use_tc = mla_tc_supported(a) &&
               (a->impl == CB200_MLA_IMPL_TCGEN05 ||
                (a->impl == CB200_MLA_IMPL_AUTO && a->num_heads >= 64 && a->kv_len >= 512));
-  if (a->impl == CB200_MLA_IMPL_TCGEN05 && !s->use_tc) return CB200_ERR_UNSUPPORTED;
+  // paged caches with at most 16 heads: the tcgen05 kernel that takes the tokens as MMA rows
+  s->use_paged_tc = paged && a->impl != CB200_MLA_IMPL_MMA_SYNC && mla_paged_tc_supported(a);
+  {
+    const long long tiles = (static_cast<long long>(a->num_kv_indices) + 63) / 64 + a->batch;  // its tiles hold 64 tokens
+    s->paged_tc_grid = static_cast<int>(tiles < grid ? (tiles > 0 ? tiles : 1) : grid);
+  }
+  if (a->impl == CB200_MLA_IMPL_TCGEN05 && !s->use_tc && !s->use_paged_tc) return CB200_ERR_UNSUPPORTED;
   const size_t n_counters = static_cast<size_t>(a->batch) * (p.head_blocks > 2 * ceil_div(a->num_heads, 128)
                                                                 ? p.head_blocks : 2 * ceil_div(a->num_heads, 128));
   if (n_counters > kWsCounterSlots) {  // the scratch of the tcgen05 kernels would start inside the counters
@@ -704,6 +715,8 @@ extern "C" int cb200_mla_decode(const cb200_mla_decode_args* a, void* stream) {
   const int rc = plan_mla(a, &s, true);
   if (rc != CB200_OK) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (s.use_paged_tc)
+    return launch_mla_paged_tc(a, s.p.status, s.p.partials, s.p.counters, s.paged_tc_grid, st);
   if (s.use_tc)
     return launch_mla_tc(a, s.p.status, static_cast<uint8_t*>(a->workspace) + s.tc_partials_off, st);
   return a->dtype == CB200_F16 ? dispatch_mla<__half>(s, st) : dispatch_mla<__nv_bfloat16>(s, st);

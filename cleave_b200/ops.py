@@ -463,14 +463,16 @@ def mla_decode(q, kv, q_pe, k_pe, sm_scale, *, out=None, lse=None, max_ctas=0, i
 
 
 def mla_paged_decode(q_nope, q_pe, ckv_cache, kpe_cache, kv_indptr, kv_indices, sm_scale, *, out=None, lse=None,
-                     max_ctas=0):
+                     max_ctas=0, impl="auto"):
     """Paged MLA decode, one token per page; argument order follows the reference's operator
-    (python/cleave/dynamic/reference.py:282-320). Returns ``(out, lse)``, ``lse`` base 2."""
+    (python/cleave/dynamic/reference.py:282-320). Returns ``(out, lse)``, ``lse`` base 2. ``impl``: "auto" takes
+    the tcgen05 kernel (tokens as MMA rows) for at most 16 heads and the warp-MMA kernel otherwise; "tcgen05" /
+    "mma_sync" force one of them."""
     batch, heads = q_nope.shape[:2]
     if lse is None:
         lse = torch.empty((batch, heads), dtype=torch.float32, device=q_nope.device)
     out = _mla(q_nope, q_pe, ckv_cache, kpe_cache, sm_scale, kv_indptr=kv_indptr, kv_indices=kv_indices,
-               out=out, lse=lse, max_ctas=max_ctas)
+               out=out, lse=lse, max_ctas=max_ctas, impl=impl)
     return out, lse
 
 

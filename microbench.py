@@ -213,7 +213,7 @@ def gqa_dynamic_prefill_case(paged, batch=8, q_len=2048, hq=32, hkv=8, d=128, dt
     return fn, flops, byts
 
 
-def mla_paged_decode_case(batch=64, heads=16, lo=512, hi=8192, dtype=torch.bfloat16):
+def mla_paged_decode_case(batch=64, heads=16, lo=512, hi=8192, dtype=torch.bfloat16, impl="auto"):
     """Paged MLA decode (one token per page, 16 heads as the reference's shipped operator)."""
     g = _gen()
     lens = torch.randint(lo, hi + 1, (batch,), generator=g)
@@ -228,7 +228,7 @@ def mla_paged_decode_case(batch=64, heads=16, lo=512, hi=8192, dtype=torch.bfloa
     out = torch.empty_like(qn)
     flops = 2 * heads * total * (576 + 512)
     byts = total * 576 * 2 + (qn.numel() + qp.numel() + out.numel()) * 2
-    fn = lambda: ops.mla_paged_decode(qn, qp, ckv, kpe, ptr, idx, 0.1352337747812271, out=out)  # noqa: E731
+    fn = lambda: ops.mla_paged_decode(qn, qp, ckv, kpe, ptr, idx, 0.1352337747812271, out=out, impl=impl)  # noqa: E731
     return fn, flops, byts
 
 
@@ -272,6 +272,7 @@ CONFIGS = {
     "gqa_ragged_prefill_causal_h32_kv8_d128_b8_q2048": lambda: gqa_dynamic_prefill_case(False),
     "gqa_paged_prefill_causal_h32_kv8_d128_ps1_b8_q2048": lambda: gqa_dynamic_prefill_case(True),
     "mla_paged_decode_h16_ps1_b64_kv512_8192": lambda: mla_paged_decode_case(),
+    "mla_paged_decode_h16_ps1_b64_kv512_8192_mma_sync": lambda: mla_paged_decode_case(impl="mma_sync"),
     "mla_paged_prefill_causal_h16_b4_q512": lambda: mla_prefill_case(),
     "mla_paged_prefill_causal_h16_b4_q512_per_token": lambda: mla_prefill_case(impl="per_token"),
     "mla_paged_prefill_causal_h16_b8_q2048": lambda: mla_prefill_case(batch=8, q_len=2048),

@@ -65,12 +65,12 @@ def test_static_mla_vs_oracle(b, h, skv, dt, max_ctas, impl):
     assert_close(got, orc.mla_decode(inp["q"], inp["kv"], inp["q_pe"], inp["k_pe"], scale, dt))
 
 
-@pytest.mark.parametrize("h", [16, 128])
+@pytest.mark.parametrize("h,impl", [(16, "tcgen05"), (16, "mma_sync"), (8, "auto"), (128, "auto")])
 @pytest.mark.parametrize("max_ctas", [0, 2])
-def test_paged_mla_vs_oracle(h, max_ctas):
-    lens = [0, 1, 63, 64, 65, 700, 3001, 17]
+def test_paged_mla_vs_oracle(h, impl, max_ctas):
+    lens = [0, 1, 63, 64, 65, 127, 128, 129, 700, 3001, 17]
     inp = cases.mla_paged_inputs(77, lens, h, 512, 64, "bf16", cases.MLA_SM_SCALE)
-    out, lse = _run_paged(inp, "bf16", max_ctas=max_ctas)
+    out, lse = _run_paged(inp, "bf16", max_ctas=max_ctas, impl=impl)
     want_out, want_lse = orc.mla_paged_decode(inp["q_nope"], inp["q_pe"], inp["ckv_cache"], inp["kpe_cache"],
                                               inp["kv_indptr"], inp["kv_indices"], inp["sm_scale"])
     assert_close(out, want_out)
@@ -104,6 +104,30 @@ def test_static_mla_large_logits_rescale_path():
     assert np.isfinite(want).all()
     for impl in ("tcgen05", "mma_sync"):
         assert_close(_run_static(inp, "bf16", scale, impl=impl), want, rtol=3e-2, atol=3e-2)
+
+
+@pytest.mark.parametrize("dt", ["bf16", "f16"])
+def test_paged_mla_tcgen05_large_logits_rescale_and_repeat(dt):
+    """Paged form on the tcgen05 kernel: the tokens late in every request have cache rows fifteen times larger,
+    so the running maxima grow by far more than 2^8 between two tiles and the accumulator in tensor memory is
+    rescaled; a single CTA walks all requests (several pieces per CTA), and two launches are bit-identical."""
+    lens = [1000, 260, 515]
+    inp = cases.mla_paged_inputs(101, lens, 16, 512, 64, dt, 0.1)
+    for b in range(len(lens)):
+        lo, hi = int(inp["kv_indptr"][b]), int(inp["kv_indptr"][b + 1])
+        late = inp["kv_indices"][lo + (hi - lo) // 2:hi]
+        inp["ckv_cache"][late] = orc.round_to(inp["ckv_cache"][late] * 3.0, dt)
+        early = inp["kv_indices"][lo:lo + (hi - lo) // 2]
+        inp["ckv_cache"][early] = orc.round_to(inp["ckv_cache"][early] * 0.2, dt)
+    want_out, want_lse = orc.mla_paged_decode(inp["q_nope"], inp["q_pe"], inp["ckv_cache"], inp["kpe_cache"],
+                                              inp["kv_indptr"], inp["kv_indices"], inp["sm_scale"], dt)
+    assert np.isfinite(want_out).all()
+    for max_ctas in (1, 0):
+        out, lse = _run_paged(inp, dt, max_ctas=max_ctas, impl="tcgen05")
+        out2, lse2 = _run_paged(inp, dt, max_ctas=max_ctas, impl="tcgen05")
+        assert np.array_equal(out, out2) and np.array_equal(lse, lse2)
+        assert_close(out, want_out, rtol=3e-2, atol=3e-2)
+        assert_lse_close(lse, want_lse)
 
 
 def test_mla_full_config_properties():

@@ -27,7 +27,8 @@
 //
 // Work split: the 64-token tiles of all requests form one stream that is cut evenly over the persistent CTAs
 // (one per SM). A request that spans CTAs leaves unnormalised partials (O, m, l) in the workspace and the last
-// CTA to arrive combines them, as the warp-MMA kernel of mla_decode.cu does (same slots and counters).
+// CTA to arrive combines them after its own tiles with all of its threads (the slots and counters are those of
+// the warp-MMA kernel of mla_decode.cu).
 //
 // Warp roles: 0 = Q staging (registers -> swizzled shared memory, prefetched a piece ahead), 1 = score-MMA issuer and
 // tensor-memory owner, 10 = value-MMA issuer, 2..5 = softmax / epilogue / combine (lanes 0..15 of a warp = 16 tokens for S^T; thread =
@@ -133,7 +134,7 @@ __global__ void __launch_bounds__(kThreads, 1) mla_paged_tc_kernel(const Params 
   uint64_t* pv_done = p_full + 2;                  // [2] the value MMAs of a tile have completed
   uint64_t* o_free = pv_done + 2;                  // the epilogue has read O^T
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(o_free + 1);
-  int* flags = reinterpret_cast<int*>(tmem_holder + 2);
+  int* pending = reinterpret_cast<int*>(tmem_holder + 2);  // [0] count, then (request, first CTA, last CTA): at most two
   int* P = reinterpret_cast<int*>(smem + kFixedBytes);  // tile prefix per request
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -188,6 +189,7 @@ __global__ void __launch_bounds__(kThreads, 1) mla_paged_tc_kernel(const Params 
     }
     mbar_init(o_free, 4);
     mbar_fence_init();
+    pending[0] = 0;
   }
   if (warp == 1) {
     tmem_alloc(tmem_holder, 128);
@@ -556,65 +558,19 @@ __global__ void __launch_bounds__(kThreads, 1) mla_paged_tc_kernel(const Params 
       if (lane == 0) mbar_arrive(o_free);  // the next piece's value MMAs may overwrite O^T
 
       if (!whole) {
+        // publish the partial; the last CTA of the request to arrive notes the request down and combines it
+        // after its own tiles, with all of its threads
         __threadfence();
         named_bar_sync(1, kSoftmaxThreads);
-        const int c_first = pc.unit0 / span, c_last = (pc.unit0 + pc.n_tiles - 1) / span;
-        int* counter = p.counters + pc.b;
         if (st == 0) {
-          const int old = atomicAdd(counter, 1);
-          flags[0] = (old == c_last - c_first) ? 1 : 0;
-        }
-        named_bar_sync(1, kSoftmaxThreads);
-        const bool combine = flags[0] != 0;
-        named_bar_sync(1, kSoftmaxThreads);  // flags[0] is read before the next piece may rewrite it
-        if (combine) {
-          __threadfence();
-          // Thread st owns latent columns j * 128 + st of all heads. All 64 values of a partial are requested
-          // before the first is used, so a partial costs one L2 round trip.
-          float acc[4][kHeads], Mc[kHeads], Lc[kHeads];
-#pragma unroll
-          for (int h = 0; h < kHeads; ++h) {
-            Mc[h] = -INFINITY;
-            Lc[h] = 0.f;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) acc[j][h] = 0.f;
+          const int c_first = pc.unit0 / span, c_last = (pc.unit0 + pc.n_tiles - 1) / span;
+          if (atomicAdd(p.counters + pc.b, 1) == c_last - c_first) {
+            int* e = pending + 1 + 3 * pending[0];
+            e[0] = pc.b;
+            e[1] = c_first;
+            e[2] = c_last;
+            pending[0] += 1;
           }
-#pragma unroll 1
-          for (int cta = c_first; cta <= c_last; ++cta) {
-            const float* src = p.partials + (static_cast<size_t>(cta) * 2 + (cta == c_first ? 1 : 0)) * kSlotFloats;
-            float x[4][kHeads];
-#pragma unroll
-            for (int h = 0; h < kHeads; ++h)
-#pragma unroll
-              for (int j = 0; j < 4; ++j) x[j][h] = __ldcg(src + h * kCkv + j * 128 + st);
-            float mi[kHeads], li[kHeads];
-#pragma unroll
-            for (int h = 0; h < kHeads; h += 4) {
-              const float4 m4 = __ldcg(reinterpret_cast<const float4*>(src + kHeads * kCkv + h));
-              const float4 l4 = __ldcg(reinterpret_cast<const float4*>(src + kHeads * kCkv + kHeads + h));
-              mi[h] = m4.x; mi[h + 1] = m4.y; mi[h + 2] = m4.z; mi[h + 3] = m4.w;
-              li[h] = l4.x; li[h + 1] = l4.y; li[h + 2] = l4.z; li[h + 3] = l4.w;
-            }
-#pragma unroll
-            for (int h = 0; h < kHeads; ++h) {
-              const float mn = fmaxf(Mc[h], mi[h]), mu = mn == -INFINITY ? 0.f : mn;
-              const float a = fast_exp2(Mc[h] - mu), b = fast_exp2(mi[h] - mu);
-              Lc[h] = a * Lc[h] + b * li[h];
-              Mc[h] = mn;
-#pragma unroll
-              for (int j = 0; j < 4; ++j) acc[j][h] = a * acc[j][h] + b * x[j][h];
-            }
-          }
-#pragma unroll
-          for (int h = 0; h < kHeads; ++h) {
-            if (h < p.heads) {
-              const float inv = Lc[h] > 0.f ? 1.f / Lc[h] : 0.f;
-#pragma unroll
-              for (int j = 0; j < 4; ++j) outp[(bh + h) * kCkv + j * 128 + st] = T(acc[j][h] * inv);
-              if (p.lse && st == h) p.lse[bh + h] = Lc[h] > 0.f ? Mc[h] + fast_log2(Lc[h]) : -INFINITY;
-            }
-          }
-          if (st == 0) *counter = 0;  // ready for the next launch
         }
       }
       u += pc.count;
@@ -626,6 +582,78 @@ __global__ void __launch_bounds__(kThreads, 1) mla_paged_tc_kernel(const Params 
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 128);
+  }
+
+  // ---- combine the requests this CTA was the last to arrive at (at most two: the one that continues from the CTA
+  // before and the one that continues into the next). All threads take part: an item is four neighbouring latent
+  // columns of one head, and the values of up to six partials for three items are requested together, so a request
+  // costs two round trips to L2 however many CTAs it spans up to six.
+  const int n_pending = pending[0];
+  for (int k = 0; k < n_pending; ++k) {
+    const int b = pending[1 + 3 * k], c_first = pending[2 + 3 * k], c_last = pending[3 + 3 * k];
+    __threadfence();
+    const size_t bh = static_cast<size_t>(b) * p.heads;
+    constexpr int kItems = kHeads * (kCkv / 4);                        // 2048
+    constexpr int kRounds = (kItems + 3 * kThreads - 1) / (3 * kThreads);  // items per thread: 3 per round
+#pragma unroll 1
+    for (int r = 0; r < kRounds; ++r) {
+      int head[3], c4[3];
+      float M[3], Lsum[3];
+      float4 acc[3];
+#pragma unroll
+      for (int q = 0; q < 3; ++q) {
+        const int item = min((r * 3 + q) * kThreads + tid, kItems - 1);  // surplus threads repeat the last item
+        head[q] = item / (kCkv / 4);
+        c4[q] = item - head[q] * (kCkv / 4);
+        M[q] = -INFINITY;
+        Lsum[q] = 0.f;
+        acc[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll 1
+      for (int cta0 = c_first; cta0 <= c_last; cta0 += 6) {
+        float4 x[6][3];
+        float mi[6][3], li[6][3];
+#pragma unroll
+        for (int i = 0; i < 6; ++i) {
+          const int cta = min(cta0 + i, c_last);
+          const float* src = p.partials + (static_cast<size_t>(cta) * 2 + (cta == c_first ? 1 : 0)) * kSlotFloats;
+#pragma unroll
+          for (int q = 0; q < 3; ++q) {
+            x[i][q] = __ldcg(reinterpret_cast<const float4*>(src + head[q] * kCkv + c4[q] * 4));
+            mi[i][q] = __ldcg(src + kHeads * kCkv + head[q]);
+            li[i][q] = __ldcg(src + kHeads * kCkv + kHeads + head[q]);
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 6; ++i) {
+          if (cta0 + i <= c_last) {
+#pragma unroll
+            for (int q = 0; q < 3; ++q) {
+              const float mn = fmaxf(M[q], mi[i][q]), mu = mn == -INFINITY ? 0.f : mn;
+              const float a = fast_exp2(M[q] - mu), w = fast_exp2(mi[i][q] - mu);
+              Lsum[q] = a * Lsum[q] + w * li[i][q];
+              M[q] = mn;
+              acc[q].x = a * acc[q].x + w * x[i][q].x;
+              acc[q].y = a * acc[q].y + w * x[i][q].y;
+              acc[q].z = a * acc[q].z + w * x[i][q].z;
+              acc[q].w = a * acc[q].w + w * x[i][q].w;
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < 3; ++q) {
+        if (head[q] < p.heads) {
+          const float inv = Lsum[q] > 0.f ? 1.f / Lsum[q] : 0.f;
+          uint2 o;
+          o.x = pack2<T>(acc[q].x * inv, acc[q].y * inv);
+          o.y = pack2<T>(acc[q].z * inv, acc[q].w * inv);
+          *reinterpret_cast<uint2*>(outp + (bh + head[q]) * kCkv + c4[q] * 4) = o;
+          if (p.lse && c4[q] == 0) p.lse[bh + head[q]] = Lsum[q] > 0.f ? M[q] + fast_log2(Lsum[q]) : -INFINITY;
+        }
+      }
+    }
+    if (tid == 0) p.counters[b] = 0;  // ready for the next launch
   }
 }
 

@@ -271,7 +271,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       mbar_wait(&k_full[kst], kph, p.status, kFaultFullBarrier);
       mbar_wait(&s_empty[sb], ((j >> 1) & 1) ^ 1, p.status, kFaultTmemBarrier);
       tc_fence_after();
-      if (lane == 0) {
+      if (elect_one()) {
         const uint32_t d = tmem_base + kColS + sb * kBN;
 #pragma unroll
         for (int c = 0; c < C::kChunks; ++c) {
@@ -298,7 +298,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       mbar_wait(&v_full[vst], vph, p.status, kFaultFullBarrier);
       mbar_wait(&p_full[pb], (j >> 1) & 1, p.status, kFaultTmemBarrier);
       tc_fence_after();
-      if (lane == 0) {
+      if (elect_one()) {
         const uint32_t va = v_addr + vst * C::kTileBytes;
 #pragma unroll
         for (int ks = 0; ks < kBN / 16; ++ks) {

@@ -38,6 +38,11 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
+// One thread of a converged warp. MMAs and their commits are issued under this, not under `lane == 0`: with a
+// provably single active thread the operands of tcgen05.mma stay in uniform registers. Measured on 128 x N x 16
+// MMAs issued back to back by one warp: 63 clocks per instruction under `lane == 0` (93 with descriptors built in
+// a loop that is not unrolled), 40 under elect.sync for N = 16, 65 for N = 128 (the tensor core's own pace).
+// A second issuing warp doubles the rate where the products are independent.
 __device__ __forceinline__ bool elect_one() {
   uint32_t pred = 0;
   asm volatile(

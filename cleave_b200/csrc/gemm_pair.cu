@@ -155,7 +155,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         for (int kb = kb0; kb < kb1; ++kb) {
           mbar_wait(&full_bar[stage], phase, p.status, kFaultFullBarrier);
           tc_fence_after();
-          if (lane == 0) {
+          if (elect_one()) {
             const uint32_t a_addr = smem_u32(stages + stage * kStageBytes);
             const uint32_t b_addr = a_addr + kABytes;
 #pragma unroll
@@ -169,7 +169,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           __syncwarp();
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
-        if (lane == 0) umma_commit_pair(&acc_full[buf], pair_mask);
+        if (elect_one()) umma_commit_pair(&acc_full[buf], pair_mask);
         __syncwarp();
         if (++buf == 2) { buf = 0; acc_phase ^= 1; }
       }

@@ -284,7 +284,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         mbar_wait((MODE == 1 && p.gamma != nullptr) ? &ready_bar[stage] : &full_bar[stage], phase, p.status,
                   kFaultFullBarrier);
         tc_fence_after();
-        if (lane == 0) {
+        if (elect_one()) {
           const uint32_t a_addr = smem_u32(stages + stage * Plan::kStageBytes);
           const uint32_t b_addr = a_addr + kABytes;
 #pragma unroll
@@ -300,7 +300,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         __syncwarp();
         if (++stage == kStages) { stage = 0; phase ^= 1; }
       }
-      if (lane == 0) umma_commit(&acc_full[buf]);
+      if (elect_one()) umma_commit(&acc_full[buf]);
       __syncwarp();
       if (++buf == 2) { buf = 0; acc_phase ^= 1; }
       x += nseg;

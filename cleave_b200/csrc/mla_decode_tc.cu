@@ -163,7 +163,7 @@ mla_scores_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_consta
       for (int c = 0; c < kChunks; ++c) {
         mbar_wait(&k_full[st], ph, p.status, kFaultFullBarrier);
         tc_fence_after();
-        if (lane == 0) {
+        if (elect_one()) {
           const uint32_t q_addr = k_addr + st * kKStageBytes;
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) {
@@ -176,7 +176,7 @@ mla_scores_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_consta
         __syncwarp();
         if (++st == kKStages) { st = 0; ph ^= 1; }
       }
-      if (lane == 0) umma_commit(&s_full[sb]);
+      if (elect_one()) umma_commit(&s_full[sb]);
       __syncwarp();
     }
   } else {
@@ -371,7 +371,7 @@ mla_values_kernel(const __grid_constant__ CUtensorMap tm_ckv, const Params p) {
       mbar_wait(&v_full[st], ph, p.status, kFaultFullBarrier);
       mbar_wait(&p_full[pb], (j >> 1) & 1, p.status, kFaultTmemBarrier);
       tc_fence_after();
-      if (lane == 0) {
+      if (elect_one()) {
         const uint32_t v_addr = v_addr0 + st * kVStageBytes;
 #pragma unroll
         for (int ks = 0; ks < kBlk / 16; ++ks) {

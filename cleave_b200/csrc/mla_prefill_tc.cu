@@ -220,7 +220,7 @@ mla_prefill_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_const
       for (int i = 0; i < kChunks; ++i) {
         mbar_wait(&k_full[st], ph, p.status, kFaultFullBarrier);
         tc_fence_after();
-        if (lane == 0) {
+        if (elect_one()) {
           const uint32_t a = ring_addr + st * kStageBytes;
           const uint32_t b = i < kChunks - kVChunks ? a + kChunkBytes
                                                     : v_addr + (j & 1) * kVBytes + (i - (kChunks - kVChunks)) * kChunkBytes;
@@ -235,7 +235,7 @@ mla_prefill_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_const
         __syncwarp();
         if (++st == kStages) { st = 0; ph ^= 1; }
       }
-      if (lane == 0) umma_commit(&s_full[j & 1]);
+      if (elect_one()) umma_commit(&s_full[j & 1]);
       __syncwarp();
     };
     if (nt > 0) issue_s(0);
@@ -244,7 +244,7 @@ mla_prefill_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_const
       const int pb = j & 1;
       mbar_wait(&p_full[pb], (j >> 1) & 1, p.status, kFaultTmemBarrier);
       tc_fence_after();
-      if (lane == 0) {
+      if (elect_one()) {
 #pragma unroll
         for (int ks = 0; ks < kBN / 16; ++ks) {
           // B: MN-major, 16 token rows of 128 bytes per step; 64-column chunks are kChunkBytes apart

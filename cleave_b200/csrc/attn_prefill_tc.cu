@@ -182,7 +182,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     int st = 0, ph = 0;
     for (int j = 0; MODE != 2 && j < nt; ++j) {
       mbar_wait(&k_empty[st], ph ^ 1, p.status, kFaultEmptyBarrier);
-      if (lane == 0) {
+      if (elect_one()) {
         mbar_arrive_expect_tx(&k_full[st], C::kTileBytes);
 #pragma unroll
         for (int c = 0; c < C::kChunks; ++c) {
@@ -199,7 +199,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     int st = 0, ph = 0;
     for (int j = 0; MODE != 2 && j < nt; ++j) {
       mbar_wait(&v_empty[st], ph ^ 1, p.status, kFaultEmptyBarrier);
-      if (lane == 0) {
+      if (elect_one()) {
         mbar_arrive_expect_tx(&v_full[st], C::kTileBytes);
 #pragma unroll
         for (int c = 0; c < C::kChunks; ++c) {

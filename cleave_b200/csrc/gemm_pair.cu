@@ -126,7 +126,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       const int col0 = MODE == 2 ? tn * 128 : tn * 256 + static_cast<int>(rank) * 128;
       for (int kb = kb0; kb < kb1; ++kb) {
         mbar_wait(&empty_bar[stage], phase ^ 1, p.status, kFaultEmptyBarrier);
-        if (lane == 0) {
+        if (elect_one()) {
           uint8_t* a_dst = stages + stage * kStageBytes;
           uint8_t* b_dst = a_dst + kABytes;
           if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * kStageBytes);  // both CTAs' bytes

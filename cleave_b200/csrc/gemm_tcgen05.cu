@@ -238,7 +238,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
           pdl_wait();  // the second operand pair is the preceding kernel's output; everything before streamed beside it
           waited2 = true;
         }
-        if (lane == 0) {
+        if (elect_one()) {
           uint8_t* a_dst = stages + stage * Plan::kStageBytes;
           uint8_t* b_dst = a_dst + kABytes;
           // rows of the A tile beyond a_rows are never fetched; the MMA reads whatever is there,

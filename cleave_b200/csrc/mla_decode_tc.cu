@@ -134,7 +134,7 @@ mla_scores_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_consta
       const int tok0 = (u0 + 2 * t) * kBlk;
       for (int c = 0; c < kChunks; ++c) {
         mbar_wait(&k_empty[st], ph ^ 1, p.status, kFaultEmptyBarrier);
-        if (lane == 0) {
+        if (elect_one()) {
           uint8_t* q_dst = k_smem + st * kKStageBytes;
           uint8_t* k_dst = q_dst + kQChunkBytes;
           mbar_arrive_expect_tx(&k_full[st], kKStageBytes);
@@ -323,7 +323,7 @@ mla_values_kernel(const __grid_constant__ CUtensorMap tm_ckv, const Params p) {
     int vst = 0, vph = 0, jv = 0;
     auto load_v = [&]() {
       mbar_wait(&v_empty[vst], vph ^ 1, p.status, kFaultEmptyBarrier);
-      if (lane == 0) {
+      if (elect_one()) {
         uint8_t* dst = v_smem + vst * kVStageBytes;
         mbar_arrive_expect_tx(&v_full[vst], kVStageBytes);
 #pragma unroll
@@ -347,7 +347,7 @@ mla_values_kernel(const __grid_constant__ CUtensorMap tm_ckv, const Params p) {
     int pst = 0, pph = 0;
     for (int j = 0; j < nt; ++j) {
       mbar_wait(&pt_empty[pst], pph ^ 1, p.status, kFaultEmptyBarrier);
-      if (lane == 0) {
+      if (elect_one()) {
         mbar_arrive_expect_tx(&pt_full[pst], kPTileBytes);
 #pragma unroll
         for (int q = 0; q < 4; ++q)

@@ -31,8 +31,8 @@
 // the warp-MMA kernel of mla_decode.cu).
 //
 // Warp roles: 0 = Q staging (registers -> swizzled shared memory, prefetched a piece ahead), 1 = score-MMA issuer and
-// tensor-memory owner, 10 = value-MMA issuer, 2..5 = softmax / epilogue / combine (lanes 0..15 of a warp = 16 tokens for S^T; thread =
-// latent column for O^T), 6..9 = row gather (16-byte cp.async, eight lanes per 128-byte line).
+// tensor-memory owner, 2 = value-MMA issuer, 3 = Q staging beside warp 0, 4..7 = softmax / epilogue / combine (lanes 0..15 of a warp = 16 tokens for S^T; thread =
+// latent column for O^T), 8..15 = row gather (16-byte cp.async, eight lanes per 128-byte line).
 //
 // Reference semantics: python/cleave/dynamic/reference.py:282-320; replaces the kernel of
 // python/cleave/dynamic/paging/builders/mla.py:220 (tests/graph/handwritten/expected_kernels/
@@ -59,7 +59,8 @@ constexpr int kPBytes = kQChunkBytes;         // 16 head rows x 64 tokens
 constexpr int kExchBytes = 1024;              // 2 x 4 x 16 tile maxima, 4 x 16 row sums
 constexpr int kBarBytes = 512;
 constexpr int kFixedBytes = kPairSlots * kPairBytes + kKpeSlots * kChunkBytes + kQBytes + 2 * kPBytes + kExchBytes + kBarBytes;
-constexpr int kThreads = 11 * 32;
+constexpr int kThreads = 16 * 32;
+constexpr int kGatherThreads = 8 * 32;        // warps 8..15
 constexpr int kSoftmaxThreads = 128;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.f;      // log2 units
@@ -133,7 +134,8 @@ __global__ void __launch_bounds__(kThreads, 1) mla_paged_tc_kernel(const Params 
   uint64_t* p_full = s_full + 2;                   // [2] P^T stored (and O^T rescaled if needed)
   uint64_t* pv_done = p_full + 2;                  // [2] the value MMAs of a tile have completed
   uint64_t* o_free = pv_done + 2;                  // the epilogue has read O^T
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(o_free + 1);
+  uint64_t* merge_bar = o_free + 1;                // partials of a split request have landed in the tile slots
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(merge_bar + 1);
   int* pending = reinterpret_cast<int*>(tmem_holder + 2);  // [0] count, then (request, first CTA, last CTA): at most two
   int* P = reinterpret_cast<int*>(smem + kFixedBytes);  // tile prefix per request
 
@@ -173,14 +175,14 @@ __global__ void __launch_bounds__(kThreads, 1) mla_paged_tc_kernel(const Params 
   }
   if (tid == 0) {
     for (int s = 0; s < kPairSlots; ++s) {
-      mbar_init(&pair_full[s], 128);
+      mbar_init(&pair_full[s], kGatherThreads);
       mbar_init(&pair_empty[s], 1);
     }
     for (int s = 0; s < kKpeSlots; ++s) {
-      mbar_init(&kpe_full[s], 128);
+      mbar_init(&kpe_full[s], kGatherThreads);
       mbar_init(&kpe_empty[s], 1);
     }
-    mbar_init(q_full, 1);
+    mbar_init(q_full, 2);
     mbar_init(q_free, 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(&s_full[s], 1);
@@ -188,6 +190,7 @@ __global__ void __launch_bounds__(kThreads, 1) mla_paged_tc_kernel(const Params 
       mbar_init(&pv_done[s], 1);
     }
     mbar_init(o_free, 4);
+    mbar_init(merge_bar, 1);
     mbar_fence_init();
     pending[0] = 0;
   }
@@ -208,8 +211,9 @@ __global__ void __launch_bounds__(kThreads, 1) mla_paged_tc_kernel(const Params 
   const Walker walker{P, p.batch, 1, 0};
   T* outp = reinterpret_cast<T*>(p.out);
 
-  if (warp == 0) {
-    // ================================================================ Q of every piece: 16 rows x 72 16-byte pieces
+  if (warp == 0 || warp == 3) {
+    // ================================================================ Q of every piece: 16 rows x 72 16-byte pieces,
+    // half of them per warp so that each warp's share is one batch of loads in registers
     const T* qn = reinterpret_cast<const T*>(p.q_nope);
     const T* qp = reinterpret_cast<const T*>(p.q_pe);
     constexpr int kPiecesPerRow = (kCkv + kKpe) / 8;                // 72
@@ -217,10 +221,12 @@ __global__ void __launch_bounds__(kThreads, 1) mla_paged_tc_kernel(const Params 
     int piece_idx = 0;
     for (int u = u0; u < u1; ++piece_idx) {
       const Piece pc = walker.at(u, u1);
-      uint4 v[kPerLane];
+      constexpr int kHalf = kPerLane / 2;
+      const int k0 = warp == 0 ? 0 : kHalf;
+      uint4 v[kHalf];
 #pragma unroll
-      for (int k = 0; k < kPerLane; ++k) {
-        const int i = lane + 32 * k, row = i / kPiecesPerRow, c = i - row * kPiecesPerRow;
+      for (int k = 0; k < kHalf; ++k) {
+        const int i = lane + 32 * (k0 + k), row = i / kPiecesPerRow, c = i - row * kPiecesPerRow;
         v[k] = make_uint4(0u, 0u, 0u, 0u);
         if (row < p.heads) {
           const size_t bh = static_cast<size_t>(pc.b) * p.heads + row;
@@ -231,28 +237,29 @@ __global__ void __launch_bounds__(kThreads, 1) mla_paged_tc_kernel(const Params 
       // the score MMAs of the piece before must have read the buffer
       if (piece_idx > 0) mbar_wait(q_free, (piece_idx - 1) & 1, p.status, kFaultMmaBarrier);
 #pragma unroll
-      for (int k = 0; k < kPerLane; ++k) {
-        const int i = lane + 32 * k, row = i / kPiecesPerRow, c = i - row * kPiecesPerRow;
-        const int chunk = c >> 3, pc8 = c & 7;
-        *reinterpret_cast<uint4*>(q_smem + chunk * kQChunkBytes + row * 128 + ((pc8 ^ (row & 7)) << 4)) = v[k];
+      for (int k = 0; k < kHalf; ++k) {
+        const int i = lane + 32 * (k0 + k), row = i / kPiecesPerRow, c = i - row * kPiecesPerRow;
+        *reinterpret_cast<uint4*>(q_smem + (c >> 3) * kQChunkBytes + row * 128 + (((c & 7) ^ (row & 7)) << 4)) = v[k];
       }
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(q_full);
       u += pc.count;
     }
-    // Requests without any live token: out = 0, lse = -inf (this warp is idle once Q is staged).
-    for (int b = blockIdx.x; b < p.batch; b += G) {
+    // Requests without any live token: out = 0, lse = -inf (warp 0, idle once Q is staged).
+    for (int b = blockIdx.x; warp == 0 && b < p.batch; b += G) {
       if (P[b + 1] - P[b] != 0) continue;
       for (int i = lane; i < p.heads * kCkv; i += 32) outp[static_cast<size_t>(b) * p.heads * kCkv + i] = T(0.f);
       if (p.lse)
         for (int i = lane; i < p.heads; i += 32) p.lse[static_cast<size_t>(b) * p.heads + i] = -INFINITY;
     }
-  } else if (warp >= 6 && warp < 10) {
+  } else if (warp >= 8) {
     // ================================================================ row gather
-    // eight lanes copy the eight 16-byte pieces of one row's 64-column chunk, so a warp instruction moves four
-    // whole 128-byte lines; the 128 threads cover 16 rows per round, four rounds per chunk
-    const int gtid = tid - 6 * 32, piece = gtid & 7, r_in = gtid >> 3;
+    // Eight lanes copy the eight 16-byte pieces of one row's 64-column chunk, so a warp instruction moves four
+    // whole 128-byte lines; the 256 threads cover 32 rows per round, two rounds per chunk. Eight warps, not four:
+    // what an SM can have in flight is bounded per issuing warp (measured with a gather-only kernel over random
+    // 1 KB rows: 4.0 TB/s with four warps per SM whatever the depth, 6.0 with eight, 6.6 with twelve).
+    const int gtid = tid - 8 * 32, piece = gtid & 7, r_in = gtid >> 3;
     const T* ckv = reinterpret_cast<const T*>(p.ckv);
     const T* kpe = reinterpret_cast<const T*>(p.kpe);
     int g = 0;
@@ -262,15 +269,15 @@ __global__ void __launch_bounds__(kThreads, 1) mla_paged_tc_kernel(const Params 
       auto page_of = [&](int tok) {
         return min(max(__ldg(p.kv_indices + base + min(tok, valid - 1)), 0), p.num_pages - 1);
       };
-      int pg[4], pg_next[4];
+      int pg[2], pg_next[2];
 #pragma unroll
-      for (int rr = 0; rr < 4; ++rr) pg_next[rr] = page_of(pc.tile0 * kTile + rr * 16 + r_in);
+      for (int rr = 0; rr < 2; ++rr) pg_next[rr] = page_of(pc.tile0 * kTile + rr * 32 + r_in);
       for (int t = pc.tile0; t < pc.tile0 + pc.count; ++t, ++g) {
 #pragma unroll
-        for (int rr = 0; rr < 4; ++rr) pg[rr] = pg_next[rr];
+        for (int rr = 0; rr < 2; ++rr) pg[rr] = pg_next[rr];
         if (t + 1 < pc.tile0 + pc.count) {  // one tile ahead: the latency of the index loads stays off the stream
 #pragma unroll
-          for (int rr = 0; rr < 4; ++rr) pg_next[rr] = page_of((t + 1) * kTile + rr * 16 + r_in);
+          for (int rr = 0; rr < 2; ++rr) pg_next[rr] = page_of((t + 1) * kTile + rr * 32 + r_in);
         }
 #pragma unroll 1
         for (int j = 0; j < 4; ++j) {
@@ -280,8 +287,8 @@ __global__ void __launch_bounds__(kThreads, 1) mla_paged_tc_kernel(const Params 
 #pragma unroll
           for (int cc = 0; cc < 2; ++cc) {
 #pragma unroll
-            for (int rr = 0; rr < 4; ++rr) {
-              const int row = rr * 16 + r_in;
+            for (int rr = 0; rr < 2; ++rr) {
+              const int row = rr * 32 + r_in;
               const T* src = ckv + static_cast<long long>(pg[rr]) * kCkv + (2 * j + cc) * 64 + piece * 8;
               const uint32_t o = cc * kChunkBytes + row * 128 + ((piece ^ (row & 7)) << 4);
               asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + o), "l"(src) : "memory");
@@ -294,8 +301,8 @@ __global__ void __launch_bounds__(kThreads, 1) mla_paged_tc_kernel(const Params 
           mbar_wait(&kpe_empty[ks], (use & 1) ^ 1, p.status, kFaultEmptyBarrier);
           const uint32_t dst = smem_u32(kpe_smem + ks * kChunkBytes);
 #pragma unroll
-          for (int rr = 0; rr < 4; ++rr) {
-            const int row = rr * 16 + r_in;
+          for (int rr = 0; rr < 2; ++rr) {
+            const int row = rr * 32 + r_in;
             const T* src = kpe + static_cast<long long>(pg[rr]) * kKpe + piece * 8;
             asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + row * 128 + ((piece ^ (row & 7)) << 4)),
                          "l"(src) : "memory");
@@ -306,8 +313,8 @@ __global__ void __launch_bounds__(kThreads, 1) mla_paged_tc_kernel(const Params 
       u += pc.count;
     }
     asm volatile("cp.async.wait_all;" ::: "memory");
-  } else if (warp == 1 || warp == 10) {
-    // ================================================================ MMA issuers: warp 1 the score products, warp 10
+  } else if (warp == 1 || warp == 2) {
+    // ================================================================ MMA issuers: warp 1 the score products, warp 2
     // the value products. One warp issues an MMA of this size every ~55 clocks, which for the 52 MMAs of a tile
     // is as long as the tile's bytes take to arrive; two warps issue side by side. The products of the two warps
     // are ordered by the barriers between them (S^T -> softmax -> P^T), never by issue order.
@@ -392,13 +399,13 @@ __global__ void __launch_bounds__(kThreads, 1) mla_paged_tc_kernel(const Params 
         u += pc.count;
       }
     }
-  } else {
-    // ================================================================ softmax / epilogue / combine (warps 2..5)
+  } else if (warp >= 4 && warp < 8) {
+    // ================================================================ softmax / epilogue / combine (warps 4..7)
     const int quarter = warp & 3;
     const int col = quarter * 32 + lane;      // latent column of the block (O^T) = TMEM lane
     const int tk = quarter * 16 + lane;       // token of the tile (S^T), lanes 0..15 only
     const bool has_token = lane < 16;
-    const int st = tid - 2 * 32;              // 0..127 inside the group
+    const int st = tid - 4 * 32;              // 0..127 inside the group
     const uint32_t lane_field = static_cast<uint32_t>(quarter * 32) << 16;
     int g = 0, piece_idx = 0;
     for (int u = u0; u < u1; ++piece_idx) {
@@ -585,72 +592,72 @@ __global__ void __launch_bounds__(kThreads, 1) mla_paged_tc_kernel(const Params 
   }
 
   // ---- combine the requests this CTA was the last to arrive at (at most two: the one that continues from the CTA
-  // before and the one that continues into the next). All threads take part: an item is four neighbouring latent
-  // columns of one head, and the values of up to six partials for three items are requested together, so a request
-  // costs two round trips to L2 however many CTAs it spans up to six.
+  // before and the one that continues into the next). The tile slots are free now: the partials come into them as
+  // bulk copies, five at a time (one L2 round trip at the SM's full pull rate, no registers in between), and all
+  // threads combine from shared memory. An item is four neighbouring latent columns of one head.
   const int n_pending = pending[0];
+  uint32_t merge_phase = 0;
   for (int k = 0; k < n_pending; ++k) {
     const int b = pending[1 + 3 * k], c_first = pending[2 + 3 * k], c_last = pending[3 + 3 * k];
-    __threadfence();
     const size_t bh = static_cast<size_t>(b) * p.heads;
-    constexpr int kItems = kHeads * (kCkv / 4);                        // 2048
-    constexpr int kRounds = (kItems + 3 * kThreads - 1) / (3 * kThreads);  // items per thread: 3 per round
+    constexpr int kItems = kHeads * (kCkv / 4);  // 2048
+    constexpr int kPerThread = kItems / kThreads;
+    static_assert(kItems % kThreads == 0, "items must divide evenly over the threads");
+    constexpr int kSlotBytes = kSlotFloats * 4;
+    constexpr int kMergeSlots = 5;
+    static_assert(kMergeSlots * kSlotBytes <= kPairSlots * kPairBytes && kSlotBytes % 16 == 0, "partials must fit the tile slots");
+    float M[kPerThread], Lsum[kPerThread];
+    float4 acc[kPerThread];
+#pragma unroll
+    for (int q = 0; q < kPerThread; ++q) {
+      M[q] = -INFINITY;
+      Lsum[q] = 0.f;
+      acc[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
 #pragma unroll 1
-    for (int r = 0; r < kRounds; ++r) {
-      int head[3], c4[3];
-      float M[3], Lsum[3];
-      float4 acc[3];
-#pragma unroll
-      for (int q = 0; q < 3; ++q) {
-        const int item = min((r * 3 + q) * kThreads + tid, kItems - 1);  // surplus threads repeat the last item
-        head[q] = item / (kCkv / 4);
-        c4[q] = item - head[q] * (kCkv / 4);
-        M[q] = -INFINITY;
-        Lsum[q] = 0.f;
-        acc[q] = make_float4(0.f, 0.f, 0.f, 0.f);
-      }
-#pragma unroll 1
-      for (int cta0 = c_first; cta0 <= c_last; cta0 += 6) {
-        float4 x[6][3];
-        float mi[6][3], li[6][3];
-#pragma unroll
-        for (int i = 0; i < 6; ++i) {
-          const int cta = min(cta0 + i, c_last);
-          const float* src = p.partials + (static_cast<size_t>(cta) * 2 + (cta == c_first ? 1 : 0)) * kSlotFloats;
-#pragma unroll
-          for (int q = 0; q < 3; ++q) {
-            x[i][q] = __ldcg(reinterpret_cast<const float4*>(src + head[q] * kCkv + c4[q] * 4));
-            mi[i][q] = __ldcg(src + kHeads * kCkv + head[q]);
-            li[i][q] = __ldcg(src + kHeads * kCkv + kHeads + head[q]);
-          }
-        }
-#pragma unroll
-        for (int i = 0; i < 6; ++i) {
-          if (cta0 + i <= c_last) {
-#pragma unroll
-            for (int q = 0; q < 3; ++q) {
-              const float mn = fmaxf(M[q], mi[i][q]), mu = mn == -INFINITY ? 0.f : mn;
-              const float a = fast_exp2(M[q] - mu), w = fast_exp2(mi[i][q] - mu);
-              Lsum[q] = a * Lsum[q] + w * li[i][q];
-              M[q] = mn;
-              acc[q].x = a * acc[q].x + w * x[i][q].x;
-              acc[q].y = a * acc[q].y + w * x[i][q].y;
-              acc[q].z = a * acc[q].z + w * x[i][q].z;
-              acc[q].w = a * acc[q].w + w * x[i][q].w;
-            }
-          }
+    for (int cta0 = c_first; cta0 <= c_last; cta0 += kMergeSlots) {
+      const int n = min(kMergeSlots, c_last - cta0 + 1);
+      __syncthreads();  // the slots are no longer read (tiles, or the chunk before)
+      if (tid == 0) {
+        __threadfence();
+        asm volatile("fence.proxy.async;" ::: "memory");  // partials were written with ordinary stores; the copy engine reads them
+        mbar_arrive_expect_tx(merge_bar, static_cast<uint32_t>(n) * kSlotBytes);
+        for (int i = 0; i < n; ++i) {
+          const int cta = cta0 + i;
+          bulk_load_1d(pair_smem + i * kSlotBytes,
+                       p.partials + (static_cast<size_t>(cta) * 2 + (cta == c_first ? 1 : 0)) * kSlotFloats, kSlotBytes, merge_bar);
         }
       }
+      mbar_wait(merge_bar, merge_phase, p.status, kFaultFullBarrier);
+      merge_phase ^= 1;
+      for (int i = 0; i < n; ++i) {
+        const float* src = reinterpret_cast<const float*>(pair_smem + i * kSlotBytes);
 #pragma unroll
-      for (int q = 0; q < 3; ++q) {
-        if (head[q] < p.heads) {
-          const float inv = Lsum[q] > 0.f ? 1.f / Lsum[q] : 0.f;
-          uint2 o;
-          o.x = pack2<T>(acc[q].x * inv, acc[q].y * inv);
-          o.y = pack2<T>(acc[q].z * inv, acc[q].w * inv);
-          *reinterpret_cast<uint2*>(outp + (bh + head[q]) * kCkv + c4[q] * 4) = o;
-          if (p.lse && c4[q] == 0) p.lse[bh + head[q]] = Lsum[q] > 0.f ? M[q] + fast_log2(Lsum[q]) : -INFINITY;
+        for (int q = 0; q < kPerThread; ++q) {
+          const int item = q * kThreads + tid, head = item / (kCkv / 4);
+          const float4 x = *reinterpret_cast<const float4*>(src + item * 4);  // item = head * 128 + column group
+          const float mi = src[kHeads * kCkv + head], li = src[kHeads * kCkv + kHeads + head];
+          const float mn = fmaxf(M[q], mi), mu = mn == -INFINITY ? 0.f : mn;
+          const float a = fast_exp2(M[q] - mu), w = fast_exp2(mi - mu);
+          Lsum[q] = a * Lsum[q] + w * li;
+          M[q] = mn;
+          acc[q].x = a * acc[q].x + w * x.x;
+          acc[q].y = a * acc[q].y + w * x.y;
+          acc[q].z = a * acc[q].z + w * x.z;
+          acc[q].w = a * acc[q].w + w * x.w;
         }
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < kPerThread; ++q) {
+      const int item = q * kThreads + tid, head = item / (kCkv / 4), c4 = item - head * (kCkv / 4);
+      if (head < p.heads) {
+        const float inv = Lsum[q] > 0.f ? 1.f / Lsum[q] : 0.f;
+        uint2 o;
+        o.x = pack2<T>(acc[q].x * inv, acc[q].y * inv);
+        o.y = pack2<T>(acc[q].z * inv, acc[q].w * inv);
+        *reinterpret_cast<uint2*>(outp + (bh + head) * kCkv + c4 * 4) = o;
+        if (p.lse && c4 == 0) p.lse[bh + head] = Lsum[q] > 0.f ? M[q] + fast_log2(Lsum[q]) : -INFINITY;
       }
     }
     if (tid == 0) p.counters[b] = 0;  // ready for the next launch

@@ -157,7 +157,7 @@ mla_prefill_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_const
       for (int i = 0; i < kChunks; ++i) {
         const int c = chunk_at(i);
         mbar_wait(&k_empty[st], ph ^ 1, p.status, kFaultEmptyBarrier);
-        if (lane == 0) {
+        if (elect_one()) {
           mbar_arrive_expect_tx(&k_full[st], kChunkBytes);
           if (c < kCkv / 64) tma_load_2d(ring + st * kStageBytes, &tm_qn, &k_full[st], c * 64, row0);
           else tma_load_2d(ring + st * kStageBytes, &tm_qp, &k_full[st], 0, row0);

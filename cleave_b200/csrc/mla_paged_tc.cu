@@ -56,7 +56,7 @@ constexpr int kKpeSlots = 2;
 constexpr int kQChunkBytes = kHeads * 128;    // 64 columns of the 16 Q rows
 constexpr int kQBytes = 9 * kQChunkBytes;
 constexpr int kPBytes = kQChunkBytes;         // 16 head rows x 64 tokens
-constexpr int kExchBytes = 1024;              // 2 x 4 x 16 tile maxima, 4 x 16 row sums
+constexpr int kExchBytes = 1024;              // 2 x 4 x 16 tile maxima, 4 x 16 row sums, 2 x 4 votes
 constexpr int kBarBytes = 512;
 constexpr int kFixedBytes = kPairSlots * kPairBytes + kKpeSlots * kChunkBytes + kQBytes + 2 * kPBytes + kExchBytes + kBarBytes;
 constexpr int kThreads = 16 * 32;
@@ -423,42 +423,50 @@ __global__ void __launch_bounds__(kThreads, 1) mla_paged_tc_kernel(const Params 
         tmem_ld_32x16(tmem_base + lane_field + kColS + sb * kHeads, sr);
         tmem_ld_wait();
         float s[kHeads];
-        float4* mx4 = reinterpret_cast<float4*>(max_exch + (sb * 4 + quarter) * kHeads);
-        {
-          float wm[kHeads];
+        bool over = false;  // some score of this thread exceeds its head's reference by more than the threshold
 #pragma unroll
-          for (int h = 0; h < kHeads; ++h) {
-            s[h] = live ? __uint_as_float(sr[h]) * p.scale_log2 : -INFINITY;
-            wm[h] = warp_max(s[h]);
-          }
-          if (lane == 0) {
-#pragma unroll
-            for (int h = 0; h < kHeads; h += 4) mx4[h >> 2] = make_float4(wm[h], wm[h + 1], wm[h + 2], wm[h + 3]);
-          }
+        for (int h = 0; h < kHeads; ++h) {
+          s[h] = live ? __uint_as_float(sr[h]) * p.scale_log2 : -INFINITY;
+          over |= s[h] > m_ref[h] + kRescaleThreshold;
         }
+        // The reference maxima move only on a piece's first tile and when a score outgrows them by 2^8 (rare), so
+        // the tile-wide maxima are not formed every tile: the four warps exchange one vote, and only when it fires
+        // do they reduce and exchange the sixteen maxima.
+        int* vote = reinterpret_cast<int*>(max_exch + 2 * 4 * kHeads + 4 * kHeads) + sb * 4;  // [2][4] behind the sums
+        const bool warp_over = i == 0 || __any_sync(0xffffffffu, over);
+        if (lane == 0) vote[quarter] = warp_over ? 1 : 0;
         named_bar_sync(1, kSoftmaxThreads);
-        float mt[kHeads];
-        {
-          const float4* all = reinterpret_cast<const float4*>(max_exch + sb * 4 * kHeads);
+        const int4 votes = *reinterpret_cast<const int4*>(vote);
+        if ((votes.x | votes.y | votes.z | votes.w) != 0) {  // the same decision in all 128 threads
+          float4* mx4 = reinterpret_cast<float4*>(max_exch + (sb * 4 + quarter) * kHeads);
+          {
+            float wm[kHeads];
 #pragma unroll
-          for (int h4 = 0; h4 < kHeads / 4; ++h4) {
-            float4 a = all[h4];
+            for (int h = 0; h < kHeads; ++h) wm[h] = warp_max(s[h]);
+            if (lane == 0) {
 #pragma unroll
-            for (int w = 1; w < 4; ++w) {
-              const float4 b = all[w * (kHeads / 4) + h4];
-              a.x = fmaxf(a.x, b.x); a.y = fmaxf(a.y, b.y); a.z = fmaxf(a.z, b.z); a.w = fmaxf(a.w, b.w);
+              for (int h = 0; h < kHeads; h += 4) mx4[h >> 2] = make_float4(wm[h], wm[h + 1], wm[h + 2], wm[h + 3]);
             }
-            mt[4 * h4] = a.x; mt[4 * h4 + 1] = a.y; mt[4 * h4 + 2] = a.z; mt[4 * h4 + 3] = a.w;
           }
-        }
-        if (i == 0) {
+          named_bar_sync(1, kSoftmaxThreads);
+          float mt[kHeads];
+          {
+            const float4* all = reinterpret_cast<const float4*>(max_exch + sb * 4 * kHeads);
 #pragma unroll
-          for (int h = 0; h < kHeads; ++h) m_ref[h] = mt[h] == -INFINITY ? 0.f : mt[h];
-        } else {
-          bool grow = false;
+            for (int h4 = 0; h4 < kHeads / 4; ++h4) {
+              float4 a = all[h4];
 #pragma unroll
-          for (int h = 0; h < kHeads; ++h) grow |= mt[h] > m_ref[h] + kRescaleThreshold;
-          if (grow) {  // rare, and the same decision in all 128 threads: a running maximum grew by more than 2^8
+              for (int w = 1; w < 4; ++w) {
+                const float4 b = all[w * (kHeads / 4) + h4];
+                a.x = fmaxf(a.x, b.x); a.y = fmaxf(a.y, b.y); a.z = fmaxf(a.z, b.z); a.w = fmaxf(a.w, b.w);
+              }
+              mt[4 * h4] = a.x; mt[4 * h4 + 1] = a.y; mt[4 * h4 + 2] = a.z; mt[4 * h4 + 3] = a.w;
+            }
+          }
+          if (i == 0) {
+#pragma unroll
+            for (int h = 0; h < kHeads; ++h) m_ref[h] = mt[h] == -INFINITY ? 0.f : mt[h];
+          } else {
             float alpha[kHeads];
 #pragma unroll
             for (int h = 0; h < kHeads; ++h) {

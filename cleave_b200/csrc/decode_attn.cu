@@ -4,7 +4,7 @@
 // all (request, kv head) items form one stream that is split evenly over the CTAs, so a CTA's
 // share may start or end in the middle of an item. A producer warp streams its share of tiles
 // into a ring of shared-memory stages (TMA tiled loads with the 128-byte swizzle when a tile maps
-// to whole boxes of the cache; otherwise four producer warps gather the token rows with 16-byte
+// to whole boxes of the cache; otherwise eight producer warps gather the token rows with 16-byte
 // cp.async into the same swizzled layout) and the
 // consumer warps run QK^T and PV on m16n8k16 tensor-core MMAs with a warp-shuffle online softmax
 // in the exp2 domain. An item finished inside one CTA is written directly; an item cut across
@@ -52,7 +52,9 @@ struct SmemPlan {
   static constexpr int kMatBytes = kTile * D * 2;
   static constexpr int kStageBytes = 2 * kMatBytes;
   static constexpr int kStages = 5;
-  static constexpr int kProducerWarps = GATHER ? 4 : 1;
+  // gather: eight copying warps - the bytes an SM keeps in flight are bounded per issuing warp (a gather-only kernel
+  // over random 1 KB rows moved 4.0 TB/s with four warps per SM whatever their depth, 6.0 with eight)
+  static constexpr int kProducerWarps = GATHER ? 8 : 1;
   static constexpr int kThreads = (kConsumerWarps + kProducerWarps) * 32;
   static constexpr int kMergeFloats = kRowsMax * D + 2 * kRowsMax;
   static constexpr int kMergeBytes = kConsumerWarps * kMergeFloats * 4;
@@ -221,7 +223,7 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
       } else {
-        // Row gather (pages smaller than a tile): four producer warps copy the 64 token
+        // Row gather (pages smaller than a tile): eight producer warps copy the 64 token
         // rows of a tile with 16-byte cp.async into the swizzled layout. Consecutive lanes copy
         // consecutive 16-byte chunks of a row, so one warp instruction moves whole rows (full 128-byte
         // lines) instead of a sliver of 32 rows; a thread's arrival on the full barrier fires when its
@@ -229,9 +231,10 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
         // critical path.
         const T* kc = reinterpret_cast<const T*>(p.k);
         const T* vc = reinterpret_cast<const T*>(p.v);
-        const int ptid = tid - kConsumerWarps * 32;   // 0..127
+        constexpr int kPThreads = Plan::kProducerWarps * 32;
+        const int ptid = tid - kConsumerWarps * 32;   // 0..kPThreads-1
         constexpr int kChunks = D / 8;                // 16-byte chunks per row
-        constexpr int kRowsPerRound = 128 / kChunks;  // rows the 128 threads cover at once
+        constexpr int kRowsPerRound = kPThreads / kChunks;  // rows the copying threads cover at once
         constexpr int kRounds = kTile / kRowsPerRound;
         const int c = ptid % kChunks, r_in = ptid / kChunks;
         auto load_pages = [&](int t, int (&pg)[kRounds]) {

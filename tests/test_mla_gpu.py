@@ -130,6 +130,19 @@ def test_paged_mla_tcgen05_large_logits_rescale_and_repeat(dt):
         assert_lse_close(lse, want_lse)
 
 
+def test_paged_mla_tcgen05_large_batch():
+    """700 short requests, some of them empty: every CTA walks many pieces, and most requests are whole inside
+    one CTA."""
+    rng = np.random.default_rng(5)
+    lens = [int(x) for x in rng.integers(0, 200, size=700)]
+    inp = cases.mla_paged_inputs(102, lens, 16, 512, 64, "bf16", cases.MLA_SM_SCALE)
+    out, lse = _run_paged(inp, "bf16", impl="tcgen05")
+    want_out, want_lse = orc.mla_paged_decode(inp["q_nope"], inp["q_pe"], inp["ckv_cache"], inp["kpe_cache"],
+                                              inp["kv_indptr"], inp["kv_indices"], inp["sm_scale"])
+    assert_close(out, want_out)
+    assert_lse_close(lse, want_lse)
+
+
 def test_mla_full_config_properties():
     """Benchmark configuration 4 at full size (batch 16, 128 heads, 512 + 64, KV 4096, bf16): compared with
     the oracle on one request, invariant under a permutation of the KV positions, and repeat

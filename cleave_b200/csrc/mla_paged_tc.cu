@@ -19,20 +19,26 @@
 // A 64-token tile is 72 KB and is fetched once: its eight latent chunks sit in four 16 KB slots of a ring of
 // eleven from the score product until the value product of their block has completed; the position chunks
 // have two slots of their own, released after the score product. The ring holds the tile whose value product
-// runs, the tile whose scores are in the softmax, and most of the tile after that, so the row gather runs a
-// tile and a half ahead of the tensor core. The score MMAs of tile g + 1 are issued before the value MMAs of
-// tile g. MMAs are issued under elect.sync with descriptors built from templates: with one provably active
-// thread the operands stay in uniform registers and an instruction goes out every ~40 clocks (measured: ~90
-// under `lane == 0` with descriptors assembled per instruction).
+// runs, the tile whose scores are in the softmax, and most of the tile after that. Two warps issue MMAs side by
+// side - one the score products, one the value products, ordered only by the barriers between them (S^T ->
+// softmax -> P^T) - because one warp issues an MMA of this size every ~55 clocks, which for the 52 MMAs of a tile
+// is as long as the tile's bytes take to arrive. MMAs are issued under elect.sync with descriptors built from
+// templates: with one provably active thread the operands stay in uniform registers (measured: an instruction
+// every ~40 clocks, against ~90 under `lane == 0` with descriptors assembled per instruction).
+//
+// The softmax keeps one reference maximum per head for the whole CTA and rescales O^T only when a score outgrows
+// it by more than 2^8 (exact). Whether that happened is one vote per warp and tile; the sixteen tile maxima are
+// reduced and exchanged only on a piece's first tile and when the vote fires.
 //
 // Work split: the 64-token tiles of all requests form one stream that is cut evenly over the persistent CTAs
 // (one per SM). A request that spans CTAs leaves unnormalised partials (O, m, l) in the workspace and the last
 // CTA to arrive combines them after its own tiles with all of its threads (the slots and counters are those of
 // the warp-MMA kernel of mla_decode.cu).
 //
-// Warp roles: 0 = Q staging (registers -> swizzled shared memory, prefetched a piece ahead), 1 = score-MMA issuer and
-// tensor-memory owner, 2 = value-MMA issuer, 3 = Q staging beside warp 0, 4..7 = softmax / epilogue / combine (lanes 0..15 of a warp = 16 tokens for S^T; thread =
-// latent column for O^T), 8..15 = row gather (16-byte cp.async, eight lanes per 128-byte line).
+// Warp roles: 0 and 3 = Q staging (registers -> swizzled shared memory, prefetched a piece ahead), 1 = score-MMA
+// issuer and tensor-memory owner, 2 = value-MMA issuer, 4..7 = softmax / epilogue (lanes 0..15 of a warp = 16
+// tokens for S^T; thread = latent column for O^T), 8..15 = row gather (16-byte cp.async, eight lanes per 128-byte
+// line; eight warps because what an SM keeps in flight is bounded per issuing warp). All warps combine.
 //
 // Reference semantics: python/cleave/dynamic/reference.py:282-320; replaces the kernel of
 // python/cleave/dynamic/paging/builders/mla.py:220 (tests/graph/handwritten/expected_kernels/

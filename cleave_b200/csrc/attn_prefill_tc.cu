@@ -9,7 +9,10 @@
 //   O += P V     A = P (tensor memory, 16-bit pairs written by the softmax warps, two buffers),
 //                B = V tile (shared memory, MN-major), D = O in tensor memory (D columns)
 // Warp roles: 0 = TMA producer for Q and K, 6 = TMA producer for V, 1 = MMA issuer and TMEM owner,
-// 2..5 = softmax / epilogue (thread = query row = TMEM lane). S(j+1) is issued before PV(j), so the
+// 2..5 and 8..11 = softmax / epilogue: two threads per query row (= TMEM lane), one for scores 0..63 of a tile
+// and one for scores 64..127, on warps of the same lane quarter; they exchange their row maxima through shared
+// memory once per tile. With one thread per row the kernel ran at the pace of its four softmax warps, one per
+// scheduler with 128 exponentials per thread and tile; eight warps put two on every scheduler. S(j+1) is issued before PV(j), so the
 // tensor pipe computes the next scores while the softmax warps work on the current ones. The softmax
 // keeps a reference maximum per row and rescales O only when the running maximum has grown by more
 // than 2^8 (exact: the factor is applied to O and to the row sum alike), so O stays in tensor memory.
@@ -27,8 +30,8 @@ namespace cb200 {
 namespace fa {
 
 constexpr int kBM = 128, kBN = 128;
-constexpr int kThreads = 224;       // static and ragged layouts
-constexpr int kThreadsPaged = 352;  // + four gather warps
+constexpr int kThreads = 384;       // static and ragged layouts: warps 0..11
+constexpr int kThreadsPaged = 512;  // + four gather warps (12..15)
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.f;  // log2 units
 // TMEM columns: S0 | S1 | O | P0 | P1
@@ -40,7 +43,7 @@ struct Cfg {
   static constexpr int kChunkBytes = 128 * 128;          // 128 rows x 128 bytes
   static constexpr int kTileBytes = kChunks * kChunkBytes;
   static constexpr int kStages = D == 64 ? 3 : 2;        // per K ring and per V ring
-  static constexpr int kSmemBytes = (1 + 2 * kStages) * kTileBytes + 1024 + 1024;
+  static constexpr int kSmemBytes = (1 + 2 * kStages) * kTileBytes + 4096 /*barriers, row exchange*/ + 1024;
 };
 
 struct Params {
@@ -93,6 +96,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   uint64_t* p_empty = p_full + 2;  // [2] the PV MMAs that read the P buffer have completed
   uint64_t* o_done = p_empty + 2;
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(o_done + 1);
+  float* mx_exch = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + 1024);  // [2 tiles][2 halves][128 rows]
+  float* l_exch = mx_exch + 2 * 2 * kBM;                                                  // [2 halves][128 rows]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   // heads of one query tile are neighbours (they share K/V in L2)
@@ -143,8 +148,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&s_full[s], 1);
-      mbar_init(&s_empty[s], 4);
-      mbar_init(&p_full[s], 4);
+      mbar_init(&s_empty[s], 8);
+      mbar_init(&p_full[s], 8);
       mbar_init(&p_empty[s], 1);
     }
     mbar_init(q_full, 1);
@@ -211,12 +216,12 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       __syncwarp();
       if (++st == kStages) { st = 0; ph ^= 1; }
     }
-  } else if (warp >= 7) {
+  } else if (warp >= 12) {
     // ================================================================ paged: K / V row gather
     if constexpr (MODE == 2) {
       // Consecutive lanes copy consecutive 16-byte chunks of a row, so one warp instruction moves whole
       // rows as full 128-byte lines; the 128 threads cover kRowsPerRound rows at once.
-      const int gtid = tid - 7 * 32;  // 0..127
+      const int gtid = tid - 12 * 32;  // 0..127
       constexpr int kChunksPerRow = D / 8;
       constexpr int kRowsPerRound = 128 / kChunksPerRow;
       constexpr int kRounds = kBN / kRowsPerRound;
@@ -313,14 +318,16 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       __syncwarp();
       if (++vst == kStages) { vst = 0; vph ^= 1; }
     }
-  } else {
-    // ================================================================ softmax / epilogue
+  } else if (warp != 7) {
+    // ================================================================ softmax / epilogue (warps 2..5 and 8..11)
     const int quarter = warp & 3;
+    const int half = warp >= 8 ? 1 : 0;   // which 64 of a tile's 128 scores this thread takes
     const int row = quarter * 32 + lane;  // query row inside the tile = TMEM lane
     const int qrow = q0 + row;
     const uint32_t lane_field = static_cast<uint32_t>(quarter * 32) << 16;
     const int key_limit = p.causal ? min(skv - 1, qrow + off) : skv - 1;  // last key this row sees
-    float m_ref = 0.f, l_run = 0.f;
+    const int pair_bar = 1 + quarter;     // named barrier of the two warps that share the rows
+    float m_ref = 0.f, l_run = 0.f;       // l_run: the sum over this thread's half of every tile
     // scores are scale_row * (q . k): the softmax scale in log2 units (the plain factor in linear mode)
     // times, for RMS-normalised queries, rsqrt(mean(q^2) + eps) of this thread's row, taken from the
     // resident Q tile (K arrives normalised)
@@ -345,31 +352,28 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       const int sb = j & 1, pb = j & 1;
       mbar_wait(&s_full[sb], (j >> 1) & 1, p.status, kFaultMmaBarrier);
       tc_fence_after();
-      uint32_t r[4][32];
+      uint32_t r[2][32];
 #pragma unroll
-      for (int q = 0; q < 4; ++q) tmem_ld_32x32(tmem_base + lane_field + kColS + sb * kBN + q * 32, r[q]);
+      for (int q = 0; q < 2; ++q) tmem_ld_32x32(tmem_base + lane_field + kColS + sb * kBN + half * 64 + q * 32, r[q]);
       tmem_ld_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_empty[sb]);
-      const int k0 = j * kBN;
+      const int k0 = j * kBN + half * 64;  // first key of this thread's scores
       if (p.linear) {
         // no softmax: P = scale * S rounded to the storage type; keys past the end are zero rows of K
         mbar_wait(&p_empty[pb], ((j >> 1) & 1) ^ 1, p.status, kFaultMmaBarrier);
         tc_fence_after();
+        uint32_t pk[32];
 #pragma unroll
-        for (int hh = 0; hh < 2; ++hh) {
-          uint32_t pk[32];
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int c = hh * 64 + 2 * i;
-            const float p0 = k0 + c <= key_limit ? __uint_as_float(r[c >> 5][c & 31]) * scale_row : 0.f;
-            const float p1 = k0 + c + 1 <= key_limit ? __uint_as_float(r[(c + 1) >> 5][(c + 1) & 31]) * scale_row : 0.f;
-            pk[i] = pack2<T>(p0, p1);
-          }
-          tmem_st_32x32(tmem_base + lane_field + kColP + pb * 64 + hh * 32, pk);
+        for (int i = 0; i < 32; ++i) {
+          const int c = 2 * i;
+          const float p0 = k0 + c <= key_limit ? __uint_as_float(r[c >> 5][c & 31]) * scale_row : 0.f;
+          const float p1 = k0 + c + 1 <= key_limit ? __uint_as_float(r[(c + 1) >> 5][(c + 1) & 31]) * scale_row : 0.f;
+          pk[i] = pack2<T>(p0, p1);
         }
-        l_run = 1.f;
+        tmem_st_32x32(tmem_base + lane_field + kColP + pb * 64 + half * 32, pk);
+        l_run = half == 0 ? 1.f : 0.f;
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
@@ -377,9 +381,9 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         continue;
       }
       float mx = -INFINITY;
-      if (k0 + kBN - 1 <= key_limit) {  // whole tile visible to this row
+      if (k0 + 63 <= key_limit) {  // this thread's half of the tile is visible to the row
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
+        for (int q = 0; q < 2; ++q) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             const float v = __uint_as_float(r[q][i]) * scale_row;
@@ -389,7 +393,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         }
       } else {
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
+        for (int q = 0; q < 2; ++q) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             const float v = k0 + q * 32 + i <= key_limit ? __uint_as_float(r[q][i]) * scale_row : -INFINITY;
@@ -398,6 +402,10 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
           }
         }
       }
+      // the row maximum over both halves: the partner thread sits in the warp of the same lane quarter
+      mx_exch[(sb * 2 + half) * kBM + row] = mx;
+      named_bar_sync(pair_bar, 64);
+      mx = fmaxf(mx, mx_exch[(sb * 2 + (half ^ 1)) * kBM + row]);
       float alpha = 1.f;
       bool rescale = false;
       if (j == 0) {
@@ -410,11 +418,12 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       // the P buffer is free once the PV MMAs of tile j - 2 have completed
       mbar_wait(&p_empty[pb], ((j >> 1) & 1) ^ 1, p.status, kFaultMmaBarrier);
       if (__any_sync(0xffffffffu, rescale)) {  // rare: the running maximum grew by more than 2^8
-        // O may only be touched when no PV MMA is in flight: tile j - 1 is the last one issued
+        // O may only be touched when no PV MMA is in flight: tile j - 1 is the last one issued. The two threads
+        // of a row came to the same decision (same maximum) and take half of the row's columns each.
         mbar_wait(&p_empty[pb ^ 1], ((j - 1) >> 1) & 1, p.status, kFaultMmaBarrier);
         tc_fence_after();
 #pragma unroll 1
-        for (int c0 = 0; c0 < D; c0 += 32) {
+        for (int c0 = half * (D / 2); c0 < (half + 1) * (D / 2); c0 += 32) {
           uint32_t o[32];
           tmem_ld_32x32(tmem_base + lane_field + kColO + c0, o);
           tmem_ld_wait();
@@ -426,18 +435,17 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       }
       tc_fence_after();
       float psum = 0.f;
-#pragma unroll
-      for (int hh = 0; hh < 2; ++hh) {
+      {
         uint32_t pk[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          const int c = hh * 64 + 2 * i;
+          const int c = 2 * i;
           const float p0 = fast_exp2(__uint_as_float(r[c >> 5][c & 31]) - m_ref);
           const float p1 = fast_exp2(__uint_as_float(r[(c + 1) >> 5][(c + 1) & 31]) - m_ref);
           psum += p0 + p1;
           pk[i] = pack2<T>(p0, p1);
         }
-        tmem_st_32x32(tmem_base + lane_field + kColP + pb * 64 + hh * 32, pk);
+        tmem_st_32x32(tmem_base + lane_field + kColP + pb * 64 + half * 32, pk);
       }
       l_run = l_run * alpha + psum;
       tmem_st_wait();
@@ -445,7 +453,10 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full[pb]);
     }
-    // ---- epilogue: O / l
+    // ---- epilogue: O / l; the row sum is the two threads' together, and each stores half of the row's columns
+    l_exch[half * kBM + row] = l_run;
+    named_bar_sync(pair_bar, 64);
+    l_run += l_exch[(half ^ 1) * kBM + row];
     if (nt > 0) {
       mbar_wait(o_done, 0, p.status, kFaultMmaBarrier);
       tc_fence_after();
@@ -455,7 +466,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     const size_t orow = RAGGED ? static_cast<size_t>(q_base + qrow) * p.hq + h : static_cast<size_t>(h) * sq + qrow;
     T* outp = reinterpret_cast<T*>(p.out) + orow * D;
 #pragma unroll 1
-    for (int c0 = 0; c0 < D; c0 += 32) {
+    for (int c0 = half * (D / 2); c0 < (half + 1) * (D / 2); c0 += 32) {
       uint32_t o[32];
       if (nt > 0) {
         tmem_ld_32x32(tmem_base + lane_field + kColO + c0, o);
@@ -477,7 +488,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         }
       }
     }
-    if (live && p.lse && !p.linear) p.lse[orow] = l_run > 0.f ? m_ref + fast_log2(l_run) : -INFINITY;
+    if (half == 0 && live && p.lse && !p.linear) p.lse[orow] = l_run > 0.f ? m_ref + fast_log2(l_run) : -INFINITY;
   }
 
   tc_fence_before();

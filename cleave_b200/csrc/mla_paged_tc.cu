@@ -141,7 +141,8 @@ __global__ void __launch_bounds__(kThreads, 1) mla_paged_tc_kernel(const Params 
   uint64_t* pv_done = p_full + 2;                  // [2] the value MMAs of a tile have completed
   uint64_t* o_free = pv_done + 2;                  // the epilogue has read O^T
   uint64_t* merge_bar = o_free + 1;                // partials of a split request have landed in the tile slots
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(merge_bar + 1);
+  uint64_t* part_ready = merge_bar + 1;            // the softmax warps have stored a piece's partial
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(part_ready + 1);
   int* pending = reinterpret_cast<int*>(tmem_holder + 2);  // [0] count, then (request, first CTA, last CTA): at most two
   int* P = reinterpret_cast<int*>(smem + kFixedBytes);  // tile prefix per request
 
@@ -197,6 +198,7 @@ __global__ void __launch_bounds__(kThreads, 1) mla_paged_tc_kernel(const Params 
     }
     mbar_init(o_free, 4);
     mbar_init(merge_bar, 1);
+    mbar_init(part_ready, 4);
     mbar_fence_init();
     pending[0] = 0;
   }
@@ -224,6 +226,31 @@ __global__ void __launch_bounds__(kThreads, 1) mla_paged_tc_kernel(const Params 
     const T* qp = reinterpret_cast<const T*>(p.q_pe);
     constexpr int kPiecesPerRow = (kCkv + kKpe) / 8;                // 72
     constexpr int kPerLane = kHeads * kPiecesPerRow / 32;           // 36
+    // Warp 3 also publishes the partials of pieces that are not whole requests: the softmax warps only store them
+    // and arrive on a barrier; the fence that makes them visible to other SMs, the arrival on the request's counter
+    // and the note for the combine happen here, off the softmax warps' path (a fence costs them about a
+    // microsecond per piece otherwise).
+    int n_partial = 0;
+    auto publish = [&](const Piece& pp, int u_at) {
+      const bool whole = u_at == pp.unit0 && pp.count == pp.n_tiles;
+      if (whole) return;
+      mbar_wait(part_ready, n_partial & 1, p.status, kFaultTmemBarrier);
+      ++n_partial;
+      if (lane == 0) {
+        __threadfence();
+        const int c_first = pp.unit0 / span, c_last = (pp.unit0 + pp.n_tiles - 1) / span;
+        if (atomicAdd(p.counters + pp.b, 1) == c_last - c_first) {
+          int* e = pending + 1 + 3 * pending[0];
+          e[0] = pp.b;
+          e[1] = c_first;
+          e[2] = c_last;
+          pending[0] += 1;
+        }
+      }
+      __syncwarp();
+    };
+    Piece prev{};
+    int prev_u = 0;
     int piece_idx = 0;
     for (int u = u0; u < u1; ++piece_idx) {
       const Piece pc = walker.at(u, u1);
@@ -250,8 +277,12 @@ __global__ void __launch_bounds__(kThreads, 1) mla_paged_tc_kernel(const Params 
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(q_full);
+      if (warp == 3 && piece_idx > 0) publish(prev, prev_u);
+      prev = pc;
+      prev_u = u;
       u += pc.count;
     }
+    if (warp == 3 && piece_idx > 0) publish(prev, prev_u);
     // Requests without any live token: out = 0, lse = -inf (warp 0, idle once Q is staged).
     for (int b = blockIdx.x; warp == 0 && b < p.batch; b += G) {
       if (P[b + 1] - P[b] != 0) continue;
@@ -578,21 +609,9 @@ __global__ void __launch_bounds__(kThreads, 1) mla_paged_tc_kernel(const Params 
       __syncwarp();
       if (lane == 0) mbar_arrive(o_free);  // the next piece's value MMAs may overwrite O^T
 
-      if (!whole) {
-        // publish the partial; the last CTA of the request to arrive notes the request down and combines it
-        // after its own tiles, with all of its threads
-        __threadfence();
-        named_bar_sync(1, kSoftmaxThreads);
-        if (st == 0) {
-          const int c_first = pc.unit0 / span, c_last = (pc.unit0 + pc.n_tiles - 1) / span;
-          if (atomicAdd(p.counters + pc.b, 1) == c_last - c_first) {
-            int* e = pending + 1 + 3 * pending[0];
-            e[0] = pc.b;
-            e[1] = c_first;
-            e[2] = c_last;
-            pending[0] += 1;
-          }
-        }
+      if (!whole) {  // the partial is stored; warp 3 publishes it (fence, counter, note for the combine)
+        __syncwarp();
+        if (lane == 0) mbar_arrive(part_ready);
       }
       u += pc.count;
     }

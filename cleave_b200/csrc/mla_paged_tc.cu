@@ -148,6 +148,37 @@ __global__ void __launch_bounds__(kThreads, 1) mla_paged_tc_kernel(const Params 
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
+  // The launch carries the programmatic-serialization attribute: this CTA may be scheduled while the kernel before
+  // it in the stream still drains. Barriers and tensor memory are set up first; nothing that kernel may have
+  // written (Q, the caches, the page table, the workspace) is touched before pdl_wait().
+  if (tid == 0) {
+    for (int s = 0; s < kPairSlots; ++s) {
+      mbar_init(&pair_full[s], kGatherThreads);
+      mbar_init(&pair_empty[s], 1);
+    }
+    for (int s = 0; s < kKpeSlots; ++s) {
+      mbar_init(&kpe_full[s], kGatherThreads);
+      mbar_init(&kpe_empty[s], 1);
+    }
+    mbar_init(q_full, 2);
+    mbar_init(q_free, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&s_full[s], 1);
+      mbar_init(&p_full[s], 4);
+      mbar_init(&pv_done[s], 1);
+    }
+    mbar_init(o_free, 4);
+    mbar_init(merge_bar, 1);
+    mbar_init(part_ready, 4);
+    mbar_fence_init();
+    pending[0] = 0;
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_holder, 128);
+    tmem_relinquish();
+  }
+  pdl_wait();
+  pdl_launch_dependents();  // the next kernel's CTAs may take SMs as this grid's CTAs retire
   // ---- tile prefix over requests (every CTA computes the same table): per-thread counts, one warp scans them
   {
     int* scratch = reinterpret_cast<int*>(p_smem);  // free until the first tile
@@ -179,32 +210,6 @@ __global__ void __launch_bounds__(kThreads, 1) mla_paged_tc_kernel(const Params 
       P[i] = run;
       run += ceil_div(req_len(p, i), kTile);
     }
-  }
-  if (tid == 0) {
-    for (int s = 0; s < kPairSlots; ++s) {
-      mbar_init(&pair_full[s], kGatherThreads);
-      mbar_init(&pair_empty[s], 1);
-    }
-    for (int s = 0; s < kKpeSlots; ++s) {
-      mbar_init(&kpe_full[s], kGatherThreads);
-      mbar_init(&kpe_empty[s], 1);
-    }
-    mbar_init(q_full, 2);
-    mbar_init(q_free, 1);
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(&s_full[s], 1);
-      mbar_init(&p_full[s], 4);
-      mbar_init(&pv_done[s], 1);
-    }
-    mbar_init(o_free, 4);
-    mbar_init(merge_bar, 1);
-    mbar_init(part_ready, 4);
-    mbar_fence_init();
-    pending[0] = 0;
-  }
-  if (warp == 1) {
-    tmem_alloc(tmem_holder, 128);
-    tmem_relinquish();
   }
   tc_fence_before();
   __syncthreads();
@@ -741,8 +746,20 @@ int launch_mla_paged_tc(const cb200_mla_decode_args* a, int* status, float* part
     CB200_CUDA_TRY(cudaFuncSetAttribute(mla_paged_tc_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     if (dev < 64) configured[dev] = true;
   }
-  if (a->dtype == CB200_F16) mla_paged_tc_kernel<__half><<<grid, kThreads, smem, stream>>>(p);
-  else mla_paged_tc_kernel<__nv_bfloat16><<<grid, kThreads, smem, stream>>>(p);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  // the grid may be scheduled while the preceding kernel of the stream drains; it waits (griddepcontrol.wait)
+  // before its first global access
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (a->dtype == CB200_F16) CB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, mla_paged_tc_kernel<__half>, p));
+  else CB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, mla_paged_tc_kernel<__nv_bfloat16>, p));
   CB200_CUDA_TRY(cudaGetLastError());
   return CB200_OK;
 }

@@ -192,6 +192,34 @@ def test_static_mla_after_a_kernel_that_appends_to_the_caches(impl):
         torch.cuda.synchronize()
 
 
+def test_paged_mla_tcgen05_after_a_kernel_that_rewrites_its_inputs():
+    """The paged tcgen05 kernel is a dependent launch too: it may be scheduled while the kernel before it on the
+    stream still runs and must not read the caches, Q or the page table before that kernel has finished."""
+    lens = [700, 64, 1300, 90]
+    a = cases.mla_paged_inputs(201, lens, 16, 512, 64, "bf16", cases.MLA_SM_SCALE)
+    b = cases.mla_paged_inputs(202, lens, 16, 512, 64, "bf16", cases.MLA_SM_SCALE)   # same shapes, other data and pages
+    ops = _ops()
+    dev_a = {k: dev(v, "bf16") if v.dtype != np.int32 else dev(v) for k, v in a.items() if isinstance(v, np.ndarray)}
+    dev_b = {k: dev(v, "bf16") if v.dtype != np.int32 else dev(v) for k, v in b.items() if isinstance(v, np.ndarray)}
+    names = ("q_nope", "q_pe", "ckv_cache", "kpe_cache", "kv_indptr", "kv_indices")
+    live = {k: dev_a[k].clone() for k in names}
+    run = lambda: ops.mla_paged_decode(live["q_nope"], live["q_pe"], live["ckv_cache"], live["kpe_cache"],   # noqa: E731
+                                       live["kv_indptr"], live["kv_indices"], a["sm_scale"], impl="tcgen05")
+    run()
+    torch.cuda.synchronize()
+    want = {}
+    for tag, src in (("a", a), ("b", b)):
+        want[tag] = orc.mla_paged_decode(src["q_nope"], src["q_pe"], src["ckv_cache"], src["kpe_cache"],
+                                         src["kv_indptr"], src["kv_indices"], src["sm_scale"])
+    for tag, src in (("b", dev_b), ("a", dev_a), ("b", dev_b)):
+        for k in names:
+            live[k].copy_(src[k])          # rewrites every input right before the launch, on the same stream
+        out, lse = run()
+        _check_ws()
+        assert_close(host(out), want[tag][0])
+        assert_lse_close(host(lse), want[tag][1])
+
+
 @pytest.mark.parametrize("impl", ["tile", "per_token"])
 def test_paged_causal_mla_prefill_matches_reference_golden_and_oracle(impl):
     """Reference: python/cleave/dynamic/reference.py:324-365 (mla_paged_prefill_causal_h16_ckv512_kpe64_ps1):

@@ -193,6 +193,40 @@ def test_compile_causal_prefill_operators(tmp_path, op):
     assert torch.equal(out, out3) and torch.equal(lse, lse3)
 
 
+SHIPPED = [  # the nine operators of the reference's registry (python/cleave/dynamic/registry.py:91-196), with their dims
+    ("gqa_paged_decode", dict(num_qo_heads=32, num_kv_heads=8, head_dim=128, page_size=1)),
+    ("gqa_paged_decode", dict(num_qo_heads=32, num_kv_heads=4, head_dim=128, page_size=1)),
+    ("gqa_paged_decode", dict(num_qo_heads=32, num_kv_heads=8, head_dim=128, page_size=64)),
+    ("gqa_paged_prefill_causal", dict(num_qo_heads=32, num_kv_heads=8, head_dim=128)),
+    ("gqa_paged_prefill_causal", dict(num_qo_heads=32, num_kv_heads=4, head_dim=128)),
+    ("gqa_ragged_prefill_causal", dict(num_qo_heads=32, num_kv_heads=8, head_dim=128)),
+    ("gqa_ragged_prefill_causal", dict(num_qo_heads=32, num_kv_heads=4, head_dim=128)),
+    ("mla_paged_decode", dict(num_qo_heads=16, head_dim_ckv=512, head_dim_kpe=64)),
+    ("mla_paged_prefill_causal", dict(num_qo_heads=16, head_dim_ckv=512, head_dim_kpe=64)),
+]
+
+
+@pytest.mark.parametrize("op,dims", SHIPPED, ids=[f"{o}-{'-'.join(str(v) for v in d.values())}" for o, d in SHIPPED])
+def test_every_shipped_paged_operator_at_its_own_dims(op, dims):
+    """Each operator the reference ships, with the head counts and page size it ships them with: compiled, validated
+    over workloads, and called on fresh inputs against the reference's torch semantics."""
+    import cleave_b200 as cleave
+    from cleave_b200.pipeline.dynamic import OPERATORS, make_inputs, reference
+
+    family = OPERATORS[op][0]
+    prefill = "prefill" in family
+    wl = ([("a", ([90, 0, 260], [300, 40, 260])), ("b", ([1, 129], [700, 129]))] if prefill
+          else [("a", [700, 1, 129, 64]), ("b", [5, 0, 2100])])
+    k = cleave.compile(op, dtype="bfloat16", workloads=wl, **dims)
+    assert k.report.n_workloads == 2 and k.report.best() is not None
+    lens = ([150, 0, 64], [410, 12, 64]) if prefill else [333, 0, 65, 1500]
+    args = make_inputs(family, dims, lens, "bfloat16", seed=11)
+    want_out, want_lse = reference(family, args)
+    out, lse = k(*args)
+    torch.testing.assert_close(out.float(), want_out.float(), rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(lse, want_lse, rtol=1e-2, atol=1e-2)
+
+
 def test_check_code_in_a_spawned_worker(tmp_path):
     """The default check function is picklable and runs in a spawned worker with its own CUDA context,
     reading the parent-built reference file (reference: python/cleave/runtime/workers.py:104-122)."""

@@ -106,14 +106,32 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   int q0, sq, skv, q_base = 0, kv_base = 0;
   if constexpr (RAGGED) {
     // late query tiles, which see the most keys under the causal mask, are scheduled first
-    int t = static_cast<int>(gridDim.x / p.hq) - 1 - static_cast<int>(blockIdx.x / p.hq), r = 0, lo = __ldg(p.qo_indptr);
+    // Every warp searches the query offsets 32 requests at a time (lane = request, tile counts scanned with shuffles):
+    // a CTA's place costs a few hundred clocks whatever the batch. (A thread walking the offsets one by one spent a
+    // microsecond per 50 requests, in every one of the thousands of small CTAs a batch of short prompts makes.)
+    int t = static_cast<int>(gridDim.x / p.hq) - 1 - static_cast<int>(blockIdx.x / p.hq), r = 0;
     bool found = false;
-    for (; r < p.batch; ++r) {
-      const int hi = __ldg(p.qo_indptr + r + 1);
+    for (int r0 = 0; r0 < p.batch && !found; r0 += 32) {
+      const int rr = r0 + lane;
+      const int lo = rr < p.batch ? __ldg(p.qo_indptr + rr) : 0, hi = rr < p.batch ? __ldg(p.qo_indptr + rr + 1) : 0;
       const int tiles = hi > lo ? ceil_div(hi - lo, kBM) : 0;
-      if (t < tiles) { found = true; q_base = lo; sq = hi - lo; break; }
-      t -= tiles;
-      lo = hi;
+      int incl = tiles;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
+      }
+      const int all = __shfl_sync(0xffffffffu, incl, 31);
+      if (t < all) {
+        const int first = __ffs(__ballot_sync(0xffffffffu, incl > t)) - 1;
+        r = r0 + first;
+        t -= __shfl_sync(0xffffffffu, incl - tiles, first);
+        q_base = __shfl_sync(0xffffffffu, lo, first);
+        sq = __shfl_sync(0xffffffffu, hi, first) - q_base;
+        found = true;
+      } else {
+        t -= all;
+      }
     }
     if (!found) return;  // the grid is an upper bound on the number of query tiles
     kv_base = __ldg(p.kv_indptr + r);
@@ -139,6 +157,19 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     nt = last_key < 0 ? 0 : min(nt, last_key / kBN + 1);
   }
 
+  if (RAGGED && nt == 0) {
+    // No key is visible to any row of this tile (an empty request, or query rows the end-aligned mask leaves
+    // blind): the rows are 0 and -inf, as the reference's preallocation leaves them, and nothing else is set up.
+    const int rows = min(kBM, sq - q0);
+    T* outp = reinterpret_cast<T*>(p.out);
+    for (int i = tid; i < rows * (D / 8); i += blockDim.x) {
+      const int rw = i / (D / 8), c = i - rw * (D / 8);
+      *reinterpret_cast<uint4*>(outp + (static_cast<size_t>(q_base + q0 + rw) * p.hq + h) * D + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+    }
+    if (p.lse && !p.linear)
+      for (int i = tid; i < rows; i += blockDim.x) p.lse[static_cast<size_t>(q_base + q0 + i) * p.hq + h] = -INFINITY;
+    return;
+  }
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&k_full[s], MODE == 2 ? 128 : 1);

@@ -129,14 +129,9 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_ckv, const __grid_const
     for (int i = i0; i < i1; ++i) sum += ceil_div(req_len(p, i), kTile);
     scratch[tid] = sum;
     __syncthreads();
-    if (tid == 0) {
-      int run = 0;
-      for (int t = 0; t < nthreads; ++t) {
-        const int s = scratch[t];
-        scratch[t] = run;
-        run += s;
-      }
-      P[p.batch] = run;
+    if (tid < 32) {
+      const int all = warp_scan_in_place(scratch, nthreads, tid);
+      if (tid == 0) P[p.batch] = all;
     }
     __syncthreads();
     int run = scratch[tid];

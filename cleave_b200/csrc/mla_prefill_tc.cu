@@ -91,15 +91,31 @@ mla_prefill_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_const
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int dh = blockIdx.x & 1;  // which half of the output columns
   // ---- which (request, query block) this CTA works on: late blocks, which see the most keys, come first
-  int t = static_cast<int>(gridDim.x >> 1) - 1 - static_cast<int>(blockIdx.x >> 1), r = 0, lo = __ldg(p.qo_indptr);
+  // (every warp searches the query offsets 32 requests at a time: lane = request, block counts scanned with shuffles)
+  int t = static_cast<int>(gridDim.x >> 1) - 1 - static_cast<int>(blockIdx.x >> 1), r = 0, lo = 0;
   int q_len = 0;
   bool found = false;
-  for (; r < p.batch; ++r) {
-    const int hi = __ldg(p.qo_indptr + r + 1);
-    const int blocks = hi > lo ? ceil_div(hi - lo, p.qb) : 0;
-    if (t < blocks) { found = true; q_len = hi - lo; break; }
-    t -= blocks;
-    lo = hi;
+  for (int r0 = 0; r0 < p.batch && !found; r0 += 32) {
+    const int rr = r0 + lane;
+    const int lo_r = rr < p.batch ? __ldg(p.qo_indptr + rr) : 0, hi_r = rr < p.batch ? __ldg(p.qo_indptr + rr + 1) : 0;
+    const int blocks = hi_r > lo_r ? ceil_div(hi_r - lo_r, p.qb) : 0;
+    int incl = blocks;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += v;
+    }
+    const int all = __shfl_sync(0xffffffffu, incl, 31);
+    if (t < all) {
+      const int first = __ffs(__ballot_sync(0xffffffffu, incl > t)) - 1;
+      r = r0 + first;
+      t -= __shfl_sync(0xffffffffu, incl - blocks, first);
+      lo = __shfl_sync(0xffffffffu, lo_r, first);
+      q_len = __shfl_sync(0xffffffffu, hi_r, first) - lo;
+      found = true;
+    } else {
+      t -= all;
+    }
   }
   if (!found) return;  // the grid is an upper bound on the number of query blocks
   const int q_base = lo;                 // first query token of the request
@@ -113,6 +129,19 @@ mla_prefill_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_const
   const int last_key = min(kv_len - 1, q0 + live_q - 1 + off);
   const int nt = last_key < 0 ? 0 : last_key / kBN + 1;
 
+  if (nt == 0) {
+    // no key is visible to any row of this block: 0 and -inf, and nothing else is set up
+    T* outp = reinterpret_cast<T*>(p.out);
+    const int rows = live_q * p.heads;  // (token, head) pairs, contiguous in out
+    const size_t row0 = static_cast<size_t>(q_base + q0) * p.heads;
+    for (int i = tid; i < rows * (kDV / 8); i += blockDim.x) {
+      const int rw = i / (kDV / 8), c = i - rw * (kDV / 8);
+      *reinterpret_cast<uint4*>(outp + (row0 + rw) * kCkv + dh * kDV + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+    }
+    if (dh == 0 && p.lse)
+      for (int i = tid; i < rows; i += blockDim.x) p.lse[row0 + i] = -INFINITY;
+    return;
+  }
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&k_full[s], 129);  // 128 gather threads + the TMA thread's expect-tx arrival

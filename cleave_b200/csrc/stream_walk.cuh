@@ -6,6 +6,29 @@
 
 namespace cb200 {
 
+// Exclusive prefix sums of scratch[0 .. n) in place, by one warp (all 32 lanes call it); returns the total in every
+// lane. A lane sums a run of consecutive entries, the runs are scanned with shuffles. (One thread walking a few hundred
+// entries of shared memory, as the kernels did at first, costs about three microseconds at the head of every launch.)
+__device__ __forceinline__ int warp_scan_in_place(int* scratch, int n, int lane) {
+  const int per = (n + 31) / 32;
+  const int b = min(lane * per, n), e = min(b + per, n);
+  int mine = 0;
+  for (int k = b; k < e; ++k) mine += scratch[k];
+  int incl = mine;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int v = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += v;
+  }
+  int run = incl - mine;
+  for (int k = b; k < e; ++k) {
+    const int t = scratch[k];
+    scratch[k] = run;
+    run += t;
+  }
+  return __shfl_sync(0xffffffffu, incl, 31);
+}
+
 // The walk over a CTA's share of the tile stream; identical in the producer and the consumers.
 struct Piece {
   int b, hv, tile0, count, n_tiles, unit0;  // unit0: stream position of the item's first tile

@@ -26,6 +26,7 @@ namespace cb200 {
 constexpr int kTile = 64;          // tokens per KV tile
 constexpr int kRowsMax = 16;       // query rows one item carries (M of the MMA tile)
 constexpr int kConsumerWarps = 4;  // each owns 16 tokens of every tile
+constexpr int kPieceUnits = 3;     // what starting and finishing a piece costs, in tiles: the stream of a paged launch is cut by cost
 constexpr int kPrefetchTiles = 16; // tiles a CTA asks into L2 while it waits for the preceding kernel (contiguous caches)
 constexpr float kLog2e = 1.4426950408889634f;
 
@@ -107,7 +108,7 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
     const int per = ceil_div(p.batch, nthreads);
     const int i0 = min(tid * per, p.batch), i1 = min(i0 + per, p.batch);
     int sum = 0;
-    for (int i = i0; i < i1; ++i) sum += ceil_div(item_valid_len(p, i), kTile);
+    for (int i = i0; i < i1; ++i) sum += Walker::units(ceil_div(item_valid_len(p, i), kTile), kPieceUnits);
     scratch[tid] = sum;
     __syncthreads();
     if (tid < 32) {
@@ -118,7 +119,7 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
     int run = scratch[tid];
     for (int i = i0; i < i1; ++i) {
       P[i] = run;
-      run += ceil_div(item_valid_len(p, i), kTile);
+      run += Walker::units(ceil_div(item_valid_len(p, i), kTile), kPieceUnits);
     }
   } else {
     tiles_per_req = ceil_div(p.kv_len, kTile);
@@ -142,14 +143,15 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
   const int span = total > 0 ? ceil_div(total, G) : 1;
   const int u0 = min(static_cast<int>(blockIdx.x) * span, total);
   const int u1 = min(u0 + span, total);
-  Walker walker{p.paged ? P : nullptr, p.batch, hkvv, tiles_per_req};
+  Walker walker{p.paged ? P : nullptr, p.batch, hkvv, tiles_per_req, p.paged ? kPieceUnits : 0};
   if (!p.paged) {
     // Contiguous caches: where this CTA's first tiles lie follows from the launch parameters alone, so
     // while the preceding kernel still runs the TMA unit is asked to bring them into L2 (a hint: nothing
     // reaches the SM, and L2 is where that kernel's writes land too). The first ring fill then comes from
     // L2 with warm address translations instead of paying the cold 2.3 us.
     if (!GATHER && warp == kConsumerWarps && lane == 0 && u0 < u1) {
-      const Piece pc = walker.at(u0, u1);
+      int uf = u0;
+      const Piece pc = walker.at(uf, u1);
       const int h = pc.hv / p.vblk;
       for (int t = pc.tile0; t < pc.tile0 + min(pc.count, kPrefetchTiles); ++t) {
 #pragma unroll
@@ -168,6 +170,7 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
     int stage = 0, phase = 0;
     for (int u = u0; u < u1;) {
       const Piece pc = walker.at(u, u1);
+      if (pc.count == 0) break;  // the share ends in front of the next item's tiles
       const int h = pc.hv / p.vblk;
       const int valid = item_valid_len(p, pc.b);
       const int page_base = p.paged ? p.kv_indptr[pc.b] : 0;
@@ -294,6 +297,7 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
   int stage = 0, phase = 0;
   for (int u = u0; u < u1;) {
     const Piece pc = walker.at(u, u1);
+    if (pc.count == 0) break;  // the share ends in front of the next item's tiles
     const int h = pc.hv / p.vblk, blk = pc.hv - h * p.vblk;
     const int valid = item_valid_len(p, pc.b);
     const int rows_here = min(kRowsMax, p.rows - blk * kRowsMax);
@@ -582,7 +586,7 @@ int plan_decode(const cb200_attn_decode_args* a, DecodeSetup* s, bool need_maps)
     // instead (5.3 - 5.5 TB/s at any page size).
     s->gather = !(ps >= kTile && ps % kTile == 0);
     p.box_tok = kTile;
-    tiles_ub = (static_cast<long long>(a->num_kv_indices) * ps + kTile - 1) / kTile + a->batch;
+    tiles_ub = (static_cast<long long>(a->num_kv_indices) * ps + kTile - 1) / kTile + static_cast<long long>(a->batch) * (1 + kPieceUnits);
   } else {
     if (a->kv_len <= 0) return CB200_ERR_BAD_ARG;
     p.kv_len = a->kv_len;
@@ -593,7 +597,7 @@ int plan_decode(const cb200_attn_decode_args* a, DecodeSetup* s, bool need_maps)
   const long long units_ub = tiles_ub * p.hkv * p.vblk;
   // The kernel counts tiles in 32 bits. Requests may share pages (overlapping kv_indptr ranges), so the
   // bound for that count is every request spanning the whole table, not the table's own size.
-  const long long tiles_max = paged ? static_cast<long long>(a->batch) * ((static_cast<long long>(a->num_kv_indices) * a->page_size + kTile - 1) / kTile + 1)
+  const long long tiles_max = paged ? static_cast<long long>(a->batch) * ((static_cast<long long>(a->num_kv_indices) * a->page_size + kTile - 1) / kTile + 1 + kPieceUnits)
                                     : tiles_ub;
   if (tiles_max * p.hkv * p.vblk >= (1LL << 31)) return CB200_ERR_UNSUPPORTED;
   const int sms = sm_count();

@@ -161,7 +161,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_ckv, const __grid_const
   const int span = total > 0 ? ceil_div(total, G) : 1;
   const int u0 = min(static_cast<int>(blockIdx.x) * span, total);
   const int u1 = min(u0 + span, total);
-  Walker walker{p.paged ? P : nullptr, p.batch, hb_count, tiles_per_req};
+  Walker walker{p.paged ? P : nullptr, p.batch, hb_count, tiles_per_req, 0};
 
   if (warp >= kConsumerWarps) {
     // ================================================================= producer warp(s)
@@ -620,7 +620,8 @@ int plan_mla(const cb200_mla_decode_args* a, MlaSetup* s, bool need_maps) {
   // paged caches with at most 16 heads: the tcgen05 kernel that takes the tokens as MMA rows
   s->use_paged_tc = paged && a->impl != CB200_MLA_IMPL_MMA_SYNC && mla_paged_tc_supported(a);
   {
-    const long long tiles = (static_cast<long long>(a->num_kv_indices) + 63) / 64 + a->batch;  // its tiles hold 64 tokens
+    // its tiles hold 64 tokens, and every request with tokens carries two overhead units (the stream is cut by cost)
+    const long long tiles = (static_cast<long long>(a->num_kv_indices) + 63) / 64 + 3LL * a->batch;
     s->paged_tc_grid = static_cast<int>(tiles < grid ? (tiles > 0 ? tiles : 1) : grid);
   }
   if (a->impl == CB200_MLA_IMPL_TCGEN05 && !s->use_tc && !s->use_paged_tc) return CB200_ERR_UNSUPPORTED;

@@ -68,6 +68,7 @@ constexpr int kFixedBytes = kPairSlots * kPairBytes + kKpeSlots * kChunkBytes + 
 constexpr int kThreads = 16 * 32;
 constexpr int kGatherThreads = 8 * 32;        // warps 8..15
 constexpr int kSoftmaxThreads = 128;
+constexpr int kPieceUnits = 2;                // what a request's start and end cost a CTA, in tiles (the stream is cut by cost)
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.f;      // log2 units
 constexpr uint32_t kColS = 0, kColO = 32;     // tensor-memory columns: S^T 0 | S^T 1 | O^T blocks 0..3
@@ -185,7 +186,7 @@ __global__ void __launch_bounds__(kThreads, 1) mla_paged_tc_kernel(const Params 
     const int per = ceil_div(p.batch, kThreads);
     const int i0 = min(tid * per, p.batch), i1 = min(i0 + per, p.batch);
     int sum = 0;
-    for (int i = i0; i < i1; ++i) sum += ceil_div(req_len(p, i), kTile);
+    for (int i = i0; i < i1; ++i) sum += Walker::units(ceil_div(req_len(p, i), kTile), kPieceUnits);
     scratch[tid] = sum;
     __syncthreads();
     if (warp == 0) {
@@ -208,7 +209,7 @@ __global__ void __launch_bounds__(kThreads, 1) mla_paged_tc_kernel(const Params 
     int run = scratch[tid];
     for (int i = i0; i < i1; ++i) {
       P[i] = run;
-      run += ceil_div(req_len(p, i), kTile);
+      run += Walker::units(ceil_div(req_len(p, i), kTile), kPieceUnits);
     }
   }
   tc_fence_before();
@@ -221,7 +222,7 @@ __global__ void __launch_bounds__(kThreads, 1) mla_paged_tc_kernel(const Params 
   const int span = total > 0 ? ceil_div(total, G) : 1;
   const int u0 = min(static_cast<int>(blockIdx.x) * span, total);
   const int u1 = min(u0 + span, total);
-  const Walker walker{P, p.batch, 1, 0};
+  const Walker walker{P, p.batch, 1, 0, kPieceUnits};
   T* outp = reinterpret_cast<T*>(p.out);
 
   if (warp == 0 || warp == 3) {
@@ -259,6 +260,7 @@ __global__ void __launch_bounds__(kThreads, 1) mla_paged_tc_kernel(const Params 
     int piece_idx = 0;
     for (int u = u0; u < u1; ++piece_idx) {
       const Piece pc = walker.at(u, u1);
+      if (pc.count == 0) break;  // the share ends in front of the next request's tiles
       constexpr int kHalf = kPerLane / 2;
       const int k0 = warp == 0 ? 0 : kHalf;
       uint4 v[kHalf];
@@ -307,6 +309,7 @@ __global__ void __launch_bounds__(kThreads, 1) mla_paged_tc_kernel(const Params 
     int g = 0;
     for (int u = u0; u < u1;) {
       const Piece pc = walker.at(u, u1);
+      if (pc.count == 0) break;  // the share ends in front of the next request's tiles
       const int valid = req_len(p, pc.b), base = req_base(p, pc.b);
       auto page_of = [&](int tok) {
         return min(max(__ldg(p.kv_indices + base + min(tok, valid - 1)), 0), p.num_pages - 1);
@@ -373,6 +376,8 @@ __global__ void __launch_bounds__(kThreads, 1) mla_paged_tc_kernel(const Params 
     if (warp == 1) {
       for (int u = u0; u < u1; ++piece_idx) {
         const Piece pc = walker.at(u, u1);
+        if (pc.count == 0) break;
+      if (pc.count == 0) break;  // the share ends in front of the next request's tiles
         mbar_wait(q_full, piece_idx & 1, p.status, kFaultFullBarrier);
         tc_fence_after();
         for (int i = 0; i < pc.count; ++i, ++g) {
@@ -415,6 +420,8 @@ __global__ void __launch_bounds__(kThreads, 1) mla_paged_tc_kernel(const Params 
     } else {
       for (int u = u0; u < u1; ++piece_idx) {
         const Piece pc = walker.at(u, u1);
+        if (pc.count == 0) break;
+      if (pc.count == 0) break;  // the share ends in front of the next request's tiles
         for (int i = 0; i < pc.count; ++i, ++g) {
           mbar_wait(&p_full[g & 1], (g >> 1) & 1, p.status, kFaultTmemBarrier);
           // O^T of the piece before must have been read before its columns are overwritten
@@ -452,6 +459,7 @@ __global__ void __launch_bounds__(kThreads, 1) mla_paged_tc_kernel(const Params 
     int g = 0, piece_idx = 0;
     for (int u = u0; u < u1; ++piece_idx) {
       const Piece pc = walker.at(u, u1);
+      if (pc.count == 0) break;  // the share ends in front of the next request's tiles
       const int valid = req_len(p, pc.b);
       float m_ref[kHeads], l_part[kHeads];
 #pragma unroll

@@ -26,7 +26,7 @@ namespace cb200 {
 constexpr int kTile = 64;          // tokens per KV tile
 constexpr int kRowsMax = 16;       // query rows one item carries (M of the MMA tile)
 constexpr int kConsumerWarps = 4;  // each owns 16 tokens of every tile
-constexpr int kPieceUnits = 3;     // what starting and finishing a piece costs, in tiles: the stream of a paged launch is cut by cost
+constexpr int kPieceUnits = 5;     // what starting and finishing a piece costs, in tiles: the stream of a paged launch is cut by cost
 constexpr int kPrefetchTiles = 16; // tiles a CTA asks into L2 while it waits for the preceding kernel (contiguous caches)
 constexpr float kLog2e = 1.4426950408889634f;
 

@@ -114,6 +114,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     for (int r0 = 0; r0 < p.batch && !found; r0 += 32) {
       const int rr = r0 + lane;
       const int lo = rr < p.batch ? __ldg(p.qo_indptr + rr) : 0, hi = rr < p.batch ? __ldg(p.qo_indptr + rr + 1) : 0;
+      // the key range of the lane's request travels with the query range: one trip to memory, not two in a row
+      const int klo = rr < p.batch ? __ldg(p.kv_indptr + rr) : 0, khi = rr < p.batch ? __ldg(p.kv_indptr + rr + 1) : 0;
       const int tiles = hi > lo ? ceil_div(hi - lo, kBM) : 0;
       int incl = tiles;
 #pragma unroll
@@ -128,14 +130,14 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         t -= __shfl_sync(0xffffffffu, incl - tiles, first);
         q_base = __shfl_sync(0xffffffffu, lo, first);
         sq = __shfl_sync(0xffffffffu, hi, first) - q_base;
+        kv_base = __shfl_sync(0xffffffffu, klo, first);
+        skv = max(__shfl_sync(0xffffffffu, khi, first) - kv_base, 0);
         found = true;
       } else {
         t -= all;
       }
     }
     if (!found) return;  // the grid is an upper bound on the number of query tiles
-    kv_base = __ldg(p.kv_indptr + r);
-    skv = max(__ldg(p.kv_indptr + r + 1) - kv_base, 0);
     if constexpr (MODE == 2) {
       // the page table is caller data: a range that runs past its stated length is read as a shorter request
       if (p.n_idx > 0) {

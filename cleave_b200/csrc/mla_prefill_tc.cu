@@ -93,11 +93,12 @@ mla_prefill_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_const
   // ---- which (request, query block) this CTA works on: late blocks, which see the most keys, come first
   // (every warp searches the query offsets 32 requests at a time: lane = request, block counts scanned with shuffles)
   int t = static_cast<int>(gridDim.x >> 1) - 1 - static_cast<int>(blockIdx.x >> 1), r = 0, lo = 0;
-  int q_len = 0;
+  int q_len = 0, kv_base_found = 0, kv_end_found = 0;
   bool found = false;
   for (int r0 = 0; r0 < p.batch && !found; r0 += 32) {
     const int rr = r0 + lane;
     const int lo_r = rr < p.batch ? __ldg(p.qo_indptr + rr) : 0, hi_r = rr < p.batch ? __ldg(p.qo_indptr + rr + 1) : 0;
+    const int klo_r = rr < p.batch ? __ldg(p.kv_indptr + rr) : 0, khi_r = rr < p.batch ? __ldg(p.kv_indptr + rr + 1) : 0;
     const int blocks = hi_r > lo_r ? ceil_div(hi_r - lo_r, p.qb) : 0;
     int incl = blocks;
 #pragma unroll
@@ -112,6 +113,8 @@ mla_prefill_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_const
       t -= __shfl_sync(0xffffffffu, incl - blocks, first);
       lo = __shfl_sync(0xffffffffu, lo_r, first);
       q_len = __shfl_sync(0xffffffffu, hi_r, first) - lo;
+      kv_base_found = __shfl_sync(0xffffffffu, klo_r, first);
+      kv_end_found = __shfl_sync(0xffffffffu, khi_r, first);
       found = true;
     } else {
       t -= all;
@@ -120,8 +123,8 @@ mla_prefill_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_const
   if (!found) return;  // the grid is an upper bound on the number of query blocks
   const int q_base = lo;                 // first query token of the request
   const int q0 = t * p.qb;               // first query token of this block, inside the request
-  int kv_base = __ldg(p.kv_indptr + r);
-  int kv_len = __ldg(p.kv_indptr + r + 1) - kv_base;
+  int kv_base = kv_base_found;  // fetched beside the query offsets: one trip to memory, not two in a row
+  int kv_len = kv_end_found - kv_base;
   if (kv_base < 0 || kv_base >= p.n_idx) kv_len = 0;   // the table is caller data: stay inside it
   kv_len = max(min(kv_len, p.n_idx - kv_base), 0);
   const int off = kv_len - q_len;        // end-aligned causal mask: query i sees keys <= i + off

@@ -159,6 +159,8 @@ def lib() -> C.CDLL:
                 "(there is no CPU or PyTorch fallback)")
         L = C.CDLL(LIB_PATH)
         L.cb200_version.restype = C.c_int
+        L.cb200_set_small_problem_limit.restype = C.c_int
+        L.cb200_set_small_problem_limit.argtypes = [C.c_int]
         L.cb200_strerror.restype = C.c_char_p
         L.cb200_strerror.argtypes = [C.c_int]
         L.cb200_last_cuda_error.restype = C.c_int

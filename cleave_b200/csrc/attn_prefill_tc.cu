@@ -743,6 +743,15 @@ extern "C" int cb200_attn_prefill_ragged(const cb200_attn_prefill_ragged_args* a
     return CB200_ERR_ALIGNMENT;
   if (!a->workspace || a->workspace_bytes < kWsHeaderBytes) return CB200_ERR_WORKSPACE;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  {
+    // A key window far shorter than the run of query rows: only the last min(q_len, kv_len) rows of a request see a
+    // key, the rest are written as 0 / -inf, and two light kernels do both faster than a CTA per tile of 128 rows.
+    const int keys = a->kv_indices ? a->num_kv_indices : a->total_kv;
+    if (a->causal && small_prefill_applies(keys, a->total_q))
+      return launch_small_gqa(a->q, a->k, a->v, a->qo_indptr, a->kv_indptr, a->kv_indices, a->out, a->lse, a->batch, a->total_q,
+                              a->num_qo_heads, a->num_kv_heads, a->head_dim, a->kv_indices ? a->total_kv : 0, keys, a->sm_scale,
+                              a->dtype, st);
+  }
   const bool f16 = a->dtype == CB200_F16;
   if (a->head_dim == 64)
     return f16 ? launch_prefill_ragged<__half, 64>(a, st) : launch_prefill_ragged<__nv_bfloat16, 64>(a, st);

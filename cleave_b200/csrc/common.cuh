@@ -423,4 +423,16 @@ bool encode_tensor_map(CUtensorMap* out, CUtensorMapDataType dt, int rank, void*
 
 int sm_count();
 
+// small_attn.cu: causal prefill whose key window is far shorter than its run of query rows (one CTA per row that
+// sees a key, one warp per blind row). small_prefill_applies: what the host can tell from the sizes alone.
+int small_problem_limit();
+bool small_prefill_applies(int keys, int total_q);
+int launch_small_gqa(const void* q, const void* k, const void* v, const int* qo_indptr, const int* kv_indptr,
+                     const int* kv_indices, void* out, float* lse, int batch, int rows, int hq, int hkv, int head_dim,
+                     int num_pages, int n_idx, float sm_scale, int dtype, cudaStream_t stream);
+int launch_small_mla(const void* q_nope, const void* q_pe, const void* ckv, const void* kpe, const int* qo_indptr,
+                     const int* kv_indptr, const int* kv_indices, void* out, float* lse, int batch, int rows, int heads,
+                     int num_pages, int n_idx, float sm_scale, int dtype, cudaStream_t stream);
+
+
 }  // namespace cb200

@@ -478,5 +478,9 @@ extern "C" int cb200_mla_prefill(const cb200_mla_prefill_args* a, void* stream) 
     return CB200_ERR_ALIGNMENT;
   if (!a->workspace || a->workspace_bytes < kWsHeaderBytes) return CB200_ERR_WORKSPACE;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // a page table far shorter than the run of query rows: most rows see no key (see small_attn.cu)
+  if (small_prefill_applies(a->num_kv_indices, a->total_q))
+    return launch_small_mla(a->q_nope, a->q_pe, a->ckv_cache, a->kpe_cache, a->qo_indptr, a->kv_indptr, a->kv_indices, a->out,
+                            a->lse, a->batch, a->total_q, a->num_heads, a->num_pages, a->num_kv_indices, a->sm_scale, a->dtype, st);
   return a->dtype == CB200_F16 ? mlapf::launch<__half>(a, st) : mlapf::launch<__nv_bfloat16>(a, st);
 }

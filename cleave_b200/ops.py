@@ -50,6 +50,13 @@ def workspace(kind: str, nbytes: int, device) -> torch.Tensor:
     return ws
 
 
+def set_small_problem_limit(tokens: int) -> int:
+    """Causal prefill with at most ``tokens`` keys (default 256) and at least eight times as many query rows runs on
+    two light kernels (one CTA per row that sees a key, one warp per row that sees none) instead of the tcgen05
+    kernels; 0 = never. Returns the previous value. Process-wide."""
+    return int(_lib.lib().cb200_set_small_problem_limit(int(tokens)))
+
+
 def check_workspace(ws: torch.Tensor) -> None:
     """Synchronise and raise ``Cb200Error`` (status 6) if a kernel recorded a bounded-wait timeout in
     ``ws``. The launch that gave up left arrival counters behind, so the workspace is zero-filled again

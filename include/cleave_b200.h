@@ -41,7 +41,7 @@ extern "C" {
  *    cb200_gemm_args gained
  *    the trailing field ldx (zero = the behaviour of version 2). */
 /* 4: cb200_attn_prefill_ragged_args gained the trailing field num_kv_indices (zero = the behaviour of
- *    version 3); the paged MLA decode clips request ranges to num_kv_indices. */
+ *    version 3); the paged MLA decode clips request ranges to num_kv_indices; new cb200_set_small_problem_limit. */
 #define CB200_VERSION 4
 
 typedef enum {
@@ -499,6 +499,18 @@ int cb200_attn_decode_static_scratch(const cb200_attn_decode_args* a, void* stre
  * the current device gave up, in which case that call's outputs are not valid. Ask before the next call: every
  * call clears the word. Allocates nothing. */
 int cb200_attn_decode_static_scratch_status(void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Causal prefill whose key window is far shorter than its run of query rows (a chunk with thousands of query tokens
+ * and a page table of a few dozen entries: only the last min(q_len, kv_len) rows of a request see a key, all others
+ * are 0 / -inf) is run by two light kernels - one CTA per row that sees a key, one warp per blind row - instead of
+ * the tcgen05 kernels: cb200_attn_prefill_ragged (causal, ragged or paged) and cb200_mla_prefill take them when the
+ * keys (num_kv_indices, or total_kv for ragged) number at most `tokens` (default 256) and the query rows at least
+ * eight times the keys. 0 turns the kernels off. Returns the previous value. Process-wide and not synchronised:
+ * set it before launching. No counterpart in the reference (its captured workloads are where such chunks come from:
+ * python/cleave/dynamic/workloads.py).
+ * ---------------------------------------------------------------------------------------- */
+int cb200_set_small_problem_limit(int tokens);
 
 #ifdef __cplusplus
 }

@@ -175,12 +175,13 @@ def attn_prefill_case_rect(hq, hkv, sq, skv, d, dtype=torch.float16):
     return fn, 4 * hq * sq * skv * d, (2 * q.numel() + 2 * k.numel()) * 2
 
 
-def paged_decode_case(page_size=1, batch=64, hi=8192):
+def paged_decode_case(page_size=1, batch=64, hi=8192, lo=512):
     """Paged GQA decode (32 / 8 heads, d 128, bf16) over a cache far larger than L2; page size 1 takes
-    the row-gather path."""
+    the row-gather path. Small ``batch`` and ``hi`` give the batches of a few short requests on which the fixed
+    cost of a launch is all there is to see."""
     from cleave_b200.workloads import paged_decode_workload
 
-    w = paged_decode_workload(batch=batch, page_size=page_size, lo=512, hi=hi, dtype=torch.bfloat16)
+    w = paged_decode_workload(batch=batch, page_size=page_size, lo=lo, hi=hi, dtype=torch.bfloat16)
     out = torch.empty_like(w.q)
     lse = torch.empty(w.q.shape[0], w.q.shape[1], dtype=torch.float32, device="cuda")
     last = None if page_size == 1 else w.kv_last_page_len
@@ -189,28 +190,43 @@ def paged_decode_case(page_size=1, batch=64, hi=8192):
     return fn, w.flops(), w.algorithmic_bytes()
 
 
-def gqa_dynamic_prefill_case(paged, batch=8, q_len=2048, hq=32, hkv=8, d=128, dtype=torch.bfloat16):
-    """Ragged or paged (one token per page) causal prefill of whole prompts."""
+def gqa_dynamic_prefill_case(paged, batch=8, q_len=2048, hq=32, hkv=8, d=128, dtype=torch.bfloat16, kv_len=None, light=True):
+    """Ragged or paged (one token per page) causal prefill: whole prompts, or with ``kv_len`` far below ``q_len`` a
+    chunk whose key window is much shorter than its run of query rows (only the last kv_len rows of a request see a
+    key); ``light=False`` keeps such a chunk on the tcgen05 kernel."""
     g = _gen()
-    tq = batch * q_len
+    kv_len = q_len if kv_len is None else kv_len
+    tq, tk = batch * q_len, batch * kv_len
     q = torch.randn(tq, hq, d, generator=g).to(dtype).cuda()
-    ptr = (torch.arange(batch + 1, dtype=torch.int32) * q_len).cuda()
+    qo = (torch.arange(batch + 1, dtype=torch.int32) * q_len).cuda()
+    kv = (torch.arange(batch + 1, dtype=torch.int32) * kv_len).cuda()
     out = torch.empty_like(q)
     lse = torch.empty(tq, hq, dtype=torch.float32, device="cuda")
-    flops = 4 * batch * hq * (q_len * (q_len + 1) // 2) * d
+    vis = min(q_len, kv_len)
+    flops = 4 * batch * hq * (vis * (vis + 1) // 2 + vis * (kv_len - vis)) * d
     if paged:
-        num_pages = tq + 8
+        num_pages = tk + 8
         kc = torch.randn(num_pages, 1, hkv, d, generator=g).to(dtype).cuda()
         vc = torch.randn(num_pages, 1, hkv, d, generator=g).to(dtype).cuda()
-        idx = torch.randperm(num_pages, generator=g)[:tq].to(torch.int32).cuda()
-        fn = lambda: ops.gqa_paged_prefill(q, kc, vc, ptr, ptr, idx, d ** -0.5, out=out, lse=lse)  # noqa: E731
-        byts = (2 * q.numel() + 2 * kc.numel()) * 2
+        idx = torch.randperm(num_pages, generator=g)[:tk].to(torch.int32).cuda()
+        call = lambda: ops.gqa_paged_prefill(q, kc, vc, qo, kv, idx, d ** -0.5, out=out, lse=lse)  # noqa: E731
+        byts = (q.numel() + q.numel() * vis // q_len + 2 * kc.numel()) * 2  # out, the rows of Q that see a key, the caches
     else:
-        k = torch.randn(tq, hkv, d, generator=g).to(dtype).cuda()
-        v = torch.randn(tq, hkv, d, generator=g).to(dtype).cuda()
-        fn = lambda: ops.gqa_ragged_prefill(q, k, v, ptr, ptr, d ** -0.5, out=out, lse=lse)  # noqa: E731
-        byts = (2 * q.numel() + 2 * k.numel()) * 2
-    return fn, flops, byts
+        k = torch.randn(tk, hkv, d, generator=g).to(dtype).cuda()
+        v = torch.randn(tk, hkv, d, generator=g).to(dtype).cuda()
+        call = lambda: ops.gqa_ragged_prefill(q, k, v, qo, kv, d ** -0.5, out=out, lse=lse)  # noqa: E731
+        byts = (q.numel() + q.numel() * vis // q_len + 2 * k.numel()) * 2
+    if light:
+        return call, flops, byts
+
+    def tile_kernels_only():
+        old = ops.set_small_problem_limit(0)
+        try:
+            return call()
+        finally:
+            ops.set_small_problem_limit(old)
+
+    return tile_kernels_only, flops, byts
 
 
 def mla_paged_decode_case(batch=64, heads=16, lo=512, hi=8192, dtype=torch.bfloat16, impl="auto"):
@@ -280,6 +296,13 @@ CONFIGS = {
     "gqa_paged_decode_ps16_b64_kv512_8192": lambda: paged_decode_case(16),
     "gqa_paged_decode_ps32_b64_kv512_8192": lambda: paged_decode_case(32),
     "gqa_paged_decode_ps64_b64_kv512_8192": lambda: paged_decode_case(64),
+    # fixed cost: a handful of short requests, and a prefill chunk of 16384 query rows over a page table of 64 tokens
+    "gqa_paged_decode_ps1_b1_kv8": lambda: paged_decode_case(1, batch=1, lo=8, hi=8),
+    "gqa_paged_decode_ps1_b16_kv32_128": lambda: paged_decode_case(1, batch=16, lo=32, hi=128),
+    "mla_paged_decode_h16_ps1_b16_kv16_64": lambda: mla_paged_decode_case(batch=16, lo=16, hi=64),
+    "gqa_paged_prefill_causal_h32_kv4_d128_ps1_b32_q512_kv2": lambda: gqa_dynamic_prefill_case(True, batch=32, q_len=512, hkv=4, kv_len=2),
+    "gqa_paged_prefill_causal_h32_kv4_d128_ps1_b32_q512_kv2_tile_kernels": lambda: gqa_dynamic_prefill_case(
+        True, batch=32, q_len=512, hkv=4, kv_len=2, light=False),
 }
 
 

@@ -39,7 +39,7 @@ FALLBACK_HBM_GBS = 6650.0
 # DRAM bytes the kernel moved per algorithmic byte in an ncu capture of this kernel on a batch of 32
 # requests of the same length distribution (every KV tile is read once, so traffic scales with the
 # live tokens). A constant from that capture, not a measurement of this run.
-TRAFFIC_PER_ALGORITHMIC_BYTE = 1.0046
+TRAFFIC_PER_ALGORITHMIC_BYTE = 1.0066
 CPU_SAMPLE_REQUESTS = 8
 
 

@@ -2,13 +2,19 @@
 //
 //   O = softmax(scale * Q K^T [+ end-aligned causal mask]) V      q (HQ, SQ, D); k, v (HKV, SKV, D)
 //
-// A CTA owns (query head, tile of 128 query rows) and walks the KV tiles of 128 tokens it may see.
+// An item is (query head, tile of 128 query rows) with the KV tiles of 128 tokens it may see. CTAs are persistent,
+// one per SM: a CTA starts on the item of its block index and takes further ones from a counter in the workspace
+// header (fetched one item ahead by a spare warp and handed to the others through a two-slot ring), and every
+// barrier phase runs on across items. The producers and the MMA warp are therefore already on the next item - its
+// place in the batch, its Q, its first K / V tiles, its first score product - while the softmax warps finish the
+// current one; a batch of short prompts, where an item is one or two KV tiles, no longer pays a CTA launch, the
+// set-up and the load latency in sequence per item.
 // Rows of every MMA are the query rows (UMMA M = 128):
 //   S = Q K^T    A = Q tile (shared memory, K-major, resident), B = K tile (shared memory, K-major),
 //                D = S in tensor memory (128 columns, two buffers)
 //   O += P V     A = P (tensor memory, 16-bit pairs written by the softmax warps, two buffers),
 //                B = V tile (shared memory, MN-major), D = O in tensor memory (D columns)
-// Warp roles: 0 = TMA producer for Q and K, 6 = TMA producer for V, 1 = MMA issuer and TMEM owner,
+// Warp roles: 0 = TMA producer for Q and K, 6 = TMA producer for V, 1 = MMA issuer and TMEM owner, 7 = item numbers,
 // 2..5 and 8..11 = softmax / epilogue: two threads per query row (= TMEM lane), one for scores 0..63 of a tile
 // and one for scores 64..127, on warps of the same lane quarter; they exchange their row maxima through shared
 // memory once per tile. With one thread per row the kernel ran at the pace of its four softmax warps, one per
@@ -95,27 +101,127 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   uint64_t* p_full = s_empty + 2;  // [2] P stored to TMEM (and O rescaled if needed)
   uint64_t* p_empty = p_full + 2;  // [2] the PV MMAs that read the P buffer have completed
   uint64_t* o_done = p_empty + 2;
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(o_done + 1);
+  uint64_t* q_empty = o_done + 1;  // the score MMAs of an item have read Q: the next item's Q may be loaded
+  uint64_t* o_free = q_empty + 1;  // the epilogue has taken O out of tensor memory
+  uint64_t* t_full = o_free + 1;   // [2] an item number is in the ring
+  uint64_t* t_empty = t_full + 2;  // [2] every warp has read it
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(t_empty + 2);
+  volatile int* item_ring = reinterpret_cast<volatile int*>(tmem_holder + 1);  // [2]
   float* mx_exch = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + 1024);  // [2 tiles][2 halves][128 rows]
   float* l_exch = mx_exch + 2 * 2 * kBM;                                                  // [2 halves][128 rows]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n_warps = static_cast<int>(blockDim.x >> 5);
+  constexpr int kTicketWarp = 7;
+  // The ranges of the first 32 requests (lane = request) are fetched before anything else: the trip to memory runs
+  // beside the set-up below, and every item's search starts from these registers - for batches of up to 32
+  // requests an item's place costs no memory access at all.
+  int pre_lo = 0, pre_hi = 0, pre_klo = 0, pre_khi = 0;
+  if constexpr (RAGGED) {
+    if (lane < p.batch) {
+      pre_lo = __ldg(p.qo_indptr + lane);
+      pre_hi = __ldg(p.qo_indptr + lane + 1);
+      pre_klo = __ldg(p.kv_indptr + lane);
+      pre_khi = __ldg(p.kv_indptr + lane + 1);
+    }
+  }
+  // ---- once per CTA: barriers, tensor memory. A CTA stays on its SM and takes (head, query tile) items one after
+  // the other, so this set-up, the launch of a CTA and above all the latency at the start of an item (its place in
+  // the batch, the first Q / K / V loads) are not paid in sequence per item: the producers and the MMA warp are
+  // already on the next item while the softmax warps finish the current one.
+  if (tid == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&k_full[s], MODE == 2 ? 128 : 1);
+      mbar_init(&k_empty[s], 1);
+      mbar_init(&v_full[s], MODE == 2 ? 128 : 1);
+      mbar_init(&v_empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&s_full[s], 1);
+      mbar_init(&s_empty[s], 8);
+      mbar_init(&p_full[s], 8);
+      mbar_init(&p_empty[s], 1);
+      mbar_init(&t_full[s], 1);
+      mbar_init(&t_empty[s], n_warps - 1);
+    }
+    mbar_init(q_full, 1);
+    mbar_init(o_done, 1);
+    mbar_init(q_empty, p.q_norm ? 9 : 1);  // with RMS-normalised queries the softmax warps read the Q tile too
+    mbar_init(o_free, 8);
+    mbar_fence_init();
+    tma_prefetch_desc(&tm_q);
+    tma_prefetch_desc(&tm_k);
+    tma_prefetch_desc(&tm_v);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_holder, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_holder);
+  // The static launch is a dependent launch: the grid may have been scheduled while the preceding kernel of
+  // the stream drains. Up to here only shared and tensor memory were set up; global memory is touched after
+  // the wait.
+  pdl_launch_dependents();
+  pdl_wait();
+
+  const int n_items = p.hq * p.q_tiles;
+  int* ticket = p.status + 8;    // items beyond the first of every CTA are dealt by this counter
+  int* finished = p.status + 9;  // CTAs that are through; the last one clears both words for the next launch
+  if (warp == kTicketWarp) {
+    // ================================================================ item numbers for the other warps
+    // The first item of a CTA is its block index, which every warp knows; the others come from a counter, fetched
+    // one item ahead and handed round through a two-slot ring. Items are numbered so that late query tiles, which
+    // see the most keys under the causal mask, come first.
+    if (lane == 0) {
+      for (int k = 0;; ++k) {
+        const int s = k & 1;
+        mbar_wait(&t_empty[s], ((k >> 1) & 1) ^ 1, p.status, kFaultEmptyBarrier);
+        // with no more items than CTAs every item is somebody's first: no counter, nothing to clear at the end
+        const int item = n_items <= static_cast<int>(gridDim.x) ? n_items : static_cast<int>(gridDim.x) + atomicAdd(ticket, 1);
+        item_ring[s] = item;
+        mbar_arrive(&t_full[s]);
+        if (item >= n_items) break;
+      }
+    }
+    __syncwarp();
+  }
+  int n_taken = 0;  // item numbers this warp has had
+  int it = 0;       // items with keys this CTA has run, jt: their KV tiles (every role counts alike)
+  int jt = 0;
+  int st_a = 0, ph_a = 0, st_b = 0, ph_b = 0;  // ring positions of this warp's role
+  while (warp != kTicketWarp) {
+    int item = static_cast<int>(blockIdx.x);
+    if (n_taken > 0) {  // the ring's entry number n_taken - 1
+      const int s = (n_taken - 1) & 1;
+      mbar_wait(&t_full[s], ((n_taken - 1) >> 1) & 1, p.status, kFaultFullBarrier);
+      item = item_ring[s];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&t_empty[s]);
+    }
+    ++n_taken;
+    if (item >= n_items) break;
   // heads of one query tile are neighbours (they share K/V in L2)
-  const int h = blockIdx.x % p.hq;
+  const int h = item % p.hq;
   const int hk = h / (p.hq / p.hkv);
   int q0, sq, skv, q_base = 0, kv_base = 0;
   if constexpr (RAGGED) {
-    // late query tiles, which see the most keys under the causal mask, are scheduled first
     // Every warp searches the query offsets 32 requests at a time (lane = request, tile counts scanned with shuffles):
-    // a CTA's place costs a few hundred clocks whatever the batch. (A thread walking the offsets one by one spent a
-    // microsecond per 50 requests, in every one of the thousands of small CTAs a batch of short prompts makes.)
-    int t = static_cast<int>(gridDim.x / p.hq) - 1 - static_cast<int>(blockIdx.x / p.hq), r = 0;
+    // an item's place costs a few hundred clocks whatever the batch.
+    int t = p.q_tiles - 1 - item / p.hq, r = 0;
     bool found = false;
     for (int r0 = 0; r0 < p.batch && !found; r0 += 32) {
       const int rr = r0 + lane;
-      const int lo = rr < p.batch ? __ldg(p.qo_indptr + rr) : 0, hi = rr < p.batch ? __ldg(p.qo_indptr + rr + 1) : 0;
-      // the key range of the lane's request travels with the query range: one trip to memory, not two in a row
-      const int klo = rr < p.batch ? __ldg(p.kv_indptr + rr) : 0, khi = rr < p.batch ? __ldg(p.kv_indptr + rr + 1) : 0;
+      int lo = pre_lo, hi = pre_hi, klo = pre_klo, khi = pre_khi;
+      if (r0 > 0) {
+        lo = rr < p.batch ? __ldg(p.qo_indptr + rr) : 0;
+        hi = rr < p.batch ? __ldg(p.qo_indptr + rr + 1) : 0;
+        // the key range of the lane's request travels with the query range: one trip to memory, not two in a row
+        klo = rr < p.batch ? __ldg(p.kv_indptr + rr) : 0;
+        khi = rr < p.batch ? __ldg(p.kv_indptr + rr + 1) : 0;
+      }
       const int tiles = hi > lo ? ceil_div(hi - lo, kBM) : 0;
       int incl = tiles;
 #pragma unroll
@@ -137,7 +243,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         t -= all;
       }
     }
-    if (!found) return;  // the grid is an upper bound on the number of query tiles
+    (void)r;
+    if (!found) continue;  // the item count is an upper bound on the number of query tiles
     if constexpr (MODE == 2) {
       // the page table is caller data: a range that runs past its stated length is read as a shorter request
       if (p.n_idx > 0) {
@@ -147,8 +254,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     }
     q0 = t * kBM;
   } else {
-    // late query tiles, which see the most keys under the causal mask, come first
-    q0 = (p.q_tiles - 1 - blockIdx.x / p.hq) * kBM;
+    q0 = (p.q_tiles - 1 - item / p.hq) * kBM;
     sq = p.sq;
     skv = p.skv;
   }
@@ -159,56 +265,27 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     nt = last_key < 0 ? 0 : min(nt, last_key / kBN + 1);
   }
 
-  if (RAGGED && nt == 0) {
+  if (nt == 0) {
     // No key is visible to any row of this tile (an empty request, or query rows the end-aligned mask leaves
-    // blind): the rows are 0 and -inf, as the reference's preallocation leaves them, and nothing else is set up.
+    // blind): the rows are 0 and -inf, as the reference's preallocation leaves them; the warps share the rows.
     const int rows = min(kBM, sq - q0);
+    const int cw = warp < kTicketWarp ? warp : warp - 1;
     T* outp = reinterpret_cast<T*>(p.out);
-    for (int i = tid; i < rows * (D / 8); i += blockDim.x) {
+    for (int i = cw * 32 + lane; i < rows * (D / 8); i += (n_warps - 1) * 32) {
       const int rw = i / (D / 8), c = i - rw * (D / 8);
-      *reinterpret_cast<uint4*>(outp + (static_cast<size_t>(q_base + q0 + rw) * p.hq + h) * D + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+      const size_t orow = RAGGED ? static_cast<size_t>(q_base + q0 + rw) * p.hq + h : static_cast<size_t>(h) * sq + q0 + rw;
+      *reinterpret_cast<uint4*>(outp + orow * D + c * 8) = make_uint4(0u, 0u, 0u, 0u);
     }
     if (p.lse && !p.linear)
-      for (int i = tid; i < rows; i += blockDim.x) p.lse[static_cast<size_t>(q_base + q0 + i) * p.hq + h] = -INFINITY;
-    return;
+      for (int i = cw * 32 + lane; i < rows; i += (n_warps - 1) * 32)
+        p.lse[RAGGED ? static_cast<size_t>(q_base + q0 + i) * p.hq + h : static_cast<size_t>(h) * sq + q0 + i] = -INFINITY;
+    continue;
   }
-  if (tid == 0) {
-    for (int s = 0; s < kStages; ++s) {
-      mbar_init(&k_full[s], MODE == 2 ? 128 : 1);
-      mbar_init(&k_empty[s], 1);
-      mbar_init(&v_full[s], MODE == 2 ? 128 : 1);
-      mbar_init(&v_empty[s], 1);
-    }
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(&s_full[s], 1);
-      mbar_init(&s_empty[s], 8);
-      mbar_init(&p_full[s], 8);
-      mbar_init(&p_empty[s], 1);
-    }
-    mbar_init(q_full, 1);
-    mbar_init(o_done, 1);
-    mbar_fence_init();
-    tma_prefetch_desc(&tm_q);
-    tma_prefetch_desc(&tm_k);
-    tma_prefetch_desc(&tm_v);
-  }
-  if (warp == 1) {
-    tmem_alloc(tmem_holder, 512);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_holder);
-  // The static launch is a dependent launch: the grid may have been scheduled while the preceding kernel of
-  // the stream drains. Up to here only shared and tensor memory were set up (the index reads of the ragged
-  // modes above belong to launches without the attribute); global memory is touched after the wait.
-  pdl_launch_dependents();
-  pdl_wait();
 
   if (warp == 0) {
     // ================================================================ TMA producer: Q, then K tiles
-    if (lane == 0 && nt > 0) {
+    mbar_wait(q_empty, (it & 1) ^ 1, p.status, kFaultEmptyBarrier);  // the item before has no use for its Q any more
+    if (lane == 0) {
       mbar_arrive_expect_tx(q_full, C::kTileBytes);
 #pragma unroll
       for (int c = 0; c < C::kChunks; ++c) {
@@ -217,37 +294,35 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       }
     }
     __syncwarp();
-    int st = 0, ph = 0;
     for (int j = 0; MODE != 2 && j < nt; ++j) {
-      mbar_wait(&k_empty[st], ph ^ 1, p.status, kFaultEmptyBarrier);
+      mbar_wait(&k_empty[st_a], ph_a ^ 1, p.status, kFaultEmptyBarrier);
       if (elect_one()) {
-        mbar_arrive_expect_tx(&k_full[st], C::kTileBytes);
+        mbar_arrive_expect_tx(&k_full[st_a], C::kTileBytes);
 #pragma unroll
         for (int c = 0; c < C::kChunks; ++c) {
-          uint8_t* dst = k_smem + st * C::kTileBytes + c * C::kChunkBytes;
-          if constexpr (RAGGED) tma_load_3d(dst, &tm_k, &k_full[st], c * 64, hk, kv_base + j * kBN);
-          else tma_load_3d(dst, &tm_k, &k_full[st], c * 64, j * kBN, hk);
+          uint8_t* dst = k_smem + st_a * C::kTileBytes + c * C::kChunkBytes;
+          if constexpr (RAGGED) tma_load_3d(dst, &tm_k, &k_full[st_a], c * 64, hk, kv_base + j * kBN);
+          else tma_load_3d(dst, &tm_k, &k_full[st_a], c * 64, j * kBN, hk);
         }
       }
       __syncwarp();
-      if (++st == kStages) { st = 0; ph ^= 1; }
+      if (++st_a == kStages) { st_a = 0; ph_a ^= 1; }
     }
   } else if (warp == 6) {
     // ================================================================ TMA producer: V tiles
-    int st = 0, ph = 0;
     for (int j = 0; MODE != 2 && j < nt; ++j) {
-      mbar_wait(&v_empty[st], ph ^ 1, p.status, kFaultEmptyBarrier);
+      mbar_wait(&v_empty[st_a], ph_a ^ 1, p.status, kFaultEmptyBarrier);
       if (elect_one()) {
-        mbar_arrive_expect_tx(&v_full[st], C::kTileBytes);
+        mbar_arrive_expect_tx(&v_full[st_a], C::kTileBytes);
 #pragma unroll
         for (int c = 0; c < C::kChunks; ++c) {
-          uint8_t* dst = v_smem + st * C::kTileBytes + c * C::kChunkBytes;
-          if constexpr (RAGGED) tma_load_3d(dst, &tm_v, &v_full[st], c * 64, hk, kv_base + j * kBN);
-          else tma_load_3d(dst, &tm_v, &v_full[st], c * 64, j * kBN, hk);
+          uint8_t* dst = v_smem + st_a * C::kTileBytes + c * C::kChunkBytes;
+          if constexpr (RAGGED) tma_load_3d(dst, &tm_v, &v_full[st_a], c * 64, hk, kv_base + j * kBN);
+          else tma_load_3d(dst, &tm_v, &v_full[st_a], c * 64, j * kBN, hk);
         }
       }
       __syncwarp();
-      if (++st == kStages) { st = 0; ph ^= 1; }
+      if (++st_a == kStages) { st_a = 0; ph_a ^= 1; }
     }
   } else if (warp >= 12) {
     // ================================================================ paged: K / V row gather
@@ -269,32 +344,31 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         }
       };
       int pg[kRounds];
-      if (nt > 0) load_pages(0, pg);
-      int st = 0, ph = 0;
+      load_pages(0, pg);
       for (int j = 0; j < nt; ++j) {
         long long src[kRounds];
 #pragma unroll
         for (int r = 0; r < kRounds; ++r)
           src[r] = (static_cast<long long>(min(max(pg[r], 0), p.num_pages - 1)) * p.hkv + hk) * D + c * 8;
         if (j + 1 < nt) load_pages(j + 1, pg);  // one tile ahead: the index latency stays off the critical path
-        const uint32_t kdst = smem_u32(k_smem + st * C::kTileBytes), vdst = smem_u32(v_smem + st * C::kTileBytes);
-        mbar_wait(&k_empty[st], ph ^ 1, p.status, kFaultEmptyBarrier);
+        const uint32_t kdst = smem_u32(k_smem + st_a * C::kTileBytes), vdst = smem_u32(v_smem + st_a * C::kTileBytes);
+        mbar_wait(&k_empty[st_a], ph_a ^ 1, p.status, kFaultEmptyBarrier);
 #pragma unroll
         for (int r = 0; r < kRounds; ++r) {
           const int row = r * kRowsPerRound + r_in;
           const uint32_t o = (c >> 3) * C::kChunkBytes + row * 128 + (((c & 7) ^ (row & 7)) << 4);
           asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(kdst + o), "l"(kc + src[r]) : "memory");
         }
-        asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&k_full[st])) : "memory");
-        mbar_wait(&v_empty[st], ph ^ 1, p.status, kFaultEmptyBarrier);
+        asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&k_full[st_a])) : "memory");
+        mbar_wait(&v_empty[st_a], ph_a ^ 1, p.status, kFaultEmptyBarrier);
 #pragma unroll
         for (int r = 0; r < kRounds; ++r) {
           const int row = r * kRowsPerRound + r_in;
           const uint32_t o = (c >> 3) * C::kChunkBytes + row * 128 + (((c & 7) ^ (row & 7)) << 4);
           asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(vdst + o), "l"(vc + src[r]) : "memory");
         }
-        asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&v_full[st])) : "memory");
-        if (++st == kStages) { st = 0; ph ^= 1; }
+        asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&v_full[st_a])) : "memory");
+        if (++st_a == kStages) { st_a = 0; ph_a ^= 1; }
       }
     }
   } else if (warp == 1) {
@@ -303,11 +377,11 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     constexpr uint32_t idesc_s = umma_idesc(kBf16, /*b_mn_major=*/false, kBM, kBN);
     constexpr uint32_t idesc_pv = umma_idesc(kBf16, /*b_mn_major=*/true, kBM, D);
     const uint32_t q_addr = smem_u32(q_smem), k_addr = smem_u32(k_smem), v_addr = smem_u32(v_smem);
-    int kst = 0, kph = 0, vst = 0, vph = 0;
+    int& kst = st_a; int& kph = ph_a; int& vst = st_b; int& vph = ph_b;
     auto issue_s = [&](int j) {
-      const int sb = j & 1;
+      const int jj = jt + j, sb = jj & 1;
       mbar_wait(&k_full[kst], kph, p.status, kFaultFullBarrier);
-      mbar_wait(&s_empty[sb], ((j >> 1) & 1) ^ 1, p.status, kFaultTmemBarrier);
+      mbar_wait(&s_empty[sb], ((jj >> 1) & 1) ^ 1, p.status, kFaultTmemBarrier);
       tc_fence_after();
       if (elect_one()) {
         const uint32_t d = tmem_base + kColS + sb * kBN;
@@ -322,19 +396,20 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         }
         umma_commit(&k_empty[kst]);
         umma_commit(&s_full[sb]);
+        if (j == nt - 1) umma_commit(q_empty);  // the item's last use of Q
       }
       __syncwarp();
       if (++kst == kStages) { kst = 0; kph ^= 1; }
     };
-    if (nt > 0) {
-      mbar_wait(q_full, 0, p.status, kFaultFullBarrier);
-      issue_s(0);
-    }
+    mbar_wait(q_full, it & 1, p.status, kFaultFullBarrier);
+    issue_s(0);
     for (int j = 0; j < nt; ++j) {
       if (j + 1 < nt) issue_s(j + 1);
-      const int pb = j & 1;
+      const int jj = jt + j, pb = jj & 1;
       mbar_wait(&v_full[vst], vph, p.status, kFaultFullBarrier);
-      mbar_wait(&p_full[pb], (j >> 1) & 1, p.status, kFaultTmemBarrier);
+      mbar_wait(&p_full[pb], (jj >> 1) & 1, p.status, kFaultTmemBarrier);
+      // the first value product of an item overwrites O: the epilogue of the item before must have read it
+      if (j == 0) mbar_wait(o_free, (it & 1) ^ 1, p.status, kFaultTmemBarrier);
       tc_fence_after();
       if (elect_one()) {
         const uint32_t va = v_addr + vst * C::kTileBytes;
@@ -365,8 +440,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     // times, for RMS-normalised queries, rsqrt(mean(q^2) + eps) of this thread's row, taken from the
     // resident Q tile (K arrives normalised)
     float scale_row = p.linear ? p.scale : p.scale_log2;
-    if (p.q_norm && nt > 0) {
-      mbar_wait(q_full, 0, p.status, kFaultFullBarrier);
+    if (p.q_norm) {
+      mbar_wait(q_full, it & 1, p.status, kFaultFullBarrier);
       float ss = 0.f;
 #pragma unroll
       for (int c = 0; c < D / 8; ++c) {
@@ -380,10 +455,12 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         }
       }
       scale_row = qrow < sq ? scale_row * rsqrtf(ss * (1.f / D) + p.norm_eps) : 0.f;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(q_empty);
     }
     for (int j = 0; j < nt; ++j) {
-      const int sb = j & 1, pb = j & 1;
-      mbar_wait(&s_full[sb], (j >> 1) & 1, p.status, kFaultMmaBarrier);
+      const int jj = jt + j, sb = jj & 1, pb = jj & 1;
+      mbar_wait(&s_full[sb], (jj >> 1) & 1, p.status, kFaultMmaBarrier);
       tc_fence_after();
       uint32_t r[2][32];
 #pragma unroll
@@ -395,7 +472,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       const int k0 = j * kBN + half * 64;  // first key of this thread's scores
       if (p.linear) {
         // no softmax: P = scale * S rounded to the storage type; keys past the end are zero rows of K
-        mbar_wait(&p_empty[pb], ((j >> 1) & 1) ^ 1, p.status, kFaultMmaBarrier);
+        mbar_wait(&p_empty[pb], ((jj >> 1) & 1) ^ 1, p.status, kFaultMmaBarrier);
         tc_fence_after();
         uint32_t pk[32];
 #pragma unroll
@@ -449,11 +526,11 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         rescale = true;
       }
       // the P buffer is free once the PV MMAs of tile j - 2 have completed
-      mbar_wait(&p_empty[pb], ((j >> 1) & 1) ^ 1, p.status, kFaultMmaBarrier);
+      mbar_wait(&p_empty[pb], ((jj >> 1) & 1) ^ 1, p.status, kFaultMmaBarrier);
       if (__any_sync(0xffffffffu, rescale)) {  // rare: the running maximum grew by more than 2^8
         // O may only be touched when no PV MMA is in flight: tile j - 1 is the last one issued. The two threads
         // of a row came to the same decision (same maximum) and take half of the row's columns each.
-        mbar_wait(&p_empty[pb ^ 1], ((j - 1) >> 1) & 1, p.status, kFaultMmaBarrier);
+        mbar_wait(&p_empty[pb ^ 1], ((jj - 1) >> 1) & 1, p.status, kFaultMmaBarrier);
         tc_fence_after();
 #pragma unroll 1
         for (int c0 = half * (D / 2); c0 < (half + 1) * (D / 2); c0 += 32) {
@@ -490,10 +567,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     l_exch[half * kBM + row] = l_run;
     named_bar_sync(pair_bar, 64);
     l_run += l_exch[(half ^ 1) * kBM + row];
-    if (nt > 0) {
-      mbar_wait(o_done, 0, p.status, kFaultMmaBarrier);
-      tc_fence_after();
-    }
+    mbar_wait(o_done, it & 1, p.status, kFaultMmaBarrier);
+    tc_fence_after();
     const bool live = qrow < sq;
     const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
     const size_t orow = RAGGED ? static_cast<size_t>(q_base + qrow) * p.hq + h : static_cast<size_t>(h) * sq + qrow;
@@ -501,12 +576,12 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 #pragma unroll 1
     for (int c0 = half * (D / 2); c0 < (half + 1) * (D / 2); c0 += 32) {
       uint32_t o[32];
-      if (nt > 0) {
-        tmem_ld_32x32(tmem_base + lane_field + kColO + c0, o);
-        tmem_ld_wait();
-      } else {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[i] = 0u;
+      tmem_ld_32x32(tmem_base + lane_field + kColO + c0, o);
+      tmem_ld_wait();
+      if (c0 + 32 >= (half + 1) * (D / 2)) {  // O is out of tensor memory: the next item's value product may start
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(o_free);
       }
       if (live) {
         const float* v = reinterpret_cast<const float*>(o);
@@ -523,12 +598,20 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     }
     if (half == 0 && live && p.lse && !p.linear) p.lse[orow] = l_run > 0.f ? m_ref + fast_log2(l_run) : -INFINITY;
   }
+    jt += nt;
+    ++it;
+  }  // items
 
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
+  }
+  if (tid == 0 && n_items > static_cast<int>(gridDim.x) && atomicAdd(finished, 1) == static_cast<int>(gridDim.x) - 1) {
+    // every CTA has fetched its last item number: the counters are clear for the next launch
+    atomicExch(ticket, 0);
+    atomicExch(finished, 0);
   }
 }
 
@@ -627,7 +710,8 @@ int launch_prefill(const cb200_attn_prefill_args* a, cudaStream_t stream) {
   }
   auto kern = attn_prefill_kernel<T, D, 0>;
   CB200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<D>::kSmemBytes));
-  const unsigned grid = static_cast<unsigned>(p.hq) * p.q_tiles;
+  // one CTA per SM at most; the CTAs deal the (head, query tile) items among themselves
+  const unsigned grid = static_cast<unsigned>(std::min<long long>(static_cast<long long>(p.hq) * p.q_tiles, sm_count()));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid, 1, 1);
   cfg.blockDim = dim3(kThreads, 1, 1);
@@ -691,8 +775,10 @@ int launch_prefill_ragged(const cb200_attn_prefill_ragged_args* a, cudaStream_t 
         !encode_tensor_map(&tm_v, dt, 3, const_cast<void*>(a->v), dk, sk, box, sw))
       return CB200_ERR_CUDA;
   }
-  // every request has at most ceil(q_len / 128) <= q_len / 128 + 1 query tiles
-  const unsigned grid = static_cast<unsigned>(p.hq) * static_cast<unsigned>(ceil_div(a->total_q, kBM) + a->batch);
+  // every request has at most ceil(q_len / 128) <= q_len / 128 + 1 query tiles: an upper bound on the items, which
+  // the CTAs (one per SM at most) deal among themselves
+  p.q_tiles = ceil_div(a->total_q, kBM) + a->batch;
+  const unsigned grid = static_cast<unsigned>(std::min<long long>(static_cast<long long>(p.hq) * p.q_tiles, sm_count()));
   if (a->kv_indices) {
     auto kern = attn_prefill_kernel<T, D, 2>;
     CB200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<D>::kSmemBytes));

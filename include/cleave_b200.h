@@ -247,7 +247,9 @@ int cb200_mla_decode(const cb200_mla_decode_args* a, void* stream);
  * (tests/graph/handwritten/expected_kernels/mha_bhsd.py); `causal` applies the end-aligned mask of
  * python/cleave/dynamic/reference.py:129-133 (query row r sees keys <= r + kv_len - q_len), the
  * mask of the paged and ragged prefill operators. head_dim 64 or 128. The workspace holds the status
- * word (cb200_workspace_status) and, with qk_norm, the normalised copy of K.
+ * word (cb200_workspace_status), the counter from which the kernel's persistent CTAs take their (head, query tile)
+ * items (in the 256-byte header; it clears itself at the end of a launch, so the zero-fill before first use is
+ * all the caller owes) and, with qk_norm, the normalised copy of K.
  * ---------------------------------------------------------------------------------------- */
 typedef enum { CB200_SCORE_SOFTMAX = 0, CB200_SCORE_LINEAR = 1 } cb200_score_mode;
 

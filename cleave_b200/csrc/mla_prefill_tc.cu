@@ -90,6 +90,31 @@ mla_prefill_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_const
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int dh = blockIdx.x & 1;  // which half of the output columns
+  // The ranges of the first 32 requests (lane = request) are fetched before anything else, so that the trip to
+  // memory runs beside the barrier set-up below; the search starts from these registers.
+  int pre_lo = 0, pre_hi = 0, pre_klo = 0, pre_khi = 0;
+  if (lane < p.batch) {
+    pre_lo = __ldg(p.qo_indptr + lane);
+    pre_hi = __ldg(p.qo_indptr + lane + 1);
+    pre_klo = __ldg(p.kv_indptr + lane);
+    pre_khi = __ldg(p.kv_indptr + lane + 1);
+  }
+  if (tid == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&k_full[s], 129);  // 128 gather threads + the TMA thread's expect-tx arrival
+      mbar_init(&k_empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&s_full[s], 1);
+      mbar_init(&p_full[s], 4);
+      mbar_init(&pv_done[s], 1);
+    }
+    mbar_init(o_done, 1);
+    mbar_fence_init();
+    tma_prefetch_desc(&tm_qn);
+    tma_prefetch_desc(&tm_qp);
+  }
+
   // ---- which (request, query block) this CTA works on: late blocks, which see the most keys, come first
   // (every warp searches the query offsets 32 requests at a time: lane = request, block counts scanned with shuffles)
   int t = static_cast<int>(gridDim.x >> 1) - 1 - static_cast<int>(blockIdx.x >> 1), r = 0, lo = 0;
@@ -97,8 +122,13 @@ mla_prefill_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_const
   bool found = false;
   for (int r0 = 0; r0 < p.batch && !found; r0 += 32) {
     const int rr = r0 + lane;
-    const int lo_r = rr < p.batch ? __ldg(p.qo_indptr + rr) : 0, hi_r = rr < p.batch ? __ldg(p.qo_indptr + rr + 1) : 0;
-    const int klo_r = rr < p.batch ? __ldg(p.kv_indptr + rr) : 0, khi_r = rr < p.batch ? __ldg(p.kv_indptr + rr + 1) : 0;
+    int lo_r = pre_lo, hi_r = pre_hi, klo_r = pre_klo, khi_r = pre_khi;
+    if (r0 > 0) {
+      lo_r = rr < p.batch ? __ldg(p.qo_indptr + rr) : 0;
+      hi_r = rr < p.batch ? __ldg(p.qo_indptr + rr + 1) : 0;
+      klo_r = rr < p.batch ? __ldg(p.kv_indptr + rr) : 0;
+      khi_r = rr < p.batch ? __ldg(p.kv_indptr + rr + 1) : 0;
+    }
     const int blocks = hi_r > lo_r ? ceil_div(hi_r - lo_r, p.qb) : 0;
     int incl = blocks;
 #pragma unroll
@@ -144,21 +174,6 @@ mla_prefill_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_const
     if (dh == 0 && p.lse)
       for (int i = tid; i < rows; i += blockDim.x) p.lse[row0 + i] = -INFINITY;
     return;
-  }
-  if (tid == 0) {
-    for (int s = 0; s < kStages; ++s) {
-      mbar_init(&k_full[s], 129);  // 128 gather threads + the TMA thread's expect-tx arrival
-      mbar_init(&k_empty[s], 1);
-    }
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(&s_full[s], 1);
-      mbar_init(&p_full[s], 4);
-      mbar_init(&pv_done[s], 1);
-    }
-    mbar_init(o_done, 1);
-    mbar_fence_init();
-    tma_prefetch_desc(&tm_qn);
-    tma_prefetch_desc(&tm_qp);
   }
   if (warp == 1) {
     tmem_alloc(tmem_holder, 512);

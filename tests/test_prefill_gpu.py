@@ -202,6 +202,46 @@ def test_ragged_long_requests():
     assert_lse_close(host(lse), want_lse)
 
 
+@pytest.mark.parametrize("paged", [False, True])
+def test_items_dealt_among_persistent_ctas(paged):
+    """45 requests (more than the 32 whose ranges a warp keeps in registers) of 0...400 rows on 32 heads: about two
+    thousand (head, query tile) items, some of them blind or surplus, for at most 148 CTAs that take them from the
+    counter in the workspace header. Three launches on the same workspace must agree bit for bit (the counter clears
+    itself) and with the oracle."""
+    rng = np.random.default_rng(2024)
+    q_lens = [int(x) for x in rng.integers(0, 401, 45)]
+    kv_lens = [int(max(0, ql + d)) for ql, d in zip(q_lens, rng.integers(-150, 300, 45))]
+    q_lens[7], kv_lens[7] = 130, 0      # rows without any key
+    q_lens[20], kv_lens[20] = 300, 40   # leading tiles blind under the end-aligned mask
+    hq, hkv, d, dt = 32, 4, 128, "bf16"
+    tq, tk = sum(q_lens), sum(kv_lens)
+    q = cases.round_to(rng.standard_normal((tq, hq, d), dtype=np.float32), dt)
+    qo = np.concatenate([[0], np.cumsum(q_lens)]).astype(np.int32)
+    kv = np.concatenate([[0], np.cumsum(kv_lens)]).astype(np.int32)
+    scale = d ** -0.5
+    if paged:
+        pool = tk + 11
+        kc = cases.round_to(rng.standard_normal((pool, 1, hkv, d), dtype=np.float32), dt)
+        vc = cases.round_to(rng.standard_normal((pool, 1, hkv, d), dtype=np.float32), dt)
+        idx = rng.permutation(pool)[:tk].astype(np.int32)
+        args = (dev(q, dt), dev(kc, dt), dev(vc, dt), torch.from_numpy(qo).cuda(), torch.from_numpy(kv).cuda(),
+                torch.from_numpy(idx).cuda(), scale)
+        call = _ops().gqa_paged_prefill
+        want, want_lse = orc.gqa_paged_prefill(q, kc, vc, qo, kv, idx, scale, dt)
+    else:
+        k = cases.round_to(rng.standard_normal((tk, hkv, d), dtype=np.float32), dt)
+        v = cases.round_to(rng.standard_normal((tk, hkv, d), dtype=np.float32), dt)
+        args = (dev(q, dt), dev(k, dt), dev(v, dt), torch.from_numpy(qo).cuda(), torch.from_numpy(kv).cuda(), scale)
+        call = _ops().gqa_ragged_prefill
+        want, want_lse = orc.gqa_ragged_prefill(q, k, v, qo, kv, scale, dt)
+    runs = [tuple(host(x) for x in call(*args)) for _ in range(3)]
+    _check_ws()
+    assert_close(runs[0][0], want)
+    assert_lse_close(runs[0][1], want_lse)
+    for out, lse in runs[1:]:
+        assert np.array_equal(out, runs[0][0]) and np.array_equal(lse, runs[0][1])
+
+
 def test_repeat_launches_are_bit_identical():
     inp = cases.attention_inputs(9, 8, 2, 300, 517, 128, "f16")
     q, k, v = (dev(inp[n], "f16") for n in ("q", "k", "v"))

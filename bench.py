@@ -237,6 +237,32 @@ def nshard_gemm_rows(dist, rank, world, torch):
                      "us": round(us, 2), "TFLOP/s": round(2 * m * n * k / us / 1e6, 1), "scaling": "strong",
                      "allgather": gather})
     rows[1]["allgather_us"] = round(rows[1]["us"] - rows[0]["us"], 2)
+    # the same with the all-gather fused into the product's kernel: finished tiles go into every rank's copy of Y
+    # (symmetric memory) through NVLink while the next tile is computed; one barrier, no NCCL collective
+    try:
+        y, handle = sharding.symmetric_result(m, n, torch.float16, "cuda")
+        fused = lambda xx, ww, **kw: ops.rmsnorm_matmul(xx, ww, eps=1e-6, **kw)  # noqa: E731
+        fn = lambda: sharding.gemm_n_sharded_fused(fused, x, (w,), n, y, handle)  # noqa: E731
+        for _ in range(3):
+            fn()
+        dist.barrier()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            fn()
+        b.record()
+        dist.barrier()
+        torch.cuda.synchronize()
+        t = torch.tensor([a.elapsed_time(b) / reps], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        us = float(t.item()) * 1e3
+        rows.append({"config": f"rmsnorm_matmul_{m}x{n}x{k}_n_sharded_over_{world}_allgather_fused", "us": round(us, 2),
+                     "TFLOP/s": round(2 * m * n * k / us / 1e6, 1), "scaling": "strong", "allgather": "fused",
+                     "allgather_us": round(us - rows[0]["us"], 2),
+                     "nvlink_bytes_out_per_rank": int(m * (hi - lo) * 2 * (world - 1))})
+    except Exception as exc:  # symmetric memory is a torch feature of recent versions
+        rows.append({"config": "n_sharded_allgather_fused", "error": f"{type(exc).__name__}: {exc}"})
     return rows
 
 

@@ -44,6 +44,7 @@ class GemmArgs(C.Structure):
         ("m", C.c_int32), ("n", C.c_int32), ("k", C.c_int32), ("op", C.c_int32), ("dtype", C.c_int32),
         ("split_k", C.c_int32), ("max_ctas", C.c_int32), ("eps", C.c_float), ("addend", C.c_void_p), ("dependent_launch", C.c_int32),
         ("x2", C.c_void_p), ("w2", C.c_void_p), ("k2", C.c_int32), ("ldx", C.c_int32),
+        ("ldy", C.c_int32), ("n_peers", C.c_int32), ("y_peers", C.c_void_p * 7),
     ]
 
 

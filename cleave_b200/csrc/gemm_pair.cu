@@ -38,7 +38,8 @@ constexpr int kBHalfChunks = 2;                  // 128 columns of B per CTA
 constexpr int kStageBytes = kABytes + kBHalfChunks * kBChunkBytes;  // 32 KB
 constexpr int kStages = 6;
 constexpr int kUmmaN = 256;
-constexpr int kThreads = 192;
+constexpr int kThreads = 256;  // warps 0 TMA, 1 MMA, 2..5 epilogue, 6..7 push finished tiles to peer GPUs (idle otherwise)
+constexpr int kMaxPeers = 7;
 constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 1024;
 constexpr uint32_t kTmemCols = 512;  // two accumulators of 256 columns
 
@@ -47,6 +48,9 @@ struct Params {
   const float* row_scale;  // MODE 0: optional per-row factor applied in the epilogue (RMSNorm)
   int* status;
   int M, N, K, tiles_m, tiles_n, kblocks;
+  int ldy;                  // elements between consecutive rows of Y (N for a dense result)
+  int n_peers;              // other GPUs whose copy of Y receives this GPU's tiles (0: none)
+  void* y_peers[kMaxPeers]; // their Y, at this GPU's column offset, same row stride
 };
 
 // Tile order: bands of kGroupM tile rows, column-major inside a band, so the tiles that the resident
@@ -76,7 +80,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   uint64_t* empty_bar = full_bar + kStages;
   uint64_t* acc_full = empty_bar + kStages;   // [2]
   uint64_t* acc_empty = acc_full + 2;         // [2] used on the first CTA: both CTAs' epilogue warps arrive
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  uint64_t* stored = acc_empty + 2;           // [2] the epilogue warps have written a tile's rows to Y
+  uint64_t* pushed = stored + 2;              // [2] the push warps have sent them on
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(pushed + 2);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t crank = cluster_ctarank();
@@ -93,6 +99,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     for (int b = 0; b < 2; ++b) {
       mbar_init(&acc_full[b], 1);
       mbar_init(&acc_empty[b], 8);  // four epilogue warps of each CTA
+      mbar_init(&stored[b], 4);
+      mbar_init(&pushed[b], 2);
     }
     mbar_fence_init();
     tma_prefetch_desc(&tm_a);
@@ -178,13 +186,56 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       cluster_sync();
       cluster_sync();
     }
+  } else if (warp >= 6) {
+    // ================================================================ finished tiles go to the other GPUs
+    // N-sharded GEMM: every GPU computes a column slice of Y and all of them want the whole of Y. The epilogue
+    // writes this GPU's rows of a tile into its own copy (at the slice's column offset); these two warps then
+    // read them back (L2) and store them into every peer's copy through NVLink, whole 512-byte row segments per
+    // warp instruction, while the pair is already on its next tile: the all-gather rides under the MMAs.
+    if constexpr (KS > 1) {  // the two meetings of the split-K combine are meetings of every thread of the cluster
+      cluster_sync();
+      cluster_sync();
+    }
+    if (p.n_peers > 0) {
+      const int pw = warp - 6;
+      const T* ysrc = reinterpret_cast<const T*>(p.y);
+      constexpr int kRowsMine = kBM / KS;
+      const int r_lo = KS > 1 ? static_cast<int>(kpart) * kRowsMine : 0;
+      int ti = 0;
+      for (int t = pair_id; t < tiles; t += n_pairs, ++ti) {
+        int tm, tn;
+        tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+        const int slot = ti & 1;
+        mbar_wait(&stored[slot], (ti >> 1) & 1, p.status, kFaultTmemBarrier);
+        const int gc0 = tn * kTileN;
+        const int pieces = min(kTileN, p.N - gc0) / 8;  // 16-byte pieces of a row segment (at most 32)
+        const int grow0 = tm * 256 + static_cast<int>(rank) * kBM;
+        for (int r = r_lo + pw * 4; r < r_lo + kRowsMine; r += 8) {
+          uint4 v[4];
+          bool ok[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            ok[i] = lane < pieces && grow0 + r + i < p.M;
+            if (ok[i]) v[i] = __ldcg(reinterpret_cast<const uint4*>(ysrc + static_cast<size_t>(grow0 + r + i) * p.ldy + gc0) + lane);
+          }
+          for (int d = 0; d < p.n_peers; ++d) {
+            T* ydst = reinterpret_cast<T*>(p.y_peers[d]);
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              if (ok[i]) *(reinterpret_cast<uint4*>(ydst + static_cast<size_t>(grow0 + r + i) * p.ldy + gc0) + lane) = v[i];
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&pushed[slot]);
+      }
+    }
   } else {
     // ================================================================ epilogue (both CTAs, own rows)
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
     T* yout = reinterpret_cast<T*>(p.y);
-    int buf = 0, acc_phase = 0;
-    for (int t = pair_id; t < tiles; t += n_pairs) {
+    int buf = 0, acc_phase = 0, ti = 0;
+    for (int t = pair_id; t < tiles; t += n_pairs, ++ti) {
       int tm, tn;
       tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
       const int gr = tm * 256 + static_cast<int>(rank) * kBM + row;
@@ -247,7 +298,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
               uint2 pk;
               pk.x = pack2<T>(o[0], o[1]);
               pk.y = pack2<T>(o[2], o[3]);
-              *reinterpret_cast<uint2*>(yout + static_cast<size_t>(grow) * p.N + gcol) = pk;
+              *reinterpret_cast<uint2*>(yout + static_cast<size_t>(grow) * p.ldy + gcol) = pk;
             }
           }
         }
@@ -267,7 +318,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             o[j] = MODE == 2 ? v / (1.f + __expf(-v)) * __uint_as_float(r2[j]) : (MODE == 2 ? v : v * row_scale);
           }
           const int gc0 = tn * kTileN + c0;
-          T* dst = yout + static_cast<size_t>(gr) * p.N + gc0;
+          T* dst = yout + static_cast<size_t>(gr) * p.ldy + gc0;
 #pragma unroll
           for (int j = 0; j < 32; j += 8) {
             if (gc0 + j < p.N) {
@@ -284,6 +335,15 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_remote(&acc_empty[buf], lead);  // the first CTA's MMA thread waits for all eight warps
+      }
+      if (p.n_peers > 0) {
+        // this warp's rows of the tile are in Y: hand them to the push warps (not before they are through with
+        // the tile two back, whose slot this is)
+        const int slot = ti & 1;
+        mbar_wait(&pushed[slot], ((ti >> 1) & 1) ^ 1, p.status, kFaultTmemBarrier);
+        __threadfence_block();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&stored[slot]);
       }
       if (++buf == 2) { buf = 0; acc_phase ^= 1; }
     }
@@ -466,6 +526,9 @@ int launch_gemm_pair(const cb200_gemm_args* a, int* status, void* scratch, int k
   p.y = a->y;
   p.status = status;
   p.M = a->m; p.N = a->n; p.K = a->k;
+  p.ldy = a->ldy > 0 ? a->ldy : a->n;
+  p.n_peers = a->n_peers;
+  for (int d = 0; d < a->n_peers && d < pair::kMaxPeers; ++d) p.y_peers[d] = a->y_peers[d];
   p.tiles_m = ceil_div(a->m, 256);
   p.tiles_n = ceil_div(a->n, a->op == CB200_GEMM_SWIGLU ? 128 : 256);
   p.kblocks = ceil_div(a->k, pair::kBK);

@@ -699,6 +699,9 @@ int plan_gemm(const cb200_gemm_args* a, GemmSetup* s, bool need_maps) {
   if (a->k2 < 0 || (a->dependent_launch == 3 && !ext)) return CB200_ERR_BAD_ARG;
   if (a->ldx != 0 && (a->ldx < a->k || a->ldx % 8)) return CB200_ERR_BAD_ARG;
   if (a->ldx != 0 && a->op != CB200_GEMM_MATMUL) return CB200_ERR_UNSUPPORTED;
+  if (a->n_peers < 0 || a->n_peers > 7 || a->ldy < 0 || (a->ldy != 0 && (a->ldy < a->n || a->ldy % 8))) return CB200_ERR_BAD_ARG;
+  for (int d = 0; d < a->n_peers; ++d)
+    if (!a->y_peers[d] || (reinterpret_cast<uintptr_t>(a->y_peers[d]) & 15)) return CB200_ERR_BAD_ARG;
   const int sms = sm_count();
   if (sms <= 0) return CB200_ERR_CUDA;
   int grid_max = sms;
@@ -792,6 +795,11 @@ int plan_gemm(const cb200_gemm_args* a, GemmSetup* s, bool need_maps) {
     double t_single = best;
     if (t_single == 0.0) t_single = static_cast<double>((tiles + grid_max - 1) / grid_max) * p.kblocks * (s->nbw == 4 || a->op == CB200_GEMM_SWIGLU ? 0.56 : 0.33);
     s->pair = t_pair > 0.0 && t_pair < t_single && !a->addend && a->dependent_launch <= 1 && !ext;  // the pair kernel has no addend and no second operand pair; mode 1 is only a permission, the pair launch stays an ordinary one
+    // a result with its own row pitch, or one that is also sent to peer GPUs, is the pair kernel's business only
+    if (a->n_peers > 0 || (a->ldy != 0 && a->ldy != a->n)) {
+      if (!(t_pair > 0.0) || a->addend || ext || a->dependent_launch > 1) return CB200_ERR_UNSUPPORTED;
+      s->pair = true;
+    }
   }
   {
     // the estimate of the plan that runs: the model's own for automatic plans; for an explicit split factor the
@@ -811,8 +819,10 @@ int plan_gemm(const cb200_gemm_args* a, GemmSetup* s, bool need_maps) {
   }
   s->partials_off = kWsHeaderBytes;
   s->counters_off = align_up(s->partials_off + static_cast<size_t>(sms) * 2 * kGemmSlotBytesMax, 256);
-  if (s->pair && a->op == CB200_GEMM_RMSNORM && static_cast<size_t>(tiles) > kWsCounterSlots)
+  if (s->pair && a->op == CB200_GEMM_RMSNORM && static_cast<size_t>(tiles) > kWsCounterSlots) {
+    if (a->n_peers > 0 || (a->ldy != 0 && a->ldy != a->n)) return CB200_ERR_UNSUPPORTED;
     s->pair = false;  // the pre-pass scratch would start inside the counters
+  }
   s->prepass_off = align_up(s->counters_off + (static_cast<size_t>(tiles) > kWsCounterSlots ? static_cast<size_t>(tiles) : kWsCounterSlots) * 4, 256);
   s->ws_needed = s->prepass_off + (s->pair ? gemm_pair_prepass_bytes(a) : 0);
   if (!need_maps) return CB200_OK;

@@ -357,7 +357,7 @@ def check_static_scratch() -> None:
 
 
 def _gemm(op, x, w, w1=None, gamma=None, eps=0.0, split_k=0, out=None, max_ctas=0, addend=None, x2=None, w2=None,
-          dependent_launch=1):
+          dependent_launch=1, peers=None):
     if not x.is_cuda or not w.is_cuda:
         raise ValueError("x and w must be CUDA tensors (there is no CPU path)")
     ldx = 0
@@ -376,8 +376,18 @@ def _gemm(op, x, w, w1=None, gamma=None, eps=0.0, split_k=0, out=None, max_ctas=
         raise ValueError("gamma must hold K values of x's dtype")
     if out is None:
         out = torch.empty((m, n), dtype=x.dtype, device=x.device)
+    elif tuple(out.shape) != (m, n) or out.dtype != x.dtype or not out.is_cuda or out.stride(1) != 1:
+        raise ValueError("out must be an (M, N) CUDA tensor of x's dtype with unit column stride")
     a = _lib.GemmArgs()
     a.x, a.w, a.y = x.data_ptr(), w.data_ptr(), out.data_ptr()
+    if out.stride(0) != n:
+        a.ldy = out.stride(0)  # a column slice of a wider result (the N-sharded form)
+    if peers:
+        if len(peers) > 7:
+            raise ValueError("at most seven peer copies")
+        a.n_peers = len(peers)
+        for i, ptr in enumerate(peers):
+            a.y_peers[i] = int(ptr)
     a.w1 = None if w1 is None else w1.data_ptr()
     a.gamma = None if gamma is None else gamma.data_ptr()
     a.m, a.n, a.k, a.op, a.dtype = m, n, k, op, _dtype_code(x)
@@ -403,7 +413,7 @@ def _gemm(op, x, w, w1=None, gamma=None, eps=0.0, split_k=0, out=None, max_ctas=
     return out
 
 
-def matmul(x, w, *, split_k=0, out=None, max_ctas=0, addend=None, x2=None, w2=None, dependent_launch=1):
+def matmul(x, w, *, split_k=0, out=None, max_ctas=0, addend=None, x2=None, w2=None, dependent_launch=1, peers=None):
     """``Y = X @ W`` (reference operator: demo/matmul.py:11-13); ``split_k`` is the plan's K split.
     ``addend`` (M, N) is added in the epilogue; ``x2`` (M, K2) and ``w2`` (K2, N) extend the contraction:
     ``Y = X @ W + X2 @ W2`` in one accumulator (the low-rank term of LoRA). ``dependent_launch`` 1 (the
@@ -412,19 +422,24 @@ def matmul(x, w, *, split_k=0, out=None, max_ctas=0, addend=None, x2=None, w2=No
     (barriers, tensor memory, descriptor prefetch) overlaps: 8.5 -> 7.2 us on back-to-back 128 x 128 x 4096
     products. 0 gives an ordinary launch."""
     return _gemm(_lib.GEMM_MATMUL, x, w, split_k=split_k, out=out, max_ctas=max_ctas, addend=addend, x2=x2, w2=w2,
-                 dependent_launch=dependent_launch)
+                 dependent_launch=dependent_launch, peers=peers)
 
 
-def rmsnorm_matmul(x, w, *, eps=0.0, gamma=None, split_k=0, out=None, max_ctas=0, dependent_launch=1):
+def rmsnorm_matmul(x, w, *, eps=0.0, gamma=None, split_k=0, out=None, max_ctas=0, dependent_launch=1, peers=None):
     """``Y = (X * rsqrt(mean(X^2) + eps) [* gamma]) @ W`` (reference operator:
     demo/rmsnorm_matmul.py:11-13 with python/cleave/frontend/composites.py:48-53)."""
     return _gemm(_lib.GEMM_RMSNORM, x, w, gamma=gamma, eps=eps, split_k=split_k, out=out, max_ctas=max_ctas,
-                 dependent_launch=dependent_launch)
+                 dependent_launch=dependent_launch, peers=peers)
 
 
-def swiglu(x, w0, w1, *, split_k=0, out=None, max_ctas=0):
-    """``Y = silu(X @ W0) * (X @ W1)`` (reference operator: demo/swiglu.py:6-10)."""
-    return _gemm(_lib.GEMM_SWIGLU, x, w0, w1=w1, split_k=split_k, out=out, max_ctas=max_ctas)
+def swiglu(x, w0, w1, *, split_k=0, out=None, max_ctas=0, peers=None):
+    """``Y = silu(X @ W0) * (X @ W1)`` (reference operator: demo/swiglu.py:6-10).
+
+    For all three GEMM operators ``out`` may be a column slice of a wider (M, N_total) tensor, and ``peers`` a list
+    of device pointers to the same element of that tensor's copies on other GPUs (symmetric memory): the kernel
+    then also stores every finished tile into those copies while it computes the next one
+    (:func:`cleave_b200.sharding.gemm_n_sharded_fused`)."""
+    return _gemm(_lib.GEMM_SWIGLU, x, w0, w1=w1, split_k=split_k, out=out, max_ctas=max_ctas, peers=peers)
 
 
 def _mla(q_nope, q_pe, ckv, kpe, sm_scale, *, kv_indptr=None, kv_indices=None, out=None, lse=None, max_ctas=0,

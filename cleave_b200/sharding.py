@@ -115,3 +115,30 @@ def gemm_n_sharded(local_gemm, x, w_shards, n_total, *, gather=True, group=None)
     bufs = [torch.empty_like(pad) for _ in range(world)]
     dist.all_gather(bufs, pad, group=group)
     return torch.cat([b[:, :hi - lo] for b, (lo, hi) in zip(bufs, bounds)], dim=1)
+
+
+def symmetric_result(m: int, n_total: int, dtype, device, group=None):
+    """An (M, N_total) result tensor in symmetric memory - one copy per GPU of the group, every copy mapped into
+    every process - and its handle. Allocate once and reuse: the rendezvous is a collective."""
+    import torch.distributed as dist
+    import torch.distributed._symmetric_memory as symm_mem
+
+    y = symm_mem.empty((m, n_total), dtype=dtype, device=device)
+    return y, symm_mem.rendezvous(y, group=group if group is not None else dist.group.WORLD)
+
+
+def gemm_n_sharded_fused(local_gemm, x, w_shards, n_total, y, handle, group=None):
+    """``Y = op(X, W)`` with W sharded along N and the all-gather fused into the product: ``local_gemm(x, *w_shards,
+    out=..., peers=...)`` (one of ``ops.matmul`` / ``rmsnorm_matmul`` / ``swiglu``) writes this rank's columns
+    into its own copy of ``y`` (from :func:`symmetric_result`) and, tile by tile while it computes the next one, into
+    every other rank's copy through NVLink. The barrier at the end orders the ranks; after it ``y`` holds the whole
+    result on every rank. No NCCL collective and no reassembly copy."""
+    import torch.distributed as dist
+
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    lo, hi = n_shard(n_total, rank, world)
+    itemsize = y.element_size()
+    peers = [int(handle.buffer_ptrs[r]) + lo * itemsize for r in range(world) if r != rank]
+    local_gemm(x, *w_shards, out=y[:, lo:hi], peers=peers)
+    handle.barrier()
+    return y

@@ -42,7 +42,9 @@ extern "C" {
  *    the trailing field ldx (zero = the behaviour of version 2). */
 /* 4: cb200_attn_prefill_ragged_args gained the trailing field num_kv_indices (zero = the behaviour of
  *    version 3); the paged MLA decode clips request ranges to num_kv_indices; new cb200_set_small_problem_limit. */
-#define CB200_VERSION 4
+/* 5: cb200_gemm_args gained the trailing fields ldy, n_peers, y_peers (zero = the behaviour of version 4): a result
+ *    with its own row pitch that the kernel also stores into the copies of peer GPUs. */
+#define CB200_VERSION 5
 
 typedef enum {
   CB200_OK = 0,
@@ -174,6 +176,18 @@ typedef struct {
   int32_t ldx; /* CB200_GEMM_MATMUL only: elements between consecutive rows of X (0 = k, a dense matrix). A
                   multiple of 8. Lets a K slice of a wider matrix be the operand: the per-split products of the
                   two-stage split-K form are X[:, s K/S : (s+1) K/S] @ W[s K/S : (s+1) K/S, :]. */
+  /* Version 5, trailing fields (zero = a dense local result, as before). A GEMM sharded along N over several GPUs
+   * of one node whose every GPU wants the whole result (the reference has no multi-GPU path; this is the fused form
+   * of "local product, then all-gather"): `y` points at this GPU's column slice inside its copy of the full result
+   * (element [0, first own column]), `ldy` is the full row length in elements (a multiple of 8; the slice starts on
+   * a multiple of 8 columns), and `y_peers[0 .. n_peers)` point at the same element of the other GPUs' copies
+   * (peer-mapped device pointers: symmetric memory, CUDA IPC). The kernel writes every finished tile into its own
+   * copy and, from two further warps, on into the peers' copies while it computes the next tile; nothing is
+   * signalled: the caller orders the GPUs (a barrier) before any of them reads the result. Taken by the CTA-pair
+   * kernel only (m >= 256, no split_k, max_ctas 0); CB200_ERR_UNSUPPORTED otherwise. */
+  int32_t ldy;
+  int32_t n_peers;      /* 0 .. 7 */
+  void* y_peers[7];
 } cb200_gemm_args;
 
 size_t cb200_gemm_workspace_bytes(const cb200_gemm_args* a);

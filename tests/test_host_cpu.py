@@ -20,7 +20,7 @@ def test_library_loads_and_exports_every_declared_symbol():
     for name in declared:
         assert hasattr(lib, name), f"{name} is declared in the header but not exported"
     lib.cb200_strerror.restype = ctypes.c_char_p
-    assert lib.cb200_version() == 4
+    assert lib.cb200_version() == 5
     assert b"workspace" in lib.cb200_strerror(4)
 
 

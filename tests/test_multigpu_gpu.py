@@ -1,5 +1,6 @@
 """Two GPUs, one process each, NCCL over 127.0.0.1: decode sharded by request with no collective on
-the data path (results gathered only to be checked), and a GEMM sharded along N with one all-gather.
+the data path (results gathered only to be checked), and a GEMM sharded along N with one all-gather - as an NCCL
+collective after the product, and fused into the product's kernel over peer memory.
 Skipped on a single-GPU box; the CPU (gloo) form of the same logic is tests/test_sharding_cpu.py."""
 
 import os
@@ -62,8 +63,35 @@ def _worker(rank, world, port, q):
                                     [f16(g["w0"][:, lo:hi])], 1000)
         ok2 = bool(np.allclose(y.float().cpu().numpy(), orc.rmsnorm_matmul(g["x"], g["w0"], 1e-6, g["gamma"], "f16"),
                                rtol=2e-2, atol=2e-2))
+        # ---- the same kind of product with the all-gather fused into the kernel: every rank writes its columns into
+        # its own copy of the full result (symmetric memory) and, tile by tile, into the other rank's copy; no NCCL
+        # collective. Unequal shards, a partial last tile, rows that do not fill a tile; the result must equal the
+        # shards computed one by one on every rank.
+        ok3 = True
+        for op, mm, nn, kk in (("matmul", 512, 1288, 1024), ("rmsnorm", 300, 2048, 512), ("swiglu", 256, 520, 256)):
+            gen = torch.Generator(device="cpu").manual_seed(5)
+            xs = torch.randn(mm, kk, generator=gen).to(torch.float16).cuda()
+            ws = (torch.randn(kk, nn, generator=gen) / kk ** 0.5).to(torch.float16).cuda()
+            w1 = (torch.randn(kk, nn, generator=gen) / kk ** 0.5).to(torch.float16).cuda()
+            bounds = [sharding.n_shard(nn, r, world) for r in range(world)]
+            if op == "matmul":
+                fn = lambda a, b, **kw: ops.matmul(a, b, **kw)  # noqa: E731
+            elif op == "rmsnorm":
+                fn = lambda a, b, **kw: ops.rmsnorm_matmul(a, b, eps=1e-6, **kw)  # noqa: E731
+            else:
+                fn = lambda a, b, c, **kw: ops.swiglu(a, b, c, **kw)  # noqa: E731
+            shards = lambda a0, a1: (ws[:, a0:a1].contiguous(),) + ((w1[:, a0:a1].contiguous(),) if op == "swiglu" else ())  # noqa: E731
+            ys, handle = sharding.symmetric_result(mm, nn, torch.float16, "cuda")
+            ys.fill_(float("nan"))
+            handle.barrier()
+            got = sharding.gemm_n_sharded_fused(fn, xs, shards(*bounds[rank]), nn, ys, handle)
+            torch.cuda.synchronize()
+            want = torch.cat([fn(xs, *shards(a0, a1)) for a0, a1 in bounds], dim=1)
+            # the shards on their own may run under another plan (split K in a cluster) than the pair kernel the fused
+            # form takes, so equality is up to the operators' tolerance; a cell nobody wrote would still be NaN
+            ok3 = ok3 and not bool(torch.isnan(got).any()) and bool(torch.allclose(got.float(), want.float(), rtol=2e-2, atol=2e-2))
         torch.cuda.synchronize()
-        q.put((rank, ok1, ok2))
+        q.put((rank, ok1, ok2 and ok3))
     finally:
         dist.destroy_process_group()
 

@@ -38,7 +38,8 @@ constexpr int kBHalfChunks = 2;                  // 128 columns of B per CTA
 constexpr int kStageBytes = kABytes + kBHalfChunks * kBChunkBytes;  // 32 KB
 constexpr int kStages = 6;
 constexpr int kUmmaN = 256;
-constexpr int kThreads = 256;  // warps 0 TMA, 1 MMA, 2..5 epilogue, 6..7 push finished tiles to peer GPUs (idle otherwise)
+constexpr int kPushWarps = 4;
+constexpr int kThreads = (6 + kPushWarps) * 32;  // warps 0 TMA, 1 MMA, 2..5 epilogue, 6.. push finished tiles to peer GPUs (idle otherwise)
 constexpr int kMaxPeers = 7;
 constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 1024;
 constexpr uint32_t kTmemCols = 512;  // two accumulators of 256 columns
@@ -100,7 +101,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       mbar_init(&acc_full[b], 1);
       mbar_init(&acc_empty[b], 8);  // four epilogue warps of each CTA
       mbar_init(&stored[b], 4);
-      mbar_init(&pushed[b], 2);
+      mbar_init(&pushed[b], kPushWarps);
     }
     mbar_fence_init();
     tma_prefetch_desc(&tm_a);
@@ -189,7 +190,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   } else if (warp >= 6) {
     // ================================================================ finished tiles go to the other GPUs
     // N-sharded GEMM: every GPU computes a column slice of Y and all of them want the whole of Y. The epilogue
-    // writes this GPU's rows of a tile into its own copy (at the slice's column offset); these two warps then
+    // writes this GPU's rows of a tile into its own copy (at the slice's column offset); these warps then
     // read them back (L2) and store them into every peer's copy through NVLink, whole 512-byte row segments per
     // warp instruction, while the pair is already on its next tile: the all-gather rides under the MMAs.
     if constexpr (KS > 1) {  // the two meetings of the split-K combine are meetings of every thread of the cluster
@@ -210,7 +211,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         const int gc0 = tn * kTileN;
         const int pieces = min(kTileN, p.N - gc0) / 8;  // 16-byte pieces of a row segment (at most 32)
         const int grow0 = tm * 256 + static_cast<int>(rank) * kBM;
-        for (int r = r_lo + pw * 4; r < r_lo + kRowsMine; r += 8) {
+        for (int r = r_lo + pw * 4; r < r_lo + kRowsMine; r += 4 * kPushWarps) {
           uint4 v[4];
           bool ok[4];
 #pragma unroll
@@ -218,7 +219,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             ok[i] = lane < pieces && grow0 + r + i < p.M;
             if (ok[i]) v[i] = __ldcg(reinterpret_cast<const uint4*>(ysrc + static_cast<size_t>(grow0 + r + i) * p.ldy + gc0) + lane);
           }
-          for (int d = 0; d < p.n_peers; ++d) {
+          // every CTA starts with another peer, so that at any moment the stores of the GPU go to all of them
+          for (int dd = 0; dd < p.n_peers; ++dd) {
+            const int d = (dd + static_cast<int>(blockIdx.x) + pw) % p.n_peers;
             T* ydst = reinterpret_cast<T*>(p.y_peers[d]);
 #pragma unroll
             for (int i = 0; i < 4; ++i)

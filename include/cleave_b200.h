@@ -182,7 +182,7 @@ typedef struct {
    * (element [0, first own column]), `ldy` is the full row length in elements (a multiple of 8; the slice starts on
    * a multiple of 8 columns), and `y_peers[0 .. n_peers)` point at the same element of the other GPUs' copies
    * (peer-mapped device pointers: symmetric memory, CUDA IPC). The kernel writes every finished tile into its own
-   * copy and, from two further warps, on into the peers' copies while it computes the next tile; nothing is
+   * copy and, from four further warps, on into the peers' copies while it computes the next tile; nothing is
    * signalled: the caller orders the GPUs (a barrier) before any of them reads the result. Taken by the CTA-pair
    * kernel only (m >= 256, no split_k, max_ctas 0); CB200_ERR_UNSUPPORTED otherwise. */
   int32_t ldy;

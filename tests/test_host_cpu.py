@@ -329,3 +329,39 @@ def test_calibrate_dispatch_threshold_rule():
     assert d2["min_tiles"] == 1 and d2["split_runs"] == 4 and not d2["applied"]
     with pytest.raises(CleaveError):
         calibrate_dispatch(pair, WorkloadCandidate("x", ""), tiles)
+
+
+def test_ctypes_structs_match_the_c_header(tmp_path):
+    """Every argument struct of include/cleave_b200.h has the same size and the same field offsets in the ctypes
+    mirror the package calls through (cleave_b200/_lib.py): a C program compiled from the header prints them."""
+    import ctypes
+    import shutil
+    import subprocess
+
+    from cleave_b200 import _lib
+
+    if shutil.which("gcc") is None:
+        pytest.skip("no C compiler")
+    pairs = {"cb200_attn_decode_args": _lib.AttnDecodeArgs, "cb200_gemm_args": _lib.GemmArgs,
+             "cb200_gemm_plan_info": _lib.GemmPlanInfo, "cb200_mla_prefill_args": _lib.MlaPrefillArgs,
+             "cb200_split_combine_args": _lib.SplitCombineArgs, "cb200_attn_unnormalise_args": _lib.AttnUnnormaliseArgs,
+             "cb200_matmul_rowsum_args": _lib.MatmulRowsumArgs, "cb200_matmul_matmul_args": _lib.MatmulMatmulArgs,
+             "cb200_lora_args": _lib.LoraArgs, "cb200_mla_decode_args": _lib.MlaDecodeArgs,
+             "cb200_attn_prefill_args": _lib.AttnPrefillArgs, "cb200_attn_prefill_ragged_args": _lib.AttnPrefillRaggedArgs}
+    lines = ["#include <stdio.h>", "#include <stddef.h>", '#include "cleave_b200.h"', "int main(void) {"]
+    for cname, cls in pairs.items():
+        lines.append(f'  printf("{cname} size %zu\\n", sizeof({cname}));')
+        for field, _ in cls._fields_:
+            lines.append(f'  printf("{cname} {field} %zu\\n", offsetof({cname}, {field}));')
+    lines += ["  return 0;", "}"]
+    src = tmp_path / "layout.c"
+    src.write_text("\n".join(lines))
+    exe = tmp_path / "layout"
+    include = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "include")
+    subprocess.run(["gcc", "-I", include, str(src), "-o", str(exe)], check=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout
+    got = {(a, b): int(c) for a, b, c in (ln.split() for ln in out.splitlines())}
+    for cname, cls in pairs.items():
+        assert got[(cname, "size")] == ctypes.sizeof(cls), cname
+        for field, _ in cls._fields_:
+            assert got[(cname, field)] == getattr(cls, field).offset, (cname, field)

@@ -91,6 +91,21 @@ def test_causal_attention_vs_oracle(hq, hkv, sq, skv, d, dt):
     assert_lse_close(host(lse), want_lse)
 
 
+@pytest.mark.parametrize("hq,hkv,sq,skv,d,dt", [(8, 2, 300, 100, 128, "bf16"), (4, 4, 513, 40, 64, "f16"), (160, 160, 257, 129, 128, "bf16")])
+def test_causal_attention_with_more_queries_than_keys(hq, hkv, sq, skv, d, dt):
+    """Static layout, end-aligned mask, S_Q > S_KV: the first S_Q - S_KV rows see no key (0 and -inf), whole query
+    tiles among them - items the persistent CTAs only write zeros for - and, with 160 heads, more items than SMs."""
+    inp = cases.attention_inputs(21, hq, hkv, sq, skv, d, dt)
+    lse = torch.empty(hq, sq, dtype=torch.float32, device="cuda")
+    scale = d ** -0.5
+    got = _ops().attention_prefill(dev(inp["q"], dt), dev(inp["k"], dt), dev(inp["v"], dt), scale, causal=True, lse=lse)
+    _check_ws()
+    want, want_lse = orc.attention_masked(inp["q"], inp["k"], inp["v"], scale, True, dt)
+    assert_close(host(got), want)
+    assert_lse_close(host(lse), want_lse)
+    assert not host(got)[:, :sq - skv].any() and np.isneginf(host(lse)[:, :sq - skv]).all()
+
+
 @pytest.mark.parametrize("heads,sq_", [(2, 128), (160, 256)])
 def test_large_logits_take_the_rescale_path(heads, sq_):
     """Keys whose norm grows along the sequence push the running maximum up by more than 2^8

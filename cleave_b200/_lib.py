@@ -13,6 +13,7 @@ LIB_PATH = os.path.join(_HERE, "libcleave_b200.so")
 
 F16, BF16 = 0, 1
 OK = 0
+ERR_UNSUPPORTED = 2
 ERR_DEVICE_TIMEOUT = 6
 
 
@@ -160,6 +161,8 @@ def lib() -> C.CDLL:
                 "(there is no CPU or PyTorch fallback)")
         L = C.CDLL(LIB_PATH)
         L.cb200_version.restype = C.c_int
+        L.cb200_peer_scatter_cols.restype = C.c_int
+        L.cb200_peer_scatter_cols.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_void_p]
         L.cb200_set_small_problem_limit.restype = C.c_int
         L.cb200_set_small_problem_limit.argtypes = [C.c_int]
         L.cb200_strerror.restype = C.c_char_p

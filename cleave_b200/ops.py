@@ -413,6 +413,17 @@ def _gemm(op, x, w, w1=None, gamma=None, eps=0.0, split_k=0, out=None, max_ctas=
     return out
 
 
+def peer_scatter_cols(src, ld_dst: int, dsts) -> None:
+    """Copies the dense (M, N) CUDA tensor ``src`` into column slices of several (M, ld_dst)-pitched matrices:
+    ``dsts`` are device pointers to element [0, first column of the slice] of each - this GPU's copy of a result
+    sharded along N and the peer GPUs' copies (symmetric memory). One kernel of plain stores on the current stream;
+    the caller orders the GPUs before anyone reads (:func:`cleave_b200.sharding.gemm_n_sharded_fused`)."""
+    src = _cuda(src, "src")
+    m, n = src.shape
+    arr = (C.c_void_p * len(dsts))(*[int(d) for d in dsts])
+    _lib.check(_lib.lib().cb200_peer_scatter_cols(src.data_ptr(), m, n, int(ld_dst), arr, len(dsts), _dtype_code(src), _stream()))
+
+
 def matmul(x, w, *, split_k=0, out=None, max_ctas=0, addend=None, x2=None, w2=None, dependent_launch=1, peers=None):
     """``Y = X @ W`` (reference operator: demo/matmul.py:11-13); ``split_k`` is the plan's K split.
     ``addend`` (M, N) is added in the epilogue; ``x2`` (M, K2) and ``w2`` (K2, N) extend the contraction:

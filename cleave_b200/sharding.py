@@ -135,10 +135,28 @@ def gemm_n_sharded_fused(local_gemm, x, w_shards, n_total, y, handle, group=None
     result on every rank. No NCCL collective and no reassembly copy."""
     import torch.distributed as dist
 
+    from . import _lib, ops
+
     world, rank = dist.get_world_size(group), dist.get_rank(group)
     lo, hi = n_shard(n_total, rank, world)
     itemsize = y.element_size()
     peers = [int(handle.buffer_ptrs[r]) + lo * itemsize for r in range(world) if r != rank]
-    local_gemm(x, *w_shards, out=y[:, lo:hi], peers=peers)
+    key = (tuple(x.shape), tuple(w_shards[0].shape), x.dtype, len(w_shards))
+    if _IN_KERNEL.get(key, True):
+        try:
+            local_gemm(x, *w_shards, out=y[:, lo:hi], peers=peers)
+            handle.barrier()
+            return y
+        except _lib.Cb200Error as exc:
+            if exc.status != _lib.ERR_UNSUPPORTED:
+                raise
+            _IN_KERNEL[key] = False  # remembered: the refusal costs a host round trip every time
+    # shapes the CTA-pair kernel does not take (few rows): the product into a dense block, then one kernel that
+    # copies the block into this rank's slice of every copy - still no collective and no reassembly pass
+    block = local_gemm(x, *w_shards)
+    ops.peer_scatter_cols(block, n_total, [y.data_ptr() + lo * itemsize] + peers)
     handle.barrier()
     return y
+
+
+_IN_KERNEL: dict = {}  # (shapes, dtype) -> False once cb200_gemm has refused to send that product's tiles itself

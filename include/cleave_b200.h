@@ -43,7 +43,7 @@ extern "C" {
 /* 4: cb200_attn_prefill_ragged_args gained the trailing field num_kv_indices (zero = the behaviour of
  *    version 3); the paged MLA decode clips request ranges to num_kv_indices; new cb200_set_small_problem_limit. */
 /* 5: cb200_gemm_args gained the trailing fields ldy, n_peers, y_peers (zero = the behaviour of version 4): a result
- *    with its own row pitch that the kernel also stores into the copies of peer GPUs. */
+ *    with its own row pitch that the kernel also stores into the copies of peer GPUs; new cb200_peer_scatter_cols. */
 #define CB200_VERSION 5
 
 typedef enum {
@@ -515,6 +515,17 @@ int cb200_attn_decode_static_scratch(const cb200_attn_decode_args* a, void* stre
  * the current device gave up, in which case that call's outputs are not valid. Ask before the next call: every
  * call clears the word. Allocates nothing. */
 int cb200_attn_decode_static_scratch_status(void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * The all-gather of an N-sharded GEMM for shapes whose product cb200_gemm does not send to the peers itself (the
+ * y_peers fields need the CTA-pair kernel, m >= 256): the dense (m, n) block `src` of this GPU is copied to
+ * `dsts[0 .. n_dst)` - element [0, first own column] of its own copy of the (m, ld_dst) result and of the peer GPUs'
+ * copies (peer-mapped device pointers; `dsts` is a host array, n_dst <= 8). n and ld_dst multiples of 8, 16-bit
+ * types. One kernel of plain stores on `stream`; nothing is signalled: put a barrier across the GPUs between this call
+ * and the first read of the result. No counterpart in the reference (single-GPU).
+ * ---------------------------------------------------------------------------------------- */
+int cb200_peer_scatter_cols(const void* src, int m, int n, int ld_dst, void* const* dsts, int n_dst, int dtype,
+                            void* stream);
 
 /* ------------------------------------------------------------------------------------------
  * Causal prefill whose key window is far shorter than its run of query rows (a chunk with thousands of query tokens

@@ -68,7 +68,9 @@ def _worker(rank, world, port, q):
         # collective. Unequal shards, a partial last tile, rows that do not fill a tile; the result must equal the
         # shards computed one by one on every rank.
         ok3 = True
-        for op, mm, nn, kk in (("matmul", 512, 1288, 1024), ("rmsnorm", 300, 2048, 512), ("swiglu", 256, 520, 256)):
+        # (64 rows: the product runs on the single-CTA kernels and one scatter kernel sends the block to the copies)
+        for op, mm, nn, kk in (("matmul", 512, 1288, 1024), ("rmsnorm", 300, 2048, 512), ("swiglu", 256, 520, 256),
+                               ("rmsnorm", 64, 1000, 512)):
             gen = torch.Generator(device="cpu").manual_seed(5)
             xs = torch.randn(mm, kk, generator=gen).to(torch.float16).cuda()
             ws = (torch.randn(kk, nn, generator=gen) / kk ** 0.5).to(torch.float16).cuda()

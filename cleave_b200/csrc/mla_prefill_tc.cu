@@ -224,14 +224,14 @@ mla_prefill_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_const
     int pg[8], pg_next[8];
     if (nt > 0) {
 #pragma unroll
-      for (int rr = 0; rr < 8; ++rr) pg_next[rr] = page_of(rr * 16 + r_in);
+      for (int rr = 0; rr < 8; ++rr) pg_next[rr] = rr * 16 < kv_len ? page_of(rr * 16 + r_in) : 0;
     }
     for (int j = 0; j < nt; ++j) {
 #pragma unroll
       for (int rr = 0; rr < 8; ++rr) pg[rr] = pg_next[rr];
       if (j + 1 < nt) {  // one tile ahead: the latency of the index loads stays off the stream
 #pragma unroll
-        for (int rr = 0; rr < 8; ++rr) pg_next[rr] = page_of((j + 1) * kBN + rr * 16 + r_in);
+        for (int rr = 0; rr < 8; ++rr) pg_next[rr] = (j + 1) * kBN + rr * 16 < kv_len ? page_of((j + 1) * kBN + rr * 16 + r_in) : 0;
       }
       for (int i = 0; i < kChunks; ++i) {
         const int c = chunk_at(i);
@@ -243,14 +243,25 @@ mla_prefill_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_const
           if (i == kChunks - kVChunks && j >= 2) mbar_wait(&pv_done[j & 1], ((j >> 1) - 1) & 1, p.status, kFaultMmaBarrier);
           dst = smem_u32(v_smem + (j & 1) * kVBytes + (i - (kChunks - kVChunks)) * kChunkBytes);
         }
+        // rounds of 16 rows; those that lie wholly past the request's last key are not fetched (a tile of a short
+        // request, or a request's last tile, is mostly such rows): zeros from the thread itself, which as keys are
+        // masked and as values meet P = 0
+        const int live_rounds = min(8, (kv_len - j * kBN + 15) >> 4);
+        bool zeroed = false;
 #pragma unroll
         for (int rr = 0; rr < 8; ++rr) {
           const int row = rr * 16 + r_in;
-          const T* src = c < kCkv / 64 ? ckv + static_cast<long long>(pg[rr]) * kCkv + c * 64 + piece * 8
-                                       : kpe + static_cast<long long>(pg[rr]) * kKpe + piece * 8;
           const uint32_t o = row * 128 + ((piece ^ (row & 7)) << 4);
-          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + o), "l"(src) : "memory");
+          if (rr < live_rounds) {
+            const T* src = c < kCkv / 64 ? ckv + static_cast<long long>(pg[rr]) * kCkv + c * 64 + piece * 8
+                                         : kpe + static_cast<long long>(pg[rr]) * kKpe + piece * 8;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + o), "l"(src) : "memory");
+          } else {
+            asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(dst + o), "r"(0u) : "memory");
+            zeroed = true;
+          }
         }
+        if (zeroed) fence_proxy_async_smem();  // the MMA reads shared memory through the async proxy
         asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&k_full[st])) : "memory");
         if (++st == kStages) { st = 0; ph ^= 1; }
       }
@@ -322,9 +333,13 @@ mla_prefill_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_const
       const uint32_t t_s = tmem_base + lane_field + kColS + sb * kBN;
       const int k0 = j * kBN;
       const bool whole = k0 + kBN - 1 <= key_limit;  // the whole tile is visible to this row
+      // the last key any row of this warp sees: groups of 32 scores beyond it are not read at all (the tile of a
+      // short request; the diagonal tile of a block's first rows)
+      const int warp_limit = __reduce_max_sync(0xffffffffu, key_limit);
       float mx = -INFINITY;
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
+        if (k0 + q * 32 > warp_limit) break;
         uint32_t rg[32];
         tmem_ld_32x32(t_s + q * 32, rg);
         tmem_ld_wait();
@@ -363,6 +378,12 @@ mla_prefill_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_const
 #pragma unroll
       for (int hh = 0; hh < 2; ++hh) {
         uint32_t ra[32], rb[32], pk[32];
+        if (k0 + hh * 64 > warp_limit) {  // nothing of this half is visible to the warp: P = 0
+#pragma unroll
+          for (int i = 0; i < 32; ++i) pk[i] = 0u;
+          tmem_st_32x32(t_s + hh * 32, pk);
+          continue;
+        }
         tmem_ld_32x32(t_s + hh * 64, ra);
         tmem_ld_32x32(t_s + hh * 64 + 32, rb);
         tmem_ld_wait();

@@ -248,6 +248,31 @@ def test_paged_causal_mla_prefill_matches_reference_golden_and_oracle(impl):
     assert_lse_close(host(lse), want_lse)
 
 
+@pytest.mark.parametrize("heads", [16, 64])
+def test_mla_prefill_short_and_ragged_key_windows(heads):
+    """Key counts on both sides of every boundary the kernel treats specially: the 16-row rounds of the gather (rows
+    past a request's last key are zero-filled in shared memory, not fetched), the 32- and 64-score groups the softmax
+    skips when no row of a warp sees them, and the 128-token tile. The shared memory a launch finds may hold anything:
+    a launch over NaN caches runs first."""
+    ops = _ops()
+    q_lens = [1, 3, 8, 1, 2, 9, 1, 20, 5, 1, 40]
+    kv_lens = [1, 15, 16, 17, 31, 32, 33, 63, 64, 65, 129 + 47]
+    inp = cases.mla_prefill_inputs(77 + heads, q_lens, kv_lens, heads, 512, 64, "bf16", cases.MLA_SM_SCALE)
+    i32 = lambda a: torch.from_numpy(a).cuda()  # noqa: E731
+    args = [dev(inp["q_nope"], "bf16"), dev(inp["q_pe"], "bf16"), dev(inp["ckv_cache"], "bf16"), dev(inp["kpe_cache"], "bf16"),
+            i32(inp["qo_indptr"]), i32(inp["kv_indptr"]), i32(inp["kv_indices"]), inp["sm_scale"]]
+    poisoned = list(args)
+    poisoned[2] = torch.full_like(args[2], float("nan"))
+    poisoned[3] = torch.full_like(args[3], float("nan"))
+    ops.mla_paged_prefill(*poisoned, impl="tile")  # leaves NaN rows behind in shared memory
+    out, lse = ops.mla_paged_prefill(*args, impl="tile")
+    ops.check_workspace(ops.workspace("mla_prefill", 0, "cuda"))
+    want, want_lse = orc.mla_paged_prefill(inp["q_nope"], inp["q_pe"], inp["ckv_cache"], inp["kpe_cache"], inp["qo_indptr"],
+                                           inp["kv_indptr"], inp["kv_indices"], inp["sm_scale"], dtype="bf16")
+    assert_close(host(out), want)
+    assert_lse_close(host(lse), want_lse)
+
+
 @pytest.mark.parametrize("heads,dt", [(16, "f16"), (32, "bf16"), (128, "bf16"), (8, "bf16")])
 def test_mla_prefill_tile_kernel_vs_oracle(heads, dt):
     """The query-tile kernel over head counts that pack 8, 4, 1 and 16 query tokens into the 128 MMA rows, with

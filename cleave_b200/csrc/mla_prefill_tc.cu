@@ -54,6 +54,8 @@ constexpr int kVChunks = kDV / 64;           // the score chunks that are this C
 constexpr int kVBytes = kVChunks * kChunkBytes;    // 64 KB, two buffers
 constexpr int kSmemBytes = kStages * kStageBytes + 2 * kVBytes + 1024 /*barriers*/ + 1024 /*alignment*/;
 constexpr int kThreads = 10 * 32;
+constexpr int kThreadsPersist = 11 * 32;     // the persistent form: one more warp hands the item numbers round
+constexpr int kTicketWarp = 10;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.f;     // log2 units
 constexpr uint32_t kColS = 0, kColO = 256;
@@ -68,12 +70,19 @@ struct Params {
   float* lse;
   int* status;
   int batch, heads, qb;  // qb = 128 / heads query tokens per item
+  int blocks;            // upper bound on the query blocks of the batch; an item is (block, half of the output columns)
   int num_pages, n_idx;
   float scale_log2;
 };
 
-template <typename T>
-__global__ void __launch_bounds__(kThreads, 1)
+// PERSIST = false: one CTA per item (the grid is the upper bound on the items). PERSIST = true: one CTA per SM, which
+// starts on the item of its block index and takes further ones from a counter in the workspace header; every barrier
+// phase and buffer parity runs on across items, so the producers and the MMA warp are on the next item while the
+// softmax warps finish the current one. The second form pays for batches of many short items and costs a call with a
+// single small item a microsecond (more barriers, the item ring, tensor memory taken before the item is known): the
+// host picks (launch below).
+template <typename T, bool PERSIST>
+__global__ void __launch_bounds__(PERSIST ? kThreadsPersist : kThreads, 1)
 mla_prefill_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_constant__ CUtensorMap tm_qp, const Params p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -86,10 +95,13 @@ mla_prefill_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_const
   uint64_t* p_full = s_full + 2;        // [2] P stored (and O rescaled if needed)
   uint64_t* pv_done = p_full + 2;       // [2] the value MMAs of a tile have completed
   uint64_t* o_done = pv_done + 2;
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(o_done + 1);
+  uint64_t* o_free = o_done + 1;        // persistent form: the epilogue has taken O out of tensor memory
+  uint64_t* t_full = o_free + 1;        // [2] persistent form: an item number is in the ring
+  uint64_t* t_empty = t_full + 2;       // [2] every warp has read it
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(t_empty + 2);
+  volatile int* item_ring = reinterpret_cast<volatile int*>(tmem_holder + 1);  // [2]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int dh = blockIdx.x & 1;  // which half of the output columns
   // The ranges of the first 32 requests (lane = request) are fetched before anything else, so that the trip to
   // memory runs beside the barrier set-up below; the search starts from these registers.
   int pre_lo = 0, pre_hi = 0, pre_klo = 0, pre_khi = 0;
@@ -110,14 +122,68 @@ mla_prefill_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_const
       mbar_init(&pv_done[s], 1);
     }
     mbar_init(o_done, 1);
+    if constexpr (PERSIST) {
+      mbar_init(o_free, 4);
+      for (int s = 0; s < 2; ++s) {
+        mbar_init(&t_full[s], 1);
+        mbar_init(&t_empty[s], kTicketWarp);
+      }
+    }
     mbar_fence_init();
     tma_prefetch_desc(&tm_qn);
     tma_prefetch_desc(&tm_qp);
   }
 
-  // ---- which (request, query block) this CTA works on: late blocks, which see the most keys, come first
+  uint32_t tmem_base = 0;
+  const int n_items = 2 * p.blocks;
+  int* ticket = p.status + 8;    // persistent form: items beyond the first of every CTA are dealt by this counter
+  int* finished = p.status + 9;  // CTAs that are through; the last one clears both words for the next launch
+  if constexpr (PERSIST) {
+    if (warp == 1) {
+      tmem_alloc(tmem_holder, 512);
+      tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_holder);
+    if (warp == kTicketWarp) {
+      // the first item of a CTA is its block index, which every warp knows; the others come from the counter, fetched
+      // one item ahead and handed round through a two-slot ring
+      if (lane == 0) {
+        for (int k = 0;; ++k) {
+          const int s = k & 1;
+          mbar_wait(&t_empty[s], ((k >> 1) & 1) ^ 1, p.status, kFaultEmptyBarrier);
+          const int item = n_items <= static_cast<int>(gridDim.x) ? n_items : static_cast<int>(gridDim.x) + atomicAdd(ticket, 1);
+          item_ring[s] = item;
+          mbar_arrive(&t_full[s]);
+          if (item >= n_items) break;
+        }
+      }
+      __syncwarp();
+    }
+  }
+  int n_taken = 0;  // item numbers this warp has had
+  int it = 0;       // items with keys this CTA has run, jt: their KV tiles (every role counts alike; 0 in the one-item form)
+  int jt = 0;
+  int st = 0, ph = 0;  // ring position of this warp's role
+  while (warp < kTicketWarp) {
+    int item = static_cast<int>(blockIdx.x);
+    if constexpr (PERSIST) {
+      if (n_taken > 0) {  // the ring's entry number n_taken - 1
+        const int s = (n_taken - 1) & 1;
+        mbar_wait(&t_full[s], ((n_taken - 1) >> 1) & 1, p.status, kFaultFullBarrier);
+        item = item_ring[s];
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&t_empty[s]);
+      }
+      ++n_taken;
+      if (item >= n_items) break;
+    }
+  const int dh = item & 1;  // which half of the output columns
+  // ---- which (request, query block) the item is: late blocks, which see the most keys, come first
   // (every warp searches the query offsets 32 requests at a time: lane = request, block counts scanned with shuffles)
-  int t = static_cast<int>(gridDim.x >> 1) - 1 - static_cast<int>(blockIdx.x >> 1), r = 0, lo = 0;
+  int t = p.blocks - 1 - (item >> 1), r = 0, lo = 0;
   int q_len = 0, kv_base_found = 0, kv_end_found = 0;
   bool found = false;
   for (int r0 = 0; r0 < p.batch && !found; r0 += 32) {
@@ -150,7 +216,11 @@ mla_prefill_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_const
       t -= all;
     }
   }
-  if (!found) return;  // the grid is an upper bound on the number of query blocks
+  (void)r;
+  if (!found) {  // the item count is an upper bound on the number of query blocks
+    if constexpr (PERSIST) continue;
+    else return;
+  }
   const int q_base = lo;                 // first query token of the request
   const int q0 = t * p.qb;               // first query token of this block, inside the request
   int kv_base = kv_base_found;  // fetched beside the query offsets: one trip to memory, not two in a row
@@ -167,22 +237,25 @@ mla_prefill_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_const
     T* outp = reinterpret_cast<T*>(p.out);
     const int rows = live_q * p.heads;  // (token, head) pairs, contiguous in out
     const size_t row0 = static_cast<size_t>(q_base + q0) * p.heads;
-    for (int i = tid; i < rows * (kDV / 8); i += blockDim.x) {
+    for (int i = tid; i < rows * (kDV / 8); i += kThreads) {
       const int rw = i / (kDV / 8), c = i - rw * (kDV / 8);
       *reinterpret_cast<uint4*>(outp + (row0 + rw) * kCkv + dh * kDV + c * 8) = make_uint4(0u, 0u, 0u, 0u);
     }
     if (dh == 0 && p.lse)
-      for (int i = tid; i < rows; i += blockDim.x) p.lse[row0 + i] = -INFINITY;
-    return;
+      for (int i = tid; i < rows; i += kThreads) p.lse[row0 + i] = -INFINITY;
+    if constexpr (PERSIST) continue;
+    else return;
   }
-  if (warp == 1) {
-    tmem_alloc(tmem_holder, 512);
-    tmem_relinquish();
+  if constexpr (!PERSIST) {
+    if (warp == 1) {
+      tmem_alloc(tmem_holder, 512);
+      tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_holder);
   }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_holder);
 
   // page id of token `tok` of this request (clamped: rows past the end repeat the last token and are masked)
   auto page_of = [&](int tok) {
@@ -199,7 +272,6 @@ mla_prefill_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_const
   if (warp == 0) {
     // ================================================================ Q chunks by TMA
     const int row0 = (q_base + q0) * p.heads;  // first row of the block in the (total_q * H, .) view
-    int st = 0, ph = 0;
     for (int j = 0; j < nt; ++j) {
       for (int i = 0; i < kChunks; ++i) {
         const int c = chunk_at(i);
@@ -220,13 +292,13 @@ mla_prefill_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_const
     const int gtid = tid - 6 * 32, piece = gtid & 7, r_in = gtid >> 3;
     const T* ckv = reinterpret_cast<const T*>(p.ckv);
     const T* kpe = reinterpret_cast<const T*>(p.kpe);
-    int st = 0, ph = 0;
     int pg[8], pg_next[8];
     if (nt > 0) {
 #pragma unroll
       for (int rr = 0; rr < 8; ++rr) pg_next[rr] = rr * 16 < kv_len ? page_of(rr * 16 + r_in) : 0;
     }
     for (int j = 0; j < nt; ++j) {
+      const int jj = jt + j;  // the tile's number in this CTA's run: buffer parities and phases run on across items
 #pragma unroll
       for (int rr = 0; rr < 8; ++rr) pg[rr] = pg_next[rr];
       if (j + 1 < nt) {  // one tile ahead: the latency of the index loads stays off the stream
@@ -240,8 +312,8 @@ mla_prefill_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_const
         if (i >= kChunks - kVChunks) {
           // a chunk that is also value columns goes to the tile's value buffer, which the value product of
           // tile j - 2 must have finished reading
-          if (i == kChunks - kVChunks && j >= 2) mbar_wait(&pv_done[j & 1], ((j >> 1) - 1) & 1, p.status, kFaultMmaBarrier);
-          dst = smem_u32(v_smem + (j & 1) * kVBytes + (i - (kChunks - kVChunks)) * kChunkBytes);
+          if (i == kChunks - kVChunks && jj >= 2) mbar_wait(&pv_done[jj & 1], ((jj >> 1) - 1) & 1, p.status, kFaultMmaBarrier);
+          dst = smem_u32(v_smem + (jj & 1) * kVBytes + (i - (kChunks - kVChunks)) * kChunkBytes);
         }
         // rounds of 16 rows; those that lie wholly past the request's last key are not fetched (a tile of a short
         // request, or a request's last tile, is mostly such rows): zeros from the thread itself, which as keys are
@@ -272,16 +344,16 @@ mla_prefill_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_const
     constexpr uint32_t idesc_s = umma_idesc(kBf16, /*b_mn_major=*/false, kBM, kBN);
     constexpr uint32_t idesc_pv = umma_idesc(kBf16, /*b_mn_major=*/true, kBM, kDV);
     const uint32_t ring_addr = smem_u32(ring), v_addr = smem_u32(v_smem);
-    int st = 0, ph = 0;
     auto issue_s = [&](int j) {
-      const uint32_t d = tmem_base + kColS + (j & 1) * kBN;
+      const int jj = jt + j;
+      const uint32_t d = tmem_base + kColS + (jj & 1) * kBN;
       for (int i = 0; i < kChunks; ++i) {
         mbar_wait(&k_full[st], ph, p.status, kFaultFullBarrier);
         tc_fence_after();
         if (elect_one()) {
           const uint32_t a = ring_addr + st * kStageBytes;
           const uint32_t b = i < kChunks - kVChunks ? a + kChunkBytes
-                                                    : v_addr + (j & 1) * kVBytes + (i - (kChunks - kVChunks)) * kChunkBytes;
+                                                    : v_addr + (jj & 1) * kVBytes + (i - (kChunks - kVChunks)) * kChunkBytes;
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) {
             const uint64_t adesc = umma_smem_desc(a + kk * 32, 16, 8 * 128);
@@ -293,14 +365,17 @@ mla_prefill_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_const
         __syncwarp();
         if (++st == kStages) { st = 0; ph ^= 1; }
       }
-      if (elect_one()) umma_commit(&s_full[j & 1]);
+      if (elect_one()) umma_commit(&s_full[jj & 1]);
       __syncwarp();
     };
-    if (nt > 0) issue_s(0);
+    issue_s(0);
     for (int j = 0; j < nt; ++j) {
       if (j + 1 < nt) issue_s(j + 1);
-      const int pb = j & 1;
-      mbar_wait(&p_full[pb], (j >> 1) & 1, p.status, kFaultTmemBarrier);
+      const int jj = jt + j, pb = jj & 1;
+      mbar_wait(&p_full[pb], (jj >> 1) & 1, p.status, kFaultTmemBarrier);
+      // persistent form: the first value product of an item overwrites O, which the epilogue of the item before
+      // must have read
+      if (PERSIST && j == 0) mbar_wait(o_free, (it & 1) ^ 1, p.status, kFaultTmemBarrier);
       tc_fence_after();
       if (elect_one()) {
 #pragma unroll
@@ -325,8 +400,8 @@ mla_prefill_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_const
     const int key_limit = live ? min(kv_len - 1, q0 + qi + off) : -1;  // last key this row sees
     float m_ref = 0.f, l_run = 0.f;
     for (int j = 0; j < nt; ++j) {
-      const int sb = j & 1;
-      mbar_wait(&s_full[sb], (j >> 1) & 1, p.status, kFaultMmaBarrier);
+      const int jj = jt + j, sb = jj & 1;
+      mbar_wait(&s_full[sb], (jj >> 1) & 1, p.status, kFaultMmaBarrier);
       tc_fence_after();
       // Two passes over the 128 scores of the row, 32 at a time from tensor memory (reads are cheap, registers
       // are not): the maximum first, then exp2 and the 16-bit P values.
@@ -358,7 +433,7 @@ mla_prefill_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_const
       }
       if (__any_sync(0xffffffffu, rescale)) {  // rare: the running maximum grew by more than 2^8
         // O may only be touched when no value MMA is in flight: tile j - 1 is the last one issued
-        mbar_wait(&pv_done[sb ^ 1], ((j - 1) >> 1) & 1, p.status, kFaultMmaBarrier);
+        mbar_wait(&pv_done[sb ^ 1], ((jj - 1) >> 1) & 1, p.status, kFaultMmaBarrier);
         tc_fence_after();
 #pragma unroll 1
         for (int c0 = 0; c0 < kDV; c0 += 32) {
@@ -406,22 +481,20 @@ mla_prefill_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_const
       if (lane == 0) mbar_arrive(&p_full[sb]);
     }
     // ---- epilogue: O / l
-    if (nt > 0) {
-      mbar_wait(o_done, 0, p.status, kFaultMmaBarrier);
-      tc_fence_after();
-    }
+    mbar_wait(o_done, it & 1, p.status, kFaultMmaBarrier);
+    tc_fence_after();
     const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
     const size_t orow = static_cast<size_t>(q_base + q0 + qi) * p.heads + head;
     T* outp = reinterpret_cast<T*>(p.out) + orow * kCkv + dh * kDV;
 #pragma unroll 1
     for (int c0 = 0; c0 < kDV; c0 += 32) {
       uint32_t o[32];
-      if (nt > 0) {
-        tmem_ld_32x32(tmem_base + lane_field + kColO + c0, o);
-        tmem_ld_wait();
-      } else {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[i] = 0u;
+      tmem_ld_32x32(tmem_base + lane_field + kColO + c0, o);
+      tmem_ld_wait();
+      if (PERSIST && c0 + 32 >= kDV) {  // O is out of tensor memory: the next item's value product may start
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(o_free);
       }
       if (live) {
         const float* v = reinterpret_cast<const float*>(o);
@@ -438,12 +511,21 @@ mla_prefill_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_const
     }
     if (live && dh == 0 && p.lse) p.lse[orow] = l_run > 0.f ? m_ref + fast_log2(l_run) : -INFINITY;
   }
+    if constexpr (!PERSIST) break;
+    jt += nt;
+    ++it;
+  }  // items
 
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
+  }
+  if (PERSIST && tid == 0 && n_items > static_cast<int>(gridDim.x) && atomicAdd(finished, 1) == static_cast<int>(gridDim.x) - 1) {
+    // every CTA has fetched its last item number: the counters are clear for the next launch
+    atomicExch(ticket, 0);
+    atomicExch(finished, 0);
   }
 }
 
@@ -476,11 +558,24 @@ int launch(const cb200_mla_prefill_args* a, cudaStream_t stream) {
         !encode_tensor_map(&tm_qp, dt, 2, const_cast<void*>(a->q_pe), dp, sp, box, CU_TENSOR_MAP_SWIZZLE_128B))
       return CB200_ERR_CUDA;
   }
-  auto kern = mla_prefill_kernel<T>;
-  CB200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-  // every request has at most ceil(q_len / qb) <= q_len / qb + 1 query blocks; two CTAs per block
+  // every request has at most ceil(q_len / qb) <= q_len / qb + 1 query blocks; two items (column halves) per block
   const long long blocks = static_cast<long long>(ceil_div(a->total_q, p.qb)) + a->batch;
-  kern<<<static_cast<unsigned>(2 * blocks), kThreads, kSmemBytes, stream>>>(tm_qn, tm_qp, p);
+  p.blocks = static_cast<int>(blocks);
+  const int sms = sm_count();
+  if (sms <= 0) return CB200_ERR_CUDA;
+  // Many short items (batches of prompts of a few hundred tokens): persistent CTAs, whose producers run ahead into the
+  // next item. Few items, or long ones (an item of a 2048-token prompt has up to sixteen KV tiles and is bound by what
+  // the SM pulls from L2, not by the boundaries): one CTA per item.
+  const bool persist = 2 * blocks >= 8LL * sms && static_cast<long long>(a->num_kv_indices) <= 320LL * a->batch;
+  if (persist) {
+    auto kern = mla_prefill_kernel<T, true>;
+    CB200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    kern<<<static_cast<unsigned>(sms), kThreadsPersist, kSmemBytes, stream>>>(tm_qn, tm_qp, p);
+  } else {
+    auto kern = mla_prefill_kernel<T, false>;
+    CB200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    kern<<<static_cast<unsigned>(2 * blocks), kThreads, kSmemBytes, stream>>>(tm_qn, tm_qp, p);
+  }
   CB200_CUDA_TRY(cudaGetLastError());
   return CB200_OK;
 }

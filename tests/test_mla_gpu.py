@@ -248,6 +248,34 @@ def test_paged_causal_mla_prefill_matches_reference_golden_and_oracle(impl):
     assert_lse_close(host(lse), want_lse)
 
 
+def test_mla_prefill_many_short_prompts():
+    """Ninety prompts of 0...120 tokens with up to 200 cached tokens in front: more than a thousand (block, column half)
+    items of one or two KV tiles, which the host hands to the persistent form of the kernel (items dealt by a counter
+    in the workspace header, barrier phases running on across items). Against the oracle, twice on one workspace."""
+    ops = _ops()
+    rng = np.random.default_rng(90)
+    q_lens = [int(x) for x in rng.integers(0, 121, 90)]
+    kv_lens = [int(q + c) for q, c in zip(q_lens, rng.integers(0, 201, 90))]
+    kv_lens[5] = 0
+    q_lens[11], kv_lens[11] = 100, 30   # leading blocks blind
+    inp = cases.mla_prefill_inputs(91, q_lens, kv_lens, 16, 512, 64, "bf16", cases.MLA_SM_SCALE)
+    i32 = lambda a: torch.from_numpy(a).cuda()  # noqa: E731
+    args = (dev(inp["q_nope"], "bf16"), dev(inp["q_pe"], "bf16"), dev(inp["ckv_cache"], "bf16"), dev(inp["kpe_cache"], "bf16"),
+            i32(inp["qo_indptr"]), i32(inp["kv_indptr"]), i32(inp["kv_indices"]), inp["sm_scale"])
+    assert 2 * (sum(-(-q // 8) for q in q_lens) + 90) >= 8 * 148 and sum(kv_lens) <= 320 * 90  # the host's rule
+    want, want_lse = orc.mla_paged_prefill(inp["q_nope"], inp["q_pe"], inp["ckv_cache"], inp["kpe_cache"], inp["qo_indptr"],
+                                           inp["kv_indptr"], inp["kv_indices"], inp["sm_scale"], dtype="bf16")
+    first = None
+    for _ in range(2):
+        out, lse = ops.mla_paged_prefill(*args, impl="tile")
+        ops.check_workspace(ops.workspace("mla_prefill", 0, "cuda"))
+        assert_close(host(out), want)
+        assert_lse_close(host(lse), want_lse)
+        if first is None:
+            first = out.clone()
+    assert torch.equal(first, out)
+
+
 @pytest.mark.parametrize("heads", [16, 64])
 def test_mla_prefill_short_and_ragged_key_windows(heads):
     """Key counts on both sides of every boundary the kernel treats specially: the 16-row rounds of the gather (rows

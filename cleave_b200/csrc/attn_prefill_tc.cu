@@ -78,7 +78,10 @@ struct Params {
 // MODE 2 (paged): q as in the ragged layout; K and V rows are gathered from page-size-1 caches through
 // kv_indices by four extra warps (16-byte cp.async into the swizzled tile, whole rows per warp instruction;
 // a thread's arrival on the full barrier fires when its copies have landed).
-template <typename T, int D, int MODE>
+// PERSIST = false is the one-item form for calls with no more items than SMs (a CTA finds its item, leaves at once if
+// there is nothing to do, and only then sets up tensor memory): the item ring, the counter and tensor memory taken
+// before the item is known cost a single small item about half a microsecond, which is most of what such a call is.
+template <typename T, int D, int MODE, bool PERSIST>
 __global__ void __launch_bounds__(MODE == 2 ? kThreadsPaged : kThreads, 1)
 attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                     const __grid_constant__ CUtensorMap tm_v, const Params p) {
@@ -153,24 +156,28 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     tma_prefetch_desc(&tm_k);
     tma_prefetch_desc(&tm_v);
   }
-  if (warp == 1) {
-    tmem_alloc(tmem_holder, 512);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_holder);
-  // The static launch is a dependent launch: the grid may have been scheduled while the preceding kernel of
-  // the stream drains. Up to here only shared and tensor memory were set up; global memory is touched after
-  // the wait.
-  pdl_launch_dependents();
-  pdl_wait();
+  uint32_t tmem_base = 0;
+  auto take_tensor_memory = [&]() {
+    if (warp == 1) {
+      tmem_alloc(tmem_holder, 512);
+      tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_holder);
+    // The static launch is a dependent launch: the grid may have been scheduled while the preceding kernel of
+    // the stream drains. Up to here only shared and tensor memory were set up (and, in the ragged layouts, whose
+    // launches do not carry the attribute, the request offsets read); the operands are touched after the wait.
+    pdl_launch_dependents();
+    pdl_wait();
+  };
+  if constexpr (PERSIST) take_tensor_memory();
 
   const int n_items = p.hq * p.q_tiles;
   int* ticket = p.status + 8;    // items beyond the first of every CTA are dealt by this counter
   int* finished = p.status + 9;  // CTAs that are through; the last one clears both words for the next launch
-  if (warp == kTicketWarp) {
+  if (PERSIST && warp == kTicketWarp) {
     // ================================================================ item numbers for the other warps
     // The first item of a CTA is its block index, which every warp knows; the others come from a counter, fetched
     // one item ahead and handed round through a two-slot ring. Items are numbered so that late query tiles, which
@@ -192,9 +199,9 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   int it = 0;       // items with keys this CTA has run, jt: their KV tiles (every role counts alike)
   int jt = 0;
   int st_a = 0, ph_a = 0, st_b = 0, ph_b = 0;  // ring positions of this warp's role
-  while (warp != kTicketWarp) {
+  while (!PERSIST || warp != kTicketWarp) {
     int item = static_cast<int>(blockIdx.x);
-    if (n_taken > 0) {  // the ring's entry number n_taken - 1
+    if (PERSIST && n_taken > 0) {  // the ring's entry number n_taken - 1
       const int s = (n_taken - 1) & 1;
       mbar_wait(&t_full[s], ((n_taken - 1) >> 1) & 1, p.status, kFaultFullBarrier);
       item = item_ring[s];
@@ -244,7 +251,10 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       }
     }
     (void)r;
-    if (!found) continue;  // the item count is an upper bound on the number of query tiles
+    if (!found) {  // the item count is an upper bound on the number of query tiles
+      if constexpr (PERSIST) continue;
+      else return;
+    }
     if constexpr (MODE == 2) {
       // the page table is caller data: a range that runs past its stated length is read as a shorter request
       if (p.n_idx > 0) {
@@ -279,8 +289,10 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     if (p.lse && !p.linear)
       for (int i = cw * 32 + lane; i < rows; i += (n_warps - 1) * 32)
         p.lse[RAGGED ? static_cast<size_t>(q_base + q0 + i) * p.hq + h : static_cast<size_t>(h) * sq + q0 + i] = -INFINITY;
-    continue;
+    if constexpr (PERSIST) continue;
+    else return;
   }
+  if constexpr (!PERSIST) take_tensor_memory();
 
   if (warp == 0) {
     // ================================================================ TMA producer: Q, then K tiles
@@ -598,6 +610,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     }
     if (half == 0 && live && p.lse && !p.linear) p.lse[orow] = l_run > 0.f ? m_ref + fast_log2(l_run) : -INFINITY;
   }
+    if constexpr (!PERSIST) break;
     jt += nt;
     ++it;
   }  // items
@@ -608,7 +621,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
-  if (tid == 0 && n_items > static_cast<int>(gridDim.x) && atomicAdd(finished, 1) == static_cast<int>(gridDim.x) - 1) {
+  if (PERSIST && tid == 0 && n_items > static_cast<int>(gridDim.x) && atomicAdd(finished, 1) == static_cast<int>(gridDim.x) - 1) {
     // every CTA has fetched its last item number: the counters are clear for the next launch
     atomicExch(ticket, 0);
     atomicExch(finished, 0);
@@ -708,10 +721,13 @@ int launch_prefill(const cb200_attn_prefill_args* a, cudaStream_t stream) {
         !encode_tensor_map(&tm_v, dt, 3, const_cast<void*>(a->v), dk, sk, box, sw))
       return CB200_ERR_CUDA;
   }
-  auto kern = attn_prefill_kernel<T, D, 0>;
+  // one CTA per SM at most, and then the CTAs deal the (head, query tile) items among themselves; with no more items
+  // than SMs every item has its own CTA and the kernel's one-item form runs
+  const long long n_items = static_cast<long long>(p.hq) * p.q_tiles;
+  const bool persist = n_items > sm_count();
+  auto kern = persist ? attn_prefill_kernel<T, D, 0, true> : attn_prefill_kernel<T, D, 0, false>;
   CB200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<D>::kSmemBytes));
-  // one CTA per SM at most; the CTAs deal the (head, query tile) items among themselves
-  const unsigned grid = static_cast<unsigned>(std::min<long long>(static_cast<long long>(p.hq) * p.q_tiles, sm_count()));
+  const unsigned grid = static_cast<unsigned>(std::min<long long>(n_items, sm_count()));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid, 1, 1);
   cfg.blockDim = dim3(kThreads, 1, 1);
@@ -778,13 +794,15 @@ int launch_prefill_ragged(const cb200_attn_prefill_ragged_args* a, cudaStream_t 
   // every request has at most ceil(q_len / 128) <= q_len / 128 + 1 query tiles: an upper bound on the items, which
   // the CTAs (one per SM at most) deal among themselves
   p.q_tiles = ceil_div(a->total_q, kBM) + a->batch;
-  const unsigned grid = static_cast<unsigned>(std::min<long long>(static_cast<long long>(p.hq) * p.q_tiles, sm_count()));
+  const long long n_items = static_cast<long long>(p.hq) * p.q_tiles;
+  const bool persist = n_items > sm_count();
+  const unsigned grid = static_cast<unsigned>(std::min<long long>(n_items, sm_count()));
   if (a->kv_indices) {
-    auto kern = attn_prefill_kernel<T, D, 2>;
+    auto kern = persist ? attn_prefill_kernel<T, D, 2, true> : attn_prefill_kernel<T, D, 2, false>;
     CB200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<D>::kSmemBytes));
     kern<<<grid, kThreadsPaged, Cfg<D>::kSmemBytes, stream>>>(tm_q, tm_k, tm_v, p);
   } else {
-    auto kern = attn_prefill_kernel<T, D, 1>;
+    auto kern = persist ? attn_prefill_kernel<T, D, 1, true> : attn_prefill_kernel<T, D, 1, false>;
     CB200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<D>::kSmemBytes));
     kern<<<grid, kThreads, Cfg<D>::kSmemBytes, stream>>>(tm_q, tm_k, tm_v, p);
   }

@@ -365,20 +365,27 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         if (j + 1 < nt) load_pages(j + 1, pg);  // one tile ahead: the index latency stays off the critical path
         const uint32_t kdst = smem_u32(k_smem + st_a * C::kTileBytes), vdst = smem_u32(v_smem + st_a * C::kTileBytes);
         mbar_wait(&k_empty[st_a], ph_a ^ 1, p.status, kFaultEmptyBarrier);
+        // rounds of rows that lie wholly past the request's last key are not fetched: zeros from the thread itself
+        // (masked as keys, and as values they meet P = 0), made visible to the MMA's proxy before the arrival
+        const int live_rounds = min(kRounds, (skv - j * kBN + kRowsPerRound - 1) / kRowsPerRound);
 #pragma unroll
         for (int r = 0; r < kRounds; ++r) {
           const int row = r * kRowsPerRound + r_in;
           const uint32_t o = (c >> 3) * C::kChunkBytes + row * 128 + (((c & 7) ^ (row & 7)) << 4);
-          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(kdst + o), "l"(kc + src[r]) : "memory");
+          if (r < live_rounds) asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(kdst + o), "l"(kc + src[r]) : "memory");
+          else asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(kdst + o), "r"(0u) : "memory");
         }
+        if (live_rounds < kRounds) fence_proxy_async_smem();
         asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&k_full[st_a])) : "memory");
         mbar_wait(&v_empty[st_a], ph_a ^ 1, p.status, kFaultEmptyBarrier);
 #pragma unroll
         for (int r = 0; r < kRounds; ++r) {
           const int row = r * kRowsPerRound + r_in;
           const uint32_t o = (c >> 3) * C::kChunkBytes + row * 128 + (((c & 7) ^ (row & 7)) << 4);
-          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(vdst + o), "l"(vc + src[r]) : "memory");
+          if (r < live_rounds) asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(vdst + o), "l"(vc + src[r]) : "memory");
+          else asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(vdst + o), "r"(0u) : "memory");
         }
+        if (live_rounds < kRounds) fence_proxy_async_smem();
         asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&v_full[st_a])) : "memory");
         if (++st_a == kStages) { st_a = 0; ph_a ^= 1; }
       }
@@ -470,18 +477,26 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       __syncwarp();
       if (lane == 0) mbar_arrive(q_empty);
     }
+    // the last key any row of this warp sees: a half tile of scores beyond it is neither read nor exponentiated (the
+    // tile of a short request, the diagonal tile of a query tile's first rows); tensor-memory loads are
+    // warp-collective, so the test is the warp's, not the row's
+    const int warp_limit = __reduce_max_sync(0xffffffffu, qrow < sq ? key_limit : -1);
     for (int j = 0; j < nt; ++j) {
       const int jj = jt + j, sb = jj & 1, pb = jj & 1;
+      const int k0 = j * kBN + half * 64;  // first key of this thread's scores
+      // (in the one-item form only: in the persistent form the test costs the long tile loops more than it saves)
+      const bool unseen = !PERSIST && !p.linear && k0 > warp_limit;
       mbar_wait(&s_full[sb], (jj >> 1) & 1, p.status, kFaultMmaBarrier);
       tc_fence_after();
       uint32_t r[2][32];
+      if (!unseen) {
 #pragma unroll
-      for (int q = 0; q < 2; ++q) tmem_ld_32x32(tmem_base + lane_field + kColS + sb * kBN + half * 64 + q * 32, r[q]);
-      tmem_ld_wait();
+        for (int q = 0; q < 2; ++q) tmem_ld_32x32(tmem_base + lane_field + kColS + sb * kBN + half * 64 + q * 32, r[q]);
+        tmem_ld_wait();
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_empty[sb]);
-      const int k0 = j * kBN + half * 64;  // first key of this thread's scores
       if (p.linear) {
         // no softmax: P = scale * S rounded to the storage type; keys past the end are zero rows of K
         mbar_wait(&p_empty[pb], ((jj >> 1) & 1) ^ 1, p.status, kFaultMmaBarrier);
@@ -503,7 +518,9 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         continue;
       }
       float mx = -INFINITY;
-      if (k0 + 63 <= key_limit) {  // this thread's half of the tile is visible to the row
+      if (unseen) {
+        // nothing to look at
+      } else if (k0 + 63 <= key_limit) {  // this thread's half of the tile is visible to the row
 #pragma unroll
         for (int q = 0; q < 2; ++q) {
 #pragma unroll
@@ -559,13 +576,18 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       float psum = 0.f;
       {
         uint32_t pk[32];
+        if (unseen) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int c = 2 * i;
-          const float p0 = fast_exp2(__uint_as_float(r[c >> 5][c & 31]) - m_ref);
-          const float p1 = fast_exp2(__uint_as_float(r[(c + 1) >> 5][(c + 1) & 31]) - m_ref);
-          psum += p0 + p1;
-          pk[i] = pack2<T>(p0, p1);
+          for (int i = 0; i < 32; ++i) pk[i] = 0u;
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int c = 2 * i;
+            const float p0 = fast_exp2(__uint_as_float(r[c >> 5][c & 31]) - m_ref);
+            const float p1 = fast_exp2(__uint_as_float(r[(c + 1) >> 5][(c + 1) & 31]) - m_ref);
+            psum += p0 + p1;
+            pk[i] = pack2<T>(p0, p1);
+          }
         }
         tmem_st_32x32(tmem_base + lane_field + kColP + pb * 64 + half * 32, pk);
       }

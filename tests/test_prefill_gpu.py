@@ -257,6 +257,44 @@ def test_items_dealt_among_persistent_ctas(paged):
         assert np.array_equal(out, runs[0][0]) and np.array_equal(lse, runs[0][1])
 
 
+@pytest.mark.parametrize("paged", [False, True])
+@pytest.mark.parametrize("kv_len", [1, 7, 8, 9, 33, 63, 64, 65, 127, 129])
+def test_single_small_item_key_boundaries(paged, kv_len):
+    """One request with a few query rows: the call has fewer items than SMs and takes the kernel's one-item form, in
+    which half tiles of scores no row of a warp sees are skipped and, in the paged layout, rounds of eight rows past the
+    last key are zero-filled in shared memory instead of fetched. Key counts on both sides of those boundaries; a launch
+    over NaN caches runs first, so stale shared memory would show."""
+    hq, hkv, d, dt = 32, 4, 128, "bf16"
+    q_len = min(3, kv_len)
+    rng = np.random.default_rng(kv_len)
+    q = cases.round_to(rng.standard_normal((q_len, hq, d), dtype=np.float32), dt)
+    qo = np.array([0, q_len], dtype=np.int32)
+    kv = np.array([0, kv_len], dtype=np.int32)
+    scale = d ** -0.5
+    if paged:
+        pool = kv_len + 5
+        kc = cases.round_to(rng.standard_normal((pool, 1, hkv, d), dtype=np.float32), dt)
+        vc = cases.round_to(rng.standard_normal((pool, 1, hkv, d), dtype=np.float32), dt)
+        idx = rng.permutation(pool)[:kv_len].astype(np.int32)
+        args = [dev(q, dt), dev(kc, dt), dev(vc, dt), torch.from_numpy(qo).cuda(), torch.from_numpy(kv).cuda(),
+                torch.from_numpy(idx).cuda(), scale]
+        call = _ops().gqa_paged_prefill
+        want, want_lse = orc.gqa_paged_prefill(q, kc, vc, qo, kv, idx, scale, dt)
+    else:
+        k = cases.round_to(rng.standard_normal((kv_len, hkv, d), dtype=np.float32), dt)
+        v = cases.round_to(rng.standard_normal((kv_len, hkv, d), dtype=np.float32), dt)
+        args = [dev(q, dt), dev(k, dt), dev(v, dt), torch.from_numpy(qo).cuda(), torch.from_numpy(kv).cuda(), scale]
+        call = _ops().gqa_ragged_prefill
+        want, want_lse = orc.gqa_ragged_prefill(q, k, v, qo, kv, scale, dt)
+    poisoned = list(args)
+    poisoned[1], poisoned[2] = torch.full_like(args[1], float("nan")), torch.full_like(args[2], float("nan"))
+    call(*poisoned)
+    out, lse = call(*args)
+    _check_ws()
+    assert_close(host(out), want)
+    assert_lse_close(host(lse), want_lse)
+
+
 def test_repeat_launches_are_bit_identical():
     inp = cases.attention_inputs(9, 8, 2, 300, 517, 128, "f16")
     q, k, v = (dev(inp[n], "f16") for n in ("q", "k", "v"))

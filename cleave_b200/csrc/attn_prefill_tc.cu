@@ -379,7 +379,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         mbar_wait(&k_empty[st_a], ph_a ^ 1, p.status, kFaultEmptyBarrier);
         // rounds of rows that lie wholly past the request's last key are not fetched: zeros from the thread itself
         // (masked as keys, and as values they meet P = 0), made visible to the MMA's proxy before the arrival
-        const int live_rounds = min(kRounds, (skv - j * kBN + kRowsPerRound - 1) / kRowsPerRound);
+        // (one-item form only: the test in the copy loop costs the long streams of the persistent form a tenth)
+        const int live_rounds = PERSIST ? kRounds : min(kRounds, (skv - j * kBN + kRowsPerRound - 1) / kRowsPerRound);
 #pragma unroll
         for (int r = 0; r < kRounds; ++r) {
           const int row = r * kRowsPerRound + r_in;

@@ -319,21 +319,30 @@ mla_prefill_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_const
         // request, or a request's last tile, is mostly such rows): zeros from the thread itself, which as keys are
         // masked and as values meet P = 0
         const int live_rounds = min(8, (kv_len - j * kBN + 15) >> 4);
-        bool zeroed = false;
+        if (live_rounds == 8) {  // the usual tile: every round holds keys, no test in the copy loop
 #pragma unroll
-        for (int rr = 0; rr < 8; ++rr) {
-          const int row = rr * 16 + r_in;
-          const uint32_t o = row * 128 + ((piece ^ (row & 7)) << 4);
-          if (rr < live_rounds) {
+          for (int rr = 0; rr < 8; ++rr) {
+            const int row = rr * 16 + r_in;
             const T* src = c < kCkv / 64 ? ckv + static_cast<long long>(pg[rr]) * kCkv + c * 64 + piece * 8
                                          : kpe + static_cast<long long>(pg[rr]) * kKpe + piece * 8;
+            const uint32_t o = row * 128 + ((piece ^ (row & 7)) << 4);
             asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + o), "l"(src) : "memory");
-          } else {
-            asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(dst + o), "r"(0u) : "memory");
-            zeroed = true;
           }
+        } else {
+#pragma unroll
+          for (int rr = 0; rr < 8; ++rr) {
+            const int row = rr * 16 + r_in;
+            const uint32_t o = row * 128 + ((piece ^ (row & 7)) << 4);
+            if (rr < live_rounds) {
+              const T* src = c < kCkv / 64 ? ckv + static_cast<long long>(pg[rr]) * kCkv + c * 64 + piece * 8
+                                           : kpe + static_cast<long long>(pg[rr]) * kKpe + piece * 8;
+              asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + o), "l"(src) : "memory");
+            } else {
+              asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(dst + o), "r"(0u) : "memory");
+            }
+          }
+          fence_proxy_async_smem();  // the MMA reads shared memory through the async proxy
         }
-        if (zeroed) fence_proxy_async_smem();  // the MMA reads shared memory through the async proxy
         asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&k_full[st])) : "memory");
         if (++st == kStages) { st = 0; ph ^= 1; }
       }

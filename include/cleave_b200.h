@@ -417,8 +417,10 @@ int cb200_lora(const cb200_lora_args* a, void* stream);
  * Replaces tests/graph/handwritten/expected_kernels/mla_paged_prefill_causal_h16_ckv512_kpe64_ps1.py
  * (python/cleave/dynamic/paging/builders/mla.py:393); argument order and meaning follow
  * python/cleave/dynamic/reference.py:324-365. A query-tile kernel on tcgen05: 128 / num_heads consecutive query
- * tokens times their heads are the 128 rows of every MMA, so num_heads must divide 128. The workspace holds the
- * status word only (cb200_workspace_status).
+ * tokens times their heads are the 128 rows of every MMA, so num_heads must divide 128. The workspace is the
+ * 256-byte header: the status word (cb200_workspace_status) and, for batches of many short prompts, which run on
+ * persistent CTAs, the counter their items are dealt from (it clears itself at the end of a launch; zero-fill the
+ * workspace once before first use, as every workspace).
  * ---------------------------------------------------------------------------------------- */
 typedef struct {
   const void* q_nope;    /* (total_q, num_heads, 512) */

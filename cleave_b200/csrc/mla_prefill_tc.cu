@@ -575,7 +575,7 @@ int launch(const cb200_mla_prefill_args* a, cudaStream_t stream) {
   // Many short items (batches of prompts of a few hundred tokens): persistent CTAs, whose producers run ahead into the
   // next item. Few items, or long ones (an item of a 2048-token prompt has up to sixteen KV tiles and is bound by what
   // the SM pulls from L2, not by the boundaries): one CTA per item.
-  const bool persist = 2 * blocks >= 8LL * sms && static_cast<long long>(a->num_kv_indices) <= 320LL * a->batch;
+  const bool persist = 2 * blocks >= 3LL * sms && static_cast<long long>(a->num_kv_indices) <= 320LL * a->batch;
   if (persist) {
     auto kern = mla_prefill_kernel<T, true>;
     CB200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));

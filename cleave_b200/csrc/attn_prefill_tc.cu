@@ -174,14 +174,21 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   };
   if constexpr (PERSIST) take_tensor_memory();
 
-  // The host's item count is an upper bound (one query tile more per request than total_q / 128). With at most 32
-  // requests their ranges are in this warp's registers and the exact number of query tiles is one warp sum away:
-  // no CTA then spends its first rounds on items that do not exist.
+  // The host's item count is an upper bound (one query tile more per request than total_q / 128); items that do not
+  // exist come first in the order, and every persistent CTA would spend its first rounds on them. The exact number
+  // of query tiles is a sum over the request ranges: the first 32 are in this warp's registers, the others cost
+  // a few independent loads per lane.
+  // (persistent form; in the one-item form a surplus CTA simply leaves, and numbering the items from the bound
+  // measured 0.35 us faster on a single-item call)
   int q_tiles = p.q_tiles;
-  if constexpr (RAGGED) {
-    // (persistent form; in the one-item form a surplus CTA simply leaves, and numbering the items from the bound
-    // measured 0.35 us faster on a single-item call)
-    if (PERSIST && p.batch <= 32) q_tiles = __reduce_add_sync(0xffffffffu, pre_hi > pre_lo ? ceil_div(pre_hi - pre_lo, kBM) : 0);
+  if constexpr (RAGGED && PERSIST) {
+    int mine = pre_hi > pre_lo ? ceil_div(pre_hi - pre_lo, kBM) : 0;
+#pragma unroll 4
+    for (int rr = 32 + lane; rr < p.batch; rr += 32) {
+      const int lo = __ldg(p.qo_indptr + rr), hi = __ldg(p.qo_indptr + rr + 1);
+      mine += hi > lo ? ceil_div(hi - lo, kBM) : 0;
+    }
+    q_tiles = __reduce_add_sync(0xffffffffu, mine);
   }
   const int n_items = p.hq * q_tiles;
   int* ticket = p.status + 8;    // items beyond the first of every CTA are dealt by this counter

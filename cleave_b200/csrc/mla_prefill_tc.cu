@@ -135,7 +135,20 @@ mla_prefill_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_const
   }
 
   uint32_t tmem_base = 0;
-  const int n_items = 2 * p.blocks;
+  // The host's block count is an upper bound (one more per request than total_q / qb); blocks that do not exist come
+  // first in the order. The persistent form takes the exact count: a sum over the request ranges, the first 32 from
+  // this warp's registers, the others a few independent loads per lane.
+  int n_blocks = p.blocks;
+  if constexpr (PERSIST) {
+    int mine = pre_hi > pre_lo ? ceil_div(pre_hi - pre_lo, p.qb) : 0;
+#pragma unroll 4
+    for (int rr = 32 + lane; rr < p.batch; rr += 32) {
+      const int lo_r = __ldg(p.qo_indptr + rr), hi_r = __ldg(p.qo_indptr + rr + 1);
+      mine += hi_r > lo_r ? ceil_div(hi_r - lo_r, p.qb) : 0;
+    }
+    n_blocks = __reduce_add_sync(0xffffffffu, mine);
+  }
+  const int n_items = 2 * n_blocks;
   int* ticket = p.status + 8;    // persistent form: items beyond the first of every CTA are dealt by this counter
   int* finished = p.status + 9;  // CTAs that are through; the last one clears both words for the next launch
   if constexpr (PERSIST) {
@@ -183,7 +196,7 @@ mla_prefill_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_const
   const int dh = item & 1;  // which half of the output columns
   // ---- which (request, query block) the item is: late blocks, which see the most keys, come first
   // (every warp searches the query offsets 32 requests at a time: lane = request, block counts scanned with shuffles)
-  int t = p.blocks - 1 - (item >> 1), r = 0, lo = 0;
+  int t = n_blocks - 1 - (item >> 1), r = 0, lo = 0;
   int q_len = 0, kv_base_found = 0, kv_end_found = 0;
   bool found = false;
   for (int r0 = 0; r0 < p.batch && !found; r0 += 32) {

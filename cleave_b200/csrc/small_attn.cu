@@ -213,10 +213,13 @@ __global__ void __launch_bounds__(kWarps * 32) small_gqa_kernel(const GqaParams 
               float sc[kKeys], bm = -INFINITY;
 #pragma unroll
               for (int u = 0; u < kKeys; ++u) {
-                float part = 0.f;
+                sc[u] = -INFINITY;
+                if (s0 + u < n_here) {  // uniform: slots past the block's end cost nothing (a row with one key is common)
+                  float part = 0.f;
 #pragma unroll
-                for (int i = 0; i < kPer; ++i) part = fmaf(q4[g][i], static_cast<float>(kk[u][i]), part);
-                sc[u] = s0 + u < n_here ? warp_sum_f(part) : -INFINITY;
+                  for (int i = 0; i < kPer; ++i) part = fmaf(q4[g][i], static_cast<float>(kk[u][i]), part);
+                  sc[u] = warp_sum_f(part);
+                }
                 bm = fmaxf(bm, sc[u]);
               }
               const float m_new = fmaxf(m_run[g], bm);  // finite: key s0 is visible
@@ -226,10 +229,12 @@ __global__ void __launch_bounds__(kWarps * 32) small_gqa_kernel(const GqaParams 
               for (int i = 0; i < kPer; ++i) o[g][i] *= alpha;
 #pragma unroll
               for (int u = 0; u < kKeys; ++u) {
-                const float pu = fast_exp2(sc[u] - m_new);  // 0 past the block's end
-                l_run[g] += pu;
+                if (s0 + u < n_here) {
+                  const float pu = fast_exp2(sc[u] - m_new);
+                  l_run[g] += pu;
 #pragma unroll
-                for (int i = 0; i < kPer; ++i) o[g][i] = fmaf(pu, static_cast<float>(vv[u][i]), o[g][i]);
+                  for (int i = 0; i < kPer; ++i) o[g][i] = fmaf(pu, static_cast<float>(vv[u][i]), o[g][i]);
+                }
               }
               m_run[g] = m_new;
             }
@@ -334,16 +339,19 @@ __global__ void __launch_bounds__(kWarps * 32) small_mla_kernel(const MlaParams 
             float sc[kKeys], bm = -INFINITY;
 #pragma unroll
             for (int u = 0; u < kKeys; ++u) {
-              float f[8], part;
-              const T* e = reinterpret_cast<const T*>(&pe[u]);
-              part = qp2[g][0] * static_cast<float>(e[0]) + qp2[g][1] * static_cast<float>(e[1]);
-              unpack8<T>(c0[u], f);
+              sc[u] = -INFINITY;
+              if (s0 + u < n_here) {  // uniform: slots past the block's end cost nothing
+                float f[8], part;
+                const T* e = reinterpret_cast<const T*>(&pe[u]);
+                part = qp2[g][0] * static_cast<float>(e[0]) + qp2[g][1] * static_cast<float>(e[1]);
+                unpack8<T>(c0[u], f);
 #pragma unroll
-              for (int i = 0; i < 8; ++i) part = fmaf(qn[g][i], f[i], part);
-              unpack8<T>(c1[u], f);
+                for (int i = 0; i < 8; ++i) part = fmaf(qn[g][i], f[i], part);
+                unpack8<T>(c1[u], f);
 #pragma unroll
-              for (int i = 0; i < 8; ++i) part = fmaf(qn[g][8 + i], f[i], part);
-              sc[u] = s0 + u < n_here ? warp_sum_f(part) : -INFINITY;
+                for (int i = 0; i < 8; ++i) part = fmaf(qn[g][8 + i], f[i], part);
+                sc[u] = warp_sum_f(part);
+              }
               bm = fmaxf(bm, sc[u]);
             }
             const float m_new = fmaxf(m_run[g], bm);
@@ -353,15 +361,17 @@ __global__ void __launch_bounds__(kWarps * 32) small_mla_kernel(const MlaParams 
             for (int i = 0; i < 16; ++i) o[g][i] *= alpha;
 #pragma unroll
             for (int u = 0; u < kKeys; ++u) {
-              const float pu = fast_exp2(sc[u] - m_new);
-              l_run[g] += pu;
-              float f[8];
-              unpack8<T>(c0[u], f);
+              if (s0 + u < n_here) {
+                const float pu = fast_exp2(sc[u] - m_new);
+                l_run[g] += pu;
+                float f[8];
+                unpack8<T>(c0[u], f);
 #pragma unroll
-              for (int i = 0; i < 8; ++i) o[g][i] = fmaf(pu, f[i], o[g][i]);
-              unpack8<T>(c1[u], f);
+                for (int i = 0; i < 8; ++i) o[g][i] = fmaf(pu, f[i], o[g][i]);
+                unpack8<T>(c1[u], f);
 #pragma unroll
-              for (int i = 0; i < 8; ++i) o[g][8 + i] = fmaf(pu, f[i], o[g][8 + i]);
+                for (int i = 0; i < 8; ++i) o[g][8 + i] = fmaf(pu, f[i], o[g][8 + i]);
+              }
             }
             m_run[g] = m_new;
           }

@@ -33,6 +33,62 @@ def test_partition_is_balanced_and_complete():
     assert all(lo % 8 == 0 for lo, _ in bounds)
 
 
+def _fused_host_logic(rank, world, x, w):
+    """The host side of the fused all-gather (sharding.gemm_n_sharded_fused) with stand-ins for the symmetric-memory
+    handle and the GEMM: which slice of the result the kernel is given, which peer addresses, one barrier per call;
+    and, when the GEMM answers "unsupported", the dense block and one scatter over all copies - remembered, so that
+    the refusal is not asked for again."""
+    from cleave_b200 import _lib, ops
+
+    n = w.shape[1]
+    lo, hi = sharding.n_shard(n, rank, world)
+
+    class Handle:
+        buffer_ptrs = [10_000 * (r + 1) for r in range(world)]
+        barriers = 0
+
+        def barrier(self):
+            Handle.barriers += 1
+
+    y = torch.zeros(x.shape[0], n)
+    calls = []
+
+    def gemm(x_, w_, out=None, peers=None):
+        calls.append((None if out is None else tuple(out.shape), peers))
+        res = R.rmsnorm_matmul(x_, w_, 1e-6)
+        if out is None:
+            return res
+        out.copy_(res)
+        return out
+
+    sharding._IN_KERNEL.clear()
+    got = sharding.gemm_n_sharded_fused(gemm, x, (w[:, lo:hi].contiguous(),), n, y, Handle())
+    want_peers = [Handle.buffer_ptrs[r] + lo * 4 for r in range(world) if r != rank]
+    ok = got is y and calls == [((x.shape[0], hi - lo), want_peers)] and Handle.barriers == 1
+    ok = ok and torch.allclose(y[:, lo:hi], R.rmsnorm_matmul(x, w, 1e-6)[:, lo:hi], rtol=1e-5, atol=1e-5)
+
+    def refusing(x_, w_, out=None, peers=None):
+        if peers is not None:
+            calls.append("refused")
+            raise _lib.Cb200Error(_lib.ERR_UNSUPPORTED, "unsupported")
+        calls.append("dense")
+        return R.rmsnorm_matmul(x_, w_, 1e-6)
+
+    scattered = []
+    real = ops.peer_scatter_cols
+    ops.peer_scatter_cols = lambda block, ld, dsts: scattered.append((tuple(block.shape), ld, list(dsts)))
+    try:
+        calls.clear()
+        sharding._IN_KERNEL.clear()
+        for _ in range(2):
+            sharding.gemm_n_sharded_fused(refusing, x, (w[:, lo:hi].contiguous(),), n, y, Handle())
+    finally:
+        ops.peer_scatter_cols = real
+    ok = ok and calls == ["refused", "dense", "dense"] and Handle.barriers == 3
+    ok = ok and scattered == [((x.shape[0], hi - lo), n, [y.data_ptr() + lo * 4] + want_peers)] * 2
+    return bool(ok)
+
+
 def _worker(rank, world, port, q):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -66,6 +122,7 @@ def _worker(rank, world, port, q):
         lo, hi = sharding.n_shard(104, rank, world)
         y = sharding.gemm_n_sharded(lambda x_, w_: R.rmsnorm_matmul(x_, w_, 1e-6), x, [w[:, lo:hi].contiguous()], 104)
         ok2 = torch.allclose(y, R.rmsnorm_matmul(x, w, 1e-6), rtol=1e-5, atol=1e-5)
+        ok2 = ok2 and _fused_host_logic(rank, world, x, w)
         q.put((rank, bool(ok1), bool(ok2)))
     finally:
         dist.destroy_process_group()

@@ -365,3 +365,40 @@ def test_ctypes_structs_match_the_c_header(tmp_path):
         assert got[(cname, "size")] == ctypes.sizeof(cls), cname
         for field, _ in cls._fields_:
             assert got[(cname, field)] == getattr(cls, field).offset, (cname, field)
+
+
+def test_peer_fields_are_checked_before_any_device_call():
+    """The multi-GPU fields of cb200_gemm_args and cb200_peer_scatter_cols are caller data: counts, pitches and
+    alignments are refused with a status before the library touches CUDA (so this runs without a GPU)."""
+    import ctypes as C
+
+    from cleave_b200 import _lib
+
+    L = _lib.lib()
+
+    def gemm(**kw):
+        a = _lib.GemmArgs()
+        a.m, a.n, a.k, a.op, a.dtype = 512, 512, 512, 0, _lib.F16
+        for k, v in kw.items():
+            setattr(a, k, v)
+        return L.cb200_gemm(C.byref(a), None)
+
+    assert gemm(n_peers=8) == 1 and gemm(n_peers=-1) == 1          # at most seven peer copies
+    assert gemm(ldy=504) == 1 and gemm(ldy=516) == 1               # the pitch covers the slice and is a multiple of 8
+    a = _lib.GemmArgs()
+    a.m, a.n, a.k, a.op, a.dtype, a.n_peers = 512, 512, 512, 0, _lib.F16, 2
+    a.y_peers[0] = 4096
+    assert L.cb200_gemm(C.byref(a), None) == 1                     # a peer pointer is missing
+    a.y_peers[1] = 4104
+    assert L.cb200_gemm(C.byref(a), None) == 1                     # ... or not 16-byte aligned
+
+    dsts = (C.c_void_p * 2)(4096, 8192)
+    scatter = lambda src, m, n, ld, d, nd, dt: L.cb200_peer_scatter_cols(src, m, n, ld, d, nd, dt, None)  # noqa: E731
+    assert scatter(None, 8, 64, 128, dsts, 2, _lib.F16) == 1
+    assert scatter(4096, 8, 60, 128, dsts, 2, _lib.F16) == 1       # 16-byte pieces
+    assert scatter(4096, 8, 64, 56, dsts, 2, _lib.F16) == 1        # pitch shorter than the block
+    assert scatter(4096, 8, 64, 128, dsts, 9, _lib.F16) == 1
+    assert scatter(4096, 8, 64, 128, dsts, 2, 7) == 2              # dtype
+    assert scatter(4100, 8, 64, 128, dsts, 2, _lib.F16) == 3       # alignment
+    bad = (C.c_void_p * 2)(4096, 8200)
+    assert scatter(4096, 8, 64, 128, bad, 2, _lib.F16) == 1

@@ -464,9 +464,9 @@ double gemm_pair_estimate_us(const cb200_gemm_args* a, int sms, int* ks_out) {
     const int cap = pair_capacity(swiglu, f16, ks);
     if (cap <= 0) continue;
     // a K split runs one tile per cluster, each cluster paying its own set-up, parking and reduce: it pays when the
-    // tiles are too few to fill the machine, not over several waves (4096 x 3584 x 4096 ran in 184 us with the split
+    // tiles are too few to fill the machine (up to two waves of clusters), not over many waves (4096 x 3584 x 4096 ran in 184 us with the split
     // the model picked for its wave count, against 118 us as whole tiles)
-    if (ks > 1 && tiles > cap) continue;
+    if (ks > 1 && tiles > 2LL * cap) continue;
     const long long waves = (tiles + cap - 1) / cap;
     double t = static_cast<double>(waves) * ceil_div(kblocks, ks) * 0.44 + 2.0;
     if (ks > 1) t += 1.0 + (128.0 / ks) * 256.0 * 4.0 * (ks - 1) / 25000.0;
